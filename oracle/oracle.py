@@ -1,0 +1,439 @@
+"""CPU oracle bindings and reference-shaped compositions.  TEST INFRASTRUCTURE ONLY.
+
+Loads ``oracle/liboracle.so`` (the float64 C restatement of the reference's
+pure-Dart eager engine, see ``oracle.c``) and stacks its ops the way the
+reference's layers do, on a tape that mirrors ``Tensor``/``Node``/``backward``
+(lib/autogradEngine/tensor.dart:5-75).  Nothing in the product package imports
+this module; only tests, the smoke check and the benchmark's CPU-baseline leg do.
+
+Parity status: pinned for matMul forward by the reference's all-ones check
+(lib/gpu_benching.dart:34-37,60); otherwise PARITY UNPINNED (the reference has no
+golden vectors and cannot be executed here), guarded by an independent
+torch-float64 autograd model and finite differences in the test-suite.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIBS = {}
+
+_dp = C.POINTER(C.c_double)
+
+
+def _p(a):
+    if a is None:
+        return None
+    assert a.dtype == np.float64 and a.flags.c_contiguous
+    return a.ctypes.data_as(_dp)
+
+
+def build():
+    """Compile both oracle variants with the committed Makefile."""
+    subprocess.run(["make", "-s", "-C", _HERE], check=True)
+
+
+def lib(omp: bool = False):
+    key = "omp" if omp else "st"
+    if key not in _LIBS:
+        path = os.path.join(_HERE, "liboracle_omp.so" if omp else "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.orc_mse_fwd.restype = C.c_double
+        L.orc_softmax_xent.restype = C.c_double
+        L.orc_threads.restype = C.c_int
+        _LIBS[key] = L
+    return _LIBS[key]
+
+
+class Ops:
+    """numpy-facing wrappers around the C functions (float64, row-major)."""
+
+    def __init__(self, omp: bool = False):
+        self.L = lib(omp)
+
+    def threads(self):
+        return int(self.L.orc_threads())
+
+    def matmul_fwd(self, A, B):
+        M, N = A.shape
+        P = B.shape[1]
+        out = np.empty((M, P))
+        self.L.orc_matmul_fwd(_p(A), _p(B), _p(out), M, N, P)
+        return out
+
+    def matmul_bwd(self, A, B, dC, dA, dB):
+        M, N = A.shape
+        P = B.shape[1]
+        self.L.orc_matmul_bwd(_p(A), _p(B), _p(dC), _p(dA), _p(dB), M, N, P)
+
+    def matvec_fwd(self, Mx, v):
+        y = np.empty(Mx.shape[0])
+        self.L.orc_matvec_fwd(_p(Mx), _p(v), _p(y), Mx.shape[0], Mx.shape[1])
+        return y
+
+    def matvec_bwd(self, Mx, v, dy, dM, dv):
+        self.L.orc_matvec_bwd(_p(Mx), _p(v), _p(dy), _p(dM), _p(dv), Mx.shape[0], Mx.shape[1])
+
+    def unary_fwd(self, name, x):
+        y = np.empty_like(x)
+        getattr(self.L, f"orc_{name}_fwd")(_p(x), _p(y), C.c_int64(x.size))
+        return y
+
+    def unary_bwd(self, name, saved, dy, dx):
+        getattr(self.L, f"orc_{name}_bwd")(_p(saved), _p(dy), _p(dx), C.c_int64(dy.size))
+
+    def softmax_fwd(self, x, causal_period=0):
+        y = np.empty_like(x)
+        self.L.orc_softmax_rows_fwd(_p(x), _p(y), x.shape[0], x.shape[1], causal_period)
+        return y
+
+    def softmax_bwd(self, y, dy, dx):
+        self.L.orc_softmax_rows_bwd(_p(y), _p(dy), _p(dx), y.shape[0], y.shape[1])
+
+    def layernorm_fwd(self, x, gamma, beta, eps=1e-5):
+        y = np.empty_like(x)
+        xhat = np.empty_like(x)
+        var = np.empty(x.shape[0])
+        self.L.orc_layernorm_fwd(_p(x), _p(gamma), _p(beta), _p(y), _p(xhat), _p(var),
+                                 x.shape[0], x.shape[1], C.c_double(eps))
+        return y, xhat, var
+
+    def layernorm_bwd(self, dy, gamma, xhat, var, dx, dgamma, dbeta, eps=1e-5):
+        self.L.orc_layernorm_bwd(_p(dy), _p(gamma), _p(xhat), _p(var), _p(dx), _p(dgamma),
+                                 _p(dbeta), dy.shape[0], dy.shape[1], C.c_double(eps))
+
+    def mse_fwd(self, p, t):
+        return float(self.L.orc_mse_fwd(_p(p), _p(t), C.c_int64(p.size)))
+
+    def mse_bwd(self, p, t, dp, upstream=1.0):
+        self.L.orc_mse_bwd(_p(p), _p(t), _p(dp), C.c_int64(p.size), C.c_double(upstream))
+
+    def softmax_xent(self, z, labels, dz, inv_count):
+        labels = np.ascontiguousarray(labels, dtype=np.int32)
+        return float(self.L.orc_softmax_xent(_p(z), labels.ctypes.data_as(C.POINTER(C.c_int32)),
+                                             _p(dz), z.shape[0], z.shape[1], C.c_double(inv_count)))
+
+    def sgd_step(self, w, g, lr):
+        self.L.orc_sgd_step(_p(w), _p(g), C.c_int64(w.size), C.c_double(lr))
+
+    def adam_step(self, w, g, m, v, lr, t, b1=0.9, b2=0.999, eps=1e-8):
+        self.L.orc_adam_step(_p(w), _p(g), _p(m), _p(v), C.c_int64(w.size), C.c_double(lr),
+                             C.c_double(b1), C.c_double(b2), C.c_double(eps), int(t))
+
+    def embedding_fwd(self, table, ids):
+        ids = np.ascontiguousarray(ids, dtype=np.float64)
+        out = np.empty((ids.size, table.shape[1]))
+        self.L.orc_embedding_fwd(_p(table), _p(ids), _p(out), ids.size, table.shape[1])
+        return out
+
+    def embedding_bwd(self, dout, ids, dtable):
+        ids = np.ascontiguousarray(ids, dtype=np.float64)
+        self.L.orc_embedding_bwd(_p(dout), _p(ids), _p(dtable), ids.size, dtable.shape[1])
+
+    def positional_table(self, max_len, d_model):
+        pe = np.empty((max_len, d_model))
+        self.L.orc_positional_table(_p(pe), max_len, d_model)
+        return pe
+
+    def lstm_fwd_bwd(self, W, b, x, target, backward=True):
+        """W [4,H,H+I] (f,i,c~,o; columns [h|x]), b [4,H], x [B,T,I], target [B,H]."""
+        B, T, I = x.shape
+        H = W.shape[1]
+        h_last = np.empty((B, H))
+        loss = C.c_double(0)
+        dW = np.zeros_like(W)
+        db = np.zeros_like(b)
+        self.L.orc_lstm_fwd_bwd(_p(W), _p(b), _p(x), _p(target), _p(h_last), C.byref(loss),
+                                _p(dW), _p(db), B, T, I, H, 1 if backward else 0)
+        return h_last, loss.value, dW, db
+
+
+# --------------------------------------------------------------------------- tape
+
+
+class T:
+    """Mirror of the reference Tensor: value, zero-initialised grad, creator node
+    (lib/autogradEngine/tensor.dart:21-41)."""
+
+    def __init__(self, value):
+        self.value = np.array(value, dtype=np.float64, order="C")
+        self.grad = np.zeros_like(self.value)
+        self.inputs = ()
+        self.backward_fn = None
+
+    def backward(self):
+        """Depth-first topological sort over creators, seed gradient 1.0, closures in
+        reverse order (tensor.dart:43-75)."""
+        topo, seen = [], set()
+        stack = [(self, False)]
+        while stack:  # iterative form of the recursive visit at :54-66
+            node, done = stack.pop()
+            if done:
+                topo.append(node)
+                continue
+            if id(node) in seen:
+                continue
+            seen.add(id(node))
+            stack.append((node, True))
+            for i in reversed(node.inputs):
+                if id(i) not in seen:
+                    stack.append((i, False))
+        self.grad = np.ones_like(self.value)
+        for node in reversed(topo):
+            if node.backward_fn is not None:
+                node.backward_fn()
+
+
+def _node(out, inputs, fn):
+    out.inputs = tuple(inputs)
+    out.backward_fn = fn
+    return out
+
+
+class Engine:
+    """Reference ops on the tape; each method follows the cited reference function."""
+
+    def __init__(self, omp: bool = False):
+        self.ops = Ops(omp)
+
+    # tensor.dart:867-947
+    def matMul(self, a, b):
+        out = T(self.ops.matmul_fwd(a.value, b.value))
+        return _node(out, [a, b], lambda: self.ops.matmul_bwd(a.value, b.value, out.grad, a.grad, b.grad))
+
+    # tensor.dart:679-709
+    def addMatrixAndVector(self, m, v):
+        out = T(m.value + v.value[None, :])
+
+        def bw():
+            m.grad += out.grad
+            for i in range(out.grad.shape[0]):  # row order, as the reference's i-outer loop
+                v.grad += out.grad[i]
+        return _node(out, [m, v], bw)
+
+    # tensor.dart:651-677
+    def addMatrix(self, a, b):
+        out = T(a.value + b.value)
+
+        def bw():
+            a.grad += out.grad
+            b.grad += out.grad
+        return _node(out, [a, b], bw)
+
+    def _unary(self, name, x, saved_is_output):
+        out = T(self.ops.unary_fwd(name, x.value))
+        saved = out.value if saved_is_output else x.value
+        return _node(out, [x], lambda: self.ops.unary_bwd(name, saved, out.grad, x.grad))
+
+    def reluMatrix(self, x):      # tensor.dart:1013-1038
+        return self._unary("relu", x, False)
+
+    def sigmoidMatrix(self, x):   # tensor.dart:1123-1151
+        return self._unary("sigmoid", x, True)
+
+    def tanhMatrix(self, x):      # tensor.dart:1178-1209
+        return self._unary("tanh", x, True)
+
+    def geluMatrix(self, x):      # EXTENSION
+        return self._unary("gelu", x, False)
+
+    # tensor.dart:1075-1101
+    def scaleMatrix(self, x, s):
+        out = T(x.value * s)
+
+        def bw():
+            x.grad += out.grad * s
+        return _node(out, [x], bw)
+
+    # tensor.dart:1211-1236
+    def transpose(self, x):
+        out = T(x.value.T.copy())
+
+        def bw():
+            x.grad += out.grad.T
+        return _node(out, [x], bw)
+
+    # tensor.dart:739-763
+    def concatenateMatricesByColumn(self, parts):
+        out = T(np.concatenate([p.value for p in parts], axis=1))
+
+        def bw():
+            c = 0
+            for p in parts:
+                w = p.value.shape[1]
+                p.grad += out.grad[:, c:c + w]
+                c += w
+        return _node(out, parts, bw)
+
+    # lib/activationFunctions/softmax.dart:68-115 (+ causal EXTENSION)
+    def softmaxMatrix(self, x, causal=False):
+        out = T(self.ops.softmax_fwd(x.value, x.value.shape[0] if causal else 0))
+        return _node(out, [x], lambda: self.ops.softmax_bwd(out.value, out.grad, x.grad))
+
+    # lib/transformer/layerNormalization.dart:137-202
+    def layerNorm(self, x, gamma, beta, eps=1e-5):
+        y, xhat, var = self.ops.layernorm_fwd(x.value, gamma.value, beta.value, eps)
+        out = T(y)
+        return _node(out, [x, gamma, beta], lambda: self.ops.layernorm_bwd(
+            out.grad, gamma.value, xhat, var, x.grad, gamma.grad, beta.grad, eps))
+
+    # tensor.dart:982-1011
+    def mseMatrix(self, p, t):
+        out = T(np.array(self.ops.mse_fwd(p.value, t.value)))
+        return _node(out, [p], lambda: self.ops.mse_bwd(p.value, t.value, p.grad, float(out.grad)))
+
+    # EXTENSION
+    def softmaxCrossEntropy(self, z, labels, inv_count):
+        out = T(np.array(self.ops.softmax_xent(z.value, labels, None, inv_count)))
+
+        def bw():
+            dz = np.zeros_like(z.value)
+            self.ops.softmax_xent(z.value, labels, dz, inv_count)
+            z.grad += float(out.grad) * dz
+        return _node(out, [z], bw)
+
+    # lib/transformer/embeddingLayer.dart:47-67
+    def embedding(self, table, ids):
+        out = T(self.ops.embedding_fwd(table.value, ids))
+        return _node(out, [table], lambda: self.ops.embedding_bwd(out.grad, ids, table.grad))
+
+    # ---------------------------------------------------------------- layers
+
+    def dense_matrix(self, x, W, b, act=None):
+        """DenseLayerMatrix.forward lib/layertypes/denseLayer.dart:116-125: act(X.W + b),
+        W stored [in x out] (:96-104)."""
+        z = self.addMatrixAndVector(self.matMul(x, W), b)
+        if act is None:
+            return z
+        return {"relu": self.reluMatrix, "sigmoid": self.sigmoidMatrix, "tanh": self.tanhMatrix,
+                "gelu": self.geluMatrix}[act](z)
+
+    def single_head(self, x, Wq, Wk, Wv, causal):
+        """SingleHeadAttention.forward lib/layertypes/singleHeadAttentionLayer.dart:70-89."""
+        Q, K, V = self.matMul(x, Wq), self.matMul(x, Wk), self.matMul(x, Wv)
+        scores = self.matMul(Q, self.transpose(K))
+        scaled = self.scaleMatrix(scores, 1 / math.sqrt(Wq.value.shape[1]))
+        P = self.softmaxMatrix(scaled, causal)
+        return self.matMul(P, V)
+
+    def multi_head(self, x, heads, Wo, causal):
+        """MultiHeadAttention.forward lib/transformer/multiHeadAttentionLayer.dart:72-84:
+        heads serially, column concat, then .Wo (no biases anywhere)."""
+        outs = [self.single_head(x, *h, causal) for h in heads]
+        return self.matMul(self.concatenateMatricesByColumn(outs), Wo)
+
+    def encoder_block(self, x, p, causal):
+        """TransformerEncoderBlock.forward lib/transformer/transformerEncodingLayer.dart:58-70
+        (post-LN; FFN = Dense(dff, ReLU) -> Dense(dModel), :48-51)."""
+        attn = self.multi_head(x, p["heads"], p["Wo"], causal)
+        h = self.layerNorm(self.addMatrix(x, attn), p["g1"], p["be1"])
+        f = self.dense_matrix(self.dense_matrix(h, p["W1"], p["b1"], "relu"), p["W2"], p["b2"])
+        return self.layerNorm(self.addMatrix(h, f), p["g2"], p["be2"])
+
+
+def block_params_to_T(p):
+    """Wrap a dict of numpy arrays (heads: list of (Wq,Wk,Wv)) into tape tensors."""
+    out = {k: T(v) for k, v in p.items() if k != "heads"}
+    out["heads"] = [tuple(T(w) for w in h) for h in p["heads"]]
+    return out
+
+
+def block_param_list(pt):
+    lst = []
+    for h in pt["heads"]:
+        lst += list(h)
+    return lst + [pt[k] for k in ("Wo", "g1", "be1", "W1", "b1", "W2", "b2", "g2", "be2")]
+
+
+# ------------------------------------------------------------------ config drivers
+
+
+def mlp_step(X, labels, params, lr=0.01, omp=False):
+    """Config 1: DenseLayerMatrix(128,ReLU) -> (64,ReLU) -> (10) -> softmax-CE (mean over
+    the batch) -> backward -> SGD (lib/nets/snet.dart:74-85 order: forward, loss,
+    backward, step).  params = [W1,b1,W2,b2,W3,b3] float64."""
+    E = Engine(omp)
+    P = [T(p) for p in params]
+    x = T(X)
+    h1 = E.dense_matrix(x, P[0], P[1], "relu")
+    h2 = E.dense_matrix(h1, P[2], P[3], "relu")
+    logits = E.dense_matrix(h2, P[4], P[5])
+    loss = E.softmaxCrossEntropy(logits, labels, 1.0 / X.shape[0])
+    loss.backward()
+    grads = [p.grad.copy() for p in P]
+    new = []
+    for p in P:
+        w = p.value.copy()
+        E.ops.sgd_step(w, p.grad, lr)
+        new.append(w)
+    return {"logits": logits.value, "loss": float(loss.value), "grads": grads, "params": new}
+
+
+def gemm_gelu_fwd_bwd(A, B, bias, dC, omp=False):
+    """Config 2: Z=A.B+bias, C=GELU(Z); dZ=dC*GELU'(Z); dA=dZ.B^T; dB=A^T.dZ; dbias."""
+    E = Engine(omp)
+    a, b, bi = T(A), T(B), T(bias)
+    z = E.addMatrixAndVector(E.matMul(a, b), bi)
+    c = E.geluMatrix(z)
+    c.grad = np.ascontiguousarray(dC, dtype=np.float64)
+    for node in (c, z):
+        node.backward_fn()
+    mm = z.inputs[0]
+    mm.backward_fn()
+    return {"Z": z.value, "C": c.value, "dZ": z.grad, "dA": a.grad, "dB": b.grad, "dbias": bi.grad}
+
+
+def encoder_block_fwd_bwd(xs, params, targets, causal=True, omp=False):
+    """Config 3: one post-LN block over a batch of sequences.  Each sequence is one
+    reference forward/backward (mseMatrix against its target); gradients accumulate
+    across sequences and the reported loss is the sum."""
+    E = Engine(omp)
+    pt = block_params_to_T(params)
+    ys, loss, dxs = [], 0.0, []
+    for x_np, t_np in zip(xs, targets):
+        x = T(x_np)
+        y = E.encoder_block(x, pt, causal)
+        l = E.mseMatrix(y, T(t_np))
+        l.backward()
+        ys.append(y.value)
+        dxs.append(x.grad)
+        loss += float(l.value)
+    return {"y": np.stack(ys), "loss": loss, "dx": np.stack(dxs),
+            "grads": [p.grad for p in block_param_list(pt)]}
+
+
+def lm_forward_backward(ids, labels, params, n_global_tokens, causal=True, omp=False):
+    """Config 5 (one data-parallel shard): Embedding -> +PositionalEncoding -> blocks ->
+    DenseLayerMatrix(vocab) -> softmax-CE normalised by the GLOBAL token count.
+    ids/labels [B,S] ints.  Returns loss contribution and gradients in parameter order
+    [emb, (block params)*, Whead, bhead]."""
+    E = Engine(omp)
+    emb = T(params["emb"])
+    blocks = [block_params_to_T(b) for b in params["blocks"]]
+    Wh, bh = T(params["Whead"]), T(params["bhead"])
+    S = ids.shape[1]
+    pe = T(E.ops.positional_table(S, emb.value.shape[1]))
+    loss = 0.0
+    logits_all = []
+    for b in range(ids.shape[0]):
+        h = E.addMatrix(E.embedding(emb, ids[b].astype(np.float64)), pe)
+        for bp in blocks:
+            h = E.encoder_block(h, bp, causal)
+        logits = E.dense_matrix(h, Wh, bh)
+        l = E.softmaxCrossEntropy(logits, labels[b], 1.0 / n_global_tokens)
+        l.backward()
+        loss += float(l.value)
+        logits_all.append(logits.value)
+    plist = [emb]
+    for bp in blocks:
+        plist += block_param_list(bp)
+    plist += [Wh, bh]
+    return {"loss": loss, "logits": np.stack(logits_all), "grads": [p.grad for p in plist],
+            "params": [p.value for p in plist]}
