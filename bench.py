@@ -1,0 +1,293 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: dense forward + both backward contractions with the fused
+bias+GELU epilogue (M=N=K=8192, fp32 storage, TF32 tensor-core products).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size S]
+
+Prints ONE JSON line.  `value` is whole-job TFLOP/s on algorithmic flops (6*M*N*K per step) with
+the operands resident in HBM; `e2e` is the same step driven from pinned host buffers (copies in
+the timed region); `roofline` is the tensor-core GEMM kernel against the measured tensor peak;
+`cpu_baseline` is the float64 CPU oracle on a bounded sample.  With N > 1 every rank runs the
+same step on its own GPU (no data-path collective; weak scaling) and the line also carries the
+data-parallel training step, which does all-reduce gradients over NCCL.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SWEEP = [(512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
+         (16384, 4096, 1024)]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        out, _ = self.proc.communicate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        # the first sample may predate the load; keep the upper half as "under load"
+        med = statistics.median(sm) if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(M, N, K, seed=1):
+    """Config 2 operands: entries N(0,1)/sqrt(K), seed 1 (tensor ids 0..3)."""
+    from flutter_ml_b200 import synth
+    s = 1.0 / np.sqrt(K)
+    return (synth.normal(seed, 0, (M, K), s), synth.normal(seed, 1, (K, N), s), synth.normal(seed, 2, (N,), s),
+            synth.normal(seed, 3, (M, N), s))
+
+
+def cpu_step(M, N, K, omp):
+    """One fwd+bwd of config 2 on the CPU oracle; returns seconds."""
+    from oracle import oracle
+    A, B, bias, dC = (np.ascontiguousarray(x, dtype=np.float64) for x in make_inputs(M, N, K))
+    t0 = time.perf_counter()
+    oracle.gemm_gelu_fwd_bwd(A, B, bias, dC, omp=omp)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank):
+    """The reference's CPU algorithm (float64 scalar loops; the Dart original cannot run here, so
+    this is the oracle port) with all host threads, on a bounded sample of the same workload."""
+    if rank != 0:
+        return
+    from oracle import oracle
+    oracle.build()
+    S = args.ref_size
+    cores = oracle.Ops(True).threads()
+    for _ in range(min(args.warmup, 1)):
+        cpu_step(S, S, S, True)
+    times = [cpu_step(S, S, S, True) for _ in range(args.steps)]
+    total = sum(times)
+    tf = 6.0 * S ** 3 * args.steps / total / 1e12
+    line = {"impl": "reference", "metric": "gemm_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * total / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": "dense fwd+bwd (bias+GELU), fp32 inputs, M=N=K=8192", "seed": 1},
+            "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                             "sample": f"M=N=K={S} fwd+bwd per step (6*{S}^3 flop), OpenMP over {cores} threads"},
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_sweep(ctx, reps=5):
+    """fwd+bwd TFLOP/s for every size of the config-2 sweep (operands are re-used buffers)."""
+    from flutter_ml_b200 import ops
+    out = []
+    for (M, N, K) in SWEEP:
+        e = ctx.empty
+        A, B, bias, dC = e(M, K), e(K, N), e(N), e(M, N)
+        for a in (A, B, bias, dC):
+            ctx.zero(a)
+        C, Z, dZ, dA, dB, db = e(M, N), e(M, N), e(M, N), e(M, K), e(K, N), e(N)
+
+        def step():
+            ops.dense_forward(ctx, A, B, bias, "gelu", M, N, K, C, Z)
+            ctx.zero(db)
+            ops.dense_backward(ctx, A, B, Z, dC, "gelu", M, N, K, dZ, dA, dB, db)
+        for _ in range(3):
+            step()
+        ctx.sync()
+        ctx.timer_start()
+        for _ in range(reps):
+            step()
+        ms = ctx.timer_stop_ms() / reps
+        out.append({"M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(6.0 * M * N * K / ms / 1e9, 1)})
+        for a in (A, B, bias, dC, C, Z, dZ, dA, dB, db):
+            a.free()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=8192, help="M=N=K of the timed step")
+    ap.add_argument("--ref-size", type=int, default=1024, help="M=N=K of one CPU sample step")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-train", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    from flutter_ml_b200 import _lib, ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    peaks = measured_peaks()
+    ctx = _lib.Context(device=local_rank, precision=_lib.PREC_TF32)
+    M = N = K = args.size
+    flops_step = 6.0 * M * N * K
+    host = ops.DenseFwdBwdHost(ctx, M, N, K, act="gelu")
+    for name, arr in zip(("A", "B", "bias", "dC"), make_inputs(M, N, K)):
+        host.h_in[name][...] = arr
+    host()  # uploads the operands once; they stay resident for the device-timed loop
+
+    # ---- device-resident loop: per-launch events around the three GEMMs of the first steps
+    for _ in range(args.warmup):
+        host.compute()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = ctx.launches
+    n_ev_steps = min(args.steps, 10)
+    ctx.timer_start()
+    for s in range(args.steps):
+        if s < n_ev_steps:
+            c = ctx
+            c.event_record(6 * s + 0)
+            ops.dense_forward(c, host.A, host.B, host.bias, "gelu", M, N, K, host.C, host.Z)
+            c.event_record(6 * s + 1)
+            c.zero(host.dbias)
+            c.call("fml_act_bwd", _lib.ACT_GELU, host.Z, host.dC, host.dZ, M, N, 0, host.dbias, launches=2)
+            c.event_record(6 * s + 2)
+            c.gemm(host.dZ, host.B, host.dA, M, K, N, transB=True)
+            c.event_record(6 * s + 3)
+            c.gemm(host.A, host.dZ, host.dB, K, N, M, transA=True)
+            c.event_record(6 * s + 4)
+        else:
+            host.compute()
+    ms_total = ctx.timer_stop_ms()
+    barrier()
+    clocks = sampler.stop()
+    launches = ctx.launches - launches0
+    ms_total = max_over_ranks(ms_total)
+    ms_step = ms_total / args.steps
+    value = world * flops_step / ms_step / 1e9
+    gemm_ms = []
+    for s in range(n_ev_steps):
+        gemm_ms += [ctx.event_elapsed_ms(6 * s, 6 * s + 1), ctx.event_elapsed_ms(6 * s + 2, 6 * s + 3),
+                    ctx.event_elapsed_ms(6 * s + 3, 6 * s + 4)]
+    gemm_avg = sum(gemm_ms) / len(gemm_ms)
+    achieved = 2.0 * M * N * K / gemm_avg / 1e9
+    long_run = ms_total > 1000.0
+    tf32_peak = (peaks["bf16_sustained"] if long_run else peaks["bf16_burst"]) / 2.0
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel", "achieved": round(achieved, 1), "peak": round(tf32_peak, 1),
+                "unit": "TFLOP/s", "frac": round(achieved / tf32_peak, 4), "traffic": None,
+                "peak_source": f"{peaks['source']}: MEASURED_PEAKS bf16 {'sustained' if long_run else 'burst'} / 2 "
+                               "(dense TF32 runs at half the bf16 rate; no TF32 figure is measured by the driver)",
+                "per_gemm_ms": {"fwd": round(statistics.mean(gemm_ms[0::3]), 4), "dA": round(statistics.mean(gemm_ms[1::3]), 4),
+                                "dW": round(statistics.mean(gemm_ms[2::3]), 4)}}
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region
+    e2e_steps = max(2, min(args.steps, 5))
+    host()
+    barrier()
+    ctx.timer_start()
+    for _ in range(e2e_steps):
+        host()
+    e2e_ms = ctx.timer_stop_ms()
+    barrier()
+    e2e_ms = max_over_ranks(max(e2e_ms, 0.0)) / e2e_steps
+    e2e = {"value": round(world * flops_step / e2e_ms / 1e9, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 3),
+           "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes}
+
+    line = {"metric": "gemm_fwd_bwd_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": f"dense fwd+bwd (bias+GELU epilogue, dZ+dbias, dA, dW), fp32, M=N=K={M}", "seed": 1,
+                       "l2": "operands (3 x %d MB) exceed the 126 MB L2; no flush needed" % (M * K * 4 // 2 ** 20),
+                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU"},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "frac_of_tf32_peak": round(value / world / tf32_peak, 4)}
+
+    if rank == 0 and not args.no_sweep:
+        line["sweep"] = time_sweep(ctx)
+    if rank == 0 and not args.no_cpu:
+        from oracle import oracle
+        oracle.build()
+        S = args.ref_size
+        sec = cpu_step(S, S, S, False)
+        line["cpu_baseline"] = {"value": 6.0 * S ** 3 / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+                                "sample": f"M=N=K={S} fwd+bwd once ({sec:.1f} s), float64 scalar loops, 1 thread"}
+    if not args.no_train:
+        try:
+            from flutter_ml_b200 import train_bench
+            line["train"] = train_bench.run(ctx, rank, world, barrier, max_over_ranks)
+        except ImportError:
+            pass
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,92 @@
+// Shared declarations of the library's translation units.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <map>
+#include <string>
+#include <tuple>
+#include <unordered_set>
+#include <vector>
+
+#include "fml.h"
+
+struct fml_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int precision = FML_PREC_TF32;
+  cudaStream_t stream = nullptr;
+  bool own_stream = true;
+  std::string last_error;
+  int* d_status = nullptr;  // device word written by kernels whose bounded waits expire
+  // scratch arena (3xTF32 operand splits)
+  char* ws = nullptr;
+  size_t ws_bytes = 0;
+  std::unordered_set<void*> allocs;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaEvent_t ev_pool[64] = {};
+  int last_gemm_path = 0;
+  // tensor-map cache: key -> encoded CUtensorMap
+  std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int>, CUtensorMap> tmaps;
+  // NCCL (loaded lazily with dlopen)
+  void* nccl_comm = nullptr;
+  int dp_rank = 0, dp_world = 1;
+};
+
+void fml_set_global_error(const std::string& msg);
+int32_t fml_fail(fml_ctx* ctx, int32_t code, const std::string& msg);
+int32_t fml_ensure_workspace(fml_ctx* ctx, size_t bytes);
+
+#define FML_CUDA(ctx, call)                                                              \
+  do {                                                                                   \
+    cudaError_t e__ = (call);                                                            \
+    if (e__ != cudaSuccess)                                                              \
+      return fml_fail((ctx), FML_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__)); \
+  } while (0)
+
+#define FML_REQUIRE(ctx, cond, msg) \
+  do {                              \
+    if (!(cond)) return fml_fail((ctx), FML_ERR_INVALID, (msg)); \
+  } while (0)
+
+#define FML_LAUNCH_CHECK(ctx, what)                                                     \
+  do {                                                                                  \
+    cudaError_t e__ = cudaGetLastError();                                               \
+    if (e__ != cudaSuccess)                                                             \
+      return fml_fail((ctx), FML_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e__)); \
+  } while (0)
+
+// internal entry points between translation units
+int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision);
+int32_t fml_gemm_simt(fml_ctx* ctx, const fml_gemm_desc* d);
+bool fml_gemm_tc_eligible(const fml_gemm_desc* d);
+
+__device__ __forceinline__ float fml_act_apply(int act, float v) {
+  switch (act) {
+    case FML_ACT_RELU: return v > 0.f ? v : 0.f;
+    case FML_ACT_SIGMOID: return 1.f / (1.f + expf(-v));
+    case FML_ACT_TANH: {
+      // same algebra as the reference: (e^{2x}-1)/(e^{2x}+1), 1 when e^{2x} overflows
+      float e2x = expf(2.f * v);
+      return isinf(e2x) ? 1.f : (e2x - 1.f) / (e2x + 1.f);
+    }
+    case FML_ACT_GELU: return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+    default: return v;
+  }
+}
+// derivative from the saved tensor: x for RELU/GELU, y for SIGMOID/TANH
+__device__ __forceinline__ float fml_act_grad(int act, float s) {
+  switch (act) {
+    case FML_ACT_RELU: return s > 0.f ? 1.f : 0.f;
+    case FML_ACT_SIGMOID: return s * (1.f - s);
+    case FML_ACT_TANH: return 1.f - s * s;
+    case FML_ACT_GELU: {
+      float cdf = 0.5f * (1.f + erff(s * 0.70710678118654752440f));
+      float pdf = 0.39894228040143267794f * expf(-0.5f * s * s);
+      return cdf + s * pdf;
+    }
+    default: return 1.f;
+  }
+}

@@ -1,0 +1,345 @@
+// Context, memory, timing, dispatch of fml_gemm and the two legacy symbols.
+#include <algorithm>
+#include <chrono>
+#include <mutex>
+
+#include "common.cuh"
+
+static std::string g_last_error;
+static std::mutex g_mu;
+
+void fml_set_global_error(const std::string& msg) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_last_error = msg;
+}
+int32_t fml_fail(fml_ctx* ctx, int32_t code, const std::string& msg) {
+  if (ctx) ctx->last_error = msg;
+  fml_set_global_error(msg);
+  return code;
+}
+
+int32_t fml_ensure_workspace(fml_ctx* ctx, size_t bytes) {
+  if (bytes <= ctx->ws_bytes) return FML_OK;
+  if (ctx->ws) {
+    FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaFree(ctx->ws);
+    ctx->ws = nullptr;
+    ctx->ws_bytes = 0;
+  }
+  size_t want = std::max(bytes, (size_t)(64u << 20));
+  cudaError_t e = cudaMalloc(&ctx->ws, want);
+  if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_OOM, std::string("workspace cudaMalloc: ") + cudaGetErrorString(e));
+  ctx->ws_bytes = want;
+  return FML_OK;
+}
+
+__global__ void f64_to_f32_kernel(const double* __restrict__ in, float* __restrict__ out, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = (float)in[i];
+}
+__global__ void f32_to_f64_kernel(const float* __restrict__ in, double* __restrict__ out, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = (double)in[i];
+}
+
+extern "C" {
+
+int32_t fml_device_count(int32_t* count) {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    *count = 0;
+    return fml_fail(nullptr, FML_ERR_NO_DEVICE, std::string("cudaGetDeviceCount: ") + cudaGetErrorString(e));
+  }
+  *count = n;
+  return FML_OK;
+}
+
+int32_t fml_device_name(int32_t device, char* buf, int32_t buf_len) {
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) return fml_fail(nullptr, FML_ERR_NO_DEVICE, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+  snprintf(buf, buf_len, "%s", prop.name);
+  return FML_OK;
+}
+
+int32_t fml_init(const fml_config* cfg, fml_ctx** out) {
+  if (!out) return fml_fail(nullptr, FML_ERR_INVALID, "fml_init: out is NULL");
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0)
+    return fml_fail(nullptr, FML_ERR_NO_DEVICE, "fml_init: no CUDA device is visible; this library has no CPU path");
+  const int dev = cfg ? cfg->device : 0;
+  if (dev < 0 || dev >= n) return fml_fail(nullptr, FML_ERR_INVALID, "fml_init: device ordinal out of range");
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fml_fail(nullptr, FML_ERR_CUDA, "cudaGetDeviceProperties failed");
+  if (prop.major != 10)
+    return fml_fail(nullptr, FML_ERR_NO_DEVICE, std::string("fml_init: kernels are built for sm_100a only; device is ") + prop.name);
+  fml_ctx* ctx = new fml_ctx();
+  ctx->device = dev;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->precision = cfg ? cfg->precision : FML_PREC_TF32;
+  FML_CUDA(ctx, cudaSetDevice(dev));
+  FML_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+  {
+    cudaMemPool_t pool;
+    FML_CUDA(ctx, cudaDeviceGetDefaultMemPool(&pool, dev));
+    uint64_t keep = UINT64_MAX;
+    FML_CUDA(ctx, cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+  }
+  FML_CUDA(ctx, cudaMalloc(&ctx->d_status, 256));
+  FML_CUDA(ctx, cudaMemset(ctx->d_status, 0, 256));
+  FML_CUDA(ctx, cudaEventCreate(&ctx->ev0));
+  FML_CUDA(ctx, cudaEventCreate(&ctx->ev1));
+  if (cfg && cfg->workspace_bytes > 0) {
+    int32_t rc = fml_ensure_workspace(ctx, (size_t)cfg->workspace_bytes);
+    if (rc) return rc;
+  }
+  *out = ctx;
+  return FML_OK;
+}
+
+int32_t fml_shutdown(fml_ctx* ctx) {
+  if (!ctx) return FML_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  fml_dp_shutdown(ctx);
+  for (void* p : ctx->allocs) cudaFreeAsync(p, ctx->stream);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->ws) cudaFree(ctx->ws);
+  cudaFree(ctx->d_status);
+  cudaEventDestroy(ctx->ev0);
+  cudaEventDestroy(ctx->ev1);
+  for (cudaEvent_t e : ctx->ev_pool)
+    if (e) cudaEventDestroy(e);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return FML_OK;
+}
+
+const char* fml_last_error(fml_ctx* ctx) {
+  if (ctx) return ctx->last_error.c_str();
+  static thread_local std::string copy;
+  std::lock_guard<std::mutex> lk(g_mu);
+  copy = g_last_error;
+  return copy.c_str();
+}
+
+int32_t fml_sm_count(fml_ctx* ctx, int32_t* count) {
+  *count = ctx->sm_count;
+  return FML_OK;
+}
+
+int32_t fml_set_stream(fml_ctx* ctx, void* s) {
+  FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+  ctx->stream = reinterpret_cast<cudaStream_t>(s);
+  ctx->own_stream = false;
+  return FML_OK;
+}
+
+int32_t fml_sync(fml_ctx* ctx) {
+  FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return FML_OK;
+}
+
+int32_t fml_device_status(fml_ctx* ctx, int32_t* code) {
+  int v = 0;
+  FML_CUDA(ctx, cudaMemcpyAsync(&v, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  *code = v;
+  if (v != 0) {
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    return fml_fail(ctx, FML_ERR_TIMEOUT, "a device-side bounded wait expired (role code " + std::to_string(v) + ")");
+  }
+  return FML_OK;
+}
+
+int32_t fml_alloc(fml_ctx* ctx, int64_t n, float** out) {
+  FML_REQUIRE(ctx, n >= 0 && out, "fml_alloc: bad arguments");
+  void* p = nullptr;
+  // stream-ordered pool: a block freed on the context's stream is reused by later calls on the
+  // same stream without a device synchronisation (training loops allocate per op)
+  cudaError_t e = cudaMallocAsync(&p, (size_t)std::max<int64_t>(n, 1) * sizeof(float), ctx->stream);
+  if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_OOM, std::string("fml_alloc: ") + cudaGetErrorString(e));
+  ctx->allocs.insert(p);
+  *out = reinterpret_cast<float*>(p);
+  return FML_OK;
+}
+
+int32_t fml_free(fml_ctx* ctx, float* p) {
+  if (!p) return FML_OK;
+  auto it = ctx->allocs.find(p);
+  FML_REQUIRE(ctx, it != ctx->allocs.end(), "fml_free: pointer was not allocated by this context");
+  ctx->allocs.erase(it);
+  // The pool keeps the range mapped (release threshold = max), so cached tensor maps that
+  // point into it stay valid for the next owner of the same address.
+  FML_CUDA(ctx, cudaFreeAsync(p, ctx->stream));
+  return FML_OK;
+}
+
+int32_t fml_zero(fml_ctx* ctx, float* p, int64_t n) {
+  FML_CUDA(ctx, cudaMemsetAsync(p, 0, (size_t)n * sizeof(float), ctx->stream));
+  return FML_OK;
+}
+
+int32_t fml_upload_f32(fml_ctx* ctx, float* dst, const float* host, int64_t n) {
+  FML_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+  return FML_OK;
+}
+int32_t fml_upload_i32(fml_ctx* ctx, int32_t* dst, const int32_t* host, int64_t n) {
+  FML_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+  return FML_OK;
+}
+int32_t fml_upload_f64(fml_ctx* ctx, float* dst, const double* host, int64_t n) {
+  // stage the doubles in the scratch arena and narrow on the device
+  int32_t rc = fml_ensure_workspace(ctx, (size_t)n * 8);
+  if (rc) return rc;
+  FML_CUDA(ctx, cudaMemcpyAsync(ctx->ws, host, (size_t)n * 8, cudaMemcpyHostToDevice, ctx->stream));
+  f64_to_f32_kernel<<<(int)std::min<int64_t>((n + 255) / 256, 4096), 256, 0, ctx->stream>>>(
+      reinterpret_cast<const double*>(ctx->ws), dst, n);
+  FML_LAUNCH_CHECK(ctx, "f64_to_f32_kernel");
+  FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return FML_OK;
+}
+int32_t fml_download_f32(fml_ctx* ctx, float* host, const float* src, int64_t n) {
+  FML_CUDA(ctx, cudaMemcpyAsync(host, src, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return FML_OK;
+}
+int32_t fml_download_f64(fml_ctx* ctx, double* host, const float* src, int64_t n) {
+  int32_t rc = fml_ensure_workspace(ctx, (size_t)n * 8);
+  if (rc) return rc;
+  f32_to_f64_kernel<<<(int)std::min<int64_t>((n + 255) / 256, 4096), 256, 0, ctx->stream>>>(
+      src, reinterpret_cast<double*>(ctx->ws), n);
+  FML_LAUNCH_CHECK(ctx, "f32_to_f64_kernel");
+  FML_CUDA(ctx, cudaMemcpyAsync(host, ctx->ws, (size_t)n * 8, cudaMemcpyDeviceToHost, ctx->stream));
+  FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return FML_OK;
+}
+int32_t fml_copy(fml_ctx* ctx, float* dst, const float* src, int64_t n) {
+  FML_CUDA(ctx, cudaMemcpyAsync(dst, src, (size_t)n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  return FML_OK;
+}
+
+int32_t fml_timer_start(fml_ctx* ctx) {
+  FML_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+  return FML_OK;
+}
+int32_t fml_timer_stop_ms(fml_ctx* ctx, float* ms) {
+  FML_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+  FML_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
+  FML_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+  return FML_OK;
+}
+
+int32_t fml_event_record(fml_ctx* ctx, int32_t slot) {
+  FML_REQUIRE(ctx, slot >= 0 && slot < 64, "fml_event_record: slot out of range");
+  if (!ctx->ev_pool[slot]) FML_CUDA(ctx, cudaEventCreate(&ctx->ev_pool[slot]));
+  FML_CUDA(ctx, cudaEventRecord(ctx->ev_pool[slot], ctx->stream));
+  return FML_OK;
+}
+int32_t fml_event_elapsed_ms(fml_ctx* ctx, int32_t a, int32_t b, float* ms) {
+  FML_REQUIRE(ctx, a >= 0 && a < 64 && b >= 0 && b < 64 && ctx->ev_pool[a] && ctx->ev_pool[b],
+              "fml_event_elapsed_ms: slot not recorded");
+  FML_CUDA(ctx, cudaEventSynchronize(ctx->ev_pool[b]));
+  FML_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_pool[a], ctx->ev_pool[b]));
+  return FML_OK;
+}
+
+int32_t fml_host_alloc(fml_ctx* ctx, int64_t bytes, void** out) {
+  FML_REQUIRE(ctx, bytes > 0 && out, "fml_host_alloc: bad arguments");
+  cudaError_t e = cudaHostAlloc(out, (size_t)bytes, cudaHostAllocDefault);
+  if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_OOM, std::string("fml_host_alloc: ") + cudaGetErrorString(e));
+  return FML_OK;
+}
+int32_t fml_host_free(fml_ctx* ctx, void* p) {
+  if (p) FML_CUDA(ctx, cudaFreeHost(p));
+  return FML_OK;
+}
+
+int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d) {
+  FML_REQUIRE(ctx, d && d->A && d->B && d->C, "fml_gemm: NULL operand");
+  FML_REQUIRE(ctx, d->M > 0 && d->N > 0 && d->K > 0, "fml_gemm: M, N, K must be positive");
+  FML_REQUIRE(ctx, d->beta == 0.f || d->beta == 1.f, "fml_gemm: beta must be 0 or 1");
+  FML_REQUIRE(ctx, d->lda >= (d->transA ? d->M : d->K), "fml_gemm: lda smaller than a row of A");
+  FML_REQUIRE(ctx, d->ldb >= (d->transB ? d->K : d->N), "fml_gemm: ldb smaller than a row of B");
+  FML_REQUIRE(ctx, d->ldc >= d->N, "fml_gemm: ldc smaller than N");
+  FML_REQUIRE(ctx, d->act >= FML_ACT_NONE && d->act <= FML_ACT_GELU, "fml_gemm: unknown activation");
+  int prec = d->precision < 0 ? ctx->precision : d->precision;
+  FML_REQUIRE(ctx, prec >= FML_PREC_TF32 && prec <= FML_PREC_FP32, "fml_gemm: unknown precision");
+  if (prec != FML_PREC_FP32 && fml_gemm_tc_eligible(d)) return fml_gemm_tc(ctx, d, prec);
+  return fml_gemm_simt(ctx, d);
+}
+
+int32_t fml_gemm_last_path(fml_ctx* ctx, int32_t* path) {
+  *path = ctx->last_gemm_path;
+  return FML_OK;
+}
+
+// ------------------------------------------------------------------- legacy symbols
+static fml_ctx* g_legacy = nullptr;
+static float *g_la = nullptr, *g_lb = nullptr, *g_lc = nullptr;
+static int64_t g_lcap[3] = {0, 0, 0};
+
+static int32_t legacy_ctx() {
+  if (g_legacy) return FML_OK;
+  fml_config cfg = {0, FML_PREC_TF32, 0};
+  return fml_init(&cfg, &g_legacy);
+}
+static int32_t legacy_buf(float** p, int64_t* cap, int64_t n) {
+  if (n <= *cap) return FML_OK;
+  if (*p) fml_free(g_legacy, *p);
+  *p = nullptr;
+  *cap = 0;
+  int32_t rc = fml_alloc(g_legacy, n, p);
+  if (rc == FML_OK) *cap = n;
+  return rc;
+}
+
+void multiplyMatrices(float* h_a, float* h_b, float* h_c, int32_t m, int32_t k, int32_t n) {
+  if (legacy_ctx()) return;
+  if (!h_a || !h_b || !h_c || m <= 0 || k <= 0 || n <= 0) {
+    fml_fail(g_legacy, FML_ERR_INVALID, "multiplyMatrices: bad arguments");
+    return;
+  }
+  // device buffers are cached between calls; rows are padded to a multiple of 4 floats so the
+  // tensor-core path always applies
+  const int64_t ldk = (k + 3) & ~3, ldn = (n + 3) & ~3;
+  if (legacy_buf(&g_la, &g_lcap[0], (int64_t)m * ldk) || legacy_buf(&g_lb, &g_lcap[1], (int64_t)k * ldn) ||
+      legacy_buf(&g_lc, &g_lcap[2], (int64_t)m * ldn))
+    return;
+  cudaStream_t st = g_legacy->stream;
+  if (cudaMemcpy2DAsync(g_la, ldk * 4, h_a, (size_t)k * 4, (size_t)k * 4, m, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+      cudaMemcpy2DAsync(g_lb, ldn * 4, h_b, (size_t)n * 4, (size_t)n * 4, k, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+    fml_fail(g_legacy, FML_ERR_CUDA, "multiplyMatrices: host to device copy failed");
+    return;
+  }
+  fml_gemm_desc d = {};
+  d.M = m; d.N = n; d.K = k;
+  d.lda = ldk; d.ldb = ldn; d.ldc = ldn;
+  d.A = g_la; d.B = g_lb; d.C = g_lc;
+  d.alpha = 1.f; d.batch1 = d.batch2 = 1; d.precision = -1;
+  if (fml_gemm(g_legacy, &d)) return;
+  if (cudaMemcpy2DAsync(h_c, (size_t)n * 4, g_lc, ldn * 4, (size_t)n * 4, m, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess)
+    fml_fail(g_legacy, FML_ERR_CUDA, "multiplyMatrices: device to host copy failed");
+}
+
+int32_t benchtest(void) {
+  // Same search as the reference (cuda_lib/kernel.cu:57-99): grow the square size by 100 until one
+  // round trip exceeds 1000 ms; host buffers are zero-filled here (the reference leaves them
+  // uninitialised, :69-71).  Capped so the host buffers stay below 3 x 1.6 GB.
+  int last_ok = 0;
+  for (int size = 100; size <= 20000; size += 100) {
+    std::vector<float> a((size_t)size * size, 0.f), b((size_t)size * size, 0.f), c((size_t)size * size, 0.f);
+    auto t0 = std::chrono::steady_clock::now();
+    multiplyMatrices(a.data(), b.data(), c.data(), size, size, size);
+    auto ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (ms > 1000.0) break;
+    last_ok = size;
+  }
+  return last_ok;
+}
+
+}  // extern "C"

@@ -1,0 +1,560 @@
+// Dense contraction on the Blackwell tensor cores: tcgen05.mma kind::tf32 with the
+// accumulator in TMEM, operands staged in shared memory by TMA, a warp-specialised
+// producer / MMA-issuer / epilogue pipeline and a persistent tile loop.
+//
+// One CTA = 192 threads:
+//   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor per stage)
+//   warp 1      MMA issuer     (one lane issues tcgen05.mma; the warp owns TMEM alloc/free)
+//   warps 2..5  epilogue       (tcgen05.ld -> bias/activation -> global stores); warp w reads
+//                              the TMEM lane quarter w % 4
+// Tile: 128 (M) x BN (N, 64/128/256) x 32 (K, one 128-byte swizzle row of fp32).
+// TMEM holds two accumulators (columns [0,256) and [256,512)) so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// Operand layouts.  op(A)[M x K] and op(B)[K x N] can each be stored K-contiguous
+// ("K-major": A not transposed, B transposed) or M/N-contiguous ("MN-major").  Both are
+// consumed in place, through the major-ness bits of the instruction descriptor:
+//   K-major : one TMA box {32 k, rows} lands as rows x 128 B, 128B-swizzled;
+//             descriptor SBO = 1024 B (8 rows), k-step of 8 elements = +32 B.
+//   MN-major: boxes {32 m, 32 k} land as 32 k-rows x 128 B with the 32-byte-chunk swizzle
+//             (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B <-> UMMA SWIZZLE_128B_BASE32B, 4-row atoms);
+//             block j of 32 m at +j*4096 B; descriptor LBO = 4096 B (next 32 m), SBO = 512 B
+//             (next 4 k), k-step of 8 elements = +1024 B.
+// So the reference's materialised transposes (tensor.dart:877-884, 908-915, 927-934) never exist.
+//
+// 3xTF32: a pre-pass writes hi = rna_tf32(x) and lo = x - hi for both operands into the
+// context's scratch arena; the K loop then runs three segments (lo.hi, hi.lo, hi.hi) into the
+// same accumulator, small terms first.
+//
+// Every wait on an mbarrier is bounded (2 s of %globaltimer); on expiry the kernel records a
+// code in *status, raises a CTA-wide abort flag, and all roles fall through to the common
+// tail, which frees TMEM.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 4;    // 16 KiB
+constexpr int B_STAGE_BYTES = 256 * BK * 4;   // 32 KiB (sized for BN = 256)
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+struct TcParams {
+  int M, N, K;
+  int tiles_m, tiles_n, nb1, nb2;
+  int BN;
+  int a_mn, b_mn;  // 1 = MN-major operand
+  int nseg;        // 1 (TF32) or 3 (3xTF32)
+  int kblocks;
+  float* C;
+  float* Z;
+  const float* bias;
+  long long ldc, sC1, sC2;
+  int act;
+  float alpha, beta;
+  int* status;
+  uint32_t idesc;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false if the CTA is aborting or the limit expired.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading
+// byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in [46,48), layout
+// type in [61,64): 2 = SWIZZLE_128B (16-byte chunks, 8-row atom) for K-major operands, 1 =
+// SWIZZLE_128B_BASE32B (32-byte chunks, 4-row atom), the only layout the tensor core accepts
+// for MN-major 32-bit operands.  Tiles are 1024-byte aligned, so the base-offset field is 0.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+
+// Tile index -> (batch, m-tile, n-tile); tiles are walked in groups of 16 m-tiles so that the
+// CTAs of one wave share A and B panels in L2.
+__device__ __forceinline__ void tile_coords(const TcParams& p, int t, int& b, int& tm, int& tn) {
+  const int per_batch = p.tiles_m * p.tiles_n;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  const int GROUP = 16;
+  int group_sz = GROUP * p.tiles_n;
+  int g = r / group_sz;
+  int first_m = g * GROUP;
+  int gm = min(GROUP, p.tiles_m - first_m);
+  int rr = r - g * group_sz;
+  tm = first_m + rr % gm;
+  tn = rr / gm;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmAlo, const __grid_constant__ CUtensorMap tmBlo,
+               const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+  // barrier layout (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2], then tmem slot + abort flag
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n * p.nb1 * p.nb2;
+  const int kiters = p.kblocks * p.nseg;
+  const uint32_t b_stage_bytes = (uint32_t)p.BN * BK * 4;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(p, t, b, tm, tn);
+        const int b1 = b % p.nb1, b2 = b / p.nb1;
+        const int m0 = tm * BM, n0 = tn * p.BN;
+        for (int it = 0; it < kiters; it++) {
+          ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1);
+          if (!ok) break;
+          const int seg = it / p.kblocks;
+          const int k0 = (it - seg * p.kblocks) * BK;
+          // 3xTF32 segments: (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi); TF32: (A,B)
+          const CUtensorMap* ta = (p.nseg == 3 && seg == 0) ? &tmAlo : &tmA;
+          const CUtensorMap* tb = (p.nseg == 3 && seg == 1) ? &tmBlo : &tmB;
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), A_STAGE_BYTES + b_stage_bytes);
+          if (p.a_mn) {
+            for (int j = 0; j < BM / 32; j++) tma_load_4d(sa + j * 4096, ta, full_bar(s), m0 + 32 * j, k0, b1, b2);
+          } else {
+            tma_load_4d(sa, ta, full_bar(s), k0, m0, b1, b2);
+          }
+          if (p.b_mn) {
+            for (int j = 0; j < p.BN / 32; j++) tma_load_4d(sb + j * 4096, tb, full_bar(s), n0 + 32 * j, k0, b1, b2);
+          } else {
+            tma_load_4d(sb, tb, full_bar(s), k0, n0, b1, b2);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      const uint32_t a_lbo = p.a_mn ? 4096u : 16u, b_lbo = p.b_mn ? 4096u : 16u;
+      const uint32_t a_kstep = p.a_mn ? (1024u >> 4) : (32u >> 4);
+      const uint32_t b_kstep = p.b_mn ? (1024u >> 4) : (32u >> 4);
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * 256u;
+        for (int it = 0; it < kiters; it++) {
+          ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 3);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, a_lbo, p.a_mn ? 512u : 1024u, p.a_mn ? 1u : 2u);
+          const uint64_t bdesc = make_smem_desc(sb, b_lbo, p.b_mn ? 512u : 1024u, p.b_mn ? 1u : 2u);
+#pragma unroll
+          for (int k = 0; k < BK / 8; k++) {
+            umma_tf32(tmem_d, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), p.idesc,
+                      (it > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));  // accumulator complete
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                        ((p.sC1 & 3) == 0) && ((p.sC2 & 3) == 0) &&
+                        (p.Z == nullptr || (reinterpret_cast<uintptr_t>(p.Z) & 15) == 0) &&
+                        (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int b, tm, tn;
+      tile_coords(p, t, b, tm, tn);
+      const int b1 = b % p.nb1, b2 = b / p.nb1;
+      const int m0 = tm * BM, n0 = tn * p.BN;
+      ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, 4);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const long long boff = (long long)b1 * p.sC1 + (long long)b2 * p.sC2 + (long long)row * p.ldc;
+      float* crow = p.C + boff;
+      float* zrow = p.Z ? p.Z + boff : nullptr;
+      const int nchunks = p.BN / 32;
+      for (int c = 0; c < nchunks; c++) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c * 32u, v);
+        tmem_ld_wait();
+        if (row < p.M) {
+          const bool full = (col0 + 32 <= p.N);
+          if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o;
+              float* op = reinterpret_cast<float*>(&o);
+              float4 bz = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.bias) bz = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+              const float* bp = reinterpret_cast<const float*>(&bz);
+#pragma unroll
+              for (int e = 0; e < 4; e++) op[e] = __uint_as_float(v[j + e]) * p.alpha + bp[e];
+              if (zrow) *reinterpret_cast<float4*>(zrow + col0 + j) = o;
+#pragma unroll
+              for (int e = 0; e < 4; e++) op[e] = fml_act_apply(p.act, op[e]);
+              if (p.beta != 0.f) {
+                float4 old = *reinterpret_cast<const float4*>(crow + col0 + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(crow + col0 + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              const int col = col0 + j;
+              if (col < p.N) {
+                float o = __uint_as_float(v[j]) * p.alpha + (p.bias ? p.bias[col] : 0.f);
+                if (zrow) zrow[col] = o;
+                o = fml_act_apply(p.act, o);
+                if (p.beta != 0.f) o += crow[col];
+                crow[col] = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  // common tail: everyone arrives, then the allocating warp frees TMEM
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// hi = round-to-nearest tf32 of x, lo = x - hi (exact in fp32); generic 4-level strided source,
+// compact destination [b2][b1][rows][ldd].
+__global__ void split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo,
+                                  int rows, int cols, long long ld, int nb1, int nb2, long long s1, long long s2,
+                                  int ldd) {
+  const long long total = (long long)nb2 * nb1 * rows * ldd;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    int c = (int)(i % ldd);
+    long long r = i / ldd;
+    int row = (int)(r % rows);
+    long long bb = r / rows;
+    int b1 = (int)(bb % nb1), b2 = (int)(bb / nb1);
+    float x = 0.f;
+    if (c < cols) x = src[(long long)b2 * s2 + (long long)b1 * s1 + (long long)row * ld + c];
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    float hf = __uint_as_float(h);
+    hi[i] = hf;
+    lo[i] = x - hf;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Rank-4 map {cols, rows, nb1, nb2} over a row-major matrix with two batch levels.
+int32_t make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, int64_t ld, int64_t nb1, int64_t nb2,
+                  int64_t s1, int64_t s2, int box_c, int box_r, bool mn_major, CUtensorMap* out) {
+  // box_r carries the swizzle kind in the cache key: MN-major boxes are always 32 rows of the 32B-atom kind
+  auto key = std::make_tuple((const void*)base, cols, rows, ld, nb1, nb2, s1, s2, box_c, mn_major ? -box_r : box_r);
+  auto it = ctx->tmaps.find(key);
+  if (it != ctx->tmaps.end()) {
+    *out = it->second;
+    return FML_OK;
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fml_fail(ctx, FML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  // unused batch levels get a harmless, 16-byte-multiple stride
+  if (nb1 <= 1) s1 = rows * ld;
+  if (nb2 <= 1) s2 = (nb1 <= 1 ? rows * ld : s1 * nb1);
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(nb1 < 1 ? 1 : nb1), (cuuint64_t)(nb2 < 1 ? 1 : nb2)};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 4, (cuuint64_t)s1 * 4, (cuuint64_t)s2 * 4};
+  cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)box_r, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[256];
+    snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled failed (%d): cols=%lld rows=%lld ld=%lld nb=(%lld,%lld) s=(%lld,%lld) box=(%d,%d)",
+             (int)r, (long long)cols, (long long)rows, (long long)ld, (long long)nb1, (long long)nb2, (long long)s1,
+             (long long)s2, box_c, box_r);
+    return fml_fail(ctx, FML_ERR_CUDA, msg);
+  }
+  if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
+  ctx->tmaps[key] = *out;
+  return FML_OK;
+}
+
+uint32_t make_idesc(int BN, int a_mn, int b_mn) {
+  uint32_t d = 0;
+  d |= 1u << 4;                    // accumulator format F32
+  d |= 2u << 7;                    // A format TF32
+  d |= 2u << 10;                   // B format TF32
+  d |= (uint32_t)(a_mn & 1) << 15; // A major-ness (0 = K, 1 = MN)
+  d |= (uint32_t)(b_mn & 1) << 16; // B major-ness
+  d |= (uint32_t)(BN >> 3) << 17;  // N / 8
+  d |= (uint32_t)(BM >> 4) << 24;  // M / 16
+  return d;
+}
+
+}  // namespace
+
+bool fml_gemm_tc_eligible(const fml_gemm_desc* d) {
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al16(d->A) || !al16(d->B)) return false;
+  if ((d->lda & 3) || (d->ldb & 3)) return false;
+  if (d->batch1 > 1 && ((d->sA1 & 3) || (d->sB1 & 3))) return false;
+  if (d->batch2 > 1 && ((d->sA2 & 3) || (d->sB2 & 3))) return false;
+  return true;
+}
+
+int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    FML_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set = true;
+  }
+  const int nb1 = d->batch1 < 1 ? 1 : d->batch1, nb2 = d->batch2 < 1 ? 1 : d->batch2;
+  const int tiles_m = (d->M + BM - 1) / BM;
+  // widest tile that still gives every SM work
+  int BN = 64;
+  for (int bn : {256, 128, 64}) {
+    long long tiles = (long long)tiles_m * ((d->N + bn - 1) / bn) * nb1 * nb2;
+    if (d->N > bn / 2 && tiles >= ctx->sm_count) { BN = bn; break; }
+  }
+  if (BN == 64) {
+    // small problem: nothing fills the machine; prefer the tile that wastes least of N
+    BN = d->N > 128 ? (d->N > 192 ? 256 : 128) : (d->N > 64 ? 128 : 64);
+    long long t256 = (long long)tiles_m * ((d->N + 255) / 256) * nb1 * nb2;
+    if (BN == 256 && t256 < ctx->sm_count / 2) BN = 128;
+    long long t128 = (long long)tiles_m * ((d->N + 127) / 128) * nb1 * nb2;
+    if (BN == 128 && t128 < ctx->sm_count / 2 && d->N > 64) BN = 64;
+  }
+  const int tiles_n = (d->N + BN - 1) / BN;
+  const int a_mn = d->transA ? 1 : 0;  // stored [K x M]: M contiguous
+  const int b_mn = d->transB ? 0 : 1;  // stored [K x N]: N contiguous
+
+  const float* A = d->A;
+  const float* B = d->B;
+  const float *Alo = nullptr, *Blo = nullptr;
+  int64_t lda = d->lda, ldb = d->ldb, sA1 = d->sA1, sA2 = d->sA2, sB1 = d->sB1, sB2 = d->sB2;
+  const int64_t a_rows = d->transA ? d->K : d->M, a_cols = d->transA ? d->M : d->K;
+  const int64_t b_rows = d->transB ? d->N : d->K, b_cols = d->transB ? d->K : d->N;
+  if (precision == FML_PREC_3XTF32) {
+    const int64_t a_ldd = (a_cols + 3) & ~3ll, b_ldd = (b_cols + 3) & ~3ll;
+    const size_t a_n = (size_t)nb1 * nb2 * a_rows * a_ldd, b_n = (size_t)nb1 * nb2 * b_rows * b_ldd;
+    int32_t rc = fml_ensure_workspace(ctx, (2 * a_n + 2 * b_n) * sizeof(float) + 1024);
+    if (rc) return rc;
+    float* w = reinterpret_cast<float*>(ctx->ws);
+    float *Ahi = w, *Al = w + a_n, *Bhi = w + 2 * a_n, *Bl = w + 2 * a_n + b_n;
+    const int threads = 256;
+    auto blocks = [&](size_t n) { return (int)std::min<size_t>((n + threads - 1) / threads, (size_t)ctx->sm_count * 16); };
+    split_tf32_kernel<<<blocks(a_n), threads, 0, ctx->stream>>>(d->A, Ahi, Al, (int)a_rows, (int)a_cols, d->lda, nb1, nb2,
+                                                                d->sA1, d->sA2, (int)a_ldd);
+    split_tf32_kernel<<<blocks(b_n), threads, 0, ctx->stream>>>(d->B, Bhi, Bl, (int)b_rows, (int)b_cols, d->ldb, nb1, nb2,
+                                                                d->sB1, d->sB2, (int)b_ldd);
+    FML_LAUNCH_CHECK(ctx, "split_tf32_kernel");
+    A = Ahi; Alo = Al; B = Bhi; Blo = Bl;
+    lda = a_ldd; ldb = b_ldd;
+    sA1 = a_rows * a_ldd; sA2 = sA1 * nb1;
+    sB1 = b_rows * b_ldd; sB2 = sB1 * nb1;
+  }
+
+  CUtensorMap tmA, tmB, tmAlo, tmBlo;
+  int32_t rc;
+  const int a_box_c = 32, a_box_r = a_mn ? 32 : BM;
+  const int b_box_c = 32, b_box_r = b_mn ? 32 : BN;
+  if ((rc = make_tmap(ctx, A, a_cols, a_rows, lda, nb1, nb2, sA1, sA2, a_box_c, a_box_r, a_mn, &tmA))) return rc;
+  if ((rc = make_tmap(ctx, B, b_cols, b_rows, ldb, nb1, nb2, sB1, sB2, b_box_c, b_box_r, b_mn, &tmB))) return rc;
+  if (Alo) {
+    if ((rc = make_tmap(ctx, Alo, a_cols, a_rows, lda, nb1, nb2, sA1, sA2, a_box_c, a_box_r, a_mn, &tmAlo))) return rc;
+    if ((rc = make_tmap(ctx, Blo, b_cols, b_rows, ldb, nb1, nb2, sB1, sB2, b_box_c, b_box_r, b_mn, &tmBlo))) return rc;
+  } else {
+    tmAlo = tmA;
+    tmBlo = tmB;
+  }
+
+  TcParams p;
+  p.M = d->M; p.N = d->N; p.K = d->K;
+  p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.nb1 = nb1; p.nb2 = nb2;
+  p.BN = BN; p.a_mn = a_mn; p.b_mn = b_mn;
+  p.nseg = (precision == FML_PREC_3XTF32) ? 3 : 1;
+  p.kblocks = (d->K + BK - 1) / BK;
+  p.C = d->C; p.Z = d->preact; p.bias = d->bias;
+  p.ldc = d->ldc; p.sC1 = d->sC1; p.sC2 = d->sC2;
+  p.act = d->act; p.alpha = d->alpha; p.beta = d->beta;
+  p.status = ctx->d_status;
+  p.idesc = make_idesc(BN, a_mn, b_mn);
+  const long long num_tiles = (long long)tiles_m * tiles_n * nb1 * nb2;
+  const int grid = (int)std::min<long long>(num_tiles, ctx->sm_count);
+  gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, p);
+  FML_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
+  ctx->last_gemm_path = 1;
+  return FML_OK;
+}

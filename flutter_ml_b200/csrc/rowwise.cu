@@ -1,0 +1,507 @@
+// Row kernels: softmax (with the attention scale and an optional causal mask folded in),
+// layer normalisation (with the residual add folded in), softmax cross-entropy and MSE.
+//
+// Rows up to 2048 floats wide whose length is a multiple of 4 run one warp per row: each lane
+// keeps its slice of the row in registers (float4 at lane + 32*i, so every load instruction of
+// the warp covers 512 contiguous bytes), reductions are warp shuffles, and the row is read from
+// HBM exactly once.  Other shapes take a block-per-row kernel.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr float NEG_INF = -INFINITY;
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// block-wide reductions for 256 threads
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; k++) t += red[k];
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = NEG_INF;
+#pragma unroll
+  for (int k = 0; k < 8; k++) t = fmaxf(t, red[k]);
+  return t;
+}
+
+// ------------------------------------------------------------------------- softmax
+template <int NV>
+__global__ void __launch_bounds__(256) softmax_fwd_warp(const float* __restrict__ x, float* __restrict__ y, long long rows,
+                                                        int cols, float scale, int causal_period) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const int lim = causal_period > 0 ? min(cols, (int)(r % causal_period) + 1) : cols;
+    const float4* xr = reinterpret_cast<const float4*>(x + r * cols);
+    float v[NV * 4];
+    float mx = NEG_INF;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int c = (lane + 32 * i) * 4;
+      float4 t = make_float4(NEG_INF, NEG_INF, NEG_INF, NEG_INF);
+      if (c < lim) t = xr[lane + 32 * i];  // columns at or beyond lim are masked below
+      v[4 * i + 0] = (c + 0 < lim) ? t.x * scale : NEG_INF;
+      v[4 * i + 1] = (c + 1 < lim) ? t.y * scale : NEG_INF;
+      v[4 * i + 2] = (c + 2 < lim) ? t.z * scale : NEG_INF;
+      v[4 * i + 3] = (c + 3 < lim) ? t.w * scale : NEG_INF;
+#pragma unroll
+      for (int e = 0; e < 4; e++) mx = fmaxf(mx, v[4 * i + e]);
+    }
+    mx = warp_max(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV * 4; i++) {
+      v[i] = (v[i] == NEG_INF) ? 0.f : expf(v[i] - mx);
+      s += v[i];
+    }
+    s = warp_sum(s);
+    float4* yr = reinterpret_cast<float4*>(y + r * cols);
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int c = (lane + 32 * i) * 4;
+      if (c < cols) yr[lane + 32 * i] = make_float4(v[4 * i] / s, v[4 * i + 1] / s, v[4 * i + 2] / s, v[4 * i + 3] / s);
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) softmax_bwd_warp(const float* __restrict__ y, const float* __restrict__ dy, float* dx,
+                                                        long long rows, int cols, float scale, int accumulate) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const float4* yr = reinterpret_cast<const float4*>(y + r * cols);
+    const float4* gr = reinterpret_cast<const float4*>(dy + r * cols);
+    float4 yv[NV], gv[NV];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      yv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      gv[i] = yv[i];
+      if ((lane + 32 * i) * 4 < cols) { yv[i] = yr[lane + 32 * i]; gv[i] = gr[lane + 32 * i]; }
+      dot += yv[i].x * gv[i].x + yv[i].y * gv[i].y + yv[i].z * gv[i].z + yv[i].w * gv[i].w;
+    }
+    dot = warp_sum(dot);
+    float4* xr = reinterpret_cast<float4*>(dx + r * cols);
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      if ((lane + 32 * i) * 4 < cols) {
+        float4 o = make_float4(scale * yv[i].x * (gv[i].x - dot), scale * yv[i].y * (gv[i].y - dot),
+                               scale * yv[i].z * (gv[i].z - dot), scale * yv[i].w * (gv[i].w - dot));
+        if (accumulate) {
+          float4 old = xr[lane + 32 * i];
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        xr[lane + 32 * i] = o;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) softmax_fwd_block(const float* __restrict__ x, float* __restrict__ y, long long rows,
+                                                         int cols, float scale, int causal_period) {
+  __shared__ float red[8];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int lim = causal_period > 0 ? min(cols, (int)(r % causal_period) + 1) : cols;
+    const float* xr = x + r * cols;
+    float mx = NEG_INF;
+    for (int c = threadIdx.x; c < lim; c += 256) mx = fmaxf(mx, xr[c] * scale);
+    mx = block_max(mx, red);
+    float s = 0.f;
+    for (int c = threadIdx.x; c < lim; c += 256) s += expf(xr[c] * scale - mx);
+    s = block_sum(s, red);
+    for (int c = threadIdx.x; c < cols; c += 256) y[r * cols + c] = c < lim ? expf(xr[c] * scale - mx) / s : 0.f;
+  }
+}
+__global__ void __launch_bounds__(256) softmax_bwd_block(const float* __restrict__ y, const float* __restrict__ dy, float* dx,
+                                                         long long rows, int cols, float scale, int accumulate) {
+  __shared__ float red[8];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    float dot = 0.f;
+    for (int c = threadIdx.x; c < cols; c += 256) dot += y[r * cols + c] * dy[r * cols + c];
+    dot = block_sum(dot, red);
+    for (int c = threadIdx.x; c < cols; c += 256) {
+      float o = scale * y[r * cols + c] * (dy[r * cols + c] - dot);
+      dx[r * cols + c] = accumulate ? dx[r * cols + c] + o : o;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------- layer norm
+template <int NV>
+__global__ void __launch_bounds__(256) layernorm_fwd_warp(const float* __restrict__ x, const float* __restrict__ res,
+                                                          const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                          float* __restrict__ y, float* __restrict__ xhat,
+                                                          float* __restrict__ rstd, long long rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  float4 g[NV], b[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    g[i] = b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((lane + 32 * i) * 4 < cols) {
+      g[i] = reinterpret_cast<const float4*>(gamma)[lane + 32 * i];
+      b[i] = reinterpret_cast<const float4*>(beta)[lane + 32 * i];
+    }
+  }
+  const float inv_c = 1.f / (float)cols;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    float4 v[NV];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if ((lane + 32 * i) * 4 < cols) {
+        v[i] = reinterpret_cast<const float4*>(x + r * cols)[lane + 32 * i];
+        if (res) {
+          float4 q = reinterpret_cast<const float4*>(res + r * cols)[lane + 32 * i];
+          v[i].x += q.x; v[i].y += q.y; v[i].z += q.z; v[i].w += q.w;
+        }
+      }
+      sum += v[i].x + v[i].y + v[i].z + v[i].w;
+    }
+    const float mean = warp_sum(sum) * inv_c;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      if ((lane + 32 * i) * 4 < cols) {
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        sq += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+      }
+    }
+    const float var = warp_sum(sq) * inv_c;  // biased variance, as the reference
+    const float rs = 1.f / sqrtf(var + eps);
+    if (lane == 0) rstd[r] = rs;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      if ((lane + 32 * i) * 4 < cols) {
+        float4 n = make_float4(v[i].x * rs, v[i].y * rs, v[i].z * rs, v[i].w * rs);
+        reinterpret_cast<float4*>(xhat + r * cols)[lane + 32 * i] = n;
+        reinterpret_cast<float4*>(y + r * cols)[lane + 32 * i] =
+            make_float4(g[i].x * n.x + b[i].x, g[i].y * n.y + b[i].y, g[i].z * n.z + b[i].z, g[i].w * n.w + b[i].w);
+      }
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) layernorm_bwd_warp(const float* __restrict__ dy, const float* __restrict__ gamma,
+                                                          const float* __restrict__ xhat, const float* __restrict__ rstd,
+                                                          float* dx, float* dgamma, float* dbeta, long long rows, int cols,
+                                                          int accumulate_dx) {
+  __shared__ float red[8][128];  // one float4 slot per lane per warp, reused for every i
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  float4 g[NV], dg[NV], db[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    g[i] = dg[i] = db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((lane + 32 * i) * 4 < cols) g[i] = reinterpret_cast<const float4*>(gamma)[lane + 32 * i];
+  }
+  const float fc = (float)cols;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    float4 d[NV], n[NV];
+    float sum_g = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      d[i] = n[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if ((lane + 32 * i) * 4 < cols) {
+        d[i] = reinterpret_cast<const float4*>(dy + r * cols)[lane + 32 * i];
+        n[i] = reinterpret_cast<const float4*>(xhat + r * cols)[lane + 32 * i];
+      }
+      dg[i].x += d[i].x * n[i].x; dg[i].y += d[i].y * n[i].y; dg[i].z += d[i].z * n[i].z; dg[i].w += d[i].w * n[i].w;
+      db[i].x += d[i].x; db[i].y += d[i].y; db[i].z += d[i].z; db[i].w += d[i].w;
+      d[i].x *= g[i].x; d[i].y *= g[i].y; d[i].z *= g[i].z; d[i].w *= g[i].w;  // grad wrt xhat
+      sum_g += d[i].x + d[i].y + d[i].z + d[i].w;
+      dot += d[i].x * n[i].x + d[i].y * n[i].y + d[i].z * n[i].z + d[i].w * n[i].w;
+    }
+    sum_g = warp_sum(sum_g);
+    dot = warp_sum(dot);
+    if (dx) {
+      const float k = rstd[r] / fc;
+#pragma unroll
+      for (int i = 0; i < NV; i++) {
+        if ((lane + 32 * i) * 4 < cols) {
+          float4 o = make_float4(k * (fc * d[i].x - sum_g - n[i].x * dot), k * (fc * d[i].y - sum_g - n[i].y * dot),
+                                 k * (fc * d[i].z - sum_g - n[i].z * dot), k * (fc * d[i].w - sum_g - n[i].w * dot));
+          float4* xp = reinterpret_cast<float4*>(dx + r * cols) + lane + 32 * i;
+          if (accumulate_dx) {
+            float4 old = *xp;
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          *xp = o;
+        }
+      }
+    }
+  }
+  // reduce the per-warp column partials across the 8 warps, then one atomic per column per block
+#pragma unroll
+  for (int pass = 0; pass < 2; pass++) {
+    float* dst = pass == 0 ? dgamma : dbeta;
+    if (!dst) continue;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const float4 v = pass == 0 ? dg[i] : db[i];
+      __syncthreads();
+      red[warp][lane * 4 + 0] = v.x; red[warp][lane * 4 + 1] = v.y;
+      red[warp][lane * 4 + 2] = v.z; red[warp][lane * 4 + 3] = v.w;
+      __syncthreads();
+      if (threadIdx.x < 128) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) t += red[w][threadIdx.x];
+        const int c = (threadIdx.x >> 2) * 4 + 128 * i + (threadIdx.x & 3);  // lane*4 + e + 128*i
+        if (c < cols) atomicAdd(dst + c, t);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) layernorm_fwd_block(const float* __restrict__ x, const float* __restrict__ res,
+                                                           const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                           float* __restrict__ y, float* __restrict__ xhat,
+                                                           float* __restrict__ rstd, long long rows, int cols, float eps) {
+  __shared__ float red[8];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < cols; c += 256) s += x[r * cols + c] + (res ? res[r * cols + c] : 0.f);
+    const float mean = block_sum(s, red) / cols;
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+      float d = x[r * cols + c] + (res ? res[r * cols + c] : 0.f) - mean;
+      sq += d * d;
+    }
+    const float rs = 1.f / sqrtf(block_sum(sq, red) / cols + eps);
+    if (threadIdx.x == 0) rstd[r] = rs;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+      float n = (x[r * cols + c] + (res ? res[r * cols + c] : 0.f) - mean) * rs;
+      xhat[r * cols + c] = n;
+      y[r * cols + c] = gamma[c] * n + beta[c];
+    }
+  }
+}
+__global__ void __launch_bounds__(256) layernorm_bwd_block(const float* __restrict__ dy, const float* __restrict__ gamma,
+                                                           const float* __restrict__ xhat, const float* __restrict__ rstd,
+                                                           float* dx, float* dgamma, float* dbeta, long long rows, int cols,
+                                                           int accumulate_dx) {
+  __shared__ float red[8];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    float sum_g = 0.f, dot = 0.f;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+      const float d = dy[r * cols + c], n = xhat[r * cols + c];
+      if (dgamma) atomicAdd(dgamma + c, d * n);
+      if (dbeta) atomicAdd(dbeta + c, d);
+      sum_g += d * gamma[c];
+      dot += d * gamma[c] * n;
+    }
+    sum_g = block_sum(sum_g, red);
+    dot = block_sum(dot, red);
+    if (dx) {
+      const float k = rstd[r] / cols;
+      for (int c = threadIdx.x; c < cols; c += 256) {
+        float o = k * (cols * dy[r * cols + c] * gamma[c] - sum_g - xhat[r * cols + c] * dot);
+        dx[r * cols + c] = accumulate_dx ? dx[r * cols + c] + o : o;
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------- softmax cross-entropy
+// One block per row, online (max, sum) in a single read, then a second read (L2-resident for
+// rows of this size) that writes the gradient.  Per-row losses go to scratch and are summed in
+// double by a single block, so the result does not depend on the launch geometry.
+__global__ void __launch_bounds__(256) xent_kernel(const float* z, const int* __restrict__ labels, float* dz,
+                                                   float* __restrict__ row_loss, long long rows, int cols, float inv_count) {
+  __shared__ float red[8];
+  __shared__ float zl_s;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float* zr = z + r * cols;
+    float mx = NEG_INF, s = 0.f;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+      const float v = zr[c];
+      if (v > mx) { s = s * expf(mx - v); mx = v; }
+      s += expf(v - mx);
+    }
+    const float bm = block_max(mx, red);
+    s = (mx == NEG_INF) ? 0.f : s * expf(mx - bm);
+    s = block_sum(s, red);
+    const int lab = labels[r];
+    if (threadIdx.x == 0) zl_s = zr[lab];
+    __syncthreads();
+    const float zl = zl_s;
+    if (threadIdx.x == 0) row_loss[r] = -(zl - bm - logf(s)) * inv_count;
+    if (dz) {
+      float* dr = dz + r * cols;
+      for (int c = threadIdx.x; c < cols; c += 256) dr[c] = (expf(zr[c] - bm) / s - (c == lab ? 1.f : 0.f)) * inv_count;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256) mse_kernel(const float* __restrict__ p, const float* __restrict__ t, float* dp,
+                                                  double* __restrict__ partial, long long n, float k) {
+  __shared__ double red[8];
+  double acc = 0.0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float e = p[i] - t[i];
+    acc += (double)e * e;
+    if (dp) dp[i] = k * e;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double tsum = 0.0;
+    for (int w = 0; w < 8; w++) tsum += red[w];
+    partial[blockIdx.x] = tsum;
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(256) final_sum_kernel(const T* __restrict__ part, long long n, double mul, float* out) {
+  __shared__ double red[8];
+  double acc = 0.0;
+  for (long long i = threadIdx.x; i < n; i += 256) acc += (double)part[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double tsum = 0.0;
+    for (int w = 0; w < 8; w++) tsum += red[w];
+    *out += (float)(tsum * mul);
+  }
+}
+
+inline int warp_row_blocks(fml_ctx* ctx, long long rows) {
+  long long b = (rows + 7) / 8;  // 8 warps per block, one row per warp per trip
+  return (int)std::max<long long>(1, std::min<long long>(b, (long long)ctx->sm_count * 8));
+}
+inline int block_row_blocks(fml_ctx* ctx, long long rows) {
+  return (int)std::max<long long>(1, std::min<long long>(rows, (long long)ctx->sm_count * 8));
+}
+
+#define DISPATCH_NV(cols, CALL)            \
+  do {                                     \
+    if ((cols) <= 128) { CALL(1); }        \
+    else if ((cols) <= 256) { CALL(2); }   \
+    else if ((cols) <= 512) { CALL(4); }   \
+    else if ((cols) <= 1024) { CALL(8); }  \
+    else { CALL(16); }                     \
+  } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int32_t fml_softmax_rows_fwd(fml_ctx* ctx, const float* x, float* y, int64_t rows, int32_t cols, float scale,
+                             int32_t causal_period) {
+  FML_REQUIRE(ctx, x && y && rows > 0 && cols > 0, "fml_softmax_rows_fwd: bad arguments");
+  if (cols % 4 == 0 && cols <= 2048 && al16(x) && al16(y)) {
+#define CALL(NV) softmax_fwd_warp<NV><<<warp_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(x, y, rows, cols, scale, causal_period)
+    DISPATCH_NV(cols, CALL);
+#undef CALL
+  } else {
+    softmax_fwd_block<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(x, y, rows, cols, scale, causal_period);
+  }
+  FML_LAUNCH_CHECK(ctx, "softmax_fwd");
+  return FML_OK;
+}
+
+int32_t fml_softmax_rows_bwd(fml_ctx* ctx, const float* y, const float* dy, float* dx, int64_t rows, int32_t cols,
+                             float scale, int32_t accumulate) {
+  FML_REQUIRE(ctx, y && dy && dx && rows > 0 && cols > 0, "fml_softmax_rows_bwd: bad arguments");
+  if (cols % 4 == 0 && cols <= 2048 && al16(y) && al16(dy) && al16(dx)) {
+#define CALL(NV) softmax_bwd_warp<NV><<<warp_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(y, dy, dx, rows, cols, scale, accumulate)
+    DISPATCH_NV(cols, CALL);
+#undef CALL
+  } else {
+    softmax_bwd_block<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(y, dy, dx, rows, cols, scale, accumulate);
+  }
+  FML_LAUNCH_CHECK(ctx, "softmax_bwd");
+  return FML_OK;
+}
+
+int32_t fml_layernorm_fwd(fml_ctx* ctx, const float* x, const float* residual, const float* gamma, const float* beta,
+                          float* y, float* xhat, float* rstd, int64_t rows, int32_t cols, float eps) {
+  FML_REQUIRE(ctx, x && gamma && beta && y && xhat && rstd && rows > 0 && cols > 0, "fml_layernorm_fwd: bad arguments");
+  if (cols % 4 == 0 && cols <= 2048 && al16(x) && al16(y) && al16(xhat) && al16(gamma) && al16(beta) &&
+      (!residual || al16(residual))) {
+#define CALL(NV) layernorm_fwd_warp<NV><<<warp_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(x, residual, gamma, beta, y, xhat, rstd, rows, cols, eps)
+    DISPATCH_NV(cols, CALL);
+#undef CALL
+  } else {
+    layernorm_fwd_block<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(x, residual, gamma, beta, y, xhat, rstd, rows, cols, eps);
+  }
+  FML_LAUNCH_CHECK(ctx, "layernorm_fwd");
+  return FML_OK;
+}
+
+int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, const float* xhat, const float* rstd,
+                          float* dx, float* dgamma, float* dbeta, int64_t rows, int32_t cols, int32_t accumulate_dx) {
+  FML_REQUIRE(ctx, dy && gamma && xhat && rstd && rows > 0 && cols > 0, "fml_layernorm_bwd: bad arguments");
+  if (cols % 4 == 0 && cols <= 1024 && al16(dy) && al16(xhat) && al16(gamma) && (!dx || al16(dx))) {
+    // fewer, fatter blocks: every block ends with one atomic per column
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((rows + 7) / 8, (long long)ctx->sm_count * 2));
+#define CALL(NV) layernorm_bwd_warp<NV><<<blocks, 256, 0, ctx->stream>>>(dy, gamma, xhat, rstd, dx, dgamma, dbeta, rows, cols, accumulate_dx)
+    if (cols <= 128) { CALL(1); } else if (cols <= 256) { CALL(2); } else if (cols <= 512) { CALL(4); } else { CALL(8); }
+#undef CALL
+  } else {
+    layernorm_bwd_block<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(dy, gamma, xhat, rstd, dx, dgamma, dbeta, rows, cols, accumulate_dx);
+  }
+  FML_LAUNCH_CHECK(ctx, "layernorm_bwd");
+  return FML_OK;
+}
+
+int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum, int64_t rows,
+                         int32_t cols, float inv_count) {
+  FML_REQUIRE(ctx, z && labels && loss_sum && rows > 0 && cols > 0, "fml_softmax_xent: bad arguments");
+  int32_t rc = fml_ensure_workspace(ctx, (size_t)rows * sizeof(float));
+  if (rc) return rc;
+  float* row_loss = reinterpret_cast<float*>(ctx->ws);
+  xent_kernel<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+  final_sum_kernel<float><<<1, 256, 0, ctx->stream>>>(row_loss, rows, 1.0, loss_sum);
+  FML_LAUNCH_CHECK(ctx, "xent_kernel");
+  return FML_OK;
+}
+
+int32_t fml_mse(fml_ctx* ctx, const float* p, const float* t, float* dp, float* loss_sum, int64_t n, float upstream) {
+  FML_REQUIRE(ctx, p && t && loss_sum && n > 0, "fml_mse: bad arguments");
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((n + 255) / 256, (long long)ctx->sm_count * 4));
+  int32_t rc = fml_ensure_workspace(ctx, (size_t)blocks * sizeof(double));
+  if (rc) return rc;
+  double* partial = reinterpret_cast<double*>(ctx->ws);
+  mse_kernel<<<blocks, 256, 0, ctx->stream>>>(p, t, dp, partial, n, upstream * 2.f / (float)n);
+  final_sum_kernel<double><<<1, 256, 0, ctx->stream>>>(partial, blocks, 1.0 / (double)n, loss_sum);
+  FML_LAUNCH_CHECK(ctx, "mse_kernel");
+  return FML_OK;
+}
+
+}  // extern "C"

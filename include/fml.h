@@ -1,0 +1,248 @@
+/*
+ * fml.h -- C ABI of libflutter_ml_b200.so, the B200 (sm_100a) compute backend
+ * for the flutter_ml autograd framework.
+ *
+ * The library replaces the reference's native stub (cuda_lib/kernel.cu, bound
+ * from Dart by lib/cuda/cudacaller.dart:6-19).  The two legacy symbols keep
+ * their signatures; everything else is a handle-based surface the Dart tape
+ * (lib/autogradEngine/tensor.dart) calls once per op instead of running the
+ * scalar loops itself.
+ *
+ * Conventions
+ *   - All matrices are row-major float32 in device memory; `ld*` are row
+ *     strides in elements.  Device pointers are plain `float*` obtained from
+ *     fml_alloc (or any other CUDA allocation on the same device).
+ *   - Every function returns 0 on success or a negative fml_status;
+ *     fml_last_error() gives the message.  Nothing throws, aborts or traps.
+ *   - Calls are asynchronous on the context's stream; fml_download_* and
+ *     fml_sync wait.  A context is driven by one host thread at a time.
+ *   - There is no CPU fallback: without a CUDA device fml_init fails.
+ */
+#ifndef FML_H_
+#define FML_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct fml_ctx fml_ctx;
+
+typedef enum {
+  FML_OK = 0,
+  FML_ERR_INVALID = -1,   /* bad argument / shape / alignment                */
+  FML_ERR_CUDA = -2,      /* a CUDA runtime or driver call failed            */
+  FML_ERR_NO_DEVICE = -3, /* no usable CUDA device                           */
+  FML_ERR_TIMEOUT = -4,   /* a bounded device-side wait expired              */
+  FML_ERR_NCCL = -5,      /* NCCL missing or a collective failed             */
+  FML_ERR_OOM = -6        /* allocation failed or a size limit was exceeded  */
+} fml_status;
+
+/* Product precision of the dense contractions. */
+typedef enum {
+  FML_PREC_TF32 = 0,   /* tcgen05 kind::tf32, fp32 accumulate (rel. error ~5e-4) */
+  FML_PREC_3XTF32 = 1, /* hi/lo split, three tf32 products (rel. error ~1e-6)     */
+  FML_PREC_FP32 = 2    /* CUDA-core fp32 FMA path (small or unaligned shapes)     */
+} fml_precision;
+
+/* Epilogue activation, applied to alpha*A.B + bias.  Mirrors the reference's
+ * reluMatrix / sigmoidMatrix / tanhMatrix (lib/autogradEngine/tensor.dart:1013,
+ * 1123, 1178); GELU (exact, erf form) is an extension. */
+typedef enum { FML_ACT_NONE = 0, FML_ACT_RELU = 1, FML_ACT_SIGMOID = 2, FML_ACT_TANH = 3, FML_ACT_GELU = 4 } fml_act;
+
+typedef struct {
+  int32_t device;           /* CUDA ordinal                                          */
+  int32_t precision;        /* fml_precision used when a call passes -1              */
+  int64_t workspace_bytes;  /* scratch arena for 3xTF32 splits etc.; 0 = grow on use */
+} fml_config;
+
+/* ---- lifetime, errors, device query ------------------------------------- */
+int32_t fml_init(const fml_config* cfg, fml_ctx** out);
+int32_t fml_shutdown(fml_ctx* ctx);
+/* ctx may be NULL: returns the last error of a call that had no context. */
+const char* fml_last_error(fml_ctx* ctx);
+/* Replaces cuda_lib/device_query.cu:5-26. */
+int32_t fml_device_count(int32_t* count);
+int32_t fml_device_name(int32_t device, char* buf, int32_t buf_len);
+int32_t fml_sm_count(fml_ctx* ctx, int32_t* count);
+/* Use an existing cudaStream_t (as void*) instead of the context's own. */
+int32_t fml_set_stream(fml_ctx* ctx, void* cuda_stream);
+int32_t fml_sync(fml_ctx* ctx);
+/* Bounded device-side waits record a code here instead of hanging; reading it
+ * synchronises.  0 means no kernel gave up. */
+int32_t fml_device_status(fml_ctx* ctx, int32_t* code);
+
+/* ---- memory ---------------------------------------------------------------
+ * Dart lists are float64 (lib/cuda/cudacaller.dart:38-43 narrows element by
+ * element); the f64 variants convert once, in C. */
+int32_t fml_alloc(fml_ctx* ctx, int64_t n_floats, float** out);
+int32_t fml_free(fml_ctx* ctx, float* p);
+int32_t fml_zero(fml_ctx* ctx, float* p, int64_t n_floats);
+int32_t fml_upload_f32(fml_ctx* ctx, float* dst, const float* host, int64_t n);
+int32_t fml_upload_f64(fml_ctx* ctx, float* dst, const double* host, int64_t n);
+int32_t fml_upload_i32(fml_ctx* ctx, int32_t* dst, const int32_t* host, int64_t n);
+int32_t fml_download_f32(fml_ctx* ctx, float* host, const float* src, int64_t n);
+int32_t fml_download_f64(fml_ctx* ctx, double* host, const float* src, int64_t n);
+int32_t fml_copy(fml_ctx* ctx, float* dst, const float* src, int64_t n);
+
+/* Page-locked host memory for staging (the reference stages through pageable
+ * calloc buffers, lib/cuda/cudacaller.dart:32-34). */
+int32_t fml_host_alloc(fml_ctx* ctx, int64_t bytes, void** out);
+int32_t fml_host_free(fml_ctx* ctx, void* p);
+
+/* ---- timing (CUDA events on the context's stream) ------------------------- */
+int32_t fml_timer_start(fml_ctx* ctx);
+int32_t fml_timer_stop_ms(fml_ctx* ctx, float* ms); /* waits for the stop event */
+/* A small pool of numbered events (0..63) for timing individual launches. */
+int32_t fml_event_record(fml_ctx* ctx, int32_t slot);
+int32_t fml_event_elapsed_ms(fml_ctx* ctx, int32_t slot_start, int32_t slot_stop, float* ms);
+
+/* ---- dense contraction ------------------------------------------------------
+ * C[M x N] = act(alpha * op(A)[M x K] . op(B)[K x N] + bias) (+ C if beta == 1)
+ * Replaces matMul forward (tensor.dart:867-899, no transposes), the two backward
+ * products dA += dC.B^T (tensor.dart:918-924: transB = 1) and dB += A^T.dC
+ * (tensor.dart:935-941: transA = 1) without materialising the transposes the
+ * reference builds (:877-884, :908-915, :927-934), the bias add
+ * addMatrixAndVector (tensor.dart:679-709) and the activation.
+ *   transA = 0: A stored [M x K];  1: stored [K x M].   same for B with [K x N] / [N x K].
+ *   preact, if non-NULL, receives alpha*A.B + bias before the activation (ldc).
+ *   batch1/batch2 > 1 run independent problems at the given element strides
+ *   (attention heads inside sequences: QK^T and P.V of
+ *   lib/layertypes/singleHeadAttentionLayer.dart:77-86).
+ *   precision = -1 uses the context default.
+ * The tensor-core path needs 16-byte aligned pointers and lda/ldb/strides that
+ * are multiples of 4; anything else runs on the FP32 CUDA-core kernel. */
+typedef struct {
+  int32_t M, N, K;
+  int32_t transA, transB;
+  int64_t lda, ldb, ldc;
+  const float* A;
+  const float* B;
+  float* C;
+  const float* bias; /* length N, or NULL */
+  float* preact;     /* [M x N] at ldc, or NULL */
+  int32_t act;       /* fml_act */
+  float alpha;
+  float beta;        /* 0 or 1 */
+  int32_t batch1, batch2;          /* >= 1 */
+  int64_t sA1, sA2, sB1, sB2, sC1, sC2; /* element strides per batch level */
+  int32_t precision; /* fml_precision or -1 */
+} fml_gemm_desc;
+
+int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d);
+/* Which kernel the last fml_gemm used: 1 = tcgen05 tensor-core, 2 = CUDA-core. */
+int32_t fml_gemm_last_path(fml_ctx* ctx, int32_t* path);
+
+/* ---- legacy symbols (cuda_lib/kernel.cu:6-11 and :57-58) --------------------
+ * Host pointers, row-major, A m x k, B k x n, C m x n; same argument order as
+ * the reference.  Backed by a cached context on device 0 and the kernels above
+ * instead of per-call cudaMalloc + cublasCreate + cublasSgemm.  multiplyMatrices
+ * stays void; failures are readable through fml_last_error(NULL). */
+void multiplyMatrices(float* h_a, float* h_b, float* h_c, int32_t m, int32_t k, int32_t n);
+/* Largest square size (steps of 100) whose round trip stays under 1000 ms. */
+int32_t benchtest(void);
+
+/* ---- elementwise -------------------------------------------------------------
+ * y = act(x)                                    (tensor.dart:1013-1038, 1123-1151, 1178-1209)
+ * dx (+)= dy * act'(saved); saved = x for RELU/GELU (tensor.dart:1030), y for
+ * SIGMOID/TANH (tensor.dart:552, 598).  accumulate != 0 adds into dx as the
+ * reference's closures do.  If dbias != NULL (cols > 0) it also receives
+ * (accumulated) column sums of the produced gradient: addMatrixAndVector
+ * backward, tensor.dart:698-704. */
+int32_t fml_act_fwd(fml_ctx* ctx, int32_t act, const float* x, float* y, int64_t n);
+int32_t fml_act_bwd(fml_ctx* ctx, int32_t act, const float* saved, const float* dy, float* dx,
+                    int64_t rows, int64_t cols, int32_t accumulate, float* dbias);
+/* y = a + b (addMatrix tensor.dart:651-677); y may alias a. */
+int32_t fml_add(fml_ctx* ctx, const float* a, const float* b, float* y, int64_t n);
+/* y += s * x  (gradient fan-in, scaleMatrix tensor.dart:1075-1101) */
+int32_t fml_axpy(fml_ctx* ctx, float s, const float* x, float* y, int64_t n);
+/* y = a * b (elementWiseMultiply tensor.dart:478-497) */
+int32_t fml_mul(fml_ctx* ctx, const float* a, const float* b, float* y, int64_t n);
+/* Y = X + 1.b^T and db (+)= column sums of dY (tensor.dart:679-709). */
+int32_t fml_add_bias(fml_ctx* ctx, const float* x, const float* b, float* y, int64_t rows, int64_t cols);
+int32_t fml_col_sum(fml_ctx* ctx, const float* dy, float* db, int64_t rows, int64_t cols, int32_t accumulate);
+/* out[cols x rows] = in[rows x cols]^T (transpose tensor.dart:1211-1236) */
+int32_t fml_transpose(fml_ctx* ctx, const float* in, float* out, int64_t rows, int64_t cols);
+
+/* ---- row kernels --------------------------------------------------------------
+ * Row softmax of scale*x (softmaxMatrix lib/activationFunctions/softmax.dart:68-96
+ * with scaleMatrix lib/layertypes/singleHeadAttentionLayer.dart:80 folded in).
+ * causal_period > 0 masks column j > (row mod causal_period) (extension).
+ * Backward: dx = scale * y * (dy - sum(dy*y)) (softmax.dart:98-112). */
+int32_t fml_softmax_rows_fwd(fml_ctx* ctx, const float* x, float* y, int64_t rows, int32_t cols,
+                             float scale, int32_t causal_period);
+int32_t fml_softmax_rows_bwd(fml_ctx* ctx, const float* y, const float* dy, float* dx, int64_t rows,
+                             int32_t cols, float scale, int32_t accumulate);
+/* y = gamma * xhat + beta over rows of (x [+ residual]); saves xhat and
+ * rstd = 1/sqrt(var+eps) (layerNorm lib/transformer/layerNormalization.dart:137-169;
+ * the residual add is addMatrix of transformerEncodingLayer.dart:63,68 fused in).
+ * Backward (:174-200): dx, and dgamma/dbeta accumulated. */
+int32_t fml_layernorm_fwd(fml_ctx* ctx, const float* x, const float* residual, const float* gamma,
+                          const float* beta, float* y, float* xhat, float* rstd, int64_t rows,
+                          int32_t cols, float eps);
+int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, const float* xhat,
+                          const float* rstd, float* dx, float* dgamma, float* dbeta, int64_t rows,
+                          int32_t cols, int32_t accumulate_dx);
+/* Softmax cross-entropy (extension): loss_sum += sum_r -log softmax(z_r)[label_r] * inv_count,
+ * dz = (softmax(z) - onehot) * inv_count written in place of z when dz == z. */
+int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz,
+                         float* loss_sum, int64_t rows, int32_t cols, float inv_count);
+/* mseMatrix (tensor.dart:982-1011): loss_sum += mean((p-t)^2); dp = 2(p-t)/n * upstream. */
+int32_t fml_mse(fml_ctx* ctx, const float* p, const float* t, float* dp, float* loss_sum, int64_t n,
+                float upstream);
+
+/* ---- embedding / positional --------------------------------------------------
+ * out[i] = table[ids[i]] (+ pe[i mod period]) (embeddingLayer.dart:47-56,
+ * positionalEncodingLayer.dart:55-65); backward scatter-adds (:58-65). */
+int32_t fml_embedding_fwd(fml_ctx* ctx, const float* table, const int32_t* ids, const float* pe,
+                          float* out, int64_t n, int32_t dim, int32_t pe_period);
+int32_t fml_embedding_bwd(fml_ctx* ctx, const float* dout, const int32_t* ids, float* dtable,
+                          int64_t n, int32_t dim);
+/* The reference's table: angle = pos / 10000^(2i/dModel), sin for even i, cos for odd i
+ * (positionalEncodingLayer.dart:39-48). */
+int32_t fml_positional_table(fml_ctx* ctx, float* pe, int32_t max_len, int32_t d_model);
+
+/* ---- optimizers ---------------------------------------------------------------
+ * SGD.step lib/optimizers/sgd.dart:24-42; Adam.step lib/optimizers/adam.dart:44-77
+ * (t = step count after the increment at :46).  grad_scale multiplies g first
+ * (1 for the reference behaviour).  Hyper-parameters are doubles, as in Dart: 1 - beta and
+ * 1 - beta^t are formed in double before narrowing (1 - 0.999f would be off by 1e-5). */
+int32_t fml_sgd_step(fml_ctx* ctx, float* w, const float* g, int64_t n, double lr, double grad_scale);
+int32_t fml_adam_step(fml_ctx* ctx, float* w, const float* g, float* m, float* v, int64_t n,
+                      double lr, double beta1, double beta2, double eps, int32_t t, double grad_scale);
+
+/* ---- LSTM ---------------------------------------------------------------------
+ * One layer over a batch of sequences (LSTMLayer.forward lib/layertypes/lstmLayer.dart:112-150).
+ * W: 4 gate matrices [H x (H+I)] in order f,i,c~,o (:64) with columns [h_{t-1} | x_t] (:119),
+ * stored as one [4H x (H+I)] matrix; b [4H]; x [T][B][I] (time-major); h0 = c0 = 0.
+ * The forward keeps gates [T][B][4H], cells [T+1][B][H] and hidden states [T+1][B][H] for BPTT.
+ * Backward takes dh_last [B][H] and produces dW, db (accumulated) and optionally dx. */
+typedef struct {
+  int32_t T, B, I, H;
+  const float* W;
+  const float* b;
+  const float* x;
+  float* gates;  /* [T][B][4H] activated gates            */
+  float* cells;  /* [T+1][B][H], slot 0 zeroed by the call */
+  float* hs;     /* [T+1][B][H], slot 0 zeroed by the call */
+  float* xproj;  /* scratch [T*B][4H]                      */
+} fml_lstm_desc;
+int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d);
+int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last, float* dW, float* db,
+                     float* dx, float* scratch /* [T*B][4H] + 2*[B][H] + [B][H+I] */);
+
+/* ---- data parallel (one process per GPU) -------------------------------------
+ * The reference has no multi-device code.  Rank 0 creates an id, the host
+ * distributes the 128 bytes by any means, every rank joins, and gradients are
+ * summed in place with NCCL over NVLink. */
+int32_t fml_dp_unique_id(uint8_t out[128]);
+int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id[128], int32_t rank, int32_t world);
+int32_t fml_dp_allreduce_sum(fml_ctx* ctx, float* buf, int64_t n);
+int32_t fml_dp_shutdown(fml_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FML_H_ */

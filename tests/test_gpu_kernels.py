@@ -1,0 +1,318 @@
+"""Parity of every CUDA kernel against the float64 oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from tests.gpu_util import TOL_3XTF32, TOL_FP32, TOL_TF32, ctx, rel  # noqa: F401
+
+pytestmark = pytest.mark.gpu
+f64 = np.float64
+
+
+def w64(x):
+    return np.ascontiguousarray(x, dtype=np.float64)
+
+
+GEMM_CASES = [
+    # M, N, K, transA, transB
+    (128, 256, 32, 0, 1), (128, 256, 128, 0, 0), (128, 256, 128, 1, 0), (128, 256, 128, 1, 1),
+    (300, 200, 100, 0, 0), (300, 200, 100, 1, 0), (300, 200, 100, 0, 1), (77, 64, 40, 1, 1),
+    (1, 4, 4, 0, 0), (513, 1028, 260, 0, 0), (64, 784, 128, 0, 1), (64, 10, 64, 0, 0), (784, 128, 64, 1, 0),
+    (1024, 1024, 1024, 0, 0), (2048, 512, 4096, 1, 0),
+]
+
+
+@pytest.mark.parametrize("prec,tol", [(0, TOL_TF32), (1, TOL_3XTF32), (2, TOL_FP32)])
+@pytest.mark.parametrize("M,N,K,tA,tB", GEMM_CASES)
+def test_gemm_matches_oracle(ctx, orc, M, N, K, tA, tB, prec, tol):
+    rng = np.random.default_rng(M + 3 * N + 7 * K + tA + 2 * tB)
+    A = (rng.standard_normal((K, M) if tA else (M, K)) / np.sqrt(K)).astype(np.float32)
+    B = (rng.standard_normal((N, K) if tB else (K, N)) / np.sqrt(K)).astype(np.float32)
+    dA, dB, dC = ctx.upload(A), ctx.upload(B), ctx.empty(M, N)
+    ctx.gemm(dA, dB, dC, M, N, K, transA=bool(tA), transB=bool(tB), precision=prec)
+    ops = orc.Ops(omp=True)
+    opA = w64(A.T if tA else A)
+    opB = w64(B.T if tB else B)
+    ref = ops.matmul_fwd(opA, opB)
+    assert rel(dC.numpy(), ref) <= tol
+    for a in (dA, dB, dC):
+        a.free()
+
+
+def test_all_ones_1024_known_answer(ctx):
+    # lib/gpu_benching.dart:34-37,60: all-ones 1024^3 => every element equals k (exact in TF32)
+    n = 1024
+    ones = np.ones((n, n), dtype=np.float32)
+    dA, dB, dC = ctx.upload(ones), ctx.upload(ones), ctx.empty(n, n)
+    ctx.gemm(dA, dB, dC, n, n, n)
+    assert ctx.gemm_last_path() == 1
+    assert np.all(dC.numpy() == float(n))
+
+
+def test_legacy_multiply_matrices(ctx):
+    # cuda_lib/kernel.cu:6-11 signature with host pointers; lib/gpu_benching.dart's check
+    m, k, n = 33, 50, 21
+    rng = np.random.default_rng(0)
+    a, b = rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32)
+    c = np.zeros((m, n), dtype=np.float32)
+    ctx.lib.multiplyMatrices(a.ctypes.data, b.ctypes.data, c.ctypes.data, m, k, n)
+    assert rel(c, w64(a) @ w64(b)) <= TOL_TF32
+
+
+@pytest.mark.parametrize("act", ["relu", "sigmoid", "tanh", "gelu"])
+@pytest.mark.parametrize("prec,tol", [(0, TOL_TF32), (1, TOL_3XTF32), (2, TOL_FP32)])
+def test_dense_forward_backward(ctx, orc, act, prec, tol):
+    """act(X.W+b) and its three gradients: the fused epilogue, the dZ kernel with column sums,
+    dX = dZ.W^T and dW = X^T.dZ (tensor.dart:867-947, 679-709, 1013-1038).
+
+    Each kernel is held to the tolerance on ITS OWN inputs: the gate of ReLU is discontinuous,
+    so a pre-activation that differs from the oracle's in the last TF32 bit may flip it; the
+    activation-gradient kernel is therefore checked against the oracle formula evaluated on the
+    pre-activation the GPU produced, and the two backward products against the oracle products
+    of the GPU's dZ."""
+    M, K, N = 200, 96, 136
+    rng = np.random.default_rng(11)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    dY = rng.standard_normal((M, N)).astype(np.float32)
+    E = orc.Engine(omp=True)
+    x, w, bt = orc.T(w64(X)), orc.T(w64(W)), orc.T(w64(b))
+    y = E.dense_matrix(x, w, bt, act)
+    z = y.inputs[0]
+    dX_, dW_, db_, Y_, Z_ = ctx.empty(M, K), ctx.empty(K, N), ctx.zeros(N), ctx.empty(M, N), ctx.empty(M, N)
+    dXd, dWd, bd, dYd = ctx.upload(X), ctx.upload(W), ctx.upload(b), ctx.upload(dY)
+    dZ = ctx.empty(M, N)
+    ctx.gemm(dXd, dWd, Y_, M, N, K, bias=bd, preact=Z_, act=act, precision=prec)
+    saved = Z_ if act in ("relu", "gelu") else Y_
+    ctx.call("fml_act_bwd", _act(act), saved, dYd, dZ, M, N, 0, db_)
+    ctx.gemm(dZ, dWd, dX_, M, K, N, transB=True, precision=prec)
+    ctx.gemm(dXd, dZ, dW_, K, N, M, transA=True, precision=prec)
+    assert rel(Y_.numpy(), y.value) <= tol
+    assert rel(Z_.numpy(), z.value) <= tol
+    # activation gradient on the GPU's own saved tensor
+    saved_h, dZ_h = w64(saved.numpy()), w64(dZ.numpy())
+    dz_ref = np.zeros((M, N))
+    E.ops.unary_bwd(act, saved_h, w64(dY), dz_ref)
+    assert rel(dZ_h, dz_ref) <= 2e-6
+    assert rel(db_.numpy(), dZ_h.sum(0)) <= 2e-6
+    if act != "relu":  # smooth activations: the whole chain also stays within the tolerance
+        y.grad = w64(dY)
+        for node in (y, z, z.inputs[0]):
+            node.backward_fn()
+        assert rel(dZ_h, z.grad) <= tol
+        assert rel(db_.numpy(), bt.grad) <= tol * 2
+        assert rel(dX_.numpy(), x.grad) <= tol * 2
+        assert rel(dW_.numpy(), w.grad) <= tol * 2
+    # backward products against the oracle products of the same dZ (tensor.dart:918-924, 935-941)
+    dx_ref, dw_ref = np.zeros((M, K)), np.zeros((K, N))
+    E.ops.matmul_bwd(w64(X), w64(W), dZ_h, dx_ref, dw_ref)
+    assert rel(dX_.numpy(), dx_ref) <= tol
+    assert rel(dW_.numpy(), dw_ref) <= tol
+
+
+def _act(name):
+    from flutter_ml_b200 import _lib
+    return _lib.ACT_BY_NAME[name]
+
+
+def test_gemm_accumulates_with_beta(ctx):
+    M, N, K = 130, 72, 64
+    rng = np.random.default_rng(5)
+    A, B, C0 = [rng.standard_normal(s).astype(np.float32) for s in ((M, K), (K, N), (M, N))]
+    dA, dB, dC = ctx.upload(A), ctx.upload(B), ctx.upload(C0)
+    ctx.gemm(dA, dB, dC, M, N, K, beta=1.0)
+    assert rel(dC.numpy(), w64(C0) + w64(A) @ w64(B)) <= TOL_TF32
+
+
+@pytest.mark.parametrize("prec,tol", [(0, TOL_TF32), (2, TOL_FP32)])
+def test_batched_strided_attention_products(ctx, prec, tol):
+    """QK^T and P.V per (sequence, head) straight out of a fused [B*S, 3d] projection
+    (lib/layertypes/singleHeadAttentionLayer.dart:77-86)."""
+    Bn, H, S, dk = 3, 4, 96, 64
+    d = H * dk
+    rng = np.random.default_rng(9)
+    qkv = rng.standard_normal((Bn * S, 3 * d)).astype(np.float32)
+    dq = ctx.upload(qkv)
+    scores = ctx.empty(Bn, H, S, S)
+    ctx.gemm(dq, dq.view(d, ()), scores, S, S, dk, transB=True, lda=3 * d, ldb=3 * d, ldc=S, batch=(H, Bn),
+             sA=(dk, S * 3 * d), sB=(dk, S * 3 * d), sC=(S * S, H * S * S), alpha=0.125, precision=prec)
+    q = w64(qkv).reshape(Bn, S, 3, H, dk)
+    ref = np.einsum("bshd,bthd->bhst", q[:, :, 0], q[:, :, 1]) * 0.125
+    assert rel(scores.numpy(), ref) <= tol
+    out = ctx.empty(Bn * S, d)
+    ctx.gemm(scores, dq.view(2 * d, ()), out, S, dk, S, lda=S, ldb=3 * d, ldc=d, batch=(H, Bn),
+             sA=(S * S, H * S * S), sB=(dk, S * 3 * d), sC=(dk, S * d), precision=prec)
+    # P.V is checked on the scores the GPU produced (one product per tolerance)
+    ref2 = np.einsum("bhst,bthd->bshd", w64(scores.numpy()), q[:, :, 2]).reshape(Bn * S, d)
+    assert rel(out.numpy(), ref2) <= tol
+
+
+@pytest.mark.parametrize("rows,cols,causal", [(64, 10, 0), (96 * 3, 96, 96), (500, 256, 0), (33, 1000, 0),
+                                              (40, 2048, 0), (7, 4100, 0), (512, 512, 512)])
+def test_softmax_rows(ctx, orc, rows, cols, causal):
+    rng = np.random.default_rng(rows + cols)
+    x = (3 * rng.standard_normal((rows, cols))).astype(np.float32)
+    dy = rng.standard_normal((rows, cols)).astype(np.float32)
+    scale = 0.125
+    ops = orc.Ops()
+    y_ref = ops.softmax_fwd(w64(x) * scale, causal)
+    dx_ref = np.zeros((rows, cols))
+    ops.softmax_bwd(y_ref, w64(dy), dx_ref)
+    dx_ref *= scale
+    dxx, dyy, y, dx = ctx.upload(x), ctx.upload(dy), ctx.empty(rows, cols), ctx.empty(rows, cols)
+    ctx.call("fml_softmax_rows_fwd", dxx, y, rows, cols, scale, causal)
+    ctx.call("fml_softmax_rows_bwd", y, dyy, dx, rows, cols, scale, 0)
+    yh = y.numpy()
+    assert rel(yh, y_ref) <= 1e-6
+    if causal:
+        r = np.arange(rows)[:, None] % causal
+        assert np.all(yh[np.arange(cols)[None, :] > r] == 0.0)
+    assert rel(dx.numpy(), dx_ref) <= 2e-6
+
+
+@pytest.mark.parametrize("rows,cols,res", [(100, 512, True), (37, 1024, False), (64, 96, True), (20, 1030, True),
+                                           (300, 2048, False), (5, 16, True)])
+def test_layernorm(ctx, orc, rows, cols, res):
+    rng = np.random.default_rng(rows * cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    r = rng.standard_normal((rows, cols)).astype(np.float32)
+    g = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(cols)).astype(np.float32)
+    dy = rng.standard_normal((rows, cols)).astype(np.float32)
+    ops = orc.Ops()
+    xin = w64(x) + (w64(r) if res else 0)
+    y_ref, xhat_ref, var_ref = ops.layernorm_fwd(xin, w64(g), w64(b))
+    dx_ref, dg_ref, db_ref = np.zeros((rows, cols)), np.zeros(cols), np.zeros(cols)
+    ops.layernorm_bwd(w64(dy), w64(g), xhat_ref, var_ref, dx_ref, dg_ref, db_ref)
+    dxx, dr, dg, db_, ddy = ctx.upload(x), ctx.upload(r), ctx.upload(g), ctx.upload(b), ctx.upload(dy)
+    y, xhat, rstd = ctx.empty(rows, cols), ctx.empty(rows, cols), ctx.empty(rows)
+    dx, dgam, dbet = ctx.empty(rows, cols), ctx.zeros(cols), ctx.zeros(cols)
+    ctx.call("fml_layernorm_fwd", dxx, dr if res else None, dg, db_, y, xhat, rstd, rows, cols, 1e-5)
+    ctx.call("fml_layernorm_bwd", ddy, dg, xhat, rstd, dx, dgam, dbet, rows, cols, 0)
+    assert rel(y.numpy(), y_ref) <= 2e-6
+    assert rel(xhat.numpy(), xhat_ref) <= 2e-6
+    assert rel(dx.numpy(), dx_ref) <= 1e-5
+    assert rel(dgam.numpy(), dg_ref) <= 1e-5 and rel(dbet.numpy(), db_ref) <= 1e-5
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 10), (200, 1000), (16, 32000)])
+def test_softmax_xent(ctx, orc, rows, cols):
+    rng = np.random.default_rng(cols)
+    z = (2 * rng.standard_normal((rows, cols))).astype(np.float32)
+    labels = rng.integers(0, cols, rows).astype(np.int32)
+    inv = 1.0 / (3 * rows)
+    dz_ref = np.zeros((rows, cols))
+    loss_ref = orc.Ops().softmax_xent(w64(z), labels, dz_ref, inv)
+    dzz, dl, loss = ctx.upload(z), ctx.upload(labels), ctx.zeros(1)
+    ctx.call("fml_softmax_xent", dzz, dl, dzz, loss, rows, cols, inv, launches=2)  # in place
+    assert abs(loss.numpy()[0] - loss_ref) <= 2e-6 * abs(loss_ref)
+    assert rel(dzz.numpy(), dz_ref) <= 2e-6
+
+
+def test_mse(ctx, orc):
+    rng = np.random.default_rng(3)
+    p, t = rng.standard_normal((257, 129)).astype(np.float32), rng.standard_normal((257, 129)).astype(np.float32)
+    ops = orc.Ops()
+    dp_ref = np.zeros(p.shape)
+    ops.mse_bwd(w64(p), w64(t), dp_ref, 1.0)
+    dpp, dt, dp, loss = ctx.upload(p), ctx.upload(t), ctx.empty(*p.shape), ctx.zeros(1)
+    ctx.call("fml_mse", dpp, dt, dp, loss, p.size, 1.0, launches=2)
+    assert abs(loss.numpy()[0] - ops.mse_fwd(w64(p), w64(t))) <= 1e-6
+    assert rel(dp.numpy(), dp_ref) <= 1e-6
+
+
+@pytest.mark.parametrize("n", [109386, 4096, 7])
+def test_sgd_and_adam(ctx, orc, n):
+    rng = np.random.default_rng(n)
+    w, g = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    ops = orc.Ops()
+    w_ref = w64(w)
+    ops.sgd_step(w_ref, w64(g), 0.01)
+    dw, dg = ctx.upload(w), ctx.upload(g)
+    ctx.call("fml_sgd_step", dw, dg, n, 0.01, 1.0)
+    assert rel(dw.numpy(), w_ref) <= 1e-7
+    w_ref, m_ref, v_ref = w64(w), np.zeros(n), np.zeros(n)
+    dw, dm, dv = ctx.upload(w), ctx.zeros(n), ctx.zeros(n)
+    for t in (1, 2, 3):
+        ops.adam_step(w_ref, w64(g), m_ref, v_ref, 1e-3, t)
+        ctx.call("fml_adam_step", dw, dg, dm, dv, n, 1e-3, 0.9, 0.999, 1e-8, t, 1.0)
+    assert rel(dw.numpy(), w_ref) <= 1e-6
+    assert rel(dm.numpy(), m_ref) <= 1e-6 and rel(dv.numpy(), v_ref) <= 1e-6
+
+
+def test_embedding_and_positional(ctx, orc):
+    V, d, S, Bn = 50, 64, 12, 3
+    rng = np.random.default_rng(8)
+    table = rng.standard_normal((V, d)).astype(np.float32)
+    ids = rng.integers(0, V, Bn * S).astype(np.int32)
+    dout = rng.standard_normal((Bn * S, d)).astype(np.float32)
+    ops = orc.Ops()
+    pe_ref = ops.positional_table(S, d)
+    out_ref = ops.embedding_fwd(w64(table), ids) + np.tile(pe_ref, (Bn, 1))
+    dt_ref = np.zeros((V, d))
+    ops.embedding_bwd(w64(dout), ids, dt_ref)
+    dtab, dids, pe, out, ddout, dtable = (ctx.upload(table), ctx.upload(ids), ctx.empty(S, d), ctx.empty(Bn * S, d),
+                                          ctx.upload(dout), ctx.zeros(V, d))
+    ctx.call("fml_positional_table", pe, S, d)
+    ctx.call("fml_embedding_fwd", dtab, dids, pe, out, Bn * S, d, S)
+    ctx.call("fml_embedding_bwd", ddout, dids, dtable, Bn * S, d)
+    assert rel(pe.numpy(), pe_ref) <= 1e-7
+    assert rel(out.numpy(), out_ref) <= 1e-7
+    assert rel(dtable.numpy(), dt_ref) <= 1e-6
+
+
+def test_small_elementwise(ctx):
+    rng = np.random.default_rng(2)
+    a, b = rng.standard_normal((67, 45)).astype(np.float32), rng.standard_normal((67, 45)).astype(np.float32)
+    da, db_, y = ctx.upload(a), ctx.upload(b), ctx.empty(67, 45)
+    ctx.call("fml_add", da, db_, y, a.size)
+    assert np.array_equal(y.numpy(), a + b)
+    ctx.call("fml_mul", da, db_, y, a.size)
+    assert np.array_equal(y.numpy(), a * b)
+    ctx.call("fml_axpy", 0.5, da, y, a.size)
+    assert np.allclose(y.numpy(), a * b + 0.5 * a, rtol=1e-6, atol=1e-6)
+    t = ctx.empty(45, 67)
+    ctx.call("fml_transpose", da, t, 67, 45)
+    assert np.array_equal(t.numpy(), a.T)
+    cs = ctx.empty(45)
+    ctx.call("fml_col_sum", da, cs, 67, 45, 0)
+    assert rel(cs.numpy(), a.astype(np.float64).sum(0)) <= 1e-6
+    bias = ctx.upload(b[0])
+    ctx.call("fml_add_bias", da, bias, y, 67, 45)
+    assert np.array_equal(y.numpy(), a + b[0][None, :])
+
+
+@pytest.mark.parametrize("prec,tol", [(0, TOL_TF32), (1, 2e-5), (2, 2e-5)])
+def test_lstm_forward_backward(orc, prec, tol):
+    """LSTMLayer (lib/layertypes/lstmLayer.dart:112-150) + mse on the last hidden state, BPTT."""
+    from flutter_ml_b200 import _lib
+    c = _lib.Context(precision=prec)
+    T, B, I, H = 12, 20, 24, 32
+    rng = np.random.default_rng(13)
+    a = 1 / np.sqrt(H)
+    W = rng.uniform(-a, a, (4, H, H + I)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (4, H)).astype(np.float32)
+    x = rng.standard_normal((B, T, I)).astype(np.float32)
+    target = rng.standard_normal((B, H)).astype(np.float32)
+    h_ref, loss_ref, dW_ref, db_ref = orc.Ops(omp=True).lstm_fwd_bwd(w64(W), w64(b), w64(x), w64(target))
+    dW_, db_, dx_ = c.zeros(4 * H, H + I), c.zeros(4 * H), c.empty(T * B, I)
+    d = _lib.LstmDesc()
+    d.T, d.B, d.I, d.H = T, B, I, H
+    bufs = dict(W=c.upload(W), b=c.upload(b), x=c.upload(np.ascontiguousarray(x.transpose(1, 0, 2))),
+                gates=c.empty(T, B, 4 * H), cells=c.empty(T + 1, B, H), hs=c.empty(T + 1, B, H), xproj=c.empty(T * B, 4 * H))
+    for k, v in bufs.items():
+        setattr(d, k, v.ptr)
+    import ctypes
+    c.check(c.lib.fml_lstm_fwd(c.h, ctypes.byref(d)))
+    h_last = bufs["hs"].view(T * B * H, (B, H))
+    # loss = sum over sequences of mse(h_T, target): dh = 2 (h - t) / H
+    dh, loss = c.empty(B, H), c.zeros(1)
+    c.call("fml_mse", h_last, c.upload(target), dh, loss, B * H, float(B))
+    scratch = c.empty(T * B * 4 * H + 2 * B * H)
+    c.check(c.lib.fml_lstm_bwd(c.h, ctypes.byref(d), dh.ptr, dW_.ptr, db_.ptr, dx_.ptr, scratch.ptr))
+    assert c.device_status() == 0
+    assert rel(h_last.numpy(), h_ref) <= tol
+    assert abs(loss.numpy()[0] * B - loss_ref) <= tol * abs(loss_ref) * 4
+    assert rel(dW_.numpy().reshape(4, H, H + I), dW_ref) <= tol * 2
+    assert rel(db_.numpy().reshape(4, H), db_ref) <= tol * 2
+    c.close()
