@@ -1,0 +1,251 @@
+"""Layers with the reference's names and call protocol (lib/layertypes, lib/transformer).
+
+`Layer.call` builds on first use and then runs `forward` (lib/layertypes/layer.dart:80-85).
+Every layer accepts a batch of sequences flattened into rows ([n_seq * seq_len, features]); a
+single sequence (n_seq = 1) is exactly the reference's `Tensor<Matrix>` input.  The reference
+draws its initial weights from an unseeded `Random()`; here each layer takes an explicit
+`seed` and uses the counter-based generator of `synth`.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import numpy as np
+
+from . import synth
+from . import tensor as T
+from .tensor import Tensor
+
+
+class Layer:
+    """lib/layertypes/layer.dart:48-86."""
+
+    name = "Layer"
+
+    def __init__(self):
+        self._built = False
+
+    @property
+    def parameters(self) -> List[Tensor]:
+        return []
+
+    def build(self, x):
+        self._built = True
+
+    def forward(self, x):
+        raise NotImplementedError
+
+    def call(self, x):
+        if not self._built:
+            self.build(x)
+        return self.forward(x)
+
+    __call__ = call
+
+
+class DenseLayerMatrix(Layer):
+    """act(X.W + b), W [in x out] (lib/layertypes/denseLayer.dart:76-126); He-normal weights
+    (:93-100), zero bias."""
+
+    name = "dense_matrix"
+
+    def __init__(self, outputSize: int, activation: Optional[str] = None, seed: int = 0, weights=None, bias=None,
+                 precision: int = -1):
+        super().__init__()
+        self.outputSize, self.activation, self.seed, self.precision = outputSize, activation, seed, precision
+        self._w0, self._b0 = weights, bias
+        self.weights: Optional[Tensor] = None
+        self.biases: Optional[Tensor] = None
+
+    @property
+    def parameters(self):
+        return [self.weights, self.biases]
+
+    def build(self, x: Tensor):
+        fan_in = x.shape[1]
+        w = self._w0 if self._w0 is not None else synth.normal(self.seed, 0, (fan_in, self.outputSize), math.sqrt(2.0 / fan_in))
+        b = self._b0 if self._b0 is not None else np.zeros(self.outputSize, dtype=np.float32)
+        self.weights, self.biases = Tensor(w, x.ctx), Tensor(b, x.ctx)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return T.denseMatrix(x, self.weights, self.biases, self.activation, self.precision)
+
+
+class LayerNormalization(Layer):
+    """lib/transformer/layerNormalization.dart:11-44: gamma = 1, beta = 0, epsilon = 1e-5."""
+
+    name = "layer_norm"
+
+    def __init__(self, epsilon: float = 1e-5):
+        super().__init__()
+        self.epsilon = epsilon
+        self.gamma = self.beta = None
+
+    @property
+    def parameters(self):
+        return [self.gamma, self.beta]
+
+    def build(self, x: Tensor):
+        d = x.shape[1]
+        self.gamma, self.beta = Tensor(np.ones(d, dtype=np.float32), x.ctx), Tensor(np.zeros(d, dtype=np.float32), x.ctx)
+        super().build(x)
+
+    def forward(self, x: Tensor, residual: Optional[Tensor] = None, alias_residual_grad: bool = False) -> Tensor:
+        return T.layerNorm(x, self.gamma, self.beta, self.epsilon, residual, alias_residual_grad)
+
+    def call(self, x, residual=None, alias_residual_grad=False):
+        if not self._built:
+            self.build(x)
+        return self.forward(x, residual, alias_residual_grad)
+
+    __call__ = call
+
+
+class MultiHeadAttention(Layer):
+    """numHeads heads of width dModel/numHeads followed by the output projection Wo, no biases
+    (lib/transformer/multiHeadAttentionLayer.dart:24-85, heads as in
+    lib/layertypes/singleHeadAttentionLayer.dart:25-90).
+
+    The per-head Wq, Wk, Wv [dModel x dK] live side by side in ONE matrix Wqkv
+    [dModel x 3*dModel] laid out [Q heads | K heads | V heads], so columns h*dK..(h+1)*dK of each
+    third are exactly head h's reference matrix and X.Wqkv is a single product."""
+
+    name = "multi_head_attention"
+
+    def __init__(self, numHeads: int, dModel: int, seq_len: Optional[int] = None, causal: bool = False, seed: int = 0,
+                 head_weights=None, Wo=None, precision: int = -1):
+        super().__init__()
+        assert dModel % numHeads == 0
+        self.numHeads, self.dModel, self.dK = numHeads, dModel, dModel // numHeads
+        self.seq_len, self.causal, self.seed, self.precision = seq_len, causal, seed, precision
+        self._heads0, self._wo0 = head_weights, Wo
+        self.Wqkv = self.Wo = None
+        self.lastAttentionWeights = None
+
+    @staticmethod
+    def pack_heads(heads):
+        """[(Wq,Wk,Wv)] per head -> Wqkv [dModel x 3*dModel]."""
+        return np.concatenate([np.concatenate([h[i] for h in heads], axis=1) for i in range(3)], axis=1)
+
+    @staticmethod
+    def unpack_heads(wqkv, numHeads):
+        d = wqkv.shape[1] // 3
+        dk = d // numHeads
+        return [tuple(wqkv[:, i * d + h * dk:i * d + (h + 1) * dk] for i in range(3)) for h in range(numHeads)]
+
+    @property
+    def parameters(self):
+        return [self.Wqkv, self.Wo]
+
+    def build(self, x: Tensor):
+        d = self.dModel
+        a = math.sqrt(1.0 / d)  # uniform(+-sqrt(1/rows)), singleHeadAttentionLayer.dart:51-56
+        if self._heads0 is not None:
+            wqkv = self.pack_heads(self._heads0)
+        else:
+            wqkv = synth.uniform(self.seed, 0, (d, 3 * d), -a, a)
+        wo = self._wo0 if self._wo0 is not None else synth.uniform(self.seed, 1, (d, d), -a, a)
+        self.Wqkv, self.Wo = Tensor(np.ascontiguousarray(wqkv, dtype=np.float32), x.ctx), Tensor(wo, x.ctx)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        S = self.seq_len or x.shape[0]
+        n_seq = x.shape[0] // S
+        qkv = T.denseMatrix(x, self.Wqkv, None, None, self.precision)
+        o = T.attentionCore(qkv, n_seq, S, self.numHeads, self.dK, self.causal, self.precision)
+        self.lastAttentionWeights = o.attention_weights
+        return T.denseMatrix(o, self.Wo, None, None, self.precision)
+
+
+class SingleHeadAttention(MultiHeadAttention):
+    """lib/layertypes/singleHeadAttentionLayer.dart:25-90 (one head, no output projection)."""
+
+    name = "single_head_attention"
+
+    def __init__(self, dModel: int, dK: int, dV: int, seq_len=None, causal=False, seed: int = 0, weights=None, precision=-1):
+        assert dK == dV == dModel, "the fused kernel path covers dK = dV = dModel for a single head"
+        super().__init__(1, dModel, seq_len, causal, seed, [weights] if weights is not None else None, None, precision)
+
+    @property
+    def parameters(self):
+        return [self.Wqkv]
+
+    def forward(self, x: Tensor) -> Tensor:
+        S = self.seq_len or x.shape[0]
+        qkv = T.denseMatrix(x, self.Wqkv, None, None, self.precision)
+        o = T.attentionCore(qkv, x.shape[0] // S, S, 1, self.dK, self.causal, self.precision)
+        self.lastAttentionWeights = o.attention_weights
+        return o
+
+
+class TransformerEncoderBlock(Layer):
+    """Post-LN block h = LN1(x + MHA(x)), y = LN2(h + FFN(h)), FFN = Dense(dff, ReLU) -> Dense(dModel)
+    (lib/transformer/transformerEncodingLayer.dart:21-71)."""
+
+    name = "transformer_encoder_block"
+
+    def __init__(self, dModel: int, numHeads: int, dff: int, seq_len=None, causal=False, seed: int = 0, params=None,
+                 precision: int = -1):
+        super().__init__()
+        p = params or {}
+        self.attention = MultiHeadAttention(numHeads, dModel, seq_len, causal, seed, p.get("heads"), p.get("Wo"), precision)
+        self.norm1, self.norm2 = LayerNormalization(), LayerNormalization()
+        self.ffn1 = DenseLayerMatrix(dff, "relu", seed + 1, p.get("W1"), p.get("b1"), precision)
+        self.ffn2 = DenseLayerMatrix(dModel, None, seed + 2, p.get("W2"), p.get("b2"), precision)
+        self._p0 = p
+
+    @property
+    def parameters(self):
+        return (self.attention.parameters + self.norm1.parameters + self.ffn1.parameters + self.ffn2.parameters +
+                self.norm2.parameters)
+
+    def build(self, x: Tensor):
+        for layer in (self.attention, self.norm1, self.norm2):
+            layer.build(x)
+        for name, layer in (("1", self.norm1), ("2", self.norm2)):
+            if "g" + name in self._p0:
+                layer.gamma = Tensor(self._p0["g" + name], x.ctx)
+                layer.beta = Tensor(self._p0["be" + name], x.ctx)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        a = self.attention(x)
+        h = self.norm1(x, residual=a, alias_residual_grad=True)
+        f = self.ffn2(self.ffn1(h))
+        return self.norm2(h, residual=f, alias_residual_grad=True)
+
+
+class EmbeddingLayer(Layer):
+    """Row gather by token id (lib/transformer/embeddingLayer.dart:18-69), init uniform(+-0.01)
+    (:38).  With `positional`, the reference's PositionalEncoding table
+    (lib/transformer/positionalEncodingLayer.dart:15-66) is added in the same pass."""
+
+    name = "embedding"
+
+    def __init__(self, vocabSize: int, embeddingDimension: int, positional_max_len: int = 0, seed: int = 0, table=None):
+        super().__init__()
+        self.vocabSize, self.embeddingDimension, self.seed = vocabSize, embeddingDimension, seed
+        self.positional_max_len, self._t0 = positional_max_len, table
+        self.embeddings = self.pe = None
+
+    @property
+    def parameters(self):
+        return [self.embeddings]
+
+    def build_on(self, ctx):
+        t = self._t0 if self._t0 is not None else synth.uniform(self.seed, 0, (self.vocabSize, self.embeddingDimension), -0.01, 0.01)
+        self.embeddings = Tensor(t, ctx)
+        if self.positional_max_len:
+            self.pe = ctx.empty(self.positional_max_len, self.embeddingDimension)
+            ctx.call("fml_positional_table", self.pe, self.positional_max_len, self.embeddingDimension)
+        self._built = True
+
+    def call(self, ids, ctx=None):
+        """ids: DeviceArray of int32 token ids (any shape, read flat)."""
+        if not self._built:
+            self.build_on(ctx or ids.ctx)
+        return T.embeddingLookup(self.embeddings, ids, self.pe, self.positional_max_len)
+
+    __call__ = call

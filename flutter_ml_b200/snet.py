@@ -1,0 +1,67 @@
+"""SNetwork: the reference's model container (lib/nets/snet.dart:34-157)."""
+from __future__ import annotations
+
+import time
+from typing import List
+
+from . import tensor as T
+from .layers import Layer
+from .tensor import Tensor
+
+
+class SNetwork(Layer):
+    name = "snetwork"
+
+    def __init__(self, layers: List[Layer]):
+        super().__init__()
+        self.layers = layers
+        self.optimizer = None
+
+    @property
+    def parameters(self):
+        return [p for layer in self.layers for p in layer.parameters]
+
+    def predict(self, x: Tensor) -> Tensor:
+        return self.forward(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        """snet.dart:51-57."""
+        for layer in self.layers:
+            x = layer.call(x)
+        return x
+
+    def call(self, x):
+        return self.forward(x)
+
+    def compile(self, configuredOptimizer):
+        self.optimizer = configuredOptimizer
+
+    def fit(self, inputs: List[Tensor], targets: List[Tensor], epochs: int, loss=T.mseMatrix, verbose: bool = False):
+        """One optimizer step per sample: forward, loss, backward, step, zeroGrad
+        (snet.dart:71-85).  Returns the average loss of each epoch."""
+        assert self.optimizer is not None, "call compile(optimizer) first"
+        t0 = time.perf_counter()
+        history = []
+        for epoch in range(epochs):
+            total = 0.0
+            for x, y in zip(inputs, targets):
+                out = self.forward(x)
+                l = loss(out, y)
+                l.backward()
+                self.optimizer.step()
+                self.optimizer.zeroGrad()
+                total += float(l.numpy()[0])
+            history.append(total / max(1, len(inputs)))
+            if verbose:
+                print(f"epoch {epoch + 1}/{epochs} avg loss {history[-1]:.6f}")
+        self.last_fit_seconds = time.perf_counter() - t0
+        return history
+
+    def evaluate(self, inputs: List[Tensor], targets: List[Tensor]) -> float:
+        """Fraction of samples whose rounded prediction equals the target (snet.dart:144-156)."""
+        import numpy as np
+        ok = 0
+        for x, y in zip(inputs, targets):
+            if np.array_equal(np.round(self.forward(x).numpy()), np.round(y.numpy())):
+                ok += 1
+        return ok / max(1, len(inputs))
