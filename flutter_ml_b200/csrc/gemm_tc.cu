@@ -22,6 +22,16 @@
 //             (next 4 k), k-step of 8 elements = +1024 B.
 // So the reference's materialised transposes (tensor.dart:877-884, 908-915, 927-934) never exist.
 //
+// Two kernel shapes share the code (template parameter PAIR):
+//   single  one CTA per 128 x BN tile, tcgen05 cta_group::1, 4 stages of 48 KiB.
+//   pair    a cluster of two CTAs per 256 x 256 tile, tcgen05 cta_group::2: each CTA stages its own
+//           128 rows of A and HALF of the B tile (128 columns), the leader CTA issues one
+//           M = 256 MMA that reads both CTAs' shared memory, and each CTA keeps the accumulator
+//           rows it owns in its own TMEM.  Shared-memory fill per flop drops by a third and the
+//           ring grows to 6 stages of 32 KiB, which is what feeds the tensor pipe on large
+//           problems.  Loads carry no multicast qualifier; the peer's loads signal the leader's
+//           full barrier, and tcgen05.commit arrives on both CTAs' empty barriers.
+//
 // 3xTF32: a pre-pass writes hi = rna_tf32(x) and lo = x - hi for both operands into the
 // context's scratch arena; the K loop then runs three segments (lo.hi, hi.lo, hi.hi) into the
 // same accumulator, small terms first.
@@ -29,17 +39,21 @@
 // Every wait on an mbarrier is bounded (2 s of %globaltimer); on expiry the kernel records a
 // code in *status, raises a CTA-wide abort flag, and all roles fall through to the common
 // tail, which frees TMEM.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 32;
-constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 4;    // 16 KiB
-constexpr int B_STAGE_BYTES = 256 * BK * 4;   // 32 KiB (sized for BN = 256)
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+template <bool PAIR> struct Cfg {
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int B_STAGE_BYTES = (PAIR ? 128 : 256) * BK * 4;  // B columns staged per CTA
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -49,6 +63,7 @@ struct TcParams {
   int tiles_m, tiles_n, nb1, nb2;
   int BN;
   int a_mn, b_mn;  // 1 = MN-major operand
+  int a_blk, b_blk;  // MN-major operand is loaded as ONE 5-D box of 32-column blocks (needs cols % 32 == 0)
   int nseg;        // 1 (TF32) or 3 (3xTF32)
   int kblocks;
   float* C;
@@ -59,6 +74,7 @@ struct TcParams {
   float alpha, beta;
   int* status;
   uint32_t idesc;
+  int debug;  // diagnostics only: 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -114,6 +130,57 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm,
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1,
+                                                 int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+// cta_group::2 form: the completion is signalled on the LEADER CTA's barrier (bit 24 of a
+// shared::cluster address selects the odd CTA of a pair; clearing it names the even one)
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
+                                                 int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(tm), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at the same offset in every CTA named by the mask
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(cta_mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(bar), "r"(cta));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(r) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate) {
@@ -175,16 +242,20 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, int t, int& b, in
   tn = rr / gm;
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmAlo, const __grid_constant__ CUtensorMap tmBlo,
                const TcParams p) {
+  constexpr int STAGES = Cfg<PAIR>::STAGES;
+  constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
+  constexpr int CTAS = PAIR ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
-  // barrier layout (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2], then tmem slot + abort flag
+  // barrier layout (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], then tmem slot + abort flag
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
@@ -194,32 +265,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader of the pair
+  const int unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;     // tile-loop start of this CTA (pair)
+  const int unit_stride = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(full_bar(s), 1);   // the leader's arrive.expect_tx (+ transaction bytes of both CTAs)
+      mbar_init(empty_bar(s), 1);  // one tcgen05.commit
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 4 * CTAS);  // every epilogue warp of the pair
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tiles_m * p.tiles_n * p.nb1 * p.nb2;
   const int kiters = p.kblocks * p.nseg;
-  const uint32_t b_stage_bytes = (uint32_t)p.BN * BK * 4;
+  const int bn_cta = PAIR ? (p.BN >> 1) : p.BN;            // B columns this CTA stages
+  const uint32_t b_stage_bytes = (uint32_t)bn_cta * BK * 4;
+  const int tile_m = PAIR ? 2 * BM : BM;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -227,11 +309,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < num_tiles && ok; t += unit_stride) {
         int b, tm, tn;
         tile_coords(p, t, b, tm, tn);
         const int b1 = b % p.nb1, b2 = b / p.nb1;
-        const int m0 = tm * BM, n0 = tn * p.BN;
+        const int m0 = tm * tile_m + (int)rank * BM;
+        const int n0 = tn * p.BN + (int)rank * bn_cta;
         for (int it = 0; it < kiters; it++) {
           ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1);
           if (!ok) break;
@@ -242,24 +325,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const CUtensorMap* tb = (p.nseg == 3 && seg == 1) ? &tmBlo : &tmB;
           const uint32_t sa = smem_base + s * STAGE_BYTES;
           const uint32_t sb = sa + A_STAGE_BYTES;
-          mbar_expect_tx(full_bar(s), A_STAGE_BYTES + b_stage_bytes);
+          if (p.debug & 1) {
+            if (rank == 0) mbar_arrive(full_bar(s));
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+            continue;
+          }
+          if (rank == 0) mbar_expect_tx(full_bar(s), CTAS * (A_STAGE_BYTES + b_stage_bytes));
+          auto load = [&](uint32_t dst, const CUtensorMap* tmap, int c0, int c1) {
+            if (PAIR) tma_load_4d_pair(dst, tmap, full_bar(s), c0, c1, b1, b2);
+            else tma_load_4d(dst, tmap, full_bar(s), c0, c1, b1, b2);
+          };
+          // One TMA instruction costs ~64 issue cycles whatever its size, so an MN-major operand is
+          // fetched as one 5-D box {32 columns, 32 k-rows, blocks} when its row length allows it.
+          auto load_blocks = [&](uint32_t dst, const CUtensorMap* tmap, int c0) {
+            if (PAIR) tma_load_5d_pair(dst, tmap, full_bar(s), 0, k0, c0 >> 5, b1, b2);
+            else tma_load_5d(dst, tmap, full_bar(s), 0, k0, c0 >> 5, b1, b2);
+          };
           if (p.a_mn) {
-            for (int j = 0; j < BM / 32; j++) tma_load_4d(sa + j * 4096, ta, full_bar(s), m0 + 32 * j, k0, b1, b2);
+            if (p.a_blk) load_blocks(sa, ta, m0);
+            else for (int j = 0; j < BM / 32; j++) load(sa + j * 4096, ta, m0 + 32 * j, k0);
           } else {
-            tma_load_4d(sa, ta, full_bar(s), k0, m0, b1, b2);
+            load(sa, ta, k0, m0);
           }
           if (p.b_mn) {
-            for (int j = 0; j < p.BN / 32; j++) tma_load_4d(sb + j * 4096, tb, full_bar(s), n0 + 32 * j, k0, b1, b2);
+            if (p.b_blk) load_blocks(sb, tb, n0);
+            else for (int j = 0; j < bn_cta / 32; j++) load(sb + j * 4096, tb, n0 + 32 * j, k0);
           } else {
-            tma_load_4d(sb, tb, full_bar(s), k0, n0, b1, b2);
+            load(sb, tb, k0, n0);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -268,7 +368,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t a_lbo = p.a_mn ? 4096u : 16u, b_lbo = p.b_mn ? 4096u : 16u;
       const uint32_t a_kstep = p.a_mn ? (1024u >> 4) : (32u >> 4);
       const uint32_t b_kstep = p.b_mn ? (1024u >> 4) : (32u >> 4);
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < num_tiles && ok; t += unit_stride) {
         ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, 2);
         if (!ok) break;
         tc_fence_after();
@@ -281,16 +381,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sb = sa + A_STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(sa, a_lbo, p.a_mn ? 512u : 1024u, p.a_mn ? 1u : 2u);
           const uint64_t bdesc = make_smem_desc(sb, b_lbo, p.b_mn ? 512u : 1024u, p.b_mn ? 1u : 2u);
+          if (p.debug & 2) {
+            if (PAIR) mbar_arrive_remote(empty_bar(s), 1);
+            mbar_arrive(empty_bar(s));
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+            continue;
+          }
 #pragma unroll
           for (int k = 0; k < BK / 8; k++) {
-            umma_tf32(tmem_d, adesc + (uint64_t)(k * a_kstep), bdesc + (uint64_t)(k * b_kstep), p.idesc,
-                      (it > 0 || k > 0) ? 1u : 0u);
+            const uint64_t ad = adesc + (uint64_t)(k * a_kstep), bd = bdesc + (uint64_t)(k * b_kstep);
+            const uint32_t accum = (it > 0 || k > 0) ? 1u : 0u;
+            if (PAIR) umma_tf32_pair(tmem_d, ad, bd, p.idesc, accum);
+            else umma_tf32(tmem_d, ad, bd, p.idesc, accum);
           }
-          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if (PAIR) umma_commit_pair(empty_bar(s), 3);
+          else umma_commit(empty_bar(s));
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull_bar(acc));  // accumulator complete
+        // accumulator complete (each CTA of a pair holds its own 128 rows)
+        if (PAIR) umma_commit_pair(tfull_bar(acc), 3);
+        else umma_commit(tfull_bar(acc));
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
       }
     }
@@ -304,11 +416,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         ((p.sC1 & 3) == 0) && ((p.sC2 & 3) == 0) &&
                         (p.Z == nullptr || (reinterpret_cast<uintptr_t>(p.Z) & 15) == 0) &&
                         (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = unit; t < num_tiles && ok; t += unit_stride) {
       int b, tm, tn;
       tile_coords(p, t, b, tm, tn);
       const int b1 = b % p.nb1, b2 = b / p.nb1;
-      const int m0 = tm * BM, n0 = tn * p.BN;
+      const int m0 = tm * tile_m + (int)rank * BM, n0 = tn * p.BN;
       ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, 4);
       if (!ok) break;
       tc_fence_after();
@@ -361,18 +473,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (PAIR && rank != 0) mbar_arrive_remote(tempty_bar(acc), 0);  // the issuer lives in the leader
+        else mbar_arrive(tempty_bar(acc));
+      }
       if (++acc == 2) { acc = 0; acc_ph ^= 1; }
     }
   }
 
-  // common tail: everyone arrives, then the allocating warp frees TMEM
+  // common tail: everyone arrives (both CTAs of a pair: the peer's barriers and TMEM stay alive
+  // until nothing can signal or read them), then the allocating warp frees TMEM
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();
   tc_fence_after();
   if (warp == 1) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -418,9 +536,11 @@ EncodeTiledFn get_encode_fn() {
 
 // Rank-4 map {cols, rows, nb1, nb2} over a row-major matrix with two batch levels.
 int32_t make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, int64_t ld, int64_t nb1, int64_t nb2,
-                  int64_t s1, int64_t s2, int box_c, int box_r, bool mn_major, CUtensorMap* out) {
-  // box_r carries the swizzle kind in the cache key: MN-major boxes are always 32 rows of the 32B-atom kind
-  auto key = std::make_tuple((const void*)base, cols, rows, ld, nb1, nb2, s1, s2, box_c, mn_major ? -box_r : box_r);
+                  int64_t s1, int64_t s2, int box_c, int box_r, bool mn_major, int blocks, CUtensorMap* out) {
+  // blocks > 0: rank-5 map {32, rows, cols/32, nb1, nb2} with box {32, 32, blocks, 1, 1} (MN-major, cols % 32 == 0).
+  // box_r carries the layout kind in the cache key: negative = MN-major (32B-atom swizzle), offset by the block count
+  auto key = std::make_tuple((const void*)base, cols, rows, ld, nb1, nb2, s1, s2, box_c,
+                             mn_major ? -(box_r + 1000 * blocks) : box_r);
   auto it = ctx->tmaps.find(key);
   if (it != ctx->tmaps.end()) {
     *out = it->second;
@@ -431,11 +551,19 @@ int32_t make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, i
   // unused batch levels get a harmless, 16-byte-multiple stride
   if (nb1 <= 1) s1 = rows * ld;
   if (nb2 <= 1) s2 = (nb1 <= 1 ? rows * ld : s1 * nb1);
-  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(nb1 < 1 ? 1 : nb1), (cuuint64_t)(nb2 < 1 ? 1 : nb2)};
-  cuuint64_t strides[3] = {(cuuint64_t)ld * 4, (cuuint64_t)s1 * 4, (cuuint64_t)s2 * 4};
-  cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)box_r, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+  cuuint64_t dims[5] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(nb1 < 1 ? 1 : nb1), (cuuint64_t)(nb2 < 1 ? 1 : nb2), 1};
+  cuuint64_t strides[4] = {(cuuint64_t)ld * 4, (cuuint64_t)s1 * 4, (cuuint64_t)s2 * 4, 0};
+  cuuint32_t box[5] = {(cuuint32_t)box_c, (cuuint32_t)box_r, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  int rank = 4;
+  if (blocks > 0) {
+    rank = 5;
+    dims[0] = 32; dims[1] = (cuuint64_t)rows; dims[2] = (cuuint64_t)(cols / 32);
+    dims[3] = (cuuint64_t)(nb1 < 1 ? 1 : nb1); dims[4] = (cuuint64_t)(nb2 < 1 ? 1 : nb2);
+    strides[0] = (cuuint64_t)ld * 4; strides[1] = 128; strides[2] = (cuuint64_t)s1 * 4; strides[3] = (cuuint64_t)s2 * 4;
+    box[0] = 32; box[1] = 32; box[2] = (cuuint32_t)blocks; box[3] = 1; box[4] = 1;
+  }
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<float*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -451,7 +579,7 @@ int32_t make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, i
   return FML_OK;
 }
 
-uint32_t make_idesc(int BN, int a_mn, int b_mn) {
+uint32_t make_idesc(int M, int BN, int a_mn, int b_mn) {
   uint32_t d = 0;
   d |= 1u << 4;                    // accumulator format F32
   d |= 2u << 7;                    // A format TF32
@@ -459,7 +587,7 @@ uint32_t make_idesc(int BN, int a_mn, int b_mn) {
   d |= (uint32_t)(a_mn & 1) << 15; // A major-ness (0 = K, 1 = MN)
   d |= (uint32_t)(b_mn & 1) << 16; // B major-ness
   d |= (uint32_t)(BN >> 3) << 17;  // N / 8
-  d |= (uint32_t)(BM >> 4) << 24;  // M / 16
+  d |= (uint32_t)(M >> 4) << 24;   // M / 16 (256 spans both CTAs of a pair)
   return d;
 }
 
@@ -477,18 +605,33 @@ bool fml_gemm_tc_eligible(const fml_gemm_desc* d) {
 int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
   static bool attr_set = false;
   if (!attr_set) {
-    FML_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    FML_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES));
+    FML_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
     attr_set = true;
   }
   const int nb1 = d->batch1 < 1 ? 1 : d->batch1, nb2 = d->batch2 < 1 ? 1 : d->batch2;
-  const int tiles_m = (d->M + BM - 1) / BM;
+  // pair mode (256 x 256 tiles over two CTAs) when the problem has enough such tiles to occupy the
+  // machine; FML_GEMM_PAIR=0/1 forces the choice (diagnostics)
+  bool pair = d->M > 128 && d->N > 128 &&
+              (long long)((d->M + 255) / 256) * ((d->N + 255) / 256) * nb1 * nb2 >= ctx->sm_count / 4;
+  {
+    static int force = -2;
+    if (force == -2) {
+      const char* e = getenv("FML_GEMM_PAIR");
+      force = e ? atoi(e) : -1;
+    }
+    if (force >= 0) pair = force != 0;
+  }
+  const int tile_m = pair ? 2 * BM : BM;
+  const int tiles_m = (d->M + tile_m - 1) / tile_m;
   // widest tile that still gives every SM work
   int BN = 64;
-  for (int bn : {256, 128, 64}) {
+  if (pair) BN = 256;
+  else for (int bn : {256, 128, 64}) {
     long long tiles = (long long)tiles_m * ((d->N + bn - 1) / bn) * nb1 * nb2;
     if (d->N > bn / 2 && tiles >= ctx->sm_count) { BN = bn; break; }
   }
-  if (BN == 64) {
+  if (BN == 64 && !pair) {
     // small problem: nothing fills the machine; prefer the tile that wastes least of N
     BN = d->N > 128 ? (d->N > 192 ? 256 : 128) : (d->N > 64 ? 128 : 64);
     long long t256 = (long long)tiles_m * ((d->N + 255) / 256) * nb1 * nb2;
@@ -528,13 +671,15 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
 
   CUtensorMap tmA, tmB, tmAlo, tmBlo;
   int32_t rc;
+  const int a_blk = (a_mn && a_cols % 32 == 0) ? BM / 32 : 0;
+  const int b_blk = (b_mn && b_cols % 32 == 0) ? (pair ? BN / 2 : BN) / 32 : 0;
   const int a_box_c = 32, a_box_r = a_mn ? 32 : BM;
-  const int b_box_c = 32, b_box_r = b_mn ? 32 : BN;
-  if ((rc = make_tmap(ctx, A, a_cols, a_rows, lda, nb1, nb2, sA1, sA2, a_box_c, a_box_r, a_mn, &tmA))) return rc;
-  if ((rc = make_tmap(ctx, B, b_cols, b_rows, ldb, nb1, nb2, sB1, sB2, b_box_c, b_box_r, b_mn, &tmB))) return rc;
+  const int b_box_c = 32, b_box_r = b_mn ? 32 : (pair ? BN / 2 : BN);
+  if ((rc = make_tmap(ctx, A, a_cols, a_rows, lda, nb1, nb2, sA1, sA2, a_box_c, a_box_r, a_mn, a_blk, &tmA))) return rc;
+  if ((rc = make_tmap(ctx, B, b_cols, b_rows, ldb, nb1, nb2, sB1, sB2, b_box_c, b_box_r, b_mn, b_blk, &tmB))) return rc;
   if (Alo) {
-    if ((rc = make_tmap(ctx, Alo, a_cols, a_rows, lda, nb1, nb2, sA1, sA2, a_box_c, a_box_r, a_mn, &tmAlo))) return rc;
-    if ((rc = make_tmap(ctx, Blo, b_cols, b_rows, ldb, nb1, nb2, sB1, sB2, b_box_c, b_box_r, b_mn, &tmBlo))) return rc;
+    if ((rc = make_tmap(ctx, Alo, a_cols, a_rows, lda, nb1, nb2, sA1, sA2, a_box_c, a_box_r, a_mn, a_blk, &tmAlo))) return rc;
+    if ((rc = make_tmap(ctx, Blo, b_cols, b_rows, ldb, nb1, nb2, sB1, sB2, b_box_c, b_box_r, b_mn, b_blk, &tmBlo))) return rc;
   } else {
     tmAlo = tmA;
     tmBlo = tmB;
@@ -543,17 +688,42 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
   TcParams p;
   p.M = d->M; p.N = d->N; p.K = d->K;
   p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.nb1 = nb1; p.nb2 = nb2;
-  p.BN = BN; p.a_mn = a_mn; p.b_mn = b_mn;
+  p.BN = BN; p.a_mn = a_mn; p.b_mn = b_mn; p.a_blk = a_blk; p.b_blk = b_blk;
   p.nseg = (precision == FML_PREC_3XTF32) ? 3 : 1;
   p.kblocks = (d->K + BK - 1) / BK;
   p.C = d->C; p.Z = d->preact; p.bias = d->bias;
   p.ldc = d->ldc; p.sC1 = d->sC1; p.sC2 = d->sC2;
   p.act = d->act; p.alpha = d->alpha; p.beta = d->beta;
   p.status = ctx->d_status;
-  p.idesc = make_idesc(BN, a_mn, b_mn);
+  p.idesc = make_idesc(tile_m, BN, a_mn, b_mn);
+  {
+    static int dbg = -1;
+    if (dbg < 0) {
+      const char* e = getenv("FML_GEMM_DEBUG");
+      dbg = e ? atoi(e) : 0;
+    }
+    p.debug = dbg;
+  }
   const long long num_tiles = (long long)tiles_m * tiles_n * nb1 * nb2;
-  const int grid = (int)std::min<long long>(num_tiles, ctx->sm_count);
-  gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, p);
+  if (pair) {
+    const int clusters = (int)std::min<long long>(num_tiles, ctx->sm_count / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, p));
+  } else {
+    const int grid = (int)std::min<long long>(num_tiles, ctx->sm_count);
+    gemm_tc_kernel<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, p);
+  }
   FML_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
   ctx->last_gemm_path = 1;
   return FML_OK;
