@@ -43,40 +43,57 @@ def measured_peaks():
 class ClockSampler:
     """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
 
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc = index, None
+        self.index, self.proc, self.t0, self.t1 = index, None, None, None
 
     def start(self):
+        """Start sampling (the tool needs a moment to come up, so call this well before the timed region)."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                          "-lms", "20", "-i", str(self.index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
         self.proc.terminate()
         out, _ = self.proc.communicate()
-        sm, mx, reasons = [], None, set()
+        import datetime
+        sm, pw, mx, reasons = [], [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             try:
-                sm.append(float(f[0]))
-                mx = float(f[1])
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, mx_ = float(f[1]), float(f[2])
             except (ValueError, IndexError):
                 continue
-            for n, v in zip(names, f[2:6]):
+            mx = mx_
+            if self.t0 is not None and not (self.t0 <= ts <= self.t1 + 0.02):
+                continue  # outside the timed region
+            sm.append(clk)
+            try:
+                pw.append(float(f[3]))
+            except ValueError:
+                pass
+            for n, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        # the first sample may predate the load; keep the upper half as "under load"
-        med = statistics.median(sm) if sm else None
-        return {"sm_mhz": med, "sm_max_mhz": mx, "samples": len(sm), "reasons": sorted(reasons)}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "samples": len(sm),
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons)}
 
 
 def make_inputs(M, N, K, seed=1):
@@ -125,11 +142,14 @@ def time_sweep(ctx, reps=5):
     """fwd+bwd TFLOP/s for every size of the config-2 sweep (operands are re-used buffers)."""
     from flutter_ml_b200 import ops
     out = []
+    # random operands (all-zero data toggles fewer wires, draws less power and clocks higher)
+    pool = np.random.default_rng(1).standard_normal(1 << 22).astype(np.float32)
     for (M, N, K) in SWEEP:
         e = ctx.empty
         A, B, bias, dC = e(M, K), e(K, N), e(N), e(M, N)
         for a in (A, B, bias, dC):
-            ctx.zero(a)
+            h = np.resize(pool, a.size) * np.float32(1.0 / np.sqrt(K))
+            ctx.upload(h.reshape(a.shape), out=a)
         C, Z, dZ, dA, dB, db = e(M, N), e(M, N), e(M, N), e(M, K), e(K, N), e(N)
 
         def step():
@@ -152,7 +172,7 @@ def time_sweep(ctx, reps=5):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M=N=K of the timed step")
@@ -200,11 +220,12 @@ def main():
     host()  # uploads the operands once; they stay resident for the device-timed loop
 
     # ---- device-resident loop: per-launch events around the three GEMMs of the first steps
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         host.compute()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.mark_begin()
     launches0 = ctx.launches
     n_ev_steps = min(args.steps, 10)
     ctx.timer_start()
@@ -225,6 +246,7 @@ def main():
             host.compute()
     ms_total = ctx.timer_stop_ms()
     barrier()
+    sampler.mark_end()
     clocks = sampler.stop()
     launches = ctx.launches - launches0
     ms_total = max_over_ranks(ms_total)

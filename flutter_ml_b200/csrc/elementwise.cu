@@ -58,6 +58,43 @@ __global__ void act_bwd_kernel(int act, const float* __restrict__ s, const float
   }
 }
 
+// dx = dy * act'(saved) and db[c] += column sums of dx in ONE pass over the data: a block owns 128
+// columns (one float4 per lane) and a slab of rows; each warp walks its rows with 512-byte
+// coalesced loads, keeps four column partials per lane in registers, and the block issues one
+// atomic per column at the end.
+__global__ void __launch_bounds__(256) act_bwd_colsum_kernel(int act, const float* __restrict__ s,
+                                                             const float* __restrict__ dy, float* __restrict__ dx,
+                                                             float* db, long long rows, long long cols,
+                                                             long long rows_per_block) {
+  __shared__ float red[8][128];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long c = blockIdx.x * 128ll + lane * 4;
+  const long long r0 = blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < cols) {
+    for (long long r = r0 + warp; r < r1; r += 8) {
+      const long long o = r * cols + c;
+      const float4 sv = *reinterpret_cast<const float4*>(s + o);
+      const float4 g = *reinterpret_cast<const float4*>(dy + o);
+      float4 d;
+      d.x = g.x * fml_act_grad(act, sv.x); d.y = g.y * fml_act_grad(act, sv.y);
+      d.z = g.z * fml_act_grad(act, sv.z); d.w = g.w * fml_act_grad(act, sv.w);
+      *reinterpret_cast<float4*>(dx + o) = d;
+      acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+    }
+  }
+  red[warp][lane * 4 + 0] = acc.x; red[warp][lane * 4 + 1] = acc.y;
+  red[warp][lane * 4 + 2] = acc.z; red[warp][lane * 4 + 3] = acc.w;
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) t += red[w][threadIdx.x];
+    const long long col = blockIdx.x * 128ll + threadIdx.x;
+    if (col < cols) atomicAdd(db + col, t);
+  }
+}
+
 // ------------------------------------------------------------------ binary ops
 // mode 0: y = a + b; 1: y = a * b; 2: y = y + s * a (b unused)
 template <bool VEC>
@@ -249,6 +286,17 @@ int32_t fml_act_bwd(fml_ctx* ctx, int32_t act, const float* saved, const float* 
   FML_REQUIRE(ctx, act == FML_ACT_NONE || saved, "fml_act_bwd: saved tensor required");
   const long long n = rows * cols;
   if (act == FML_ACT_NONE) saved = dy;
+  if (dbias && !accumulate && cols % 4 == 0 && al16(saved) && al16(dy) && al16(dx)) {
+    const long long cb = (cols + 127) / 128;
+    long long rb = std::max<long long>(1, std::min<long long>((rows + 31) / 32, ((long long)ctx->sm_count * 8 + cb - 1) / cb));
+    const long long rows_per_block = (rows + rb - 1) / rb;
+    rb = (rows + rows_per_block - 1) / rows_per_block;
+    FML_REQUIRE(ctx, rb <= 65535, "fml_act_bwd: too many row slabs");
+    act_bwd_colsum_kernel<<<dim3((unsigned)cb, (unsigned)rb), 256, 0, ctx->stream>>>(act, saved, dy, dx, dbias, rows, cols,
+                                                                                    rows_per_block);
+    FML_LAUNCH_CHECK(ctx, "act_bwd_colsum_kernel");
+    return FML_OK;
+  }
   const bool vec = (n % 4 == 0) && al16(saved) && al16(dy) && al16(dx);
   int32_t rc = launch_vec(ctx, "act_bwd_kernel", vec, n, act_bwd_kernel<true>, act_bwd_kernel<false>, act, saved, dy, dx, n,
                           accumulate);
