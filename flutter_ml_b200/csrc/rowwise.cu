@@ -492,6 +492,55 @@ int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, fl
   return FML_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free softmax cross-entropy.
+//
+// fml_softmax_xent keeps its per-row losses in the context's scratch arena, which it grows with
+// cudaMalloc when a larger batch arrives.  Some callers must never reach an allocator: a host
+// framework whose own caching allocator already owns all of HBM (a cudaMalloc there fails or
+// fragments its pool), a serving loop that cannot afford the device-wide synchronisation cudaMalloc
+// and cudaFree imply, or code that runs while the allocator is locked.  For them the per-row
+// losses live in the fixed array below, which every GPU that loads this library holds until the
+// process exits (FML_XENT_STATIC_MAX_ROWS floats = 256 KiB).
+//
+// In host code the name `g_xent_static_rows` is only a stand-in for the symbol, not a device
+// address, so the set-up asks the runtime for the address once per device (with that device
+// current) and the launches pass the pointer it returned.
+__device__ __align__(256) float g_xent_static_rows[FML_XENT_STATIC_MAX_ROWS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_xent_static_ptr[kMaxDevices] = {};
+int g_xent_static_sms[kMaxDevices] = {};
+}  // namespace
+
+int32_t fml_softmax_xent_static(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum,
+                                int64_t rows, int32_t cols, float inv_count) {
+  FML_REQUIRE(ctx, z && labels && loss_sum && rows > 0 && cols > 0, "fml_softmax_xent_static: bad arguments");
+  if (rows > FML_XENT_STATIC_MAX_ROWS)
+    return fml_fail(ctx, FML_ERR_OOM,
+                    "fml_softmax_xent_static: " + std::to_string((long long)rows) + " rows exceed the fixed scratch of " +
+                        std::to_string(FML_XENT_STATIC_MAX_ROWS) + " rows; split the batch or use fml_softmax_xent");
+  const int dev = ctx->device;
+  FML_REQUIRE(ctx, dev >= 0 && dev < kMaxDevices, "fml_softmax_xent_static: device ordinal out of range");
+  if (!g_xent_static_ptr[dev]) {
+    // first call on this device: resolve the symbol (no allocation; do this before any stream capture)
+    FML_CUDA(ctx, cudaSetDevice(dev));
+    float* ptr = nullptr;
+    FML_CUDA(ctx, cudaGetSymbolAddress((void**)&ptr, g_xent_static_rows));
+    FML_REQUIRE(ctx, ptr != nullptr, "fml_softmax_xent_static: the scratch symbol has no device address");
+    g_xent_static_sms[dev] = ctx->sm_count;
+    g_xent_static_ptr[dev] = ptr;
+  }
+  float* row_loss = g_xent_static_ptr[dev];
+  // every row slot read by the final sum is written by this launch first, so nothing needs clearing
+  const int blocks = (int)std::max<long long>(1, std::min<long long>(rows, (long long)g_xent_static_sms[dev] * 8));
+  xent_kernel<<<blocks, 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+  final_sum_kernel<float><<<1, 256, 0, ctx->stream>>>(row_loss, rows, 1.0, loss_sum);
+  FML_LAUNCH_CHECK(ctx, "xent_kernel (static scratch)");
+  return FML_OK;
+}
+
 int32_t fml_mse(fml_ctx* ctx, const float* p, const float* t, float* dp, float* loss_sum, int64_t n, float upstream) {
   FML_REQUIRE(ctx, p && t && loss_sum && n > 0, "fml_mse: bad arguments");
   const int blocks = (int)std::max<long long>(1, std::min<long long>((n + 255) / 256, (long long)ctx->sm_count * 4));

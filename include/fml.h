@@ -189,6 +189,22 @@ int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, con
  * dz = (softmax(z) - onehot) * inv_count written in place of z when dz == z. */
 int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz,
                          float* loss_sum, int64_t rows, int32_t cols, float inv_count);
+/* Same computation and results as fml_softmax_xent, for callers that must not allocate.
+ * (No counterpart in the reference: it has neither this loss nor device memory management.)
+ * fml_softmax_xent may grow the context's scratch arena with cudaMalloc; this entry point never
+ * calls cudaMalloc, cudaFree or any allocating routine.  Its per-row scratch is a fixed array
+ * inside the library (FML_XENT_STATIC_MAX_ROWS floats = 256 KiB, held by every GPU that loads
+ * the library until the process exits).  Use it from hosts whose own allocator owns all device
+ * memory, or that cannot tolerate the device-wide synchronisation an allocation implies.
+ *   - rows > FML_XENT_STATIC_MAX_ROWS is refused with FML_ERR_OOM; split the batch.
+ *   - The first call on each device resolves the array's device address; make that call
+ *     before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents (nothing in it
+ *     needs clearing: each call overwrites the slots it reads).  Calls that overlap on the GPU,
+ *     from different streams or contexts of the same device, race on it: serialise them. */
+#define FML_XENT_STATIC_MAX_ROWS 65536
+int32_t fml_softmax_xent_static(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz,
+                                float* loss_sum, int64_t rows, int32_t cols, float inv_count);
 /* mseMatrix (tensor.dart:982-1011): loss_sum += mean((p-t)^2); dp = 2(p-t)/n * upstream. */
 int32_t fml_mse(fml_ctx* ctx, const float* p, const float* t, float* dp, float* loss_sum, int64_t n,
                 float upstream);
