@@ -1,0 +1,52 @@
+"""The shared library loads on a machine without a GPU and exports every symbol fml.h declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib_path():
+    from flutter_ml_b200 import _build
+    return _build.build()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fml.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b(?:int32_t|void|const char\*)\s+(\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_header_symbols_are_exported(lib_path):
+    lib = ctypes.CDLL(lib_path)
+    names = declared_symbols()
+    assert "fml_gemm" in names and "multiplyMatrices" in names and "benchtest" in names
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_python_prototypes_cover_the_header(lib_path):
+    from flutter_ml_b200 import _lib
+    assert set(declared_symbols()) == set(_lib.PROTOTYPES)
+
+
+def test_init_fails_loudly_without_a_device(lib_path):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from flutter_ml_b200 import _lib
+    with pytest.raises(_lib.FmlError, match="no CUDA device"):
+        _lib.Context()
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "flutter_ml_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith(".py"):
+                src = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle", src, flags=re.M) and "oracle." not in src, f

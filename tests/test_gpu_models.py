@@ -1,0 +1,129 @@
+"""Model-level parity: the reference-shaped layers on the GPU against the oracle's tape."""
+import numpy as np
+import pytest
+
+from tests.gpu_util import rel
+
+pytestmark = pytest.mark.gpu
+w64 = lambda x: np.ascontiguousarray(x, dtype=np.float64)  # noqa: E731
+
+# Whole-model tolerances (relative Frobenius error vs the float64 oracle): (outputs, gradients).
+#  - 3xTF32: 2e-5 / 5e-5.  This mode pins the LOGIC of every layer and of the tape.
+#  - TF32: a single product is within 1e-3 (5.5e-4 measured, test_gpu_kernels.py); outputs of a chain of
+#    products are held to 2e-3.  Gradients of these three models pass through ReLU gates
+#    (tensor.dart:1030), which are discontinuous: a pre-activation within ~5e-4 of zero can land on the
+#    other side of the gate than in float64, and a fraction f of flipped gates gives a relative gradient
+#    error of about sqrt(f) (f ~ 5e-4 -> ~2e-2) for ANY TF32 product, however exact the kernel is.  The
+#    gradient bound in TF32 mode is therefore 5e-2; per-kernel gradient parity at 1e-3 is asserted in
+#    test_gpu_kernels.py on identical gate inputs.
+TOLS = {0: (2e-3, 5e-2), 1: (2e-5, 5e-5)}
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_mlp_training_step_config1(orc, prec):
+    """Config 1 at full size: 784-128-64-10, batch 64, seed 0, one SGD step."""
+    from flutter_ml_b200 import _lib, models, synth
+    ctx = _lib.Context(precision=prec)
+    params = models.init_mlp(0)
+    X = synth.uniform(0, 0, (64, 784))
+    labels = synth.integers(0, 1, (64,), 10)
+    ref = orc.mlp_step(w64(X), labels, [w64(p) for p in params], lr=0.01, omp=True)
+    mlp = models.MLP(ctx, params, lr=0.01)
+    loss, logits, grads = mlp.train_step(ctx.upload(X), ctx.upload(labels), keep=True)
+    t_out, t_grad = TOLS[prec]
+    lg = logits.numpy()
+    assert rel(lg, ref["logits"]) <= t_out
+    assert np.array_equal(lg.argmax(1), ref["logits"].argmax(1))      # argmax-identical logits
+    assert abs(loss.numpy()[0] - ref["loss"]) <= t_out * abs(ref["loss"])
+    flat_ref = np.concatenate([np.pad(g.ravel(), (0, (-g.size) % 4)) for g in ref["grads"]])
+    assert rel(grads, flat_ref) <= t_grad
+    new = mlp.arena.values.numpy()
+    flat_new = np.concatenate([np.pad(p.ravel(), (0, (-p.size) % 4)) for p in ref["params"]])
+    assert rel(new, flat_new) <= 1e-5
+    assert ctx.device_status() == 0
+    ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+@pytest.mark.parametrize("causal", [True, False])
+def test_encoder_block_config3_scaled(orc, prec, causal):
+    """Config 3's block (post-LN, ReLU FFN, causal attention) at d=128, 4 heads, dff 256, seq 64, 3 sequences."""
+    from flutter_ml_b200 import _lib, models, synth
+    ctx = _lib.Context(precision=prec)
+    d, heads, dff, S, B = 128, 4, 256, 64, 3
+    p = models.init_block(2, d, heads, dff, std=0.08)
+    x, tgt = synth.normal(2, 500, (B, S, d)), synth.normal(2, 501, (B, S, d))
+    p64 = {k: (w64(v) if k != "heads" else [tuple(w64(w) for w in h) for h in v]) for k, v in p.items()}
+    ref = orc.encoder_block_fwd_bwd(w64(x), p64, w64(tgt), causal, omp=True)
+    y, loss, dx, grads = models.encoder_block_fwd_bwd(ctx, x, p, tgt, heads, causal)
+    t_out, t_grad = TOLS[prec]
+    assert rel(y, ref["y"]) <= t_out
+    assert abs(loss - ref["loss"]) <= t_out * abs(ref["loss"])
+    assert rel(dx, ref["dx"]) <= t_grad
+    for g, r in zip(grads, ref["grads"]):
+        assert rel(g, r) <= t_grad
+    assert ctx.device_status() == 0
+    ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_transformer_lm_step_config5_scaled(orc, prec):
+    """Config 5 scaled down (2 layers, d 128, 4 heads, dff 256, seq 32, vocab 1000, batch 4): loss, logits
+    argmax, every gradient, and the Adam update."""
+    from flutter_ml_b200 import _lib, models, synth
+    ctx = _lib.Context(precision=prec)
+    V, d, heads, dff, L, S, B = 1000, 128, 4, 256, 2, 32, 4
+    params = models.init_lm(4, V, d, heads, dff, L, std=0.05)
+    ids, labels = synth.integers(4, 100, (B, S), V), synth.integers(4, 101, (B, S), V)
+    conv = lambda b: {k: (w64(v) if k != "heads" else [tuple(w64(w) for w in h) for h in v]) for k, v in b.items()}  # noqa: E731
+    p64 = {"emb": w64(params["emb"]), "blocks": [conv(b) for b in params["blocks"]], "Whead": w64(params["Whead"]),
+           "bhead": w64(params["bhead"])}
+    ref = orc.lm_forward_backward(ids, labels, p64, B * S, True, omp=True)
+    lm = models.TransformerLM(ctx, params, S, heads, lr=1e-3)
+    loss, logits = lm.forward_backward(ctx.upload(ids.reshape(-1)), ctx.upload(labels.reshape(-1)), B * S, keep_logits=True)
+    t_out, t_grad = TOLS[prec]
+    lg = logits.numpy().reshape(B, S, V)
+    assert rel(lg, ref["logits"]) <= t_out
+    agree = (lg.argmax(-1) == ref["logits"].argmax(-1)).mean()
+    assert agree == 1.0 if prec == 1 else agree >= 0.99   # near-ties among 1000 random logits can flip under TF32
+    assert abs(loss.numpy()[0] - ref["loss"]) <= t_out * abs(ref["loss"])
+    for g, r in zip(lm.grads_in_reference_order(), ref["grads"]):
+        assert rel(g, r) <= t_grad
+    # Adam step on the whole arena equals the oracle's per-tensor update
+    ops = orc.Ops()
+    g_flat = lm.arena.grads.numpy().astype(np.float64)
+    w_flat = lm.arena.values.numpy().astype(np.float64)
+    m, v = np.zeros_like(w_flat), np.zeros_like(w_flat)
+    ops.adam_step(w_flat, g_flat, m, v, 1e-3, 1)
+    lm.optimizer.step()
+    assert rel(lm.arena.values.numpy(), w_flat) <= 1e-6
+    assert ctx.device_status() == 0
+    ctx.close()
+
+
+def test_snetwork_fit_xor():
+    """The reference's XOR demo (lib/nets/snet.dart:159-227): per-sample fit with mse lowers the loss."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200.layers import DenseLayerMatrix
+    from flutter_ml_b200.optimizers import SGD
+    from flutter_ml_b200.snet import SNetwork
+    from flutter_ml_b200.tensor import Tensor, set_default_context
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    set_default_context(ctx)
+    net = SNetwork([DenseLayerMatrix(8, "tanh", seed=5), DenseLayerMatrix(1, "sigmoid", seed=6)])
+    xs = [Tensor(np.array([[a, b]], dtype=np.float32), ctx) for a in (0, 1) for b in (0, 1)]
+    ys = [Tensor(np.array([[float(a ^ b)]], dtype=np.float32), ctx) for a in (0, 1) for b in (0, 1)]
+    net.predict(xs[0])
+    net.compile(SGD(net.parameters, 0.5))
+    hist = net.fit(xs, ys, epochs=300)
+    assert hist[-1] < 0.5 * hist[0]
+    assert net.evaluate(xs, ys) >= 0.75
+    ctx.close()
+
+
+def test_cudacaller_matmult_signature():
+    """CudaCaller.matmult(A, B, m, k, n) -> flat list of doubles (lib/cuda/cudacaller.dart:25-60)."""
+    from flutter_ml_b200.cuda import CudaCaller
+    m, k, n = 8, 16, 4
+    out = CudaCaller.matmult([1.0] * (m * k), [1.0] * (k * n), m, k, n)
+    assert isinstance(out, list) and len(out) == m * n and all(v == float(k) for v in out)
