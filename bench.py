@@ -121,6 +121,8 @@ def run_reference(args, rank):
     from oracle import oracle
     oracle.build()
     S = args.ref_size
+    # launchers such as torchrun export OMP_NUM_THREADS=1; this arm is meant to use every host thread
+    oracle.Ops(True).set_threads(os.cpu_count() or 1)
     cores = oracle.Ops(True).threads()
     for _ in range(min(args.warmup, 1)):
         cpu_step(S, S, S, True)

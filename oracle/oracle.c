@@ -33,6 +33,15 @@
 #define ORC_PAR_FOR
 #endif
 
+/* Number of OpenMP threads to use from now on (ignored by the single-thread build). */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -61,6 +61,9 @@ class Ops:
     def threads(self):
         return int(self.L.orc_threads())
 
+    def set_threads(self, n):
+        self.L.orc_set_threads(int(n))
+
     def matmul_fwd(self, A, B):
         M, N = A.shape
         P = B.shape[1]
