@@ -171,6 +171,58 @@ def time_sweep(ctx, reps=5):
     return out
 
 
+def time_membound(ctx, hbm_gbs, reps=5, rows=262144, params=1 << 28):
+    """Achieved HBM GB/s of the memory-bound kernels on footprints of 1 GiB and more (algorithmic bytes:
+    every input read once, every output written once)."""
+    pool = np.random.default_rng(2).standard_normal(1 << 22).astype(np.float32)
+
+    def filled(*shape, scale=1.0, positive=False):
+        a = ctx.empty(*shape)
+        h = np.resize(pool, a.size) * np.float32(scale)
+        ctx.upload(np.abs(h) if positive else h, out=a.reshape(a.size))
+        return a
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        ctx.sync()
+        ctx.timer_start()
+        for _ in range(reps):
+            fn()
+        return ctx.timer_stop_ms() / reps
+
+    out = []
+
+    def record(name, ms, nbytes, shape):
+        gbs = nbytes / ms / 1e6
+        out.append({"kernel": name, "shape": shape, "ms": round(ms, 4), "gbs": round(gbs, 1), "frac_hbm": round(gbs / hbm_gbs, 3)})
+
+    R, C = rows, 1024
+    n = R * C
+    x, dy = filled(R, C, scale=2.0), filled(R, C)
+    y, dx = ctx.empty(R, C), ctx.empty(R, C)
+    record("softmax_rows_fwd", timed(lambda: ctx.call("fml_softmax_rows_fwd", x, y, R, C, 0.125, 0)), 8 * n, [R, C])
+    record("softmax_rows_bwd", timed(lambda: ctx.call("fml_softmax_rows_bwd", y, dy, dx, R, C, 0.125, 0)), 12 * n, [R, C])
+    g, b = filled(C), filled(C)
+    xhat, rstd, dg, db = ctx.empty(R, C), ctx.empty(R), ctx.zeros(C), ctx.zeros(C)
+    record("layernorm_fwd", timed(lambda: ctx.call("fml_layernorm_fwd", x, None, g, b, y, xhat, rstd, R, C, 1e-5)), 12 * n, [R, C])
+    record("layernorm_bwd", timed(lambda: ctx.call("fml_layernorm_bwd", dy, g, xhat, rstd, dx, dg, db, R, C, 0)), 12 * n, [R, C])
+    record("act_bwd_gelu+dbias", timed(lambda: ctx.call("fml_act_bwd", 4, x, dy, dx, R, C, 0, dg)), 12 * n, [R, C])
+    for a in (y, dx, xhat):
+        a.free()
+    P = min(params, n)
+    w, gr = x.reshape(P), dy.reshape(P)
+    m, v = ctx.zeros(P), ctx.zeros(P)
+    record("sgd_step", timed(lambda: ctx.call("fml_sgd_step", w, gr, P, 1e-3, 1.0)), 12 * P, [P])
+    t = [0]
+
+    def adam():
+        t[0] += 1
+        ctx.call("fml_adam_step", w, gr, m, v, P, 1e-3, 0.9, 0.999, 1e-8, t[0], 1.0)
+    record("adam_step", timed(adam), 28 * P, [P])
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -182,6 +234,9 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-train", action="store_true")
+    ap.add_argument("--no-membound", action="store_true")
+    ap.add_argument("--membound-only", action="store_true", help="run only the memory-bound kernel sweep (profiling)")
+    ap.add_argument("--membound-rows", type=int, default=262144)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -214,6 +269,11 @@ def main():
 
     peaks = measured_peaks()
     ctx = _lib.Context(device=local_rank, precision=_lib.PREC_TF32)
+    if args.membound_only:
+        res = time_membound(ctx, peaks["hbm_gbs"], reps=2, rows=args.membound_rows)
+        print(json.dumps({"membound": res}), flush=True)
+        ctx.close()
+        return
     M = N = K = args.size
     flops_step = 6.0 * M * N * K
     host = ops.DenseFwdBwdHost(ctx, M, N, K, act="gelu")
@@ -293,6 +353,8 @@ def main():
 
     if rank == 0 and not args.no_sweep:
         line["sweep"] = time_sweep(ctx)
+    if rank == 0 and not args.no_membound:
+        line["membound"] = time_membound(ctx, peaks["hbm_gbs"], rows=args.membound_rows)
     if rank == 0 and not args.no_cpu:
         from oracle import oracle
         oracle.build()

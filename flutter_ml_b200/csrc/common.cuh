@@ -84,7 +84,7 @@ __device__ __forceinline__ float fml_act_grad(int act, float s) {
     case FML_ACT_TANH: return 1.f - s * s;
     case FML_ACT_GELU: {
       float cdf = 0.5f * (1.f + erff(s * 0.70710678118654752440f));
-      float pdf = 0.39894228040143267794f * expf(-0.5f * s * s);
+      float pdf = 0.39894228040143267794f * __expf(-0.5f * s * s);
       return cdf + s * pdf;
     }
     default: return 1.f;

@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(256) softmax_fwd_warp(const float* __restrict_
   for (long long r = warp0; r < rows; r += nwarps) {
     const int lim = causal_period > 0 ? min(cols, (int)(r % causal_period) + 1) : cols;
     const float4* xr = reinterpret_cast<const float4*>(x + r * cols);
+    // work in base 2: exp(s*x - m) = 2^(s*log2e*x - m'), one multiply folded into the scale
+    const float k = scale * 1.4426950408889634f;
     float v[NV * 4];
     float mx = NEG_INF;
 #pragma unroll
@@ -63,10 +65,10 @@ __global__ void __launch_bounds__(256) softmax_fwd_warp(const float* __restrict_
       const int c = (lane + 32 * i) * 4;
       float4 t = make_float4(NEG_INF, NEG_INF, NEG_INF, NEG_INF);
       if (c < lim) t = xr[lane + 32 * i];  // columns at or beyond lim are masked below
-      v[4 * i + 0] = (c + 0 < lim) ? t.x * scale : NEG_INF;
-      v[4 * i + 1] = (c + 1 < lim) ? t.y * scale : NEG_INF;
-      v[4 * i + 2] = (c + 2 < lim) ? t.z * scale : NEG_INF;
-      v[4 * i + 3] = (c + 3 < lim) ? t.w * scale : NEG_INF;
+      v[4 * i + 0] = (c + 0 < lim) ? t.x * k : NEG_INF;
+      v[4 * i + 1] = (c + 1 < lim) ? t.y * k : NEG_INF;
+      v[4 * i + 2] = (c + 2 < lim) ? t.z * k : NEG_INF;
+      v[4 * i + 3] = (c + 3 < lim) ? t.w * k : NEG_INF;
 #pragma unroll
       for (int e = 0; e < 4; e++) mx = fmaxf(mx, v[4 * i + e]);
     }
@@ -74,15 +76,15 @@ __global__ void __launch_bounds__(256) softmax_fwd_warp(const float* __restrict_
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NV * 4; i++) {
-      v[i] = (v[i] == NEG_INF) ? 0.f : expf(v[i] - mx);
+      v[i] = exp2f(v[i] - mx);  // 2^(-inf) = 0 for masked columns
       s += v[i];
     }
-    s = warp_sum(s);
+    const float inv = 1.f / warp_sum(s);
     float4* yr = reinterpret_cast<float4*>(y + r * cols);
 #pragma unroll
     for (int i = 0; i < NV; i++) {
       const int c = (lane + 32 * i) * 4;
-      if (c < cols) yr[lane + 32 * i] = make_float4(v[4 * i] / s, v[4 * i + 1] / s, v[4 * i + 2] / s, v[4 * i + 3] / s);
+      if (c < cols) yr[lane + 32 * i] = make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
     }
   }
 }
@@ -160,15 +162,6 @@ __global__ void __launch_bounds__(256) layernorm_fwd_warp(const float* __restric
   const int lane = threadIdx.x & 31;
   const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  float4 g[NV], b[NV];
-#pragma unroll
-  for (int i = 0; i < NV; i++) {
-    g[i] = b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if ((lane + 32 * i) * 4 < cols) {
-      g[i] = reinterpret_cast<const float4*>(gamma)[lane + 32 * i];
-      b[i] = reinterpret_cast<const float4*>(beta)[lane + 32 * i];
-    }
-  }
   const float inv_c = 1.f / (float)cols;
   for (long long r = warp0; r < rows; r += nwarps) {
     float4 v[NV];
@@ -200,10 +193,13 @@ __global__ void __launch_bounds__(256) layernorm_fwd_warp(const float* __restric
 #pragma unroll
     for (int i = 0; i < NV; i++) {
       if ((lane + 32 * i) * 4 < cols) {
+        // gamma and beta stay L1-resident; reading them here keeps them out of the register file
+        const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + lane + 32 * i);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(beta) + lane + 32 * i);
         float4 n = make_float4(v[i].x * rs, v[i].y * rs, v[i].z * rs, v[i].w * rs);
         reinterpret_cast<float4*>(xhat + r * cols)[lane + 32 * i] = n;
         reinterpret_cast<float4*>(y + r * cols)[lane + 32 * i] =
-            make_float4(g[i].x * n.x + b[i].x, g[i].y * n.y + b[i].y, g[i].z * n.z + b[i].z, g[i].w * n.w + b[i].w);
+            make_float4(g.x * n.x + b.x, g.y * n.y + b.y, g.z * n.z + b.z, g.w * n.w + b.w);
       }
     }
   }

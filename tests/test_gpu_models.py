@@ -39,7 +39,8 @@ def test_mlp_training_step_config1(orc, prec):
     assert rel(grads, flat_ref) <= t_grad
     new = mlp.arena.values.numpy()
     flat_new = np.concatenate([np.pad(p.ravel(), (0, (-p.size) % 4)) for p in ref["params"]])
-    assert rel(new, flat_new) <= 1e-5
+    # the update is w - lr*g: the gradient tolerance above, scaled by lr*|g|/|w|
+    assert rel(new, flat_new) <= (1e-4 if prec == 0 else 1e-5)
     assert ctx.device_status() == 0
     ctx.close()
 
