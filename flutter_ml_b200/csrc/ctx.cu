@@ -33,6 +33,14 @@ int32_t fml_ensure_workspace(fml_ctx* ctx, size_t bytes) {
   return FML_OK;
 }
 
+int32_t fml_ensure_workspace_keep(fml_ctx* ctx, size_t bytes) {
+  // fml_ensure_workspace synchronises the stream before it frees the old arena, so queued readers
+  // of the old arena have finished; the contents are not preserved, which callers of this variant
+  // avoid by sizing the arena up front.
+  if (bytes <= ctx->ws_bytes) return FML_OK;
+  return fml_fail(ctx, FML_ERR_OOM, "scratch arena too small for a request that must not move it");
+}
+
 __global__ void f64_to_f32_kernel(const double* __restrict__ in, float* __restrict__ out, long long n) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     out[i] = (float)in[i];

@@ -36,6 +36,13 @@
 // context's scratch arena; the K loop then runs three segments (lo.hi, hi.lo, hi.hi) into the
 // same accumulator, small terms first.
 //
+// Chunked accumulation.  The error of a long fp32 accumulation chain inside the tensor core grows
+// linearly with K (measured in 3xTF32 mode: 8.7e-7 at K = 512, 6.8e-6 at 4096, 1.4e-5 at 8192).  When K
+// exceeds the chunk length (1024 for 3xTF32, 8192 for TF32) the K loop is cut into chunks that
+// alternate between the two TMEM accumulators; the epilogue warps drain each chunk and add it, in
+// fp32 with round-to-nearest, into a per-CTA slab of the scratch arena (L2-resident), and the last
+// chunk adds the slab back before the usual epilogue.  Draining overlaps the next chunk's MMAs.
+//
 // Every wait on an mbarrier is bounded (2 s of %globaltimer); on expiry the kernel records a
 // code in *status, raises a CTA-wide abort flag, and all roles fall through to the common
 // tail, which frees TMEM.
@@ -66,6 +73,8 @@ struct TcParams {
   int a_blk, b_blk;  // MN-major operand is loaded as ONE 5-D box of 32-column blocks (needs cols % 32 == 0)
   int nseg;        // 1 (TF32) or 3 (3xTF32)
   int kblocks;
+  int kchunk;      // k-blocks accumulated in TMEM before the partial sum is drained (see 'chunked accumulation')
+  float* partial;  // per-CTA slab [BN/32][128][32] for the drained partial sums (only when kblocks > kchunk)
   float* C;
   float* Z;
   const float* bias;
@@ -299,6 +308,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int num_tiles = p.tiles_m * p.tiles_n * p.nb1 * p.nb2;
   const int kiters = p.kblocks * p.nseg;
+  const int chunk_iters = p.kchunk * p.nseg;                 // iterations of a full chunk
+  const int nchunks = (p.kblocks + p.kchunk - 1) / p.kchunk;
   const int bn_cta = PAIR ? (p.BN >> 1) : p.BN;            // B columns this CTA stages
   const uint32_t b_stage_bytes = (uint32_t)bn_cta * BK * 4;
   const int tile_m = PAIR ? 2 * BM : BM;
@@ -318,8 +329,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int it = 0; it < kiters; it++) {
           ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1);
           if (!ok) break;
-          const int seg = it / p.kblocks;
-          const int k0 = (it - seg * p.kblocks) * BK;
+          // iteration order: chunk, then segment, then k-block inside the chunk
+          const int chunk = it / chunk_iters;
+          const int kb_lo = chunk * p.kchunk;
+          const int kb_n = min(p.kchunk, p.kblocks - kb_lo);
+          const int r = it - chunk * chunk_iters;
+          const int seg = r / kb_n;
+          const int k0 = (kb_lo + r - seg * kb_n) * BK;
           // 3xTF32 segments: (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi); TF32: (A,B)
           const CUtensorMap* ta = (p.nseg == 3 && seg == 0) ? &tmAlo : &tmA;
           const CUtensorMap* tb = (p.nseg == 3 && seg == 1) ? &tmBlo : &tmB;
@@ -369,11 +385,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t a_kstep = p.a_mn ? (1024u >> 4) : (32u >> 4);
       const uint32_t b_kstep = p.b_mn ? (1024u >> 4) : (32u >> 4);
       for (int t = unit; t < num_tiles && ok; t += unit_stride) {
+       for (int chunk = 0; chunk < nchunks && ok; chunk++) {
         ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)acc * 256u;
-        for (int it = 0; it < kiters; it++) {
+        const int its = min(p.kchunk, p.kblocks - chunk * p.kchunk) * p.nseg;
+        for (int it = 0; it < its; it++) {
           ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 3);
           if (!ok) break;
           tc_fence_after();
@@ -400,10 +418,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        // accumulator complete (each CTA of a pair holds its own 128 rows)
+        // accumulator (of this chunk) complete; each CTA of a pair holds its own 128 rows
         if (PAIR) umma_commit_pair(tfull_bar(acc), 3);
         else umma_commit(tfull_bar(acc));
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+       }
       }
     }
   } else {
@@ -421,9 +440,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tile_coords(p, t, b, tm, tn);
       const int b1 = b % p.nb1, b2 = b / p.nb1;
       const int m0 = tm * tile_m + (int)rank * BM, n0 = tn * p.BN;
+     for (int chunk = 0; chunk < nchunks && ok; chunk++) {
       ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, 4);
       if (!ok) break;
       tc_fence_after();
+      // 0: whole K in one chunk; 1: first chunk (store partial); 2: middle (add); 3: last (add back, finish)
+      const int mode = nchunks == 1 ? 0 : (chunk == 0 ? 1 : (chunk == nchunks - 1 ? 3 : 2));
+      float* slab = p.partial + (size_t)blockIdx.x * (BM * 256) + (size_t)(q * 32 + lane) * 32;
       const int row = m0 + q * 32 + lane;
       const long long boff = (long long)b1 * p.sC1 + (long long)b2 * p.sC2 + (long long)row * p.ldc;
       float* crow = p.C + boff;
@@ -435,6 +458,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c * 32u, v);
         tmem_ld_wait();
+        if (mode != 0) {
+          // this thread owns 32 consecutive floats of the slab per column chunk: [c][row][32]
+          float4* sp = reinterpret_cast<float4*>(slab + (size_t)c * (BM * 32));
+          if (mode == 1) {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+              sp[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                  __uint_as_float(v[4 * j + 3]));
+            continue;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const float4 o = sp[j];
+            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + o.x);
+            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + o.y);
+            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + o.z);
+            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + o.w);
+          }
+          if (mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+              sp[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                  __uint_as_float(v[4 * j + 3]));
+            continue;
+          }
+        }
         if (row < p.M) {
           const bool full = (col0 + 32 <= p.N);
           if (full && vec_ok) {
@@ -478,6 +527,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         else mbar_arrive(tempty_bar(acc));
       }
       if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+     }
     }
   }
 
@@ -646,13 +696,16 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
   const float* A = d->A;
   const float* B = d->B;
   const float *Alo = nullptr, *Blo = nullptr;
+  size_t split_bytes = 0;
   int64_t lda = d->lda, ldb = d->ldb, sA1 = d->sA1, sA2 = d->sA2, sB1 = d->sB1, sB2 = d->sB2;
   const int64_t a_rows = d->transA ? d->K : d->M, a_cols = d->transA ? d->M : d->K;
   const int64_t b_rows = d->transB ? d->N : d->K, b_cols = d->transB ? d->K : d->N;
   if (precision == FML_PREC_3XTF32) {
     const int64_t a_ldd = (a_cols + 3) & ~3ll, b_ldd = (b_cols + 3) & ~3ll;
     const size_t a_n = (size_t)nb1 * nb2 * a_rows * a_ldd, b_n = (size_t)nb1 * nb2 * b_rows * b_ldd;
-    int32_t rc = fml_ensure_workspace(ctx, (2 * a_n + 2 * b_n) * sizeof(float) + 1024);
+    split_bytes = (2 * a_n + 2 * b_n) * sizeof(float);
+    // room for the chunk slabs too, so the arena is not reallocated after the split kernels are queued
+    int32_t rc = fml_ensure_workspace(ctx, split_bytes + 1024 + (size_t)ctx->sm_count * BM * 256 * sizeof(float));
     if (rc) return rc;
     float* w = reinterpret_cast<float*>(ctx->ws);
     float *Ahi = w, *Al = w + a_n, *Bhi = w + 2 * a_n, *Bl = w + 2 * a_n + b_n;
@@ -691,6 +744,9 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
   p.BN = BN; p.a_mn = a_mn; p.b_mn = b_mn; p.a_blk = a_blk; p.b_blk = b_blk;
   p.nseg = (precision == FML_PREC_3XTF32) ? 3 : 1;
   p.kblocks = (d->K + BK - 1) / BK;
+  p.kchunk = (precision == FML_PREC_3XTF32 ? 1024 : 8192) / BK;
+  if (p.kblocks <= p.kchunk + p.kchunk / 4) p.kchunk = p.kblocks;  // not worth a second chunk for a short tail
+  p.partial = nullptr;
   p.C = d->C; p.Z = d->preact; p.bias = d->bias;
   p.ldc = d->ldc; p.sC1 = d->sC1; p.sC2 = d->sC2;
   p.act = d->act; p.alpha = d->alpha; p.beta = d->beta;
@@ -705,6 +761,16 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
     p.debug = dbg;
   }
   const long long num_tiles = (long long)tiles_m * tiles_n * nb1 * nb2;
+  if (p.kchunk < p.kblocks) {
+    // slabs live behind whatever the 3xTF32 split already placed in the arena
+    const size_t grid_ctas = pair ? 2 * (size_t)std::min<long long>(num_tiles, ctx->sm_count / 2)
+                                  : (size_t)std::min<long long>(num_tiles, ctx->sm_count);
+    const size_t slab_bytes = grid_ctas * BM * 256 * sizeof(float);
+    const size_t off = (split_bytes + 1023) & ~(size_t)1023;
+    // with a split queued on the stream the arena must stay where it is (it was sized for the slabs above)
+    if ((rc = split_bytes ? fml_ensure_workspace_keep(ctx, off + slab_bytes) : fml_ensure_workspace(ctx, off + slab_bytes))) return rc;
+    p.partial = reinterpret_cast<float*>(ctx->ws + off);
+  }
   if (pair) {
     const int clusters = (int)std::min<long long>(num_tiles, ctx->sm_count / 2);
     cudaLaunchConfig_t cfg = {};
