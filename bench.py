@@ -235,8 +235,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-train", action="store_true")
     ap.add_argument("--no-membound", action="store_true")
+    ap.add_argument("--no-configs", action="store_true")
     ap.add_argument("--membound-only", action="store_true", help="run only the memory-bound kernel sweep (profiling)")
     ap.add_argument("--membound-rows", type=int, default=262144)
+    ap.add_argument("--train-only", action="store_true", help="run only the data-parallel training step (profiling)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -269,6 +271,15 @@ def main():
 
     peaks = measured_peaks()
     ctx = _lib.Context(device=local_rank, precision=_lib.PREC_TF32)
+    if args.train_only:
+        from flutter_ml_b200 import train_bench
+        res = train_bench.run(ctx, rank, world, barrier, max_over_ranks, steps=max(1, min(args.steps, 3)), warmup=1)
+        if rank == 0:
+            print(json.dumps({"train": res}), flush=True)
+        ctx.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.membound_only:
         res = time_membound(ctx, peaks["hbm_gbs"], reps=2, rows=args.membound_rows)
         print(json.dumps({"membound": res}), flush=True)
@@ -353,6 +364,9 @@ def main():
 
     if rank == 0 and not args.no_sweep:
         line["sweep"] = time_sweep(ctx)
+    if rank == 0 and not args.no_configs:
+        from flutter_ml_b200 import config_bench
+        line["configs"] = config_bench.run(ctx)
     if rank == 0 and not args.no_membound:
         line["membound"] = time_membound(ctx, peaks["hbm_gbs"], rows=args.membound_rows)
     if rank == 0 and not args.no_cpu:

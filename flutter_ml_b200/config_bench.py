@@ -1,0 +1,87 @@
+"""Timing of benchmark configurations 1, 3 and 4 at their stated sizes (config 2 is bench.py's main
+line, config 5 is train_bench).  Inputs are seeded synthetic tensors; times are CUDA events on the
+library's stream, averaged over `reps` steps after `warm` untimed ones."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from . import _lib, models, synth
+from . import tensor as T
+from .tensor import Tensor
+
+
+def _timed(ctx, fn, warm=2, reps=5):
+    for _ in range(warm):
+        fn()
+    ctx.sync()
+    l0 = ctx.launches
+    ctx.timer_start()
+    for _ in range(reps):
+        fn()
+    ms = ctx.timer_stop_ms() / reps
+    return ms, (ctx.launches - l0) // reps
+
+
+def config1_mlp(ctx):
+    """MLP 784-128-64-10, batch 64, one forward + backward + SGD step."""
+    mlp = models.MLP(ctx, models.init_mlp(0), lr=0.01)
+    X, labels = ctx.upload(synth.uniform(0, 0, (64, 784))), ctx.upload(synth.integers(0, 1, (64,), 10))
+    ms, launches = _timed(ctx, lambda: mlp.train_step(X, labels), warm=5, reps=50)
+    flops = 41926656.0
+    return {"config": "C1 MLP 784-128-64-10 batch 64 fwd+bwd+SGD", "us_per_step": round(ms * 1e3, 1),
+            "samples_per_s": round(64 / ms * 1e3, 1), "gflops": round(flops / ms / 1e6, 1), "launches_per_step": launches}
+
+
+def config3_encoder_block(ctx):
+    """Post-LN encoder block d512 h8 dff2048, seq 256, batch 32, causal, forward + backward."""
+    d, heads, dff, S, B = 512, 8, 2048, 256, 32
+    from .layers import TransformerEncoderBlock
+    block = TransformerEncoderBlock(d, heads, dff, seq_len=S, causal=True, params=models.init_block(2, d, heads, dff))
+    x = ctx.upload(synth.normal(2, 500, (B * S, d)))
+    tgt = Tensor(ctx.upload(synth.normal(2, 501, (B * S, d))), ctx)
+
+    def step():
+        xt = Tensor(x, ctx)
+        loss = T.mseMatrix(block(xt), tgt, weight=float(B))
+        loss.backward()
+        for p in block.parameters:
+            p.grad = None
+    ms, launches = _timed(ctx, step)
+    flops = 1.675e11
+    return {"config": "C3 encoder block d512 h8 dff2048 S256 B32 causal fwd+bwd", "ms_per_step": round(ms, 3),
+            "tflops": round(flops / ms / 1e9, 1), "sequences_per_s": round(B / ms * 1e3, 1), "launches_per_step": launches}
+
+
+def config4_lstm(ctx):
+    """LSTM input 256, hidden 512, seq 128, batch 128, forward + BPTT (loss: mse of the last hidden state)."""
+    Tn, B, I, H = 128, 128, 256, 512
+    a = 1.0 / np.sqrt(512.0)
+    W, b = ctx.upload(synth.uniform(3, 0, (4 * H, H + I), -a, a)), ctx.zeros(4 * H)
+    x = ctx.upload(synth.normal(3, 2, (Tn * B, I)))
+    target = ctx.upload(synth.normal(3, 3, (B, H)))
+    d = _lib.LstmDesc()
+    d.T, d.B, d.I, d.H = Tn, B, I, H
+    bufs = dict(W=W, b=b, x=x, gates=ctx.empty(Tn, B, 4 * H), cells=ctx.empty(Tn + 1, B, H), hs=ctx.empty(Tn + 1, B, H),
+                xproj=ctx.empty(Tn * B, 4 * H))
+    for k, v in bufs.items():
+        setattr(d, k, v.ptr)
+    dW, db, dh, loss = ctx.zeros(4 * H, H + I), ctx.zeros(4 * H), ctx.empty(B, H), ctx.zeros(1)
+    scratch = ctx.empty(Tn * B * 4 * H + 2 * B * H)
+    h_last = bufs["hs"].view(Tn * B * H, (B, H))
+
+    def step():
+        ctx.check(ctx.lib.fml_lstm_fwd(ctx.h, ctypes.byref(d)))
+        ctx.call("fml_mse", h_last, target, dh, loss, B * H, float(B), launches=2)
+        ctx.check(ctx.lib.fml_lstm_bwd(ctx.h, ctypes.byref(d), dh.ptr, dW.ptr, db.ptr, None, scratch.ptr))
+        ctx.launches += 4 * Tn + 6
+    ms, launches = _timed(ctx, step)
+    flops = 1.546e11
+    return {"config": "C4 LSTM I256 H512 T128 B128 fwd+BPTT", "ms_per_step": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
+            "us_per_timestep": round(ms * 1e3 / (2 * Tn), 1), "sequences_per_s": round(B / ms * 1e3, 1),
+            "launches_per_step": launches}
+
+
+def run(ctx):
+    return [config1_mlp(ctx), config3_encoder_block(ctx), config4_lstm(ctx)]

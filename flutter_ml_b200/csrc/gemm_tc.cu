@@ -43,6 +43,12 @@
 // fp32 with round-to-nearest, into a per-CTA slab of the scratch arena (L2-resident), and the last
 // chunk adds the slab back before the usual epilogue.  Draining overlaps the next chunk's MMAs.
 //
+// Split K.  A product with few output tiles and a long K (weight gradients: K = all tokens of the
+// batch) would leave most SMs idle; its K range is then divided over several CTAs per tile, each of
+// which adds its partial product into C with vector atomics (C is zeroed first unless beta = 1).  Only
+// for plain products (no bias, activation or pre-activation output).  The order of the atomic adds
+// is not fixed, so results can differ in the last fp32 bit between runs.
+//
 // Every wait on an mbarrier is bounded (2 s of %globaltimer); on expiry the kernel records a
 // code in *status, raises a CTA-wide abort flag, and all roles fall through to the common
 // tail, which frees TMEM.
@@ -74,6 +80,8 @@ struct TcParams {
   int nseg;        // 1 (TF32) or 3 (3xTF32)
   int kblocks;
   int kchunk;      // k-blocks accumulated in TMEM before the partial sum is drained (see 'chunked accumulation')
+  int ksplit;      // > 1: the K range of a tile is divided over this many CTAs that add into C atomically
+  int kb_per_split;
   float* partial;  // per-CTA slab [BN/32][128][32] for the drained partial sums (only when kblocks > kchunk)
   float* C;
   float* Z;
@@ -307,9 +315,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tiles_m * p.tiles_n * p.nb1 * p.nb2;
-  const int kiters = p.kblocks * p.nseg;
-  const int chunk_iters = p.kchunk * p.nseg;                 // iterations of a full chunk
-  const int nchunks = (p.kblocks + p.kchunk - 1) / p.kchunk;
+  const int num_units = num_tiles * p.ksplit;  // work units: (tile, K split)
+  // unit -> tile index, first k-block and number of k-blocks of its K range
+  auto unit_range = [&](int u, int& tile, int& kb0, int& nkb) {
+    const int split = u / num_tiles;
+    tile = u - split * num_tiles;
+    kb0 = split * p.kb_per_split;
+    nkb = min(p.kb_per_split, p.kblocks - kb0);
+  };
   const int bn_cta = PAIR ? (p.BN >> 1) : p.BN;            // B columns this CTA stages
   const uint32_t b_stage_bytes = (uint32_t)bn_cta * BK * 4;
   const int tile_m = PAIR ? 2 * BM : BM;
@@ -320,22 +333,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = unit; t < num_tiles && ok; t += unit_stride) {
-        int b, tm, tn;
+      for (int u = unit; u < num_units && ok; u += unit_stride) {
+        int t, kb0, nkb, b, tm, tn;
+        unit_range(u, t, kb0, nkb);
         tile_coords(p, t, b, tm, tn);
         const int b1 = b % p.nb1, b2 = b / p.nb1;
         const int m0 = tm * tile_m + (int)rank * BM;
         const int n0 = tn * p.BN + (int)rank * bn_cta;
-        for (int it = 0; it < kiters; it++) {
+        // iteration order: chunk, then segment, then k-block inside the chunk
+        for (int kb_lo = kb0; kb_lo < kb0 + nkb && ok; kb_lo += p.kchunk) {
+         const int kb_n = min(p.kchunk, kb0 + nkb - kb_lo);
+         for (int seg = 0; seg < p.nseg && ok; seg++) {
+         for (int kb = kb_lo; kb < kb_lo + kb_n; kb++) {
           ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1);
           if (!ok) break;
-          // iteration order: chunk, then segment, then k-block inside the chunk
-          const int chunk = it / chunk_iters;
-          const int kb_lo = chunk * p.kchunk;
-          const int kb_n = min(p.kchunk, p.kblocks - kb_lo);
-          const int r = it - chunk * chunk_iters;
-          const int seg = r / kb_n;
-          const int k0 = (kb_lo + r - seg * kb_n) * BK;
+          const int k0 = kb * BK;
           // 3xTF32 segments: (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi); TF32: (A,B)
           const CUtensorMap* ta = (p.nseg == 3 && seg == 0) ? &tmAlo : &tmA;
           const CUtensorMap* tb = (p.nseg == 3 && seg == 1) ? &tmBlo : &tmB;
@@ -370,6 +382,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             load(sb, tb, k0, n0);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
+         }
+         }
         }
       }
     }
@@ -384,13 +398,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t a_lbo = p.a_mn ? 4096u : 16u, b_lbo = p.b_mn ? 4096u : 16u;
       const uint32_t a_kstep = p.a_mn ? (1024u >> 4) : (32u >> 4);
       const uint32_t b_kstep = p.b_mn ? (1024u >> 4) : (32u >> 4);
-      for (int t = unit; t < num_tiles && ok; t += unit_stride) {
-       for (int chunk = 0; chunk < nchunks && ok; chunk++) {
+      for (int u = unit; u < num_units && ok; u += unit_stride) {
+       int t, kb0, nkb;
+       unit_range(u, t, kb0, nkb);
+       for (int kb_lo = kb0; kb_lo < kb0 + nkb && ok; kb_lo += p.kchunk) {
         ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, p.status, 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)acc * 256u;
-        const int its = min(p.kchunk, p.kblocks - chunk * p.kchunk) * p.nseg;
+        const int its = min(p.kchunk, kb0 + nkb - kb_lo) * p.nseg;
         for (int it = 0; it < its; it++) {
           ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 3);
           if (!ok) break;
@@ -435,11 +451,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         ((p.sC1 & 3) == 0) && ((p.sC2 & 3) == 0) &&
                         (p.Z == nullptr || (reinterpret_cast<uintptr_t>(p.Z) & 15) == 0) &&
                         (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
-    for (int t = unit; t < num_tiles && ok; t += unit_stride) {
-      int b, tm, tn;
+    for (int u = unit; u < num_units && ok; u += unit_stride) {
+      int t, kb0, nkb, b, tm, tn;
+      unit_range(u, t, kb0, nkb);
       tile_coords(p, t, b, tm, tn);
       const int b1 = b % p.nb1, b2 = b / p.nb1;
       const int m0 = tm * tile_m + (int)rank * BM, n0 = tn * p.BN;
+      const int nchunks = (nkb + p.kchunk - 1) / p.kchunk;
      for (int chunk = 0; chunk < nchunks && ok; chunk++) {
       ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, 4);
       if (!ok) break;
@@ -451,8 +469,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const long long boff = (long long)b1 * p.sC1 + (long long)b2 * p.sC2 + (long long)row * p.ldc;
       float* crow = p.C + boff;
       float* zrow = p.Z ? p.Z + boff : nullptr;
-      const int nchunks = p.BN / 32;
-      for (int c = 0; c < nchunks; c++) {
+      const int ncols32 = p.BN / 32;
+      for (int c = 0; c < ncols32; c++) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
         uint32_t v[32];
@@ -499,6 +517,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               if (zrow) *reinterpret_cast<float4*>(zrow + col0 + j) = o;
 #pragma unroll
               for (int e = 0; e < 4; e++) op[e] = fml_act_apply(p.act, op[e]);
+              if (p.ksplit > 1) {
+                atomicAdd(reinterpret_cast<float4*>(crow + col0 + j), o);  // K split: partial products add up in C
+                continue;
+              }
               if (p.beta != 0.f) {
                 float4 old = *reinterpret_cast<const float4*>(crow + col0 + j);
                 o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
@@ -513,6 +535,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 float o = __uint_as_float(v[j]) * p.alpha + (p.bias ? p.bias[col] : 0.f);
                 if (zrow) zrow[col] = o;
                 o = fml_act_apply(p.act, o);
+                if (p.ksplit > 1) { atomicAdd(crow + col, o); continue; }
                 if (p.beta != 0.f) o += crow[col];
                 crow[col] = o;
               }
@@ -747,6 +770,25 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
   p.kchunk = (precision == FML_PREC_3XTF32 ? 1024 : 8192) / BK;
   if (p.kblocks <= p.kchunk + p.kchunk / 4) p.kchunk = p.kblocks;  // not worth a second chunk for a short tail
   p.partial = nullptr;
+  p.ksplit = 1;
+  p.kb_per_split = p.kblocks;
+  {
+    // K split for plain TF32 products whose tiles occupy less than ~60 % of the SMs
+    const long long tiles_all = (long long)tiles_m * tiles_n * nb1 * nb2;
+    const long long ctas = tiles_all * (pair ? 2 : 1);
+    if (precision == FML_PREC_TF32 && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE &&
+        ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 64) {
+      int want = (int)(ctx->sm_count / ctas);                 // CTAs available per tile
+      int maxs = p.kblocks / 32;                              // at least 1024 k per split
+      int ks = std::max(1, std::min(want, maxs));
+      if (ks > 1) {
+        p.kb_per_split = (p.kblocks + ks - 1) / ks;
+        p.ksplit = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
+        if (d->beta == 0.f)
+          FML_CUDA(ctx, cudaMemset2DAsync(d->C, (size_t)d->ldc * 4, 0, (size_t)d->N * 4, (size_t)d->M, ctx->stream));
+      }
+    }
+  }
   p.C = d->C; p.Z = d->preact; p.bias = d->bias;
   p.ldc = d->ldc; p.sC1 = d->sC1; p.sC2 = d->sC2;
   p.act = d->act; p.alpha = d->alpha; p.beta = d->beta;
@@ -760,8 +802,8 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
     }
     p.debug = dbg;
   }
-  const long long num_tiles = (long long)tiles_m * tiles_n * nb1 * nb2;
-  if (p.kchunk < p.kblocks) {
+  const long long num_tiles = (long long)tiles_m * tiles_n * nb1 * nb2 * p.ksplit;  // work units
+  if (p.kchunk < p.kb_per_split) {
     // slabs live behind whatever the 3xTF32 split already placed in the arena
     const size_t grid_ctas = pair ? 2 * (size_t)std::min<long long>(num_tiles, ctx->sm_count / 2)
                                   : (size_t)std::min<long long>(num_tiles, ctx->sm_count);
