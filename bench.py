@@ -238,6 +238,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true")
     ap.add_argument("--membound-only", action="store_true", help="run only the memory-bound kernel sweep (profiling)")
     ap.add_argument("--membound-rows", type=int, default=262144)
+    ap.add_argument("--configs-only", action="store_true", help="run only configurations 1, 3, 4 (profiling)")
     ap.add_argument("--train-only", action="store_true", help="run only the data-parallel training step (profiling)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -279,6 +280,11 @@ def main():
         ctx.close()
         if world > 1:
             dist.destroy_process_group()
+        return
+    if args.configs_only:
+        from flutter_ml_b200 import config_bench
+        print(json.dumps({"configs": config_bench.run(ctx)}), flush=True)
+        ctx.close()
         return
     if args.membound_only:
         res = time_membound(ctx, peaks["hbm_gbs"], reps=2, rows=args.membound_rows)
@@ -340,18 +346,27 @@ def main():
                 "per_gemm_ms": {"fwd": round(statistics.mean(gemm_ms[0::3]), 4), "dA": round(statistics.mean(gemm_ms[1::3]), 4),
                                 "dW": round(statistics.mean(gemm_ms[2::3]), 4)}}
 
-    # ---- end to end: host buffers in, host buffers out, copies inside the timed region
-    e2e_steps = max(2, min(args.steps, 5))
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region.
+    # Serial form (upload, kernels, download one after the other) and pipelined form (copies on two
+    # side streams, two buffer sets); both move the same bytes every step.
+    e2e_steps = max(4, min(args.steps, 10))
     host()
     barrier()
     ctx.timer_start()
-    for _ in range(e2e_steps):
+    for _ in range(2):
         host()
+    serial_ms = max_over_ranks(ctx.timer_stop_ms()) / 2
+    host.pipelined(2)
+    barrier()
+    ctx.timer_start()
+    host.pipelined(e2e_steps)
     e2e_ms = ctx.timer_stop_ms()
     barrier()
-    e2e_ms = max_over_ranks(max(e2e_ms, 0.0)) / e2e_steps
+    e2e_ms = max_over_ranks(e2e_ms) / e2e_steps
     e2e = {"value": round(world * flops_step / e2e_ms / 1e9, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 3),
-           "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes}
+           "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes, "steps": e2e_steps,
+           "serial_ms_per_step": round(serial_ms, 3),
+           "pcie_gbs_each_way": round(host.h2d_bytes / e2e_ms / 1e6, 1)}
 
     line = {"metric": "gemm_fwd_bwd_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",

@@ -70,6 +70,11 @@ PROTOTYPES = {
     "fml_host_free": [fp, fp],
     "fml_event_record": [fp, i32],
     "fml_event_elapsed_ms": [fp, i32, i32, C.POINTER(f32)],
+    "fml_lane_h2d": [fp, i32, fp, fp, i64],
+    "fml_lane_d2h": [fp, i32, fp, fp, i64],
+    "fml_lane_sync": [fp, i32],
+    "fml_event_record_on": [fp, i32, i32],
+    "fml_wait_event": [fp, i32, i32],
     "fml_timer_start": [fp],
     "fml_timer_stop_ms": [fp, C.POINTER(f32)],
     "fml_gemm": [fp, C.POINTER(GemmDesc)],

@@ -27,6 +27,7 @@ struct fml_ctx {
   std::unordered_set<void*> allocs;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   cudaEvent_t ev_pool[64] = {};
+  cudaStream_t lanes[2] = {nullptr, nullptr};  // copy streams, created on first use
   int last_gemm_path = 0;
   // tensor-map cache: key -> encoded CUtensorMap
   std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int>, CUtensorMap> tmaps;

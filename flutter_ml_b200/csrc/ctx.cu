@@ -120,6 +120,8 @@ int32_t fml_shutdown(fml_ctx* ctx) {
   cudaEventDestroy(ctx->ev1);
   for (cudaEvent_t e : ctx->ev_pool)
     if (e) cudaEventDestroy(e);
+  for (cudaStream_t l : ctx->lanes)
+    if (l) { cudaStreamSynchronize(l); cudaStreamDestroy(l); }
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
   return FML_OK;
@@ -252,6 +254,55 @@ int32_t fml_event_elapsed_ms(fml_ctx* ctx, int32_t a, int32_t b, float* ms) {
               "fml_event_elapsed_ms: slot not recorded");
   FML_CUDA(ctx, cudaEventSynchronize(ctx->ev_pool[b]));
   FML_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_pool[a], ctx->ev_pool[b]));
+  return FML_OK;
+}
+
+static int32_t lane_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
+  FML_REQUIRE(ctx, lane >= 0 && lane < 2, "copy lane must be 0 or 1");
+  if (!ctx->lanes[lane]) FML_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->lanes[lane], cudaStreamNonBlocking));
+  *out = ctx->lanes[lane];
+  return FML_OK;
+}
+static int32_t any_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
+  if (lane < 0) { *out = ctx->stream; return FML_OK; }
+  return lane_stream(ctx, lane, out);
+}
+int32_t fml_event_record_on(fml_ctx* ctx, int32_t slot, int32_t lane) {
+  FML_REQUIRE(ctx, slot >= 0 && slot < 64, "fml_event_record_on: slot out of range");
+  cudaStream_t s;
+  int32_t rc = any_stream(ctx, lane, &s);
+  if (rc) return rc;
+  if (!ctx->ev_pool[slot]) FML_CUDA(ctx, cudaEventCreate(&ctx->ev_pool[slot]));
+  FML_CUDA(ctx, cudaEventRecord(ctx->ev_pool[slot], s));
+  return FML_OK;
+}
+int32_t fml_wait_event(fml_ctx* ctx, int32_t lane, int32_t slot) {
+  FML_REQUIRE(ctx, slot >= 0 && slot < 64 && ctx->ev_pool[slot], "fml_wait_event: slot not recorded");
+  cudaStream_t s;
+  int32_t rc = any_stream(ctx, lane, &s);
+  if (rc) return rc;
+  FML_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev_pool[slot], 0));
+  return FML_OK;
+}
+int32_t fml_lane_h2d(fml_ctx* ctx, int32_t lane, float* dst, const float* host, int64_t n) {
+  cudaStream_t s;
+  int32_t rc = lane_stream(ctx, lane, &s);
+  if (rc) return rc;
+  FML_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)n * 4, cudaMemcpyHostToDevice, s));
+  return FML_OK;
+}
+int32_t fml_lane_d2h(fml_ctx* ctx, int32_t lane, float* host, const float* src, int64_t n) {
+  cudaStream_t s;
+  int32_t rc = lane_stream(ctx, lane, &s);
+  if (rc) return rc;
+  FML_CUDA(ctx, cudaMemcpyAsync(host, src, (size_t)n * 4, cudaMemcpyDeviceToHost, s));
+  return FML_OK;
+}
+int32_t fml_lane_sync(fml_ctx* ctx, int32_t lane) {
+  cudaStream_t s;
+  int32_t rc = lane_stream(ctx, lane, &s);
+  if (rc) return rc;
+  FML_CUDA(ctx, cudaStreamSynchronize(s));
   return FML_OK;
 }
 

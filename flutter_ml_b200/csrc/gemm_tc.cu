@@ -320,8 +320,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   auto unit_range = [&](int u, int& tile, int& kb0, int& nkb) {
     const int split = u / num_tiles;
     tile = u - split * num_tiles;
-    kb0 = split * p.kb_per_split;
-    nkb = min(p.kb_per_split, p.kblocks - kb0);
+    if (p.ksplit > 1) {
+      // interleaved: split s owns k-blocks s, s + ksplit, ...  All splits then stream through the same
+      // region of the operands at the same time (shared DRAM pages and L2 lines) instead of ksplit distant ones
+      kb0 = 0;
+      nkb = (p.kblocks - split + p.ksplit - 1) / p.ksplit;
+    } else {
+      kb0 = 0;
+      nkb = p.kblocks;
+    }
   };
   const int bn_cta = PAIR ? (p.BN >> 1) : p.BN;            // B columns this CTA stages
   const uint32_t b_stage_bytes = (uint32_t)bn_cta * BK * 4;
@@ -347,7 +354,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
          for (int kb = kb_lo; kb < kb_lo + kb_n; kb++) {
           ok = mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1);
           if (!ok) break;
-          const int k0 = kb * BK;
+          const int k0 = (p.ksplit > 1 ? (u / num_tiles) + kb * p.ksplit : kb) * BK;
           // 3xTF32 segments: (A_lo,B_hi), (A_hi,B_lo), (A_hi,B_hi); TF32: (A,B)
           const CUtensorMap* ta = (p.nseg == 3 && seg == 0) ? &tmAlo : &tmA;
           const CUtensorMap* tb = (p.nseg == 3 && seg == 1) ? &tmBlo : &tmB;
@@ -652,6 +659,15 @@ int32_t make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, i
   return FML_OK;
 }
 
+bool splitk_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("FML_GEMM_SPLITK");  // diagnostics: 0 disables the K split
+    v = e ? atoi(e) : 1;
+  }
+  return v != 0;
+}
+
 uint32_t make_idesc(int M, int BN, int a_mn, int b_mn) {
   uint32_t d = 0;
   d |= 1u << 4;                    // accumulator format F32
@@ -777,9 +793,9 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
     const long long tiles_all = (long long)tiles_m * tiles_n * nb1 * nb2;
     const long long ctas = tiles_all * (pair ? 2 : 1);
     if (precision == FML_PREC_TF32 && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE &&
-        ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 64) {
+        ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 8 && splitk_enabled()) {
       int want = (int)(ctx->sm_count / ctas);                 // CTAs available per tile
-      int maxs = p.kblocks / 32;                              // at least 1024 k per split
+      int maxs = p.kblocks / 4;                               // at least 128 k per split
       int ks = std::max(1, std::min(want, maxs));
       if (ks > 1) {
         p.kb_per_split = (p.kblocks + ks - 1) / ks;

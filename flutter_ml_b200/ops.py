@@ -60,6 +60,51 @@ class DenseFwdBwdHost:
         dense_backward(c, self.A, self.B, self.Z, self.dC, self.act, self.M, self.N, self.K, self.dZ, self.dA, self.dB,
                        self.dbias, precision=self.precision)
 
+    def pipelined(self, steps: int):
+        """`steps` end-to-end steps with the copies on two side streams and two sets of device buffers,
+        so the upload of step s+1, the kernels of step s and the download of step s-1 overlap (PCIe is
+        full duplex).  Same bytes per step as __call__; every step still uploads and downloads everything."""
+        c, L = self.ctx, self.ctx.lib
+        if not hasattr(self, "_sets"):
+            e, (M, N, K) = c.empty, (self.M, self.N, self.K)
+            second = dict(A=e(M, K), B=e(K, N), bias=e(N), dC=e(M, N), C=e(M, N), Z=e(M, N), dZ=e(M, N), dA=e(M, K),
+                          dB=e(K, N), dbias=e(N))
+            first = {k: getattr(self, k) for k in second}
+            self._sets = [first, second]
+        EV_UP, EV_COMP, EV_DOWN = 40, 42, 44     # event slots, +0/+1 per buffer set
+        chk = c.check
+
+        def upload(s):
+            b = s % 2
+            if s >= 2:
+                chk(L.fml_wait_event(c.h, 0, EV_COMP + b))   # the kernels of step s-2 have read this set
+            for k in ("A", "B", "bias", "dC"):
+                chk(L.fml_lane_h2d(c.h, 0, self._sets[b][k].ptr, self.h_in[k].ctypes.data, self.h_in[k].size))
+            chk(L.fml_event_record_on(c.h, EV_UP + b, 0))
+
+        upload(0)
+        for s in range(steps):
+            b = s % 2
+            d = self._sets[b]
+            if s + 1 < steps:
+                upload(s + 1)
+            chk(L.fml_wait_event(c.h, -1, EV_UP + b))
+            if s >= 2:
+                chk(L.fml_wait_event(c.h, -1, EV_DOWN + b))  # the download of step s-2 has drained this set
+            dense_forward(c, d["A"], d["B"], d["bias"], self.act, self.M, self.N, self.K, d["C"], d["Z"], self.precision)
+            c.zero(d["dbias"])
+            dense_backward(c, d["A"], d["B"], d["Z"], d["dC"], self.act, self.M, self.N, self.K, d["dZ"], d["dA"], d["dB"],
+                           d["dbias"], precision=self.precision)
+            chk(L.fml_event_record_on(c.h, EV_COMP + b, -1))
+            chk(L.fml_wait_event(c.h, 1, EV_COMP + b))
+            for k in ("C", "dA", "dB", "dbias"):
+                chk(L.fml_lane_d2h(c.h, 1, self.h_out[k].ctypes.data, d[k].ptr, d[k].size))
+            chk(L.fml_event_record_on(c.h, EV_DOWN + b, 1))
+        chk(L.fml_lane_sync(c.h, 1))
+        chk(L.fml_lane_sync(c.h, 0))
+        c.sync()
+        return self.h_out
+
     def __call__(self):
         """One end-to-end step: pinned host -> device, compute, device -> pinned host."""
         c = self.ctx

@@ -92,6 +92,16 @@ int32_t fml_copy(fml_ctx* ctx, float* dst, const float* src, int64_t n);
 int32_t fml_host_alloc(fml_ctx* ctx, int64_t bytes, void** out);
 int32_t fml_host_free(fml_ctx* ctx, void* p);
 
+/* Copy lanes: two extra streams (lane 0 and 1) for host<->device copies that overlap the kernels
+ * on the context's stream (the reference copies synchronously before and after every product,
+ * cuda_lib/kernel.cu:23-24,44).  Ordering between the main stream (lane -1) and the lanes is
+ * expressed with the numbered events of the pool below: record on one, wait on another. */
+int32_t fml_lane_h2d(fml_ctx* ctx, int32_t lane, float* dst, const float* host, int64_t n);
+int32_t fml_lane_d2h(fml_ctx* ctx, int32_t lane, float* host, const float* src, int64_t n);
+int32_t fml_lane_sync(fml_ctx* ctx, int32_t lane);
+int32_t fml_event_record_on(fml_ctx* ctx, int32_t slot, int32_t lane);
+int32_t fml_wait_event(fml_ctx* ctx, int32_t lane, int32_t slot);
+
 /* ---- timing (CUDA events on the context's stream) ------------------------- */
 int32_t fml_timer_start(fml_ctx* ctx);
 int32_t fml_timer_stop_ms(fml_ctx* ctx, float* ms); /* waits for the stop event */
