@@ -65,7 +65,8 @@ template <bool PAIR> struct Cfg {
   static constexpr int STAGES = PAIR ? 6 : 4;
   static constexpr int B_STAGE_BYTES = (PAIR ? 128 : 256) * BK * 4;  // B columns staged per CTA
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int STAGING_BYTES = 4 * 2 * 4096;  // epilogue: 4 warps x 2 buffers x (32 rows x 128 B)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
@@ -91,6 +92,7 @@ struct TcParams {
   float alpha, beta;
   int* status;
   uint32_t idesc;
+  int tma_out;  // 1: the epilogue stages 32x32 blocks in shared memory and writes them with TMA (store or reduce-add)
   int debug;  // diagnostics only: 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
 };
 
@@ -162,6 +164,18 @@ __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(tm), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
+// shared -> global tile store / reduce-add (bulk async group completion); out-of-range parts of the box are clipped
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(tm), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(tm), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // cta_group::2 form: the completion is signalled on the LEADER CTA's barrier (bit 24 of a
 // shared::cluster address selects the odd CTA of a pair; clearing it names the even one)
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
@@ -263,6 +277,7 @@ template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmAlo, const __grid_constant__ CUtensorMap tmBlo,
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmZ,
                const TcParams p) {
   constexpr int STAGES = Cfg<PAIR>::STAGES;
   constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
@@ -271,13 +286,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+  constexpr int STAGING_BYTES = Cfg<PAIR>::STAGING_BYTES;
+  const uint32_t staging = smem_base + STAGES * STAGE_BYTES;  // 1024-byte aligned
+  const uint32_t bars = staging + STAGING_BYTES;
   // barrier layout (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], then tmem slot + abort flag
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * STAGE_BYTES + STAGING_BYTES + 8 * (2 * STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -451,6 +468,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int stage_buf = 0;       // which of this warp's two staging blocks is written next
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
@@ -509,6 +527,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             continue;
           }
         }
+        if (p.tma_out) {
+          // Optional output path (FML_GEMM_TMA_OUT=1): each thread puts its 32 values (one row of the 32x32
+          // block) into a 128B-swizzled staging block and one lane hands the block to TMA (store, or
+          // reduce-add for beta = 1 and K splits); the bulk store clips at the matrix edge.
+          const int row0 = m0 + q * 32;
+          if (row0 < p.M) {  // warp-uniform
+            float o[32];
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 bz = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.bias && col0 + j < p.N) bz = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+              o[j] = __uint_as_float(v[j]) * p.alpha + bz.x;
+              o[j + 1] = __uint_as_float(v[j + 1]) * p.alpha + bz.y;
+              o[j + 2] = __uint_as_float(v[j + 2]) * p.alpha + bz.z;
+              o[j + 3] = __uint_as_float(v[j + 3]) * p.alpha + bz.w;
+            }
+            const uint32_t my_staging = staging + (uint32_t)((warp - 2) * 2) * 4096u;
+#pragma unroll
+            for (int pass = 0; pass < 2; pass++) {
+              if (pass == 0 && p.Z == nullptr) continue;  // pass 0: pre-activation, pass 1: result
+              if (pass == 1) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[j] = fml_act_apply(p.act, o[j]);
+              }
+              const uint32_t blk = my_staging + (uint32_t)stage_buf * 4096u;
+              if (lane == 0) bulk_wait_read_1();  // the store that last used this block has read it
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const uint32_t a = blk + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(o[4 * j]), "f"(o[4 * j + 1]),
+                             "f"(o[4 * j + 2]), "f"(o[4 * j + 3]) : "memory");
+              }
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                if (pass == 0) tma_store_4d(&tmZ, blk, col0, row0, b1, b2);
+                else if (p.beta != 0.f || p.ksplit > 1) tma_reduce_add_4d(&tmC, blk, col0, row0, b1, b2);
+                else tma_store_4d(&tmC, blk, col0, row0, b1, b2);
+                bulk_commit();
+              }
+              stage_buf ^= 1;
+            }
+          }
+          continue;
+        }
         if (row < p.M) {
           const bool full = (col0 + 32 <= p.N);
           if (full && vec_ok) {
@@ -561,6 +625,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
 
+  if (warp >= 2 && lane == 0 && p.tma_out) bulk_wait_all();  // every bulk store of this thread has completed
   // common tail: everyone arrives (both CTAs of a pair: the peer's barriers and TMEM stay alive
   // until nothing can signal or read them), then the allocating warp frees TMEM
   tc_fence_before();
@@ -657,6 +722,18 @@ int32_t make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, i
   if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
   ctx->tmaps[key] = *out;
   return FML_OK;
+}
+
+bool tma_out_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    // Off by default.  Measured on B200 (16384 x 4096 x 1024, bias + ReLU, two outputs): 284 TFLOP/s with the
+    // staged TMA epilogue against 567 with direct 128-bit stores; two 4 KiB staging blocks per warp are too
+    // few bytes in flight, and shared memory has no room for more next to the operand ring.
+    const char* e = getenv("FML_GEMM_TMA_OUT");
+    v = e ? atoi(e) : 0;
+  }
+  return v != 0;
 }
 
 bool splitk_enabled() {
@@ -777,7 +854,24 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
     tmBlo = tmB;
   }
 
+  // output maps for the TMA epilogue: rank 4 {N, M, nb1, nb2}, box 32 x 32, 128B swizzle
+  CUtensorMap tmC, tmZ;
+  auto al16p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  bool tma_out = al16p(d->C) && (d->ldc & 3) == 0 && (nb1 <= 1 || (d->sC1 & 3) == 0) && (nb2 <= 1 || (d->sC2 & 3) == 0) &&
+                 (!d->preact || al16p(d->preact)) && (!d->bias || (al16p(d->bias) && (d->N & 3) == 0)) && tma_out_enabled();
+  if (tma_out) {
+    if ((rc = make_tmap(ctx, d->C, d->N, d->M, d->ldc, nb1, nb2, d->sC1, d->sC2, 32, 32, false, 0, &tmC))) return rc;
+    if (d->preact) {
+      if ((rc = make_tmap(ctx, d->preact, d->N, d->M, d->ldc, nb1, nb2, d->sC1, d->sC2, 32, 32, false, 0, &tmZ))) return rc;
+    } else {
+      tmZ = tmC;
+    }
+  } else {
+    tmC = tmA;
+    tmZ = tmA;
+  }
   TcParams p;
+  p.tma_out = tma_out ? 1 : 0;
   p.M = d->M; p.N = d->N; p.K = d->K;
   p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.nb1 = nb1; p.nb2 = nb2;
   p.BN = BN; p.a_mn = a_mn; p.b_mn = b_mn; p.a_blk = a_blk; p.b_blk = b_blk;
@@ -843,10 +937,10 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, p));
+    FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, tmC, tmZ, p));
   } else {
     const int grid = (int)std::min<long long>(num_tiles, ctx->sm_count);
-    gemm_tc_kernel<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, p);
+    gemm_tc_kernel<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, tmC, tmZ, p);
   }
   FML_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
   ctx->last_gemm_path = 1;
