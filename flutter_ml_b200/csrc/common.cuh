@@ -61,10 +61,29 @@ int32_t fml_ensure_workspace_keep(fml_ctx* ctx, size_t bytes);
       return fml_fail((ctx), FML_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e__)); \
   } while (0)
 
+// LSTM gate epilogue of the tensor-core GEMM: the product's columns are gate-interleaved
+// (column 4*r + q = gate q of hidden unit r, q in f,i,c~,o); `addend` [M x N] is added to the product
+// (the input projection of this timestep), then the thread that owns a row applies the gate
+// nonlinearities and the cell update for 8 hidden units per 32-column block.
+struct fml_lstm_epilogue {
+  const float* addend;  // [M][N] pre-activation part computed ahead of time (ld = N)
+  const float* c_prev;  // [M][N/4]
+  float* c_out;         // [M][N/4]
+  float* h_out;         // [M][N/4]
+  float* gates;         // [M][N] activated gates, interleaved like the columns
+};
+
 // internal entry points between translation units
-int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision);
+int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const fml_lstm_epilogue* lstm = nullptr);
 int32_t fml_gemm_simt(fml_ctx* ctx, const fml_gemm_desc* d);
 bool fml_gemm_tc_eligible(const fml_gemm_desc* d);
+
+__device__ __forceinline__ float fml_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+// the reference's tanh: (e^{2x}-1)/(e^{2x}+1), exactly 1 when e^{2x} overflows (tensor.dart:582-586)
+__device__ __forceinline__ float fml_tanh_ref(float x) {
+  const float e2x = expf(2.f * x);
+  return isinf(e2x) ? 1.f : (e2x - 1.f) / (e2x + 1.f);
+}
 
 __device__ __forceinline__ float fml_act_apply(int act, float v) {
   switch (act) {

@@ -62,11 +62,13 @@ constexpr int BM = 128;
 constexpr int BK = 32;
 constexpr int A_STAGE_BYTES = BM * BK * 4;    // 16 KiB
 template <bool PAIR> struct Cfg {
-  static constexpr int STAGES = PAIR ? 6 : 4;
-  static constexpr int B_STAGE_BYTES = (PAIR ? 128 : 256) * BK * 4;  // B columns staged per CTA
-  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  // The operand ring holds RING_BYTES; a stage is 16 KiB of A plus 128 B per staged B column, so narrow
+  // tiles get a deeper ring (BN = 256 single: 4 stages, pair or BN = 128: 6, BN = 64: 8), which is what
+  // hides the load latency of short, latency-bound products.
+  static constexpr int RING_BYTES = 6 * 32768;
+  static constexpr int MAX_STAGES = 12;
   static constexpr int STAGING_BYTES = 4 * 2 * 4096;  // epilogue: 4 warps x 2 buffers x (32 rows x 128 B)
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = RING_BYTES + STAGING_BYTES + 1024 /*align*/ + 512 /*barriers*/;
 };
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
@@ -79,6 +81,7 @@ struct TcParams {
   int a_mn, b_mn;  // 1 = MN-major operand
   int a_blk, b_blk;  // MN-major operand is loaded as ONE 5-D box of 32-column blocks (needs cols % 32 == 0)
   int nseg;        // 1 (TF32) or 3 (3xTF32)
+  int nstages, stage_bytes;  // operand ring geometry
   int kblocks;
   int kchunk;      // k-blocks accumulated in TMEM before the partial sum is drained (see 'chunked accumulation')
   int ksplit;      // > 1: the K range of a tile is divided over this many CTAs that add into C atomically
@@ -92,6 +95,8 @@ struct TcParams {
   float alpha, beta;
   int* status;
   uint32_t idesc;
+  int lstm;     // 1: LSTM gate epilogue (see fml_lstm_epilogue); C is not written
+  fml_lstm_epilogue le;
   int tma_out;  // 1: the epilogue stages 32x32 blocks in shared memory and writes them with TMA (store or reduce-add)
   int debug;  // diagnostics only: 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
 };
@@ -279,22 +284,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmAlo, const __grid_constant__ CUtensorMap tmBlo,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmZ,
                const TcParams p) {
-  constexpr int STAGES = Cfg<PAIR>::STAGES;
-  constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
+  constexpr int MAX_STAGES = Cfg<PAIR>::MAX_STAGES;
+  constexpr int RING_BYTES = Cfg<PAIR>::RING_BYTES;
+  const int STAGES = p.nstages;            // runtime: depends on the tile width
+  const int STAGE_BYTES = p.stage_bytes;   // multiple of 1024
   constexpr int CTAS = PAIR ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   constexpr int STAGING_BYTES = Cfg<PAIR>::STAGING_BYTES;
-  const uint32_t staging = smem_base + STAGES * STAGE_BYTES;  // 1024-byte aligned
+  const uint32_t staging = smem_base + RING_BYTES;  // 1024-byte aligned
   const uint32_t bars = staging + STAGING_BYTES;
   // barrier layout (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], then tmem slot + abort flag
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + STAGES * STAGE_BYTES + STAGING_BYTES + 8 * (2 * STAGES + 4));
+  auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + RING_BYTES + STAGING_BYTES + 8 * (2 * MAX_STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -526,6 +533,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                   __uint_as_float(v[4 * j + 3]));
             continue;
           }
+        }
+        if (p.lstm) {
+          // LSTM step: pre-activation = product + input projection; this thread owns batch row `row` and the
+          // four gates of hidden units col0/4 .. col0/4 + 7
+          if (row < p.M) {
+            const int H = p.N >> 2, r0 = col0 >> 2;
+            const long long po = (long long)row * p.N + col0, ho = (long long)row * H + r0;
+            float cp[8];
+            *reinterpret_cast<float4*>(cp) = *reinterpret_cast<const float4*>(p.le.c_prev + ho);
+            *reinterpret_cast<float4*>(cp + 4) = *reinterpret_cast<const float4*>(p.le.c_prev + ho + 4);
+            float cn[8], hn[8];
+#pragma unroll
+            for (int uu = 0; uu < 8; uu++) {
+              const float4 xa = *reinterpret_cast<const float4*>(p.le.addend + po + 4 * uu);
+              const float f = fml_sigmoid(__uint_as_float(v[4 * uu]) + xa.x);
+              const float i = fml_sigmoid(__uint_as_float(v[4 * uu + 1]) + xa.y);
+              const float g = fml_tanh_ref(__uint_as_float(v[4 * uu + 2]) + xa.z);
+              const float o = fml_sigmoid(__uint_as_float(v[4 * uu + 3]) + xa.w);
+              cn[uu] = f * cp[uu] + i * g;
+              hn[uu] = o * fml_tanh_ref(cn[uu]);
+              *reinterpret_cast<float4*>(p.le.gates + po + 4 * uu) = make_float4(f, i, g, o);
+            }
+            *reinterpret_cast<float4*>(p.le.c_out + ho) = *reinterpret_cast<float4*>(cn);
+            *reinterpret_cast<float4*>(p.le.c_out + ho + 4) = *reinterpret_cast<float4*>(cn + 4);
+            *reinterpret_cast<float4*>(p.le.h_out + ho) = *reinterpret_cast<float4*>(hn);
+            *reinterpret_cast<float4*>(p.le.h_out + ho + 4) = *reinterpret_cast<float4*>(hn + 4);
+          }
+          continue;
         }
         if (p.tma_out) {
           // Optional output path (FML_GEMM_TMA_OUT=1): each thread puts its 32 values (one row of the 32x32
@@ -768,7 +803,7 @@ bool fml_gemm_tc_eligible(const fml_gemm_desc* d) {
   return true;
 }
 
-int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
+int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const fml_lstm_epilogue* lstm) {
   static bool attr_set = false;
   if (!attr_set) {
     FML_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES));
@@ -871,11 +906,20 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
     tmZ = tmA;
   }
   TcParams p;
+  p.lstm = lstm ? 1 : 0;
+  if (lstm) {
+    p.le = *lstm;
+    tma_out = false;
+  } else {
+    p.le = fml_lstm_epilogue{nullptr, nullptr, nullptr, nullptr, nullptr};
+  }
   p.tma_out = tma_out ? 1 : 0;
   p.M = d->M; p.N = d->N; p.K = d->K;
   p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.nb1 = nb1; p.nb2 = nb2;
   p.BN = BN; p.a_mn = a_mn; p.b_mn = b_mn; p.a_blk = a_blk; p.b_blk = b_blk;
   p.nseg = (precision == FML_PREC_3XTF32) ? 3 : 1;
+  p.stage_bytes = A_STAGE_BYTES + (pair ? BN / 2 : BN) * BK * 4;
+  p.nstages = std::min((int)Cfg<false>::MAX_STAGES, (int)Cfg<false>::RING_BYTES / p.stage_bytes);
   p.kblocks = (d->K + BK - 1) / BK;
   p.kchunk = (precision == FML_PREC_3XTF32 ? 1024 : 8192) / BK;
   if (p.kblocks <= p.kchunk + p.kchunk / 4) p.kchunk = p.kblocks;  // not worth a second chunk for a short tail
@@ -886,7 +930,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision) {
     // K split for plain TF32 products whose tiles occupy less than ~60 % of the SMs
     const long long tiles_all = (long long)tiles_m * tiles_n * nb1 * nb2;
     const long long ctas = tiles_all * (pair ? 2 : 1);
-    if (precision == FML_PREC_TF32 && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE &&
+    if (precision == FML_PREC_TF32 && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE && !lstm &&
         ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 8 && splitk_enabled()) {
       int want = (int)(ctx->sm_count / ctas);                 // CTAs available per tile
       int maxs = p.kblocks / 4;                               // at least 128 k per split

@@ -1,9 +1,12 @@
-// LSTM layer over a batch of sequences, built from the contraction kernels plus two fused
-// gate kernels.  The input projection of ALL timesteps is one large GEMM (bias folded into its
-// epilogue); each timestep then adds the recurrent product h_{t-1}.Wh^T into its slice with a
-// beta = 1 epilogue and runs one kernel that applies the four gate nonlinearities and the cell
-// update.  BPTT mirrors it: one gate-gradient kernel and one small GEMM per step, then the
-// weight gradients of all timesteps as two large GEMMs.
+// LSTM layer over a batch of sequences.  The four gate matrices are regrouped so that the gates of
+// one hidden unit are adjacent rows ("gate-interleaved"); then
+//   - the input projection of ALL timesteps is one large GEMM (bias in its epilogue);
+//   - each timestep is ONE tensor-core GEMM h_{t-1}.Wh^T whose epilogue adds the input projection,
+//     applies the four gate nonlinearities and the cell update, and writes gates, c_t and h_t
+//     (a thread owns one batch row and 32 consecutive columns = 8 hidden units x 4 gates);
+//   - BPTT is one gate-gradient kernel and one small (split-K) GEMM per step, then the weight
+//     gradients of all timesteps as two large GEMMs, regrouped back to the reference's row order.
+// Saved gates are [T][B][H][4] (f, i, c~, o per hidden unit).
 //
 // Reference: LSTMLayer.forward lib/layertypes/lstmLayer.dart:112-150.  Gate order f,i,c~,o
 // (:64); weight columns [h_{t-1} | x_t] (:119).
@@ -13,47 +16,58 @@
 
 namespace {
 
-__device__ __forceinline__ float sigf(float x) { return 1.f / (1.f + expf(-x)); }
-__device__ __forceinline__ float tanh_ref(float x) {
-  float e2x = expf(2.f * x);
-  return isinf(e2x) ? 1.f : (e2x - 1.f) / (e2x + 1.f);
+// W' = W with rows regrouped so that the four gates of a hidden unit are adjacent:
+// W'[4*r + q][:] = W[q*H + r][:]   (reference order: gate-major, lstmLayer.dart:64)
+__global__ void lstm_interleave_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, int H, int Z) {
+  const long long n = 4ll * H * Z;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % Z);
+    const int row = (int)(i / Z);  // destination row 4*r + q
+    const int r = row >> 2, q = row & 3;
+    dst[i] = src[((long long)q * H + r) * Z + c];
+  }
+}
+// dst[q*H + r][:] += src[4*r + q][:]  (gradients back into the reference's row order)
+__global__ void lstm_deinterleave_add_kernel(const float* __restrict__ src, float* __restrict__ dst, int H, int Z) {
+  const long long n = 4ll * H * Z;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % Z);
+    const int row = (int)(i / Z);
+    const int r = row >> 2, q = row & 3;
+    dst[((long long)q * H + r) * Z + c] += src[i];
+  }
 }
 
-// pre [B][4H] -> activated gates (in a separate buffer), c_t, h_t
+// Fallback gate kernel (CUDA-core path, shapes the tensor-core epilogue cannot take): pre [B][4H]
+// gate-interleaved -> activated gates, c_t, h_t
 __global__ void lstm_gates_fwd_kernel(const float* __restrict__ pre, const float* __restrict__ c_prev,
                                       float* __restrict__ gates, float* __restrict__ c_out, float* __restrict__ h_out,
                                       int B, int H) {
   const int n = B * H;
   for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
-    const int b = idx / H, r = idx - b * H;
-    const float* p = pre + (long long)b * 4 * H;
-    const float f = sigf(p[r]), i = sigf(p[H + r]), g = tanh_ref(p[2 * H + r]), o = sigf(p[3 * H + r]);
+    const float4 p = reinterpret_cast<const float4*>(pre)[idx];
+    const float f = fml_sigmoid(p.x), i = fml_sigmoid(p.y), g = fml_tanh_ref(p.z), o = fml_sigmoid(p.w);
     const float c = f * c_prev[idx] + i * g;
-    float* gt = gates + (long long)b * 4 * H;
-    gt[r] = f; gt[H + r] = i; gt[2 * H + r] = g; gt[3 * H + r] = o;
+    reinterpret_cast<float4*>(gates)[idx] = make_float4(f, i, g, o);
     c_out[idx] = c;
-    h_out[idx] = o * tanh_ref(c);
+    h_out[idx] = o * fml_tanh_ref(c);
   }
 }
 
-// dh, dc (in/out: becomes dc_{t-1}), saved gates and cells -> gradient of the pre-activations
+// dh, dc (in/out: becomes dc_{t-1}), saved gates (interleaved) and cells -> gradient of the pre-activations
 __global__ void lstm_gates_bwd_kernel(const float* __restrict__ dh, float* dc, const float* __restrict__ gates,
                                       const float* __restrict__ c_prev, const float* __restrict__ c_cur,
                                       float* __restrict__ dpre, int B, int H) {
   const int n = B * H;
   for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
-    const int b = idx / H, r = idx - b * H;
-    const float* gt = gates + (long long)b * 4 * H;
-    const float f = gt[r], i = gt[H + r], g = gt[2 * H + r], o = gt[3 * H + r];
-    const float tc = tanh_ref(c_cur[idx]);
+    const float4 gt = reinterpret_cast<const float4*>(gates)[idx];
+    const float f = gt.x, i = gt.y, g = gt.z, o = gt.w;
+    const float tc = fml_tanh_ref(c_cur[idx]);
     const float dhv = dh[idx];
     const float d_o = dhv * tc;
     const float dct = dc[idx] + dhv * o * (1.f - tc * tc);
-    float* dp = dpre + (long long)b * 4 * H;
-    dp[r] = dct * c_prev[idx] * (f * (1.f - f));
-    dp[H + r] = dct * g * (i * (1.f - i));
-    dp[2 * H + r] = dct * i * (1.f - g * g);
-    dp[3 * H + r] = d_o * (o * (1.f - o));
+    reinterpret_cast<float4*>(dpre)[idx] = make_float4(dct * c_prev[idx] * (f * (1.f - f)), dct * g * (i * (1.f - i)),
+                                                       dct * i * (1.f - g * g), d_o * (o * (1.f - o)));
     dc[idx] = dct * f;
   }
 }
@@ -70,6 +84,13 @@ fml_gemm_desc gemm_defaults() {
   return g;
 }
 
+// stream-ordered temporary (freed with cudaFreeAsync by the caller)
+int32_t temp_alloc(fml_ctx* ctx, size_t n_floats, float** out) {
+  cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(out), n_floats * sizeof(float), ctx->stream);
+  if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_OOM, std::string("lstm temporary: ") + cudaGetErrorString(e));
+  return FML_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -81,29 +102,46 @@ int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d) {
   const long long bh = (long long)B * H, b4h = (long long)B * 4 * H;
   FML_CUDA(ctx, cudaMemsetAsync(d->cells, 0, bh * 4, ctx->stream));
   FML_CUDA(ctx, cudaMemsetAsync(d->hs, 0, bh * 4, ctx->stream));
-  // xproj[T*B][4H] = x . Wx^T + b   (Wx = columns H.. of W)
+  // gate-interleaved copies of W and b: the four gates of a hidden unit become adjacent columns of every product
+  float* Wi = nullptr;
+  int32_t rc = temp_alloc(ctx, (size_t)4 * H * Z + 4 * H, &Wi);
+  if (rc) return rc;
+  float* bi = Wi + (size_t)4 * H * Z;
+  lstm_interleave_rows_kernel<<<blocks_for(ctx, 4ll * H * Z), 256, 0, ctx->stream>>>(d->W, Wi, H, Z);
+  lstm_interleave_rows_kernel<<<blocks_for(ctx, 4ll * H), 256, 0, ctx->stream>>>(d->b, bi, H, 1);
+  // xproj[T*B][4H] = x . Wx^T + b   (Wx = columns H.. of W), all timesteps in one product
   fml_gemm_desc g = gemm_defaults();
   g.M = T * B; g.N = 4 * H; g.K = I;
   g.A = d->x; g.lda = I;
-  g.B = d->W + H; g.ldb = Z; g.transB = 1;
+  g.B = Wi + H; g.ldb = Z; g.transB = 1;
   g.C = d->xproj; g.ldc = 4 * H;
-  g.bias = d->b;
-  int32_t rc = fml_gemm(ctx, &g);
-  if (rc) return rc;
-  for (int t = 0; t < T; t++) {
+  g.bias = bi;
+  rc = fml_gemm(ctx, &g);
+  const int prec = ctx->precision;
+  for (int t = 0; t < T && rc == FML_OK; t++) {
     float* pre = d->xproj + t * b4h;
-    if (t > 0) {
-      fml_gemm_desc r = gemm_defaults();
-      r.M = B; r.N = 4 * H; r.K = H;
-      r.A = d->hs + t * bh; r.lda = H;
-      r.B = d->W; r.ldb = Z; r.transB = 1;
-      r.C = pre; r.ldc = 4 * H; r.beta = 1.f;
-      if ((rc = fml_gemm(ctx, &r))) return rc;
+    fml_gemm_desc r = gemm_defaults();
+    r.M = B; r.N = 4 * H; r.K = H;
+    r.A = d->hs + t * bh; r.lda = H;
+    r.B = Wi; r.ldb = Z; r.transB = 1;
+    r.C = pre; r.ldc = 4 * H; r.beta = 1.f;
+    const bool fused = prec != FML_PREC_FP32 && fml_gemm_tc_eligible(&r) && (H % 8 == 0) &&
+                       (reinterpret_cast<uintptr_t>(pre) & 15) == 0;
+    if (fused) {
+      // recurrent product with the gate nonlinearity and the cell update in its epilogue
+      fml_lstm_epilogue le = {pre, d->cells + t * bh, d->cells + (t + 1) * bh, d->hs + (t + 1) * bh, d->gates + t * b4h};
+      r.beta = 0.f;
+      rc = fml_gemm_tc(ctx, &r, prec, &le);
+    } else {
+      if (t > 0) rc = fml_gemm(ctx, &r);
+      if (rc == FML_OK)
+        lstm_gates_fwd_kernel<<<blocks_for(ctx, bh), 256, 0, ctx->stream>>>(pre, d->cells + t * bh, d->gates + t * b4h,
+                                                                            d->cells + (t + 1) * bh, d->hs + (t + 1) * bh, B, H);
     }
-    lstm_gates_fwd_kernel<<<blocks_for(ctx, bh), 256, 0, ctx->stream>>>(pre, d->cells + t * bh, d->gates + t * b4h,
-                                                                        d->cells + (t + 1) * bh, d->hs + (t + 1) * bh, B, H);
   }
-  FML_LAUNCH_CHECK(ctx, "lstm_gates_fwd_kernel");
+  cudaFreeAsync(Wi, ctx->stream);
+  if (rc) return rc;
+  FML_LAUNCH_CHECK(ctx, "lstm forward");
   return FML_OK;
 }
 
@@ -112,48 +150,66 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
   FML_REQUIRE(ctx, d && dh_last && dW && db && scratch, "fml_lstm_bwd: NULL buffer");
   const int T = d->T, B = d->B, I = d->I, H = d->H, Z = H + I;
   const long long bh = (long long)B * H, b4h = (long long)B * 4 * H;
-  float* dpre = scratch;                 // [T*B][4H]
+  float* dpre = scratch;                     // [T*B][4H], gate-interleaved
   float* dh = scratch + (long long)T * b4h;  // [B][H]
-  float* dc = dh + bh;                   // [B][H]
-  FML_CUDA(ctx, cudaMemcpyAsync(dh, dh_last, bh * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-  FML_CUDA(ctx, cudaMemsetAsync(dc, 0, bh * 4, ctx->stream));
-  int32_t rc;
-  for (int t = T - 1; t >= 0; t--) {
+  float* dc = dh + bh;                       // [B][H]
+  // temporaries: interleaved W, interleaved dW and db
+  float* Wi = nullptr;
+  int32_t rc = temp_alloc(ctx, (size_t)2 * 4 * H * Z + 4 * H, &Wi);
+  if (rc) return rc;
+  float* dWi = Wi + (size_t)4 * H * Z;
+  float* dbi = dWi + (size_t)4 * H * Z;
+  lstm_interleave_rows_kernel<<<blocks_for(ctx, 4ll * H * Z), 256, 0, ctx->stream>>>(d->W, Wi, H, Z);
+  cudaMemsetAsync(dWi, 0, ((size_t)4 * H * Z + 4 * H) * sizeof(float), ctx->stream);
+  cudaMemcpyAsync(dh, dh_last, bh * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+  cudaMemsetAsync(dc, 0, bh * 4, ctx->stream);
+  for (int t = T - 1; t >= 0 && rc == FML_OK; t--) {
     lstm_gates_bwd_kernel<<<blocks_for(ctx, bh), 256, 0, ctx->stream>>>(dh, dc, d->gates + t * b4h, d->cells + t * bh,
                                                                         d->cells + (t + 1) * bh, dpre + t * b4h, B, H);
     if (t > 0) {
-      // dh_{t-1} = dpre_t . Wh   (Wh = columns 0..H-1 of W)
+      // dh_{t-1} = dpre_t . Wh   (Wh = columns 0..H-1 of the interleaved W)
       fml_gemm_desc r = gemm_defaults();
       r.M = B; r.N = H; r.K = 4 * H;
       r.A = dpre + t * b4h; r.lda = 4 * H;
-      r.B = d->W; r.ldb = Z;
+      r.B = Wi; r.ldb = Z;
       r.C = dh; r.ldc = H;
-      if ((rc = fml_gemm(ctx, &r))) return rc;
+      rc = fml_gemm(ctx, &r);
     }
   }
-  FML_LAUNCH_CHECK(ctx, "lstm_gates_bwd_kernel");
-  // dW[:, 0:H] += dpre^T . h_{t-1} over all steps; dW[:, H:] += dpre^T . x; db += column sums
-  fml_gemm_desc wh = gemm_defaults();
-  wh.M = 4 * H; wh.N = H; wh.K = T * B;
-  wh.A = dpre; wh.lda = 4 * H; wh.transA = 1;
-  wh.B = d->hs; wh.ldb = H;
-  wh.C = dW; wh.ldc = Z; wh.beta = 1.f;
-  if ((rc = fml_gemm(ctx, &wh))) return rc;
-  fml_gemm_desc wx = gemm_defaults();
-  wx.M = 4 * H; wx.N = I; wx.K = T * B;
-  wx.A = dpre; wx.lda = 4 * H; wx.transA = 1;
-  wx.B = d->x; wx.ldb = I;
-  wx.C = dW + H; wx.ldc = Z; wx.beta = 1.f;
-  if ((rc = fml_gemm(ctx, &wx))) return rc;
-  if ((rc = fml_col_sum(ctx, dpre, db, (int64_t)T * B, 4 * H, 1))) return rc;
-  if (dx) {
+  // dW'[:, 0:H] = dpre^T . h_{t-1} over all steps; dW'[:, H:] = dpre^T . x; db' = column sums
+  if (rc == FML_OK) {
+    fml_gemm_desc wh = gemm_defaults();
+    wh.M = 4 * H; wh.N = H; wh.K = T * B;
+    wh.A = dpre; wh.lda = 4 * H; wh.transA = 1;
+    wh.B = d->hs; wh.ldb = H;
+    wh.C = dWi; wh.ldc = Z; wh.beta = 1.f;
+    rc = fml_gemm(ctx, &wh);
+  }
+  if (rc == FML_OK) {
+    fml_gemm_desc wx = gemm_defaults();
+    wx.M = 4 * H; wx.N = I; wx.K = T * B;
+    wx.A = dpre; wx.lda = 4 * H; wx.transA = 1;
+    wx.B = d->x; wx.ldb = I;
+    wx.C = dWi + H; wx.ldc = Z; wx.beta = 1.f;
+    rc = fml_gemm(ctx, &wx);
+  }
+  if (rc == FML_OK) rc = fml_col_sum(ctx, dpre, dbi, (int64_t)T * B, 4 * H, 1);
+  if (rc == FML_OK) {
+    // back to the reference's gate-major row order, accumulating like every gradient
+    lstm_deinterleave_add_kernel<<<blocks_for(ctx, 4ll * H * Z), 256, 0, ctx->stream>>>(dWi, dW, H, Z);
+    lstm_deinterleave_add_kernel<<<blocks_for(ctx, 4ll * H), 256, 0, ctx->stream>>>(dbi, db, H, 1);
+  }
+  if (rc == FML_OK && dx) {
     fml_gemm_desc gx = gemm_defaults();
     gx.M = T * B; gx.N = I; gx.K = 4 * H;
     gx.A = dpre; gx.lda = 4 * H;
-    gx.B = d->W + H; gx.ldb = Z;
+    gx.B = Wi + H; gx.ldb = Z;
     gx.C = dx; gx.ldc = I;
-    if ((rc = fml_gemm(ctx, &gx))) return rc;
+    rc = fml_gemm(ctx, &gx);
   }
+  cudaFreeAsync(Wi, ctx->stream);
+  if (rc) return rc;
+  FML_LAUNCH_CHECK(ctx, "lstm backward");
   return FML_OK;
 }
 

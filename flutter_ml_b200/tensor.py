@@ -99,9 +99,11 @@ class Tensor:
             self.ctx.zero(buf)
         self.ctx.call("fml_axpy", float(scale), g, buf, buf.size)
 
-    def backward(self):
+    def backward(self, retain_graph: bool = False):
         """Topological order by depth-first search over creators, seed gradient 1, closures in
-        reverse (tensor.dart:43-75)."""
+        reverse (tensor.dart:43-75).  Unless `retain_graph`, the creators are dropped afterwards: every
+        closure refers to its own output tensor, a reference cycle that would keep the saved
+        activations in device memory until Python's cycle collector happens to run."""
         topo, seen, stack = [], set(), [(self, False)]
         while stack:
             t, done = stack.pop()
@@ -121,6 +123,9 @@ class Tensor:
         for t in reversed(topo):
             if t.creator is not None:
                 t.creator.backwardFn()
+        if not retain_graph:
+            for t in topo:
+                t.creator = None
 
     def detach_graph(self):
         """Drop creators (and with them saved activations) reachable from this tensor."""

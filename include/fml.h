@@ -250,14 +250,14 @@ typedef struct {
   const float* W;
   const float* b;
   const float* x;
-  float* gates;  /* [T][B][4H] activated gates            */
+  float* gates;  /* [T][B][H][4] activated gates f,i,c~,o per unit */
   float* cells;  /* [T+1][B][H], slot 0 zeroed by the call */
   float* hs;     /* [T+1][B][H], slot 0 zeroed by the call */
   float* xproj;  /* scratch [T*B][4H]                      */
 } fml_lstm_desc;
 int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d);
 int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last, float* dW, float* db,
-                     float* dx, float* scratch /* [T*B][4H] + 2*[B][H] + [B][H+I] */);
+                     float* dx, float* scratch /* [T*B][4H] + 2*[B][H] floats */);
 
 /* ---- data parallel (one process per GPU) -------------------------------------
  * The reference has no multi-device code.  Rank 0 creates an id, the host
