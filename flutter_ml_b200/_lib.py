@@ -106,6 +106,7 @@ PROTOTYPES = {
     "fml_dp_unique_id": [C.c_char_p],
     "fml_dp_init": [fp, C.c_char_p, i32, i32],
     "fml_dp_allreduce_sum": [fp, fp, i64],
+    "fml_dp_allreduce_sum_on": [fp, i32, fp, i64],
     "fml_dp_shutdown": [fp],
 }
 _RESTYPES = {"fml_last_error": C.c_char_p, "multiplyMatrices": None}

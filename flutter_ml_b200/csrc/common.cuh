@@ -39,6 +39,8 @@ struct fml_ctx {
 void fml_set_global_error(const std::string& msg);
 int32_t fml_fail(fml_ctx* ctx, int32_t code, const std::string& msg);
 int32_t fml_ensure_workspace(fml_ctx* ctx, size_t bytes);
+// stream of copy lane `lane` (created on first use); lane < 0 is the context's main stream
+extern "C" int32_t fml_any_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out);
 // like fml_ensure_workspace, but fails instead of reallocating when work already queued on the stream uses the arena
 int32_t fml_ensure_workspace_keep(fml_ctx* ctx, size_t bytes);
 

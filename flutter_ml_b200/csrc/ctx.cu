@@ -263,10 +263,11 @@ static int32_t lane_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
   *out = ctx->lanes[lane];
   return FML_OK;
 }
-static int32_t any_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
+int32_t fml_any_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
   if (lane < 0) { *out = ctx->stream; return FML_OK; }
   return lane_stream(ctx, lane, out);
 }
+static int32_t any_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) { return fml_any_stream(ctx, lane, out); }
 int32_t fml_event_record_on(fml_ctx* ctx, int32_t slot, int32_t lane) {
   FML_REQUIRE(ctx, slot >= 0 && slot < 64, "fml_event_record_on: slot out of range");
   cudaStream_t s;

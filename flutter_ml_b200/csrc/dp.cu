@@ -81,14 +81,19 @@ int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id_bytes[128], int32_t rank, int
   return FML_OK;
 }
 
-int32_t fml_dp_allreduce_sum(fml_ctx* ctx, float* buf, int64_t n) {
+int32_t fml_dp_allreduce_sum_on(fml_ctx* ctx, int32_t lane, float* buf, int64_t n) {
   if (ctx->dp_world == 1) return FML_OK;
   FML_REQUIRE(ctx, ctx->nccl_comm, "fml_dp_allreduce_sum: fml_dp_init has not been called");
+  cudaStream_t s;
+  int32_t rc0 = fml_any_stream(ctx, lane, &s);
+  if (rc0) return rc0;
   NcclApi* a = nccl();
-  int rc = a->all_reduce(buf, buf, (size_t)n, /*ncclFloat32*/ 7, /*ncclSum*/ 0, ctx->nccl_comm, ctx->stream);
+  int rc = a->all_reduce(buf, buf, (size_t)n, /*ncclFloat32*/ 7, /*ncclSum*/ 0, ctx->nccl_comm, s);
   if (rc) return nccl_fail(ctx, "ncclAllReduce", rc);
   return FML_OK;
 }
+
+int32_t fml_dp_allreduce_sum(fml_ctx* ctx, float* buf, int64_t n) { return fml_dp_allreduce_sum_on(ctx, -1, buf, n); }
 
 int32_t fml_dp_shutdown(fml_ctx* ctx) {
   if (ctx->nccl_comm) {

@@ -140,25 +140,55 @@ class TransformerLM:
         self.optimizer = Adam(self.parameters, lr, arena=self.arena)
         del probe, h
 
-    def forward_backward(self, ids, labels, n_global_tokens: int, keep_logits: bool = False):
-        """ids, labels: int32 DeviceArrays [n_seq * seq_len] of this rank's shard."""
+    def _slice(self, first_param: int, n_params: int):
+        """(offset, length) in the arena of `n_params` consecutive parameters."""
+        offs = self.arena.offsets
+        end = offs[first_param + n_params] if first_param + n_params < len(offs) else self.arena.size
+        return offs[first_param], end - offs[first_param]
+
+    def _exchange(self, off: int, n: int):
+        """Sum one finished slice of the gradient arena across ranks on the communication lane, after
+        everything queued so far on the main stream."""
+        c = self.ctx
+        c.check(c.lib.fml_event_record_on(c.h, 50, -1))
+        c.check(c.lib.fml_wait_event(c.h, 0, 50))
+        c.check(c.lib.fml_dp_allreduce_sum_on(c.h, 0, self.arena.grads.ptr + 4 * off, n))
+
+    def forward_backward(self, ids, labels, n_global_tokens: int, keep_logits: bool = False, overlap_exchange: bool = False):
+        """ids, labels: int32 DeviceArrays [n_seq * seq_len] of this rank's shard.  With
+        `overlap_exchange` the all-reduce of each finished slice of the gradient arena (head, then the
+        blocks from last to first, then the embedding) runs on a side stream under the rest of backward."""
         ctx = self.ctx
         h = self.embedding(ids)
+        inputs = []
         for blk in self.blocks:
+            inputs.append(h)
             h = blk(h)
+        inputs.append(h)
         logits = self.head(h)
+        before = None
+        if overlap_exchange and self.world > 1:
+            per_block = len(self.blocks[0].parameters)
+            L = len(self.blocks)
+            before = {id(inputs[L]): (lambda: self._exchange(*self._slice(1 + L * per_block, 2)))}
+            for i in range(L - 1, -1, -1):
+                before[id(inputs[i])] = (lambda i=i: self._exchange(*self._slice(1 + i * per_block, per_block)))
         kept = None
         if keep_logits:
             kept = ctx.empty(*logits.shape)
             ctx.copy(kept, logits.value)
         loss = T.softmaxCrossEntropy(logits, labels, 1.0 / n_global_tokens)
-        loss.backward()
-        loss.detach_graph()
+        loss.backward(before=before)
+        if before:
+            self._exchange(*self._slice(0, 1))              # the embedding table's gradient, last
+            c = self.ctx
+            c.check(c.lib.fml_event_record_on(c.h, 51, 0))  # main stream continues once the lane is done
+            c.check(c.lib.fml_wait_event(c.h, -1, 51))
         return loss, kept
 
-    def train_step(self, ids, labels, n_global_tokens: int):
-        loss, _ = self.forward_backward(ids, labels, n_global_tokens)
-        if self.world > 1:
+    def train_step(self, ids, labels, n_global_tokens: int, overlap_exchange: bool = True):
+        loss, _ = self.forward_backward(ids, labels, n_global_tokens, overlap_exchange=overlap_exchange)
+        if self.world > 1 and not overlap_exchange:
             self.ctx.call("fml_dp_allreduce_sum", self.arena.grads, self.arena.size)
         self.optimizer.step()
         self.optimizer.zeroGrad()

@@ -99,7 +99,7 @@ class Tensor:
             self.ctx.zero(buf)
         self.ctx.call("fml_axpy", float(scale), g, buf, buf.size)
 
-    def backward(self, retain_graph: bool = False):
+    def backward(self, retain_graph: bool = False, before=None):
         """Topological order by depth-first search over creators, seed gradient 1, closures in
         reverse (tensor.dart:43-75).  Unless `retain_graph`, the creators are dropped afterwards: every
         closure refers to its own output tensor, a reference cycle that would keep the saved
@@ -120,7 +120,11 @@ class Tensor:
                         stack.append((i, False))
         if self.grad is None:
             self.grad = self.ctx.upload(np.ones(self.value.shape, dtype=np.float32))
+        # `before`: {id(tensor): callable} run just before that tensor's creator, i.e. once every consumer
+        # of the tensor has contributed its gradient (used to start exchanging finished gradient slices)
         for t in reversed(topo):
+            if before and id(t) in before:
+                before[id(t)]()
             if t.creator is not None:
                 t.creator.backwardFn()
         if not retain_graph:

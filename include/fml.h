@@ -266,6 +266,9 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
 int32_t fml_dp_unique_id(uint8_t out[128]);
 int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id[128], int32_t rank, int32_t world);
 int32_t fml_dp_allreduce_sum(fml_ctx* ctx, float* buf, int64_t n);
+/* The same on copy lane `lane` (or -1: the main stream), to overlap the exchange of finished gradient
+ * slices with the rest of the backward pass; order it against the main stream with the event calls. */
+int32_t fml_dp_allreduce_sum_on(fml_ctx* ctx, int32_t lane, float* buf, int64_t n);
 int32_t fml_dp_shutdown(fml_ctx* ctx);
 
 #ifdef __cplusplus
