@@ -26,6 +26,10 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch (mean of forward, dA, dW), from the ncu
+# captures summarised under profiles/ (keyed by M=N=K)
+NCU_DRAM_BYTES_PER_LAUNCH = {4096: 406_000_000}
+
 SWEEP = [(512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
          (16384, 4096, 1024)]
 
@@ -169,6 +173,29 @@ def time_sweep(ctx, reps=5):
         for a in (A, B, bias, dC, C, Z, dZ, dA, dB, db):
             a.free()
     return out
+
+
+def cublas_tf32_yardstick(n=8192, reps=10):
+    """Library TF32 GEMM (torch.matmul -> cuBLAS) on the same GPU with random operands: a yardstick for
+    the tensor-core ceiling beside the driver-measured bf16 figure.  Not on the hot path."""
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = True
+    a = torch.randn(n, n, device="cuda")
+    b = torch.randn(n, n, device="cuda")
+    for _ in range(3):
+        a @ b
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        a @ b
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    del a, b
+    torch.cuda.empty_cache()
+    return {"library": "torch.matmul (cuBLAS), allow_tf32", "M=N=K": n, "ms": round(ms, 4),
+            "tflops": round(2.0 * n ** 3 / ms / 1e9, 1), "note": "one plain product, no epilogue; for scale only"}
 
 
 def time_membound(ctx, hbm_gbs, reps=5, rows=262144, params=1 << 28):
@@ -340,7 +367,8 @@ def main():
     long_run = ms_total > 1000.0
     tf32_peak = (peaks["bf16_sustained"] if long_run else peaks["bf16_burst"]) / 2.0
     roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel", "achieved": round(achieved, 1), "peak": round(tf32_peak, 1),
-                "unit": "TFLOP/s", "frac": round(achieved / tf32_peak, 4), "traffic": None,
+                "unit": "TFLOP/s", "frac": round(achieved / tf32_peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(M),
+                "algorithmic_bytes": 4 * (M * K + K * N + M * N),
                 "peak_source": f"{peaks['source']}: MEASURED_PEAKS bf16 {'sustained' if long_run else 'burst'} / 2 "
                                "(dense TF32 runs at half the bf16 rate; no TF32 figure is measured by the driver)",
                 "per_gemm_ms": {"fwd": round(statistics.mean(gemm_ms[0::3]), 4), "dA": round(statistics.mean(gemm_ms[1::3]), 4),
@@ -379,6 +407,11 @@ def main():
 
     if rank == 0 and not args.no_sweep:
         line["sweep"] = time_sweep(ctx)
+    if rank == 0 and not args.no_sweep:
+        try:
+            line["calibration"] = cublas_tf32_yardstick()
+        except Exception as exc:  # the yardstick must never break the benchmark
+            line["calibration"] = {"error": str(exc)[:200]}
     if rank == 0 and not args.no_configs:
         from flutter_ml_b200 import config_bench
         line["configs"] = config_bench.run(ctx)
