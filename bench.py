@@ -28,7 +28,7 @@ sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch (mean of forward, dA, dW), from the ncu
 # captures summarised under profiles/ (keyed by M=N=K)
-NCU_DRAM_BYTES_PER_LAUNCH = {4096: 406_000_000}
+NCU_DRAM_BYTES_PER_LAUNCH = {4096: 406_000_000, 8192: 2_967_000_000}
 
 SWEEP = [(512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
          (16384, 4096, 1024)]
@@ -253,7 +253,7 @@ def time_membound(ctx, hbm_gbs, reps=5, rows=262144, params=1 << 28):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M=N=K of the timed step")
