@@ -2,11 +2,13 @@
 // accumulator in TMEM, operands staged in shared memory by TMA, a warp-specialised
 // producer / MMA-issuer / epilogue pipeline and a persistent tile loop.
 //
-// One CTA = 192 threads:
+// One CTA = 320 threads:
 //   warp 0      TMA producer   (one lane issues cp.async.bulk.tensor per stage)
 //   warp 1      MMA issuer     (one lane issues tcgen05.mma; the warp owns TMEM alloc/free)
-//   warps 2..5  epilogue       (tcgen05.ld -> bias/activation -> global stores); warp w reads
-//                              the TMEM lane quarter w % 4
+//   warps 2..9  epilogue       (tcgen05.ld -> bias/activation -> global stores); warp w reads the TMEM
+//                              lane quarter w % 4, and the two warps of a quarter take alternate
+//                              32-column blocks (the epilogue is instruction-latency bound: these are
+//                              the only busy warps of their schedulers)
 // Tile: 128 (M) x BN (N, 64/128/256) x 32 (K, one 128-byte swizzle row of fp32).
 // TMEM holds two accumulators (columns [0,256) and [256,512)) so the epilogue of tile i
 // overlaps the main loop of tile i+1.
@@ -63,14 +65,13 @@ constexpr int BK = 32;
 constexpr int A_STAGE_BYTES = BM * BK * 4;    // 16 KiB
 template <bool PAIR> struct Cfg {
   // The operand ring holds RING_BYTES; a stage is 16 KiB of A plus 128 B per staged B column, so narrow
-  // tiles get a deeper ring (BN = 256 single: 4 stages, pair or BN = 128: 6, BN = 64: 8), which is what
+  // tiles get a deeper ring (BN = 256 single: 4 stages, pair or BN = 128: 7, BN = 64: 9), which is what
   // hides the load latency of short, latency-bound products.
-  static constexpr int RING_BYTES = 6 * 32768;
+  static constexpr int RING_BYTES = 7 * 32768;
   static constexpr int MAX_STAGES = 12;
-  static constexpr int STAGING_BYTES = 4 * 2 * 4096;  // epilogue: 4 warps x 2 buffers x (32 rows x 128 B)
-  static constexpr int SMEM_BYTES = RING_BYTES + STAGING_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int SMEM_BYTES = RING_BYTES + 1024 /*align*/ + 512 /*barriers*/;
 };
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // producer warp, issuer warp, 8 epilogue warps
 constexpr uint32_t TMEM_COLS = 512;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
@@ -98,7 +99,6 @@ struct TcParams {
   uint32_t idesc;
   int lstm;     // 1: LSTM gate epilogue (see fml_lstm_epilogue); C is not written
   fml_lstm_epilogue le;
-  int tma_out;  // 1: the epilogue stages 32x32 blocks in shared memory and writes them with TMA (store or reduce-add)
   int debug;  // diagnostics only: 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
 };
 
@@ -170,18 +170,6 @@ __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(tm), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
-// shared -> global tile store / reduce-add (bulk async group completion); out-of-range parts of the box are clipped
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-               ::"l"(tm), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-               ::"l"(tm), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // cta_group::2 form: the completion is signalled on the LEADER CTA's barrier (bit 24 of a
 // shared::cluster address selects the odd CTA of a pair; clearing it names the even one)
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
@@ -283,7 +271,6 @@ template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmAlo, const __grid_constant__ CUtensorMap tmBlo,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmZ,
                const TcParams p) {
   constexpr int MAX_STAGES = Cfg<PAIR>::MAX_STAGES;
   constexpr int RING_BYTES = Cfg<PAIR>::RING_BYTES;
@@ -294,15 +281,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 B
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  constexpr int STAGING_BYTES = Cfg<PAIR>::STAGING_BYTES;
-  const uint32_t staging = smem_base + RING_BYTES;  // 1024-byte aligned
-  const uint32_t bars = staging + STAGING_BYTES;
+  const uint32_t bars = smem_base + RING_BYTES;
   // barrier layout (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], then tmem slot + abort flag
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + RING_BYTES + STAGING_BYTES + 8 * (2 * MAX_STAGES + 4));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + RING_BYTES + 8 * (2 * MAX_STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -318,7 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4 * CTAS);  // every epilogue warp of the pair
+      mbar_init(tempty_bar(a), 8 * CTAS);  // every epilogue warp of the pair
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -475,8 +460,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    int stage_buf = 0;       // which of this warp's two staging blocks is written next
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;  // two warps share a quarter and take alternate 32-column blocks
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
@@ -484,6 +469,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         ((p.sC1 & 3) == 0) && ((p.sC2 & 3) == 0) &&
                         (p.Z == nullptr || (reinterpret_cast<uintptr_t>(p.Z) & 15) == 0) &&
                         (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
+    const bool plain = !p.bias && p.alpha == 1.f && p.act == FML_ACT_NONE && !p.Z && p.beta == 0.f && p.ksplit == 1;
     for (int u = unit; u < num_units && ok; u += unit_stride) {
       int t, kb0, nkb, b, tm, tn;
       unit_range(u, t, kb0, nkb);
@@ -502,13 +488,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const long long boff = (long long)b1 * p.sC1 + (long long)b2 * p.sC2 + (long long)row * p.ldc;
       float* crow = p.C + boff;
       float* zrow = p.Z ? p.Z + boff : nullptr;
-      const int ncols32 = p.BN / 32;
-      for (int c = 0; c < ncols32; c++) {
+      const int ncols32 = min(p.BN / 32, (p.N - n0 + 31) / 32);  // 32-column blocks of this tile inside the matrix
+      const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u;
+      // one 32x32 block of the accumulator, held as one row per thread
+      auto process = [&](const int c, uint32_t (&v)[32]) {
         const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;  // warp-uniform
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * 256u + (uint32_t)c * 32u, v);
-        tmem_ld_wait();
         if (mode != 0) {
           // this thread owns 32 consecutive floats of the slab per column chunk: [c][row][32]
           float4* sp = reinterpret_cast<float4*>(slab + (size_t)c * (BM * 32));
@@ -517,7 +501,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int j = 0; j < 8; j++)
               sp[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
                                   __uint_as_float(v[4 * j + 3]));
-            continue;
+            return;
           }
 #pragma unroll
           for (int j = 0; j < 8; j++) {
@@ -532,7 +516,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int j = 0; j < 8; j++)
               sp[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
                                   __uint_as_float(v[4 * j + 3]));
-            continue;
+            return;
           }
         }
         if (p.lstm) {
@@ -561,79 +545,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             *reinterpret_cast<float4*>(p.le.h_out + ho) = *reinterpret_cast<float4*>(hn);
             *reinterpret_cast<float4*>(p.le.h_out + ho + 4) = *reinterpret_cast<float4*>(hn + 4);
           }
-          continue;
-        }
-        if (p.tma_out) {
-          // Optional output path (FML_GEMM_TMA_OUT=1): each thread puts its 32 values (one row of the 32x32
-          // block) into a 128B-swizzled staging block and one lane hands the block to TMA (store, or
-          // reduce-add for beta = 1 and K splits); the bulk store clips at the matrix edge.
-          const int row0 = m0 + q * 32;
-          if (row0 < p.M) {  // warp-uniform
-            float o[32];
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 bz = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (p.bias && col0 + j < p.N) bz = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-              o[j] = __uint_as_float(v[j]) * p.alpha + bz.x;
-              o[j + 1] = __uint_as_float(v[j + 1]) * p.alpha + bz.y;
-              o[j + 2] = __uint_as_float(v[j + 2]) * p.alpha + bz.z;
-              o[j + 3] = __uint_as_float(v[j + 3]) * p.alpha + bz.w;
-            }
-            const uint32_t my_staging = staging + (uint32_t)((warp - 2) * 2) * 4096u;
-#pragma unroll
-            for (int pass = 0; pass < 2; pass++) {
-              if (pass == 0 && p.Z == nullptr) continue;  // pass 0: pre-activation, pass 1: result
-              if (pass == 1) {
-#pragma unroll
-                for (int j = 0; j < 32; j++) o[j] = fml_act_apply(p.act, o[j]);
-              }
-              const uint32_t blk = my_staging + (uint32_t)stage_buf * 4096u;
-              if (lane == 0) bulk_wait_read_1();  // the store that last used this block has read it
-              __syncwarp();
-#pragma unroll
-              for (int j = 0; j < 8; j++) {
-                const uint32_t a = blk + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
-                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(o[4 * j]), "f"(o[4 * j + 1]),
-                             "f"(o[4 * j + 2]), "f"(o[4 * j + 3]) : "memory");
-              }
-              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-              __syncwarp();
-              if (lane == 0) {
-                if (pass == 0) tma_store_4d(&tmZ, blk, col0, row0, b1, b2);
-                else if (p.beta != 0.f || p.ksplit > 1) tma_reduce_add_4d(&tmC, blk, col0, row0, b1, b2);
-                else tma_store_4d(&tmC, blk, col0, row0, b1, b2);
-                bulk_commit();
-              }
-              stage_buf ^= 1;
-            }
-          }
-          continue;
+          return;
         }
         if (row < p.M) {
           const bool full = (col0 + 32 <= p.N);
           if (full && vec_ok) {
+            // The four epilogue warps are the only warps of their schedulers, so every instruction waits out
+            // its full latency: the code below keeps branches out of the per-element loops and gives the
+            // common plain product (no bias, scale, activation, second output or accumulation) a store-only path.
+            float4* cp = reinterpret_cast<float4*>(crow + col0);
+            if (plain) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o;
-              float* op = reinterpret_cast<float*>(&o);
-              float4 bz = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (p.bias) bz = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-              const float* bp = reinterpret_cast<const float*>(&bz);
-#pragma unroll
-              for (int e = 0; e < 4; e++) op[e] = __uint_as_float(v[j + e]) * p.alpha + bp[e];
-              if (zrow) *reinterpret_cast<float4*>(zrow + col0 + j) = o;
-#pragma unroll
-              for (int e = 0; e < 4; e++) op[e] = fml_act_apply(p.act, op[e]);
-              if (p.ksplit > 1) {
-                atomicAdd(reinterpret_cast<float4*>(crow + col0 + j), o);  // K split: partial products add up in C
-                continue;
-              }
-              if (p.beta != 0.f) {
-                float4 old = *reinterpret_cast<const float4*>(crow + col0 + j);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(crow + col0 + j) = o;
+              for (int j = 0; j < 8; j++)
+                reinterpret_cast<uint4*>(cp)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              return;
             }
+            float o[32];
+            if (p.bias) {
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const float4 bz = *reinterpret_cast<const float4*>(p.bias + col0 + 4 * j);
+                o[4 * j] = fmaf(__uint_as_float(v[4 * j]), p.alpha, bz.x);
+                o[4 * j + 1] = fmaf(__uint_as_float(v[4 * j + 1]), p.alpha, bz.y);
+                o[4 * j + 2] = fmaf(__uint_as_float(v[4 * j + 2]), p.alpha, bz.z);
+                o[4 * j + 3] = fmaf(__uint_as_float(v[4 * j + 3]), p.alpha, bz.w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * p.alpha;
+            }
+            if (zrow) {
+              float4* zp = reinterpret_cast<float4*>(zrow + col0);
+#pragma unroll
+              for (int j = 0; j < 8; j++) zp[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            }
+            if (p.act == FML_ACT_RELU) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) o[j] = o[j] > 0.f ? o[j] : 0.f;
+            } else if (p.act != FML_ACT_NONE) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) o[j] = fml_act_apply_slow(p.act, o[j]);
+            }
+            if (p.ksplit > 1) {
+#pragma unroll
+              for (int j = 0; j < 8; j++)  // K split: partial products add up in C
+                atomicAdd(cp + j, make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+              return;
+            }
+            if (p.beta != 0.f) {
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const float4 old = cp[j];
+                o[4 * j] += old.x; o[4 * j + 1] += old.y; o[4 * j + 2] += old.z; o[4 * j + 3] += old.w;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) cp[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
@@ -649,6 +616,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
         }
+      };
+      // The eight epilogue warps are the only warps on their schedulers besides the two single-lane roles, so
+      // each instruction waits out its full latency; two warps per TMEM lane quarter interleave their blocks.
+      for (int c = half; c < ncols32; c += 2) {
+        uint32_t v[32];
+        tmem_ld32(tacc + (uint32_t)c * 32u, v);
+        tmem_ld_wait();
+        process(c, v);
       }
       tc_fence_before();
       __syncwarp();
@@ -661,7 +636,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
 
-  if (warp >= 2 && lane == 0 && p.tma_out) bulk_wait_all();  // every bulk store of this thread has completed
   // common tail: everyone arrives (both CTAs of a pair: the peer's barriers and TMEM stay alive
   // until nothing can signal or read them), then the allocating warp frees TMEM
   tc_fence_before();
@@ -758,18 +732,6 @@ int32_t make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, i
   if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
   ctx->tmaps[key] = *out;
   return FML_OK;
-}
-
-bool tma_out_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    // Off by default.  Measured on B200 (16384 x 4096 x 1024, bias + ReLU, two outputs): 284 TFLOP/s with the
-    // staged TMA epilogue against 567 with direct 128-bit stores; two 4 KiB staging blocks per warp are too
-    // few bytes in flight, and shared memory has no room for more next to the operand ring.
-    const char* e = getenv("FML_GEMM_TMA_OUT");
-    v = e ? atoi(e) : 0;
-  }
-  return v != 0;
 }
 
 bool splitk_enabled() {
@@ -890,31 +852,13 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     tmBlo = tmB;
   }
 
-  // output maps for the TMA epilogue: rank 4 {N, M, nb1, nb2}, box 32 x 32, 128B swizzle
-  CUtensorMap tmC, tmZ;
-  auto al16p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-  bool tma_out = al16p(d->C) && (d->ldc & 3) == 0 && (nb1 <= 1 || (d->sC1 & 3) == 0) && (nb2 <= 1 || (d->sC2 & 3) == 0) &&
-                 (!d->preact || al16p(d->preact)) && (!d->bias || (al16p(d->bias) && (d->N & 3) == 0)) && tma_out_enabled();
-  if (tma_out) {
-    if ((rc = make_tmap(ctx, d->C, d->N, d->M, d->ldc, nb1, nb2, d->sC1, d->sC2, 32, 32, false, 0, &tmC))) return rc;
-    if (d->preact) {
-      if ((rc = make_tmap(ctx, d->preact, d->N, d->M, d->ldc, nb1, nb2, d->sC1, d->sC2, 32, 32, false, 0, &tmZ))) return rc;
-    } else {
-      tmZ = tmC;
-    }
-  } else {
-    tmC = tmA;
-    tmZ = tmA;
-  }
   TcParams p;
   p.lstm = lstm ? 1 : 0;
   if (lstm) {
     p.le = *lstm;
-    tma_out = false;
   } else {
     p.le = fml_lstm_epilogue{nullptr, nullptr, nullptr, nullptr, nullptr};
   }
-  p.tma_out = tma_out ? 1 : 0;
   p.M = d->M; p.N = d->N; p.K = d->K;
   p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.nb1 = nb1; p.nb2 = nb2;
   p.BN = BN; p.a_mn = a_mn; p.b_mn = b_mn; p.a_blk = a_blk; p.b_blk = b_blk;
@@ -994,10 +938,10 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, tmC, tmZ, p));
+    FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, p));
   } else {
     const int grid = (int)std::min<long long>(num_tiles, ctx->sm_count);
-    gemm_tc_kernel<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, tmC, tmZ, p);
+    gemm_tc_kernel<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, p);
   }
   FML_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
   ctx->last_gemm_path = 1;
