@@ -28,7 +28,7 @@ def dense_backward(ctx, X, W, saved, dY, act, M, N, K, dZ, dX=None, dW=None, db=
     if code == _lib.ACT_NONE and db is None:
         dZ = dY
     else:
-        ctx.call("fml_act_bwd", code, saved, dY, dZ, M, N, 0, db, launches=2 if db is not None else 1)
+        ctx.call("fml_act_bwd", code, saved, dY, dZ, M, N, 0, db)
     beta = 1.0 if accumulate else 0.0
     if dX is not None:
         ctx.gemm(dZ, W, dX, M, K, N, transB=True, beta=beta, precision=precision)
