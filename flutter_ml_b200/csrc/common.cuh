@@ -108,6 +108,19 @@ __device__ __forceinline__ float fml_act_apply(int act, float v) {
   return fml_act_apply_slow(act, v);
 }
 // derivative from the saved tensor: x for RELU/GELU, y for SIGMOID/TANH
+static __device__ __noinline__ float fml_act_grad_gelu(float s) {
+  const float cdf = 0.5f * (1.f + erff(s * 0.70710678118654752440f));
+  const float pdf = 0.39894228040143267794f * __expf(-0.5f * s * s);
+  return cdf + s * pdf;
+}
+// compact form for the GEMM epilogue (the erf code stays out of line)
+__device__ __forceinline__ float fml_act_grad_small(int act, float s) {
+  if (act == FML_ACT_RELU) return s > 0.f ? 1.f : 0.f;
+  if (act == FML_ACT_SIGMOID) return s * (1.f - s);
+  if (act == FML_ACT_TANH) return 1.f - s * s;
+  if (act == FML_ACT_GELU) return fml_act_grad_gelu(s);
+  return 1.f;
+}
 __device__ __forceinline__ float fml_act_grad(int act, float s) {
   switch (act) {
     case FML_ACT_RELU: return s > 0.f ? 1.f : 0.f;

@@ -326,6 +326,8 @@ int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d) {
   FML_REQUIRE(ctx, d->ldb >= (d->transB ? d->K : d->N), "fml_gemm: ldb smaller than a row of B");
   FML_REQUIRE(ctx, d->ldc >= d->N, "fml_gemm: ldc smaller than N");
   FML_REQUIRE(ctx, d->act >= FML_ACT_NONE && d->act <= FML_ACT_GELU, "fml_gemm: unknown activation");
+  FML_REQUIRE(ctx, !d->dact_saved || (d->dact >= FML_ACT_NONE && d->dact <= FML_ACT_GELU), "fml_gemm: unknown dact");
+  FML_REQUIRE(ctx, !d->dact_saved || d->beta == 0.f, "fml_gemm: the gradient epilogue cannot accumulate (beta must be 0)");
   int prec = d->precision < 0 ? ctx->precision : d->precision;
   FML_REQUIRE(ctx, prec >= FML_PREC_TF32 && prec <= FML_PREC_FP32, "fml_gemm: unknown precision");
   if (prec != FML_PREC_FP32 && fml_gemm_tc_eligible(d)) return fml_gemm_tc(ctx, d, prec);

@@ -17,6 +17,7 @@ struct SimtParams {
   int nb1;
   long long sA1, sA2, sB1, sB2, sC1, sC2;
   int act; float alpha, beta;
+  const float* dact_saved; int dact;
 };
 
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
       float v = acc[i][j] * p.alpha + (p.bias ? p.bias[col] : 0.f);
       if (p.Z) p.Z[o] = v;
       v = fml_act_apply(p.act, v);
+      if (p.dact_saved) v *= fml_act_grad_small(p.dact, p.dact_saved[o]);
       if (p.beta != 0.f) v += p.C[o];
       p.C[o] = v;
     }
@@ -91,6 +93,7 @@ int32_t fml_gemm_simt(fml_ctx* ctx, const fml_gemm_desc* d) {
   p.nb1 = nb1;
   p.sA1 = d->sA1; p.sA2 = d->sA2; p.sB1 = d->sB1; p.sB2 = d->sB2; p.sC1 = d->sC1; p.sC2 = d->sC2;
   p.act = d->act; p.alpha = d->alpha; p.beta = d->beta;
+  p.dact_saved = d->dact_saved; p.dact = d->dact;
   FML_REQUIRE(ctx, (long long)nb1 * nb2 <= 65535, "fml_gemm: more than 65535 batches on the CUDA-core path");
   dim3 grid((d->N + TN - 1) / TN, (d->M + TM - 1) / TM, nb1 * nb2);
   FML_REQUIRE(ctx, grid.y <= 65535, "fml_gemm: M too large for the CUDA-core path");

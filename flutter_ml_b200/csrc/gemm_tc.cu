@@ -97,6 +97,8 @@ struct TcParams {
   float alpha, beta;
   int* status;
   uint32_t idesc;
+  const float* dact_saved;  // gradient epilogue: result *= act'(dact_saved) (same indexing as C)
+  int dact;
   int lstm;     // 1: LSTM gate epilogue (see fml_lstm_epilogue); C is not written
   fml_lstm_epilogue le;
   int debug;  // diagnostics only: 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
@@ -468,8 +470,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool vec_ok = ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                         ((p.sC1 & 3) == 0) && ((p.sC2 & 3) == 0) &&
                         (p.Z == nullptr || (reinterpret_cast<uintptr_t>(p.Z) & 15) == 0) &&
-                        (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
-    const bool plain = !p.bias && p.alpha == 1.f && p.act == FML_ACT_NONE && !p.Z && p.beta == 0.f && p.ksplit == 1;
+                        (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
+                        (p.dact_saved == nullptr || (reinterpret_cast<uintptr_t>(p.dact_saved) & 15) == 0);
+    const bool plain = !p.bias && p.alpha == 1.f && p.act == FML_ACT_NONE && !p.Z && p.beta == 0.f && p.ksplit == 1 && !p.dact_saved;
     for (int u = unit; u < num_units && ok; u += unit_stride) {
       int t, kb0, nkb, b, tm, tn;
       unit_range(u, t, kb0, nkb);
@@ -586,6 +589,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
               for (int j = 0; j < 32; j++) o[j] = fml_act_apply_slow(p.act, o[j]);
             }
+            if (p.dact_saved) {
+              // dLoss/dAct multiply of the layer below: this product is the gradient of that layer's output
+              const float4* sp = reinterpret_cast<const float4*>(p.dact_saved + boff + col0);
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const float4 sv = sp[j];
+                o[4 * j] *= fml_act_grad_small(p.dact, sv.x);
+                o[4 * j + 1] *= fml_act_grad_small(p.dact, sv.y);
+                o[4 * j + 2] *= fml_act_grad_small(p.dact, sv.z);
+                o[4 * j + 3] *= fml_act_grad_small(p.dact, sv.w);
+              }
+            }
             if (p.ksplit > 1) {
 #pragma unroll
               for (int j = 0; j < 8; j++)  // K split: partial products add up in C
@@ -609,6 +624,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 float o = __uint_as_float(v[j]) * p.alpha + (p.bias ? p.bias[col] : 0.f);
                 if (zrow) zrow[col] = o;
                 o = fml_act_apply(p.act, o);
+                if (p.dact_saved) o *= fml_act_grad_small(p.dact, p.dact_saved[boff + col]);
                 if (p.ksplit > 1) { atomicAdd(crow + col, o); continue; }
                 if (p.beta != 0.f) o += crow[col];
                 crow[col] = o;
@@ -853,6 +869,8 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   }
 
   TcParams p;
+  p.dact_saved = d->dact_saved;
+  p.dact = d->dact;
   p.lstm = lstm ? 1 : 0;
   if (lstm) {
     p.le = *lstm;
@@ -887,7 +905,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     // K split for plain TF32 products whose tiles occupy less than ~60 % of the SMs
     const long long tiles_all = (long long)tiles_m * tiles_n * nb1 * nb2;
     const long long ctas = tiles_all * (pair ? 2 : 1);
-    if (precision == FML_PREC_TF32 && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE && !lstm &&
+    if (precision == FML_PREC_TF32 && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE && !lstm && !d->dact_saved &&
         ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 8 && splitk_enabled()) {
       int want = (int)(ctx->sm_count / ctas);                 // CTAs available per tile
       int maxs = p.kblocks / 4;                               // at least 128 k per split

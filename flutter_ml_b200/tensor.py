@@ -45,6 +45,8 @@ class Node:
     def __init__(self, inputs, backwardFn, opName="", cost=0, extraParams=None):
         self.inputs, self.backwardFn, self.opName, self.cost = list(inputs), backwardFn, opName, cost
         self.extraParams = extraParams or {}
+        for i in self.inputs:  # consumer count: a tensor used once receives its whole gradient from one node
+            i._nuse = getattr(i, "_nuse", 0) + 1
 
 
 class Tensor:
@@ -180,12 +182,14 @@ def denseMatrix(x: Tensor, W: Tensor, b: Optional[Tensor], act=None, precision: 
     ctx.gemm(x.value, W.value, out.value, M, N, K, bias=b.value if b is not None else None, preact=z, act=code,
              precision=precision)
     saved = z if code == _lib.ACT_GELU else out.value
+    if code != _lib.ACT_NONE:
+        out._dact = (code, saved)  # lets the single consumer's dX product apply act'() in its epilogue
 
     def bw():
         if b is not None and b.grad is None:
             b.zeroGrad()
-        if code == _lib.ACT_NONE:
-            dz = out.grad
+        if code == _lib.ACT_NONE or getattr(out, "_grad_is_dz", False):
+            dz = out.grad  # already dLoss/dZ (no activation, or act' applied by the consumer's product)
             if b is not None:
                 ctx.call("fml_col_sum", dz, b.grad, M, N, 1)
         else:
@@ -193,7 +197,14 @@ def denseMatrix(x: Tensor, W: Tensor, b: Optional[Tensor], act=None, precision: 
             ctx.call("fml_act_bwd", code, saved, out.grad, dz, M, N, 0, b.grad if b is not None else None,
                      launches=2 if b is not None else 1)
         gx, acc_x = x._grad_target()
-        ctx.gemm(dz, W.value, gx, M, K, N, transB=True, beta=1.0 if acc_x else 0.0, precision=precision)
+        fuse = (not acc_x) and getattr(x, "_dact", None) is not None and getattr(x, "_nuse", 0) == 1
+        if fuse:
+            # x is the activated output of the dense layer below and nothing else consumes it: the product
+            # that forms dLoss/dx multiplies by act'() on the way out (tensor.dart:1030 / :552 / :598)
+            ctx.gemm(dz, W.value, gx, M, K, N, transB=True, precision=precision, dact_saved=x._dact[1], dact=x._dact[0])
+            x._grad_is_dz = True
+        else:
+            ctx.gemm(dz, W.value, gx, M, K, N, transB=True, beta=1.0 if acc_x else 0.0, precision=precision)
         gw, acc_w = W._grad_target()
         ctx.gemm(x.value, dz, gw, K, N, M, transA=True, beta=1.0 if acc_w else 0.0, precision=precision)
     out.creator = Node([x, W] + ([b] if b is not None else []), bw, "dense_matrix", 2 * M * K * N,

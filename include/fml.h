@@ -139,6 +139,13 @@ typedef struct {
   int32_t batch1, batch2;          /* >= 1 */
   int64_t sA1, sA2, sB1, sB2, sC1, sC2; /* element strides per batch level */
   int32_t precision; /* fml_precision or -1 */
+  /* Gradient epilogue: if dact_saved != NULL the result is multiplied elementwise by act'(dact_saved)
+   * before it is stored: the dLoss/dAct multiply of the layer BELOW, fused into the product that
+   * computes the gradient of its output (dX = dZ.W^T of tensor.dart:918-924 followed by
+   * tensor.dart:1030 / :552 / :598).  dact_saved is [M x N] at ldc with C's batch strides; it holds the
+   * pre-activation for RELU/GELU and the activation output for SIGMOID/TANH, as in fml_act_bwd. */
+  const float* dact_saved;
+  int32_t dact; /* fml_act of the layer below */
 } fml_gemm_desc;
 
 int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d);

@@ -316,3 +316,23 @@ def test_lstm_forward_backward(orc, prec, tol):
     assert rel(dW_.numpy().reshape(4, H, H + I), dW_ref) <= tol * 2
     assert rel(db_.numpy().reshape(4, H), db_ref) <= tol * 2
     c.close()
+
+
+@pytest.mark.parametrize("act", ["relu", "sigmoid", "tanh", "gelu"])
+@pytest.mark.parametrize("prec", [0, 2])
+def test_gemm_gradient_epilogue_equals_separate_kernel(ctx, act, prec):
+    """fml_gemm with dact_saved: (dZ.W^T) * act'(saved) in the epilogue equals the product followed by fml_act_bwd
+    (the dLoss/dAct multiply of tensor.dart:1030 / :552 / :598 applied to tensor.dart:918-924)."""
+    M, N, K = 200, 136, 96
+    rng = np.random.default_rng(21)
+    dZ = rng.standard_normal((M, K)).astype(np.float32)
+    W = rng.standard_normal((N, K)).astype(np.float32)
+    saved = rng.standard_normal((M, N)).astype(np.float32)
+    if act in ("sigmoid", "tanh"):
+        saved = np.tanh(saved).astype(np.float32) * (0.5 if act == "sigmoid" else 1.0) + (0.5 if act == "sigmoid" else 0.0)
+    d_dz, d_w, d_s = ctx.upload(dZ), ctx.upload(W), ctx.upload(saved)
+    fused, plain, ref = ctx.empty(M, N), ctx.empty(M, N), ctx.empty(M, N)
+    ctx.gemm(d_dz, d_w, fused, M, N, K, transB=True, precision=prec, dact_saved=d_s, dact=act)
+    ctx.gemm(d_dz, d_w, plain, M, N, K, transB=True, precision=prec)
+    ctx.call("fml_act_bwd", _act(act), d_s, plain, ref, M, N, 0, None)
+    assert rel(fused.numpy(), ref.numpy()) <= 2e-6
