@@ -38,7 +38,8 @@ class GemmDesc(C.Structure):
                 ("A", fp), ("B", fp), ("C", fp), ("bias", fp), ("preact", fp),
                 ("act", i32), ("alpha", f32), ("beta", f32), ("batch1", i32), ("batch2", i32),
                 ("sA1", i64), ("sA2", i64), ("sB1", i64), ("sB2", i64), ("sC1", i64), ("sC2", i64),
-                ("precision", i32), ("dact_saved", fp), ("dact", i32)]
+                ("precision", i32), ("dact_saved", fp), ("dact", i32),
+                ("rowop", i32), ("rowop_causal", i32), ("rowop_aux", fp)]
 
 
 class LstmDesc(C.Structure):
@@ -296,7 +297,7 @@ class Context:
     # ------------------------------------------------------------------ gemm
     def gemm(self, A, B, C_, M, N, K, transA=False, transB=False, lda=None, ldb=None, ldc=None, bias=None,
              preact=None, act=ACT_NONE, alpha=1.0, beta=0.0, batch=(1, 1), sA=(0, 0), sB=(0, 0), sC=(0, 0),
-             precision=-1, dact_saved=None, dact=ACT_NONE):
+             precision=-1, dact_saved=None, dact=ACT_NONE, rowop=0, rowop_causal=False, rowop_aux=None):
         d = GemmDesc()
         d.M, d.N, d.K = M, N, K
         d.transA, d.transB = int(transA), int(transB)
@@ -314,6 +315,7 @@ class Context:
         d.precision = precision
         d.dact_saved = _addr(dact_saved)
         d.dact = ACT_BY_NAME.get(dact, dact) if not isinstance(dact, int) else dact
+        d.rowop, d.rowop_causal, d.rowop_aux = int(rowop), int(bool(rowop_causal)), _addr(rowop_aux)
         self.check(self.lib.fml_gemm(self.h, C.byref(d)))
         self.launches += 3 if (precision == PREC_3XTF32 or (precision < 0 and self.precision == PREC_3XTF32)) else 1
 

@@ -328,6 +328,17 @@ int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d) {
   FML_REQUIRE(ctx, d->act >= FML_ACT_NONE && d->act <= FML_ACT_GELU, "fml_gemm: unknown activation");
   FML_REQUIRE(ctx, !d->dact_saved || (d->dact >= FML_ACT_NONE && d->dact <= FML_ACT_GELU), "fml_gemm: unknown dact");
   FML_REQUIRE(ctx, !d->dact_saved || d->beta == 0.f, "fml_gemm: the gradient epilogue cannot accumulate (beta must be 0)");
+  if (d->rowop) {
+    FML_REQUIRE(ctx, d->rowop == 1 || d->rowop == 2, "fml_gemm: unknown rowop");
+    FML_REQUIRE(ctx, d->N <= 512 && (d->N & 31) == 0, "fml_gemm: the row epilogue needs N <= 512 and N % 32 == 0");
+    FML_REQUIRE(ctx, !d->bias && !d->preact && d->act == FML_ACT_NONE && d->beta == 0.f && !d->dact_saved,
+                "fml_gemm: the row epilogue excludes bias, activation, pre-activation output, beta and dact");
+    FML_REQUIRE(ctx, d->rowop != 2 || d->rowop_aux, "fml_gemm: rowop 2 needs rowop_aux (the softmax output)");
+    FML_REQUIRE(ctx, (d->precision < 0 ? ctx->precision : d->precision) != FML_PREC_FP32 && fml_gemm_tc_eligible(d) &&
+                         (reinterpret_cast<uintptr_t>(d->C) & 15) == 0 && (d->ldc & 3) == 0 &&
+                         (!d->rowop_aux || (reinterpret_cast<uintptr_t>(d->rowop_aux) & 15) == 0),
+                "fml_gemm: the row epilogue exists on the tensor-core path only (aligned operands, not FML_PREC_FP32)");
+  }
   int prec = d->precision < 0 ? ctx->precision : d->precision;
   FML_REQUIRE(ctx, prec >= FML_PREC_TF32 && prec <= FML_PREC_FP32, "fml_gemm: unknown precision");
   if (prec != FML_PREC_FP32 && fml_gemm_tc_eligible(d)) return fml_gemm_tc(ctx, d, prec);

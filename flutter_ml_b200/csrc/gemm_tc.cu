@@ -99,6 +99,8 @@ struct TcParams {
   uint32_t idesc;
   const float* dact_saved;  // gradient epilogue: result *= act'(dact_saved) (same indexing as C)
   int dact;
+  int rowop, rowop_causal;  // row epilogue over complete rows (attention): 1 softmax, 2 softmax backward
+  const float* rowop_aux;
   int lstm;     // 1: LSTM gate epilogue (see fml_lstm_epilogue); C is not written
   fml_lstm_epilogue le;
   int debug;  // diagnostics only: 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
@@ -259,6 +261,11 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, int t, int& b, in
   const int per_batch = p.tiles_m * p.tiles_n;
   b = t / per_batch;
   int r = t - b * per_batch;
+  if (p.rowop) {  // the n-tiles of a row block are consecutive: they fill the two accumulators of one CTA
+    tm = r / p.tiles_n;
+    tn = r - tm * p.tiles_n;
+    return;
+  }
   const int GROUP = p.group_m;
   int group_sz = GROUP * p.tiles_n;
   int g = r / group_sz;
@@ -328,6 +335,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int num_tiles = p.tiles_m * p.tiles_n * p.nb1 * p.nb2;
   const int num_units = num_tiles * p.ksplit;  // work units: (tile, K split)
+  // i-th work unit of this CTA (pair).  With a row epilogue a CTA takes the tiles_n consecutive tiles of a row block.
+  auto nth_unit = [&](int i) {
+    if (p.rowop) return (unit + (i / p.tiles_n) * unit_stride) * p.tiles_n + i % p.tiles_n;
+    return unit + i * unit_stride;
+  };
   // unit -> tile index, first k-block and number of k-blocks of its K range
   auto unit_range = [&](int u, int& tile, int& kb0, int& nkb) {
     const int split = u / num_tiles;
@@ -352,7 +364,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int u = unit; u < num_units && ok; u += unit_stride) {
+      for (int it_u = 0; ok; it_u++) {
+        const int u = nth_unit(it_u);
+        if (u >= num_units) break;
         int t, kb0, nkb, b, tm, tn;
         unit_range(u, t, kb0, nkb);
         tile_coords(p, t, b, tm, tn);
@@ -417,7 +431,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t a_lbo = p.a_mn ? 4096u : 16u, b_lbo = p.b_mn ? 4096u : 16u;
       const uint32_t a_kstep = p.a_mn ? (1024u >> 4) : (32u >> 4);
       const uint32_t b_kstep = p.b_mn ? (1024u >> 4) : (32u >> 4);
-      for (int u = unit; u < num_units && ok; u += unit_stride) {
+      for (int it_u = 0; ok; it_u++) {
+       const int u = nth_unit(it_u);
+       if (u >= num_units) break;
        int t, kb0, nkb;
        unit_range(u, t, kb0, nkb);
        for (int kb_lo = kb0; kb_lo < kb0 + nkb && ok; kb_lo += p.kchunk) {
@@ -473,12 +489,136 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
                         (p.dact_saved == nullptr || (reinterpret_cast<uintptr_t>(p.dact_saved) & 15) == 0);
     const bool plain = !p.bias && p.alpha == 1.f && p.act == FML_ACT_NONE && !p.Z && p.beta == 0.f && p.ksplit == 1 && !p.dact_saved;
-    for (int u = unit; u < num_units && ok; u += unit_stride) {
+    for (int it_u = 0; ok; it_u++) {
+      const int u = nth_unit(it_u);
+      if (u >= num_units) break;
       int t, kb0, nkb, b, tm, tn;
       unit_range(u, t, kb0, nkb);
       tile_coords(p, t, b, tm, tn);
       const int b1 = b % p.nb1, b2 = b / p.nb1;
       const int m0 = tm * tile_m + (int)rank * BM, n0 = tn * p.BN;
+      if (p.rowop) {
+        // ---- row epilogue: the complete rows of this 128-row block sit in TMEM (one or both accumulators)
+        int accs[2];
+        for (int j = 0; j < p.tiles_n && ok; j++) {
+          accs[j] = acc;
+          ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, 4);
+          if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+        if (!ok) break;
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;                 // row of the [M x N] problem (= position in the sequence)
+        const int ncb = p.N >> 5;                           // 32-column blocks per row
+        const int lim = p.rowop_causal ? min(p.N, row + 1) : p.N;                 // valid columns of my row
+        const int lim_warp = p.rowop_causal ? min(p.N, m0 + q * 32 + 32) : p.N;   // ... of any row of this warp
+        const long long roff = (long long)b1 * p.sC1 + (long long)b2 * p.sC2 + (long long)row * p.ldc;
+        // partner exchange area in the unused tail of the operand ring (4 stages of 48 KiB leave 32 KiB)
+        float* xch = reinterpret_cast<float*>(smem_gen + 4 * 49152) + ((q * 2 + half) * 32 + lane) * 2;
+        float* xch_other = reinterpret_cast<float*>(smem_gen + 4 * 49152) + ((q * 2 + (half ^ 1)) * 32 + lane) * 2;
+        auto tcol = [&](int cb) { return tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)accs[cb >> 3] * 256u + (uint32_t)(cb & 7) * 32u; };
+        uint32_t v[32];
+        if (p.rowop == 1) {
+          const float k2 = p.alpha * 1.4426950408889634f;   // base-2 exponentials
+          float mx = -INFINITY, sum = 0.f;
+          for (int cb = half; cb < ncb; cb += 2) {
+            if (cb * 32 >= lim_warp) break;  // warp-uniform: nothing valid from here on
+            tmem_ld32(tcol(cb), v);
+            tmem_ld_wait();
+            float cm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+              const float x = (cb * 32 + j < lim) ? __uint_as_float(v[j]) * k2 : -INFINITY;
+              v[j] = __float_as_uint(x);
+              cm = fmaxf(cm, x);
+            }
+            if (cm > mx) { sum *= exp2f(mx - cm); mx = cm; }
+            if (mx != -INFINITY) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) sum += exp2f(__uint_as_float(v[j]) - mx);
+            }
+          }
+          xch[0] = mx; xch[1] = sum;
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+          const float om = xch_other[0], os = xch_other[1];
+          const float M2 = fmaxf(mx, om);   // finite: column 0 is valid for every row and belongs to one of the two
+          const float S2 = (mx == -INFINITY ? 0.f : sum * exp2f(mx - M2)) + (om == -INFINITY ? 0.f : os * exp2f(om - M2));
+          const float inv = 1.f / S2;
+          for (int cb = half; cb < ncb; cb += 2) {
+            float4* dst = reinterpret_cast<float4*>(p.C + roff + cb * 32);
+            if (cb * 32 >= lim_warp) {
+              if (row < p.M) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) dst[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+              continue;
+            }
+            tmem_ld32(tcol(cb), v);
+            tmem_ld_wait();
+            if (row < p.M) {
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                float4 o;
+                o.x = (cb * 32 + 4 * j + 0 < lim) ? exp2f(__uint_as_float(v[4 * j + 0]) * k2 - M2) * inv : 0.f;
+                o.y = (cb * 32 + 4 * j + 1 < lim) ? exp2f(__uint_as_float(v[4 * j + 1]) * k2 - M2) * inv : 0.f;
+                o.z = (cb * 32 + 4 * j + 2 < lim) ? exp2f(__uint_as_float(v[4 * j + 2]) * k2 - M2) * inv : 0.f;
+                o.w = (cb * 32 + 4 * j + 3 < lim) ? exp2f(__uint_as_float(v[4 * j + 3]) * k2 - M2) * inv : 0.f;
+                dst[j] = o;
+              }
+            }
+          }
+        } else {
+          // dS = alpha * P * (dP - sum_j dP_j P_j); masked P entries are exactly 0
+          float dot = 0.f;
+          for (int cb = half; cb < ncb; cb += 2) {
+            if (cb * 32 >= lim_warp) break;
+            tmem_ld32(tcol(cb), v);
+            tmem_ld_wait();
+            if (row < p.M) {
+              const float4* pp = reinterpret_cast<const float4*>(p.rowop_aux + roff + cb * 32);
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const float4 pv = pp[j];
+                dot += __uint_as_float(v[4 * j]) * pv.x + __uint_as_float(v[4 * j + 1]) * pv.y +
+                       __uint_as_float(v[4 * j + 2]) * pv.z + __uint_as_float(v[4 * j + 3]) * pv.w;
+              }
+            }
+          }
+          xch[0] = dot;
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+          dot += xch_other[0];
+          for (int cb = half; cb < ncb; cb += 2) {
+            float4* dst = reinterpret_cast<float4*>(p.C + roff + cb * 32);
+            if (cb * 32 >= lim_warp) {
+              if (row < p.M) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) dst[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+              continue;
+            }
+            tmem_ld32(tcol(cb), v);
+            tmem_ld_wait();
+            if (row < p.M) {
+              const float4* pp = reinterpret_cast<const float4*>(p.rowop_aux + roff + cb * 32);
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                const float4 pv = pp[j];
+                dst[j] = make_float4(p.alpha * pv.x * (__uint_as_float(v[4 * j]) - dot),
+                                     p.alpha * pv.y * (__uint_as_float(v[4 * j + 1]) - dot),
+                                     p.alpha * pv.z * (__uint_as_float(v[4 * j + 2]) - dot),
+                                     p.alpha * pv.w * (__uint_as_float(v[4 * j + 3]) - dot));
+              }
+            }
+          }
+        }
+        // the exchange slots are rewritten only after the partner has read them
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          for (int j = 0; j < p.tiles_n; j++) mbar_arrive(tempty_bar(accs[j]));
+        it_u += p.tiles_n - 1;  // the unit's remaining n-tiles were consumed here
+        continue;
+      }
       const int nchunks = (nkb + p.kchunk - 1) / p.kchunk;
      for (int chunk = 0; chunk < nchunks && ok; chunk++) {
       ok = mbar_wait(tfull_bar(acc), acc_ph, abort_flag, p.status, 4);
@@ -794,24 +934,25 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   // machine; FML_GEMM_PAIR=0/1 forces the choice (diagnostics)
   bool pair = d->M > 128 && d->N > 128 &&
               (long long)((d->M + 255) / 256) * ((d->N + 255) / 256) * nb1 * nb2 >= ctx->sm_count / 4;
+  if (d->rowop) pair = false;  // a row block (128 rows x up to 512 columns) lives in ONE CTA's tensor memory
   {
     static int force = -2;
     if (force == -2) {
       const char* e = getenv("FML_GEMM_PAIR");
       force = e ? atoi(e) : -1;
     }
-    if (force >= 0) pair = force != 0;
+    if (force >= 0 && !d->rowop) pair = force != 0;
   }
   const int tile_m = pair ? 2 * BM : BM;
   const int tiles_m = (d->M + tile_m - 1) / tile_m;
   // widest tile that still gives every SM work
   int BN = 64;
-  if (pair) BN = 256;
+  if (pair || d->rowop) BN = 256;
   else for (int bn : {256, 128, 64}) {
     long long tiles = (long long)tiles_m * ((d->N + bn - 1) / bn) * nb1 * nb2;
     if (d->N > bn / 2 && tiles >= ctx->sm_count) { BN = bn; break; }
   }
-  if (BN == 64 && !pair) {
+  if (BN == 64 && !pair && !d->rowop) {
     // small problem: nothing fills the machine; prefer the tile that wastes least of N
     BN = d->N > 128 ? (d->N > 192 ? 256 : 128) : (d->N > 64 ? 128 : 64);
     long long t256 = (long long)tiles_m * ((d->N + 255) / 256) * nb1 * nb2;
@@ -869,6 +1010,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   }
 
   TcParams p;
+  p.rowop = d->rowop; p.rowop_causal = d->rowop_causal; p.rowop_aux = d->rowop_aux;
   p.dact_saved = d->dact_saved;
   p.dact = d->dact;
   p.lstm = lstm ? 1 : 0;
@@ -897,7 +1039,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   p.nstages = std::min((int)Cfg<false>::MAX_STAGES, (int)Cfg<false>::RING_BYTES / p.stage_bytes);
   p.kblocks = (d->K + BK - 1) / BK;
   p.kchunk = (precision == FML_PREC_3XTF32 ? 1024 : 8192) / BK;
-  if (p.kblocks <= p.kchunk + p.kchunk / 4) p.kchunk = p.kblocks;  // not worth a second chunk for a short tail
+  if (p.kblocks <= p.kchunk + p.kchunk / 4 || d->rowop) p.kchunk = p.kblocks;  // not worth a second chunk for a short tail
   p.partial = nullptr;
   p.ksplit = 1;
   p.kb_per_split = p.kblocks;
@@ -905,7 +1047,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     // K split for plain TF32 products whose tiles occupy less than ~60 % of the SMs
     const long long tiles_all = (long long)tiles_m * tiles_n * nb1 * nb2;
     const long long ctas = tiles_all * (pair ? 2 : 1);
-    if (precision == FML_PREC_TF32 && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE && !lstm && !d->dact_saved &&
+    if (precision == FML_PREC_TF32 && !d->rowop && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE && !lstm && !d->dact_saved &&
         ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 8 && splitk_enabled()) {
       int want = (int)(ctx->sm_count / ctas);                 // CTAs available per tile
       int maxs = p.kblocks / 4;                               // at least 128 k per split
@@ -958,7 +1100,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     cfg.numAttrs = 1;
     FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, p));
   } else {
-    const int grid = (int)std::min<long long>(num_tiles, ctx->sm_count);
+    const int grid = (int)std::min<long long>(d->rowop ? num_tiles / tiles_n : num_tiles, ctx->sm_count);
     gemm_tc_kernel<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, p);
   }
   FML_LAUNCH_CHECK(ctx, "gemm_tc_kernel");

@@ -23,6 +23,13 @@ from ._lib import ACT_BY_NAME, Context, DeviceArray
 
 _default_ctx: Optional[Context] = None
 
+# Epilogue fusions that need global LOADS inside the GEMM epilogue are implemented and tested but off by default:
+# the epilogue warps are latency-bound and each of their loads is fully exposed (measured on B200: the dX product
+# with the act'() multiply 386 us against 223 us + 132 us for product + separate kernel, but then one more
+# column-sum pass for the bias gradient; softmax-backward epilogue 670 us against 263 + 237 us).
+FUSE_DACT_INTO_DX = False
+FUSE_SOFTMAX_BACKWARD = False
+
 
 def default_context() -> Context:
     """The process-wide context (device 0 unless set_default_context was called)."""
@@ -197,7 +204,7 @@ def denseMatrix(x: Tensor, W: Tensor, b: Optional[Tensor], act=None, precision: 
             ctx.call("fml_act_bwd", code, saved, out.grad, dz, M, N, 0, b.grad if b is not None else None,
                      launches=2 if b is not None else 1)
         gx, acc_x = x._grad_target()
-        fuse = (not acc_x) and getattr(x, "_dact", None) is not None and getattr(x, "_nuse", 0) == 1
+        fuse = FUSE_DACT_INTO_DX and (not acc_x) and getattr(x, "_dact", None) is not None and getattr(x, "_nuse", 0) == 1
         if fuse:
             # x is the activated output of the dense layer below and nothing else consumes it: the product
             # that forms dLoss/dx multiplies by act'() on the way out (tensor.dart:1030 / :552 / :598)
@@ -379,8 +386,16 @@ def attentionCore(qkv: Tensor, n_seq: int, seq_len: int, heads: int, d_head: int
     out = Tensor(ctx.empty(Bn * S, d), ctx)
     bat = dict(batch=(H, Bn), precision=precision)
     s_qkv, s_p, s_o = (dk, S * ld), (S * S, H * S * S), (dk, S * d)
-    ctx.gemm(q, k, P, S, S, dk, transB=True, lda=ld, ldb=ld, ldc=S, sA=s_qkv, sB=s_qkv, sC=s_p, **bat)
-    ctx.call("fml_softmax_rows_fwd", P, P, Bn * H * S, S, scale, S if causal else 0)
+    eff_prec = ctx.precision if precision < 0 else precision
+    # scores of up to 512 keys fit one CTA's tensor memory: scale, mask and softmax run in the epilogue of the
+    # Q.K^T product (and the softmax backward in the epilogue of dO.V^T), so S never makes a round trip
+    fused_rows = S <= 512 and S % 32 == 0 and eff_prec != _lib.PREC_FP32
+    if fused_rows:
+        ctx.gemm(q, k, P, S, S, dk, transB=True, lda=ld, ldb=ld, ldc=S, sA=s_qkv, sB=s_qkv, sC=s_p, alpha=scale,
+                 rowop=1, rowop_causal=causal, **bat)
+    else:
+        ctx.gemm(q, k, P, S, S, dk, transB=True, lda=ld, ldb=ld, ldc=S, sA=s_qkv, sB=s_qkv, sC=s_p, **bat)
+        ctx.call("fml_softmax_rows_fwd", P, P, Bn * H * S, S, scale, S if causal else 0)
     ctx.gemm(P, v, out.value, S, dk, S, lda=S, ldb=ld, ldc=d, sA=s_p, sB=s_qkv, sC=s_o, **bat)
 
     def bw():
@@ -392,10 +407,18 @@ def attentionCore(qkv: Tensor, n_seq: int, seq_len: int, heads: int, d_head: int
         dO = out.grad
         dP = ctx.empty(Bn * H * S, S)
         # dP = dO_h . V_h^T ; dV_h = P^T . dO_h
-        ctx.gemm(dO, v, dP, S, S, dk, transB=True, lda=d, ldb=ld, ldc=S, sA=s_o, sB=s_qkv, sC=s_p, **bat)
+        # The backward row epilogue (rowop 2) exists and is tested, but re-reading P from the epilogue warps made
+        # it slower than the separate kernels (670 us against 263 + 237 us per layer at 16 heads x 32 x 512^2).
+        if fused_rows and FUSE_SOFTMAX_BACKWARD:
+            # dS = scale * P * (dP - sum(dP*P)) straight out of the product's epilogue
+            ctx.gemm(dO, v, dP, S, S, dk, transB=True, lda=d, ldb=ld, ldc=S, sA=s_o, sB=s_qkv, sC=s_p, alpha=scale,
+                     rowop=2, rowop_aux=P, **bat)
+        else:
+            ctx.gemm(dO, v, dP, S, S, dk, transB=True, lda=d, ldb=ld, ldc=S, sA=s_o, sB=s_qkv, sC=s_p, **bat)
         ctx.gemm(P, dO, gv, S, dk, S, transA=True, lda=S, ldb=d, ldc=ld, sA=s_p, sB=s_o, sC=s_qkv, beta=beta, **bat)
-        # dS = scale * P * (dP - sum(dP*P)), in place over dP
-        ctx.call("fml_softmax_rows_bwd", P, dP, dP, Bn * H * S, S, scale, 0)
+        if not (fused_rows and FUSE_SOFTMAX_BACKWARD):
+            # dS = scale * P * (dP - sum(dP*P)), in place over dP
+            ctx.call("fml_softmax_rows_bwd", P, dP, dP, Bn * H * S, S, scale, 0)
         # dQ_h = dS . K_h ; dK_h = dS^T . Q_h
         ctx.gemm(dP, k, gq, S, dk, S, lda=S, ldb=ld, ldc=ld, sA=s_p, sB=s_qkv, sC=s_qkv, beta=beta, **bat)
         ctx.gemm(dP, q, gk, S, dk, S, transA=True, lda=S, ldb=ld, ldc=ld, sA=s_p, sB=s_qkv, sC=s_qkv, beta=beta, **bat)

@@ -146,6 +146,15 @@ typedef struct {
    * pre-activation for RELU/GELU and the activation output for SIGMOID/TANH, as in fml_act_bwd. */
   const float* dact_saved;
   int32_t dact; /* fml_act of the layer below */
+  /* Row epilogue for attention scores (N <= 512, N a multiple of 32; no bias/act/preact/beta):
+   *   rowop = 1: C = row softmax of alpha * (A.B), columns j > row masked when rowop_causal != 0
+   *              (matMul + scaleMatrix + softmaxMatrix of singleHeadAttentionLayer.dart:77-81 in one kernel);
+   *   rowop = 2: C = alpha * P * ((A.B) - rowsum((A.B) * P)) with P = rowop_aux laid out like C
+   *              (the softmax backward of softmax.dart:98-112 applied to the product dP = dO.V^T).
+   * The whole row of a 128-row block stays in tensor memory, so the scores never make a round trip. */
+  int32_t rowop;
+  int32_t rowop_causal;
+  const float* rowop_aux;
 } fml_gemm_desc;
 
 int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d);

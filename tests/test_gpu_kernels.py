@@ -336,3 +336,36 @@ def test_gemm_gradient_epilogue_equals_separate_kernel(ctx, act, prec):
     ctx.gemm(d_dz, d_w, plain, M, N, K, transB=True, precision=prec)
     ctx.call("fml_act_bwd", _act(act), d_s, plain, ref, M, N, 0, None)
     assert rel(fused.numpy(), ref.numpy()) <= 2e-6
+
+
+@pytest.mark.parametrize("S,causal", [(64, True), (96, False), (256, True), (512, True), (512, False), (320, True)])
+@pytest.mark.parametrize("prec,tol", [(0, TOL_TF32), (1, 2e-5)])
+def test_attention_scores_with_row_epilogue(ctx, orc, S, causal, prec, tol):
+    """fml_gemm rowop 1/2: Q.K^T with scale + causal mask + softmax in the epilogue, and dO.V^T with the softmax
+    backward in the epilogue, against the oracle's matMul / scaleMatrix / softmaxMatrix chain
+    (singleHeadAttentionLayer.dart:77-81, softmax.dart:68-115)."""
+    Bn, H, dk = 2, 3, 64
+    rng = np.random.default_rng(S + 7 * causal)
+    Q, Kx = rng.standard_normal((Bn, H, S, dk)).astype(np.float32), rng.standard_normal((Bn, H, S, dk)).astype(np.float32)
+    dPh = rng.standard_normal((Bn, H, S, dk)).astype(np.float32)  # plays dO; V below
+    V = rng.standard_normal((Bn, H, S, dk)).astype(np.float32)
+    scale = 0.125
+    dq, dkk, ddo, dv = ctx.upload(Q), ctx.upload(Kx), ctx.upload(dPh), ctx.upload(V)
+    P, dS = ctx.empty(Bn, H, S, S), ctx.empty(Bn, H, S, S)
+    kw = dict(batch=(H, Bn), sA=(S * dk, H * S * dk), sB=(S * dk, H * S * dk), sC=(S * S, H * S * S), precision=prec)
+    ctx.gemm(dq, dkk, P, S, S, dk, transB=True, alpha=scale, rowop=1, rowop_causal=causal, **kw)
+    ctx.gemm(ddo, dv, dS, S, S, dk, transB=True, alpha=scale, rowop=2, rowop_aux=P, **kw)
+    ops = orc.Ops(omp=True)
+    Ph, dSh = P.numpy(), dS.numpy()
+    for b in range(Bn):
+        for h in range(H):
+            s_ref = ops.matmul_fwd(w64(Q[b, h]), w64(Kx[b, h].T.copy())) * scale
+            p_ref = ops.softmax_fwd(s_ref, S if causal else 0)
+            assert rel(Ph[b, h], p_ref) <= 2 * tol  # softmax scales the error of the scores by their magnitude
+            if causal:
+                assert np.all(np.triu(Ph[b, h], 1) == 0.0)
+            # backward on the GPU's own P (one product per tolerance)
+            dp_ref = ops.matmul_fwd(w64(dPh[b, h]), w64(V[b, h].T.copy()))
+            ds_ref = np.zeros((S, S))
+            ops.softmax_bwd(w64(Ph[b, h]), dp_ref, ds_ref)
+            assert rel(dSh[b, h], ds_ref * scale) <= 2 * tol

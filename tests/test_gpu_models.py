@@ -148,3 +148,24 @@ def test_pipelined_host_step_equals_serial():
         assert np.allclose(out[k], ref[k], rtol=1e-5, atol=1e-6), k
     assert ctx.device_status() == 0
     ctx.close()
+
+
+def test_optional_epilogue_fusions_give_the_same_gradients(orc):
+    """tensor.FUSE_DACT_INTO_DX / FUSE_SOFTMAX_BACKWARD (off by default because they measured slower) against the
+    default path, on the encoder block."""
+    from flutter_ml_b200 import _lib, models, synth
+    from flutter_ml_b200 import tensor as T
+    ctx = _lib.Context(precision=_lib.PREC_3XTF32)
+    d, heads, dff, S, B = 128, 4, 256, 64, 2
+    p = models.init_block(2, d, heads, dff, std=0.08)
+    x, tgt = synth.normal(2, 500, (B, S, d)), synth.normal(2, 501, (B, S, d))
+    base = models.encoder_block_fwd_bwd(ctx, x, p, tgt, heads, True)
+    T.FUSE_DACT_INTO_DX = T.FUSE_SOFTMAX_BACKWARD = True
+    try:
+        fused = models.encoder_block_fwd_bwd(ctx, x, p, tgt, heads, True)
+    finally:
+        T.FUSE_DACT_INTO_DX = T.FUSE_SOFTMAX_BACKWARD = False
+    assert rel(fused[2], base[2]) <= 2e-5
+    for g, r in zip(fused[3], base[3]):
+        assert rel(g, r) <= 2e-5
+    ctx.close()
