@@ -61,6 +61,7 @@ PROTOTYPES = {
     "fml_alloc": [fp, i64, C.POINTER(fp)],
     "fml_free": [fp, fp],
     "fml_zero": [fp, fp, i64],
+    "fml_fill": [fp, fp, i64, f32],
     "fml_upload_f32": [fp, fp, fp, i64],
     "fml_upload_f64": [fp, fp, fp, i64],
     "fml_upload_i32": [fp, fp, fp, i64],
@@ -76,6 +77,10 @@ PROTOTYPES = {
     "fml_lane_sync": [fp, i32],
     "fml_event_record_on": [fp, i32, i32],
     "fml_wait_event": [fp, i32, i32],
+    "fml_graph_begin": [fp],
+    "fml_graph_end": [fp, C.POINTER(i32)],
+    "fml_graph_launch": [fp, i32],
+    "fml_graph_destroy": [fp, i32],
     "fml_timer_start": [fp],
     "fml_timer_stop_ms": [fp, C.POINTER(f32)],
     "fml_gemm": [fp, C.POINTER(GemmDesc)],
@@ -266,6 +271,18 @@ class Context:
         ms = f32(0)
         self.check(self.lib.fml_timer_stop_ms(self.h, C.byref(ms)))
         return ms.value
+
+    def graph_begin(self):
+        self.check(self.lib.fml_graph_begin(self.h))
+
+    def graph_end(self):
+        gid = i32(-1)
+        self.check(self.lib.fml_graph_end(self.h, C.byref(gid)))
+        return gid.value
+
+    def graph_launch(self, gid, launches=0):
+        self.check(self.lib.fml_graph_launch(self.h, gid))
+        self.launches += launches
 
     def event_record(self, slot):
         self.check(self.lib.fml_event_record(self.h, slot))

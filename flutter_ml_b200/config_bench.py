@@ -30,8 +30,13 @@ def config1_mlp(ctx):
     X, labels = ctx.upload(synth.uniform(0, 0, (64, 784))), ctx.upload(synth.integers(0, 1, (64,), 10))
     ms, launches = _timed(ctx, lambda: mlp.train_step(X, labels), warm=5, reps=50)
     flops = 41926656.0
-    return {"config": "C1 MLP 784-128-64-10 batch 64 fwd+bwd+SGD", "us_per_step": round(ms * 1e3, 1),
-            "samples_per_s": round(64 / ms * 1e3, 1), "gflops": round(flops / ms / 1e6, 1), "launches_per_step": launches}
+    out = {"config": "C1 MLP 784-128-64-10 batch 64 fwd+bwd+SGD", "us_per_step": round(ms * 1e3, 1),
+           "samples_per_s": round(64 / ms * 1e3, 1), "gflops": round(flops / ms / 1e6, 1), "launches_per_step": launches}
+    # the same step recorded once as a CUDA graph and replayed (one call per step instead of ~15)
+    mlp.record_step(X, labels)
+    gms, _ = _timed(ctx, mlp.replay_step, warm=5, reps=200)
+    out.update({"graph_us_per_step": round(gms * 1e3, 1), "graph_samples_per_s": round(64 / gms * 1e3, 1)})
+    return out
 
 
 def config3_encoder_block(ctx):

@@ -28,6 +28,8 @@ struct fml_ctx {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   cudaEvent_t ev_pool[64] = {};
   cudaStream_t lanes[2] = {nullptr, nullptr};  // copy streams, created on first use
+  std::vector<cudaGraphExec_t> graphs;         // instantiated graphs, index = graph id
+  bool capturing = false;
   int last_gemm_path = 0;
   // tensor-map cache: key -> encoded CUtensorMap
   std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int>, CUtensorMap> tmaps;

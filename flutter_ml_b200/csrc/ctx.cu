@@ -20,6 +20,8 @@ int32_t fml_fail(fml_ctx* ctx, int32_t code, const std::string& msg) {
 
 int32_t fml_ensure_workspace(fml_ctx* ctx, size_t bytes) {
   if (bytes <= ctx->ws_bytes) return FML_OK;
+  if (ctx->capturing)
+    return fml_fail(ctx, FML_ERR_INVALID, "the scratch arena would have to grow while a graph is being recorded; run the sequence once eagerly first");
   if (ctx->ws) {
     FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     cudaFree(ctx->ws);
@@ -120,6 +122,8 @@ int32_t fml_shutdown(fml_ctx* ctx) {
   cudaEventDestroy(ctx->ev1);
   for (cudaEvent_t e : ctx->ev_pool)
     if (e) cudaEventDestroy(e);
+  for (cudaGraphExec_t ge : ctx->graphs)
+    if (ge) cudaGraphExecDestroy(ge);
   for (cudaStream_t l : ctx->lanes)
     if (l) { cudaStreamSynchronize(l); cudaStreamDestroy(l); }
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
@@ -304,6 +308,37 @@ int32_t fml_lane_sync(fml_ctx* ctx, int32_t lane) {
   int32_t rc = lane_stream(ctx, lane, &s);
   if (rc) return rc;
   FML_CUDA(ctx, cudaStreamSynchronize(s));
+  return FML_OK;
+}
+
+int32_t fml_graph_begin(fml_ctx* ctx) {
+  FML_REQUIRE(ctx, !ctx->capturing, "fml_graph_begin: a recording is already in progress");
+  FML_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+  ctx->capturing = true;
+  return FML_OK;
+}
+int32_t fml_graph_end(fml_ctx* ctx, int32_t* graph_id) {
+  FML_REQUIRE(ctx, ctx->capturing && graph_id, "fml_graph_end: no recording in progress");
+  ctx->capturing = false;
+  cudaGraph_t g = nullptr;
+  FML_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &g));
+  cudaGraphExec_t ge = nullptr;
+  cudaError_t e = cudaGraphInstantiate(&ge, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+  ctx->graphs.push_back(ge);
+  *graph_id = (int32_t)ctx->graphs.size() - 1;
+  return FML_OK;
+}
+int32_t fml_graph_launch(fml_ctx* ctx, int32_t id) {
+  FML_REQUIRE(ctx, id >= 0 && id < (int32_t)ctx->graphs.size() && ctx->graphs[id], "fml_graph_launch: unknown graph");
+  FML_CUDA(ctx, cudaGraphLaunch(ctx->graphs[id], ctx->stream));
+  return FML_OK;
+}
+int32_t fml_graph_destroy(fml_ctx* ctx, int32_t id) {
+  FML_REQUIRE(ctx, id >= 0 && id < (int32_t)ctx->graphs.size() && ctx->graphs[id], "fml_graph_destroy: unknown graph");
+  FML_CUDA(ctx, cudaGraphExecDestroy(ctx->graphs[id]));
+  ctx->graphs[id] = nullptr;
   return FML_OK;
 }
 

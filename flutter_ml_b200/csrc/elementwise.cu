@@ -122,6 +122,10 @@ __global__ void binary_kernel(int mode, float s, const float* a, const float* b,
   }
 }
 
+__global__ void fill_kernel(float* __restrict__ p, long long n, float value) {
+  EW_LOOP(i, n) p[i] = value;
+}
+
 __global__ void add_bias_kernel(const float* __restrict__ x, const float* __restrict__ b, float* __restrict__ y,
                                 long long rows, long long cols) {
   EW_LOOP(i, rows * cols) y[i] = x[i] + b[i % cols];
@@ -261,6 +265,14 @@ int32_t launch_vec(fml_ctx* ctx, const char* name, bool vec, long long n, K kvec
 }  // namespace
 
 extern "C" {
+
+int32_t fml_fill(fml_ctx* ctx, float* p, int64_t n, float value) {
+  FML_REQUIRE(ctx, p && n >= 0, "fml_fill: bad arguments");
+  if (n == 0) return FML_OK;
+  fill_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(p, n, value);
+  FML_LAUNCH_CHECK(ctx, "fill_kernel");
+  return FML_OK;
+}
 
 int32_t fml_act_fwd(fml_ctx* ctx, int32_t act, const float* x, float* y, int64_t n) {
   FML_REQUIRE(ctx, x && y && n >= 0, "fml_act_fwd: bad arguments");

@@ -67,6 +67,31 @@ class MLP:
         return loss, logits_copy, grads
 
 
+    def record_step(self, X, labels):
+        """Record one training step on (X, labels) as a CUDA graph.  The step is launch-bound (~15 kernels of a few
+        microseconds each); replaying the graph issues them with one call.  X and labels are read from the
+        same device buffers at every replay (refill them in place); the loss lands in `self.loss`."""
+        import gc
+        ctx = self.ctx
+        self.train_step(X, labels)          # eager once: sizes the scratch arena, fills the tensor-map cache
+        self.loss = ctx.zeros(1)
+        gc.collect()
+        n0 = ctx.launches
+        ctx.graph_begin()
+        try:
+            loss, _, _ = self.train_step(X, labels)
+            ctx.copy(self.loss, loss.value)
+            del loss
+            gc.collect()                    # every buffer allocated while recording is freed while recording
+        finally:
+            self._graph = ctx.graph_end()
+        self._graph_launches = ctx.launches - n0
+        return self._graph
+
+    def replay_step(self):
+        self.ctx.graph_launch(self._graph, launches=self._graph_launches)
+
+
 # ----------------------------------------------------------------------------------- config 3
 def init_block(seed: int, d_model: int, heads: int, dff: int, std: float = 0.02, tid: int = 0) -> Dict:
     """Encoder-block weights N(0, std), LayerNorm gamma 1 / beta 0, biases 0."""

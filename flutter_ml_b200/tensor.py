@@ -127,8 +127,9 @@ class Tensor:
                 for i in reversed(t.creator.inputs):
                     if id(i) not in seen:
                         stack.append((i, False))
-        if self.grad is None:
-            self.grad = self.ctx.upload(np.ones(self.value.shape, dtype=np.float32))
+        if self.grad is None:  # seed gradient 1 (tensor.dart:70), filled on the device: no host copy, no sync
+            self.grad = self.ctx.empty(*self.value.shape)
+            self.ctx.call("fml_fill", self.grad, self.grad.size, 1.0)
         # `before`: {id(tensor): callable} run just before that tensor's creator, i.e. once every consumer
         # of the tensor has contributed its gradient (used to start exchanging finished gradient slices)
         for t in reversed(topo):

@@ -80,6 +80,7 @@ int32_t fml_device_status(fml_ctx* ctx, int32_t* code);
 int32_t fml_alloc(fml_ctx* ctx, int64_t n_floats, float** out);
 int32_t fml_free(fml_ctx* ctx, float* p);
 int32_t fml_zero(fml_ctx* ctx, float* p, int64_t n_floats);
+int32_t fml_fill(fml_ctx* ctx, float* p, int64_t n_floats, float value);
 int32_t fml_upload_f32(fml_ctx* ctx, float* dst, const float* host, int64_t n);
 int32_t fml_upload_f64(fml_ctx* ctx, float* dst, const double* host, int64_t n);
 int32_t fml_upload_i32(fml_ctx* ctx, int32_t* dst, const int32_t* host, int64_t n);
@@ -101,6 +102,18 @@ int32_t fml_lane_d2h(fml_ctx* ctx, int32_t lane, float* host, const float* src, 
 int32_t fml_lane_sync(fml_ctx* ctx, int32_t lane);
 int32_t fml_event_record_on(fml_ctx* ctx, int32_t slot, int32_t lane);
 int32_t fml_wait_event(fml_ctx* ctx, int32_t lane, int32_t slot);
+
+/* ---- CUDA graphs --------------------------------------------------------------
+ * Launch-bound sequences (the 64-row MLP step of lib/nets/snet.dart:74-85 is ~15 small kernels) can be
+ * recorded once and replayed with one launch.  Everything the library enqueues on the context's stream
+ * between begin and end, including fml_alloc/fml_free pairs, becomes part of the graph; buffers that must
+ * outlive the recording have to be allocated before it starts, every buffer allocated inside has to be freed
+ * inside, and anything that would grow the scratch arena must have run once before (run the sequence
+ * eagerly first).  Host reads (fml_download_*, fml_sync) are not allowed while recording. */
+int32_t fml_graph_begin(fml_ctx* ctx);
+int32_t fml_graph_end(fml_ctx* ctx, int32_t* graph_id);
+int32_t fml_graph_launch(fml_ctx* ctx, int32_t graph_id);
+int32_t fml_graph_destroy(fml_ctx* ctx, int32_t graph_id);
 
 /* ---- timing (CUDA events on the context's stream) ------------------------- */
 int32_t fml_timer_start(fml_ctx* ctx);

@@ -169,3 +169,22 @@ def test_optional_epilogue_fusions_give_the_same_gradients(orc):
     for g, r in zip(fused[3], base[3]):
         assert rel(g, r) <= 2e-5
     ctx.close()
+
+
+def test_mlp_step_recorded_as_cuda_graph_matches_eager_steps():
+    """fml_graph_*: N replays of the recorded MLP training step leave the parameters where N eager steps do."""
+    from flutter_ml_b200 import _lib, models, synth
+    ctx = _lib.Context()
+    params = models.init_mlp(0)
+    X, labels = ctx.upload(synth.uniform(0, 0, (64, 784))), ctx.upload(synth.integers(0, 1, (64,), 10))
+    eager, graph = models.MLP(ctx, params, lr=0.01), models.MLP(ctx, params, lr=0.01)
+    graph.record_step(X, labels)            # runs one eager step and one recorded (not executed) step
+    for _ in range(4):
+        graph.replay_step()
+    for _ in range(5):
+        loss, _, _ = eager.train_step(X, labels)
+    a, b = graph.arena.values.numpy(), eager.arena.values.numpy()
+    assert rel(a, b) <= 1e-6                # split-K / bias sums use atomics: last-bit differences only
+    assert abs(graph.loss.numpy()[0] - loss.numpy()[0]) <= 1e-5 * abs(loss.numpy()[0])
+    assert ctx.device_status() == 0
+    ctx.close()
