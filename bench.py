@@ -28,7 +28,7 @@ sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch (mean of forward, dA, dW), from the ncu
 # captures summarised under profiles/ (keyed by M=N=K)
-NCU_DRAM_BYTES_PER_LAUNCH = {4096: 406_000_000, 8192: 2_967_000_000}
+NCU_DRAM_BYTES_PER_LAUNCH = {4096: 403_600_000, 8192: 3_051_000_000}
 
 SWEEP = [(512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
          (16384, 4096, 1024)]
