@@ -198,6 +198,24 @@ def cublas_tf32_yardstick(n=8192, reps=10):
             "tflops": round(2.0 * n ** 3 / ms / 1e9, 1), "note": "one plain product, no epilogue; for scale only"}
 
 
+def legacy_roundtrip(n=1024, reps=5):
+    """The reference's own micro-benchmark (lib/gpu_benching.dart:25-60): one all-ones n x n x n product through the
+    legacy FFI symbol, host buffers in and out, wall clock; c[0] must equal n."""
+    from flutter_ml_b200 import _lib
+    lib = _lib.load()
+    a = np.ones((n, n), dtype=np.float32)
+    b = np.ones((n, n), dtype=np.float32)
+    c = np.zeros((n, n), dtype=np.float32)
+    lib.multiplyMatrices(a.ctypes.data, b.ctypes.data, c.ctypes.data, n, n, n)  # first call creates the cached context
+    t = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        lib.multiplyMatrices(a.ctypes.data, b.ctypes.data, c.ctypes.data, n, n, n)
+        t.append(time.perf_counter() - t0)
+    return {"call": "multiplyMatrices(h_a, h_b, h_c, 1024, 1024, 1024), pageable host buffers", "ms": round(1e3 * min(t), 3),
+            "c0": float(c[0, 0]), "c0_expected": float(n)}
+
+
 def time_membound(ctx, hbm_gbs, reps=5, rows=262144, params=1 << 28):
     """Achieved HBM GB/s of the memory-bound kernels on footprints of 1 GiB and more (algorithmic bytes:
     every input read once, every output written once)."""
@@ -419,6 +437,8 @@ def main():
     if rank == 0 and not args.no_configs:
         from flutter_ml_b200 import config_bench
         line["configs"] = config_bench.run(ctx)
+        if local_rank == 0:  # the legacy symbol owns a context on device 0
+            line["legacy_roundtrip"] = legacy_roundtrip()
     if rank == 0 and not args.no_membound:
         line["membound"] = time_membound(ctx, peaks["hbm_gbs"], rows=args.membound_rows)
     if rank == 0 and not args.no_cpu:
