@@ -107,6 +107,9 @@ PROTOTYPES = {
     "fml_positional_table": [fp, fp, i32, i32],
     "fml_sgd_step": [fp, fp, fp, i64, C.c_double, C.c_double],
     "fml_adam_step": [fp, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, i32, C.c_double],
+    "fml_optimizer_step": [fp, i32, fp, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, i32],
+    "fml_act2_fwd": [fp, i32, f32, fp, fp, i64],
+    "fml_act2_bwd": [fp, i32, f32, fp, fp, fp, i64, i32],
     "fml_lstm_fwd": [fp, C.POINTER(LstmDesc)],
     "fml_lstm_bwd": [fp, C.POINTER(LstmDesc), fp, fp, fp, fp, fp],
     "fml_dp_unique_id": [C.c_char_p],

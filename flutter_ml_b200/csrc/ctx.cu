@@ -406,6 +406,9 @@ static int32_t legacy_buf(float** p, int64_t* cap, int64_t n) {
 }
 
 void multiplyMatrices(float* h_a, float* h_b, float* h_c, int32_t m, int32_t k, int32_t n) {
+  // this symbol has no status return: fml_last_error(NULL) afterwards is empty exactly when the call succeeded,
+  // whatever an earlier call on some other context left there
+  fml_set_global_error("");
   if (legacy_ctx()) return;
   if (!h_a || !h_b || !h_c || m <= 0 || k <= 0 || n <= 0) {
     fml_fail(g_legacy, FML_ERR_INVALID, "multiplyMatrices: bad arguments");

@@ -209,6 +209,75 @@ __global__ void adam_kernel(float* w, const float* __restrict__ g, float* m, flo
   }
 }
 
+struct OptK { float lr, h1, h2, h3, h4, omh1, omh2, c1, c2; int kind; };
+__global__ void optimizer_kernel(float* w, const float* __restrict__ g, float* s1, float* s2, float* s3, long long n, const OptK k) {
+  EW_LOOP(i, n) {
+    const float gi = g[i];
+    float wi = w[i];
+    switch (k.kind) {
+      case FML_OPT_MOMENTUM: { const float v = k.h1 * s1[i] + k.lr * gi; s1[i] = v; wi -= v; break; }
+      case FML_OPT_NAG: { const float v = k.h1 * s1[i] + gi; s1[i] = v; wi -= k.lr * (gi + k.h1 * v); break; }
+      case FML_OPT_RMSPROP: { const float s = k.h1 * s1[i] + k.omh1 * (gi * gi); s1[i] = s; wi -= k.lr * gi / (sqrtf(s) + k.h2); break; }
+      case FML_OPT_ADAGRAD: { const float s = s1[i] + gi * gi; s1[i] = s; wi -= k.lr * gi / (sqrtf(s) + k.h2); break; }
+      case FML_OPT_ADAMW: {
+        const float m = k.h1 * s1[i] + k.omh1 * gi, v = k.h2 * s2[i] + k.omh2 * (gi * gi);
+        s1[i] = m; s2[i] = v;
+        wi -= k.lr * (m / k.c1) / (sqrtf(v / k.c2) + k.h3);
+        wi -= k.lr * k.h4 * wi;
+        break;
+      }
+      case FML_OPT_AMSGRAD: {
+        const float m = k.h1 * s1[i] + k.omh1 * gi, v = k.h2 * s2[i] + k.omh2 * (gi * gi);
+        const float vh = fmaxf(s3[i], v);
+        s1[i] = m; s2[i] = v; s3[i] = vh;
+        wi -= k.lr * (m / k.c1) / (sqrtf(vh) + k.h3);
+        break;
+      }
+      default: break;
+    }
+    w[i] = wi;
+  }
+}
+
+// tanh(log(1 + e^x)) = ((1+e^x)^2 - 1) / ((1+e^x)^2 + 1) = n / (n + 2) with n = e^x (e^x + 2): no cancellation for
+// negative x, and 1 to float precision once e^x > 2^12.
+__device__ __forceinline__ float mish_tanh_softplus(float v) {
+  if (v > 20.f) return 1.f;
+  const float e = expf(v), n = e * (e + 2.f);
+  return n / (n + 2.f);
+}
+__device__ __forceinline__ float act2_apply(int kind, float alpha, float v) {
+  switch (kind) {
+    case FML_ACT2_LEAKY_RELU: return v > 0.f ? v : alpha * v;
+    case FML_ACT2_ELU: return v > 0.f ? v : alpha * (expf(v) - 1.f);
+    case FML_ACT2_SWISH: return v * (1.f / (1.f + expf(-v)));
+    case FML_ACT2_MISH: return v * mish_tanh_softplus(v);
+    default: return v;
+  }
+}
+__device__ __forceinline__ float act2_grad(int kind, float alpha, float v) {
+  switch (kind) {
+    case FML_ACT2_LEAKY_RELU: return v > 0.f ? 1.f : alpha;
+    case FML_ACT2_ELU: return v > 0.f ? 1.f : alpha * (expf(v) - 1.f) + alpha;
+    case FML_ACT2_SWISH: { const float sg = 1.f / (1.f + expf(-v)); return sg * (1.f + v * (1.f - sg)); }
+    case FML_ACT2_MISH: {
+      const float th = mish_tanh_softplus(v), sg = 1.f / (1.f + expf(-v));
+      return th + v * (1.f - th * th) * sg;
+    }
+    default: return 1.f;
+  }
+}
+__global__ void act2_fwd_kernel(int kind, float alpha, const float* __restrict__ x, float* __restrict__ y, long long n) {
+  EW_LOOP(i, n) y[i] = act2_apply(kind, alpha, x[i]);
+}
+__global__ void act2_bwd_kernel(int kind, float alpha, const float* __restrict__ x, const float* __restrict__ dy, float* dx,
+                                long long n, int accumulate) {
+  EW_LOOP(i, n) {
+    const float o = dy[i] * act2_grad(kind, alpha, x[i]);
+    dx[i] = accumulate ? dx[i] + o : o;
+  }
+}
+
 // ------------------------------------------------------------------ embedding
 __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int* __restrict__ ids,
                                      const float* __restrict__ pe, float* __restrict__ out, long long n, int dim,
@@ -359,6 +428,41 @@ int32_t fml_adam_step(fml_ctx* ctx, float* w, const float* g, float* m, float* v
   k.c1 = (float)(1.0 - pow(beta1, (double)t)); k.c2 = (float)(1.0 - pow(beta2, (double)t));
   const bool vec = (n % 4 == 0) && al16(w) && al16(g) && al16(m) && al16(v);
   return launch_vec(ctx, "adam_kernel", vec, n, adam_kernel<true>, adam_kernel<false>, w, g, m, v, (long long)n, k);
+}
+
+int32_t fml_optimizer_step(fml_ctx* ctx, int32_t kind, float* w, const float* g, float* s1, float* s2, float* s3, int64_t n,
+                           double lr, double h1, double h2, double h3, double h4, int32_t t) {
+  FML_REQUIRE(ctx, w && g && n >= 0, "fml_optimizer_step: bad arguments");
+  const bool two = kind == FML_OPT_ADAMW || kind == FML_OPT_AMSGRAD;
+  FML_REQUIRE(ctx, kind == FML_OPT_MOMENTUM || kind == FML_OPT_NAG || kind == FML_OPT_RMSPROP || kind == FML_OPT_ADAGRAD || two,
+              "fml_optimizer_step: unknown optimizer");
+  FML_REQUIRE(ctx, s1 && (!two || s2) && (kind != FML_OPT_AMSGRAD || s3), "fml_optimizer_step: missing state buffer");
+  FML_REQUIRE(ctx, !two || t >= 1, "fml_optimizer_step: t must be >= 1");
+  OptK k;
+  k.kind = kind; k.lr = (float)lr; k.h1 = (float)h1; k.h2 = (float)h2; k.h3 = (float)h3; k.h4 = (float)h4;
+  k.omh1 = (float)(1.0 - h1); k.omh2 = (float)(1.0 - h2);
+  k.c1 = two ? (float)(1.0 - pow(h1, (double)t)) : 1.f;
+  k.c2 = two ? (float)(1.0 - pow(h2, (double)t)) : 1.f;
+  if (n == 0) return FML_OK;
+  optimizer_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(w, g, s1, s2, s3, n, k);
+  FML_LAUNCH_CHECK(ctx, "optimizer_kernel");
+  return FML_OK;
+}
+
+int32_t fml_act2_fwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, float* y, int64_t n) {
+  FML_REQUIRE(ctx, x && y && n >= 0 && kind >= FML_ACT2_LEAKY_RELU && kind <= FML_ACT2_MISH, "fml_act2_fwd: bad arguments");
+  if (n == 0) return FML_OK;
+  act2_fwd_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(kind, alpha, x, y, n);
+  FML_LAUNCH_CHECK(ctx, "act2_fwd_kernel");
+  return FML_OK;
+}
+int32_t fml_act2_bwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, const float* dy, float* dx, int64_t n,
+                     int32_t accumulate) {
+  FML_REQUIRE(ctx, x && dy && dx && n >= 0 && kind >= FML_ACT2_LEAKY_RELU && kind <= FML_ACT2_MISH, "fml_act2_bwd: bad arguments");
+  if (n == 0) return FML_OK;
+  act2_bwd_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(kind, alpha, x, dy, dx, n, accumulate);
+  FML_LAUNCH_CHECK(ctx, "act2_bwd_kernel");
+  return FML_OK;
 }
 
 int32_t fml_embedding_fwd(fml_ctx* ctx, const float* table, const int32_t* ids, const float* pe, float* out, int64_t n,

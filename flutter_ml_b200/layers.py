@@ -70,6 +70,11 @@ class DenseLayerMatrix(Layer):
         super().build(x)
 
     def forward(self, x: Tensor) -> Tensor:
+        if self.activation in T.ACT2_BY_NAME:
+            # LeakyReLU / ELU / Swish / Mish are not epilogue functors of the contraction: bias-fused product, then
+            # the streaming activation (lib/layertypes/denseLayer.dart:116-125 applies them the same way)
+            z = T.denseMatrix(x, self.weights, self.biases, None, self.precision)
+            return T.ACT2_BY_NAME[self.activation](z)
         return T.denseMatrix(x, self.weights, self.biases, self.activation, self.precision)
 
 

@@ -89,3 +89,108 @@ class Adam(Optimizer):
         for p, m, v in zip(self.parameters, self._m, self._v):
             if p.grad is not None:
                 p.ctx.call("fml_adam_step", p.value, p.grad, m, v, p.value.size, *hp)
+
+
+class _StatefulOptimizer(Optimizer):
+    """Shared host side of the optimizers that run through `fml_optimizer_step`: up to three
+    zero-initialised state buffers shaped like the parameters (one flat buffer each with an arena)."""
+
+    KIND, N_STATE = 0, 1
+
+    def __init__(self, parameters, learningRate, arena=None):
+        super().__init__(parameters, learningRate, arena)
+        self._t = 0
+        if arena is not None:
+            self._state = [arena.ctx.zeros(arena.size) for _ in range(self.N_STATE)]
+        else:
+            self._state = [[p.ctx.zeros(*p.value.shape) for p in parameters] for _ in range(self.N_STATE)]
+
+    def _hyper(self):
+        raise NotImplementedError
+
+    def step(self):
+        self._t += 1
+        h = tuple(float(v) for v in self._hyper()) + (0.0,) * 4
+        tail = (float(self.learningRate), h[0], h[1], h[2], h[3], self._t)
+        if self.arena is not None:
+            a = self.arena
+            s = list(self._state) + [None] * (3 - self.N_STATE)
+            a.ctx.call("fml_optimizer_step", self.KIND, a.values, a.grads, s[0], s[1], s[2], a.size, *tail)
+            return
+        for i, p in enumerate(self.parameters):
+            if p.grad is None:
+                continue
+            s = [st[i] for st in self._state] + [None] * (3 - self.N_STATE)
+            p.ctx.call("fml_optimizer_step", self.KIND, p.value, p.grad, s[0], s[1], s[2], p.value.size, *tail)
+
+
+class SGDMomentum(_StatefulOptimizer):
+    """v = momentum*v + lr*g; w -= v (lib/optimizers/sgdmomentum.dart:56-57)."""
+    KIND, N_STATE = 1, 1
+
+    def __init__(self, parameters, learningRate, momentum=0.9, arena=None):
+        super().__init__(parameters, learningRate, arena)
+        self.momentum = momentum
+
+    def _hyper(self):
+        return (self.momentum,)
+
+
+class NAG(_StatefulOptimizer):
+    """v = momentum*v + g; w -= lr*(g + momentum*v) (lib/optimizers/nag.dart:58-60)."""
+    KIND, N_STATE = 2, 1
+
+    def __init__(self, parameters, learningRate, momentum=0.9, arena=None):
+        super().__init__(parameters, learningRate, arena)
+        self.momentum = momentum
+
+    def _hyper(self):
+        return (self.momentum,)
+
+
+class RMSprop(_StatefulOptimizer):
+    """s = beta*s + (1-beta)*g^2; w -= lr*g/(sqrt(s)+eps) (lib/optimizers/rmsprop.dart:57-58)."""
+    KIND, N_STATE = 3, 1
+
+    def __init__(self, parameters, learningRate, beta=0.9, epsilon=1e-8, arena=None):
+        super().__init__(parameters, learningRate, arena)
+        self.beta, self.epsilon = beta, epsilon
+
+    def _hyper(self):
+        return (self.beta, self.epsilon)
+
+
+class Adagrad(_StatefulOptimizer):
+    """s += g^2; w -= lr*g/(sqrt(s)+eps) (lib/optimizers/adagrad.dart:54-55)."""
+    KIND, N_STATE = 4, 1
+
+    def __init__(self, parameters, learningRate, epsilon=1e-8, arena=None):
+        super().__init__(parameters, learningRate, arena)
+        self.epsilon = epsilon
+
+    def _hyper(self):
+        return (0.0, self.epsilon)
+
+
+class AdamW(_StatefulOptimizer):
+    """Adam update followed by the decoupled decay w -= lr*weightDecay*w (lib/optimizers/adamw.dart:82-89)."""
+    KIND, N_STATE = 6, 2
+
+    def __init__(self, parameters, learningRate, beta1=0.9, beta2=0.999, epsilon=1e-8, weightDecay=0.01, arena=None):
+        super().__init__(parameters, learningRate, arena)
+        self.beta1, self.beta2, self.epsilon, self.weightDecay = beta1, beta2, epsilon, weightDecay
+
+    def _hyper(self):
+        return (self.beta1, self.beta2, self.epsilon, self.weightDecay)
+
+
+class AMSGrad(_StatefulOptimizer):
+    """Adam with the running maximum of v in the denominator (lib/optimizers/amsgrad.dart:80-86)."""
+    KIND, N_STATE = 7, 3
+
+    def __init__(self, parameters, learningRate, beta1=0.9, beta2=0.999, epsilon=1e-8, arena=None):
+        super().__init__(parameters, learningRate, arena)
+        self.beta1, self.beta2, self.epsilon = beta1, beta2, epsilon
+
+    def _hyper(self):
+        return (self.beta1, self.beta2, self.epsilon)

@@ -298,6 +298,39 @@ def geluMatrix(x):      # extension: exact GELU
     return _activation(x, "gelu", "gelu")
 
 
+def _activation2(x: Tensor, kind: int, alpha: float, op_name: str) -> Tensor:
+    """Parameterised activations: forward y = f(x), backward dx += dy * f'(x) from the saved input."""
+    ctx = x.ctx
+    out = Tensor(ctx.empty(*x.shape), ctx)
+    ctx.call("fml_act2_fwd", kind, float(alpha), x.value, out.value, x.value.size)
+    saved = x.value
+
+    def bw():
+        gx, acc = x._grad_target()
+        ctx.call("fml_act2_bwd", kind, float(alpha), saved, out.grad, gx, saved.size, 1 if acc else 0)
+    out.creator = Node([x], bw, op_name, x.value.size)
+    return out
+
+
+def leakyReluMatrix(x, alpha: float = 0.01):   # lib/activationFunctions/leakyRelu.dart:35-48
+    return _activation2(x, 5, alpha, "leaky_relu")
+
+
+def eluMatrix(x, alpha: float = 1.0):          # lib/activationFunctions/elu.dart:27-41
+    return _activation2(x, 6, alpha, "elu")
+
+
+def swishMatrix(x):                            # lib/activationFunctions/silu.dart:29-49
+    return _activation2(x, 7, 0.0, "swish")
+
+
+def mishMatrix(x):                             # lib/activationFunctions/mish.dart:29-31
+    return _activation2(x, 8, 0.0, "mish")
+
+
+ACT2_BY_NAME = {"leaky_relu": leakyReluMatrix, "elu": eluMatrix, "swish": swishMatrix, "silu": swishMatrix,
+                "mish": mishMatrix}
+
 relu, sigmoid, vectorTanh = reluMatrix, sigmoidMatrix, tanhMatrix  # vector forms :521, :541, :581
 
 

@@ -268,6 +268,26 @@ int32_t fml_sgd_step(fml_ctx* ctx, float* w, const float* g, int64_t n, double l
 int32_t fml_adam_step(fml_ctx* ctx, float* w, const float* g, float* m, float* v, int64_t n,
                       double lr, double beta1, double beta2, double eps, int32_t t, double grad_scale);
 
+/* The other optimizers of lib/optimizers, one kernel (state buffers start at zero; unused ones may be NULL):
+ *   FML_OPT_MOMENTUM sgdmomentum.dart:56-57 (h1 = momentum; s1 = velocity)
+ *   FML_OPT_NAG      nag.dart:58-60         (h1 = momentum; s1 = velocity)
+ *   FML_OPT_RMSPROP  rmsprop.dart:57-58     (h1 = beta, h2 = epsilon; s1 = mean square)
+ *   FML_OPT_ADAGRAD  adagrad.dart:54-55     (h2 = epsilon; s1 = squared-gradient sum)
+ *   FML_OPT_ADAMW    adamw.dart:82-89       (h1 = beta1, h2 = beta2, h3 = epsilon, h4 = weight decay; s1 = m, s2 = v)
+ *   FML_OPT_AMSGRAD  amsgrad.dart:80-86     (h1 = beta1, h2 = beta2, h3 = epsilon; s1 = m, s2 = v, s3 = max v) */
+typedef enum { FML_OPT_MOMENTUM = 1, FML_OPT_NAG = 2, FML_OPT_RMSPROP = 3, FML_OPT_ADAGRAD = 4, FML_OPT_ADAMW = 6,
+               FML_OPT_AMSGRAD = 7 } fml_optimizer;
+int32_t fml_optimizer_step(fml_ctx* ctx, int32_t kind, float* w, const float* g, float* s1, float* s2, float* s3,
+                           int64_t n, double lr, double h1, double h2, double h3, double h4, int32_t t);
+
+/* The other activations of lib/activationFunctions, with their parameter: FML_ACT2_LEAKY_RELU (alpha, leakyRelu.dart:35-48),
+ * FML_ACT2_ELU (alpha, elu.dart:27-41), FML_ACT2_SWISH (silu.dart:29-49), FML_ACT2_MISH (mish.dart:29-31).
+ * Backward takes the INPUT x and adds into dx when accumulate != 0. */
+typedef enum { FML_ACT2_LEAKY_RELU = 5, FML_ACT2_ELU = 6, FML_ACT2_SWISH = 7, FML_ACT2_MISH = 8 } fml_act2;
+int32_t fml_act2_fwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, float* y, int64_t n);
+int32_t fml_act2_bwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, const float* dy, float* dx, int64_t n,
+                     int32_t accumulate);
+
 /* ---- LSTM ---------------------------------------------------------------------
  * One layer over a batch of sequences (LSTMLayer.forward lib/layertypes/lstmLayer.dart:112-150).
  * W: 4 gate matrices [H x (H+I)] in order f,i,c~,o (:64) with columns [h_{t-1} | x_t] (:119),

@@ -353,6 +353,76 @@ void orc_adam_step(double* w, const double* g, double* m, double* v, int64_t n, 
   }
 }
 
+/* The other optimizers of lib/optimizers (same per-element loops; state arrays start at zero):
+ *   1 Momentum  sgdmomentum.dart:56-57   v = mu v + lr g;  w -= v
+ *   2 NAG       nag.dart:58-60           v = mu v + g;     w -= lr (g + mu v)
+ *   3 RMSprop   rmsprop.dart:57-58       s = b s + (1-b) g^2;  w -= lr g / (sqrt(s) + eps)
+ *   4 Adagrad   adagrad.dart:54-55       G += g^2;             w -= lr g / (sqrt(G) + eps)
+ *   6 AdamW     adamw.dart:82-89         Adam step, then w -= lr wd w
+ *   7 AMSGrad   amsgrad.dart:80-86       m, v as Adam; vhat = max(vhat, v); w -= lr mHat / (sqrt(vhat) + eps)
+ * h1..h4: (mu) | (mu) | (b, eps) | (-, eps) | (b1, b2, eps, wd) | (b1, b2, eps). */
+void orc_optimizer_step(int kind, double* w, const double* g, double* s1, double* s2, double* s3, int64_t n,
+                        double lr, double h1, double h2, double h3, double h4, int t) {
+  for (int64_t i = 0; i < n; i++) {
+    switch (kind) {
+      case 1: s1[i] = h1 * s1[i] + lr * g[i]; w[i] -= s1[i]; break;
+      case 2: { double vNew = h1 * s1[i] + g[i]; s1[i] = vNew; w[i] -= lr * (g[i] + h1 * vNew); break; }
+      case 3: s1[i] = h1 * s1[i] + (1 - h1) * (g[i] * g[i]); w[i] -= lr * g[i] / (sqrt(s1[i]) + h2); break;
+      case 4: s1[i] += g[i] * g[i]; w[i] -= lr * g[i] / (sqrt(s1[i]) + h2); break;
+      case 6: {
+        s1[i] = h1 * s1[i] + (1 - h1) * g[i];
+        s2[i] = h2 * s2[i] + (1 - h2) * (g[i] * g[i]);
+        double mHat = s1[i] / (1 - pow(h1, t)), vHat = s2[i] / (1 - pow(h2, t));
+        w[i] -= lr * mHat / (sqrt(vHat) + h3);
+        w[i] -= lr * h4 * w[i];
+        break;
+      }
+      case 7: {
+        s1[i] = h1 * s1[i] + (1 - h1) * g[i];
+        s2[i] = h2 * s2[i] + (1 - h2) * (g[i] * g[i]);
+        s3[i] = s3[i] > s2[i] ? s3[i] : s2[i];
+        double mHat = s1[i] / (1 - pow(h1, t));
+        w[i] -= lr * mHat / (sqrt(s3[i]) + h3);
+        break;
+      }
+      default: break;
+    }
+  }
+}
+
+/* LeakyReLU lib/activationFunctions/leakyRelu.dart:35-48, ELU elu.dart:27-41 (grad out + alpha for x <= 0),
+ * Swish silu.dart:29-49, Mish mish.dart:29-31 = x * tanh(log(exp(x) + 1)) composed from tape ops. */
+void orc_act2_fwd(int kind, double alpha, const double* x, double* y, int64_t n) {
+  for (int64_t i = 0; i < n; i++) {
+    double v = x[i];
+    switch (kind) {
+      case 5: y[i] = v > 0 ? v : alpha * v; break;
+      case 6: y[i] = v > 0 ? v : alpha * (exp(v) - 1); break;
+      case 7: y[i] = v * (1.0 / (1.0 + exp(-v))); break;
+      case 8: { double sp = log(exp(v) + 1.0); double e2 = exp(2 * sp); y[i] = v * (isinf(e2) ? 1.0 : (e2 - 1) / (e2 + 1)); break; }
+      default: y[i] = v;
+    }
+  }
+}
+void orc_act2_bwd(int kind, double alpha, const double* x, const double* dy, double* dx, int64_t n) {
+  for (int64_t i = 0; i < n; i++) {
+    double v = x[i], d = 1.0;
+    switch (kind) {
+      case 5: d = v > 0 ? 1.0 : alpha; break;
+      case 6: d = v > 0 ? 1.0 : (alpha * (exp(v) - 1)) + alpha; break;
+      case 7: { double sg = 1.0 / (1.0 + exp(-v)); d = sg * (1 + v * (1 - sg)); break; }
+      case 8: {
+        /* chain rule through multiply, tanh (1 - y^2), log (1/u), exp: as the tape would */
+        double ex = exp(v), sp = log(ex + 1.0), e2 = exp(2 * sp), th = isinf(e2) ? 1.0 : (e2 - 1) / (e2 + 1);
+        d = th + v * (1 - th * th) * (ex / (ex + 1.0));
+        break;
+      }
+      default: break;
+    }
+    dx[i] += dy[i] * d;
+  }
+}
+
 /* ------------------------------------------------- embedding / positional --- */
 
 /* EmbeddingLayer.forward lib/transformer/embeddingLayer.dart:47-56: ids arrive

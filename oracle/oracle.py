@@ -130,6 +130,20 @@ class Ops:
         self.L.orc_adam_step(_p(w), _p(g), _p(m), _p(v), C.c_int64(w.size), C.c_double(lr),
                              C.c_double(b1), C.c_double(b2), C.c_double(eps), int(t))
 
+    def optimizer_step(self, kind, w, g, s1, s2, s3, lr, h=(0, 0, 0, 0), t=1):
+        """kind: 1 Momentum, 2 NAG, 3 RMSprop, 4 Adagrad, 6 AdamW, 7 AMSGrad (see oracle.c)."""
+        h = list(h) + [0.0] * (4 - len(h))
+        self.L.orc_optimizer_step(int(kind), _p(w), _p(g), _p(s1), _p(s2), _p(s3), C.c_int64(w.size), C.c_double(lr),
+                                  *[C.c_double(x) for x in h], int(t))
+
+    def act2_fwd(self, kind, alpha, x):
+        y = np.empty_like(x)
+        self.L.orc_act2_fwd(int(kind), C.c_double(alpha), _p(x), _p(y), C.c_int64(x.size))
+        return y
+
+    def act2_bwd(self, kind, alpha, x, dy, dx):
+        self.L.orc_act2_bwd(int(kind), C.c_double(alpha), _p(x), _p(dy), _p(dx), C.c_int64(x.size))
+
     def embedding_fwd(self, table, ids):
         ids = np.ascontiguousarray(ids, dtype=np.float64)
         out = np.empty((ids.size, table.shape[1]))

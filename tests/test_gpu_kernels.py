@@ -369,3 +369,54 @@ def test_attention_scores_with_row_epilogue(ctx, orc, S, causal, prec, tol):
             ds_ref = np.zeros((S, S))
             ops.softmax_bwd(w64(Ph[b, h]), dp_ref, ds_ref)
             assert rel(dSh[b, h], ds_ref * scale) <= 2 * tol
+
+
+@pytest.mark.parametrize("kind,h,nstate", [(1, (0.9,), 1), (2, (0.9,), 1), (3, (0.9, 1e-8), 1), (4, (0.0, 1e-8), 1),
+                                           (6, (0.9, 0.999, 1e-8, 0.01), 2), (7, (0.9, 0.999, 1e-8), 3)])
+@pytest.mark.parametrize("n", [109386, 5])
+def test_optimizer_family(ctx, orc, kind, h, nstate, n):
+    """fml_optimizer_step against the oracle's restatement of lib/optimizers/{sgdmomentum,nag,rmsprop,adagrad,adamw,
+    amsgrad}.dart over three steps with fresh gradients."""
+    rng = np.random.default_rng(kind * 100 + n)
+    w = rng.standard_normal(n).astype(np.float32)
+    ops = orc.Ops()
+    w_ref = w64(w)
+    s_ref = [np.zeros(n) for _ in range(nstate)] + [None] * (3 - nstate)
+    dw = ctx.upload(w)
+    ds = [ctx.zeros(n) for _ in range(nstate)] + [None] * (3 - nstate)
+    hh = tuple(h) + (0.0,) * (4 - len(h))
+    for t in (1, 2, 3):
+        g = rng.standard_normal(n).astype(np.float32)
+        ops.optimizer_step(kind, w_ref, w64(g), s_ref[0], s_ref[1], s_ref[2], 1e-2, h, t)
+        ctx.call("fml_optimizer_step", kind, dw, ctx.upload(g), ds[0], ds[1], ds[2], n, 1e-2, *hh, t)
+    assert rel(dw.numpy(), w_ref) <= 1e-6
+    for i in range(nstate):
+        assert rel(ds[i].numpy(), s_ref[i]) <= 1e-6
+
+
+def test_optimizer_family_rejects_bad_arguments(ctx):
+    w, g = ctx.zeros(8), ctx.zeros(8)
+    with pytest.raises(RuntimeError):
+        ctx.call("fml_optimizer_step", 5, w, g, ctx.zeros(8), None, None, 8, 0.1, 0.9, 0.0, 0.0, 0.0, 1)   # unknown kind
+    with pytest.raises(RuntimeError):
+        ctx.call("fml_optimizer_step", 7, w, g, ctx.zeros(8), ctx.zeros(8), None, 8, 0.1, 0.9, 0.999, 1e-8, 0.0, 1)  # no s3
+
+
+@pytest.mark.parametrize("kind,alpha", [(5, 0.01), (5, 0.3), (6, 1.0), (6, 0.5), (7, 0.0), (8, 0.0)])
+def test_parameterised_activations(ctx, orc, kind, alpha):
+    """fml_act2_fwd/bwd (LeakyReLU, ELU, Swish, Mish) against the oracle, including saturating inputs."""
+    rng = np.random.default_rng(kind)
+    x = np.concatenate([rng.standard_normal(70001) * 3, [0.0, -30.0, 30.0, 80.0, -80.0]]).astype(np.float32)
+    dy = rng.standard_normal(x.size).astype(np.float32)
+    ops = orc.Ops()
+    y_ref = ops.act2_fwd(kind, alpha, w64(x))
+    dx_ref = np.zeros(x.size)
+    ops.act2_bwd(kind, alpha, w64(x), w64(dy), dx_ref)
+    dxd, ddy, y, dx = ctx.upload(x), ctx.upload(dy), ctx.empty(x.size), ctx.empty(x.size)
+    ctx.call("fml_act2_fwd", kind, alpha, dxd, y, x.size)
+    ctx.call("fml_act2_bwd", kind, alpha, dxd, ddy, dx, x.size, 0)
+    assert rel(y.numpy(), y_ref) <= 1e-6
+    assert rel(dx.numpy(), dx_ref) <= 1e-6
+    assert np.all(np.isfinite(y.numpy())) and np.all(np.isfinite(dx.numpy()))
+    ctx.call("fml_act2_bwd", kind, alpha, dxd, ddy, dx, x.size, 1)   # accumulate
+    assert rel(dx.numpy(), 2 * dx_ref) <= 1e-6

@@ -188,3 +188,55 @@ def test_mlp_step_recorded_as_cuda_graph_matches_eager_steps():
     assert abs(graph.loss.numpy()[0] - loss.numpy()[0]) <= 1e-5 * abs(loss.numpy()[0])
     assert ctx.device_status() == 0
     ctx.close()
+
+
+@pytest.mark.parametrize("act", ["leaky_relu", "elu", "swish", "mish"])
+@pytest.mark.parametrize("opt_name", ["SGDMomentum", "NAG", "RMSprop", "Adagrad", "AdamW", "AMSGrad"])
+def test_dense_net_with_other_activations_and_optimizers(orc, act, opt_name):
+    """Two dense layers with one of the remaining activation functions, trained two steps with one of the remaining
+    optimizers (flat parameter arena): parameters after the steps against the same steps in the oracle."""
+    from flutter_ml_b200 import _lib, optimizers
+    from flutter_ml_b200.layers import DenseLayerMatrix
+    from flutter_ml_b200.tensor import Tensor, mseMatrix, set_default_context
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    set_default_context(ctx)
+    rng = np.random.default_rng(11)
+    Bn, din, dh, dout = 32, 24, 40, 8
+    X, Y = rng.standard_normal((Bn, din)).astype(np.float32), rng.standard_normal((Bn, dout)).astype(np.float32)
+    l1, l2 = DenseLayerMatrix(dh, act, seed=1), DenseLayerMatrix(dout, None, seed=2)
+    x = Tensor(X, ctx)
+    l2(l1(x))
+    params = l1.parameters + l2.parameters
+    ref = [p.numpy(np.float64).copy() for p in params]
+    arena = optimizers.ParameterArena(ctx, params)
+    kind, h, nstate = {"SGDMomentum": (1, (0.9,), 1), "NAG": (2, (0.9,), 1), "RMSprop": (3, (0.9, 1e-8), 1),
+                       "Adagrad": (4, (0.0, 1e-8), 1), "AdamW": (6, (0.9, 0.999, 1e-8, 0.01), 2),
+                       "AMSGrad": (7, (0.9, 0.999, 1e-8), 3)}[opt_name]
+    opt = getattr(optimizers, opt_name)(params, 0.01, arena=arena)
+    ops = orc.Ops()
+    code, alpha = {"leaky_relu": (5, 0.01), "elu": (6, 1.0), "swish": (7, 0.0), "mish": (8, 0.0)}[act]
+    state = [[np.zeros(r.size) for _ in range(nstate)] + [None] * (3 - nstate) for r in ref]
+    X64, Y64 = X.astype(np.float64), Y.astype(np.float64)
+    for t in (1, 2):
+        opt.zeroGrad()
+        loss = mseMatrix(l2(l1(Tensor(X, ctx))), Tensor(Y, ctx))
+        loss.backward()
+        opt.step()
+        W1, b1, W2, b2 = ref
+        z = X64 @ W1 + b1
+        a = ops.act2_fwd(code, alpha, np.ascontiguousarray(z))
+        out = a @ W2 + b2
+        dout_ = 2.0 * (out - Y64) / out.size
+        gW2, gb2 = a.T @ dout_, dout_.sum(0)
+        da = np.ascontiguousarray(dout_ @ W2.T)
+        dz = np.zeros_like(z)
+        ops.act2_bwd(code, alpha, np.ascontiguousarray(z), da, dz)
+        gW1, gb1 = X64.T @ dz, dz.sum(0)
+        if t == 1:
+            assert abs(float(loss.numpy().ravel()[0]) - float(((out - Y64) ** 2).mean())) <= 1e-5 * float(((out - Y64) ** 2).mean())
+        for r, g, s in zip(ref, (gW1, gb1, gW2, gb2), state):
+            rf, gf = r.reshape(-1), np.ascontiguousarray(g.reshape(-1))
+            ops.optimizer_step(kind, rf, gf, s[0], s[1], s[2], 0.01, h, t)
+    for p, r in zip(params, ref):
+        assert rel(p.numpy(), r) <= 2e-5
+    ctx.close()

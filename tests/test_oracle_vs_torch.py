@@ -207,3 +207,73 @@ def test_finite_difference_layernorm_softmax(orc):
         xm[idx] -= 1e-6
         num[idx] = (f(xp) - f(xm)) / 2e-6
     assert rel(dx, num) < 1e-6
+
+
+@pytest.mark.parametrize("kind,alpha,fn", [
+    (5, 0.01, lambda x: torch.nn.functional.leaky_relu(x, 0.01)),
+    (5, 0.3, lambda x: torch.nn.functional.leaky_relu(x, 0.3)),
+    (6, 1.0, lambda x: torch.nn.functional.elu(x, 1.0)),
+    (6, 0.5, lambda x: torch.nn.functional.elu(x, 0.5)),
+    (7, 0.0, torch.nn.functional.silu),
+    (8, 0.0, torch.nn.functional.mish),
+])
+def test_parameterised_activations(orc, kind, alpha, fn):
+    rng = np.random.default_rng(kind)
+    x = np.concatenate([rng.standard_normal(500) * 3, [0.0, -30.0, 30.0, 400.0, -400.0]])
+    dy = rng.standard_normal(x.size)
+    ops = orc.Ops()
+    y = ops.act2_fwd(kind, alpha, x)
+    dx = np.zeros_like(x)
+    ops.act2_bwd(kind, alpha, x, dy, dx)
+    xt = tt(x)
+    yt = fn(xt)
+    yt.backward(torch.tensor(dy))
+    assert rel(y, yt.detach().numpy()) <= 1e-12
+    assert rel(dx, xt.grad.numpy()) <= 1e-12
+    # backward accumulates (+=), as every tape closure of the reference does
+    ops.act2_bwd(kind, alpha, x, dy, dx)
+    assert rel(dx, 2 * xt.grad.numpy()) <= 1e-12
+
+
+def test_optimizer_family(orc):
+    """Momentum / NAG / RMSprop / Adagrad against torch.optim (same update rules at constant learning rate);
+    AdamW and AMSGrad against the reference's formulas written out in numpy (torch orders the decay and the
+    bias correction of the running maximum differently)."""
+    rng = np.random.default_rng(3)
+    n, lr = 257, 0.01
+    w0 = rng.standard_normal(n)
+    grads = [rng.standard_normal(n) for _ in range(4)]
+    ops = orc.Ops()
+
+    def run_oracle(kind, h, nstate):
+        w = w0.copy()
+        s = [np.zeros(n) for _ in range(nstate)] + [None] * (3 - nstate)
+        for t, g in enumerate(grads, 1):
+            ops.optimizer_step(kind, w, g, s[0], s[1], s[2], lr, h, t)
+        return w
+
+    def run_torch(make):
+        p = torch.nn.Parameter(torch.tensor(w0))
+        opt = make([p])
+        for g in grads:
+            p.grad = torch.tensor(g)
+            opt.step()
+        return p.detach().numpy()
+
+    assert rel(run_oracle(1, (0.9,), 1), run_torch(lambda p: torch.optim.SGD(p, lr=lr, momentum=0.9))) <= TOL
+    assert rel(run_oracle(2, (0.9,), 1), run_torch(lambda p: torch.optim.SGD(p, lr=lr, momentum=0.9, nesterov=True))) <= TOL
+    assert rel(run_oracle(3, (0.9, 1e-8), 1), run_torch(lambda p: torch.optim.RMSprop(p, lr=lr, alpha=0.9, eps=1e-8))) <= TOL
+    assert rel(run_oracle(4, (0.0, 1e-8), 1), run_torch(lambda p: torch.optim.Adagrad(p, lr=lr, eps=1e-8))) <= TOL
+
+    b1, b2, eps, wd = 0.9, 0.999, 1e-8, 0.01
+    w, m, v, vmax = w0.copy(), np.zeros(n), np.zeros(n), np.zeros(n)
+    w2 = w0.copy()
+    for t, g in enumerate(grads, 1):
+        m = b1 * m + (1 - b1) * g
+        v = b2 * v + (1 - b2) * g * g
+        w = w - lr * (m / (1 - b1 ** t)) / (np.sqrt(v / (1 - b2 ** t)) + eps)
+        w = w - lr * wd * w
+        vmax = np.maximum(vmax, v)
+        w2 = w2 - lr * (m / (1 - b1 ** t)) / (np.sqrt(vmax) + eps)
+    assert rel(run_oracle(6, (b1, b2, eps, wd), 2), w) <= TOL
+    assert rel(run_oracle(7, (b1, b2, eps), 3), w2) <= TOL
