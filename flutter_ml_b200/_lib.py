@@ -47,6 +47,13 @@ class LstmDesc(C.Structure):
                 ("gates", fp), ("cells", fp), ("hs", fp), ("xproj", fp)]
 
 
+class Op(C.Structure):
+    """fml_op: one autograd node of a tape handed to fml_tape_run."""
+    _fields_ = [("kind", i32), ("rows", i32), ("cols", i32), ("inner", i32), ("inp", fp * 3), ("gin", fp * 3),
+                ("out", fp), ("gout", fp), ("aux", fp * 2), ("ids", fp), ("parts", fp), ("gparts", fp),
+                ("part_cols", fp), ("n_parts", i32), ("s", f32), ("iparam", i32), ("precision", i32)]
+
+
 # name -> argument types (restype is int32 unless listed in _RESTYPES)
 PROTOTYPES = {
     "fml_init": [C.POINTER(Config), C.POINTER(fp)],
@@ -110,6 +117,8 @@ PROTOTYPES = {
     "fml_optimizer_step": [fp, i32, fp, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, i32],
     "fml_act2_fwd": [fp, i32, f32, fp, fp, i64],
     "fml_act2_bwd": [fp, i32, f32, fp, fp, fp, i64, i32],
+    "fml_tape_run": [fp, C.POINTER(Op), i32, i32],
+    "fml_tape_kind": [C.c_char_p],
     "fml_lstm_fwd": [fp, C.POINTER(LstmDesc)],
     "fml_lstm_bwd": [fp, C.POINTER(LstmDesc), fp, fp, fp, fp, fp],
     "fml_dp_unique_id": [C.c_char_p],

@@ -36,7 +36,31 @@ def config1_mlp(ctx):
     mlp.record_step(X, labels)
     gms, _ = _timed(ctx, mlp.replay_step, warm=5, reps=200)
     out.update({"graph_us_per_step": round(gms * 1e3, 1), "graph_samples_per_s": round(64 / gms * 1e3, 1)})
+    out.update(_config1_tape(ctx))
     return out
+
+
+def _config1_tape(ctx):
+    """The same step as a node list for the tape executor: three `dense` nodes + softmax cross-entropy, one library
+    call per sweep (forward, backward) and one for SGD over the six parameters' flat arena."""
+    from .optimizers import ParameterArena
+    from .tape import Tape
+    tp = Tape(ctx)
+    P = [tp.tensor(p) for p in models.init_mlp(0)]
+    h = tp.tensor(synth.uniform(0, 0, (64, 784)), requires_grad=False)
+    for l, act in enumerate(("relu", "relu", None)):
+        h = tp.dense(h, P[2 * l], P[2 * l + 1], act)
+    tp.softmaxCrossEntropy(h, tp.ids(synth.integers(0, 1, (64,), 10)), 1.0 / 64)
+    arena = ParameterArena(ctx, P)   # parameters and their gradients become slices of two flat buffers
+    tp.compile()
+
+    def step():
+        tp.forward()
+        tp.backward()
+        ctx.call("fml_sgd_step", arena.values, arena.grads, arena.size, 0.01, 1.0)
+        arena.zero_grads()
+    ms, _ = _timed(ctx, step, warm=5, reps=200)
+    return {"tape_us_per_step": round(ms * 1e3, 1), "tape_samples_per_s": round(64 / ms * 1e3, 1)}
 
 
 def config3_encoder_block(ctx):

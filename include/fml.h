@@ -288,6 +288,78 @@ int32_t fml_act2_fwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, fl
 int32_t fml_act2_bwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, const float* dy, float* dx, int64_t n,
                      int32_t accumulate);
 
+/* ---- tape executor ---------------------------------------------------------------
+ * One call runs a whole list of autograd nodes on the device: the replacement for
+ * walking Node.opName / Node.extraParams (lib/autogradEngine/tensor.dart:5-19) and
+ * calling one closure per node (Tensor.backward, tensor.dart:43-75).  The caller lists
+ * the nodes in creation (topological) order, as tensor.dart:54-66 produces them; every
+ * tensor is a device buffer of rows x cols floats (vectors: rows = 1, scalars: 1 x 1).
+ *
+ *   FML_TAPE_FORWARD   computes out of every op, first to last.
+ *   FML_TAPE_BACKWARD  sets gout of the LAST op to 1 (tensor.dart:70) and runs the
+ *                      gradient rule of every op last to first.  Gradients ACCUMULATE
+ *                      into gin[] (+=) exactly as the reference's closures do, so the
+ *                      caller zeroes gradient buffers first (Tensor.zeroGrad,
+ *                      tensor.dart:77-91).  A NULL gin[i] means "no gradient wanted".
+ *   FML_TAPE_BACKWARD_NOSEED  the same without touching the last gout.
+ *
+ * kind follows the reference's opName strings (fml_tape_kind maps a string to its kind):
+ *   matMul              out[r x c] = in0[r x inner] . in1[inner x c]          tensor.dart:867-947
+ *   matVecMul           out[c] = in0[c x inner] . in1[inner]                   tensor.dart:949-980
+ *   addMatrixAndVector  out = in0 + 1.in1^T                                    tensor.dart:679-709
+ *   add_matrix, add_vector, add_3d               out = in0 + in1               tensor.dart:651-677, 395-414
+ *   multiply_matrix, multiply_vector             out = in0 * in1 (elementwise) tensor.dart:478-497, 835-865
+ *   relu_*, sigmoid_*, tanh_* (vector and matrix forms), gelu (extension)      tensor.dart:521-605, 1013-1209
+ *   leaky_relu, elu(_matrix), swish, mish        s = alpha                     lib/activationFunctions
+ *   scale_matrix        out = s * in0                                          tensor.dart:1075-1101
+ *   transpose           out[r x c] = in0[c x r]^T                              tensor.dart:1211-1236
+ *   concat_matrix_col, concat_vector   out = [parts[0] | parts[1] | ...], n_parts buffers of
+ *                       part_cols[i] columns each (gparts[i] may be NULL)      tensor.dart:739-763, 437-455
+ *   softmax_matrix, softmax            rows; iparam = causal period (0 = none; extension)  softmax.dart:68-115
+ *   layer_norm(_vector) in0 = x, in1 = gamma, in2 = beta, s = epsilon; aux0 [r x c] and aux1 [r]
+ *                       are caller-provided buffers for x-hat and 1/sigma      layerNormalization.dart:137-202
+ *   embedding_lookup    in0 = table [inner x c], ids = r row indices           embeddingLayer.dart:47-67
+ *   mse_matrix, mse_vector   in0 = prediction, in1 = target, inner = their element count, out 1 x 1
+ *                                                                              tensor.dart:499-519, 982-1011
+ *   sum_matrix, sum_vector   out 1 x 1 = sum of the inner elements of in0      tensor.dart:561-579, 1153-1176
+ *   softmax_xent (extension) in0 = logits [inner x iparam], ids = labels, s = 1/count, out 1 x 1; aux0
+ *                       [inner x iparam] keeps the gradient between the sweeps
+ *   dense (extension)   out = act(in0[r x inner] . in1[inner x c] + in2), iparam = fml_act, aux0 = pre-activation
+ *                       buffer for GELU: matMul + addMatrixAndVector + activation of
+ *                       DenseLayerMatrix.forward (denseLayer.dart:116-125) as one launch; its backward rule
+ *                       leaves dLoss/dZ in gout */
+typedef enum {
+  FML_OP_MATMUL = 1, FML_OP_MATVECMUL = 2, FML_OP_ADD_MATRIX_AND_VECTOR = 3, FML_OP_ADD = 4, FML_OP_MULTIPLY = 5,
+  FML_OP_RELU = 6, FML_OP_SIGMOID = 7, FML_OP_TANH = 8, FML_OP_GELU = 9, FML_OP_LEAKY_RELU = 10, FML_OP_ELU = 11,
+  FML_OP_SWISH = 12, FML_OP_MISH = 13, FML_OP_SCALE_MATRIX = 14, FML_OP_TRANSPOSE = 15, FML_OP_CONCAT = 16,
+  FML_OP_SOFTMAX_MATRIX = 17, FML_OP_LAYER_NORM = 18, FML_OP_EMBEDDING_LOOKUP = 19, FML_OP_MSE = 20, FML_OP_SUM = 21,
+  FML_OP_SOFTMAX_XENT = 22, FML_OP_DENSE = 23
+} fml_op_kind;
+typedef enum { FML_TAPE_FORWARD = 0, FML_TAPE_BACKWARD = 1, FML_TAPE_BACKWARD_NOSEED = 2 } fml_tape_direction;
+
+typedef struct fml_op {
+  int32_t kind;            /* fml_op_kind */
+  int32_t rows, cols;      /* shape of out */
+  int32_t inner;           /* contraction length / table rows, see above */
+  float* in[3];            /* input values */
+  float* gin[3];           /* their gradient buffers, same shapes, or NULL */
+  float* out;              /* output value */
+  float* gout;             /* its gradient buffer (read by the backward rule) */
+  float* aux[2];           /* op-private saved tensors, caller-allocated (see the list above) */
+  const int32_t* ids;      /* embedding_lookup row indices / softmax_xent labels (device) */
+  float* const* parts;     /* concat: host array of n_parts device pointers */
+  float* const* gparts;    /* concat: their gradient buffers (entries may be NULL), or NULL */
+  const int32_t* part_cols;/* concat: host array of n_parts column counts */
+  int32_t n_parts;
+  float s;                 /* extraParams: 's' (tensor.dart:1098), alpha, epsilon, 1/count */
+  int32_t iparam;          /* causal period / activation code */
+  int32_t precision;       /* contraction precision, -1 = context default */
+} fml_op;
+
+int32_t fml_tape_run(fml_ctx* ctx, const fml_op* ops, int32_t n_ops, int32_t direction);
+/* opName string -> fml_op_kind, 0 if the executor does not know the name. */
+int32_t fml_tape_kind(const char* op_name);
+
 /* ---- LSTM ---------------------------------------------------------------------
  * One layer over a batch of sequences (LSTMLayer.forward lib/layertypes/lstmLayer.dart:112-150).
  * W: 4 gate matrices [H x (H+I)] in order f,i,c~,o (:64) with columns [h_{t-1} | x_t] (:119),

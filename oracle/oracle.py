@@ -321,6 +321,45 @@ class Engine:
         out = T(self.ops.embedding_fwd(table.value, ids))
         return _node(out, [table], lambda: self.ops.embedding_bwd(out.grad, ids, table.grad))
 
+    # tensor.dart:949-980
+    def matVecMul(self, M, v):
+        out = T(self.ops.matvec_fwd(M.value, v.value))
+        return _node(out, [M, v], lambda: self.ops.matvec_bwd(M.value, v.value, out.grad, M.grad, v.grad))
+
+    # tensor.dart:478-497 (vector), 835-865 (matrix)
+    def elementWiseMultiply(self, a, b):
+        out = T(a.value * b.value)
+
+        def bw():
+            a.grad += out.grad * b.value
+            b.grad += out.grad * a.value
+        return _node(out, [a, b], bw)
+
+    # tensor.dart:561-579 (sum), 1153-1176 (sumMatrix): row-major running total
+    def sum(self, x):
+        total = 0.0
+        for v in x.value.ravel():
+            total += v
+        out = T(np.array(total))
+
+        def bw():
+            x.grad += float(out.grad)
+        return _node(out, [x], bw)
+
+    # lib/activationFunctions/{leakyRelu,elu,silu,mish}.dart (kinds 5..8 of orc_act2_*)
+    def act2(self, kind, x, alpha=0.0):
+        out = T(self.ops.act2_fwd(kind, alpha, x.value))
+        return _node(out, [x], lambda: self.ops.act2_bwd(kind, alpha, x.value, out.grad, x.grad))
+
+    # tensor.dart:437-455
+    def concatenate(self, a, b):
+        out = T(np.concatenate([a.value, b.value]))
+
+        def bw():
+            a.grad += out.grad[:a.value.size]
+            b.grad += out.grad[a.value.size:]
+        return _node(out, [a, b], bw)
+
     # ---------------------------------------------------------------- layers
 
     def dense_matrix(self, x, W, b, act=None):

@@ -50,3 +50,23 @@ def test_product_never_imports_the_oracle():
             if f.endswith(".py"):
                 src = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle", src, flags=re.M) and "oracle." not in src, f
+
+
+def test_tape_kind_knows_the_reference_op_names():
+    """fml_tape_kind is host-only: every opName string of the reference's hot path
+    (lib/autogradEngine/tensor.dart:410-1232, softmax.dart:113, layerNormalization.dart:200,
+    embeddingLayer.dart:65) maps to a kind, vector and matrix spellings to the same one."""
+    from flutter_ml_b200 import _lib
+    lib = _lib.load()
+    names = ["matMul", "matVecMul", "addMatrixAndVector", "add_matrix", "add_vector", "relu_matrix", "relu_vector",
+             "sigmoid_vector", "sigmoid_matrix", "tanh_vector", "tanh_matrix", "multiply_vector", "multiply_matrix",
+             "concat_vector", "concat_matrix_col", "scale_matrix", "transpose", "softmax_matrix", "layer_norm",
+             "embedding_lookup", "mse_vector", "mse_matrix", "sum_vector", "sum_matrix", "leaky_relu", "elu", "swish",
+             "gelu", "softmax_xent", "dense"]
+    kinds = {n: lib.fml_tape_kind(n.encode()) for n in names}
+    assert all(k > 0 for k in kinds.values()), kinds
+    assert kinds["relu_matrix"] == kinds["relu_vector"] and kinds["add_matrix"] == kinds["add_vector"]
+    assert kinds["matMul"] == 1 and kinds["dense"] == 23
+    assert lib.fml_tape_kind(b"conv2d") == 0 and lib.fml_tape_kind(None) == 0
+    from flutter_ml_b200 import tape
+    assert tape.KIND["matMul"] == kinds["matMul"] and tape.KIND["layer_norm"] == kinds["layer_norm"]

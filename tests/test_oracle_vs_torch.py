@@ -277,3 +277,25 @@ def test_optimizer_family(orc):
         w2 = w2 - lr * (m / (1 - b1 ** t)) / (np.sqrt(vmax) + eps)
     assert rel(run_oracle(6, (b1, b2, eps, wd), 2), w) <= TOL
     assert rel(run_oracle(7, (b1, b2, eps), 3), w2) <= TOL
+
+
+def test_vector_form_tape_ops(orc):
+    """matVecMul, concatenate, elementWiseMultiply, sum and the parameterised activations on the oracle's tape
+    against torch autograd: one LSTM-style step written in the reference's vector vocabulary."""
+    rng = np.random.default_rng(21)
+    H, I = 7, 5
+    W1, W2, b, h0, x = (rng.standard_normal(s) for s in ((H, H + I), (H, H + I), (H,), (H,), (I,)))
+    E = orc.Engine()
+    oW1, oW2, ob, oh, ox = (orc.T(a) for a in (W1, W2, b, h0, x))
+    z = E.concatenate(oh, ox)
+    g1 = E.sigmoidMatrix(E.addMatrix(E.matVecMul(oW1, z), ob))
+    g2 = E.act2(7, E.matVecMul(oW2, z))
+    out = E.sum(E.elementWiseMultiply(E.elementWiseMultiply(g1, g2), oh))
+    out.backward()
+    tW1, tW2, tb, th, tx = (tt(a) for a in (W1, W2, b, h0, x))
+    tz = torch.cat([th, tx])
+    tout = (torch.sigmoid(tW1 @ tz + tb) * torch.nn.functional.silu(tW2 @ tz) * th).sum()
+    tout.backward()
+    assert abs(float(out.value) - float(tout)) <= 1e-12 * abs(float(tout))
+    for o, t in ((oW1, tW1), (oW2, tW2), (ob, tb), (oh, th), (ox, tx)):
+        assert rel(o.grad, t.grad.numpy()) <= TOL
