@@ -376,6 +376,78 @@ __global__ void __launch_bounds__(256) xent_kernel(const float* z, const int* __
   }
 }
 
+// Wide rows (vocabulary-sized logits): one 1024-thread block per row keeps the whole row in registers
+// (NV float4 per thread, all loads issued before the first use), so the logits are read from HBM exactly once
+// and the gradient written once: 8 bytes per element.  Two block reductions (max, sum of 2^(k(v - max))).
+template <int NV>
+__global__ void __launch_bounds__(1024) xent_rowreg_kernel(const float* z, const int* __restrict__ labels,
+                                                           float* dz /* may alias z */, float* __restrict__ row_loss,
+                                                           long long rows, int cols, float inv_count) {
+  __shared__ float red[32];
+  __shared__ float bcast[3];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr float LOG2E = 1.4426950408889634f;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float4* zr = reinterpret_cast<const float4*>(z + r * cols);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int c4 = threadIdx.x + 1024 * i;
+      v[i] = make_float4(NEG_INF, NEG_INF, NEG_INF, NEG_INF);
+      if (c4 * 4 < cols) v[i] = zr[c4];
+    }
+    const int lab = labels[r];
+    float mx = NEG_INF;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+      const int d = lab - (threadIdx.x + 1024 * i) * 4;  // the owner of the label's column publishes its logit
+      if (d >= 0 && d < 4) bcast[2] = d == 0 ? v[i].x : d == 1 ? v[i].y : d == 2 ? v[i].z : v[i].w;
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (warp == 0) {
+      const float t = warp_max(red[lane]);
+      if (lane == 0) bcast[0] = t;
+    }
+    __syncthreads();
+    const float bm = bcast[0];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {  // 2^(-inf) = 0 for the padding beyond cols
+      v[i].x = exp2f((v[i].x - bm) * LOG2E); v[i].y = exp2f((v[i].y - bm) * LOG2E);
+      v[i].z = exp2f((v[i].z - bm) * LOG2E); v[i].w = exp2f((v[i].w - bm) * LOG2E);
+      s += v[i].x + v[i].y + v[i].z + v[i].w;
+    }
+    s = warp_sum(s);
+    if (lane == 0) red[warp] = s;   // all reads of red[] for the max finished before the barrier above
+    __syncthreads();
+    if (warp == 0) {
+      const float t = warp_sum(red[lane]);
+      if (lane == 0) bcast[1] = t;
+    }
+    __syncthreads();
+    const float tot = bcast[1];
+    if (threadIdx.x == 0) row_loss[r] = -(bcast[2] - bm - logf(tot)) * inv_count;
+    if (dz) {
+      const float k = inv_count / tot;
+      float4* dr = reinterpret_cast<float4*>(dz + r * cols);
+#pragma unroll
+      for (int i = 0; i < NV; i++) {
+        const int c4 = threadIdx.x + 1024 * i;
+        if (c4 * 4 < cols) {
+          float4 o = make_float4(v[i].x * k, v[i].y * k, v[i].z * k, v[i].w * k);
+          const int d = lab - c4 * 4;
+          if (d == 0) o.x -= inv_count; else if (d == 1) o.y -= inv_count; else if (d == 2) o.z -= inv_count; else if (d == 3) o.w -= inv_count;
+          dr[c4] = o;
+        }
+      }
+    }
+    __syncthreads();  // bcast / red are rewritten by the next row
+  }
+}
+
 __global__ void __launch_bounds__(256) mse_kernel(const float* __restrict__ p, const float* __restrict__ t, float* dp,
                                                   double* __restrict__ partial, long long n, float k) {
   __shared__ double red[8];
@@ -516,7 +588,14 @@ int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, fl
   int32_t rc = fml_ensure_workspace(ctx, (size_t)rows * sizeof(float));
   if (rc) return rc;
   float* row_loss = reinterpret_cast<float*>(ctx->ws);
-  xent_kernel<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+  if (cols >= 4096 && cols <= 32768 && cols % 4 == 0 && al16(z) && (!dz || al16(dz))) {
+    const int blocks = (int)std::max<long long>(1, std::min<long long>(rows, (long long)ctx->sm_count * 2));
+    if (cols <= 8192) xent_rowreg_kernel<2><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+    else if (cols <= 16384) xent_rowreg_kernel<4><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+    else xent_rowreg_kernel<8><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+  } else {
+    xent_kernel<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+  }
   final_sum_kernel<float><<<1, 256, 0, ctx->stream>>>(row_loss, rows, 1.0, loss_sum);
   FML_LAUNCH_CHECK(ctx, "xent_kernel");
   return FML_OK;

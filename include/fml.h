@@ -360,6 +360,16 @@ int32_t fml_tape_run(fml_ctx* ctx, const fml_op* ops, int32_t n_ops, int32_t dir
 /* opName string -> fml_op_kind, 0 if the executor does not know the name. */
 int32_t fml_tape_kind(const char* op_name);
 
+/* ---- checkpoints -----------------------------------------------------------------
+ * (No counterpart in the reference, which has no serialisation.)  One file holds named fp32 device buffers -
+ * parameter arena, optimizer state - plus a caller-defined step counter; every entry carries a CRC-32.  Load
+ * looks entries up by name, checks sizes and checksums BEFORE it overwrites anything, and may restore a subset.
+ * Both calls stage through pinned memory on a copy lane and return when the file / the buffers are complete. */
+int32_t fml_checkpoint_save(fml_ctx* ctx, const char* path, int64_t step, int32_t n, const char* const* names,
+                            const float* const* bufs, const int64_t* sizes);
+int32_t fml_checkpoint_load(fml_ctx* ctx, const char* path, int64_t* step, int32_t n, const char* const* names,
+                            float* const* bufs, const int64_t* sizes);
+
 /* ---- LSTM ---------------------------------------------------------------------
  * One layer over a batch of sequences (LSTMLayer.forward lib/layertypes/lstmLayer.dart:112-150).
  * W: 4 gate matrices [H x (H+I)] in order f,i,c~,o (:64) with columns [h_{t-1} | x_t] (:119),

@@ -195,7 +195,7 @@ def test_layernorm(ctx, orc, rows, cols, res):
     assert rel(dgam.numpy(), dg_ref) <= 1e-5 and rel(dbet.numpy(), db_ref) <= 1e-5
 
 
-@pytest.mark.parametrize("rows,cols", [(64, 10), (200, 1000), (16, 32000)])
+@pytest.mark.parametrize("rows,cols", [(64, 10), (200, 1000), (16, 32000), (301, 4100), (40, 12288), (9, 32768)])
 def test_softmax_xent(ctx, orc, rows, cols):
     rng = np.random.default_rng(cols)
     z = (2 * rng.standard_normal((rows, cols))).astype(np.float32)
