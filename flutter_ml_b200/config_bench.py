@@ -106,8 +106,10 @@ def config4_lstm(ctx):
         ctx.check(ctx.lib.fml_lstm_bwd(ctx.h, ctypes.byref(d), dh.ptr, dW.ptr, db.ptr, None, scratch.ptr))
         ctx.launches += 4 * Tn + 6
     ms, launches = _timed(ctx, step)
+    fwd_ms, _ = _timed(ctx, lambda: ctx.check(ctx.lib.fml_lstm_fwd(ctx.h, ctypes.byref(d))))
+    bwd_ms, _ = _timed(ctx, lambda: ctx.check(ctx.lib.fml_lstm_bwd(ctx.h, ctypes.byref(d), dh.ptr, dW.ptr, db.ptr, None, scratch.ptr)))
     flops = 1.546e11
-    return {"config": "C4 LSTM I256 H512 T128 B128 fwd+BPTT", "ms_per_step": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
+    return {"fwd_ms": round(fwd_ms, 3), "bwd_ms": round(bwd_ms, 3), "config": "C4 LSTM I256 H512 T128 B128 fwd+BPTT", "ms_per_step": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
             "us_per_timestep": round(ms * 1e3 / (2 * Tn), 1), "sequences_per_s": round(B / ms * 1e3, 1),
             "launches_per_step": launches}
 

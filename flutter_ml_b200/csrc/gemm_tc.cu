@@ -299,6 +299,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + RING_BYTES + 8 * (2 * MAX_STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  // let the next kernel of the stream be scheduled as SMs free up (it parks at its own griddepcontrol.wait)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader of the pair
@@ -332,6 +334,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: everything above (barrier init, TMEM allocation, the cluster handshake) touched
+  // no global memory and may run while the previous kernel of the stream is still finishing; from here on this
+  // kernel reads and writes tensors, so it first waits until that kernel has completed and its writes are visible.
+  // A no-op when the launch did not ask for the overlap.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int num_tiles = p.tiles_m * p.tiles_n * p.nb1 * p.nb2;
   const int num_units = num_tiles * p.ksplit;  // work units: (tile, K split)
@@ -668,17 +675,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (row < p.M) {
             const int H = p.N >> 2, r0 = col0 >> 2;
             const long long po = (long long)row * p.N + col0, ho = (long long)row * H + r0;
+            // all ten loads first: with the loads inside the loop below each one sat behind the previous
+            // iteration's store to `gates` (possible alias) and the block cost eight L2 round trips instead of one
             float cp[8];
+            float4 xa[8];
             *reinterpret_cast<float4*>(cp) = *reinterpret_cast<const float4*>(p.le.c_prev + ho);
             *reinterpret_cast<float4*>(cp + 4) = *reinterpret_cast<const float4*>(p.le.c_prev + ho + 4);
+#pragma unroll
+            for (int uu = 0; uu < 8; uu++) xa[uu] = *reinterpret_cast<const float4*>(p.le.addend + po + 4 * uu);
             float cn[8], hn[8];
 #pragma unroll
             for (int uu = 0; uu < 8; uu++) {
-              const float4 xa = *reinterpret_cast<const float4*>(p.le.addend + po + 4 * uu);
-              const float f = fml_sigmoid(__uint_as_float(v[4 * uu]) + xa.x);
-              const float i = fml_sigmoid(__uint_as_float(v[4 * uu + 1]) + xa.y);
-              const float g = fml_tanh_ref(__uint_as_float(v[4 * uu + 2]) + xa.z);
-              const float o = fml_sigmoid(__uint_as_float(v[4 * uu + 3]) + xa.w);
+              const float f = fml_sigmoid(__uint_as_float(v[4 * uu]) + xa[uu].x);
+              const float i = fml_sigmoid(__uint_as_float(v[4 * uu + 1]) + xa[uu].y);
+              const float g = fml_tanh_ref(__uint_as_float(v[4 * uu + 2]) + xa[uu].z);
+              const float o = fml_sigmoid(__uint_as_float(v[4 * uu + 3]) + xa[uu].w);
               cn[uu] = f * cp[uu] + i * g;
               hn[uu] = o * fml_tanh_ref(cn[uu]);
               *reinterpret_cast<float4*>(p.le.gates + po + 4 * uu) = make_float4(f, i, g, o);
@@ -1084,24 +1095,39 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     if ((rc = split_bytes ? fml_ensure_workspace_keep(ctx, off + slab_bytes) : fml_ensure_workspace(ctx, off + slab_bytes))) return rc;
     p.partial = reinterpret_cast<float*>(ctx->ws + off);
   }
+  static int pdl = -1;
+  if (pdl < 0) {
+    const char* e = getenv("FML_GEMM_PDL");
+    pdl = e ? atoi(e) : 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl) {  // this kernel's prologue may overlap the tail of the kernel queued before it
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    na++;
+  }
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.stream = ctx->stream;
+  cfg.attrs = attr;
   if (pair) {
     const int clusters = (int)std::min<long long>(num_tiles, ctx->sm_count / 2);
-    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * clusters);
-    cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 2;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    na++;
+    cfg.numAttrs = na;
     FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, p));
   } else {
     const int grid = (int)std::min<long long>(d->rowop ? num_tiles / tiles_n : num_tiles, ctx->sm_count);
-    gemm_tc_kernel<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, ctx->stream>>>(tmA, tmB, tmAlo, tmBlo, p);
+    cfg.gridDim = dim3(grid);
+    cfg.dynamicSmemBytes = Cfg<false>::SMEM_BYTES;
+    cfg.numAttrs = na;
+    FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, tmA, tmB, tmAlo, tmBlo, p));
   }
   FML_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
   ctx->last_gemm_path = 1;

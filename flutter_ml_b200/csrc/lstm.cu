@@ -55,15 +55,20 @@ __global__ void lstm_gates_fwd_kernel(const float* __restrict__ pre, const float
 }
 
 // dh, dc (in/out: becomes dc_{t-1}), saved gates (interleaved) and cells -> gradient of the pre-activations
-__global__ void lstm_gates_bwd_kernel(const float* __restrict__ dh, float* dc, const float* __restrict__ gates,
+__global__ void lstm_gates_bwd_kernel(float* __restrict__ dh, float* dc, const float* __restrict__ gates,
                                       const float* __restrict__ c_prev, const float* __restrict__ c_cur,
                                       float* __restrict__ dpre, int B, int H) {
+  // the recurrent product queued behind this kernel may set up (barriers, TMEM) while this one runs, and this
+  // kernel itself is launched while the previous product drains: it waits here for that product's dh
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int n = B * H;
   for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
     const float4 gt = reinterpret_cast<const float4*>(gates)[idx];
     const float f = gt.x, i = gt.y, g = gt.z, o = gt.w;
     const float tc = fml_tanh_ref(c_cur[idx]);
     const float dhv = dh[idx];
+    dh[idx] = 0.f;  // the product that follows ADDS dpre_t . Wh into dh (its K-split partial sums need a zeroed target)
     const float d_o = dhv * tc;
     const float dct = dc[idx] + dhv * o * (1.f - tc * tc);
     reinterpret_cast<float4*>(dpre)[idx] = make_float4(dct * c_prev[idx] * (f * (1.f - f)), dct * g * (i * (1.f - i)),
@@ -164,15 +169,27 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
   cudaMemcpyAsync(dh, dh_last, bh * 4, cudaMemcpyDeviceToDevice, ctx->stream);
   cudaMemsetAsync(dc, 0, bh * 4, ctx->stream);
   for (int t = T - 1; t >= 0 && rc == FML_OK; t--) {
-    lstm_gates_bwd_kernel<<<blocks_for(ctx, bh), 256, 0, ctx->stream>>>(dh, dc, d->gates + t * b4h, d->cells + t * bh,
-                                                                        d->cells + (t + 1) * bh, dpre + t * b4h, B, H);
+    {
+      cudaLaunchConfig_t cfg = {};
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.gridDim = dim3(blocks_for(ctx, bh));
+      cfg.blockDim = dim3(256);
+      cfg.stream = ctx->stream;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, lstm_gates_bwd_kernel, dh, dc, (const float*)(d->gates + t * b4h),
+                                       (const float*)(d->cells + t * bh), (const float*)(d->cells + (t + 1) * bh),
+                                       dpre + t * b4h, B, H));
+    }
     if (t > 0) {
       // dh_{t-1} = dpre_t . Wh   (Wh = columns 0..H-1 of the interleaved W)
       fml_gemm_desc r = gemm_defaults();
       r.M = B; r.N = H; r.K = 4 * H;
       r.A = dpre + t * b4h; r.lda = 4 * H;
       r.B = Wi; r.ldb = Z;
-      r.C = dh; r.ldc = H;
+      r.C = dh; r.ldc = H; r.beta = 1.f;  // dh was zeroed by the gate kernel above
       rc = fml_gemm(ctx, &r);
     }
   }
