@@ -117,6 +117,8 @@ PROTOTYPES = {
     "fml_optimizer_step": [fp, i32, fp, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, i32],
     "fml_act2_fwd": [fp, i32, f32, fp, fp, i64],
     "fml_act2_bwd": [fp, i32, f32, fp, fp, fp, i64, i32],
+    "fml_conv2d_fwd": [fp, fp, fp, fp, fp, i32, i32, i32, i32, i32, i32, i32],
+    "fml_conv2d_bwd": [fp, fp, fp, fp, fp, fp, fp, i32, i32, i32, i32, i32, i32, i32],
     "fml_checkpoint_save": [fp, C.c_char_p, i64, i32, fp, fp, fp],
     "fml_checkpoint_load": [fp, C.c_char_p, C.POINTER(i64), i32, fp, fp, fp],
     "fml_tape_run": [fp, C.POINTER(Op), i32, i32],

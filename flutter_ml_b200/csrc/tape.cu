@@ -42,6 +42,12 @@ __global__ void broadcast_add_dev_kernel(float* gin, const float* __restrict__ g
   const float g = gout[0];
   TP_LOOP(i, n) gin[i] += g;
 }
+// out = in + s[0]   (addScalarToMatrix, tensor.dart:711-723)
+__global__ void add_scalar_dev_kernel(const float* __restrict__ in, const float* __restrict__ s, float* __restrict__ out, long long n) {
+  const float v = s[0];
+  TP_LOOP(i, n) out[i] = in[i] + v;
+}
+__global__ void add_one_dev_kernel(float* y, const float* __restrict__ x) { y[0] += x[0]; }
 // part[r][c] += whole[r][off + c]   (concat backward, tensor.dart:443-449, 749-757)
 __global__ void split_add_kernel(float* part, const float* __restrict__ whole, long long rows, int pc, int ld, int off) {
   TP_LOOP(i, rows * pc) {
@@ -261,6 +267,16 @@ int32_t op_forward(fml_ctx* ctx, const fml_op& o, int idx) {
       FML_LAUNCH_CHECK(ctx, "sum_kernel");
       return FML_OK;
     }
+    case FML_OP_CONV2D: {
+      const int pad = (int)o.s, H = o.rows + o.inner - 1 - 2 * pad, W = o.cols + o.iparam - 1 - 2 * pad;
+      FML_REQUIRE(ctx, o.in[0] && o.in[1] && o.inner > 0 && o.iparam > 0 && pad >= 0 && H > 0 && W > 0, where + " (conv2d): bad input, kernel or padding");
+      return fml_conv2d_fwd(ctx, o.in[0], o.in[1], nullptr, o.out, 1, H, W, 1, o.inner, o.iparam, pad);
+    }
+    case FML_OP_ADD_SCALAR_TO_MATRIX:
+      FML_REQUIRE(ctx, o.in[0] && o.in[1], where + " (addScalarToMatrix): missing input");
+      add_scalar_dev_kernel<<<tp_blocks(ctx, n), TP_THREADS, 0, st>>>(o.in[0], o.in[1], o.out, n);
+      FML_LAUNCH_CHECK(ctx, "add_scalar_dev_kernel");
+      return FML_OK;
     case FML_OP_SOFTMAX_XENT: {
       FML_REQUIRE(ctx, o.in[0] && o.ids && o.aux[0] && o.inner > 0, where + " (softmax_xent): missing logits, labels or aux[0]");
       TP_TRY(fml_zero(ctx, o.out, 1));
@@ -373,6 +389,23 @@ int32_t op_backward(fml_ctx* ctx, const fml_op& o, int idx) {
         FML_LAUNCH_CHECK(ctx, "broadcast_add_dev_kernel");
       }
       return FML_OK;
+    case FML_OP_CONV2D: {
+      const int pad = (int)o.s, H = o.rows + o.inner - 1 - 2 * pad, W = o.cols + o.iparam - 1 - 2 * pad;
+      if (!o.gin[0] && !o.gin[1]) return FML_OK;
+      return fml_conv2d_bwd(ctx, o.in[0], o.in[1], o.gout, o.gin[0], o.gin[1], nullptr, 1, H, W, 1, o.inner, o.iparam, pad);
+    }
+    case FML_OP_ADD_SCALAR_TO_MATRIX:
+      TP_TRY(acc_into(ctx, o.gin[0], o.gout, n));
+      if (o.gin[1]) {  // s.grad += sum of out.grad (tensor.dart:729)
+        const int blocks = tp_blocks(ctx, n);
+        TP_TRY(fml_ensure_workspace(ctx, (size_t)(blocks + 1) * sizeof(double)));
+        double* part = reinterpret_cast<double*>(ctx->ws);
+        sum_partial_kernel<<<blocks, TP_THREADS, 0, st>>>(o.gout, part, n);
+        sum_final_kernel<<<1, TP_THREADS, 0, st>>>(part, blocks, reinterpret_cast<float*>(part + blocks));
+        add_one_dev_kernel<<<1, 1, 0, st>>>(o.gin[1], reinterpret_cast<const float*>(part + blocks));
+        FML_LAUNCH_CHECK(ctx, "add_scalar backward");
+      }
+      return FML_OK;
     case FML_OP_SOFTMAX_XENT:
       if (o.gin[0]) {
         const long long m = (long long)o.inner * o.iparam;
@@ -397,7 +430,7 @@ const KindName KIND_NAMES[] = {
     {"concat_matrix_col", FML_OP_CONCAT}, {"concat_vector", FML_OP_CONCAT}, {"softmax_matrix", FML_OP_SOFTMAX_MATRIX},
     {"softmax", FML_OP_SOFTMAX_MATRIX}, {"layer_norm", FML_OP_LAYER_NORM}, {"layer_norm_vector", FML_OP_LAYER_NORM},
     {"embedding_lookup", FML_OP_EMBEDDING_LOOKUP}, {"mse_matrix", FML_OP_MSE}, {"mse_vector", FML_OP_MSE},
-    {"sum_matrix", FML_OP_SUM}, {"sum_vector", FML_OP_SUM}, {"softmax_xent", FML_OP_SOFTMAX_XENT}, {"dense", FML_OP_DENSE},
+    {"conv2d", FML_OP_CONV2D}, {"addScalarToMatrix", FML_OP_ADD_SCALAR_TO_MATRIX}, {"sum_matrix", FML_OP_SUM}, {"sum_vector", FML_OP_SUM}, {"softmax_xent", FML_OP_SOFTMAX_XENT}, {"dense", FML_OP_DENSE},
     {"dense_matrix", FML_OP_DENSE}};
 
 }  // namespace

@@ -78,6 +78,38 @@ class DenseLayerMatrix(Layer):
         return T.denseMatrix(x, self.weights, self.biases, self.activation, self.precision)
 
 
+class Conv2DLayer(Layer):
+    """lib/layertypes/conv2d.dart:11-75: `outChannels` square kernels over a single-channel input, one scalar bias
+    each, padding 'valid' or 'same'.  The reference keeps a list of kernel matrices; here they are the rows of one
+    [outChannels x kernelSize^2] tensor so that the layer is one launch.  Input [n_img, H, W] -> output [n_img, outChannels, OH, OW]; a single matrix [H, W]
+    -> [outChannels, OH, OW] like the reference's Tensor3D.  Initial kernels uniform(+-sqrt(2 / k^2)) as conv2d.dart:37-45, biases 0."""
+
+    name = "conv2d_layer"
+
+    def __init__(self, outChannels: int, kernelSize: int, padding: str = "valid", seed: int = 0, kernels=None, biases=None):
+        super().__init__()
+        self.outChannels, self.kernelSize, self.padding, self.seed = outChannels, kernelSize, padding, seed
+        self._k0, self._b0 = kernels, biases
+        self.kernels: Optional[Tensor] = None
+        self.biases: Optional[Tensor] = None
+
+    @property
+    def parameters(self):
+        return [self.kernels, self.biases]
+
+    def build(self, x: Tensor):
+        k2 = self.kernelSize * self.kernelSize
+        a = math.sqrt(2.0 / k2)
+        k = self._k0 if self._k0 is not None else synth.uniform(self.seed, 0, (self.outChannels, k2), -a, a)
+        b = self._b0 if self._b0 is not None else np.zeros(self.outChannels, dtype=np.float32)
+        self.kernels = Tensor(np.asarray(k, dtype=np.float32).reshape(self.outChannels, k2), x.ctx)
+        self.biases = Tensor(b, x.ctx)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return T.conv2dBatch(x, self.kernels, self.biases, self.kernelSize, self.kernelSize, self.padding)
+
+
 class LayerNormalization(Layer):
     """lib/transformer/layerNormalization.dart:11-44: gamma = 1, beta = 0, epsilon = 1e-5."""
 

@@ -22,7 +22,7 @@ from . import _lib
 KIND = {"matMul": 1, "matVecMul": 2, "addMatrixAndVector": 3, "add": 4, "multiply": 5, "relu": 6, "sigmoid": 7,
         "tanh": 8, "gelu": 9, "leaky_relu": 10, "elu": 11, "swish": 12, "mish": 13, "scale_matrix": 14,
         "transpose": 15, "concat": 16, "softmax_matrix": 17, "layer_norm": 18, "embedding_lookup": 19, "mse": 20,
-        "sum": 21, "softmax_xent": 22, "dense": 23}
+        "sum": 21, "softmax_xent": 22, "dense": 23, "conv2d": 24, "addScalarToMatrix": 25}
 FORWARD, BACKWARD, BACKWARD_NOSEED = 0, 1, 2
 
 
@@ -166,6 +166,15 @@ class Tape:
         return self._record("sum", self._new(1, 1), (x,), inner=x.rows * x.cols)
 
     sum = sumMatrix
+
+    def conv2d(self, x, kernel, padding: str = "valid"):   # tensor.dart:765-833, extraParams {'padding': ...}
+        pad = (kernel.rows - 1) // 2 if padding == "same" else 0
+        out = self._new(x.rows + 2 * pad - kernel.rows + 1, x.cols + 2 * pad - kernel.cols + 1)
+        return self._record("conv2d", out, (x, kernel), inner=kernel.rows, iparam=kernel.cols, s=pad)
+
+    def addScalarToMatrix(self, m, s):            # tensor.dart:711-737 (s is a 1 x 1 tensor)
+        assert s.shape == (1, 1)
+        return self._record("addScalarToMatrix", self._new(m.rows, m.cols), (m, s))
 
     def softmaxCrossEntropy(self, logits, labels, inv_count):   # extension
         aux = (self.ctx.empty(logits.rows, logits.cols),)

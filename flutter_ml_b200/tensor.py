@@ -461,6 +461,31 @@ def attentionCore(qkv: Tensor, n_seq: int, seq_len: int, heads: int, d_head: int
     return out
 
 
+def conv2dBatch(x: Tensor, kernels: Tensor, biases: Optional[Tensor], kh: int, kw: int, padding: str = "valid") -> Tensor:
+    """conv2d (tensor.dart:765-833) of every image in x [n_img, H, W] with every kernel in `kernels`
+    [n_k, kh*kw] (x may also be one matrix [H, W]), plus addScalarToMatrix of `biases` [n_k] (tensor.dart:711-737): Conv2DLayer.forward
+    (lib/layertypes/conv2d.dart:60-75) as one launch.  Output [n_img, n_k, OH, OW]."""
+    ctx = x.ctx
+    single = len(x.shape) == 2   # one matrix, as in the reference
+    n_img, H, W = (1,) + tuple(x.shape) if single else x.shape
+    n_k = kernels.shape[0]
+    pad = (kh - 1) // 2 if padding == "same" else 0
+    OH, OW = H + 2 * pad - kh + 1, W + 2 * pad - kw + 1
+    out = Tensor(ctx.empty(*((n_k, OH, OW) if single else (n_img, n_k, OH, OW))), ctx)
+    args = (n_img, H, W, n_k, kh, kw, pad)
+    ctx.call("fml_conv2d_fwd", x.value, kernels.value, biases.value if biases is not None else None, out.value, *args)
+
+    def bw():
+        for t in (x, kernels, biases):
+            if t is not None and t.grad is None:
+                t.zeroGrad()   # the backward kernels add into their targets
+        ctx.call("fml_conv2d_bwd", x.value, kernels.value, out.grad, x.grad, kernels.grad,
+                 biases.grad if biases is not None else None, *args, launches=2)
+    out.creator = Node([x, kernels] + ([biases] if biases is not None else []), bw, "conv2d", 2 * n_img * n_k * OH * OW * kh * kw,
+                       {"padding": padding})
+    return out
+
+
 # --------------------------------------------------------------------------------- losses
 
 

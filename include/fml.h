@@ -324,6 +324,9 @@ int32_t fml_act2_bwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, co
  *   sum_matrix, sum_vector   out 1 x 1 = sum of the inner elements of in0      tensor.dart:561-579, 1153-1176
  *   softmax_xent (extension) in0 = logits [inner x iparam], ids = labels, s = 1/count, out 1 x 1; aux0
  *                       [inner x iparam] keeps the gradient between the sweeps
+ *   conv2d              out[r x c] = in0 (image) cross-correlated with in1 (kernel, inner x iparam taps),
+ *                       s = padding on every side (0 'valid', (inner - 1) / 2 'same')  tensor.dart:765-833
+ *   addScalarToMatrix   out = in0 + in1[0] (in1 is 1 x 1)                      tensor.dart:711-737
  *   dense (extension)   out = act(in0[r x inner] . in1[inner x c] + in2), iparam = fml_act, aux0 = pre-activation
  *                       buffer for GELU: matMul + addMatrixAndVector + activation of
  *                       DenseLayerMatrix.forward (denseLayer.dart:116-125) as one launch; its backward rule
@@ -333,7 +336,7 @@ typedef enum {
   FML_OP_RELU = 6, FML_OP_SIGMOID = 7, FML_OP_TANH = 8, FML_OP_GELU = 9, FML_OP_LEAKY_RELU = 10, FML_OP_ELU = 11,
   FML_OP_SWISH = 12, FML_OP_MISH = 13, FML_OP_SCALE_MATRIX = 14, FML_OP_TRANSPOSE = 15, FML_OP_CONCAT = 16,
   FML_OP_SOFTMAX_MATRIX = 17, FML_OP_LAYER_NORM = 18, FML_OP_EMBEDDING_LOOKUP = 19, FML_OP_MSE = 20, FML_OP_SUM = 21,
-  FML_OP_SOFTMAX_XENT = 22, FML_OP_DENSE = 23
+  FML_OP_SOFTMAX_XENT = 22, FML_OP_DENSE = 23, FML_OP_CONV2D = 24, FML_OP_ADD_SCALAR_TO_MATRIX = 25
 } fml_op_kind;
 typedef enum { FML_TAPE_FORWARD = 0, FML_TAPE_BACKWARD = 1, FML_TAPE_BACKWARD_NOSEED = 2 } fml_tape_direction;
 
@@ -359,6 +362,16 @@ typedef struct fml_op {
 int32_t fml_tape_run(fml_ctx* ctx, const fml_op* ops, int32_t n_ops, int32_t direction);
 /* opName string -> fml_op_kind, 0 if the executor does not know the name. */
 int32_t fml_tape_kind(const char* op_name);
+
+/* ---- convolution -----------------------------------------------------------------
+ * conv2d (tensor.dart:765-833) for every kernel of a Conv2DLayer (lib/layertypes/conv2d.dart:60-75) and every image
+ * of a batch in one launch: in [n_img][H][W], w [n_k][kh][kw], bias [n_k] or NULL (addScalarToMatrix,
+ * tensor.dart:711-737), out [n_img][n_k][OH][OW] with OH = H + 2 pad - kh + 1.  pad = 0 is 'valid', (kh - 1) / 2
+ * is 'same'.  Backward ADDS into din / dw / dbias (NULL skips one), padded positions contribute nothing. */
+int32_t fml_conv2d_fwd(fml_ctx* ctx, const float* in, const float* w, const float* bias, float* out, int32_t n_img,
+                       int32_t H, int32_t W, int32_t n_k, int32_t kh, int32_t kw, int32_t pad);
+int32_t fml_conv2d_bwd(fml_ctx* ctx, const float* in, const float* w, const float* dout, float* din, float* dw,
+                       float* dbias, int32_t n_img, int32_t H, int32_t W, int32_t n_k, int32_t kh, int32_t kw, int32_t pad);
 
 /* ---- checkpoints -----------------------------------------------------------------
  * (No counterpart in the reference, which has no serialisation.)  One file holds named fp32 device buffers -

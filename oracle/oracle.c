@@ -567,3 +567,36 @@ void orc_lstm_fwd_bwd(const double* W, const double* b, const double* x, const d
   free(losses);
   *loss_out = loss;
 }
+
+/* conv2d lib/autogradEngine/tensor.dart:765-833: one input matrix [H x W], one kernel [kh x kw], cross-correlation
+ * (no kernel flip); padding 'same' pads (kh - 1) / 2 zeros on every side (:773-776, integer division), so the
+ * output is [H + 2p - kh + 1] x [W + 2p - kw + 1].  Loop order y, x, ky, kx as the reference. */
+void orc_conv2d_fwd(const double* in, const double* k, double* out, int H, int W, int kh, int kw, int pad) {
+  const int OH = H + 2 * pad - kh + 1, OW = W + 2 * pad - kw + 1;
+  for (int y = 0; y < OH; y++)
+    for (int x = 0; x < OW; x++) {
+      double sum = 0;
+      for (int ky = 0; ky < kh; ky++)
+        for (int kx = 0; kx < kw; kx++) {
+          const int iy = y + ky - pad, ix = x + kx - pad;
+          const double v = (iy < 0 || iy >= H || ix < 0 || ix >= W) ? 0.0 : in[(size_t)iy * W + ix];
+          sum += v * k[ky * kw + kx];
+        }
+      out[(size_t)y * OW + x] = sum;
+    }
+}
+/* closure :808-826: input.grad += kernel * out.grad, kernel.grad += padded input * out.grad; positions in the
+ * padding are skipped for BOTH gradients (the `continue` at :813-818). */
+void orc_conv2d_bwd(const double* in, const double* k, const double* dout, double* din, double* dk, int H, int W,
+                    int kh, int kw, int pad) {
+  const int OH = H + 2 * pad - kh + 1, OW = W + 2 * pad - kw + 1;
+  for (int y = 0; y < OH; y++)
+    for (int x = 0; x < OW; x++)
+      for (int ky = 0; ky < kh; ky++)
+        for (int kx = 0; kx < kw; kx++) {
+          const int iy = y + ky - pad, ix = x + kx - pad;
+          if (iy < 0 || iy >= H || ix < 0 || ix >= W) continue;
+          din[(size_t)iy * W + ix] += k[ky * kw + kx] * dout[(size_t)y * OW + x];
+          dk[ky * kw + kx] += in[(size_t)iy * W + ix] * dout[(size_t)y * OW + x];
+        }
+}

@@ -144,6 +144,16 @@ class Ops:
     def act2_bwd(self, kind, alpha, x, dy, dx):
         self.L.orc_act2_bwd(int(kind), C.c_double(alpha), _p(x), _p(dy), _p(dx), C.c_int64(x.size))
 
+    def conv2d_fwd(self, x, k, pad):
+        H, W = x.shape
+        kh, kw = k.shape
+        out = np.empty((H + 2 * pad - kh + 1, W + 2 * pad - kw + 1))
+        self.L.orc_conv2d_fwd(_p(x), _p(k), _p(out), H, W, kh, kw, pad)
+        return out
+
+    def conv2d_bwd(self, x, k, dout, dx, dk, pad):
+        self.L.orc_conv2d_bwd(_p(x), _p(k), _p(dout), _p(dx), _p(dk), x.shape[0], x.shape[1], k.shape[0], k.shape[1], pad)
+
     def embedding_fwd(self, table, ids):
         ids = np.ascontiguousarray(ids, dtype=np.float64)
         out = np.empty((ids.size, table.shape[1]))
@@ -320,6 +330,21 @@ class Engine:
     def embedding(self, table, ids):
         out = T(self.ops.embedding_fwd(table.value, ids))
         return _node(out, [table], lambda: self.ops.embedding_bwd(out.grad, ids, table.grad))
+
+    # tensor.dart:765-833; padding 'valid' or 'same'
+    def conv2d(self, x, k, padding="valid"):
+        pad = (k.value.shape[0] - 1) // 2 if padding == "same" else 0
+        out = T(self.ops.conv2d_fwd(x.value, k.value, pad))
+        return _node(out, [x, k], lambda: self.ops.conv2d_bwd(x.value, k.value, out.grad, x.grad, k.grad, pad))
+
+    # tensor.dart:711-737: m + s for a scalar tensor s; s.grad += sum of out.grad
+    def addScalarToMatrix(self, m, s):
+        out = T(m.value + float(np.asarray(s.value).reshape(-1)[0]))
+
+        def bw():
+            m.grad += out.grad
+            s.grad += out.grad.sum()
+        return _node(out, [m, s], bw)
 
     # tensor.dart:949-980
     def matVecMul(self, M, v):

@@ -240,3 +240,43 @@ def test_dense_net_with_other_activations_and_optimizers(orc, act, opt_name):
     for p, r in zip(params, ref):
         assert rel(p.numpy(), r) <= 2e-5
     ctx.close()
+
+
+@pytest.mark.parametrize("padding", ["valid", "same"])
+def test_conv2d_layer_batched(orc, padding):
+    """Conv2DLayer (lib/layertypes/conv2d.dart:60-75) over a batch of images in one launch: every feature map and
+    every gradient against per-image, per-kernel conv2d + addScalarToMatrix on the oracle's tape."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200.layers import Conv2DLayer
+    from flutter_ml_b200.tensor import Tensor, mseMatrix, set_default_context
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    set_default_context(ctx)
+    rng = np.random.default_rng(4)
+    n_img, H, W, n_k, k = 5, 20, 33, 6, 3
+    X = rng.standard_normal((n_img, H, W)).astype(np.float32)
+    Kn = (rng.standard_normal((n_k, k * k)) * 0.5).astype(np.float32)
+    Bv = rng.standard_normal(n_k).astype(np.float32)
+    layer = Conv2DLayer(n_k, k, padding, kernels=Kn, biases=Bv)
+    x = Tensor(X, ctx)
+    out = layer(x)
+    target = np.zeros(out.shape, np.float32)
+    loss = mseMatrix(out, Tensor(target, ctx))
+    loss.backward()
+    E = orc.Engine()
+    ok = [orc.T(Kn[c].reshape(k, k).astype(np.float64)) for c in range(n_k)]
+    ob = [orc.T(np.float64(Bv[c])) for c in range(n_k)]
+    ox = [orc.T(X[b].astype(np.float64)) for b in range(n_img)]
+    maps = [[E.addScalarToMatrix(E.conv2d(ox[b], ok[c], padding), ob[c]) for c in range(n_k)] for b in range(n_img)]
+    ref = np.stack([np.stack([m.value for m in row]) for row in maps])
+    assert rel(out.numpy(), ref) <= 2e-6
+    # d(mean over all elements of out^2): seed every map with its slice of the gradient and run its closures
+    for b in range(n_img):
+        for c in range(n_k):
+            m = maps[b][c]
+            m.grad = 2.0 * m.value / ref.size
+            m.backward_fn()                 # addScalarToMatrix
+            m.inputs[0].backward_fn()       # conv2d
+    assert rel(x.grad_numpy(), np.stack([t.grad for t in ox])) <= 1e-5
+    assert rel(layer.kernels.grad_numpy(), np.stack([t.grad.ravel() for t in ok])) <= 1e-5
+    assert rel(layer.biases.grad_numpy(), np.array([float(t.grad) for t in ob])) <= 1e-5
+    ctx.close()

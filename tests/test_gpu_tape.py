@@ -257,3 +257,77 @@ def test_tape_training_step_with_flat_parameter_arena(orc):
     for p, r in zip(P, ref):
         assert rel(p.numpy().reshape(r.shape), r) <= 1e-5
     ctx.close()
+
+
+def test_multi_tier_lstm_variant_as_a_tape(orc, fp32_ctx):
+    """MultiTierLSTMLayer.forward (lib/layertypes/multilstm.dart:100-150): tier 0 sees [h_0, c_1, x_t] every
+    step, tier 1 sees [h_1, h_0] every second step.  The variant needs no kernel of its own: it is a list of the
+    same vector-form nodes, so it runs on the tape executor as it stands."""
+    from flutter_ml_b200.tape import Tape
+    I, H, Tn, cycle = 3, 10, 4, 2
+    rng = np.random.default_rng(31)
+    f = lambda *s: (rng.standard_normal(s) * 0.4).astype(np.float32)
+    sizes = [H + H + I, H + H]       # combined input of tier 0 and tier 1
+    Ws = [[f(H, n) for _ in range(4)] for n in sizes]
+    bs = [[f(H) for _ in range(4)] for _ in sizes]
+    xs, target = [f(I) for _ in range(Tn)], f(H)
+
+    def run(E, mk, vec):
+        W = [[mk(w) for w in tier] for tier in Ws]
+        b = [[mk(v) for v in tier] for tier in bs]
+        h = [mk(np.zeros(H, np.float32)) for _ in sizes]
+        c = [mk(np.zeros(H, np.float32)) for _ in sizes]
+
+        def step(z, c_prev, t):
+            gate = lambda k, fn: fn(vec.add(E.matVecMul(W[t][k], z), b[t][k]))
+            f_t, i_t, c_t = gate(0, vec.sigmoid), gate(1, vec.sigmoid), gate(2, vec.tanh)
+            c_next = vec.add(E.elementWiseMultiply(f_t, c_prev), E.elementWiseMultiply(i_t, c_t))
+            return E.elementWiseMultiply(gate(3, vec.sigmoid), vec.tanh(c_next)), c_next
+        for g, x in enumerate(xs):
+            h[0], c[0] = step(E.concatenate(E.concatenate(h[0], c[1]), mk(x)), c[0], 0)
+            if (g + 1) % cycle == 0:
+                h[1], c[1] = step(E.concatenate(h[1], h[0]), c[1], 1)
+        return vec.mse(h[0], mk(target)), h[0], [w for tier in W for w in tier] + [v for tier in b for v in tier]
+
+    E = orc.Engine()
+
+    class OV:
+        add, sigmoid, tanh = staticmethod(E.addMatrix), staticmethod(E.sigmoidMatrix), staticmethod(E.tanhMatrix)
+        mse = staticmethod(E.mseMatrix)
+    oloss, oh, oparams = run(E, lambda a: orc.T(w64(a)), OV)
+    oloss.backward()
+    tp = Tape(fp32_ctx)
+
+    class TV:
+        add, sigmoid, tanh, mse = tp.addVector, tp.sigmoid, tp.vectorTanh, tp.mse
+    tloss, th, tparams = run(tp, tp.tensor, TV)
+    tp.forward()
+    tp.backward()
+    assert rel(th.numpy().ravel(), oh.value) <= 2e-6
+    assert abs(float(tloss.numpy()[0, 0]) - float(oloss.value)) <= 2e-6 * float(oloss.value)
+    for t, o in zip(tparams, oparams):
+        assert rel(t.grad_numpy().reshape(o.grad.shape), o.grad) <= 1e-5
+
+
+@pytest.mark.parametrize("padding,kh,kw", [("valid", 3, 3), ("same", 3, 3), ("same", 5, 5), ("valid", 2, 4)])
+def test_conv2d_on_the_tape(orc, fp32_ctx, padding, kh, kw):
+    """conv2d + addScalarToMatrix nodes (tensor.dart:765-833, 711-737) against the oracle, gradients of image,
+    kernel and scalar bias; the image feeds two convolutions, so its gradient also tests the += of the rule."""
+    from flutter_ml_b200.tape import Tape
+    rng = np.random.default_rng(kh * 10 + kw)
+    x, k1, k2, bias = (rng.standard_normal(s).astype(np.float32) for s in ((13, 17), (kh, kw), (kh, kw), (1, 1)))
+    E = orc.Engine()
+    ox, ok1, ok2, ob = orc.T(w64(x)), orc.T(w64(k1)), orc.T(w64(k2)), orc.T(w64(bias[0, 0]))
+    oo = E.addMatrix(E.addScalarToMatrix(E.conv2d(ox, ok1, padding), ob), E.conv2d(ox, ok2, padding))
+    ol = E.mseMatrix(oo, orc.T(np.zeros_like(oo.value)))
+    ol.backward()
+    tp = Tape(fp32_ctx)
+    tx, tk1, tk2, tb = tp.tensor(x), tp.tensor(k1), tp.tensor(k2), tp.tensor(bias)
+    to = tp.addMatrix(tp.addScalarToMatrix(tp.conv2d(tx, tk1, padding), tb), tp.conv2d(tx, tk2, padding))
+    tl = tp.mseMatrix(to, tp.tensor(np.zeros(to.shape, np.float32), requires_grad=False))
+    tp.forward()
+    tp.backward()
+    assert to.shape == oo.value.shape
+    assert rel(to.numpy(), oo.value) <= 2e-6
+    for t, o in ((tx, ox), (tk1, ok1), (tk2, ok2), (tb, ob)):
+        assert rel(t.grad_numpy().reshape(np.shape(o.grad)), o.grad) <= 1e-5

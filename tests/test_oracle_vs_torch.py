@@ -299,3 +299,23 @@ def test_vector_form_tape_ops(orc):
     assert abs(float(out.value) - float(tout)) <= 1e-12 * abs(float(tout))
     for o, t in ((oW1, tW1), (oW2, tW2), (ob, tb), (oh, th), (ox, tx)):
         assert rel(o.grad, t.grad.numpy()) <= TOL
+
+
+@pytest.mark.parametrize("padding,kh", [("valid", 3), ("same", 3), ("same", 5), ("valid", 1), ("same", 4)])
+def test_conv2d(orc, padding, kh):
+    """conv2d (tensor.dart:765-833) against torch's cross-correlation; 'same' with an even kernel pads (k-1)//2 on
+    every side like the reference, so the output shrinks by one."""
+    rng = np.random.default_rng(kh)
+    x, k, bias = rng.standard_normal((9, 11)), rng.standard_normal((kh, kh)), rng.standard_normal(())
+    E = orc.Engine()
+    ox, ok, ob = orc.T(x), orc.T(k), orc.T(bias)
+    out = E.addScalarToMatrix(E.conv2d(ox, ok, padding), ob)
+    loss = E.mseMatrix(out, orc.T(np.zeros_like(out.value)))
+    loss.backward()
+    tx, tk, tb = tt(x), tt(k), tt(bias)
+    pad = (kh - 1) // 2 if padding == "same" else 0
+    tout = torch.nn.functional.conv2d(tx[None, None], tk[None, None], padding=pad)[0, 0] + tb
+    (tout ** 2).mean().backward()
+    assert rel(out.value, tout.detach().numpy()) <= TOL
+    for o, t in ((ox, tx), (ok, tk), (ob, tb)):
+        assert rel(o.grad, t.grad.numpy()) <= TOL
