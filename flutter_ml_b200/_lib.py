@@ -47,6 +47,11 @@ class LstmDesc(C.Structure):
                 ("gates", fp), ("cells", fp), ("hs", fp), ("xproj", fp)]
 
 
+class AttentionDesc(C.Structure):
+    _fields_ = [("n_seq", i32), ("seq_len", i32), ("heads", i32), ("d_head", i32), ("q", fp), ("k", fp), ("v", fp),
+                ("ld_qkv", i64), ("out", fp), ("ld_out", i64), ("lse", fp), ("scale", f32), ("causal", i32)]
+
+
 class Op(C.Structure):
     """fml_op: one autograd node of a tape handed to fml_tape_run."""
     _fields_ = [("kind", i32), ("rows", i32), ("cols", i32), ("inner", i32), ("inp", fp * 3), ("gin", fp * 3),
@@ -117,6 +122,8 @@ PROTOTYPES = {
     "fml_optimizer_step": [fp, i32, fp, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, i32],
     "fml_act2_fwd": [fp, i32, f32, fp, fp, i64],
     "fml_act2_bwd": [fp, i32, f32, fp, fp, fp, i64, i32],
+    "fml_attention_fwd": [fp, C.POINTER(AttentionDesc)],
+    "fml_attention_bwd": [fp, C.POINTER(AttentionDesc), fp, i64, fp, fp, fp, i64, i32, fp],
     "fml_conv2d_fwd": [fp, fp, fp, fp, fp, i32, i32, i32, i32, i32, i32, i32],
     "fml_conv2d_bwd": [fp, fp, fp, fp, fp, fp, fp, i32, i32, i32, i32, i32, i32, i32],
     "fml_checkpoint_save": [fp, C.c_char_p, i64, i32, fp, fp, fp],

@@ -1,0 +1,748 @@
+// Fused scaled-dot-product attention forward on the tensor cores: for one block of 128 queries of one
+// (sequence, head) the kernel walks the key/value blocks, S = Q.K^T lands in TMEM, four softmax warps turn it into
+// probabilities with a running row maximum and row sum (scale and causal mask folded in, base-2 exponentials),
+// write them to shared memory in the tensor core's K-major operand layout, and a second product P.V accumulates the
+// output.  The score matrix never reaches global memory: the reference's transpose + matMul + scaleMatrix +
+// softmaxMatrix + matMul chain (lib/layertypes/singleHeadAttentionLayer.dart:77-86) becomes one pass over Q, K, V.
+//
+// One CTA = 192 threads:
+//   warp 0      TMA producer: Q once, then K_j / V_j through a two-stage ring
+//   warp 1      MMA issuer: S_j = Q.K_j^T (into one of two TMEM buffers, so S_{j+1} overlaps the softmax of S_j),
+//               then PV_j = P_j.V_j once the softmax warps have published P_j
+//   warps 2..5  softmax: thread = one query row (TMEM lane); keeps the running max m, the running sum l and the 64
+//               output values of its row in registers: O = O * 2^(m_old - m_new) + PV_j
+// Shared memory (224 KiB): Q 32 KiB, 2 x K 32 KiB, 2 x V 32 KiB, P 64 KiB.  TMEM: S0 [0,128), S1 [128,256), PV [256,320).
+// V is consumed as an MN-major B operand (32-byte-atom swizzle, the layout notes of gemm_tc.cu apply).
+// Requirements: d_head = 64, seq_len a multiple of 128, 16-byte aligned rows.  Every mbarrier wait is bounded.
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+int32_t fml_tc_make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, int64_t ld, int64_t nb1, int64_t nb2,
+                         int64_t s1, int64_t s2, int box_c, int box_r, bool mn_major, int blocks, CUtensorMap* out);
+
+using namespace fml_tc;
+
+namespace {
+
+constexpr int BQ = 128, BKV = 128, DH = 64;
+constexpr int FA_THREADS = 192;
+constexpr uint32_t OFF_Q = 0, OFF_K = 32768, OFF_V = 98304, OFF_P = 163840, OFF_BAR = 229376;
+constexpr int FA_SMEM = OFF_BAR + 256 + 1024;
+constexpr uint32_t TM_S = 0, TM_PV = 256;
+
+struct FaParams {
+  int S, H, n_qb;        // sequence length, heads, query blocks per sequence
+  int causal;
+  float k2;              // scale * log2(e)
+  float* out; long long ld_out;
+  float* lse;            // [n_seq][H][S]: m + log2(l) of every row in the scaled base-2 domain, or NULL
+  int* status;
+};
+
+enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KVEMPTY = 5, B_SFULL = 7, B_SEMPTY = 9, B_PFULL = 11, B_PVFULL = 12, B_COUNT = 13 };
+
+__device__ __forceinline__ uint32_t fa_idesc(int M, int N, int a_mn, int b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a_mn & 1) << 15) | ((uint32_t)(b_mn & 1) << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  auto bar = [&](int i) { return smem_base + OFF_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + 8 * B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item: heavy (late) query blocks first, so the causal triangle balances over the grid
+  const int qb = p.n_qb - 1 - (int)(blockIdx.x % p.n_qb);
+  const int bh = blockIdx.x / p.n_qb;
+  const int h = bh % p.H, b = bh / p.H;
+  const int n_kv = p.causal ? qb + 1 : p.S / BKV;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < B_COUNT; i++) {
+      const bool from_softmax = (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL);
+      mbar_init(bar(i), from_softmax ? 128u : 1u);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      mbar_expect_tx(bar(B_QFULL), BQ * DH * 4);
+      for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + kb * 16384, &tmQ, bar(B_QFULL), kb * 32, qb * BQ, h, b);
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; j++) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        ok = mbar_wait(bar(B_KVEMPTY + s), ph ^ 1u, abort_flag, p.status, 11);
+        if (!ok) break;
+        mbar_expect_tx(bar(B_KFULL + s), BKV * DH * 4);
+        for (int kb = 0; kb < 2; kb++)
+          tma_load_4d(smem_base + OFF_K + s * 32768 + kb * 16384, &tmK, bar(B_KFULL + s), kb * 32, j * BKV, h, b);
+        mbar_expect_tx(bar(B_VFULL + s), BKV * DH * 4);
+        for (int c = 0; c < 4; c++)
+          tma_load_5d(smem_base + OFF_V + s * 32768 + c * 8192, &tmV, bar(B_VFULL + s), 0, j * BKV + 32 * c, 0, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = fa_idesc(BQ, BKV, 0, 0), idesc_pv = fa_idesc(BQ, DH, 0, 1);
+      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, p.status, 12);
+      auto issue_s = [&](int j) {  // S_j = Q . K_j^T into buffer j & 1
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(bar(B_KFULL + s), ph, abort_flag, p.status, 13)) return false;
+        if (!mbar_wait(bar(B_SEMPTY + s), ph ^ 1u, abort_flag, p.status, 14)) return false;
+        tc_fence_after();
+        for (int kb = 0; kb < 2; kb++) {
+          const uint64_t ad = make_smem_desc(smem_base + OFF_Q + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bd = make_smem_desc(smem_base + OFF_K + s * 32768 + kb * 16384, 16u, 1024u, 2u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + s * 128, ad + 2u * k, bd + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+        }
+        umma_commit(bar(B_SFULL + s));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; j++) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (j + 1 < n_kv) ok = issue_s(j + 1);
+        if (!ok) break;
+        ok = mbar_wait(bar(B_PFULL), (uint32_t)j & 1u, abort_flag, p.status, 15) &&
+             mbar_wait(bar(B_VFULL + s), ph, abort_flag, p.status, 16);
+        if (!ok) break;
+        tc_fence_after();
+        for (int c = 0; c < 4; c++) {  // 32 keys per chunk
+          const uint64_t ad = make_smem_desc(smem_base + OFF_P + c * 16384, 16u, 1024u, 2u);
+          const uint64_t bd = make_smem_desc(smem_base + OFF_V + s * 32768 + c * 8192, 4096u, 512u, 1u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_PV, ad + 2u * k, bd + 64u * k, idesc_pv, (c | k) ? 1u : 0u);
+        }
+        umma_commit(bar(B_PVFULL));       // PV_j readable, P free again
+        umma_commit(bar(B_KVEMPTY + s));  // K_j and V_j consumed
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / output
+    const int q4 = warp & 3;                        // TMEM lane quarter of this warp
+    const int row = q4 * 32 + lane;                 // row inside the query block
+    const int qi = qb * BQ + row;                   // position in the sequence
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+    float m = -INFINITY, l = 0.f;
+    float o[DH];
+#pragma unroll
+    for (int i = 0; i < DH; i++) o[i] = 0.f;
+    bool ok = true;
+    uint32_t v[32];
+    for (int j = 0; j < n_kv && ok; j++) {
+      const int s = j & 1;
+      ok = mbar_wait(bar(B_SFULL + s), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, 17);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diag = p.causal && j == qb;
+      const int lim = diag ? row + 1 : BKV;        // valid keys of this row inside the block
+      // pass 1: row maximum of the scaled scores
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 128 dependent maxima
+      for (int c = 0; c < 4; c++) {
+        tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          const float sc = (c * 32 + e < lim) ? __uint_as_float(v[e]) : -INFINITY;
+          mx4[e & 3] = fmaxf(mx4[e & 3], sc);
+        }
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.k2;   // k2 > 0: max commutes with the scale
+      const float m_new = fmaxf(m, mx);            // finite: key 0 is visible to every row
+      const float alpha = exp2f(m - m_new);        // 0 for the first block (m = -inf)
+      // the previous block's P.V must be folded in (and P be free) before P is overwritten
+      if (j > 0) {
+        ok = mbar_wait(bar(B_PVFULL), (uint32_t)(j - 1) & 1u, abort_flag, p.status, 18);
+        if (!ok) break;
+        tc_fence_after();
+        for (int c = 0; c < 2; c++) {
+          tmem_ld32(lane_addr + TM_PV + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e++) o[c * 32 + e] += __uint_as_float(v[e]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < DH; i++) o[i] *= alpha;
+      l *= alpha;
+      // pass 2: probabilities (unnormalised) into the K-major operand layout: k-block c = 32 keys = one 128-byte row
+      // per query, 16-byte chunks XOR-swizzled with the row index
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = 0; c < 4; c++) {
+        tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
+        tmem_ld_wait();
+        uint8_t* prow = smem_gen + OFF_P + c * 16384 + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+          float4 pv;
+          float* pe = reinterpret_cast<float*>(&pv);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int col = c * 32 + ch * 4 + e;
+            const float pr = (col < lim) ? exp2f(fmaf(__uint_as_float(v[ch * 4 + e]), p.k2, -m_new)) : 0.f;
+            pe[e] = pr;
+            ls4[e] += pr;
+          }
+          *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
+        }
+      }
+      l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+      m = m_new;
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(bar(B_PFULL));
+      mbar_arrive(bar(B_SEMPTY + s));
+    }
+    if (ok) ok = mbar_wait(bar(B_PVFULL), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 19);
+    if (ok) {
+      tc_fence_after();
+      for (int c = 0; c < 2; c++) {
+        tmem_ld32(lane_addr + TM_PV + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e++) o[c * 32 + e] += __uint_as_float(v[e]);
+      }
+      const float inv = 1.f / l;
+      float* orow = p.out + ((long long)b * p.S + qi) * p.ld_out + h * DH;
+#pragma unroll
+      for (int i = 0; i < DH; i += 4)
+        *reinterpret_cast<float4*>(orow + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+      if (p.lse) p.lse[((long long)b * p.H + h) * p.S + qi] = m + log2f(l);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------------------------
+// Backward, first kernel: for one block of 128 queries it rebuilds the probabilities of every key block from the
+// saved row statistics, forms dS = scale * P * (dP - D) with dP = dO.V^T and D = rowsum(dO * O), and accumulates
+// dQ = dS.K over the key blocks in TMEM.
+//   warp 0      TMA: Q, dO once; per key block K_j, V_j (K-major) and K_j again as an MN-major B operand
+//   warp 1      MMA: S = Q.K_j^T and dP = dO.V_j^T into TMEM, then dQ += dS.K_j once dS is published
+//   warps 2..5  thread = query row: P, dS from TMEM, dS into the K-major operand layout
+// Shared memory (224 KiB): Q, dO, K, V, K(MN) 32 KiB each, dS 64 KiB.  TMEM: S [0,128), dP [128,256), dQ [256,320).
+constexpr uint32_t BO_Q = 0, BO_DO = 32768, BO_K = 65536, BO_V = 98304, BO_KMN = 131072, BO_DS = 163840;
+constexpr uint32_t TM_DP = 128, TM_DQ = 256;
+enum { C_QFULL = 0, C_KVFULL = 1, C_KVEMPTY = 2, C_KMNFULL = 3, C_KMNEMPTY = 4, C_SDPFULL = 5, C_SDPEMPTY = 6, C_DSFULL = 7,
+       C_DQDONE = 8, C_COUNT = 9 };
+
+struct FaBwdParams {
+  int S, H, n_qb, causal;
+  float k2, scale;
+  const float* lse;   // [n_seq][H][S]
+  const float* dsum;  // [n_seq][H][S]: D = rowsum(dO * O)
+  float* dq; long long ld_dq;
+  int accumulate;
+  int* status;
+};
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                        const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const __grid_constant__ CUtensorMap tmKmn, const FaBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  auto bar = [&](int i) { return smem_base + OFF_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + 8 * C_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = p.n_qb - 1 - (int)(blockIdx.x % p.n_qb);
+  const int bh = blockIdx.x / p.n_qb;
+  const int h = bh % p.H, b = bh / p.H;
+  const int n_kv = p.causal ? qb + 1 : p.S / BKV;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C_COUNT; i++) mbar_init(bar(i), (i == C_SDPEMPTY || i == C_DSFULL) ? 128u : 1u);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(C_QFULL), 2 * BQ * DH * 4);
+      for (int kb = 0; kb < 2; kb++) {
+        tma_load_4d(smem_base + BO_Q + kb * 16384, &tmQ, bar(C_QFULL), kb * 32, qb * BQ, h, b);
+        tma_load_4d(smem_base + BO_DO + kb * 16384, &tmDO, bar(C_QFULL), kb * 32, qb * BQ, h, b);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; j++) {
+        const uint32_t ph = (uint32_t)j & 1u;
+        ok = mbar_wait(bar(C_KVEMPTY), ph ^ 1u, abort_flag, p.status, 21);
+        if (!ok) break;
+        mbar_expect_tx(bar(C_KVFULL), 2 * BKV * DH * 4);
+        for (int kb = 0; kb < 2; kb++) {
+          tma_load_4d(smem_base + BO_K + kb * 16384, &tmK, bar(C_KVFULL), kb * 32, j * BKV, h, b);
+          tma_load_4d(smem_base + BO_V + kb * 16384, &tmV, bar(C_KVFULL), kb * 32, j * BKV, h, b);
+        }
+        ok = mbar_wait(bar(C_KMNEMPTY), ph ^ 1u, abort_flag, p.status, 22);
+        if (!ok) break;
+        mbar_expect_tx(bar(C_KMNFULL), BKV * DH * 4);
+        for (int c = 0; c < 4; c++) tma_load_5d(smem_base + BO_KMN + c * 8192, &tmKmn, bar(C_KMNFULL), 0, j * BKV + 32 * c, 0, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = fa_idesc(BQ, BKV, 0, 0), idesc_dq = fa_idesc(BQ, DH, 0, 1);
+      bool ok = mbar_wait(bar(C_QFULL), 0, abort_flag, p.status, 23);
+      for (int j = 0; j < n_kv && ok; j++) {
+        const uint32_t ph = (uint32_t)j & 1u;
+        ok = mbar_wait(bar(C_KVFULL), ph, abort_flag, p.status, 24) && mbar_wait(bar(C_SDPEMPTY), ph ^ 1u, abort_flag, p.status, 25);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = 0; kb < 2; kb++) {
+          const uint64_t aq = make_smem_desc(smem_base + BO_Q + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bk = make_smem_desc(smem_base + BO_K + kb * 16384, 16u, 1024u, 2u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S, aq + 2u * k, bk + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+        }
+        for (int kb = 0; kb < 2; kb++) {
+          const uint64_t ad = make_smem_desc(smem_base + BO_DO + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bv = make_smem_desc(smem_base + BO_V + kb * 16384, 16u, 1024u, 2u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DP, ad + 2u * k, bv + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+        }
+        umma_commit(bar(C_SDPFULL));
+        umma_commit(bar(C_KVEMPTY));
+        ok = mbar_wait(bar(C_DSFULL), ph, abort_flag, p.status, 26) && mbar_wait(bar(C_KMNFULL), ph, abort_flag, p.status, 27);
+        if (!ok) break;
+        tc_fence_after();
+        for (int c = 0; c < 4; c++) {
+          const uint64_t ad = make_smem_desc(smem_base + BO_DS + c * 16384, 16u, 1024u, 2u);
+          const uint64_t bd = make_smem_desc(smem_base + BO_KMN + c * 8192, 4096u, 512u, 1u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DQ, ad + 2u * k, bd + 64u * k, idesc_dq, (j | c | k) ? 1u : 0u);
+        }
+        umma_commit(bar(C_DQDONE));
+        umma_commit(bar(C_KMNEMPTY));
+      }
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    const int qi = qb * BQ + row;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+    const long long stat = ((long long)b * p.H + h) * p.S + qi;
+    const float L = p.lse[stat], Dv = p.dsum[stat];
+    bool ok = true;
+    uint32_t sv[32], dv[32];
+    for (int j = 0; j < n_kv && ok; j++) {
+      const uint32_t ph = (uint32_t)j & 1u;
+      ok = mbar_wait(bar(C_SDPFULL), ph, abort_flag, p.status, 28);
+      if (ok && j > 0) ok = mbar_wait(bar(C_DQDONE), ph ^ 1u, abort_flag, p.status, 29);  // dS tile free again
+      if (!ok) break;
+      tc_fence_after();
+      const int lim = (p.causal && j == qb) ? row + 1 : BKV;
+      for (int c = 0; c < 4; c++) {
+        tmem_ld32(lane_addr + TM_S + c * 32, sv);
+        tmem_ld32(lane_addr + TM_DP + c * 32, dv);
+        tmem_ld_wait();
+        uint8_t* srow = smem_gen + BO_DS + c * 16384 + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+          float4 dsv;
+          float* de = reinterpret_cast<float*>(&dsv);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int col = c * 32 + ch * 4 + e;
+            const float pr = (col < lim) ? exp2f(__uint_as_float(sv[ch * 4 + e]) * p.k2 - L) : 0.f;
+            de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dv) * p.scale;
+          }
+          *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
+        }
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(bar(C_DSFULL));
+      mbar_arrive(bar(C_SDPEMPTY));
+    }
+    if (ok) ok = mbar_wait(bar(C_DQDONE), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 30);
+    if (ok) {
+      tc_fence_after();
+      float* qrow = p.dq + ((long long)b * p.S + qi) * p.ld_dq + h * DH;
+      for (int c = 0; c < 2; c++) {
+        tmem_ld32(lane_addr + TM_DQ + c * 32, sv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 o = make_float4(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1]), __uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3]));
+          float4* dst = reinterpret_cast<float4*>(qrow + c * 32 + e);
+          if (p.accumulate) {
+            const float4 old = *dst;
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          *dst = o;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Backward, second kernel: dK and dV of one block of 128 keys, accumulated over the query blocks that see it.
+// The contraction of both products runs over the queries, so the tensor core needs P^T and dS^T with the KEY
+// index on the TMEM lanes.  The kernel therefore rebuilds the scores transposed, S^T = K_j.Q_i^T and
+// dP^T = V_j.dO_i^T (both operands K-major), lets each thread (= one key) form its row of P^T and dS^T from the
+// saved row statistics of the queries, and writes them to shared memory as K-major A operands of
+//   dV_j += P^T . dO_i      dK_j += dS^T . Q_i        (dO_i and Q_i as MN-major B operands)
+// Nothing score-sized is written to global memory.  Query blocks are 64 rows here (shared memory budget):
+//   K_j, V_j 32 KiB each (resident), Q_i, dO_i as K-major and as MN-major tiles 16 KiB each, P^T, dS^T 32 KiB each.
+// TMEM: S^T [0,64), dP^T [64,128), dV [128,192), dK [192,256).
+constexpr int BQ2 = 64;
+constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 81920, CO_QMN = 98304, CO_DOMN = 114688, CO_PT = 131072,
+                   CO_DST = 163840, CO_STAT = 196608, CO_BAR = 197632;
+constexpr int FA2_SMEM = CO_BAR + 256 + 1024;
+constexpr uint32_t T2_ST = 0, T2_DPT = 64, T2_DV = 128, T2_DK = 192;
+enum { D_KVFULL = 0, D_QFULL = 1, D_QEMPTY = 2, D_STFULL = 3, D_STEMPTY = 4, D_PTFULL = 5, D_ACCDONE = 6, D_COUNT = 7 };
+
+struct FaBwd2Params {
+  int S, H, n_kb, causal;
+  float k2, scale;
+  const float* lse;
+  const float* dsum;
+  float* dk; float* dv; long long ld;
+  int accumulate;
+  int* status;
+};
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                         const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                         const __grid_constant__ CUtensorMap tmQmn, const __grid_constant__ CUtensorMap tmDOmn,
+                         const FaBwd2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  auto bar = [&](int i) { return smem_base + CO_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + CO_BAR + 8 * D_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kbk = blockIdx.x % p.n_kb;            // light (late) key blocks last
+  const int bh = blockIdx.x / p.n_kb;
+  const int h = bh % p.H, b = bh / p.H;
+  const int n_q = p.S / BQ2;
+  const int i0 = p.causal ? kbk * (BKV / BQ2) : 0;   // first 64-row query block that sees this key block
+  const int n_it = n_q - i0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_STEMPTY || i == D_PTFULL) ? 128u : 1u);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(D_KVFULL), 2 * BKV * DH * 4);
+      for (int kb = 0; kb < 2; kb++) {
+        tma_load_4d(smem_base + CO_K + kb * 16384, &tmK, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
+        tma_load_4d(smem_base + CO_V + kb * 16384, &tmV, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_it && ok; it++) {
+        const uint32_t ph = (uint32_t)it & 1u;
+        ok = mbar_wait(bar(D_QEMPTY), ph ^ 1u, abort_flag, p.status, 31);
+        if (!ok) break;
+        const int q0 = (i0 + it) * BQ2;
+        mbar_expect_tx(bar(D_QFULL), 4 * BQ2 * DH * 4);
+        for (int kb = 0; kb < 2; kb++) {
+          tma_load_4d(smem_base + CO_Q + kb * 8192, &tmQ, bar(D_QFULL), kb * 32, q0, h, b);
+          tma_load_4d(smem_base + CO_DO + kb * 8192, &tmDO, bar(D_QFULL), kb * 32, q0, h, b);
+        }
+        for (int c = 0; c < 2; c++) {
+          tma_load_5d(smem_base + CO_QMN + c * 8192, &tmQmn, bar(D_QFULL), 0, q0 + 32 * c, 0, h, b);
+          tma_load_5d(smem_base + CO_DOMN + c * 8192, &tmDOmn, bar(D_QFULL), 0, q0 + 32 * c, 0, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_st = fa_idesc(BKV, BQ2, 0, 0), idesc_acc = fa_idesc(BKV, DH, 0, 1);
+      bool ok = mbar_wait(bar(D_KVFULL), 0, abort_flag, p.status, 32);
+      for (int it = 0; it < n_it && ok; it++) {
+        const uint32_t ph = (uint32_t)it & 1u;
+        ok = mbar_wait(bar(D_QFULL), ph, abort_flag, p.status, 33) && mbar_wait(bar(D_STEMPTY), ph ^ 1u, abort_flag, p.status, 34);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = 0; kb < 2; kb++) {
+          const uint64_t ak = make_smem_desc(smem_base + CO_K + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bq = make_smem_desc(smem_base + CO_Q + kb * 8192, 16u, 1024u, 2u);
+          const uint64_t av = make_smem_desc(smem_base + CO_V + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bd = make_smem_desc(smem_base + CO_DO + kb * 8192, 16u, 1024u, 2u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            umma_tf32(tmem_base + T2_ST, ak + 2u * k, bq + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
+            umma_tf32(tmem_base + T2_DPT, av + 2u * k, bd + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
+          }
+        }
+        umma_commit(bar(D_STFULL));
+        ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35);
+        if (!ok) break;
+        tc_fence_after();
+        for (int c = 0; c < 2; c++) {   // 32 queries per chunk
+          const uint64_t ap = make_smem_desc(smem_base + CO_PT + c * 16384, 16u, 1024u, 2u);
+          const uint64_t as = make_smem_desc(smem_base + CO_DST + c * 16384, 16u, 1024u, 2u);
+          const uint64_t bdo = make_smem_desc(smem_base + CO_DOMN + c * 8192, 4096u, 512u, 1u);
+          const uint64_t bq = make_smem_desc(smem_base + CO_QMN + c * 8192, 4096u, 512u, 1u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            umma_tf32(tmem_base + T2_DV, ap + 2u * k, bdo + 64u * k, idesc_acc, (it | c | k) ? 1u : 0u);
+            umma_tf32(tmem_base + T2_DK, as + 2u * k, bq + 64u * k, idesc_acc, (it | c | k) ? 1u : 0u);
+          }
+        }
+        umma_commit(bar(D_ACCDONE));
+        umma_commit(bar(D_QEMPTY));
+      }
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;            // key inside the block
+    const int kj = kbk * BKV + row;            // key position in the sequence
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+    const long long stat_base = ((long long)b * p.H + h) * p.S;
+    bool ok = true;
+    uint32_t sv[32], dv[32];
+    for (int it = 0; it < n_it && ok; it++) {
+      const uint32_t ph = (uint32_t)it & 1u;
+      const int q0 = (i0 + it) * BQ2;
+      // row statistics of the 64 queries of this block: lane l holds queries 2l and 2l + 1, the inner loop fetches
+      // the one it needs with a shuffle (no block-wide barrier inside a loop whose waits can give up)
+      const float2 Lq = __ldg(reinterpret_cast<const float2*>(p.lse + stat_base + q0) + lane);
+      const float2 Dq = __ldg(reinterpret_cast<const float2*>(p.dsum + stat_base + q0) + lane);
+      ok = mbar_wait(bar(D_STFULL), ph, abort_flag, p.status, 36);
+      if (ok && it > 0) ok = mbar_wait(bar(D_ACCDONE), ph ^ 1u, abort_flag, p.status, 37);   // P^T / dS^T tiles free again
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        tmem_ld32(lane_addr + T2_ST + c * 32, sv);
+        tmem_ld32(lane_addr + T2_DPT + c * 32, dv);
+        tmem_ld_wait();
+        uint8_t* prow = smem_gen + CO_PT + c * 16384 + row * 128;
+        uint8_t* srow = smem_gen + CO_DST + c * 16384 + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ch++) {
+          float4 pv, dsv;
+          float* pe = reinterpret_cast<float*>(&pv);
+          float* de = reinterpret_cast<float*>(&dsv);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int col = c * 32 + ch * 4 + e;            // query inside the block
+            const bool vis = !p.causal || (q0 + col >= kj);
+            const float Lc = __shfl_sync(0xffffffffu, (col & 1) ? Lq.y : Lq.x, col >> 1);
+            const float Dc = __shfl_sync(0xffffffffu, (col & 1) ? Dq.y : Dq.x, col >> 1);
+            const float pr = vis ? exp2f(__uint_as_float(sv[ch * 4 + e]) * p.k2 - Lc) : 0.f;
+            pe[e] = pr;
+            de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale;
+          }
+          *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
+          *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
+        }
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(bar(D_PTFULL));
+      mbar_arrive(bar(D_STEMPTY));
+    }
+    if (ok && n_it > 0) ok = mbar_wait(bar(D_ACCDONE), (uint32_t)(n_it - 1) & 1u, abort_flag, p.status, 38);
+    if (ok) {
+      tc_fence_after();
+      for (int which = 0; which < 2; which++) {
+        float* grow = (which ? p.dk : p.dv) + ((long long)b * p.S + kj) * p.ld + h * DH;
+        for (int c = 0; c < 2; c++) {
+          tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + c * 32, sv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            float4 o = make_float4(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1]), __uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3]));
+            float4* dst = reinterpret_cast<float4*>(grow + c * 32 + e);
+            if (p.accumulate) {
+              const float4 old = *dst;
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *dst = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
+// D[b][h][i] = sum_c dO[b, i, h, c] * O[b, i, h, c]: 16 lanes per (row, head), float4 each
+__global__ void attention_rowdot_kernel(const float* __restrict__ dout, long long ld_do, const float* __restrict__ out, long long ld_o,
+                                        float* __restrict__ dsum, long long rows_total, int S, int H) {
+  const long long item = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 4;   // (global row, head)
+  const int part = threadIdx.x & 15;
+  if (item >= rows_total * H) return;   // whole 16-lane groups leave together
+  const long long r = item / H;
+  const int h = (int)(item - r * H);
+  const float4 a = *reinterpret_cast<const float4*>(dout + r * ld_do + h * DH + part * 4);
+  const float4 o = *reinterpret_cast<const float4*>(out + r * ld_o + h * DH + part * 4);
+  float v = a.x * o.x + a.y * o.y + a.z * o.z + a.w * o.w;
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off, 16);
+  if (part == 0) {
+    const long long bseq = r / S;
+    dsum[(bseq * H + h) * S + (r - bseq * S)] = v;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
+  FML_REQUIRE(ctx, d && d->q && d->k && d->v && d->out, "fml_attention_fwd: NULL buffer");
+  FML_REQUIRE(ctx, d->n_seq > 0 && d->heads > 0 && d->seq_len > 0, "fml_attention_fwd: bad sizes");
+  FML_REQUIRE(ctx, d->d_head == DH, "fml_attention_fwd: d_head must be 64");
+  FML_REQUIRE(ctx, d->seq_len % BQ == 0, "fml_attention_fwd: seq_len must be a multiple of 128");
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  FML_REQUIRE(ctx, al16(d->q) && al16(d->k) && al16(d->v) && al16(d->out) && d->ld_qkv % 4 == 0 && d->ld_out % 4 == 0,
+              "fml_attention_fwd: operands must be 16-byte aligned with row strides that are multiples of 4 floats");
+  FML_REQUIRE(ctx, d->ld_qkv >= (int64_t)d->heads * DH && d->ld_out >= (int64_t)d->heads * DH, "fml_attention_fwd: row stride smaller than heads * 64");
+  const int S = d->seq_len, H = d->heads, Bn = d->n_seq;
+  CUtensorMap tmQ, tmK, tmV;
+  int32_t rc;
+  const int64_t s2 = (int64_t)S * d->ld_qkv;
+  if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BQ, false, 0, &tmQ))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, d->k, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BKV, false, 0, &tmK))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, d->v, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmV))) return rc;
+  FaParams p;
+  p.S = S; p.H = H; p.n_qb = S / BQ;
+  p.causal = d->causal ? 1 : 0;
+  p.k2 = d->scale * 1.4426950408889634f;
+  p.out = d->out; p.ld_out = d->ld_out;
+  p.lse = d->lse;
+  p.status = ctx->d_status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    FML_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
+    attr_set = true;
+  }
+  const long long grid = (long long)Bn * H * p.n_qb;
+  FML_REQUIRE(ctx, grid <= 0x7fffffffLL, "fml_attention_fwd: too many work items");
+  attention_fwd_kernel<<<(unsigned)grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
+  FML_LAUNCH_CHECK(ctx, "attention_fwd_kernel");
+  return FML_OK;
+}
+
+
+int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float* dout, int64_t ld_dout, float* dq, float* dk,
+                          float* dv, int64_t ld_dqkv, int32_t accumulate, float* scratch) {
+  FML_REQUIRE(ctx, d && d->q && d->k && d->v && d->out && d->lse && dout && dq && dk && dv && scratch, "fml_attention_bwd: NULL buffer");
+  FML_REQUIRE(ctx, d->n_seq > 0 && d->heads > 0 && d->seq_len > 0 && d->d_head == DH && d->seq_len % BQ == 0,
+              "fml_attention_bwd: d_head must be 64 and seq_len a multiple of 128");
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  FML_REQUIRE(ctx, al16(d->q) && al16(d->k) && al16(d->v) && al16(d->out) && al16(dout) && al16(dq) && al16(dk) && al16(dv) && al16(scratch) &&
+                       d->ld_qkv % 4 == 0 && d->ld_out % 4 == 0 && ld_dout % 4 == 0 && ld_dqkv % 4 == 0,
+              "fml_attention_bwd: operands must be 16-byte aligned with row strides that are multiples of 4 floats");
+  const int S = d->seq_len, H = d->heads, Bn = d->n_seq;
+  const long long rows = (long long)Bn * S;
+  float* dsum = scratch;
+  {
+    const long long threads = rows * H * 16;
+    attention_rowdot_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(dout, ld_dout, d->out, d->ld_out, dsum, rows, S, H);
+    FML_LAUNCH_CHECK(ctx, "attention_rowdot_kernel");
+  }
+  CUtensorMap tmQ, tmDO, tmK, tmV, tmKmn, tmQ64, tmDO64, tmQmn, tmDOmn;
+  int32_t rc;
+  const int64_t s2 = (int64_t)S * d->ld_qkv, s2o = (int64_t)S * ld_dout;
+  if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BQ, false, 0, &tmQ))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, BQ, false, 0, &tmDO))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, d->k, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BKV, false, 0, &tmK))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, d->v, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BKV, false, 0, &tmV))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, d->k, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmKmn))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BQ2, false, 0, &tmQ64))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, BQ2, false, 0, &tmDO64))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmQmn))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, 32, true, 2, &tmDOmn))) return rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    FML_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
+    FML_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA2_SMEM));
+    attr_set = true;
+  }
+  const unsigned grid = (unsigned)((long long)Bn * H * (S / BQ));
+  FaBwdParams p;
+  p.S = S; p.H = H; p.n_qb = S / BQ; p.causal = d->causal ? 1 : 0;
+  p.scale = d->scale; p.k2 = d->scale * 1.4426950408889634f;
+  p.lse = d->lse; p.dsum = dsum;
+  p.dq = dq; p.ld_dq = ld_dqkv; p.accumulate = accumulate ? 1 : 0;
+  p.status = ctx->d_status;
+  attention_bwd_dq_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, p);
+  FML_LAUNCH_CHECK(ctx, "attention_bwd_dq_kernel");
+  FaBwd2Params p2;
+  p2.S = S; p2.H = H; p2.n_kb = S / BKV; p2.causal = p.causal;
+  p2.k2 = p.k2; p2.scale = p.scale; p2.lse = d->lse; p2.dsum = dsum;
+  p2.dk = dk; p2.dv = dv; p2.ld = ld_dqkv; p2.accumulate = p.accumulate;
+  p2.status = ctx->d_status;
+  attention_bwd_dkv_kernel<<<grid, FA_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ64, tmDO64, tmQmn, tmDOmn, p2);
+  FML_LAUNCH_CHECK(ctx, "attention_bwd_dkv_kernel");
+  return FML_OK;
+}
+
+}  // extern "C"

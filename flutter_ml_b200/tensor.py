@@ -29,6 +29,7 @@ _default_ctx: Optional[Context] = None
 # column-sum pass for the bias gradient; softmax-backward epilogue 670 us against 263 + 237 us).
 FUSE_DACT_INTO_DX = False
 FUSE_SOFTMAX_BACKWARD = False
+FUSE_ATTENTION = True   # one kernel for softmax(scale Q.K^T).V (TF32 mode, d_head 64, seq_len % 128 == 0)
 
 
 def default_context() -> Context:
@@ -404,6 +405,34 @@ def layerNorm(x: Tensor, gamma: Tensor, beta: Tensor, epsilon: float = 1e-5, res
     return out
 
 
+def _attentionFused(qkv: Tensor, q, k, v, Bn, S, H, dk, causal, scale):
+    """fml_attention_fwd / fml_attention_bwd: the score matrices stay on chip in the forward pass; the backward
+    pass rebuilds the probabilities from the saved row statistics and writes only P and dS once."""
+    import ctypes
+    ctx = qkv.ctx
+    d = H * dk
+    out = Tensor(ctx.empty(Bn * S, d), ctx)
+    lse = ctx.empty(Bn * H * S)
+    desc = _lib.AttentionDesc()
+    desc.n_seq, desc.seq_len, desc.heads, desc.d_head = Bn, S, H, dk
+    desc.q, desc.k, desc.v, desc.ld_qkv = q.ptr, k.ptr, v.ptr, 3 * d
+    desc.out, desc.ld_out, desc.lse = out.value.ptr, d, lse.ptr
+    desc.scale, desc.causal = scale, int(bool(causal))
+    ctx.check(ctx.lib.fml_attention_fwd(ctx.h, ctypes.byref(desc)))
+    ctx.launches += 1
+
+    def bw():
+        g, acc = qkv._grad_target()
+        scratch = ctx.empty(Bn * H * S)
+        ctx.check(ctx.lib.fml_attention_bwd(ctx.h, ctypes.byref(desc), out.grad.ptr, d, g.ptr, g.ptr + 4 * d, g.ptr + 8 * d, 3 * d,
+                                            1 if acc else 0, scratch.ptr))
+        ctx.launches += 4
+        _keep = (lse, out)  # the descriptor holds raw pointers into these
+    out.creator = Node([qkv], bw, "attention", 4 * Bn * H * S * S * dk, {"causal": causal, "fused": True})
+    out.attention_weights = None   # never materialised on this path (set FUSE_ATTENTION = False to inspect them)
+    return out
+
+
 def attentionCore(qkv: Tensor, n_seq: int, seq_len: int, heads: int, d_head: int, causal: bool, precision: int = -1):
     """Scaled dot-product attention for all (sequence, head) pairs at once, reading Q, K, V as
     column slices of the fused projection [n_seq*seq_len, 3*heads*d_head] and writing the heads
@@ -416,6 +445,9 @@ def attentionCore(qkv: Tensor, n_seq: int, seq_len: int, heads: int, d_head: int
     ld = 3 * d
     scale = 1.0 / math.sqrt(dk)
     q, k, v = qkv.value, qkv.value.view(d, ()), qkv.value.view(2 * d, ())
+    eff_prec = ctx.precision if precision < 0 else precision
+    if FUSE_ATTENTION and eff_prec == _lib.PREC_TF32 and dk == 64 and S % 128 == 0:
+        return _attentionFused(qkv, q, k, v, Bn, S, H, dk, causal, scale)
     P = ctx.empty(Bn * H * S, S)
     out = Tensor(ctx.empty(Bn * S, d), ctx)
     bat = dict(batch=(H, Bn), precision=precision)

@@ -363,6 +363,34 @@ int32_t fml_tape_run(fml_ctx* ctx, const fml_op* ops, int32_t n_ops, int32_t dir
 /* opName string -> fml_op_kind, 0 if the executor does not know the name. */
 int32_t fml_tape_kind(const char* op_name);
 
+/* ---- fused attention ---------------------------------------------------------------
+ * softmax(scale * Q.K^T [+ causal mask]) . V for every (sequence, head) in one kernel, the scores kept on chip:
+ * transpose + matMul + scaleMatrix + softmaxMatrix + matMul of SingleHeadAttention.forward
+ * (lib/layertypes/singleHeadAttentionLayer.dart:77-86) and the head concat of
+ * lib/transformer/multiHeadAttentionLayer.dart:80.  q, k, v are row-major [n_seq * seq_len, >= heads * 64]
+ * matrices with row stride ld_qkv (they may be column slices of one fused projection); head h occupies columns
+ * 64 h .. 64 h + 63.  out has the same form with stride ld_out.  d_head must be 64 and seq_len a multiple of 128.
+ * lse (optional, [n_seq][heads][seq_len]) receives log2 of every row's softmax denominator in the scaled domain
+ * (max + log2 sum), which a backward pass needs to rebuild the probabilities. */
+typedef struct fml_attention_desc {
+  int32_t n_seq, seq_len, heads, d_head;
+  const float* q; const float* k; const float* v;
+  int64_t ld_qkv;
+  float* out;
+  int64_t ld_out;
+  float* lse;
+  float scale;
+  int32_t causal;
+} fml_attention_desc;
+int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d);
+/* Backward of fml_attention_fwd (d as in the forward call, with the out and lse it produced).  dout is the gradient of
+ * out (row stride ld_dout); dq, dk, dv have the layout of q, k, v with row stride ld_dqkv and are overwritten, or
+ * added to when accumulate != 0.  scratch: n_seq * heads * seq_len floats.  Two kernels rebuild the probabilities
+ * from lse on chip - one per query block for dQ, one per key block (scores transposed) for dK and dV - so no
+ * score-sized tensor is written to or read from global memory in either pass. */
+int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float* dout, int64_t ld_dout, float* dq,
+                          float* dk, float* dv, int64_t ld_dqkv, int32_t accumulate, float* scratch);
+
 /* ---- convolution -----------------------------------------------------------------
  * conv2d (tensor.dart:765-833) for every kernel of a Conv2DLayer (lib/layertypes/conv2d.dart:60-75) and every image
  * of a batch in one launch: in [n_img][H][W], w [n_k][kh][kw], bias [n_k] or NULL (addScalarToMatrix,

@@ -1,0 +1,107 @@
+"""Fused attention (fml_attention_fwd / fml_attention_bwd) against the oracle's matMul / scaleMatrix / softmaxMatrix
+chain (singleHeadAttentionLayer.dart:77-86), per (sequence, head)."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+from tests.gpu_util import rel
+
+pytestmark = pytest.mark.gpu
+
+
+def w64(a):
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32), dtype=np.float64)
+
+
+def attention_desc(ctx, qkv, out, lse, Bn, S, H, causal, scale):
+    from flutter_ml_b200 import _lib
+    d = _lib.AttentionDesc()
+    dm = H * 64
+    d.n_seq, d.seq_len, d.heads, d.d_head = Bn, S, H, 64
+    d.q, d.k, d.v = qkv.ptr, qkv.ptr + 4 * dm, qkv.ptr + 8 * dm
+    d.ld_qkv, d.out, d.ld_out = 3 * dm, out.ptr, dm
+    d.lse = lse.ptr if lse is not None else None
+    d.scale, d.causal = scale, int(causal)
+    return d
+
+
+@pytest.mark.parametrize("S,causal", [(128, False), (128, True), (384, True), (512, True), (256, False)])
+def test_fused_attention_forward(orc, S, causal):
+    from flutter_ml_b200 import _lib
+    ctx = _lib.Context(precision=_lib.PREC_TF32)
+    Bn, H, dk = 2, 3, 64
+    dm = H * dk
+    rng = np.random.default_rng(S + causal)
+    qkv = rng.standard_normal((Bn * S, 3 * dm)).astype(np.float32)
+    scale = 1 / math.sqrt(dk)
+    dq, out, lse = ctx.upload(qkv), ctx.empty(Bn * S, dm), ctx.empty(Bn * H * S)
+    d = attention_desc(ctx, dq, out, lse, Bn, S, H, causal, scale)
+    ctx.check(ctx.lib.fml_attention_fwd(ctx.h, C.byref(d)))
+    assert ctx.device_status() == 0
+    got, got_lse = out.numpy(), lse.numpy().reshape(Bn, H, S)
+    ops = orc.Ops(omp=True)
+    for b in range(Bn):
+        for h in range(H):
+            rows = slice(b * S, (b + 1) * S)
+            Q, K, V = (w64(qkv[rows, i * dm + h * dk:i * dm + (h + 1) * dk]) for i in range(3))
+            s_ref = ops.matmul_fwd(Q, np.ascontiguousarray(K.T)) * scale
+            p_ref = ops.softmax_fwd(s_ref, S if causal else 0)
+            o_ref = ops.matmul_fwd(p_ref, V)
+            assert rel(got[rows, h * dk:(h + 1) * dk], o_ref) <= 2e-3          # two TF32 products in a chain
+            masked = np.where(np.tril(np.ones((S, S), bool)) | (not causal), s_ref, -np.inf)
+            lse_ref = (np.log(np.exp(masked - masked.max(1, keepdims=True)).sum(1)) + masked.max(1)) / math.log(2)
+            assert np.max(np.abs(got_lse[b, h] - lse_ref)) <= 2e-2
+    ctx.close()
+
+
+def test_fused_attention_rejects_unsupported_shapes():
+    from flutter_ml_b200 import _lib
+    ctx = _lib.Context()
+    buf, out = ctx.zeros(128, 3 * 64), ctx.zeros(128, 64)
+    d = attention_desc(ctx, buf, out, None, 1, 128, 1, True, 0.125)
+    d.d_head = 32
+    assert ctx.lib.fml_attention_fwd(ctx.h, C.byref(d)) == -1
+    d.d_head, d.seq_len = 64, 96
+    assert ctx.lib.fml_attention_fwd(ctx.h, C.byref(d)) == -1
+    ctx.close()
+
+
+@pytest.mark.parametrize("S,causal", [(128, True), (256, True), (384, False), (512, True)])
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_fused_attention_backward(orc, S, causal, accumulate):
+    """dQ, dK, dV of the fused backward against the oracle's tape for the same head: matMul, transpose,
+    scale_matrix, softmax_matrix, matMul with an arbitrary upstream gradient."""
+    from flutter_ml_b200 import _lib
+    if accumulate and S != 256:
+        pytest.skip("accumulation is shape-independent")
+    ctx = _lib.Context(precision=_lib.PREC_TF32)
+    Bn, H, dk = 2, 2, 64
+    dm = H * dk
+    rng = np.random.default_rng(7 * S + causal)
+    qkv = rng.standard_normal((Bn * S, 3 * dm)).astype(np.float32)
+    G = rng.standard_normal((Bn * S, dm)).astype(np.float32)
+    scale = 1 / math.sqrt(dk)
+    dq, out, lse, dG = ctx.upload(qkv), ctx.empty(Bn * S, dm), ctx.empty(Bn * H * S), ctx.upload(G)
+    d = attention_desc(ctx, dq, out, lse, Bn, S, H, causal, scale)
+    ctx.check(ctx.lib.fml_attention_fwd(ctx.h, C.byref(d)))
+    base = rng.standard_normal((Bn * S, 3 * dm)).astype(np.float32) if accumulate else np.zeros((Bn * S, 3 * dm), np.float32)
+    dqkv = ctx.upload(base)
+    scratch = ctx.empty(Bn * H * S)
+    ctx.check(ctx.lib.fml_attention_bwd(ctx.h, C.byref(d), dG.ptr, dm, dqkv.ptr, dqkv.ptr + 4 * dm, dqkv.ptr + 8 * dm, 3 * dm,
+                                        accumulate, scratch.ptr))
+    assert ctx.device_status() == 0
+    got = dqkv.numpy() - base
+    E = orc.Engine(omp=True)
+    for b in range(Bn):
+        for h in range(H):
+            rows = slice(b * S, (b + 1) * S)
+            Q, K, V = (orc.T(w64(qkv[rows, i * dm + h * dk:i * dm + (h + 1) * dk])) for i in range(3))
+            P = E.softmaxMatrix(E.scaleMatrix(E.matMul(Q, E.transpose(K)), scale), causal)
+            O = E.matMul(P, V)
+            E.sum(E.elementWiseMultiply(O, orc.T(w64(G[rows, h * dk:(h + 1) * dk])))).backward()
+            for i, t in enumerate((Q, K, V)):
+                g = got[rows, i * dm + h * dk:i * dm + (h + 1) * dk]
+                assert rel(g, t.grad) <= (5e-3 if not accumulate else 2e-2), (b, h, "qkv"[i])
+    ctx.close()
