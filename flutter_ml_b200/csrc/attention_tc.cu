@@ -28,7 +28,8 @@ using namespace fml_tc;
 namespace {
 
 constexpr int BQ = 128, BKV = 128, DH = 64;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 192;      // forward: producer, issuer, 4 softmax warps
+constexpr int FA_BWD_THREADS = 320;  // backward: producer, issuer, 8 compute warps (two per TMEM lane quarter, alternate 32-column chunks)
 constexpr uint32_t OFF_Q = 0, OFF_K = 32768, OFF_V = 98304, OFF_P = 163840, OFF_BAR = 229376;
 constexpr int FA_SMEM = OFF_BAR + 256 + 1024;
 constexpr uint32_t TM_S = 0, TM_PV = 256;
@@ -252,7 +253,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // dQ = dS.K over the key blocks in TMEM.
 //   warp 0      TMA: Q, dO once; per key block K_j, V_j (K-major) and K_j again as an MN-major B operand
 //   warp 1      MMA: S = Q.K_j^T and dP = dO.V_j^T into TMEM, then dQ += dS.K_j once dS is published
-//   warps 2..5  thread = query row: P, dS from TMEM, dS into the K-major operand layout
+//   warps 2..9  thread = query row and half of the columns: P, dS from TMEM, dS into the K-major operand layout
 // Shared memory (224 KiB): Q, dO, K, V, K(MN) 32 KiB each, dS 64 KiB.  TMEM: S [0,128), dP [128,256), dQ [256,320).
 constexpr uint32_t BO_Q = 0, BO_DO = 32768, BO_K = 65536, BO_V = 98304, BO_KMN = 131072, BO_DS = 163840;
 constexpr uint32_t TM_DP = 128, TM_DQ = 256;
@@ -269,7 +270,7 @@ struct FaBwdParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const __grid_constant__ CUtensorMap tmKmn, const FaBwdParams p) {
@@ -286,7 +287,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const int n_kv = p.causal ? qb + 1 : p.S / BKV;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C_COUNT; i++) mbar_init(bar(i), (i == C_SDPEMPTY || i == C_DSFULL) ? 128u : 1u);
+    for (int i = 0; i < C_COUNT; i++) mbar_init(bar(i), (i == C_SDPEMPTY || i == C_DSFULL) ? 256u : 1u);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -362,6 +363,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
   } else {
     const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;   // the two warps of a lane quarter take alternate 32-column chunks
     const int row = q4 * 32 + lane;
     const int qi = qb * BQ + row;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
@@ -376,7 +378,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       if (!ok) break;
       tc_fence_after();
       const int lim = (p.causal && j == qb) ? row + 1 : BKV;
-      for (int c = 0; c < 4; c++) {
+      for (int c = half; c < 4; c += 2) {
         tmem_ld32(lane_addr + TM_S + c * 32, sv);
         tmem_ld32(lane_addr + TM_DP + c * 32, dv);
         tmem_ld_wait();
@@ -403,7 +405,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     if (ok) {
       tc_fence_after();
       float* qrow = p.dq + ((long long)b * p.S + qi) * p.ld_dq + h * DH;
-      for (int c = 0; c < 2; c++) {
+      {
+        const int c = half;
         tmem_ld32(lane_addr + TM_DQ + c * 32, sv);
         tmem_ld_wait();
 #pragma unroll
@@ -454,7 +457,7 @@ struct FaBwd2Params {
   int* status;
 };
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                          const __grid_constant__ CUtensorMap tmQmn, const __grid_constant__ CUtensorMap tmDOmn,
@@ -474,7 +477,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   const int n_it = n_q - i0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_STEMPTY || i == D_PTFULL) ? 128u : 1u);
+    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_STEMPTY || i == D_PTFULL) ? 256u : 1u);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -554,6 +557,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
   } else {
     const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;          // which 32-query chunk of every block this warp handles
     const int row = q4 * 32 + lane;            // key inside the block
     const int kj = kbk * BKV + row;            // key position in the sequence
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
@@ -571,8 +575,8 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       if (ok && it > 0) ok = mbar_wait(bar(D_ACCDONE), ph ^ 1u, abort_flag, p.status, 37);   // P^T / dS^T tiles free again
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; c++) {
+      {
+        const int c = half;
         tmem_ld32(lane_addr + T2_ST + c * 32, sv);
         tmem_ld32(lane_addr + T2_DPT + c * 32, dv);
         tmem_ld_wait();
@@ -607,7 +611,8 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       tc_fence_after();
       for (int which = 0; which < 2; which++) {
         float* grow = (which ? p.dk : p.dv) + ((long long)b * p.S + kj) * p.ld + h * DH;
-        for (int c = 0; c < 2; c++) {
+        {
+          const int c = half;
           tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + c * 32, sv);
           tmem_ld_wait();
 #pragma unroll
@@ -733,14 +738,14 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   p.lse = d->lse; p.dsum = dsum;
   p.dq = dq; p.ld_dq = ld_dqkv; p.accumulate = accumulate ? 1 : 0;
   p.status = ctx->d_status;
-  attention_bwd_dq_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, p);
+  attention_bwd_dq_kernel<<<grid, FA_BWD_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, p);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dq_kernel");
   FaBwd2Params p2;
   p2.S = S; p2.H = H; p2.n_kb = S / BKV; p2.causal = p.causal;
   p2.k2 = p.k2; p2.scale = p.scale; p2.lse = d->lse; p2.dsum = dsum;
   p2.dk = dk; p2.dv = dv; p2.ld = ld_dqkv; p2.accumulate = p.accumulate;
   p2.status = ctx->d_status;
-  attention_bwd_dkv_kernel<<<grid, FA_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ64, tmDO64, tmQmn, tmDOmn, p2);
+  attention_bwd_dkv_kernel<<<grid, FA_BWD_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ64, tmDO64, tmQmn, tmDOmn, p2);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dkv_kernel");
   return FML_OK;
 }
