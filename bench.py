@@ -268,6 +268,41 @@ def time_membound(ctx, hbm_gbs, reps=5, rows=262144, params=1 << 28):
     return out
 
 
+def time_attention(ctx, n_seq=32, seq_len=512, heads=16, reps=10):
+    """Fused attention at the shape of one config-5 layer (d_head 64, causal): forward and backward, microseconds per
+    call and TFLOP/s on the full S x S flop count (2 products forward, 5 backward including the recomputation)."""
+    import ctypes
+    from flutter_ml_b200 import _lib
+    dk = 64
+    d = heads * dk
+    pool = np.random.default_rng(5).standard_normal(1 << 22).astype(np.float32)
+    qkv, G = ctx.empty(n_seq * seq_len, 3 * d), ctx.empty(n_seq * seq_len, d)
+    ctx.upload(np.resize(pool, qkv.size), out=qkv.reshape(qkv.size))
+    ctx.upload(np.resize(pool[::-1], G.size), out=G.reshape(G.size))
+    out, lse, dqkv, scratch = ctx.empty(n_seq * seq_len, d), ctx.empty(n_seq * heads * seq_len), ctx.empty(n_seq * seq_len, 3 * d), ctx.empty(n_seq * heads * seq_len)
+    de = _lib.AttentionDesc()
+    de.n_seq, de.seq_len, de.heads, de.d_head = n_seq, seq_len, heads, dk
+    de.q, de.k, de.v, de.ld_qkv = qkv.ptr, qkv.ptr + 4 * d, qkv.ptr + 8 * d, 3 * d
+    de.out, de.ld_out, de.lse, de.scale, de.causal = out.ptr, d, lse.ptr, 0.125, 1
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ctx.sync()
+        ctx.timer_start()
+        for _ in range(reps):
+            fn()
+        return ctx.timer_stop_ms() / reps
+
+    f_ms = timed(lambda: ctx.check(ctx.lib.fml_attention_fwd(ctx.h, ctypes.byref(de))))
+    b_ms = timed(lambda: ctx.check(ctx.lib.fml_attention_bwd(ctx.h, ctypes.byref(de), G.ptr, d, dqkv.ptr, dqkv.ptr + 4 * d,
+                                                            dqkv.ptr + 8 * d, 3 * d, 0, scratch.ptr)))
+    unit = 2.0 * n_seq * heads * seq_len * seq_len * dk
+    return {"shape": {"n_seq": n_seq, "seq_len": seq_len, "heads": heads, "d_head": dk, "causal": True},
+            "fwd_us": round(f_ms * 1e3, 1), "bwd_us": round(b_ms * 1e3, 1),
+            "fwd_tflops_full_square": round(2 * unit / f_ms / 1e9, 1), "bwd_tflops_full_square": round(5 * unit / b_ms / 1e9, 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -283,6 +318,8 @@ def main():
     ap.add_argument("--no-configs", action="store_true")
     ap.add_argument("--membound-only", action="store_true", help="run only the memory-bound kernel sweep (profiling)")
     ap.add_argument("--membound-rows", type=int, default=262144)
+    ap.add_argument("--attention-only", action="store_true", help="run only the fused attention kernels (profiling)")
+    ap.add_argument("--attention-seqs", type=int, default=32)
     ap.add_argument("--configs-only", action="store_true", help="run only configurations 1, 3, 4 (profiling)")
     ap.add_argument("--train-only", action="store_true", help="run only the data-parallel training step (profiling)")
     args = ap.parse_args()
@@ -329,6 +366,10 @@ def main():
     if args.configs_only:
         from flutter_ml_b200 import config_bench
         print(json.dumps({"configs": config_bench.run(ctx)}), flush=True)
+        ctx.close()
+        return
+    if args.attention_only:
+        print(json.dumps({"attention": time_attention(ctx, n_seq=args.attention_seqs, reps=2)}), flush=True)
         ctx.close()
         return
     if args.membound_only:
@@ -441,6 +482,7 @@ def main():
             line["legacy_roundtrip"] = legacy_roundtrip()
     if rank == 0 and not args.no_membound:
         line["membound"] = time_membound(ctx, peaks["hbm_gbs"], rows=args.membound_rows)
+        line["attention"] = time_attention(ctx)
     if rank == 0 and not args.no_cpu:
         from oracle import oracle
         oracle.build()

@@ -801,8 +801,14 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   const int nb1 = d->batch1 < 1 ? 1 : d->batch1, nb2 = d->batch2 < 1 ? 1 : d->batch2;
   // pair mode (256 x 256 tiles over two CTAs) when the problem has enough such tiles to occupy the
   // machine; FML_GEMM_PAIR=0/1 forces the choice (diagnostics)
-  bool pair = d->M > 128 && d->N > 128 &&
-              (long long)((d->M + 255) / 256) * ((d->N + 255) / 256) * nb1 * nb2 >= ctx->sm_count / 4;
+  const long long pair_tiles = (long long)((d->M + 255) / 256) * ((d->N + 255) / 256) * nb1 * nb2;
+  bool pair = d->M > 128 && d->N > 128 && pair_tiles >= ctx->sm_count / 4;
+  // A plain TF32 product with few output tiles but a long K (weight gradients: K = all tokens of the batch) can
+  // still fill the machine with 256 x 256 pair tiles if its K range is divided over several pairs; narrow single
+  // tiles ran such products at a third of the rate (1024 x 1024 x 16384: 180 TFLOP/s with 128 x 64 tiles).
+  const bool splittable = precision == FML_PREC_TF32 && !d->rowop && nb1 * nb2 == 1 && !d->bias && !d->preact &&
+                          d->act == FML_ACT_NONE && !lstm && !d->dact_saved && splitk_enabled();
+  if (!pair && splittable && d->M > 128 && d->N > 128 && pair_tiles * ((d->K + BK - 1) / BK / 8) >= ctx->sm_count / 4) pair = true;
   if (d->rowop) pair = false;  // a row block (128 rows x up to 512 columns) lives in ONE CTA's tensor memory
   {
     static int force = -2;
@@ -916,8 +922,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     // K split for plain TF32 products whose tiles occupy less than ~60 % of the SMs
     const long long tiles_all = (long long)tiles_m * tiles_n * nb1 * nb2;
     const long long ctas = tiles_all * (pair ? 2 : 1);
-    if (precision == FML_PREC_TF32 && !d->rowop && nb1 * nb2 == 1 && !d->bias && !d->preact && d->act == FML_ACT_NONE && !lstm && !d->dact_saved &&
-        ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 8 && splitk_enabled()) {
+    if (splittable && ctas * 5 < (long long)ctx->sm_count * 3 && p.kblocks >= 8) {
       int want = (int)(ctx->sm_count / ctas);                 // CTAs available per tile
       int maxs = p.kblocks / 4;                               // at least 128 k per split
       int ks = std::max(1, std::min(want, maxs));
