@@ -36,6 +36,7 @@ constexpr uint32_t TM_S = 0, TM_PV = 256;
 
 struct FaParams {
   int S, H, n_qb;        // sequence length, heads, query blocks per sequence
+  int n_items;           // n_seq * H * n_qb work items
   int causal;
   float k2;              // scale * log2(e)
   float* out; long long ld_out;
@@ -43,7 +44,7 @@ struct FaParams {
   int* status;
 };
 
-enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KVEMPTY = 5, B_SFULL = 7, B_SEMPTY = 9, B_PFULL = 11, B_PVFULL = 12, B_COUNT = 13 };
+enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KVEMPTY = 5, B_SFULL = 7, B_SEMPTY = 9, B_PFULL = 11, B_PVFULL = 12, B_QEMPTY = 13, B_COUNT = 14 };
 
 __device__ __forceinline__ uint32_t fa_idesc(int M, int N, int a_mn, int b_mn) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a_mn & 1) << 15) | ((uint32_t)(b_mn & 1) << 16) |
@@ -61,11 +62,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // work item: heavy (late) query blocks first, so the causal triangle balances over the grid
-  const int qb = p.n_qb - 1 - (int)(blockIdx.x % p.n_qb);
-  const int bh = blockIdx.x / p.n_qb;
-  const int h = bh % p.H, b = bh / p.H;
-  const int n_kv = p.causal ? qb + 1 : p.S / BKV;
+  // Persistent loop: this CTA takes work items blockIdx.x, blockIdx.x + gridDim.x, ...  Items are ordered heaviest
+  // first (all last query blocks, then the ones before, ...), so the causal triangle spreads evenly over the CTAs.
+  // Barrier phases are driven by running counters (g = key blocks processed so far, it = items), which lets the
+  // producer and the MMA issuer run ahead into the next item while the softmax warps finish the current one.
+  const int n_bh = p.n_items / p.n_qb;
+  auto item_coords = [&](int item, int& qb, int& h, int& b, int& n_kv) {
+    qb = p.n_qb - 1 - item / n_bh;
+    const int bh = item - (item / n_bh) * n_bh;
+    h = bh % p.H;
+    b = bh / p.H;
+    n_kv = p.causal ? qb + 1 : p.S / BKV;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < B_COUNT; i++) {
@@ -89,30 +97,44 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      mbar_expect_tx(bar(B_QFULL), BQ * DH * 4);
-      for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + kb * 16384, &tmQ, bar(B_QFULL), kb * 32, qb * BQ, h, b);
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; j++) {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        ok = mbar_wait(bar(B_KVEMPTY + s), ph ^ 1u, abort_flag, p.status, 11);
+      uint32_t g = 0, it = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        // Q is single-buffered: the previous item's last S product must have read it
+        ok = mbar_wait(bar(B_QEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 10);
         if (!ok) break;
-        mbar_expect_tx(bar(B_KFULL + s), BKV * DH * 4);
-        for (int kb = 0; kb < 2; kb++)
-          tma_load_4d(smem_base + OFF_K + s * 32768 + kb * 16384, &tmK, bar(B_KFULL + s), kb * 32, j * BKV, h, b);
-        mbar_expect_tx(bar(B_VFULL + s), BKV * DH * 4);
-        for (int c = 0; c < 4; c++)
-          tma_load_5d(smem_base + OFF_V + s * 32768 + c * 8192, &tmV, bar(B_VFULL + s), 0, j * BKV + 32 * c, 0, h, b);
+        mbar_expect_tx(bar(B_QFULL), BQ * DH * 4);
+        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + kb * 16384, &tmQ, bar(B_QFULL), kb * 32, qb * BQ, h, b);
+        for (int j = 0; j < n_kv && ok; j++, g++) {
+          const int s = g & 1;
+          const uint32_t ph = (g >> 1) & 1u;
+          ok = mbar_wait(bar(B_KVEMPTY + s), ph ^ 1u, abort_flag, p.status, 11);
+          if (!ok) break;
+          mbar_expect_tx(bar(B_KFULL + s), BKV * DH * 4);
+          for (int kb = 0; kb < 2; kb++)
+            tma_load_4d(smem_base + OFF_K + s * 32768 + kb * 16384, &tmK, bar(B_KFULL + s), kb * 32, j * BKV, h, b);
+          mbar_expect_tx(bar(B_VFULL + s), BKV * DH * 4);
+          for (int c = 0; c < 4; c++)
+            tma_load_5d(smem_base + OFF_V + s * 32768 + c * 8192, &tmV, bar(B_VFULL + s), 0, j * BKV + 32 * c, 0, h, b);
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc_s = fa_idesc(BQ, BKV, 0, 0), idesc_pv = fa_idesc(BQ, DH, 0, 1);
-      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, p.status, 12);
-      auto issue_s = [&](int j) {  // S_j = Q . K_j^T into buffer j & 1
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      bool ok = true;
+      // cursor of the next S product to issue: it runs one key block ahead of the P.V products, across item boundaries
+      int s_item = blockIdx.x, s_j = 0, s_nkv = 0;
+      uint32_t s_g = 0, s_it = 0;
+      if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
+      auto issue_next_s = [&]() {
+        if (s_item >= p.n_items) return true;
+        const int s = s_g & 1;
+        const uint32_t ph = (s_g >> 1) & 1u;
+        if (s_j == 0 && !mbar_wait(bar(B_QFULL), s_it & 1u, abort_flag, p.status, 12)) return false;
         if (!mbar_wait(bar(B_KFULL + s), ph, abort_flag, p.status, 13)) return false;
         if (!mbar_wait(bar(B_SEMPTY + s), ph ^ 1u, abort_flag, p.status, 14)) return false;
         tc_fence_after();
@@ -123,65 +145,122 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + s * 128, ad + 2u * k, bd + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
         }
         umma_commit(bar(B_SFULL + s));
+        s_g++;
+        if (++s_j == s_nkv) {   // last S of its item: Q may be replaced
+          umma_commit(bar(B_QEMPTY));
+          s_item += gridDim.x;
+          s_it++;
+          s_j = 0;
+          if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
+        }
         return true;
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; j++) {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (j + 1 < n_kv) ok = issue_s(j + 1);
-        if (!ok) break;
-        ok = mbar_wait(bar(B_PFULL), (uint32_t)j & 1u, abort_flag, p.status, 15) &&
-             mbar_wait(bar(B_VFULL + s), ph, abort_flag, p.status, 16);
-        if (!ok) break;
-        tc_fence_after();
-        for (int c = 0; c < 4; c++) {  // 32 keys per chunk
-          const uint64_t ad = make_smem_desc(smem_base + OFF_P + c * 16384, 16u, 1024u, 2u);
-          const uint64_t bd = make_smem_desc(smem_base + OFF_V + s * 32768 + c * 8192, 4096u, 512u, 1u);
+      uint32_t g = 0;
+      ok = issue_next_s();
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        for (int j = 0; j < n_kv && ok; j++, g++) {
+          const int s = g & 1;
+          const uint32_t ph = (g >> 1) & 1u;
+          if (s_g == g + 1) ok = issue_next_s();   // keep one S product ahead
+          if (!ok) break;
+          ok = mbar_wait(bar(B_PFULL), g & 1u, abort_flag, p.status, 15) && mbar_wait(bar(B_VFULL + s), ph, abort_flag, p.status, 16);
+          if (!ok) break;
+          tc_fence_after();
+          for (int c = 0; c < 4; c++) {  // 32 keys per chunk
+            const uint64_t ad = make_smem_desc(smem_base + OFF_P + c * 16384, 16u, 1024u, 2u);
+            const uint64_t bd = make_smem_desc(smem_base + OFF_V + s * 32768 + c * 8192, 4096u, 512u, 1u);
 #pragma unroll
-          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_PV, ad + 2u * k, bd + 64u * k, idesc_pv, (c | k) ? 1u : 0u);
+            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_PV, ad + 2u * k, bd + 64u * k, idesc_pv, (c | k) ? 1u : 0u);
+          }
+          umma_commit(bar(B_PVFULL));       // PV readable, P free again
+          umma_commit(bar(B_KVEMPTY + s));  // K and V of this block consumed
         }
-        umma_commit(bar(B_PVFULL));       // PV_j readable, P free again
-        umma_commit(bar(B_KVEMPTY + s));  // K_j and V_j consumed
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax / output
     const int q4 = warp & 3;                        // TMEM lane quarter of this warp
     const int row = q4 * 32 + lane;                 // row inside the query block
-    const int qi = qb * BQ + row;                   // position in the sequence
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
-    float m = -INFINITY, l = 0.f;
-    float o[DH];
-#pragma unroll
-    for (int i = 0; i < DH; i++) o[i] = 0.f;
     bool ok = true;
     uint32_t v[32];
-    for (int j = 0; j < n_kv && ok; j++) {
-      const int s = j & 1;
-      ok = mbar_wait(bar(B_SFULL + s), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, 17);
-      if (!ok) break;
-      tc_fence_after();
-      const bool diag = p.causal && j == qb;
-      const int lim = diag ? row + 1 : BKV;        // valid keys of this row inside the block
-      // pass 1: row maximum of the scaled scores
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 128 dependent maxima
-      for (int c = 0; c < 4; c++) {
-        tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
-        tmem_ld_wait();
+    uint32_t g = 0;
+    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      int qb, h, b, n_kv;
+      item_coords(item, qb, h, b, n_kv);
+      const int qi = qb * BQ + row;                 // position in the sequence
+      float m = -INFINITY, l = 0.f;
+      float o[DH];
 #pragma unroll
-        for (int e = 0; e < 32; e++) {
-          const float sc = (c * 32 + e < lim) ? __uint_as_float(v[e]) : -INFINITY;
-          mx4[e & 3] = fmaxf(mx4[e & 3], sc);
-        }
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.k2;   // k2 > 0: max commutes with the scale
-      const float m_new = fmaxf(m, mx);            // finite: key 0 is visible to every row
-      const float alpha = exp2f(m - m_new);        // 0 for the first block (m = -inf)
-      // the previous block's P.V must be folded in (and P be free) before P is overwritten
-      if (j > 0) {
-        ok = mbar_wait(bar(B_PVFULL), (uint32_t)(j - 1) & 1u, abort_flag, p.status, 18);
+      for (int i = 0; i < DH; i++) o[i] = 0.f;
+      for (int j = 0; j < n_kv && ok; j++, g++) {
+        const int s = g & 1;
+        ok = mbar_wait(bar(B_SFULL + s), (g >> 1) & 1u, abort_flag, p.status, 17);
         if (!ok) break;
+        tc_fence_after();
+        const bool diag = p.causal && j == qb;
+        const int lim = diag ? row + 1 : BKV;        // valid keys of this row inside the block
+        // pass 1: row maximum of the scores (four chains instead of one of 128 dependent maxima)
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        for (int c = 0; c < 4; c++) {
+          tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e++) {
+            const float sc = (c * 32 + e < lim) ? __uint_as_float(v[e]) : -INFINITY;
+            mx4[e & 3] = fmaxf(mx4[e & 3], sc);
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.k2;   // k2 > 0: max commutes with the scale
+        const float m_new = fmaxf(m, mx);            // finite: key 0 is visible to every row
+        const float alpha = exp2f(m - m_new);        // 0 for the first block (m = -inf)
+        // the previous block's P.V must be folded in (and P be free) before P is overwritten
+        if (j > 0) {
+          ok = mbar_wait(bar(B_PVFULL), (g - 1) & 1u, abort_flag, p.status, 18);
+          if (!ok) break;
+          tc_fence_after();
+          for (int c = 0; c < 2; c++) {
+            tmem_ld32(lane_addr + TM_PV + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; e++) o[c * 32 + e] += __uint_as_float(v[e]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < DH; i++) o[i] *= alpha;
+        l *= alpha;
+        // pass 2: probabilities (unnormalised) into the K-major operand layout: k-block c = 32 keys = one 128-byte row
+        // per query, 16-byte chunks XOR-swizzled with the row index
+        float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < 4; c++) {
+          tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
+          tmem_ld_wait();
+          uint8_t* prow = smem_gen + OFF_P + c * 16384 + row * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ch++) {
+            float4 pv;
+            float* pe = reinterpret_cast<float*>(&pv);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const int col = c * 32 + ch * 4 + e;
+              const float pr = (col < lim) ? exp2f(fmaf(__uint_as_float(v[ch * 4 + e]), p.k2, -m_new)) : 0.f;
+              pe[e] = pr;
+              ls4[e] += pr;
+            }
+            *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
+          }
+        }
+        l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        m = m_new;
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(bar(B_PFULL));
+        mbar_arrive(bar(B_SEMPTY + s));
+      }
+      if (ok) ok = mbar_wait(bar(B_PVFULL), (g - 1) & 1u, abort_flag, p.status, 19);
+      if (ok) {
         tc_fence_after();
         for (int c = 0; c < 2; c++) {
           tmem_ld32(lane_addr + TM_PV + c * 32, v);
@@ -189,53 +268,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int e = 0; e < 32; e++) o[c * 32 + e] += __uint_as_float(v[e]);
         }
+        // the P.V accumulator has been read: order these loads before the next item's first P.V product
+        tc_fence_before();
+        const float inv = 1.f / l;
+        float* orow = p.out + ((long long)b * p.S + qi) * p.ld_out + h * DH;
+#pragma unroll
+        for (int i = 0; i < DH; i += 4)
+          *reinterpret_cast<float4*>(orow + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+        if (p.lse) p.lse[((long long)b * p.H + h) * p.S + qi] = m + log2f(l);
       }
-#pragma unroll
-      for (int i = 0; i < DH; i++) o[i] *= alpha;
-      l *= alpha;
-      // pass 2: probabilities (unnormalised) into the K-major operand layout: k-block c = 32 keys = one 128-byte row
-      // per query, 16-byte chunks XOR-swizzled with the row index
-      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int c = 0; c < 4; c++) {
-        tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
-        tmem_ld_wait();
-        uint8_t* prow = smem_gen + OFF_P + c * 16384 + row * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-          float4 pv;
-          float* pe = reinterpret_cast<float*>(&pv);
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const int col = c * 32 + ch * 4 + e;
-            const float pr = (col < lim) ? exp2f(fmaf(__uint_as_float(v[ch * 4 + e]), p.k2, -m_new)) : 0.f;
-            pe[e] = pr;
-            ls4[e] += pr;
-          }
-          *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
-        }
-      }
-      l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-      m = m_new;
-      tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(bar(B_PFULL));
-      mbar_arrive(bar(B_SEMPTY + s));
-    }
-    if (ok) ok = mbar_wait(bar(B_PVFULL), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 19);
-    if (ok) {
-      tc_fence_after();
-      for (int c = 0; c < 2; c++) {
-        tmem_ld32(lane_addr + TM_PV + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; e++) o[c * 32 + e] += __uint_as_float(v[e]);
-      }
-      const float inv = 1.f / l;
-      float* orow = p.out + ((long long)b * p.S + qi) * p.ld_out + h * DH;
-#pragma unroll
-      for (int i = 0; i < DH; i += 4)
-        *reinterpret_cast<float4*>(orow + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
-      if (p.lse) p.lse[((long long)b * p.H + h) * p.S + qi] = m + log2f(l);
     }
   }
   tc_fence_before();
@@ -246,6 +287,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
 }
 
+}  // namespace
+
+namespace {
 
 // ------------------------------------------------------------------------------------------------------------
 // Backward, first kernel: for one block of 128 queries it rebuilds the probabilities of every key block from the
@@ -688,9 +732,11 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
     FML_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
     attr_set = true;
   }
-  const long long grid = (long long)Bn * H * p.n_qb;
-  FML_REQUIRE(ctx, grid <= 0x7fffffffLL, "fml_attention_fwd: too many work items");
-  attention_fwd_kernel<<<(unsigned)grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
+  const long long items = (long long)Bn * H * p.n_qb;
+  FML_REQUIRE(ctx, items <= 0x7fffffffLL, "fml_attention_fwd: too many work items");
+  p.n_items = (int)items;
+  const unsigned grid = (unsigned)std::min<long long>(items, ctx->sm_count);
+  attention_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
   FML_LAUNCH_CHECK(ctx, "attention_fwd_kernel");
   return FML_OK;
 }
