@@ -67,7 +67,47 @@ def rows():
                         softmax_bwd=dsm, ln_y=y, ln_dx=dx, ln_dgamma=dg, ln_dbeta=db)
 
 
+def widened():
+    """The later additions in one file: the six optimizer rules over three steps, the four parameterised activations,
+    conv2d ('same', 3 x 3) with its gradients, and one causal attention head (output and dQ, dK, dV)."""
+    ops = oracle.Ops()
+    d = {}
+    n = 37
+    w0 = synth.normal(7, 0, (n,))
+    grads = [synth.normal(7, 1 + t, (n,)) for t in range(3)]
+    d["opt_w0"], d["opt_grads"] = w0, np.stack(grads)
+    for kind, h, nstate in ((1, (0.9,), 1), (2, (0.9,), 1), (3, (0.9, 1e-8), 1), (4, (0.0, 1e-8), 1),
+                            (6, (0.9, 0.999, 1e-8, 0.01), 2), (7, (0.9, 0.999, 1e-8), 3)):
+        w = w64(w0)
+        st = [np.zeros(n) for _ in range(nstate)] + [None] * (3 - nstate)
+        for t, g in enumerate(grads, 1):
+            ops.optimizer_step(kind, w, w64(g), st[0], st[1], st[2], 0.01, h, t)
+        d[f"opt_w_kind{kind}"] = w
+    x = synth.normal(7, 10, (64,), 3.0)
+    dy = synth.normal(7, 11, (64,))
+    d["act_x"], d["act_dy"] = x, dy
+    for kind, alpha in ((5, 0.01), (6, 1.0), (7, 0.0), (8, 0.0)):
+        d[f"act_y_kind{kind}"] = ops.act2_fwd(kind, alpha, w64(x))
+        dx = np.zeros(64)
+        ops.act2_bwd(kind, alpha, w64(x), w64(dy), dx)
+        d[f"act_dx_kind{kind}"] = dx
+    img, ker, dout = synth.normal(7, 20, (9, 11)), synth.normal(7, 21, (3, 3)), synth.normal(7, 22, (9, 11))
+    d["conv_x"], d["conv_k"], d["conv_dout"] = img, ker, dout
+    d["conv_out"] = ops.conv2d_fwd(w64(img), w64(ker), 1)
+    dimg, dker = np.zeros((9, 11)), np.zeros((3, 3))
+    ops.conv2d_bwd(w64(img), w64(ker), w64(dout), dimg, dker, 1)
+    d["conv_dx"], d["conv_dk"] = dimg, dker
+    S, dk = 128, 64
+    Q, K, V, G = (synth.normal(7, 30 + i, (S, dk)) for i in range(4))
+    E = oracle.Engine()
+    tq, tk, tv = oracle.T(w64(Q)), oracle.T(w64(K)), oracle.T(w64(V))
+    O = E.matMul(E.softmaxMatrix(E.scaleMatrix(E.matMul(tq, E.transpose(tk)), 0.125), True), tv)
+    E.sum(E.elementWiseMultiply(O, oracle.T(w64(G)))).backward()
+    d.update(att_q=Q, att_k=K, att_v=V, att_g=G, att_out=O.value, att_dq=tq.grad, att_dk=tk.grad, att_dv=tv.grad)
+    np.savez_compressed(os.path.join(HERE, "widened_ops.npz"), **d)
+
+
 if __name__ == "__main__":
     oracle.build()
-    gemm_gelu(); mlp(); lstm(); rows()
+    gemm_gelu(); mlp(); lstm(); rows(); widened()
     print(sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
