@@ -483,13 +483,16 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 //   dV_j += P^T . dO_i      dK_j += dS^T . Q_i        (dO_i and Q_i as MN-major B operands)
 // Nothing score-sized is written to global memory.  Query blocks are 64 rows here (shared memory budget):
 //   K_j, V_j 32 KiB each (resident), Q_i, dO_i as K-major and as MN-major tiles 16 KiB each, P^T, dS^T 32 KiB each.
-// TMEM: S^T [0,64), dP^T [64,128), dV [128,192), dK [192,256).
+// TMEM: two buffers of S^T / dP^T ([0,128) and [128,256)), dV [256,320), dK [320,384): the score products of the next
+// query block run while the compute warps work on the current one.  The K-major copies of Q_i / dO_i are released as
+// soon as the score products have read them, the MN-major copies after the accumulating products.
 constexpr int BQ2 = 64;
 constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 81920, CO_QMN = 98304, CO_DOMN = 114688, CO_PT = 131072,
                    CO_DST = 163840, CO_STAT = 196608, CO_BAR = 197632;
 constexpr int FA2_SMEM = CO_BAR + 256 + 1024;
-constexpr uint32_t T2_ST = 0, T2_DPT = 64, T2_DV = 128, T2_DK = 192;
-enum { D_KVFULL = 0, D_QFULL = 1, D_QEMPTY = 2, D_STFULL = 3, D_STEMPTY = 4, D_PTFULL = 5, D_ACCDONE = 6, D_COUNT = 7 };
+constexpr uint32_t T2_ST = 0, T2_DPT = 64, T2_BUF = 128, T2_DV = 256, T2_DK = 320;   // S^T / dP^T double-buffered (+T2_BUF)
+enum { D_KVFULL = 0, D_QKFULL = 1, D_QKEMPTY = 2, D_QMNFULL = 3, D_QMNEMPTY = 4, D_STFULL = 5, D_STEMPTY = 7, D_PTFULL = 9,
+       D_ACCDONE = 10, D_COUNT = 11 };
 
 struct FaBwd2Params {
   int S, H, n_kb, causal;
@@ -521,13 +524,13 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   const int n_it = n_q - i0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_STEMPTY || i == D_PTFULL) ? 256u : 1u);
+    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_STEMPTY || i == D_STEMPTY + 1 || i == D_PTFULL) ? 256u : 1u);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -546,17 +549,20 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       bool ok = true;
       for (int it = 0; it < n_it && ok; it++) {
         const uint32_t ph = (uint32_t)it & 1u;
-        ok = mbar_wait(bar(D_QEMPTY), ph ^ 1u, abort_flag, p.status, 31);
-        if (!ok) break;
         const int q0 = (i0 + it) * BQ2;
-        mbar_expect_tx(bar(D_QFULL), 4 * BQ2 * DH * 4);
+        ok = mbar_wait(bar(D_QKEMPTY), ph ^ 1u, abort_flag, p.status, 31);
+        if (!ok) break;
+        mbar_expect_tx(bar(D_QKFULL), 2 * BQ2 * DH * 4);
         for (int kb = 0; kb < 2; kb++) {
-          tma_load_4d(smem_base + CO_Q + kb * 8192, &tmQ, bar(D_QFULL), kb * 32, q0, h, b);
-          tma_load_4d(smem_base + CO_DO + kb * 8192, &tmDO, bar(D_QFULL), kb * 32, q0, h, b);
+          tma_load_4d(smem_base + CO_Q + kb * 8192, &tmQ, bar(D_QKFULL), kb * 32, q0, h, b);
+          tma_load_4d(smem_base + CO_DO + kb * 8192, &tmDO, bar(D_QKFULL), kb * 32, q0, h, b);
         }
+        ok = mbar_wait(bar(D_QMNEMPTY), ph ^ 1u, abort_flag, p.status, 39);
+        if (!ok) break;
+        mbar_expect_tx(bar(D_QMNFULL), 2 * BQ2 * DH * 4);
         for (int c = 0; c < 2; c++) {
-          tma_load_5d(smem_base + CO_QMN + c * 8192, &tmQmn, bar(D_QFULL), 0, q0 + 32 * c, 0, h, b);
-          tma_load_5d(smem_base + CO_DOMN + c * 8192, &tmDOmn, bar(D_QFULL), 0, q0 + 32 * c, 0, h, b);
+          tma_load_5d(smem_base + CO_QMN + c * 8192, &tmQmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
+          tma_load_5d(smem_base + CO_DOMN + c * 8192, &tmDOmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
         }
       }
     }
@@ -564,10 +570,10 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     if (lane == 0) {
       const uint32_t idesc_st = fa_idesc(BKV, BQ2, 0, 0), idesc_acc = fa_idesc(BKV, DH, 0, 1);
       bool ok = mbar_wait(bar(D_KVFULL), 0, abort_flag, p.status, 32);
-      for (int it = 0; it < n_it && ok; it++) {
-        const uint32_t ph = (uint32_t)it & 1u;
-        ok = mbar_wait(bar(D_QFULL), ph, abort_flag, p.status, 33) && mbar_wait(bar(D_STEMPTY), ph ^ 1u, abort_flag, p.status, 34);
-        if (!ok) break;
+      auto issue_scores = [&](int it) {   // S^T and dP^T of query block `it` into TMEM buffer it & 1
+        const int bf = it & 1;
+        if (!mbar_wait(bar(D_QKFULL), (uint32_t)it & 1u, abort_flag, p.status, 33)) return false;
+        if (!mbar_wait(bar(D_STEMPTY + bf), (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag, p.status, 34)) return false;
         tc_fence_after();
         for (int kb = 0; kb < 2; kb++) {
           const uint64_t ak = make_smem_desc(smem_base + CO_K + kb * 16384, 16u, 1024u, 2u);
@@ -576,12 +582,20 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           const uint64_t bd = make_smem_desc(smem_base + CO_DO + kb * 8192, 16u, 1024u, 2u);
 #pragma unroll
           for (int k = 0; k < 4; k++) {
-            umma_tf32(tmem_base + T2_ST, ak + 2u * k, bq + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
-            umma_tf32(tmem_base + T2_DPT, av + 2u * k, bd + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
+            umma_tf32(tmem_base + bf * T2_BUF + T2_ST, ak + 2u * k, bq + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
+            umma_tf32(tmem_base + bf * T2_BUF + T2_DPT, av + 2u * k, bd + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
           }
         }
-        umma_commit(bar(D_STFULL));
-        ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35);
+        umma_commit(bar(D_STFULL + bf));
+        umma_commit(bar(D_QKEMPTY));   // the K-major copies of Q_i, dO_i may be replaced
+        return true;
+      };
+      if (ok && n_it > 0) ok = issue_scores(0);
+      for (int it = 0; it < n_it && ok; it++) {
+        const uint32_t ph = (uint32_t)it & 1u;
+        if (it + 1 < n_it) ok = issue_scores(it + 1);   // overlaps the compute warps' work on block `it`
+        if (!ok) break;
+        ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35) && mbar_wait(bar(D_QMNFULL), ph, abort_flag, p.status, 40);
         if (!ok) break;
         tc_fence_after();
         for (int c = 0; c < 2; c++) {   // 32 queries per chunk
@@ -596,7 +610,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           }
         }
         umma_commit(bar(D_ACCDONE));
-        umma_commit(bar(D_QEMPTY));
+        umma_commit(bar(D_QMNEMPTY));
       }
     }
   } else {
@@ -615,14 +629,15 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       // the one it needs with a shuffle (no block-wide barrier inside a loop whose waits can give up)
       const float2 Lq = __ldg(reinterpret_cast<const float2*>(p.lse + stat_base + q0) + lane);
       const float2 Dq = __ldg(reinterpret_cast<const float2*>(p.dsum + stat_base + q0) + lane);
-      ok = mbar_wait(bar(D_STFULL), ph, abort_flag, p.status, 36);
+      const int bf = it & 1;
+      ok = mbar_wait(bar(D_STFULL + bf), ((uint32_t)it >> 1) & 1u, abort_flag, p.status, 36);
       if (ok && it > 0) ok = mbar_wait(bar(D_ACCDONE), ph ^ 1u, abort_flag, p.status, 37);   // P^T / dS^T tiles free again
       if (!ok) break;
       tc_fence_after();
       {
         const int c = half;
-        tmem_ld32(lane_addr + T2_ST + c * 32, sv);
-        tmem_ld32(lane_addr + T2_DPT + c * 32, dv);
+        tmem_ld32(lane_addr + bf * T2_BUF + T2_ST + c * 32, sv);
+        tmem_ld32(lane_addr + bf * T2_BUF + T2_DPT + c * 32, dv);
         tmem_ld_wait();
         uint8_t* prow = smem_gen + CO_PT + c * 16384 + row * 128;
         uint8_t* srow = smem_gen + CO_DST + c * 16384 + row * 128;
@@ -648,7 +663,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(bar(D_PTFULL));
-      mbar_arrive(bar(D_STEMPTY));
+      mbar_arrive(bar(D_STEMPTY + bf));
     }
     if (ok && n_it > 0) ok = mbar_wait(bar(D_ACCDONE), (uint32_t)(n_it - 1) & 1u, abort_flag, p.status, 38);
     if (ok) {
@@ -677,7 +692,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
