@@ -302,10 +302,11 @@ namespace {
 constexpr uint32_t BO_Q = 0, BO_DO = 32768, BO_K = 65536, BO_V = 98304, BO_KMN = 131072, BO_DS = 163840;
 constexpr uint32_t TM_DP = 128, TM_DQ = 256;
 enum { C_QFULL = 0, C_KVFULL = 1, C_KVEMPTY = 2, C_KMNFULL = 3, C_KMNEMPTY = 4, C_SDPFULL = 5, C_SDPEMPTY = 6, C_DSFULL = 7,
-       C_DQDONE = 8, C_COUNT = 9 };
+       C_DQDONE = 8, C_QEMPTY = 9, C_COUNT = 10 };
 
 struct FaBwdParams {
   int S, H, n_qb, causal;
+  int n_items;
   float k2, scale;
   const float* lse;   // [n_seq][H][S]
   const float* dsum;  // [n_seq][H][S]: D = rowsum(dO * O)
@@ -325,10 +326,15 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + 8 * C_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = p.n_qb - 1 - (int)(blockIdx.x % p.n_qb);
-  const int bh = blockIdx.x / p.n_qb;
-  const int h = bh % p.H, b = bh / p.H;
-  const int n_kv = p.causal ? qb + 1 : p.S / BKV;
+  // persistent loop over work items (heaviest first), barrier phases from running counters: g = key blocks, it = items
+  const int n_bh = p.n_items / p.n_qb;
+  auto item_coords = [&](int item, int& qb, int& h, int& b, int& n_kv) {
+    qb = p.n_qb - 1 - item / n_bh;
+    const int bh = item - (item / n_bh) * n_bh;
+    h = bh % p.H;
+    b = bh / p.H;
+    n_kv = p.causal ? qb + 1 : p.S / BKV;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C_COUNT; i++) mbar_init(bar(i), (i == C_SDPEMPTY || i == C_DSFULL) ? 256u : 1u);
@@ -348,111 +354,129 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(bar(C_QFULL), 2 * BQ * DH * 4);
-      for (int kb = 0; kb < 2; kb++) {
-        tma_load_4d(smem_base + BO_Q + kb * 16384, &tmQ, bar(C_QFULL), kb * 32, qb * BQ, h, b);
-        tma_load_4d(smem_base + BO_DO + kb * 16384, &tmDO, bar(C_QFULL), kb * 32, qb * BQ, h, b);
-      }
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; j++) {
-        const uint32_t ph = (uint32_t)j & 1u;
-        ok = mbar_wait(bar(C_KVEMPTY), ph ^ 1u, abort_flag, p.status, 21);
+      uint32_t g = 0, it = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        ok = mbar_wait(bar(C_QEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 20);   // previous item's score products done
         if (!ok) break;
-        mbar_expect_tx(bar(C_KVFULL), 2 * BKV * DH * 4);
+        mbar_expect_tx(bar(C_QFULL), 2 * BQ * DH * 4);
         for (int kb = 0; kb < 2; kb++) {
-          tma_load_4d(smem_base + BO_K + kb * 16384, &tmK, bar(C_KVFULL), kb * 32, j * BKV, h, b);
-          tma_load_4d(smem_base + BO_V + kb * 16384, &tmV, bar(C_KVFULL), kb * 32, j * BKV, h, b);
+          tma_load_4d(smem_base + BO_Q + kb * 16384, &tmQ, bar(C_QFULL), kb * 32, qb * BQ, h, b);
+          tma_load_4d(smem_base + BO_DO + kb * 16384, &tmDO, bar(C_QFULL), kb * 32, qb * BQ, h, b);
         }
-        ok = mbar_wait(bar(C_KMNEMPTY), ph ^ 1u, abort_flag, p.status, 22);
-        if (!ok) break;
-        mbar_expect_tx(bar(C_KMNFULL), BKV * DH * 4);
-        for (int c = 0; c < 4; c++) tma_load_5d(smem_base + BO_KMN + c * 8192, &tmKmn, bar(C_KMNFULL), 0, j * BKV + 32 * c, 0, h, b);
+        for (int j = 0; j < n_kv && ok; j++, g++) {
+          const uint32_t ph = g & 1u;
+          ok = mbar_wait(bar(C_KVEMPTY), ph ^ 1u, abort_flag, p.status, 21);
+          if (!ok) break;
+          mbar_expect_tx(bar(C_KVFULL), 2 * BKV * DH * 4);
+          for (int kb = 0; kb < 2; kb++) {
+            tma_load_4d(smem_base + BO_K + kb * 16384, &tmK, bar(C_KVFULL), kb * 32, j * BKV, h, b);
+            tma_load_4d(smem_base + BO_V + kb * 16384, &tmV, bar(C_KVFULL), kb * 32, j * BKV, h, b);
+          }
+          ok = mbar_wait(bar(C_KMNEMPTY), ph ^ 1u, abort_flag, p.status, 22);
+          if (!ok) break;
+          mbar_expect_tx(bar(C_KMNFULL), BKV * DH * 4);
+          for (int c = 0; c < 4; c++) tma_load_5d(smem_base + BO_KMN + c * 8192, &tmKmn, bar(C_KMNFULL), 0, j * BKV + 32 * c, 0, h, b);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = fa_idesc(BQ, BKV, 0, 0), idesc_dq = fa_idesc(BQ, DH, 0, 1);
-      bool ok = mbar_wait(bar(C_QFULL), 0, abort_flag, p.status, 23);
-      for (int j = 0; j < n_kv && ok; j++) {
-        const uint32_t ph = (uint32_t)j & 1u;
-        ok = mbar_wait(bar(C_KVFULL), ph, abort_flag, p.status, 24) && mbar_wait(bar(C_SDPEMPTY), ph ^ 1u, abort_flag, p.status, 25);
-        if (!ok) break;
-        tc_fence_after();
-        for (int kb = 0; kb < 2; kb++) {
-          const uint64_t aq = make_smem_desc(smem_base + BO_Q + kb * 16384, 16u, 1024u, 2u);
-          const uint64_t bk = make_smem_desc(smem_base + BO_K + kb * 16384, 16u, 1024u, 2u);
+      bool ok = true;
+      uint32_t g = 0, it = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        ok = mbar_wait(bar(C_QFULL), it & 1u, abort_flag, p.status, 23);
+        for (int j = 0; j < n_kv && ok; j++, g++) {
+          const uint32_t ph = g & 1u;
+          ok = mbar_wait(bar(C_KVFULL), ph, abort_flag, p.status, 24) && mbar_wait(bar(C_SDPEMPTY), ph ^ 1u, abort_flag, p.status, 25);
+          if (!ok) break;
+          tc_fence_after();
+          for (int kb = 0; kb < 2; kb++) {
+            const uint64_t aq = make_smem_desc(smem_base + BO_Q + kb * 16384, 16u, 1024u, 2u);
+            const uint64_t bk = make_smem_desc(smem_base + BO_K + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
-          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S, aq + 2u * k, bk + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
-        }
-        for (int kb = 0; kb < 2; kb++) {
-          const uint64_t ad = make_smem_desc(smem_base + BO_DO + kb * 16384, 16u, 1024u, 2u);
-          const uint64_t bv = make_smem_desc(smem_base + BO_V + kb * 16384, 16u, 1024u, 2u);
+            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S, aq + 2u * k, bk + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+          }
+          for (int kb = 0; kb < 2; kb++) {
+            const uint64_t ad = make_smem_desc(smem_base + BO_DO + kb * 16384, 16u, 1024u, 2u);
+            const uint64_t bv = make_smem_desc(smem_base + BO_V + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
-          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DP, ad + 2u * k, bv + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
-        }
-        umma_commit(bar(C_SDPFULL));
-        umma_commit(bar(C_KVEMPTY));
-        ok = mbar_wait(bar(C_DSFULL), ph, abort_flag, p.status, 26) && mbar_wait(bar(C_KMNFULL), ph, abort_flag, p.status, 27);
-        if (!ok) break;
-        tc_fence_after();
-        for (int c = 0; c < 4; c++) {
-          const uint64_t ad = make_smem_desc(smem_base + BO_DS + c * 16384, 16u, 1024u, 2u);
-          const uint64_t bd = make_smem_desc(smem_base + BO_KMN + c * 8192, 4096u, 512u, 1u);
+            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DP, ad + 2u * k, bv + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(bar(C_SDPFULL));
+          umma_commit(bar(C_KVEMPTY));
+          if (j == n_kv - 1) umma_commit(bar(C_QEMPTY));   // Q and dO of this item are no longer read
+          ok = mbar_wait(bar(C_DSFULL), ph, abort_flag, p.status, 26) && mbar_wait(bar(C_KMNFULL), ph, abort_flag, p.status, 27);
+          if (!ok) break;
+          tc_fence_after();
+          for (int c = 0; c < 4; c++) {
+            const uint64_t ad = make_smem_desc(smem_base + BO_DS + c * 16384, 16u, 1024u, 2u);
+            const uint64_t bd = make_smem_desc(smem_base + BO_KMN + c * 8192, 4096u, 512u, 1u);
 #pragma unroll
-          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DQ, ad + 2u * k, bd + 64u * k, idesc_dq, (j | c | k) ? 1u : 0u);
+            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DQ, ad + 2u * k, bd + 64u * k, idesc_dq, (j | c | k) ? 1u : 0u);
+          }
+          umma_commit(bar(C_DQDONE));
+          umma_commit(bar(C_KMNEMPTY));
         }
-        umma_commit(bar(C_DQDONE));
-        umma_commit(bar(C_KMNEMPTY));
       }
     }
   } else {
     const int q4 = warp & 3;
     const int half = (warp - 2) >> 2;   // the two warps of a lane quarter take alternate 32-column chunks
     const int row = q4 * 32 + lane;
-    const int qi = qb * BQ + row;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
-    const long long stat = ((long long)b * p.H + h) * p.S + qi;
-    const float L = p.lse[stat], Dv = p.dsum[stat];
     bool ok = true;
     uint32_t sv[32], dv[32];
-    for (int j = 0; j < n_kv && ok; j++) {
-      const uint32_t ph = (uint32_t)j & 1u;
-      ok = mbar_wait(bar(C_SDPFULL), ph, abort_flag, p.status, 28);
-      if (ok && j > 0) ok = mbar_wait(bar(C_DQDONE), ph ^ 1u, abort_flag, p.status, 29);  // dS tile free again
-      if (!ok) break;
-      tc_fence_after();
-      const int lim = (p.causal && j == qb) ? row + 1 : BKV;
-      for (int c = half; c < 4; c += 2) {
-        tmem_ld32(lane_addr + TM_S + c * 32, sv);
-        tmem_ld32(lane_addr + TM_DP + c * 32, dv);
-        tmem_ld_wait();
-        uint8_t* srow = smem_gen + BO_DS + c * 16384 + row * 128;
+    uint32_t g = 0;
+    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      int qb, h, b, n_kv;
+      item_coords(item, qb, h, b, n_kv);
+      const int qi = qb * BQ + row;
+      const long long stat = ((long long)b * p.H + h) * p.S + qi;
+      const float L = p.lse[stat], Dv = p.dsum[stat];
+      for (int j = 0; j < n_kv && ok; j++, g++) {
+        const uint32_t ph = g & 1u;
+        ok = mbar_wait(bar(C_SDPFULL), ph, abort_flag, p.status, 28);
+        if (ok && j > 0) ok = mbar_wait(bar(C_DQDONE), ph ^ 1u, abort_flag, p.status, 29);  // dS tile free again
+        if (!ok) break;
+        tc_fence_after();
+        const int lim = (p.causal && j == qb) ? row + 1 : BKV;
+        for (int c = half; c < 4; c += 2) {
+          tmem_ld32(lane_addr + TM_S + c * 32, sv);
+          tmem_ld32(lane_addr + TM_DP + c * 32, dv);
+          tmem_ld_wait();
+          uint8_t* srow = smem_gen + BO_DS + c * 16384 + row * 128;
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-          float4 dsv;
-          float* de = reinterpret_cast<float*>(&dsv);
+          for (int ch = 0; ch < 8; ch++) {
+            float4 dsv;
+            float* de = reinterpret_cast<float*>(&dsv);
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const int col = c * 32 + ch * 4 + e;
-            const float pr = (col < lim) ? exp2f(__uint_as_float(sv[ch * 4 + e]) * p.k2 - L) : 0.f;
-            de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dv) * p.scale;
+            for (int e = 0; e < 4; e++) {
+              const int col = c * 32 + ch * 4 + e;
+              const float pr = (col < lim) ? exp2f(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -L)) : 0.f;
+              de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dv) * p.scale;
+            }
+            *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
           }
-          *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
         }
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(bar(C_DSFULL));
+        mbar_arrive(bar(C_SDPEMPTY));
       }
-      tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(bar(C_DSFULL));
-      mbar_arrive(bar(C_SDPEMPTY));
-    }
-    if (ok) ok = mbar_wait(bar(C_DQDONE), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 30);
-    if (ok) {
-      tc_fence_after();
-      float* qrow = p.dq + ((long long)b * p.S + qi) * p.ld_dq + h * DH;
-      {
+      if (ok) ok = mbar_wait(bar(C_DQDONE), (g - 1) & 1u, abort_flag, p.status, 30);
+      if (ok) {
+        tc_fence_after();
+        float* qrow = p.dq + ((long long)b * p.S + qi) * p.ld_dq + h * DH;
         const int c = half;
         tmem_ld32(lane_addr + TM_DQ + c * 32, sv);
         tmem_ld_wait();
+        tc_fence_before();   // the accumulator has been read before this thread publishes the next item's first dS
 #pragma unroll
         for (int e = 0; e < 32; e += 4) {
           float4 o = make_float4(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1]), __uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3]));
@@ -799,7 +823,8 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   p.lse = d->lse; p.dsum = dsum;
   p.dq = dq; p.ld_dq = ld_dqkv; p.accumulate = accumulate ? 1 : 0;
   p.status = ctx->d_status;
-  attention_bwd_dq_kernel<<<grid, FA_BWD_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, p);
+  p.n_items = (int)grid;
+  attention_bwd_dq_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, p);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dq_kernel");
   FaBwd2Params p2;
   p2.S = S; p2.H = H; p2.n_kb = S / BKV; p2.causal = p.causal;
