@@ -516,10 +516,11 @@ constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 81920, CO_QMN =
 constexpr int FA2_SMEM = CO_BAR + 256 + 1024;
 constexpr uint32_t T2_ST = 0, T2_DPT = 64, T2_BUF = 128, T2_DV = 256, T2_DK = 320;   // S^T / dP^T double-buffered (+T2_BUF)
 enum { D_KVFULL = 0, D_QKFULL = 1, D_QKEMPTY = 2, D_QMNFULL = 3, D_QMNEMPTY = 4, D_STFULL = 5, D_STEMPTY = 7, D_PTFULL = 9,
-       D_ACCDONE = 10, D_COUNT = 11 };
+       D_ACCDONE = 10, D_KVEMPTY = 11, D_COUNT = 12 };
 
 struct FaBwd2Params {
   int S, H, n_kb, causal;
+  int n_items;
   float k2, scale;
   const float* lse;
   const float* dsum;
@@ -540,12 +541,18 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + CO_BAR + 8 * D_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kbk = blockIdx.x % p.n_kb;            // light (late) key blocks last
-  const int bh = blockIdx.x / p.n_kb;
-  const int h = bh % p.H, b = bh / p.H;
+  // Persistent loop over (sequence, head, key block) items, heaviest first (key block 0 is seen by every query block).
+  // u counts 64-query iterations over all items of this CTA, it counts items; every barrier phase derives from them.
+  const int n_bh = p.n_items / p.n_kb;
   const int n_q = p.S / BQ2;
-  const int i0 = p.causal ? kbk * (BKV / BQ2) : 0;   // first 64-row query block that sees this key block
-  const int n_it = n_q - i0;
+  auto item_coords = [&](int item, int& kbk, int& h, int& b, int& i0, int& n_it) {
+    kbk = item / n_bh;
+    const int bh = item - kbk * n_bh;
+    h = bh % p.H;
+    b = bh / p.H;
+    i0 = p.causal ? kbk * (BKV / BQ2) : 0;   // first 64-row query block that sees this key block
+    n_it = n_q - i0;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_STEMPTY || i == D_STEMPTY + 1 || i == D_PTFULL) ? 256u : 1u);
@@ -565,39 +572,52 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(bar(D_KVFULL), 2 * BKV * DH * 4);
-      for (int kb = 0; kb < 2; kb++) {
-        tma_load_4d(smem_base + CO_K + kb * 16384, &tmK, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
-        tma_load_4d(smem_base + CO_V + kb * 16384, &tmV, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
-      }
       bool ok = true;
-      for (int it = 0; it < n_it && ok; it++) {
-        const uint32_t ph = (uint32_t)it & 1u;
-        const int q0 = (i0 + it) * BQ2;
-        ok = mbar_wait(bar(D_QKEMPTY), ph ^ 1u, abort_flag, p.status, 31);
+      uint32_t u = 0, it = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
+        int kbk, h, b, i0, n_it;
+        item_coords(item, kbk, h, b, i0, n_it);
+        ok = mbar_wait(bar(D_KVEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 41);   // previous item's score products done
         if (!ok) break;
-        mbar_expect_tx(bar(D_QKFULL), 2 * BQ2 * DH * 4);
+        mbar_expect_tx(bar(D_KVFULL), 2 * BKV * DH * 4);
         for (int kb = 0; kb < 2; kb++) {
-          tma_load_4d(smem_base + CO_Q + kb * 8192, &tmQ, bar(D_QKFULL), kb * 32, q0, h, b);
-          tma_load_4d(smem_base + CO_DO + kb * 8192, &tmDO, bar(D_QKFULL), kb * 32, q0, h, b);
+          tma_load_4d(smem_base + CO_K + kb * 16384, &tmK, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
+          tma_load_4d(smem_base + CO_V + kb * 16384, &tmV, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
         }
-        ok = mbar_wait(bar(D_QMNEMPTY), ph ^ 1u, abort_flag, p.status, 39);
-        if (!ok) break;
-        mbar_expect_tx(bar(D_QMNFULL), 2 * BQ2 * DH * 4);
-        for (int c = 0; c < 2; c++) {
-          tma_load_5d(smem_base + CO_QMN + c * 8192, &tmQmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
-          tma_load_5d(smem_base + CO_DOMN + c * 8192, &tmDOmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
+        for (int i = 0; i < n_it && ok; i++, u++) {
+          const uint32_t ph = u & 1u;
+          const int q0 = (i0 + i) * BQ2;
+          ok = mbar_wait(bar(D_QKEMPTY), ph ^ 1u, abort_flag, p.status, 31);
+          if (!ok) break;
+          mbar_expect_tx(bar(D_QKFULL), 2 * BQ2 * DH * 4);
+          for (int kb = 0; kb < 2; kb++) {
+            tma_load_4d(smem_base + CO_Q + kb * 8192, &tmQ, bar(D_QKFULL), kb * 32, q0, h, b);
+            tma_load_4d(smem_base + CO_DO + kb * 8192, &tmDO, bar(D_QKFULL), kb * 32, q0, h, b);
+          }
+          ok = mbar_wait(bar(D_QMNEMPTY), ph ^ 1u, abort_flag, p.status, 39);
+          if (!ok) break;
+          mbar_expect_tx(bar(D_QMNFULL), 2 * BQ2 * DH * 4);
+          for (int c = 0; c < 2; c++) {
+            tma_load_5d(smem_base + CO_QMN + c * 8192, &tmQmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
+            tma_load_5d(smem_base + CO_DOMN + c * 8192, &tmDOmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_st = fa_idesc(BKV, BQ2, 0, 0), idesc_acc = fa_idesc(BKV, DH, 0, 1);
-      bool ok = mbar_wait(bar(D_KVFULL), 0, abort_flag, p.status, 32);
-      auto issue_scores = [&](int it) {   // S^T and dP^T of query block `it` into TMEM buffer it & 1
-        const int bf = it & 1;
-        if (!mbar_wait(bar(D_QKFULL), (uint32_t)it & 1u, abort_flag, p.status, 33)) return false;
-        if (!mbar_wait(bar(D_STEMPTY + bf), (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag, p.status, 34)) return false;
+      bool ok = true;
+      // cursor of the next pair of score products: one iteration ahead of the accumulating products, across items
+      int s_item = blockIdx.x, s_i = 0, s_nit = 0;
+      uint32_t s_u = 0, s_it = 0;
+      if (s_item < p.n_items) { int a, b2, c, d2; item_coords(s_item, a, b2, c, d2, s_nit); }
+      auto issue_scores = [&]() {   // S^T and dP^T of the next query block into TMEM buffer s_u & 1
+        if (s_item >= p.n_items) return true;
+        const int bf = s_u & 1;
+        if (s_i == 0 && !mbar_wait(bar(D_KVFULL), s_it & 1u, abort_flag, p.status, 32)) return false;
+        if (!mbar_wait(bar(D_QKFULL), s_u & 1u, abort_flag, p.status, 33)) return false;
+        if (!mbar_wait(bar(D_STEMPTY + bf), ((s_u >> 1) & 1u) ^ 1u, abort_flag, p.status, 34)) return false;
         tc_fence_after();
         for (int kb = 0; kb < 2; kb++) {
           const uint64_t ak = make_smem_desc(smem_base + CO_K + kb * 16384, 16u, 1024u, 2u);
@@ -612,95 +632,115 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
         umma_commit(bar(D_STFULL + bf));
         umma_commit(bar(D_QKEMPTY));   // the K-major copies of Q_i, dO_i may be replaced
+        s_u++;
+        if (++s_i == s_nit) {          // last score products of the item: K_j, V_j may be replaced
+          umma_commit(bar(D_KVEMPTY));
+          s_item += gridDim.x;
+          s_it++;
+          s_i = 0;
+          if (s_item < p.n_items) { int a, b2, c, d2; item_coords(s_item, a, b2, c, d2, s_nit); }
+        }
         return true;
       };
-      if (ok && n_it > 0) ok = issue_scores(0);
-      for (int it = 0; it < n_it && ok; it++) {
-        const uint32_t ph = (uint32_t)it & 1u;
-        if (it + 1 < n_it) ok = issue_scores(it + 1);   // overlaps the compute warps' work on block `it`
-        if (!ok) break;
-        ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35) && mbar_wait(bar(D_QMNFULL), ph, abort_flag, p.status, 40);
-        if (!ok) break;
-        tc_fence_after();
-        for (int c = 0; c < 2; c++) {   // 32 queries per chunk
-          const uint64_t ap = make_smem_desc(smem_base + CO_PT + c * 16384, 16u, 1024u, 2u);
-          const uint64_t as = make_smem_desc(smem_base + CO_DST + c * 16384, 16u, 1024u, 2u);
-          const uint64_t bdo = make_smem_desc(smem_base + CO_DOMN + c * 8192, 4096u, 512u, 1u);
-          const uint64_t bq = make_smem_desc(smem_base + CO_QMN + c * 8192, 4096u, 512u, 1u);
+      uint32_t u = 0;
+      ok = issue_scores();
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        int kbk, h, b, i0, n_it;
+        item_coords(item, kbk, h, b, i0, n_it);
+        for (int i = 0; i < n_it && ok; i++, u++) {
+          const uint32_t ph = u & 1u;
+          if (s_u == u + 1) ok = issue_scores();   // overlaps the compute warps' work on this block
+          if (!ok) break;
+          ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35) && mbar_wait(bar(D_QMNFULL), ph, abort_flag, p.status, 40);
+          if (!ok) break;
+          tc_fence_after();
+          for (int c = 0; c < 2; c++) {   // 32 queries per chunk
+            const uint64_t ap = make_smem_desc(smem_base + CO_PT + c * 16384, 16u, 1024u, 2u);
+            const uint64_t as = make_smem_desc(smem_base + CO_DST + c * 16384, 16u, 1024u, 2u);
+            const uint64_t bdo = make_smem_desc(smem_base + CO_DOMN + c * 8192, 4096u, 512u, 1u);
+            const uint64_t bq = make_smem_desc(smem_base + CO_QMN + c * 8192, 4096u, 512u, 1u);
 #pragma unroll
-          for (int k = 0; k < 4; k++) {
-            umma_tf32(tmem_base + T2_DV, ap + 2u * k, bdo + 64u * k, idesc_acc, (it | c | k) ? 1u : 0u);
-            umma_tf32(tmem_base + T2_DK, as + 2u * k, bq + 64u * k, idesc_acc, (it | c | k) ? 1u : 0u);
+            for (int k = 0; k < 4; k++) {
+              umma_tf32(tmem_base + T2_DV, ap + 2u * k, bdo + 64u * k, idesc_acc, (i | c | k) ? 1u : 0u);
+              umma_tf32(tmem_base + T2_DK, as + 2u * k, bq + 64u * k, idesc_acc, (i | c | k) ? 1u : 0u);
+            }
           }
+          umma_commit(bar(D_ACCDONE));
+          umma_commit(bar(D_QMNEMPTY));
         }
-        umma_commit(bar(D_ACCDONE));
-        umma_commit(bar(D_QMNEMPTY));
       }
     }
   } else {
     const int q4 = warp & 3;
     const int half = (warp - 2) >> 2;          // which 32-query chunk of every block this warp handles
     const int row = q4 * 32 + lane;            // key inside the block
-    const int kj = kbk * BKV + row;            // key position in the sequence
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
-    const long long stat_base = ((long long)b * p.H + h) * p.S;
     bool ok = true;
     uint32_t sv[32], dv[32];
-    for (int it = 0; it < n_it && ok; it++) {
-      const uint32_t ph = (uint32_t)it & 1u;
-      const int q0 = (i0 + it) * BQ2;
-      // row statistics of the 64 queries of this block: lane l holds queries 2l and 2l + 1, the inner loop fetches
-      // the one it needs with a shuffle (no block-wide barrier inside a loop whose waits can give up)
-      const float2 Lq = __ldg(reinterpret_cast<const float2*>(p.lse + stat_base + q0) + lane);
-      const float2 Dq = __ldg(reinterpret_cast<const float2*>(p.dsum + stat_base + q0) + lane);
-      const int bf = it & 1;
-      ok = mbar_wait(bar(D_STFULL + bf), ((uint32_t)it >> 1) & 1u, abort_flag, p.status, 36);
-      if (ok && it > 0) ok = mbar_wait(bar(D_ACCDONE), ph ^ 1u, abort_flag, p.status, 37);   // P^T / dS^T tiles free again
-      if (!ok) break;
-      tc_fence_after();
-      {
-        const int c = half;
-        tmem_ld32(lane_addr + bf * T2_BUF + T2_ST + c * 32, sv);
-        tmem_ld32(lane_addr + bf * T2_BUF + T2_DPT + c * 32, dv);
-        tmem_ld_wait();
-        uint8_t* prow = smem_gen + CO_PT + c * 16384 + row * 128;
-        uint8_t* srow = smem_gen + CO_DST + c * 16384 + row * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ch++) {
-          float4 pv, dsv;
-          float* pe = reinterpret_cast<float*>(&pv);
-          float* de = reinterpret_cast<float*>(&dsv);
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const int col = c * 32 + ch * 4 + e;            // query inside the block
-            const bool vis = !p.causal || (q0 + col >= kj);
-            const float Lc = __shfl_sync(0xffffffffu, (col & 1) ? Lq.y : Lq.x, col >> 1);
-            const float Dc = __shfl_sync(0xffffffffu, (col & 1) ? Dq.y : Dq.x, col >> 1);
-            const float pr = vis ? exp2f(__uint_as_float(sv[ch * 4 + e]) * p.k2 - Lc) : 0.f;
-            pe[e] = pr;
-            de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale;
-          }
-          *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
-          *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
-        }
-      }
-      tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(bar(D_PTFULL));
-      mbar_arrive(bar(D_STEMPTY + bf));
-    }
-    if (ok && n_it > 0) ok = mbar_wait(bar(D_ACCDONE), (uint32_t)(n_it - 1) & 1u, abort_flag, p.status, 38);
-    if (ok) {
-      tc_fence_after();
-      for (int which = 0; which < 2; which++) {
-        float* grow = (which ? p.dk : p.dv) + ((long long)b * p.S + kj) * p.ld + h * DH;
+    uint32_t u = 0;
+    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      int kbk, h, b, i0, n_it;
+      item_coords(item, kbk, h, b, i0, n_it);
+      const int kj = kbk * BKV + row;            // key position in the sequence
+      const long long stat_base = ((long long)b * p.H + h) * p.S;
+      for (int i = 0; i < n_it && ok; i++, u++) {
+        const uint32_t ph = u & 1u;
+        const int q0 = (i0 + i) * BQ2;
+        // row statistics of the 64 queries of this block: lane l holds queries 2l and 2l + 1, the inner loop fetches
+        // the one it needs with a shuffle (no block-wide barrier inside a loop whose waits can give up)
+        const float2 Lq = __ldg(reinterpret_cast<const float2*>(p.lse + stat_base + q0) + lane);
+        const float2 Dq = __ldg(reinterpret_cast<const float2*>(p.dsum + stat_base + q0) + lane);
+        const int bf = u & 1;
+        ok = mbar_wait(bar(D_STFULL + bf), (u >> 1) & 1u, abort_flag, p.status, 36);
+        if (ok && i > 0) ok = mbar_wait(bar(D_ACCDONE), ph ^ 1u, abort_flag, p.status, 37);   // P^T / dS^T tiles free again
+        if (!ok) break;
+        tc_fence_after();
         {
           const int c = half;
-          tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + c * 32, sv);
+          tmem_ld32(lane_addr + bf * T2_BUF + T2_ST + c * 32, sv);
+          tmem_ld32(lane_addr + bf * T2_BUF + T2_DPT + c * 32, dv);
           tmem_ld_wait();
+          uint8_t* prow = smem_gen + CO_PT + c * 16384 + row * 128;
+          uint8_t* srow = smem_gen + CO_DST + c * 16384 + row * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ch++) {
+            float4 pv, dsv;
+            float* pe = reinterpret_cast<float*>(&pv);
+            float* de = reinterpret_cast<float*>(&dsv);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const int col = c * 32 + ch * 4 + e;            // query inside the block
+              const bool vis = !p.causal || (q0 + col >= kj);
+              const float Lc = __shfl_sync(0xffffffffu, (col & 1) ? Lq.y : Lq.x, col >> 1);
+              const float Dc = __shfl_sync(0xffffffffu, (col & 1) ? Dq.y : Dq.x, col >> 1);
+              const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -Lc)) : 0.f;
+              pe[e] = pr;
+              de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale;
+            }
+            *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
+            *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
+          }
+        }
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(bar(D_PTFULL));
+        mbar_arrive(bar(D_STEMPTY + bf));
+      }
+      if (ok && n_it > 0) ok = mbar_wait(bar(D_ACCDONE), (u - 1) & 1u, abort_flag, p.status, 38);
+      if (ok) {
+        tc_fence_after();
+        uint32_t kv[32];
+        const int c = half;
+        tmem_ld32(lane_addr + T2_DV + c * 32, sv);
+        tmem_ld32(lane_addr + T2_DK + c * 32, kv);
+        tmem_ld_wait();
+        tc_fence_before();   // both accumulators read before this thread publishes the next item's first P^T
+        for (int which = 0; which < 2; which++) {
+          float* grow = (which ? p.dk : p.dv) + ((long long)b * p.S + kj) * p.ld + h * DH;
+          const uint32_t* src = which ? kv : sv;
 #pragma unroll
           for (int e = 0; e < 32; e += 4) {
-            float4 o = make_float4(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1]), __uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3]));
+            float4 o = make_float4(__uint_as_float(src[e]), __uint_as_float(src[e + 1]), __uint_as_float(src[e + 2]), __uint_as_float(src[e + 3]));
             float4* dst = reinterpret_cast<float4*>(grow + c * 32 + e);
             if (p.accumulate) {
               const float4 old = *dst;
@@ -831,7 +871,9 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   p2.k2 = p.k2; p2.scale = p.scale; p2.lse = d->lse; p2.dsum = dsum;
   p2.dk = dk; p2.dv = dv; p2.ld = ld_dqkv; p2.accumulate = p.accumulate;
   p2.status = ctx->d_status;
-  attention_bwd_dkv_kernel<<<grid, FA_BWD_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ64, tmDO64, tmQmn, tmDOmn, p2);
+  p2.n_items = (int)grid;
+  attention_bwd_dkv_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ64, tmDO64, tmQmn,
+                                                                                                                    tmDOmn, p2);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dkv_kernel");
   return FML_OK;
 }
