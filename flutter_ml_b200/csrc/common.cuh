@@ -75,6 +75,8 @@ struct fml_lstm_epilogue {
   float* c_out;         // [M][N/4]
   float* h_out;         // [M][N/4]
   float* gates;         // [M][N] activated gates, interleaved like the columns
+  int fast_math;        // TF32 mode: hardware exponential and reciprocal in the gate functions (error ~1e-6, far inside
+                        // the 1e-3 bound of that mode; the epilogue warps are latency-bound and these are 40 calls per thread)
 };
 
 // internal entry points between translation units
@@ -87,6 +89,12 @@ __device__ __forceinline__ float fml_sigmoid(float x) { return 1.f / (1.f + expf
 __device__ __forceinline__ float fml_tanh_ref(float x) {
   const float e2x = expf(2.f * x);
   return isinf(e2x) ? 1.f : (e2x - 1.f) / (e2x + 1.f);
+}
+
+__device__ __forceinline__ float fml_sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+__device__ __forceinline__ float fml_tanh_fast(float x) {
+  const float e2x = __expf(2.f * x);          // same algebra and the same overflow rule as fml_tanh_ref
+  return e2x > 3.0e38f ? 1.f : __fdividef(e2x - 1.f, e2x + 1.f);
 }
 
 // Standard normal CDF and e^{-x^2/2} from ONE exponential: erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) e^{-z^2},

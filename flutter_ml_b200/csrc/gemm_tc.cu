@@ -539,12 +539,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             float cn[8], hn[8];
 #pragma unroll
             for (int uu = 0; uu < 8; uu++) {
-              const float f = fml_sigmoid(__uint_as_float(v[4 * uu]) + xa[uu].x);
-              const float i = fml_sigmoid(__uint_as_float(v[4 * uu + 1]) + xa[uu].y);
-              const float g = fml_tanh_ref(__uint_as_float(v[4 * uu + 2]) + xa[uu].z);
-              const float o = fml_sigmoid(__uint_as_float(v[4 * uu + 3]) + xa[uu].w);
+              const float zf = __uint_as_float(v[4 * uu]) + xa[uu].x, zi = __uint_as_float(v[4 * uu + 1]) + xa[uu].y;
+              const float zg = __uint_as_float(v[4 * uu + 2]) + xa[uu].z, zo = __uint_as_float(v[4 * uu + 3]) + xa[uu].w;
+              float f, i, g, o;
+              if (p.le.fast_math) {
+                f = fml_sigmoid_fast(zf); i = fml_sigmoid_fast(zi); g = fml_tanh_fast(zg); o = fml_sigmoid_fast(zo);
+              } else {
+                f = fml_sigmoid(zf); i = fml_sigmoid(zi); g = fml_tanh_ref(zg); o = fml_sigmoid(zo);
+              }
               cn[uu] = f * cp[uu] + i * g;
-              hn[uu] = o * fml_tanh_ref(cn[uu]);
+              hn[uu] = o * (p.le.fast_math ? fml_tanh_fast(cn[uu]) : fml_tanh_ref(cn[uu]));
               *reinterpret_cast<float4*>(p.le.gates + po + 4 * uu) = make_float4(f, i, g, o);
             }
             *reinterpret_cast<float4*>(p.le.c_out + ho) = *reinterpret_cast<float4*>(cn);
@@ -892,7 +896,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   if (lstm) {
     p.le = *lstm;
   } else {
-    p.le = fml_lstm_epilogue{nullptr, nullptr, nullptr, nullptr, nullptr};
+    p.le = fml_lstm_epilogue{nullptr, nullptr, nullptr, nullptr, nullptr, 0};
   }
   p.M = d->M; p.N = d->N; p.K = d->K;
   p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.nb1 = nb1; p.nb2 = nb2;

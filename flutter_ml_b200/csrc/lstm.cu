@@ -134,7 +134,8 @@ int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d) {
                        (reinterpret_cast<uintptr_t>(pre) & 15) == 0;
     if (fused) {
       // recurrent product with the gate nonlinearity and the cell update in its epilogue
-      fml_lstm_epilogue le = {pre, d->cells + t * bh, d->cells + (t + 1) * bh, d->hs + (t + 1) * bh, d->gates + t * b4h};
+      fml_lstm_epilogue le = {pre, d->cells + t * bh, d->cells + (t + 1) * bh, d->hs + (t + 1) * bh, d->gates + t * b4h,
+                              prec == FML_PREC_TF32 ? 1 : 0};
       r.beta = 0.f;
       rc = fml_gemm_tc(ctx, &r, prec, &le);
     } else {
