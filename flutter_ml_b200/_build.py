@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libflutter_ml_b200.so")
-SOURCES = ["ctx.cu", "gemm_tc.cu", "gemm_simt.cu", "elementwise.cu", "rowwise.cu", "lstm.cu", "dp.cu", "tape.cu", "checkpoint.cu", "conv.cu", "attention_tc.cu"]
+SOURCES = ["ctx.cu", "gemm_tc.cu", "gemm_simt.cu", "elementwise.cu", "rowwise.cu", "lstm.cu", "dp.cu", "tape.cu", "checkpoint.cu", "conv.cu", "attention_tc.cu", "lstm_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE]
 

@@ -10,9 +10,14 @@
 //
 // Reference: LSTMLayer.forward lib/layertypes/lstmLayer.dart:112-150.  Gate order f,i,c~,o
 // (:64); weight columns [h_{t-1} | x_t] (:119).
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "common.cuh"
+
+// the recurrence of all time steps in one cooperative kernel (lstm_tc.cu); 1 = shape not eligible
+int32_t fml_lstm_fwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const float* Wi, int fast_math);
 
 namespace {
 
@@ -123,6 +128,20 @@ int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d) {
   g.bias = bi;
   rc = fml_gemm(ctx, &g);
   const int prec = ctx->precision;
+  {
+    static int persistent = -1;
+    if (persistent < 0) {
+      const char* e = getenv("FML_LSTM_PERSISTENT");   // diagnostics: 0 keeps the per-step kernels
+      persistent = e ? atoi(e) : 1;
+    }
+    if (rc == FML_OK && persistent && prec == FML_PREC_TF32) {
+      const int32_t pr = fml_lstm_fwd_persistent(ctx, d, Wi, 1);
+      if (pr <= 0) {   // done, or failed for good
+        cudaFreeAsync(Wi, ctx->stream);
+        return pr;
+      }
+    }
+  }
   for (int t = 0; t < T && rc == FML_OK; t++) {
     float* pre = d->xproj + t * b4h;
     fml_gemm_desc r = gemm_defaults();
