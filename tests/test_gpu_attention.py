@@ -27,7 +27,7 @@ def attention_desc(ctx, qkv, out, lse, Bn, S, H, causal, scale):
     return d
 
 
-@pytest.mark.parametrize("S,causal", [(128, False), (128, True), (384, True), (512, True), (256, False)])
+@pytest.mark.parametrize("S,causal", [(128, False), (128, True), (384, True), (512, True), (256, False), (1024, True)])
 def test_fused_attention_forward(orc, S, causal):
     from flutter_ml_b200 import _lib
     ctx = _lib.Context(precision=_lib.PREC_TF32)

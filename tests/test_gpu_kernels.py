@@ -318,6 +318,43 @@ def test_lstm_forward_backward(orc, prec, tol):
     c.close()
 
 
+@pytest.mark.parametrize("T,B,I,H", [(6, 128, 16, 256), (5, 70, 8, 320), (9, 3, 4, 64), (3, 16, 8, 1024), (1, 5, 4, 32)])
+def test_lstm_single_kernel_forward_recurrence(orc, T, B, I, H):
+    """The cooperative forward kernel (TF32 mode, batch <= 128) on shapes that exercise a full 128-row batch, a TMA ring
+    that wraps (H = 320: 10 k-blocks through 8 stages) and a nearly empty batch: every h_t, c_t and saved gate against
+    the oracle's step-by-step recurrence (lstmLayer.dart:112-150)."""
+    import ctypes
+    from flutter_ml_b200 import _lib
+    c = _lib.Context(precision=_lib.PREC_TF32)
+    rng = np.random.default_rng(T * 1000 + H)
+    a = 1 / np.sqrt(H)
+    W = rng.uniform(-a, a, (4, H, H + I)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (4, H)).astype(np.float32)
+    x = rng.standard_normal((T, B, I)).astype(np.float32)
+    d = _lib.LstmDesc()
+    d.T, d.B, d.I, d.H = T, B, I, H
+    bufs = dict(W=c.upload(W), b=c.upload(b), x=c.upload(x), gates=c.empty(T, B, 4 * H), cells=c.empty(T + 1, B, H),
+                hs=c.empty(T + 1, B, H), xproj=c.empty(T * B, 4 * H))
+    for k, v in bufs.items():
+        setattr(d, k, v.ptr)
+    c.check(c.lib.fml_lstm_fwd(c.h, ctypes.byref(d)))
+    assert c.device_status() == 0
+    hs, cs, gates = bufs["hs"].numpy(), bufs["cells"].numpy(), bufs["gates"].numpy().reshape(T, B, H, 4)
+    W64, b64 = w64(W), w64(b)
+    h, cc = np.zeros((B, H)), np.zeros((B, H))
+    sig = lambda z: 1 / (1 + np.exp(-z))
+    for t in range(T):
+        z = np.concatenate([h, w64(x[t])], axis=1)                     # [h_{t-1}, x_t] (lstmLayer.dart:119)
+        f, i, g, o = (z @ W64[q].T + b64[q] for q in range(4))
+        f, i, g, o = sig(f), sig(i), np.tanh(g), sig(o)
+        cc = f * cc + i * g
+        h = o * np.tanh(cc)
+        assert rel(hs[t + 1], h) <= TOL_TF32 and rel(cs[t + 1], cc) <= TOL_TF32, t
+        assert rel(gates[t], np.stack([f, i, g, o], axis=-1)) <= TOL_TF32, t
+    assert np.all(hs[0] == 0)
+    c.close()
+
+
 @pytest.mark.parametrize("act", ["relu", "sigmoid", "tanh", "gelu"])
 @pytest.mark.parametrize("prec", [0, 2])
 def test_gemm_gradient_epilogue_equals_separate_kernel(ctx, act, prec):
