@@ -70,6 +70,7 @@ PROTOTYPES = {
     "fml_set_stream": [fp, fp],
     "fml_sync": [fp],
     "fml_device_status": [fp, C.POINTER(i32)],
+    "fml_selftest_wait_timeout": [fp, i32],
     "fml_alloc": [fp, i64, C.POINTER(fp)],
     "fml_free": [fp, fp],
     "fml_zero": [fp, fp, i64],

@@ -781,6 +781,28 @@ uint32_t make_idesc(int M, int BN, int a_mn, int b_mn) {
 
 }  // namespace
 
+namespace {
+// One CTA waits on an mbarrier that nothing ever arrives at, with the same bounded wait every pipeline role of the
+// tensor-core kernels uses, and must come back with the error code instead of hanging.
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ alignas(8) unsigned long long mbar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&mbar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait_limit(smem_u32(&mbar), 0, &abort_flag, status, 99, limit_ns);
+  }
+}
+}  // namespace
+
+extern "C" int32_t fml_selftest_wait_timeout(fml_ctx* ctx, int32_t limit_us) {
+  FML_REQUIRE(ctx, ctx && limit_us > 0 && limit_us <= 1000000, "fml_selftest_wait_timeout: the limit must be 1 .. 1000000 us");
+  wait_timeout_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, (unsigned long long)limit_us * 1000ull);
+  FML_LAUNCH_CHECK(ctx, "wait_timeout_selftest_kernel");
+  return FML_OK;
+}
+
 int32_t fml_tc_make_tmap(fml_ctx* ctx, const float* base, int64_t cols, int64_t rows, int64_t ld, int64_t nb1, int64_t nb2,
                          int64_t s1, int64_t s2, int box_c, int box_r, bool mn_major, int blocks, CUtensorMap* out) {
   return make_tmap(ctx, base, cols, rows, ld, nb1, nb2, s1, s2, box_c, box_r, mn_major, blocks, out);

@@ -39,15 +39,15 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 // Bounded wait.  Returns false if the CTA is aborting or the limit expired.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                                unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xFF) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -55,6 +55,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, code, WAIT_LIMIT_NS);
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
                                             int c1, int c2, int c3) {

@@ -73,6 +73,10 @@ int32_t fml_sync(fml_ctx* ctx);
 /* Bounded device-side waits record a code here instead of hanging; reading it
  * synchronises.  0 means no kernel gave up. */
 int32_t fml_device_status(fml_ctx* ctx, int32_t* code);
+/* Failure-path self test: one CTA waits (with the bounded wait all pipeline roles use) on a barrier that nothing
+ * signals; after limit_us microseconds it records code 99 and returns.  fml_device_status then reports
+ * FML_ERR_TIMEOUT once and the context stays usable.  Nothing faults, traps or hangs. */
+int32_t fml_selftest_wait_timeout(fml_ctx* ctx, int32_t limit_us);
 
 /* ---- memory ---------------------------------------------------------------
  * Dart lists are float64 (lib/cuda/cudacaller.dart:38-43 narrows element by

@@ -457,3 +457,24 @@ def test_parameterised_activations(ctx, orc, kind, alpha):
     assert np.all(np.isfinite(y.numpy())) and np.all(np.isfinite(dx.numpy()))
     ctx.call("fml_act2_bwd", kind, alpha, dxd, ddy, dx, x.size, 1)   # accumulate
     assert rel(dx.numpy(), 2 * dx_ref) <= 1e-6
+
+
+def test_bounded_wait_times_out_and_the_context_survives():
+    """A device-side wait that nothing ever satisfies (the failure made by a barrier nobody signals, not by a fault):
+    the kernel gives up after its limit, the host reads FML_ERR_TIMEOUT with the recorded code once, and the same
+    context then runs a product correctly."""
+    import ctypes
+    from flutter_ml_b200 import _lib
+    c = _lib.Context(precision=_lib.PREC_TF32)
+    assert c.device_status() == 0
+    c.check(c.lib.fml_selftest_wait_timeout(c.h, 2000))          # 2 ms
+    code = ctypes.c_int32(0)
+    assert c.lib.fml_device_status(c.h, ctypes.byref(code)) == -4   # FML_ERR_TIMEOUT
+    assert code.value == 99 and b"bounded wait expired" in c.lib.fml_last_error(c.h)
+    assert c.device_status() == 0                                 # reported once, then clear
+    a = np.random.default_rng(0).standard_normal((256, 256)).astype(np.float32)
+    A, B, C = c.upload(a), c.upload(a.T.copy()), c.empty(256, 256)
+    c.gemm(A, B, C, 256, 256, 256)
+    assert rel(C.numpy(), a.astype(np.float64) @ a.T.astype(np.float64)) <= TOL_TF32
+    assert c.lib.fml_selftest_wait_timeout(c.h, 0) == -1          # limit out of range
+    c.close()
