@@ -252,6 +252,11 @@ int32_t fml_lstm_fwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const floa
   void* args[] = {(void*)&tmH, (void*)&tmW, (void*)&p};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)lstm_fwd_persistent_kernel, dim3(n_cta), dim3(LT_THREADS), args, smem, ctx->stream);
   cudaFreeAsync(gbar, ctx->stream);
-  if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_CUDA, std::string("lstm_fwd_persistent_kernel: ") + cudaGetErrorString(e));
+  if (e != cudaSuccess) {
+    // the cooperative launch was refused (the grid cannot be co-resident on this device right now): nothing ran,
+    // the caller takes the per-step kernels
+    cudaGetLastError();
+    return 1;
+  }
   return FML_OK;
 }

@@ -331,3 +331,37 @@ def test_conv2d_on_the_tape(orc, fp32_ctx, padding, kh, kw):
     assert rel(to.numpy(), oo.value) <= 2e-6
     for t, o in ((tx, ox), (tk1, ok1), (tk2, ok2), (tb, ob)):
         assert rel(t.grad_numpy().reshape(np.shape(o.grad)), o.grad) <= 1e-5
+
+
+def test_conv_lstm_cell_as_a_tape(orc, fp32_ctx):
+    """A ConvLSTM cell (lib/layertypes/convlstmLayer.dart:94-127) over two frames, written with the nodes it is made
+    of: eight 'same' conv2d per step, add_matrix with a frame-shaped bias, sigmoid_matrix / tanh_matrix,
+    multiply_matrix.  (The reference passes (kernel, frame) to conv2d in that file; the frame is the image here.)"""
+    from flutter_ml_b200.tape import Tape
+    Hh, Ww, k, Tn = 7, 9, 3, 2
+    rng = np.random.default_rng(17)
+    f = lambda *s: (rng.standard_normal(s) * 0.5).astype(np.float32)
+    Kx, Kh, bs = [f(k, k) for _ in range(4)], [f(k, k) for _ in range(4)], [f(Hh, Ww) * 0.1 for _ in range(4)]
+    frames, target = [f(Hh, Ww) for _ in range(Tn)], f(Hh, Ww)
+
+    def run(E, mk, sig, tanh):
+        kx, kh, b = [mk(a) for a in Kx], [mk(a) for a in Kh], [mk(a) for a in bs]
+        h, c = mk(np.zeros((Hh, Ww), np.float32)), mk(np.zeros((Hh, Ww), np.float32))
+        for fr in frames:
+            x = mk(fr)
+            gate = lambda q, fn: fn(E.addMatrix(E.addMatrix(E.conv2d(x, kx[q], "same"), E.conv2d(h, kh[q], "same")), b[q]))
+            f_t, i_t, c_t = gate(0, sig), gate(1, sig), gate(2, tanh)
+            c = E.addMatrix(E.elementWiseMultiply(f_t, c), E.elementWiseMultiply(i_t, c_t))
+            h = E.elementWiseMultiply(gate(3, sig), tanh(c))
+        return E.mseMatrix(h, mk(target)), h, kx + kh + b
+
+    E = orc.Engine()
+    oloss, oh, oparams = run(E, lambda a: orc.T(w64(a)), E.sigmoidMatrix, E.tanhMatrix)
+    oloss.backward()
+    tp = Tape(fp32_ctx)
+    tloss, th, tparams = run(tp, tp.tensor, tp.sigmoidMatrix, tp.tanhMatrix)
+    tp.forward()
+    tp.backward()
+    assert rel(th.numpy(), oh.value) <= 2e-6
+    for t, o in zip(tparams, oparams):
+        assert rel(t.grad_numpy(), o.grad) <= 2e-5
