@@ -37,6 +37,7 @@ constexpr uint32_t TM_S = 0, TM_PV = 256;
 struct FaParams {
   int S, H, n_qb;        // sequence length, heads, query blocks per sequence
   int n_items;           // n_seq * H * n_qb work items
+  int round_p;           // 1: P is rounded to TF32 before it is summed and multiplied (0 only for diagnostics, FML_FA_NOROUND)
   int causal;
   float k2;              // scale * log2(e)
   float* out; long long ld_out;
@@ -46,6 +47,8 @@ struct FaParams {
 
 enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KVEMPTY = 5, B_SFULL = 7, B_SEMPTY = 9, B_PFULL = 11, B_PVFULL = 12, B_QEMPTY = 13, B_COUNT = 14 };
 
+// round-to-nearest of a finite non-negative float to TF32 (10 mantissa bits) with two integer instructions
+__device__ __forceinline__ float fa_round_tf32(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ uint32_t fa_idesc(int M, int N, int a_mn, int b_mn) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a_mn & 1) << 15) | ((uint32_t)(b_mn & 1) << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
@@ -245,7 +248,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const int col = c * 32 + ch * 4 + e;
-              const float pr = (col < lim) ? exp2f(fmaf(__uint_as_float(v[ch * 4 + e]), p.k2, -m_new)) : 0.f;
+              // rounded to TF32 here, and the ROUNDED value enters the row sum: the tensor core would otherwise cut the
+              // low mantissa bits of P on its own and every output would come out low by up to 2^-11 relative to l
+              const float pe_ = exp2f(fmaf(__uint_as_float(v[ch * 4 + e]), p.k2, -m_new));
+              const float pr = (col < lim) ? (p.round_p ? fa_round_tf32(pe_) : pe_) : 0.f;
               pe[e] = pr;
               ls4[e] += pr;
             }
@@ -814,6 +820,7 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
   const long long items = (long long)Bn * H * p.n_qb;
   FML_REQUIRE(ctx, items <= 0x7fffffffLL, "fml_attention_fwd: too many work items");
   p.n_items = (int)items;
+  p.round_p = getenv("FML_FA_NOROUND") ? 0 : 1;
   const unsigned grid = (unsigned)std::min<long long>(items, ctx->sm_count);
   attention_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
   FML_LAUNCH_CHECK(ctx, "attention_fwd_kernel");

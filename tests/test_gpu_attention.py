@@ -105,3 +105,41 @@ def test_fused_attention_backward(orc, S, causal, accumulate):
                 g = got[rows, i * dm + h * dk:i * dm + (h + 1) * dk]
                 assert rel(g, t.grad) <= (5e-3 if not accumulate else 2e-2), (b, h, "qkv"[i])
     ctx.close()
+
+
+def test_fused_attention_full_size_properties():
+    """One config-5 layer (32 sequences x 16 heads x 512 x 64, causal), too large for the float64 oracle: properties
+    that hold at any size.  With V = 1 every output equals 1 (the probabilities of a row sum to 1); the first query of
+    a causal sequence sees only key 0, so its output row is V[0]; dV summed over keys equals dO summed over queries
+    (each probability row sums to 1), and dQ, dK vanish when V is constant (dP is constant along a row, so dS = 0)."""
+    from flutter_ml_b200 import _lib
+    ctx = _lib.Context(precision=_lib.PREC_TF32)
+    Bn, S, H, dk = 32, 512, 16, 64
+    dm = H * dk
+    rng = np.random.default_rng(99)
+    qkv = rng.standard_normal((Bn * S, 3 * dm), dtype=np.float32)
+    qkv[:, 2 * dm:] = 1.0
+    G = rng.standard_normal((Bn * S, dm), dtype=np.float32)
+    dq, out, lse, dG = ctx.upload(qkv), ctx.empty(Bn * S, dm), ctx.empty(Bn * H * S), ctx.upload(G)
+    d = attention_desc(ctx, dq, out, lse, Bn, S, H, True, 0.125)
+    ctx.check(ctx.lib.fml_attention_fwd(ctx.h, C.byref(d)))
+    o = out.numpy()
+    assert np.max(np.abs(o - 1.0)) <= 1e-5
+    dqkv, scratch = ctx.empty(Bn * S, 3 * dm), ctx.empty(Bn * H * S)
+    ctx.check(ctx.lib.fml_attention_bwd(ctx.h, C.byref(d), dG.ptr, dm, dqkv.ptr, dqkv.ptr + 4 * dm, dqkv.ptr + 8 * dm, 3 * dm, 0,
+                                        scratch.ptr))
+    g = dqkv.numpy()
+    assert np.max(np.abs(g[:, :2 * dm])) <= 5e-3 * np.max(np.abs(G))          # dQ = dK = 0 up to the TF32 rounding of dO in dP
+    dv_sum = g[:, 2 * dm:].reshape(Bn, S, dm).sum(1)
+    do_sum = G.reshape(Bn, S, dm).astype(np.float64).sum(1)
+    assert rel(dv_sum, do_sum) <= 1e-3
+    # random V again: the first query of every sequence attends to key 0 only
+    qkv[:, 2 * dm:] = rng.standard_normal((Bn * S, dm), dtype=np.float32)
+    dq2 = ctx.upload(qkv)
+    d2 = attention_desc(ctx, dq2, out, lse, Bn, S, H, True, 0.125)
+    ctx.check(ctx.lib.fml_attention_fwd(ctx.h, C.byref(d2)))
+    o = out.numpy().reshape(Bn, S, dm)
+    v = qkv[:, 2 * dm:].reshape(Bn, S, dm)
+    assert rel(o[:, 0, :], v[:, 0, :]) <= 1e-3        # one TF32 rounding of V
+    assert ctx.device_status() == 0
+    ctx.close()

@@ -478,3 +478,42 @@ def test_bounded_wait_times_out_and_the_context_survives():
     assert rel(C.numpy(), a.astype(np.float64) @ a.T.astype(np.float64)) <= TOL_TF32
     assert c.lib.fml_selftest_wait_timeout(c.h, 0) == -1          # limit out of range
     c.close()
+
+
+@pytest.mark.parametrize("prec,tol", [(0, TOL_TF32), (1, 1e-5)])
+def test_gemm_full_size_sampled_entries_and_exact_properties(prec, tol):
+    """Config 2's largest square (8192^3), too large for the float64 oracle in full: 4096 randomly chosen output
+    entries of C = A.B, dA = dC.B^T and dW = A^T.dC against exact float64 dot products of the same float32 operands,
+    plus two size-independent properties: scaling an operand by a power of two scales the result bit-exactly, and
+    (A.B)^T computed as B^T.A^T through the transposed-operand paths agrees with C."""
+    from flutter_ml_b200 import _lib
+    n = 8192
+    c = _lib.Context(precision=prec)
+    rng = np.random.default_rng(8192 + prec)
+    A = (rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
+    B = (rng.standard_normal((n, n), dtype=np.float32) / np.float32(np.sqrt(n)))
+    dA_, dB_, C_, D_ = c.upload(A), c.upload(B), c.empty(n, n), c.empty(n, n)
+    ii, jj = rng.integers(0, n, 4096), rng.integers(0, n, 4096)
+
+    def sampled(got, left_rows, right_cols):     # got[i, j] vs sum_k left_rows[i, k] * right_cols[k, j]
+        ref = np.einsum("sk,sk->s", left_rows.astype(np.float64), right_cols.astype(np.float64))
+        return float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+
+    c.gemm(dA_, dB_, C_, n, n, n)
+    C = C_.numpy()
+    assert sampled(C[ii, jj], A[ii, :], B[:, jj].T) <= tol
+    # dA = dC . B^T with dC := C's operand role played by A (any matrix serves), dW = A^T . dC likewise
+    c.gemm(dA_, dB_, D_, n, n, n, transB=True)
+    assert sampled(D_.numpy()[ii, jj], A[ii, :], B[jj, :]) <= tol
+    c.gemm(dA_, dB_, D_, n, n, n, transA=True)
+    assert sampled(D_.numpy()[ii, jj], A[:, ii].T, B[:, jj].T) <= tol
+    # (A.B)^T = B^T.A^T through both transposed-operand paths
+    c.gemm(dB_, dA_, D_, n, n, n, transA=True, transB=True)
+    Dt = D_.numpy()
+    assert rel(Dt[jj, ii], C[ii, jj]) <= max(tol * 1e-2, 2e-6)
+    # power-of-two scaling is exact in every rounding step
+    c.call("fml_axpy", 3.0, dA_, dA_, n * n)          # A <- 4 A
+    c.gemm(dA_, dB_, D_, n, n, n)
+    assert np.array_equal(D_.numpy()[ii, jj], 4.0 * C[ii, jj])
+    assert c.device_status() == 0
+    c.close()
