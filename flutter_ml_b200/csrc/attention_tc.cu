@@ -47,6 +47,13 @@ struct FaParams {
 
 enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KVEMPTY = 5, B_SFULL = 7, B_SEMPTY = 9, B_PFULL = 11, B_PVFULL = 12, B_QEMPTY = 13, B_COUNT = 14 };
 
+// 2^x on the special-function unit with flush-to-zero: the library exp2f adds a rescaling sequence for results below
+// 2^-126, which are zero for every purpose here
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // round-to-nearest of a finite non-negative float to TF32 (10 mantissa bits) with two integer instructions
 __device__ __forceinline__ float fa_round_tf32(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ uint32_t fa_idesc(int M, int N, int a_mn, int b_mn) {
@@ -218,7 +225,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.k2;   // k2 > 0: max commutes with the scale
         const float m_new = fmaxf(m, mx);            // finite: key 0 is visible to every row
-        const float alpha = exp2f(m - m_new);        // 0 for the first block (m = -inf)
+        const float alpha = fa_exp2(m - m_new);        // 0 for the first block (m = -inf)
         // the previous block's P.V must be folded in (and P be free) before P is overwritten
         if (j > 0) {
           ok = mbar_wait(bar(B_PVFULL), (g - 1) & 1u, abort_flag, p.status, 18);
@@ -250,7 +257,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               const int col = c * 32 + ch * 4 + e;
               // rounded to TF32 here, and the ROUNDED value enters the row sum: the tensor core would otherwise cut the
               // low mantissa bits of P on its own and every output would come out low by up to 2^-11 relative to l
-              const float pe_ = exp2f(fmaf(__uint_as_float(v[ch * 4 + e]), p.k2, -m_new));
+              const float pe_ = fa_exp2(fmaf(__uint_as_float(v[ch * 4 + e]), p.k2, -m_new));
               const float pr = (col < lim) ? (p.round_p ? fa_round_tf32(pe_) : pe_) : 0.f;
               pe[e] = pr;
               ls4[e] += pr;
@@ -464,7 +471,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const int col = c * 32 + ch * 4 + e;
-              const float pr = (col < lim) ? exp2f(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -L)) : 0.f;
+              const float pr = (col < lim) ? fa_exp2(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -L)) : 0.f;
               de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dv) * p.scale;
             }
             *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
@@ -719,7 +726,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
               const bool vis = !p.causal || (q0 + col >= kj);
               const float Lc = __shfl_sync(0xffffffffu, (col & 1) ? Lq.y : Lq.x, col >> 1);
               const float Dc = __shfl_sync(0xffffffffu, (col & 1) ? Dq.y : Dq.x, col >> 1);
-              const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -Lc)) : 0.f;
+              const float pr = vis ? fa_exp2(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -Lc)) : 0.f;
               pe[e] = pr;
               de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale;
             }
