@@ -91,6 +91,12 @@ __device__ __forceinline__ float fml_tanh_ref(float x) {
   return isinf(e2x) ? 1.f : (e2x - 1.f) / (e2x + 1.f);
 }
 
+// 2^x on the special-function unit, results below 2^-126 flushed to zero (exp2f adds a rescaling sequence for them)
+__device__ __forceinline__ float fml_exp2_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float fml_sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 __device__ __forceinline__ float fml_tanh_fast(float x) {
   const float e2x = __expf(2.f * x);          // same algebra and the same overflow rule as fml_tanh_ref

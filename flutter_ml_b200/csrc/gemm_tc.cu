@@ -391,17 +391,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               v[j] = __float_as_uint(x);
               cm = fmaxf(cm, x);
             }
-            if (cm > mx) { sum *= exp2f(mx - cm); mx = cm; }
+            if (cm > mx) { sum *= fml_exp2_ftz(mx - cm); mx = cm; }
             if (mx != -INFINITY) {
 #pragma unroll
-              for (int j = 0; j < 32; j++) sum += exp2f(__uint_as_float(v[j]) - mx);
+              for (int j = 0; j < 32; j++) sum += fml_exp2_ftz(__uint_as_float(v[j]) - mx);
             }
           }
           xch[0] = mx; xch[1] = sum;
           asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
           const float om = xch_other[0], os = xch_other[1];
           const float M2 = fmaxf(mx, om);   // finite: column 0 is valid for every row and belongs to one of the two
-          const float S2 = (mx == -INFINITY ? 0.f : sum * exp2f(mx - M2)) + (om == -INFINITY ? 0.f : os * exp2f(om - M2));
+          const float S2 = (mx == -INFINITY ? 0.f : sum * fml_exp2_ftz(mx - M2)) + (om == -INFINITY ? 0.f : os * fml_exp2_ftz(om - M2));
           const float inv = 1.f / S2;
           for (int cb = half; cb < ncb; cb += 2) {
             float4* dst = reinterpret_cast<float4*>(p.C + roff + cb * 32);
@@ -418,10 +418,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
               for (int j = 0; j < 8; j++) {
                 float4 o;
-                o.x = (cb * 32 + 4 * j + 0 < lim) ? exp2f(__uint_as_float(v[4 * j + 0]) * k2 - M2) * inv : 0.f;
-                o.y = (cb * 32 + 4 * j + 1 < lim) ? exp2f(__uint_as_float(v[4 * j + 1]) * k2 - M2) * inv : 0.f;
-                o.z = (cb * 32 + 4 * j + 2 < lim) ? exp2f(__uint_as_float(v[4 * j + 2]) * k2 - M2) * inv : 0.f;
-                o.w = (cb * 32 + 4 * j + 3 < lim) ? exp2f(__uint_as_float(v[4 * j + 3]) * k2 - M2) * inv : 0.f;
+                o.x = (cb * 32 + 4 * j + 0 < lim) ? fml_exp2_ftz(__uint_as_float(v[4 * j + 0]) * k2 - M2) * inv : 0.f;
+                o.y = (cb * 32 + 4 * j + 1 < lim) ? fml_exp2_ftz(__uint_as_float(v[4 * j + 1]) * k2 - M2) * inv : 0.f;
+                o.z = (cb * 32 + 4 * j + 2 < lim) ? fml_exp2_ftz(__uint_as_float(v[4 * j + 2]) * k2 - M2) * inv : 0.f;
+                o.w = (cb * 32 + 4 * j + 3 < lim) ? fml_exp2_ftz(__uint_as_float(v[4 * j + 3]) * k2 - M2) * inv : 0.f;
                 dst[j] = o;
               }
             }

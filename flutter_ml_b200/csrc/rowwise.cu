@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(256) softmax_fwd_warp(const float* __restrict_
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NV * 4; i++) {
-      v[i] = exp2f(v[i] - mx);  // 2^(-inf) = 0 for masked columns
+      v[i] = fml_exp2_ftz(v[i] - mx);  // 2^(-inf) = 0 for masked columns
       s += v[i];
     }
     const float inv = 1.f / warp_sum(s);
@@ -416,8 +416,8 @@ __global__ void __launch_bounds__(1024) xent_rowreg_kernel(const float* z, const
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; i++) {  // 2^(-inf) = 0 for the padding beyond cols
-      v[i].x = exp2f((v[i].x - bm) * LOG2E); v[i].y = exp2f((v[i].y - bm) * LOG2E);
-      v[i].z = exp2f((v[i].z - bm) * LOG2E); v[i].w = exp2f((v[i].w - bm) * LOG2E);
+      v[i].x = fml_exp2_ftz((v[i].x - bm) * LOG2E); v[i].y = fml_exp2_ftz((v[i].y - bm) * LOG2E);
+      v[i].z = fml_exp2_ftz((v[i].z - bm) * LOG2E); v[i].w = fml_exp2_ftz((v[i].w - bm) * LOG2E);
       s += v[i].x + v[i].y + v[i].z + v[i].w;
     }
     s = warp_sum(s);
