@@ -113,6 +113,7 @@ PROTOTYPES = {
     "fml_layernorm_fwd": [fp, fp, fp, fp, fp, fp, fp, fp, i64, i32, f32],
     "fml_layernorm_bwd": [fp, fp, fp, fp, fp, fp, fp, fp, i64, i32, i32],
     "fml_softmax_xent": [fp, fp, fp, fp, fp, i64, i32, f32],
+    "fml_softmax_xent_dbias": [fp, fp, fp, fp, fp, i64, i32, f32, fp],
     "fml_softmax_xent_static": [fp, fp, fp, fp, fp, i64, i32, f32],
     "fml_mse": [fp, fp, fp, fp, fp, i64, f32],
     "fml_embedding_fwd": [fp, fp, fp, fp, fp, i64, i32, i32],

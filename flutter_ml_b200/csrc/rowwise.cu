@@ -379,12 +379,23 @@ __global__ void __launch_bounds__(256) xent_kernel(const float* z, const int* __
 // Wide rows (vocabulary-sized logits): one 1024-thread block per row keeps the whole row in registers
 // (NV float4 per thread, all loads issued before the first use), so the logits are read from HBM exactly once
 // and the gradient written once: 8 bytes per element.  Two block reductions (max, sum of 2^(k(v - max))).
-template <int NV>
+// COLSUM: the block also sums the gradient rows it produces, column by column, in dynamic shared memory (every
+// thread owns its columns, so no synchronisation) and leaves one partial row per block in `colpart`: the bias
+// gradient of the layer that produced the logits, without a second pass over the gradient.
+template <int NV, bool COLSUM>
 __global__ void __launch_bounds__(1024) xent_rowreg_kernel(const float* z, const int* __restrict__ labels,
                                                            float* dz /* may alias z */, float* __restrict__ row_loss,
-                                                           long long rows, int cols, float inv_count) {
+                                                           long long rows, int cols, float inv_count, float* __restrict__ colpart) {
+  extern __shared__ float4 colacc[];   // [cols / 4], COLSUM only
   __shared__ float red[32];
   __shared__ float bcast[3];
+  if (COLSUM) {
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int c4 = threadIdx.x + 1024 * i;
+      if (c4 * 4 < cols) colacc[c4] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr float LOG2E = 1.4426950408889634f;
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -441,10 +452,22 @@ __global__ void __launch_bounds__(1024) xent_rowreg_kernel(const float* z, const
           const int d = lab - c4 * 4;
           if (d == 0) o.x -= inv_count; else if (d == 1) o.y -= inv_count; else if (d == 2) o.z -= inv_count; else if (d == 3) o.w -= inv_count;
           dr[c4] = o;
+          if (COLSUM) {
+            float4 a = colacc[c4];
+            a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w;
+            colacc[c4] = a;
+          }
         }
       }
     }
     __syncthreads();  // bcast / red are rewritten by the next row
+  }
+  if (COLSUM) {
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      const int c4 = threadIdx.x + 1024 * i;
+      if (c4 * 4 < cols) reinterpret_cast<float4*>(colpart + (size_t)blockIdx.x * cols)[c4] = colacc[c4];
+    }
   }
 }
 
@@ -582,23 +605,57 @@ int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, con
   return FML_OK;
 }
 
-int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum, int64_t rows,
-                         int32_t cols, float inv_count) {
-  FML_REQUIRE(ctx, z && labels && loss_sum && rows > 0 && cols > 0, "fml_softmax_xent: bad arguments");
-  int32_t rc = fml_ensure_workspace(ctx, (size_t)rows * sizeof(float));
+static int32_t softmax_xent_impl(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum, int64_t rows,
+                                 int32_t cols, float inv_count, float* dbias) {
+  const bool wide = cols >= 4096 && cols <= 32768 && cols % 4 == 0 && al16(z) && (!dz || al16(dz));
+  const int blocks = (int)std::max<long long>(1, std::min<long long>(rows, (long long)ctx->sm_count * 2));
+  const bool fuse = dbias && dz && wide;
+  const size_t loss_bytes = ((size_t)rows * sizeof(float) + 255) & ~(size_t)255;
+  int32_t rc = fml_ensure_workspace(ctx, loss_bytes + (fuse ? (size_t)blocks * cols * sizeof(float) : 0));
   if (rc) return rc;
   float* row_loss = reinterpret_cast<float*>(ctx->ws);
-  if (cols >= 4096 && cols <= 32768 && cols % 4 == 0 && al16(z) && (!dz || al16(dz))) {
-    const int blocks = (int)std::max<long long>(1, std::min<long long>(rows, (long long)ctx->sm_count * 2));
-    if (cols <= 8192) xent_rowreg_kernel<2><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
-    else if (cols <= 16384) xent_rowreg_kernel<4><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
-    else xent_rowreg_kernel<8><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+  float* colpart = reinterpret_cast<float*>(ctx->ws + loss_bytes);
+  if (wide) {
+#define XENT(NV)                                                                                                              \
+  do {                                                                                                                        \
+    if (fuse) {                                                                                                               \
+      static bool attr_set = false;                                                                                           \
+      if (!attr_set) {                                                                                                        \
+        FML_CUDA(ctx, cudaFuncSetAttribute(xent_rowreg_kernel<NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4)); \
+        attr_set = true;                                                                                                      \
+      }                                                                                                                       \
+      xent_rowreg_kernel<NV, true><<<blocks, 1024, (size_t)cols * 4, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, colpart); \
+    } else {                                                                                                                  \
+      xent_rowreg_kernel<NV, false><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, nullptr); \
+    }                                                                                                                         \
+  } while (0)
+    if (cols <= 8192) XENT(2);
+    else if (cols <= 16384) XENT(4);
+    else XENT(8);
+#undef XENT
   } else {
     xent_kernel<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
   }
   final_sum_kernel<float><<<1, 256, 0, ctx->stream>>>(row_loss, rows, 1.0, loss_sum);
   FML_LAUNCH_CHECK(ctx, "xent_kernel");
+  if (dbias) {
+    FML_REQUIRE(ctx, dz, "fml_softmax_xent_dbias: the bias gradient needs dz");
+    // one partial row per block (fused) or the gradient itself (other shapes), summed into dbias
+    return fuse ? fml_col_sum(ctx, colpart, dbias, blocks, cols, 1) : fml_col_sum(ctx, dz, dbias, rows, cols, 1);
+  }
   return FML_OK;
+}
+
+int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum, int64_t rows,
+                         int32_t cols, float inv_count) {
+  FML_REQUIRE(ctx, z && labels && loss_sum && rows > 0 && cols > 0, "fml_softmax_xent: bad arguments");
+  return softmax_xent_impl(ctx, z, labels, dz, loss_sum, rows, cols, inv_count, nullptr);
+}
+
+int32_t fml_softmax_xent_dbias(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum, int64_t rows,
+                               int32_t cols, float inv_count, float* dbias) {
+  FML_REQUIRE(ctx, z && labels && dz && loss_sum && dbias && rows > 0 && cols > 0, "fml_softmax_xent_dbias: bad arguments");
+  return softmax_xent_impl(ctx, z, labels, dz, loss_sum, rows, cols, inv_count, dbias);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -202,7 +202,7 @@ class TransformerLM:
         if keep_logits:
             kept = ctx.empty(*logits.shape)
             ctx.copy(kept, logits.value)
-        loss = T.softmaxCrossEntropy(logits, labels, 1.0 / n_global_tokens)
+        loss = T.softmaxCrossEntropy(logits, labels, 1.0 / n_global_tokens, bias_grad=True)
         loss.backward(before=before)
         if before:
             self._exchange(*self._slice(0, 1))              # the embedding table's gradient, last

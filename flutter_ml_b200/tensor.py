@@ -200,7 +200,11 @@ def denseMatrix(x: Tensor, W: Tensor, b: Optional[Tensor], act=None, precision: 
         if code == _lib.ACT_NONE or getattr(out, "_grad_is_dz", False):
             dz = out.grad  # already dLoss/dZ (no activation, or act' applied by the consumer's product)
             if b is not None:
-                ctx.call("fml_col_sum", dz, b.grad, M, N, 1)
+                pre = getattr(out, "_dbias", None)   # column sums already formed by the loss kernel
+                if pre is not None:
+                    ctx.call("fml_axpy", 1.0, pre, b.grad, N)
+                else:
+                    ctx.call("fml_col_sum", dz, b.grad, M, N, 1)
         else:
             dz = ctx.empty(M, N)
             ctx.call("fml_act_bwd", code, saved, out.grad, dz, M, N, 0, b.grad if b is not None else None,
@@ -543,14 +547,21 @@ def mseMatrix(pred: Tensor, target: Tensor, weight: float = 1.0) -> Tensor:
 mse = mseMatrix
 
 
-def softmaxCrossEntropy(logits: Tensor, labels: DeviceArray, inv_count: float) -> Tensor:
+def softmaxCrossEntropy(logits: Tensor, labels: DeviceArray, inv_count: float, bias_grad: bool = False) -> Tensor:
     """Extension (the reference has only mse / binaryCrossEntropy): sum over rows of
     -log softmax(z)[label] * inv_count.  The gradient overwrites the logits buffer in the same
-    kernel, so the [tokens x vocab] tensor exists once."""
+    kernel, so the [tokens x vocab] tensor exists once.  With `bias_grad` the same kernel also sums the
+    gradient over the rows; the dense node that produced the logits then adds that vector to its bias
+    gradient instead of reading the [tokens x vocab] gradient again (tensor.dart:698-704)."""
     ctx = logits.ctx
     R, C = logits.shape
     out = Tensor(ctx.zeros(1), ctx)
-    ctx.call("fml_softmax_xent", logits.value, labels, logits.value, out.value, R, C, float(inv_count), launches=2)
+    if bias_grad:
+        db = ctx.zeros(C)
+        ctx.call("fml_softmax_xent_dbias", logits.value, labels, logits.value, out.value, R, C, float(inv_count), db, launches=3)
+        logits._dbias = db
+    else:
+        ctx.call("fml_softmax_xent", logits.value, labels, logits.value, out.value, R, C, float(inv_count), launches=2)
 
     def bw():
         logits._add_grad(logits.value, alias=True)

@@ -232,6 +232,10 @@ int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, con
  * dz = (softmax(z) - onehot) * inv_count written in place of z when dz == z. */
 int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz,
                          float* loss_sum, int64_t rows, int32_t cols, float inv_count);
+/* fml_softmax_xent that also ADDS the column sums of dz into dbias: the bias gradient of the layer that produced
+ * the logits (addMatrixAndVector backward, tensor.dart:698-704) without a second pass over the gradient. */
+int32_t fml_softmax_xent_dbias(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz,
+                               float* loss_sum, int64_t rows, int32_t cols, float inv_count, float* dbias);
 /* Same computation and results as fml_softmax_xent, for callers that must not allocate.
  * (No counterpart in the reference: it has neither this loss nor device memory management.)
  * fml_softmax_xent may grow the context's scratch arena with cudaMalloc; this entry point never

@@ -209,6 +209,26 @@ def test_softmax_xent(ctx, orc, rows, cols):
     assert rel(dzz.numpy(), dz_ref) <= 2e-6
 
 
+@pytest.mark.parametrize("rows,cols", [(64, 10), (301, 4100), (700, 12288), (40, 32768)])
+def test_softmax_xent_with_bias_gradient(ctx, orc, rows, cols):
+    """fml_softmax_xent_dbias: loss and gradient as fml_softmax_xent, plus the column sums of the gradient ADDED into
+    dbias (addMatrixAndVector backward, tensor.dart:698-704) by the same pass."""
+    rng = np.random.default_rng(cols + 1)
+    z = (2 * rng.standard_normal((rows, cols))).astype(np.float32)
+    labels = rng.integers(0, cols, rows).astype(np.int32)
+    inv = 1.0 / rows
+    dz_ref = np.zeros((rows, cols))
+    loss_ref = orc.Ops().softmax_xent(w64(z), labels, dz_ref, inv)
+    base = rng.standard_normal(cols).astype(np.float32)
+    dzz, dl, loss, db = ctx.upload(z), ctx.upload(labels), ctx.zeros(1), ctx.upload(base)
+    ctx.call("fml_softmax_xent_dbias", dzz, dl, dzz, loss, rows, cols, inv, db, launches=3)
+    assert abs(loss.numpy()[0] - loss_ref) <= 2e-6 * abs(loss_ref)
+    assert rel(dzz.numpy(), dz_ref) <= 2e-6
+    got = db.numpy().astype(np.float64) - base
+    # fp32: one rounding of base + sum per column, plus the summation error of the column sums themselves
+    assert np.linalg.norm(got - dz_ref.sum(0)) <= 2e-7 * np.linalg.norm(base) + 1e-5 * np.linalg.norm(dz_ref.sum(0))
+
+
 def test_mse(ctx, orc):
     rng = np.random.default_rng(3)
     p, t = rng.standard_normal((257, 129)).astype(np.float32), rng.standard_normal((257, 129)).astype(np.float32)
