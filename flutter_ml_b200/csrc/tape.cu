@@ -186,6 +186,17 @@ int act2_of_kind(int kind) {
     if (rc__) return rc__;    \
   } while (0)
 
+int32_t attention_desc_of(fml_ctx* ctx, const fml_op& o, const std::string& where, fml_attention_desc* d) {
+  FML_REQUIRE(ctx, o.in[0] && o.in[1] && o.in[2] && o.aux[0] && o.aux[1] && o.inner > 0 && o.rows % o.inner == 0 && o.cols % 64 == 0,
+              where + " (attention): needs Q, K, V, aux[0], aux[1], rows = sequences * inner and cols = heads * 64");
+  std::memset(d, 0, sizeof(*d));
+  d->n_seq = o.rows / o.inner; d->seq_len = o.inner; d->heads = o.cols / 64; d->d_head = 64;
+  d->q = o.in[0]; d->k = o.in[1]; d->v = o.in[2]; d->ld_qkv = o.cols;
+  d->out = o.out; d->ld_out = o.cols; d->lse = o.aux[0];
+  d->scale = o.s; d->causal = o.iparam != 0;
+  return FML_OK;
+}
+
 int32_t op_forward(fml_ctx* ctx, const fml_op& o, int idx) {
   const long long n = (long long)o.rows * o.cols;
   const std::string where = "fml_tape_run: op " + std::to_string(idx);
@@ -266,6 +277,11 @@ int32_t op_forward(fml_ctx* ctx, const fml_op& o, int idx) {
       sum_final_kernel<<<1, TP_THREADS, 0, st>>>(reinterpret_cast<const double*>(ctx->ws), blocks, o.out);
       FML_LAUNCH_CHECK(ctx, "sum_kernel");
       return FML_OK;
+    }
+    case FML_OP_ATTENTION: {
+      fml_attention_desc d;
+      TP_TRY(attention_desc_of(ctx, o, where, &d));
+      return fml_attention_fwd(ctx, &d);
     }
     case FML_OP_CONV2D: {
       const int pad = (int)o.s, H = o.rows + o.inner - 1 - 2 * pad, W = o.cols + o.iparam - 1 - 2 * pad;
@@ -389,6 +405,13 @@ int32_t op_backward(fml_ctx* ctx, const fml_op& o, int idx) {
         FML_LAUNCH_CHECK(ctx, "broadcast_add_dev_kernel");
       }
       return FML_OK;
+    case FML_OP_ATTENTION: {
+      if (!o.gin[0] && !o.gin[1] && !o.gin[2]) return FML_OK;
+      FML_REQUIRE(ctx, o.gin[0] && o.gin[1] && o.gin[2], where + " (attention): dQ, dK and dV are produced together; give all three or none");
+      fml_attention_desc d;
+      TP_TRY(attention_desc_of(ctx, o, where, &d));
+      return fml_attention_bwd(ctx, &d, o.gout, o.cols, o.gin[0], o.gin[1], o.gin[2], o.cols, 1, o.aux[1]);
+    }
     case FML_OP_CONV2D: {
       const int pad = (int)o.s, H = o.rows + o.inner - 1 - 2 * pad, W = o.cols + o.iparam - 1 - 2 * pad;
       if (!o.gin[0] && !o.gin[1]) return FML_OK;
@@ -430,7 +453,7 @@ const KindName KIND_NAMES[] = {
     {"concat_matrix_col", FML_OP_CONCAT}, {"concat_vector", FML_OP_CONCAT}, {"softmax_matrix", FML_OP_SOFTMAX_MATRIX},
     {"softmax", FML_OP_SOFTMAX_MATRIX}, {"layer_norm", FML_OP_LAYER_NORM}, {"layer_norm_vector", FML_OP_LAYER_NORM},
     {"embedding_lookup", FML_OP_EMBEDDING_LOOKUP}, {"mse_matrix", FML_OP_MSE}, {"mse_vector", FML_OP_MSE},
-    {"conv2d", FML_OP_CONV2D}, {"addScalarToMatrix", FML_OP_ADD_SCALAR_TO_MATRIX}, {"sum_matrix", FML_OP_SUM}, {"sum_vector", FML_OP_SUM}, {"softmax_xent", FML_OP_SOFTMAX_XENT}, {"dense", FML_OP_DENSE},
+    {"attention", FML_OP_ATTENTION}, {"conv2d", FML_OP_CONV2D}, {"addScalarToMatrix", FML_OP_ADD_SCALAR_TO_MATRIX}, {"sum_matrix", FML_OP_SUM}, {"sum_vector", FML_OP_SUM}, {"softmax_xent", FML_OP_SOFTMAX_XENT}, {"dense", FML_OP_DENSE},
     {"dense_matrix", FML_OP_DENSE}};
 
 }  // namespace

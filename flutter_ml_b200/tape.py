@@ -22,7 +22,7 @@ from . import _lib
 KIND = {"matMul": 1, "matVecMul": 2, "addMatrixAndVector": 3, "add": 4, "multiply": 5, "relu": 6, "sigmoid": 7,
         "tanh": 8, "gelu": 9, "leaky_relu": 10, "elu": 11, "swish": 12, "mish": 13, "scale_matrix": 14,
         "transpose": 15, "concat": 16, "softmax_matrix": 17, "layer_norm": 18, "embedding_lookup": 19, "mse": 20,
-        "sum": 21, "softmax_xent": 22, "dense": 23, "conv2d": 24, "addScalarToMatrix": 25}
+        "sum": 21, "softmax_xent": 22, "dense": 23, "conv2d": 24, "addScalarToMatrix": 25, "attention": 26}
 FORWARD, BACKWARD, BACKWARD_NOSEED = 0, 1, 2
 
 
@@ -175,6 +175,14 @@ class Tape:
     def addScalarToMatrix(self, m, s):            # tensor.dart:711-737 (s is a 1 x 1 tensor)
         assert s.shape == (1, 1)
         return self._record("addScalarToMatrix", self._new(m.rows, m.cols), (m, s))
+
+    def attention(self, q, k, v, seq_len: int, scale: float, causal: bool = False):   # extension: one fused node
+        """softmax(scale Q.K^T [+ causal mask]) . V for rows / seq_len sequences and cols / 64 heads
+        (singleHeadAttentionLayer.dart:77-86 + the head concat of multiHeadAttentionLayer.dart:80)."""
+        assert q.shape == k.shape == v.shape and q.rows % seq_len == 0 and q.cols % 64 == 0
+        n = q.rows * (q.cols // 64)
+        aux = (self.ctx.empty(n), self.ctx.empty(n))
+        return self._record("attention", self._new(q.rows, q.cols), (q, k, v), inner=seq_len, aux=aux, s=scale, iparam=int(causal))
 
     def softmaxCrossEntropy(self, logits, labels, inv_count):   # extension
         aux = (self.ctx.empty(logits.rows, logits.cols),)

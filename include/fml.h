@@ -335,6 +335,10 @@ int32_t fml_act2_bwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, co
  *   conv2d              out[r x c] = in0 (image) cross-correlated with in1 (kernel, inner x iparam taps),
  *                       s = padding on every side (0 'valid', (inner - 1) / 2 'same')  tensor.dart:765-833
  *   addScalarToMatrix   out = in0 + in1[0] (in1 is 1 x 1)                      tensor.dart:711-737
+ *   attention (extension)  out[r x c] = softmax(s * Q.K^T [+ causal mask]) . V for r / inner sequences of inner positions
+ *                       and c / 64 heads in one fused kernel (fml_attention_fwd): in0, in1, in2 = Q, K, V, each [r x c]
+ *                       with head h in columns 64 h .. 64 h + 63; s = scale, iparam != 0 = causal; aux0 and aux1 are
+ *                       caller-provided buffers of r * c / 64 floats (row statistics, backward scratch)
  *   dense (extension)   out = act(in0[r x inner] . in1[inner x c] + in2), iparam = fml_act, aux0 = pre-activation
  *                       buffer for GELU: matMul + addMatrixAndVector + activation of
  *                       DenseLayerMatrix.forward (denseLayer.dart:116-125) as one launch; its backward rule
@@ -344,7 +348,7 @@ typedef enum {
   FML_OP_RELU = 6, FML_OP_SIGMOID = 7, FML_OP_TANH = 8, FML_OP_GELU = 9, FML_OP_LEAKY_RELU = 10, FML_OP_ELU = 11,
   FML_OP_SWISH = 12, FML_OP_MISH = 13, FML_OP_SCALE_MATRIX = 14, FML_OP_TRANSPOSE = 15, FML_OP_CONCAT = 16,
   FML_OP_SOFTMAX_MATRIX = 17, FML_OP_LAYER_NORM = 18, FML_OP_EMBEDDING_LOOKUP = 19, FML_OP_MSE = 20, FML_OP_SUM = 21,
-  FML_OP_SOFTMAX_XENT = 22, FML_OP_DENSE = 23, FML_OP_CONV2D = 24, FML_OP_ADD_SCALAR_TO_MATRIX = 25
+  FML_OP_SOFTMAX_XENT = 22, FML_OP_DENSE = 23, FML_OP_CONV2D = 24, FML_OP_ADD_SCALAR_TO_MATRIX = 25, FML_OP_ATTENTION = 26
 } fml_op_kind;
 typedef enum { FML_TAPE_FORWARD = 0, FML_TAPE_BACKWARD = 1, FML_TAPE_BACKWARD_NOSEED = 2 } fml_tape_direction;
 

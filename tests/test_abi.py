@@ -62,7 +62,7 @@ def test_tape_kind_knows_the_reference_op_names():
              "sigmoid_vector", "sigmoid_matrix", "tanh_vector", "tanh_matrix", "multiply_vector", "multiply_matrix",
              "concat_vector", "concat_matrix_col", "scale_matrix", "transpose", "softmax_matrix", "layer_norm",
              "embedding_lookup", "mse_vector", "mse_matrix", "sum_vector", "sum_matrix", "leaky_relu", "elu", "swish",
-             "gelu", "softmax_xent", "dense", "conv2d", "addScalarToMatrix"]
+             "gelu", "softmax_xent", "dense", "conv2d", "addScalarToMatrix", "attention"]
     kinds = {n: lib.fml_tape_kind(n.encode()) for n in names}
     assert all(k > 0 for k in kinds.values()), kinds
     assert kinds["relu_matrix"] == kinds["relu_vector"] and kinds["add_matrix"] == kinds["add_vector"]

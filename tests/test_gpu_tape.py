@@ -365,3 +365,36 @@ def test_conv_lstm_cell_as_a_tape(orc, fp32_ctx):
     assert rel(th.numpy(), oh.value) <= 2e-6
     for t, o in zip(tparams, oparams):
         assert rel(t.grad_numpy(), o.grad) <= 2e-5
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_fused_attention_node_on_the_tape(orc, causal):
+    """The `attention` node (one fused kernel for all heads) inside a tape: projections by matMul, the node, the
+    output projection and an mse loss, against the oracle's per-head chain (multiHeadAttentionLayer.dart:72-84)."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200.tape import Tape
+    ctx = _lib.Context(precision=_lib.PREC_3XTF32)   # the surrounding products near-exact; the node itself is TF32
+    S, d, H, dk = 128, 96, 2, 64
+    rng = np.random.default_rng(3 + causal)
+    f = lambda *s: rng.standard_normal(s).astype(np.float32)
+    x, target = f(S, d), f(S, d)
+    Wq, Wk, Wv, Wo = f(d, H * dk) * 0.1, f(d, H * dk) * 0.1, f(d, H * dk) * 0.1, f(H * dk, d) * 0.1
+    E = orc.Engine()
+    ox, oWo = orc.T(w64(x)), orc.T(w64(Wo))
+    oheads = [tuple(orc.T(w64(W[:, h * dk:(h + 1) * dk])) for W in (Wq, Wk, Wv)) for h in range(H)]
+    oy = E.multi_head(ox, oheads, oWo, causal)
+    E.mseMatrix(oy, orc.T(w64(target))).backward()
+    tp = Tape(ctx)
+    tx, tq, tk, tv, tWo = tp.tensor(x), tp.tensor(Wq), tp.tensor(Wk), tp.tensor(Wv), tp.tensor(Wo)
+    att = tp.attention(tp.matMul(tx, tq), tp.matMul(tx, tk), tp.matMul(tx, tv), S, 1 / math.sqrt(dk), causal)
+    ty = tp.matMul(att, tWo)
+    tp.mseMatrix(ty, tp.tensor(target, requires_grad=False))
+    tp.forward()
+    tp.backward()
+    assert ctx.device_status() == 0
+    assert rel(ty.numpy(), oy.value) <= 2e-3
+    assert rel(tx.grad_numpy(), ox.grad) <= 5e-3 and rel(tWo.grad_numpy(), oWo.grad) <= 5e-3
+    for h in range(H):
+        for t, o in zip((tq, tk, tv), oheads[h]):
+            assert rel(t.grad_numpy()[:, h * dk:(h + 1) * dk], o.grad) <= 5e-3
+    ctx.close()
