@@ -958,6 +958,24 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
         if (d->beta == 0.f)
           FML_CUDA(ctx, cudaMemset2DAsync(d->C, (size_t)d->ldc * 4, 0, (size_t)d->N * 4, (size_t)d->M, ctx->stream));
       }
+    } else if (splittable && p.kblocks >= 64 && (long long)d->M * d->N <= (4ll << 20)) {
+      // Partial single wave (a weight gradient with 48 pair tiles on 74 pairs leaves a third of the machine idle
+      // for the whole K loop): a small K split that makes the work units fill whole waves.  cost = waves / split.
+      const long long slots = pair ? ctx->sm_count / 2 : ctx->sm_count;
+      if (tiles_all < slots) {
+        int best = 1;
+        double best_cost = 1.0;
+        for (int ks = 2; ks <= 6; ks++) {
+          const double cost = (double)((tiles_all * ks + slots - 1) / slots) / ks * (1.0 + 0.03 * (ks - 1));
+          if (cost < best_cost * 0.85) { best = ks; best_cost = cost; }
+        }
+        if (best > 1) {
+          p.kb_per_split = (p.kblocks + best - 1) / best;
+          p.ksplit = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
+          if (d->beta == 0.f)
+            FML_CUDA(ctx, cudaMemset2DAsync(d->C, (size_t)d->ldc * 4, 0, (size_t)d->N * 4, (size_t)d->M, ctx->stream));
+        }
+      }
     }
   }
   p.C = d->C; p.Z = d->preact; p.bias = d->bias;
