@@ -699,10 +699,10 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       for (int i = 0; i < n_it && ok; i++, u++) {
         const uint32_t ph = u & 1u;
         const int q0 = (i0 + i) * BQ2;
-        // row statistics of the 64 queries of this block: lane l holds queries 2l and 2l + 1, the inner loop fetches
-        // the one it needs with a shuffle (no block-wide barrier inside a loop whose waits can give up)
-        const float2 Lq = __ldg(reinterpret_cast<const float2*>(p.lse + stat_base + q0) + lane);
-        const float2 Dq = __ldg(reinterpret_cast<const float2*>(p.dsum + stat_base + q0) + lane);
+        // row statistics of the 32 queries this warp handles: every lane reads the same addresses (one transaction per
+        // warp, L1 hits); shuffles cost a warp-wide issue slot each and were a seventh of this loop
+        const float4* Lp = reinterpret_cast<const float4*>(p.lse + stat_base + q0 + half * 32);
+        const float4* Dp = reinterpret_cast<const float4*>(p.dsum + stat_base + q0 + half * 32);
         const int bf = u & 1;
         ok = mbar_wait(bar(D_STFULL + bf), (u >> 1) & 1u, abort_flag, p.status, 36);
         if (ok && i > 0) ok = mbar_wait(bar(D_ACCDONE), ph ^ 1u, abort_flag, p.status, 37);   // P^T / dS^T tiles free again
@@ -720,12 +720,14 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             float4 pv, dsv;
             float* pe = reinterpret_cast<float*>(&pv);
             float* de = reinterpret_cast<float*>(&dsv);
+            const float4 L4 = __ldg(Lp + ch), D4 = __ldg(Dp + ch);
+            const float* Le = reinterpret_cast<const float*>(&L4);
+            const float* De = reinterpret_cast<const float*>(&D4);
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const int col = c * 32 + ch * 4 + e;            // query inside the block
               const bool vis = !p.causal || (q0 + col >= kj);
-              const float Lc = __shfl_sync(0xffffffffu, (col & 1) ? Lq.y : Lq.x, col >> 1);
-              const float Dc = __shfl_sync(0xffffffffu, (col & 1) ? Dq.y : Dq.x, col >> 1);
+              const float Lc = Le[e], Dc = De[e];
               const float pr = vis ? fa_exp2(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -Lc)) : 0.f;
               pe[e] = pr;
               de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale;
