@@ -218,24 +218,27 @@ __global__ void __launch_bounds__(256) layernorm_fwd_warp(const float* __restric
   }
 }
 
+// The per-warp column partials of dgamma and dbeta live in dynamic shared memory (every lane owns its slots, so no
+// synchronisation inside the row loop): with them in registers the kernel needed 187 registers and only one block
+// fitted an SM; now two do.
 template <int NV, bool ACC>
-__global__ void __launch_bounds__(256) layernorm_bwd_warp(const float* __restrict__ dy, const float* __restrict__ gamma,
-                                                          const float* __restrict__ xhat, const float* __restrict__ rstd,
-                                                          float* dx, float* dgamma, float* dbeta, long long rows, int cols) {
-  __shared__ float red[8][128];  // one float4 slot per lane per warp, reused for every i
+__global__ void __launch_bounds__(256, 2) layernorm_bwd_warp(const float* __restrict__ dy, const float* __restrict__ gamma,
+                                                             const float* __restrict__ xhat, const float* __restrict__ rstd,
+                                                             float* dx, float* dgamma, float* dbeta, long long rows, int cols) {
+  extern __shared__ float4 ln_acc[];   // [2 (dgamma, dbeta)][8 warps][NV * 32] float4
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  float4 g[NV], dg[NV], db[NV];
+  float4* ag = ln_acc + warp * (NV * 32) + lane;
+  float4* ab = ln_acc + (8 + warp) * (NV * 32) + lane;
 #pragma unroll
   for (int i = 0; i < NV; i++) {
-    g[i] = dg[i] = db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if ((lane + 32 * i) * 4 < cols) g[i] = reinterpret_cast<const float4*>(gamma)[lane + 32 * i];
+    ag[32 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ab[32 * i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   const float fc = (float)cols;
   for (long long r = warp0; r < rows; r += nwarps) {
     float4 d[NV], n[NV];
-    float sum_g = 0.f, dot = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; i++) {
       d[i] = n[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -243,9 +246,18 @@ __global__ void __launch_bounds__(256) layernorm_bwd_warp(const float* __restric
         d[i] = reinterpret_cast<const float4*>(dy + r * cols)[lane + 32 * i];
         n[i] = reinterpret_cast<const float4*>(xhat + r * cols)[lane + 32 * i];
       }
-      dg[i].x += d[i].x * n[i].x; dg[i].y += d[i].y * n[i].y; dg[i].z += d[i].z * n[i].z; dg[i].w += d[i].w * n[i].w;
-      db[i].x += d[i].x; db[i].y += d[i].y; db[i].z += d[i].z; db[i].w += d[i].w;
-      d[i].x *= g[i].x; d[i].y *= g[i].y; d[i].z *= g[i].z; d[i].w *= g[i].w;  // grad wrt xhat
+    }
+    float sum_g = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      float4 a = ag[32 * i], bb = ab[32 * i];
+      a.x += d[i].x * n[i].x; a.y += d[i].y * n[i].y; a.z += d[i].z * n[i].z; a.w += d[i].w * n[i].w;
+      bb.x += d[i].x; bb.y += d[i].y; bb.z += d[i].z; bb.w += d[i].w;
+      ag[32 * i] = a;
+      ab[32 * i] = bb;
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);   // gamma stays in L1: re-read per row instead of held in registers
+      if ((lane + 32 * i) * 4 < cols) g = __ldg(reinterpret_cast<const float4*>(gamma) + lane + 32 * i);
+      d[i].x *= g.x; d[i].y *= g.y; d[i].z *= g.z; d[i].w *= g.w;  // grad wrt xhat
       sum_g += d[i].x + d[i].y + d[i].z + d[i].w;
       dot += d[i].x * n[i].x + d[i].y * n[i].y + d[i].z * n[i].z + d[i].w * n[i].w;
     }
@@ -272,25 +284,17 @@ __global__ void __launch_bounds__(256) layernorm_bwd_warp(const float* __restric
       }
     }
   }
-  // reduce the per-warp column partials across the 8 warps, then one atomic per column per block
-#pragma unroll
+  // column partials of the 8 warps -> one atomic per column per block
+  __syncthreads();
+  const float* accf = reinterpret_cast<const float*>(ln_acc);
   for (int pass = 0; pass < 2; pass++) {
     float* dst = pass == 0 ? dgamma : dbeta;
     if (!dst) continue;
+    for (int c = threadIdx.x; c < NV * 128; c += 256) {
+      float t = 0.f;
 #pragma unroll
-    for (int i = 0; i < NV; i++) {
-      const float4 v = pass == 0 ? dg[i] : db[i];
-      __syncthreads();
-      red[warp][lane * 4 + 0] = v.x; red[warp][lane * 4 + 1] = v.y;
-      red[warp][lane * 4 + 2] = v.z; red[warp][lane * 4 + 3] = v.w;
-      __syncthreads();
-      if (threadIdx.x < 128) {
-        float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; w++) t += red[w][threadIdx.x];
-        const int c = (threadIdx.x >> 2) * 4 + 128 * i + (threadIdx.x & 3);  // lane*4 + e + 128*i
-        if (c < cols) atomicAdd(dst + c, t);
-      }
+      for (int w = 0; w < 8; w++) t += accf[(size_t)(pass * 8 + w) * (NV * 128) + c];
+      if (c < cols) atomicAdd(dst + c, t);
     }
   }
 }
@@ -591,10 +595,17 @@ int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, con
     const int blocks = (int)std::max<long long>(1, std::min<long long>((rows + 7) / 8, (long long)ctx->sm_count * 2));
 #define CALL(NV)                                                                                                     \
   do {                                                                                                               \
+    const size_t sm = (size_t)2 * 8 * NV * 128 * sizeof(float);                                                      \
+    static bool attr_set = false;                                                                                    \
+    if (!attr_set) {                                                                                                 \
+      FML_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_warp<NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));  \
+      FML_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_warp<NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
+      attr_set = true;                                                                                               \
+    }                                                                                                                \
     if (accumulate_dx && dx)                                                                                         \
-      layernorm_bwd_warp<NV, true><<<blocks, 256, 0, ctx->stream>>>(dy, gamma, xhat, rstd, dx, dgamma, dbeta, rows, cols);  \
+      layernorm_bwd_warp<NV, true><<<blocks, 256, sm, ctx->stream>>>(dy, gamma, xhat, rstd, dx, dgamma, dbeta, rows, cols);  \
     else                                                                                                             \
-      layernorm_bwd_warp<NV, false><<<blocks, 256, 0, ctx->stream>>>(dy, gamma, xhat, rstd, dx, dgamma, dbeta, rows, cols); \
+      layernorm_bwd_warp<NV, false><<<blocks, 256, sm, ctx->stream>>>(dy, gamma, xhat, rstd, dx, dgamma, dbeta, rows, cols); \
   } while (0)
     if (cols <= 128) { CALL(1); } else if (cols <= 256) { CALL(2); } else if (cols <= 512) { CALL(4); } else { CALL(8); }
 #undef CALL
