@@ -83,6 +83,8 @@ PROTOTYPES = {
     "fml_copy": [fp, fp, fp, i64],
     "fml_host_alloc": [fp, i64, C.POINTER(fp)],
     "fml_host_free": [fp, fp],
+    "fml_event_sync": [fp, i32],
+    "fml_stage_rows": [fp, fp, fp, i32, i64, fp, i64, i64, i32],
     "fml_event_record": [fp, i32],
     "fml_event_elapsed_ms": [fp, i32, i32, C.POINTER(f32)],
     "fml_lane_h2d": [fp, i32, fp, fp, i64],

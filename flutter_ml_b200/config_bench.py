@@ -37,6 +37,48 @@ def config1_mlp(ctx):
     gms, _ = _timed(ctx, mlp.replay_step, warm=5, reps=200)
     out.update({"graph_us_per_step": round(gms * 1e3, 1), "graph_samples_per_s": round(64 / gms * 1e3, 1)})
     out.update(_config1_tape(ctx))
+    out.update(_config1_fed(ctx, mlp))
+    return out
+
+
+def _feed_arms(ctx, mlp, X, y, B):
+    """(prefetching feeder, blocking upload per step) in ms per step of batch B over the host arrays X, y."""
+    from .feeder import BatchFeeder
+    batches = X.shape[0] // B
+    feeder = BatchFeeder(ctx, [X, y], B)
+    for xb, yb in feeder.batches():      # warm-up epoch
+        mlp.train_step(xb, yb)
+    ctx.sync()
+    ctx.timer_start()
+    for xb, yb in feeder.batches():
+        mlp.train_step(xb, yb)
+    fed_ms = ctx.timer_stop_ms() / batches
+    dX, dy = ctx.empty(B, X.shape[1]), ctx.empty(B, dtype=np.int32)
+    ctx.sync()
+    ctx.timer_start()
+    for s in range(batches):
+        ctx.upload(X[B * s:B * s + B], out=dX)
+        ctx.upload(y[B * s:B * s + B], out=dy)
+        mlp.train_step(dX, dy)
+    return fed_ms, ctx.timer_stop_ms() / batches
+
+
+def _config1_fed(ctx, mlp):
+    """The same step with every batch coming from HOST memory: through the prefetching feeder (staging + copy lane,
+    one batch ahead) and, for comparison, with a blocking upload in front of every step the way the reference's
+    binding stages its operands (lib/cuda/cudacaller.dart:32-47).  At batch 64 the step is bound by the host's
+    launch rate either way; the second pair uses batches of 16384 rows (51 MB), where the copy is what is hidden."""
+    X = np.concatenate([synth.uniform(0, 100 + i, (64, 784)) for i in range(200)])
+    y = np.concatenate([synth.integers(0, 300 + i, (64,), 10) for i in range(200)])
+    fed_ms, blk_ms = _feed_arms(ctx, mlp, X, y, 64)
+    out = {"fed_us_per_step": round(fed_ms * 1e3, 1), "fed_samples_per_s": round(64 / fed_ms * 1e3, 1),
+           "blocking_upload_us_per_step": round(blk_ms * 1e3, 1), "fed_h2d_bytes_per_step": 64 * 785 * 4}
+    B = 16384
+    X = synth.uniform(0, 500, (12 * B, 784))
+    y = synth.integers(0, 501, (12 * B,), 10)
+    fed_ms, blk_ms = _feed_arms(ctx, mlp, X, y, B)
+    out["fed_batch16384"] = {"fed_ms_per_step": round(fed_ms, 3), "blocking_upload_ms_per_step": round(blk_ms, 3),
+                             "fed_samples_per_s": round(B / fed_ms * 1e3, 1), "h2d_gbs": round(B * 785 * 4 / fed_ms / 1e6, 1)}
     return out
 
 

@@ -1,7 +1,10 @@
 // Context, memory, timing, dispatch of fml_gemm and the two legacy symbols.
 #include <algorithm>
 #include <chrono>
+#include <cstring>
 #include <mutex>
+#include <thread>
+#include <vector>
 
 #include "common.cuh"
 
@@ -289,6 +292,11 @@ int32_t fml_wait_event(fml_ctx* ctx, int32_t lane, int32_t slot) {
   FML_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev_pool[slot], 0));
   return FML_OK;
 }
+int32_t fml_event_sync(fml_ctx* ctx, int32_t slot) {
+  FML_REQUIRE(ctx, slot >= 0 && slot < 64 && ctx->ev_pool[slot], "fml_event_sync: slot not recorded");
+  FML_CUDA(ctx, cudaEventSynchronize(ctx->ev_pool[slot]));
+  return FML_OK;
+}
 int32_t fml_lane_h2d(fml_ctx* ctx, int32_t lane, float* dst, const float* host, int64_t n) {
   cudaStream_t s;
   int32_t rc = lane_stream(ctx, lane, &s);
@@ -350,6 +358,64 @@ int32_t fml_host_alloc(fml_ctx* ctx, int64_t bytes, void** out) {
 }
 int32_t fml_host_free(fml_ctx* ctx, void* p) {
   if (p) FML_CUDA(ctx, cudaFreeHost(p));
+  return FML_OK;
+}
+
+// Rows of a host array -> a (page-locked) staging buffer, on several host threads.  One thread moves about
+// 10 GB/s, a quarter of what the PCIe link takes, so a single-threaded gather would be the bottleneck of a feeder.
+extern "C++" {
+namespace {
+template <typename S, typename D>
+void stage_rows_range(D* dst, const S* src, int64_t row_elems, const int64_t* index, int64_t first, int64_t r0, int64_t r1) {
+  for (int64_t r = r0; r < r1; r++) {
+    const S* s = src + (index ? index[r] : first + r) * row_elems;
+    D* d = dst + r * row_elems;
+    if (sizeof(S) == sizeof(D)) {
+      memcpy(d, s, (size_t)row_elems * sizeof(D));
+    } else {
+      for (int64_t i = 0; i < row_elems; i++) d[i] = (D)s[i];
+    }
+  }
+}
+}  // namespace
+}  // extern "C++"
+
+int32_t fml_stage_rows(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
+                       const int64_t* index, int64_t first_row, int64_t rows, int32_t threads) {
+  FML_REQUIRE(ctx, dst && src && row_elems > 0 && rows >= 0, "fml_stage_rows: bad arguments");
+  FML_REQUIRE(ctx, src_kind >= 0 && src_kind <= 3, "fml_stage_rows: src_kind is 0 f32, 1 f64, 2 i32, 3 i64");
+  if (rows == 0) return FML_OK;
+  const int64_t bytes = rows * row_elems * 4;
+  int nt = threads > 0 ? threads : (int)std::min<int64_t>(std::max(1u, std::thread::hardware_concurrency()), 16);
+  nt = (int)std::max<int64_t>(1, std::min<int64_t>(nt, std::min<int64_t>(rows, bytes / (1 << 20) + 1)));  // >= 1 MiB per thread
+  auto run = [&](int64_t r0, int64_t r1) {
+    switch (src_kind) {
+      case 0: stage_rows_range((float*)dst, (const float*)src, row_elems, index, first_row, r0, r1); break;
+      case 1: stage_rows_range((float*)dst, (const double*)src, row_elems, index, first_row, r0, r1); break;
+      case 2: stage_rows_range((int32_t*)dst, (const int32_t*)src, row_elems, index, first_row, r0, r1); break;
+      default: stage_rows_range((int32_t*)dst, (const int64_t*)src, row_elems, index, first_row, r0, r1); break;
+    }
+  };
+  if (nt == 1) {
+    run(0, rows);
+    return FML_OK;
+  }
+  std::vector<std::thread> pool;
+  pool.reserve(nt - 1);
+  const int64_t per = (rows + nt - 1) / nt;
+  try {
+    for (int t = 1; t < nt; t++) {
+      const int64_t r0 = std::min(rows, t * per), r1 = std::min(rows, r0 + per);
+      if (r0 < r1) pool.emplace_back(run, r0, r1);
+    }
+  } catch (...) {   // thread creation failed: finish what was started, do the rest here
+    for (auto& th : pool) th.join();
+    run(std::min(rows, (int64_t)(pool.size() + 1) * per), rows);
+    run(0, std::min(rows, per));
+    return FML_OK;
+  }
+  run(0, std::min(rows, per));
+  for (auto& th : pool) th.join();
   return FML_OK;
 }
 

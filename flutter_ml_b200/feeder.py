@@ -1,0 +1,118 @@
+"""Batched data feeding for SNetwork.fit-style training loops (lib/nets/snet.dart:71-85).
+
+The reference's fit() walks host lists sample by sample and, on the CUDA path, stages every operand through
+pageable buffers with blocking copies (lib/cuda/cudacaller.dart:32-58).  Here the training set stays in host
+memory (numpy), and a feeder moves one batch at a time:
+
+  host rows --threaded gather (fml_stage_rows)--> page-locked staging[b] --copy lane 0, async--> device batch[b]      (b = step % 2)
+
+Two staging buffers and two device buffers per stream of data, so the host memcpy and the host->device copy of
+batch s+1 run while the kernels of batch s execute on the context's stream.  Ordering is carried by the
+library's numbered events: the copy lane waits for "kernels of the step that last used set b are done" before it
+overwrites device set b, the main stream waits for "upload of set b is done" before the step's first kernel.
+The host refills a staging buffer only after the lane has drained the copy that read it.
+"""
+from __future__ import annotations
+
+from typing import Iterator, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ._lib import Context, DeviceArray
+
+# event slots of the library's pool (0..63) owned by the feeder: +0 / +1 per buffer set
+_EV_UPLOADED, _EV_CONSUMED = 46, 48
+_LANE = 0
+
+
+class BatchFeeder:
+    """Iterates over (inputs, targets) batches as device arrays, prefetching the next batch.
+
+    `arrays` are host arrays that share their first dimension (the sample axis); float arrays are fed as
+    float32, integer arrays (labels, token ids) as int32.  `order` is an optional permutation of the sample
+    indices (a seeded shuffle is the caller's business: the feeder itself is deterministic).  The last batch
+    may be smaller; `drop_last` skips it.
+
+    The device arrays handed out by one iteration are overwritten two iterations later, so a consumer must not
+    keep them across steps (the training loop does not: the tape of a step is dropped by backward())."""
+
+    def __init__(self, ctx: Context, arrays: Sequence[np.ndarray], batch_size: int, drop_last: bool = False):
+        assert len(arrays) > 0 and batch_size > 0
+        self.ctx, self.batch_size, self.drop_last = ctx, int(batch_size), drop_last
+        self.n = int(arrays[0].shape[0])
+        self.host = []
+        self.kinds = []   # source element type for the staging gather: 0 f32, 1 f64, 2 i32, 3 i64
+        for a in arrays:
+            a = np.asarray(a)
+            assert a.shape[0] == self.n, "all arrays share the sample axis"
+            if a.dtype not in (np.float32, np.float64, np.int32, np.int64):
+                a = a.astype(np.int64 if np.issubdtype(a.dtype, np.integer) else np.float32)
+            self.host.append(np.ascontiguousarray(a))
+            self.kinds.append({np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.int32): 2,
+                               np.dtype(np.int64): 3}[self.host[-1].dtype])
+        self.dtypes = [np.int32 if k >= 2 else np.float32 for k in self.kinds]
+        self.row_shapes = [tuple(a.shape[1:]) for a in self.host]
+        self.row_elems = [int(np.prod(s)) if s else 1 for s in self.row_shapes]
+        B = self.batch_size
+        # [set][array]
+        self.staging = [[ctx.pinned((B,) + s, dt) for s, dt in zip(self.row_shapes, self.dtypes)] for _ in range(2)]
+        self.device = [[ctx.empty(*((B,) + s), dtype=dt) for s, dt in zip(self.row_shapes, self.dtypes)] for _ in range(2)]
+        self.h2d_bytes = 0          # bytes copied host->device since construction
+        self._used = [False, False]  # set b has been consumed by a step at least once
+
+    def __len__(self):
+        full, rem = divmod(self.n, self.batch_size)
+        return full + (1 if rem and not self.drop_last else 0)
+
+    # -- one upload ---------------------------------------------------------------------------------------------
+    def _stage_and_upload(self, b: int, idx: np.ndarray):
+        c, L = self.ctx, self.ctx.lib
+        rows = len(idx)
+        contiguous = rows > 0 and int(idx[-1]) - int(idx[0]) == rows - 1 and (rows == 1 or bool(np.all(np.diff(idx) == 1)))
+        index = None if contiguous else np.ascontiguousarray(idx, dtype=np.int64)
+        for a, st, kind, per_row in zip(self.host, self.staging[b], self.kinds, self.row_elems):
+            # gather + narrowing straight into page-locked memory, on the library's host threads
+            c.check(L.fml_stage_rows(c.h, st.ctypes.data, a.ctypes.data, kind, per_row,
+                                     None if index is None else index.ctypes.data, int(idx[0]) if rows else 0, rows, 0))
+        if self._used[b]:
+            c.check(L.fml_wait_event(c.h, _LANE, _EV_CONSUMED + b))   # kernels that read device set b are done
+        for st, dev, per_row in zip(self.staging[b], self.device[b], self.row_elems):
+            n = rows * per_row
+            # one call per array; 4-byte elements either way, so the float entry point moves int32 ids as well
+            c.check(L.fml_lane_h2d(c.h, _LANE, dev.ptr, st.ctypes.data, n))
+            self.h2d_bytes += 4 * n
+        c.check(L.fml_event_record_on(c.h, _EV_UPLOADED + b, _LANE))
+
+    def batches(self, order: Optional[np.ndarray] = None) -> Iterator[Tuple[DeviceArray, ...]]:
+        c, L = self.ctx, self.ctx.lib
+        order = np.arange(self.n) if order is None else np.asarray(order)
+        B = self.batch_size
+        cuts = [(s, min(s + B, len(order))) for s in range(0, len(order), B)]
+        if self.drop_last and cuts and cuts[-1][1] - cuts[-1][0] < B:
+            cuts.pop()
+        if not cuts:
+            return
+        # the staging buffers may still be the source of a copy issued by an earlier epoch
+        c.check(L.fml_lane_sync(c.h, _LANE))
+        self._stage_and_upload(0, order[cuts[0][0]:cuts[0][1]])
+        for s, (lo, hi) in enumerate(cuts):
+            b = s % 2
+            if s + 1 < len(cuts):
+                nb = (s + 1) % 2
+                # staging[nb] was the source of the upload of batch s-1: that copy was enqueued a whole step ago
+                self._wait_staging_free(nb, s)
+                self._stage_and_upload(nb, order[cuts[s + 1][0]:cuts[s + 1][1]])
+            c.check(L.fml_wait_event(c.h, -1, _EV_UPLOADED + b))
+            rows = hi - lo
+            yield tuple(dev if rows == B else dev.view(0, (rows,) + shp)
+                        for dev, shp in zip(self.device[b], self.row_shapes))
+            # everything the consumer enqueued on the main stream for this batch precedes this record
+            c.check(L.fml_event_record_on(c.h, _EV_CONSUMED + b, -1))
+            self._used[b] = True
+
+    def _wait_staging_free(self, b: int, s: int):
+        """The host may rewrite staging[b] once the copy that read it (the upload of batch s-1) has finished.  Only
+        that copy is waited for: the upload of batch s, enqueued after it, keeps running while the host stages
+        batch s+1."""
+        if s >= 1:
+            self.ctx.check(self.ctx.lib.fml_event_sync(self.ctx.h, _EV_UPLOADED + b))

@@ -96,6 +96,13 @@ int32_t fml_copy(fml_ctx* ctx, float* dst, const float* src, int64_t n);
  * calloc buffers, lib/cuda/cudacaller.dart:32-34). */
 int32_t fml_host_alloc(fml_ctx* ctx, int64_t bytes, void** out);
 int32_t fml_host_free(fml_ctx* ctx, void* p);
+/* Gather `rows` rows of `row_elems` elements from a host array into a staging buffer (normally page-locked, from
+ * fml_host_alloc) on several host threads, narrowing on the way: src_kind 0 float32, 1 float64 (Dart's doubles,
+ * lib/cuda/cudacaller.dart:38-43 narrows them one element at a time on one thread) -> float32; 2 int32, 3 int64 ->
+ * int32.  Row r comes from source row index[r], or first_row + r when index is NULL.  threads <= 0 picks a count from
+ * the size (at least 1 MiB per thread, at most 16).  Synchronous: dst is complete on return. */
+int32_t fml_stage_rows(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
+                       const int64_t* index, int64_t first_row, int64_t rows, int32_t threads);
 
 /* Copy lanes: two extra streams (lane 0 and 1) for host<->device copies that overlap the kernels
  * on the context's stream (the reference copies synchronously before and after every product,
@@ -106,6 +113,9 @@ int32_t fml_lane_d2h(fml_ctx* ctx, int32_t lane, float* host, const float* src, 
 int32_t fml_lane_sync(fml_ctx* ctx, int32_t lane);
 int32_t fml_event_record_on(fml_ctx* ctx, int32_t slot, int32_t lane);
 int32_t fml_wait_event(fml_ctx* ctx, int32_t lane, int32_t slot);
+/* The HOST waits until the event last recorded in `slot` has happened (e.g. before it rewrites a staging buffer
+ * that a copy on a lane was reading), without draining anything enqueued after it. */
+int32_t fml_event_sync(fml_ctx* ctx, int32_t slot);
 
 /* ---- CUDA graphs --------------------------------------------------------------
  * Launch-bound sequences (the 64-row MLP step of lib/nets/snet.dart:74-85 is ~15 small kernels) can be

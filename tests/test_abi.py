@@ -70,3 +70,27 @@ def test_tape_kind_knows_the_reference_op_names():
     assert lib.fml_tape_kind(b"max_pool_2d") == 0 and lib.fml_tape_kind(None) == 0
     from flutter_ml_b200 import tape
     assert tape.KIND["matMul"] == kinds["matMul"] and tape.KIND["layer_norm"] == kinds["layer_norm"]
+
+
+def test_stage_rows_gathers_and_narrows_on_host_threads():
+    """fml_stage_rows is host-only work (no context state, no device): rows picked by index or by range, float64 and
+    int64 sources narrowed to 4-byte elements, any thread count gives the same bytes."""
+    import ctypes as C
+    import numpy as np
+    from flutter_ml_b200 import _lib
+    L = _lib.load()
+    rng = np.random.default_rng(0)
+    n, row = 5000, 257
+    for kind, src in ((0, rng.standard_normal((n, row)).astype(np.float32)), (1, rng.standard_normal((n, row))),
+                      (2, rng.integers(-9, 9, (n, row)).astype(np.int32)), (3, rng.integers(-9, 9, (n, row)))):
+        out_dt = np.float32 if kind < 2 else np.int32
+        idx = rng.permutation(n)[:3000].astype(np.int64)
+        for threads in (1, 4, 0):
+            dst = np.zeros((3000, row), out_dt)
+            assert L.fml_stage_rows(None, dst.ctypes.data, src.ctypes.data, kind, row, idx.ctypes.data, 0, 3000, threads) == 0
+            assert np.array_equal(dst, src[idx].astype(out_dt))
+            dst = np.zeros((1234, row), out_dt)
+            assert L.fml_stage_rows(None, dst.ctypes.data, src.ctypes.data, kind, row, None, 77, 1234, threads) == 0
+            assert np.array_equal(dst, src[77:77 + 1234].astype(out_dt))
+    assert L.fml_stage_rows(None, None, None, 0, 1, None, 0, 1, 0) != 0      # rejected, not a crash
+    assert L.fml_stage_rows(None, dst.ctypes.data, src.ctypes.data, 9, row, None, 0, 1, 0) != 0

@@ -38,6 +38,26 @@ def test_gemm_matches_oracle(ctx, orc, M, N, K, tA, tB, prec, tol):
         a.free()
 
 
+@pytest.mark.parametrize("beta", [0.0, 1.0])
+@pytest.mark.parametrize("M,N,K,tA,tB,prec", [(64, 10, 16384, 1, 0, 0), (64, 10, 16384, 1, 0, 2), (100, 30, 5000, 0, 1, 2),
+                                             (10, 64, 4099, 0, 0, 2)])
+def test_cuda_core_gemm_with_k_slices(ctx, orc, M, N, K, tA, tB, prec, beta):
+    """A few output tiles under a long k on the CUDA-core path (a 10-wide head's weight gradient over a 16384-row
+    batch: leading dimension 10 keeps it off the tensor-core path): k is cut into slices that are summed with
+    atomics; beta 0 starts from a zeroed C, beta 1 adds to what is there."""
+    rng = np.random.default_rng(M + N + K)
+    A = (rng.standard_normal((K, M) if tA else (M, K)) / np.sqrt(K)).astype(np.float32)
+    B = (rng.standard_normal((N, K) if tB else (K, N)) / np.sqrt(K)).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    dA, dB, dC = ctx.upload(A), ctx.upload(B), ctx.upload(C0)
+    ctx.gemm(dA, dB, dC, M, N, K, transA=bool(tA), transB=bool(tB), precision=prec, alpha=0.5, beta=beta)
+    assert ctx.gemm_last_path() == 2
+    ref = 0.5 * orc.Ops(omp=True).matmul_fwd(w64(A.T if tA else A), w64(B.T if tB else B)) + beta * w64(C0)
+    assert rel(dC.numpy(), ref) <= TOL_FP32
+    for a in (dA, dB, dC):
+        a.free()
+
+
 def test_all_ones_1024_known_answer(ctx):
     # lib/gpu_benching.dart:34-37,60: all-ones 1024^3 => every element equals k (exact in TF32)
     n = 1024
