@@ -85,6 +85,8 @@ PROTOTYPES = {
     "fml_host_free": [fp, fp],
     "fml_event_sync": [fp, i32],
     "fml_stage_rows": [fp, fp, fp, i32, i64, fp, i64, i64, i32],
+    "fml_stage_rows_async": [fp, fp, fp, i32, i64, fp, i64, i64, i32],
+    "fml_stage_wait": [fp],
     "fml_event_record": [fp, i32],
     "fml_event_elapsed_ms": [fp, i32, i32, C.POINTER(f32)],
     "fml_lane_h2d": [fp, i32, fp, fp, i64],

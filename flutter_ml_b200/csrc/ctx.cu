@@ -380,42 +380,80 @@ void stage_rows_range(D* dst, const S* src, int64_t row_elems, const int64_t* in
 }  // namespace
 }  // extern "C++"
 
-int32_t fml_stage_rows(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
-                       const int64_t* index, int64_t first_row, int64_t rows, int32_t threads) {
-  FML_REQUIRE(ctx, dst && src && row_elems > 0 && rows >= 0, "fml_stage_rows: bad arguments");
-  FML_REQUIRE(ctx, src_kind >= 0 && src_kind <= 3, "fml_stage_rows: src_kind is 0 f32, 1 f64, 2 i32, 3 i64");
-  if (rows == 0) return FML_OK;
+extern "C++" {
+namespace {
+// Workers of a background gather (fml_stage_rows_async); joined by fml_stage_wait or by the next gather.
+std::mutex g_stage_mu;
+std::vector<std::thread> g_stage_pool;
+
+void stage_join_locked() {
+  for (auto& th : g_stage_pool)
+    if (th.joinable()) th.join();
+  g_stage_pool.clear();
+}
+
+void stage_run(void* dst, const void* src, int32_t src_kind, int64_t row_elems, const int64_t* index, int64_t first_row,
+               int64_t r0, int64_t r1) {
+  switch (src_kind) {
+    case 0: stage_rows_range((float*)dst, (const float*)src, row_elems, index, first_row, r0, r1); break;
+    case 1: stage_rows_range((float*)dst, (const double*)src, row_elems, index, first_row, r0, r1); break;
+    case 2: stage_rows_range((int32_t*)dst, (const int32_t*)src, row_elems, index, first_row, r0, r1); break;
+    default: stage_rows_range((int32_t*)dst, (const int64_t*)src, row_elems, index, first_row, r0, r1); break;
+  }
+}
+
+int stage_thread_count(int32_t threads, int64_t rows, int64_t row_elems) {
   const int64_t bytes = rows * row_elems * 4;
   int nt = threads > 0 ? threads : (int)std::min<int64_t>(std::max(1u, std::thread::hardware_concurrency()), 16);
-  nt = (int)std::max<int64_t>(1, std::min<int64_t>(nt, std::min<int64_t>(rows, bytes / (1 << 20) + 1)));  // >= 1 MiB per thread
-  auto run = [&](int64_t r0, int64_t r1) {
-    switch (src_kind) {
-      case 0: stage_rows_range((float*)dst, (const float*)src, row_elems, index, first_row, r0, r1); break;
-      case 1: stage_rows_range((float*)dst, (const double*)src, row_elems, index, first_row, r0, r1); break;
-      case 2: stage_rows_range((int32_t*)dst, (const int32_t*)src, row_elems, index, first_row, r0, r1); break;
-      default: stage_rows_range((int32_t*)dst, (const int64_t*)src, row_elems, index, first_row, r0, r1); break;
-    }
-  };
-  if (nt == 1) {
-    run(0, rows);
+  return (int)std::max<int64_t>(1, std::min<int64_t>(nt, std::min<int64_t>(rows, bytes / (1 << 20) + 1)));  // >= 1 MiB each
+}
+}  // namespace
+}  // extern "C++"
+
+static int32_t stage_rows_impl(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
+                               const int64_t* index, int64_t first_row, int64_t rows, int32_t threads, bool background) {
+  FML_REQUIRE(ctx, dst && src && row_elems > 0 && rows >= 0, "fml_stage_rows: bad arguments");
+  FML_REQUIRE(ctx, src_kind >= 0 && src_kind <= 3, "fml_stage_rows: src_kind is 0 f32, 1 f64, 2 i32, 3 i64");
+  std::lock_guard<std::mutex> lock(g_stage_mu);
+  // background gathers accumulate in g_stage_pool until fml_stage_wait joins them; a foreground one leaves them alone
+  if (rows == 0) return FML_OK;
+  const int nt = stage_thread_count(threads, rows, row_elems);
+  if (nt == 1) {   // under 1 MiB: the copy is cheaper than starting a thread, in either form
+    stage_run(dst, src, src_kind, row_elems, index, first_row, 0, rows);
     return FML_OK;
   }
-  std::vector<std::thread> pool;
-  pool.reserve(nt - 1);
   const int64_t per = (rows + nt - 1) / nt;
+  std::vector<std::thread> local;
+  std::vector<std::thread>& pool = background ? g_stage_pool : local;
+  int64_t done_to = background ? 0 : std::min(rows, per);   // the caller's own share in the foreground form
+  const int64_t first_spawned = done_to;
   try {
-    for (int t = 1; t < nt; t++) {
-      const int64_t r0 = std::min(rows, t * per), r1 = std::min(rows, r0 + per);
-      if (r0 < r1) pool.emplace_back(run, r0, r1);
+    for (int64_t r0 = first_spawned; r0 < rows; r0 += per) {
+      pool.emplace_back(stage_run, dst, src, src_kind, row_elems, index, first_row, r0, std::min(rows, r0 + per));
+      done_to = std::min(rows, r0 + per);
     }
-  } catch (...) {   // thread creation failed: finish what was started, do the rest here
-    for (auto& th : pool) th.join();
-    run(std::min(rows, (int64_t)(pool.size() + 1) * per), rows);
-    run(0, std::min(rows, per));
-    return FML_OK;
+  } catch (...) {   // thread creation failed: the rest is done here, on the calling thread
+    stage_run(dst, src, src_kind, row_elems, index, first_row, done_to, rows);
   }
-  run(0, std::min(rows, per));
-  for (auto& th : pool) th.join();
+  if (!background) {
+    stage_run(dst, src, src_kind, row_elems, index, first_row, 0, first_spawned);
+    for (auto& th : local) th.join();
+  }
+  return FML_OK;
+}
+
+int32_t fml_stage_rows(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
+                       const int64_t* index, int64_t first_row, int64_t rows, int32_t threads) {
+  return stage_rows_impl(ctx, dst, src, src_kind, row_elems, index, first_row, rows, threads, false);
+}
+int32_t fml_stage_rows_async(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
+                             const int64_t* index, int64_t first_row, int64_t rows, int32_t threads) {
+  return stage_rows_impl(ctx, dst, src, src_kind, row_elems, index, first_row, rows, threads, true);
+}
+int32_t fml_stage_wait(fml_ctx* ctx) {
+  (void)ctx;
+  std::lock_guard<std::mutex> lock(g_stage_mu);
+  stage_join_locked();
   return FML_OK;
 }
 

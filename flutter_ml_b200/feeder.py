@@ -6,11 +6,12 @@ memory (numpy), and a feeder moves one batch at a time:
 
   host rows --threaded gather (fml_stage_rows)--> page-locked staging[b] --copy lane 0, async--> device batch[b]      (b = step % 2)
 
-Two staging buffers and two device buffers per stream of data, so the host memcpy and the host->device copy of
-batch s+1 run while the kernels of batch s execute on the context's stream.  Ordering is carried by the
+Two staging buffers and two device buffers per stream of data: while the kernels of batch s execute on the
+context's stream, batch s+1 is copied host->device on the lane and batch s+2 is gathered into staging memory by
+background host threads (fml_stage_rows_async), so the calling thread only enqueues.  Ordering is carried by the
 library's numbered events: the copy lane waits for "kernels of the step that last used set b are done" before it
 overwrites device set b, the main stream waits for "upload of set b is done" before the step's first kernel.
-The host refills a staging buffer only after the lane has drained the copy that read it.
+A staging buffer is refilled only after the copy that read it has finished (fml_event_sync on that upload's event).
 """
 from __future__ import annotations
 
@@ -59,21 +60,28 @@ class BatchFeeder:
         self.device = [[ctx.empty(*((B,) + s), dtype=dt) for s, dt in zip(self.row_shapes, self.dtypes)] for _ in range(2)]
         self.h2d_bytes = 0          # bytes copied host->device since construction
         self._used = [False, False]  # set b has been consumed by a step at least once
+        self._index_alive = [None, None]
 
     def __len__(self):
         full, rem = divmod(self.n, self.batch_size)
         return full + (1 if rem and not self.drop_last else 0)
 
-    # -- one upload ---------------------------------------------------------------------------------------------
-    def _stage_and_upload(self, b: int, idx: np.ndarray):
+    # -- staging and upload ---------------------------------------------------------------------------------------
+    def _stage(self, b: int, idx: np.ndarray, background: bool):
+        """Gather + narrow the rows `idx` into staging set b on the library's host threads; with `background` the call
+        returns at once and fml_stage_wait completes it."""
         c, L = self.ctx, self.ctx.lib
         rows = len(idx)
         contiguous = rows > 0 and int(idx[-1]) - int(idx[0]) == rows - 1 and (rows == 1 or bool(np.all(np.diff(idx) == 1)))
         index = None if contiguous else np.ascontiguousarray(idx, dtype=np.int64)
+        self._index_alive[b] = index      # read by the background threads until fml_stage_wait
+        fn = L.fml_stage_rows_async if background else L.fml_stage_rows
         for a, st, kind, per_row in zip(self.host, self.staging[b], self.kinds, self.row_elems):
-            # gather + narrowing straight into page-locked memory, on the library's host threads
-            c.check(L.fml_stage_rows(c.h, st.ctypes.data, a.ctypes.data, kind, per_row,
-                                     None if index is None else index.ctypes.data, int(idx[0]) if rows else 0, rows, 0))
+            c.check(fn(c.h, st.ctypes.data, a.ctypes.data, kind, per_row,
+                       None if index is None else index.ctypes.data, int(idx[0]) if rows else 0, rows, 0))
+
+    def _upload(self, b: int, rows: int):
+        c, L = self.ctx, self.ctx.lib
         if self._used[b]:
             c.check(L.fml_wait_event(c.h, _LANE, _EV_CONSUMED + b))   # kernels that read device set b are done
         for st, dev, per_row in zip(self.staging[b], self.device[b], self.row_elems):
@@ -84,6 +92,8 @@ class BatchFeeder:
         c.check(L.fml_event_record_on(c.h, _EV_UPLOADED + b, _LANE))
 
     def batches(self, order: Optional[np.ndarray] = None) -> Iterator[Tuple[DeviceArray, ...]]:
+        """Three stages run concurrently once the pipeline is full: the kernels of batch s (context's stream), the
+        upload of batch s+1 (copy lane) and the gather of batch s+2 into staging memory (host threads)."""
         c, L = self.ctx, self.ctx.lib
         order = np.arange(self.n) if order is None else np.asarray(order)
         B = self.batch_size
@@ -92,27 +102,30 @@ class BatchFeeder:
             cuts.pop()
         if not cuts:
             return
+        rows_of = lambda s: order[cuts[s][0]:cuts[s][1]]
         # the staging buffers may still be the source of a copy issued by an earlier epoch
         c.check(L.fml_lane_sync(c.h, _LANE))
-        self._stage_and_upload(0, order[cuts[0][0]:cuts[0][1]])
-        for s, (lo, hi) in enumerate(cuts):
-            b = s % 2
-            if s + 1 < len(cuts):
-                nb = (s + 1) % 2
-                # staging[nb] was the source of the upload of batch s-1: that copy was enqueued a whole step ago
-                self._wait_staging_free(nb, s)
-                self._stage_and_upload(nb, order[cuts[s + 1][0]:cuts[s + 1][1]])
-            c.check(L.fml_wait_event(c.h, -1, _EV_UPLOADED + b))
-            rows = hi - lo
-            yield tuple(dev if rows == B else dev.view(0, (rows,) + shp)
-                        for dev, shp in zip(self.device[b], self.row_shapes))
-            # everything the consumer enqueued on the main stream for this batch precedes this record
-            c.check(L.fml_event_record_on(c.h, _EV_CONSUMED + b, -1))
-            self._used[b] = True
-
-    def _wait_staging_free(self, b: int, s: int):
-        """The host may rewrite staging[b] once the copy that read it (the upload of batch s-1) has finished.  Only
-        that copy is waited for: the upload of batch s, enqueued after it, keeps running while the host stages
-        batch s+1."""
-        if s >= 1:
-            self.ctx.check(self.ctx.lib.fml_event_sync(self.ctx.h, _EV_UPLOADED + b))
+        try:
+            self._stage(0, rows_of(0), background=False)
+            self._upload(0, len(rows_of(0)))
+            if len(cuts) > 1:
+                self._stage(1, rows_of(1), background=True)
+            for s, (lo, hi) in enumerate(cuts):
+                b = s % 2
+                if s + 1 < len(cuts):
+                    c.check(L.fml_stage_wait(c.h))                     # batch s+1 is in staging set 1-b
+                    self._upload(1 - b, cuts[s + 1][1] - cuts[s + 1][0])
+                    if s + 2 < len(cuts):
+                        # staging set b is the source of the upload of batch s, enqueued one step ago: wait for that
+                        # copy alone (the upload of s+1 keeps running), then gather batch s+2 behind the host's back
+                        c.check(L.fml_event_sync(c.h, _EV_UPLOADED + b))
+                        self._stage(b, rows_of(s + 2), background=True)
+                c.check(L.fml_wait_event(c.h, -1, _EV_UPLOADED + b))
+                rows = hi - lo
+                yield tuple(dev if rows == B else dev.view(0, (rows,) + shp)
+                            for dev, shp in zip(self.device[b], self.row_shapes))
+                # everything the consumer enqueued on the main stream for this batch precedes this record
+                c.check(L.fml_event_record_on(c.h, _EV_CONSUMED + b, -1))
+                self._used[b] = True
+        finally:
+            L.fml_stage_wait(c.h)      # also when the consumer stops early: no thread may outlive the arrays it reads

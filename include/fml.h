@@ -103,6 +103,12 @@ int32_t fml_host_free(fml_ctx* ctx, void* p);
  * the size (at least 1 MiB per thread, at most 16).  Synchronous: dst is complete on return. */
 int32_t fml_stage_rows(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
                        const int64_t* index, int64_t first_row, int64_t rows, int32_t threads);
+/* The same gather on background threads only: returns at once, so the caller can go on enqueueing the current
+ * step's kernels while the next batch is staged.  dst, src and index must stay valid, and dst unread, until
+ * fml_stage_wait has returned; several background gathers may be outstanding, fml_stage_wait joins them all. */
+int32_t fml_stage_rows_async(fml_ctx* ctx, void* dst, const void* src, int32_t src_kind, int64_t row_elems,
+                             const int64_t* index, int64_t first_row, int64_t rows, int32_t threads);
+int32_t fml_stage_wait(fml_ctx* ctx);
 
 /* Copy lanes: two extra streams (lane 0 and 1) for host<->device copies that overlap the kernels
  * on the context's stream (the reference copies synchronously before and after every product,

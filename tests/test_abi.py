@@ -92,5 +92,14 @@ def test_stage_rows_gathers_and_narrows_on_host_threads():
             dst = np.zeros((1234, row), out_dt)
             assert L.fml_stage_rows(None, dst.ctypes.data, src.ctypes.data, kind, row, None, 77, 1234, threads) == 0
             assert np.array_equal(dst, src[77:77 + 1234].astype(out_dt))
+    # background form: two gathers outstanding at once, complete after fml_stage_wait
+    a64, i64_ = rng.standard_normal((n, row)), rng.integers(0, 99, (n,))
+    idx = rng.permutation(n).astype(np.int64)
+    d1, d2 = np.zeros((n, row), np.float32), np.zeros((n,), np.int32)
+    assert L.fml_stage_rows_async(None, d1.ctypes.data, a64.ctypes.data, 1, row, idx.ctypes.data, 0, n, 3) == 0
+    assert L.fml_stage_rows_async(None, d2.ctypes.data, i64_.ctypes.data, 3, 1, idx.ctypes.data, 0, n, 3) == 0
+    assert L.fml_stage_wait(None) == 0
+    assert np.array_equal(d1, a64[idx].astype(np.float32)) and np.array_equal(d2, i64_[idx].astype(np.int32))
+    assert L.fml_stage_wait(None) == 0                                         # nothing outstanding: returns at once
     assert L.fml_stage_rows(None, None, None, 0, 1, None, 0, 1, 0) != 0      # rejected, not a crash
     assert L.fml_stage_rows(None, dst.ctypes.data, src.ctypes.data, 9, row, None, 0, 1, 0) != 0
