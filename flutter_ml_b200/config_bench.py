@@ -73,6 +73,22 @@ def _config1_fed(ctx, mlp):
     fed_ms, blk_ms = _feed_arms(ctx, mlp, X, y, 64)
     out = {"fed_us_per_step": round(fed_ms * 1e3, 1), "fed_samples_per_s": round(64 / fed_ms * 1e3, 1),
            "blocking_upload_us_per_step": round(blk_ms * 1e3, 1), "fed_h2d_bytes_per_step": 64 * 785 * 4}
+    # fed + graph replay: one recorded step per device batch buffer of the feeder, replayed alternately, so a step
+    # from host memory costs two library calls (events) and one graph launch
+    from .feeder import BatchFeeder
+    feeder = BatchFeeder(ctx, [X, y], 64)
+    for b in range(2):                   # recording runs the step once eagerly: give it defined inputs
+        ctx.zero(feeder.device[b][0])
+        ctx.zero(feeder.device[b][1])
+    graphs = [mlp.record_step(feeder.device[b][0], feeder.device[b][1]) for b in range(2)]
+    launches = mlp._graph_launches
+    for _ in range(2):                   # first pass warms up, second is timed
+        ctx.sync()
+        ctx.timer_start()
+        for s, _batch in enumerate(feeder.batches()):
+            ctx.graph_launch(graphs[s % 2], launches=launches)
+        fg_ms = ctx.timer_stop_ms() / len(feeder)
+    out.update({"fed_graph_us_per_step": round(fg_ms * 1e3, 1), "fed_graph_samples_per_s": round(64 / fg_ms * 1e3, 1)})
     B = 16384
     X = synth.uniform(0, 500, (12 * B, 784))
     y = synth.integers(0, 501, (12 * B,), 10)

@@ -125,3 +125,36 @@ def test_fit_batched_with_labels_and_shuffle_follows_the_oracle(orc):
     assert np.allclose(hist, want_hist, rtol=1e-4)
     assert ctx.device_status() == 0
     ctx.close()
+
+
+def test_fed_graph_replay_equals_fed_eager_steps():
+    """One recorded step per device batch buffer of the feeder, replayed alternately while the feeder refills the
+    other buffer: same parameters as the eager step over the same batches."""
+    from flutter_ml_b200 import _lib, models, synth
+    from flutter_ml_b200.feeder import BatchFeeder
+    ctx = _lib.Context()
+    n, B = 64 * 9, 64
+    X = np.concatenate([synth.uniform(0, 100 + i, (64, 784)) for i in range(9)])
+    y = np.concatenate([synth.integers(0, 300 + i, (64,), 10) for i in range(9)])
+    finals = []
+    for use_graph in (False, True):
+        mlp = models.MLP(ctx, models.init_mlp(0), lr=0.01)
+        feeder = BatchFeeder(ctx, [X, y], B)
+        for b in range(2):
+            ctx.zero(feeder.device[b][0])
+            ctx.zero(feeder.device[b][1])
+        if use_graph:
+            graphs = [mlp.record_step(feeder.device[b][0], feeder.device[b][1]) for b in range(2)]
+        else:
+            for b in range(2):              # the eager step that recording runs first
+                mlp.train_step(feeder.device[b][0], feeder.device[b][1])
+        for s, (xb, yb) in enumerate(feeder.batches()):
+            if use_graph:
+                ctx.graph_launch(graphs[s % 2])
+            else:
+                mlp.train_step(xb, yb)
+        finals.append(mlp.arena.values.numpy())
+    assert np.isfinite(finals[0]).all()
+    assert rel(finals[1], finals[0]) <= 1e-6
+    assert ctx.device_status() == 0
+    ctx.close()
