@@ -37,8 +37,13 @@ class BatchFeeder:
     The device arrays handed out by one iteration are overwritten two iterations later, so a consumer must not
     keep them across steps (the training loop does not: the tape of a step is dropped by backward())."""
 
-    def __init__(self, ctx: Context, arrays: Sequence[np.ndarray], batch_size: int, drop_last: bool = False):
+    def __init__(self, ctx: Context, arrays: Sequence[np.ndarray], batch_size: int, drop_last: bool = False,
+                 event_slots: int = _EV_UPLOADED):
+        """`event_slots`: first of four consecutive slots of the context's event pool this feeder owns; two feeders
+        that are iterated at the same time on one context (training and validation, say) need different ones."""
         assert len(arrays) > 0 and batch_size > 0
+        assert 0 <= event_slots <= 60
+        self._ev_uploaded, self._ev_consumed = event_slots, event_slots + 2
         self.ctx, self.batch_size, self.drop_last = ctx, int(batch_size), drop_last
         self.n = int(arrays[0].shape[0])
         self.host = []
@@ -83,13 +88,13 @@ class BatchFeeder:
     def _upload(self, b: int, rows: int):
         c, L = self.ctx, self.ctx.lib
         if self._used[b]:
-            c.check(L.fml_wait_event(c.h, _LANE, _EV_CONSUMED + b))   # kernels that read device set b are done
+            c.check(L.fml_wait_event(c.h, _LANE, self._ev_consumed + b))   # kernels that read device set b are done
         for st, dev, per_row in zip(self.staging[b], self.device[b], self.row_elems):
             n = rows * per_row
             # one call per array; 4-byte elements either way, so the float entry point moves int32 ids as well
             c.check(L.fml_lane_h2d(c.h, _LANE, dev.ptr, st.ctypes.data, n))
             self.h2d_bytes += 4 * n
-        c.check(L.fml_event_record_on(c.h, _EV_UPLOADED + b, _LANE))
+        c.check(L.fml_event_record_on(c.h, self._ev_uploaded + b, _LANE))
 
     def batches(self, order: Optional[np.ndarray] = None) -> Iterator[Tuple[DeviceArray, ...]]:
         """Three stages run concurrently once the pipeline is full: the kernels of batch s (context's stream), the
@@ -118,14 +123,14 @@ class BatchFeeder:
                     if s + 2 < len(cuts):
                         # staging set b is the source of the upload of batch s, enqueued one step ago: wait for that
                         # copy alone (the upload of s+1 keeps running), then gather batch s+2 behind the host's back
-                        c.check(L.fml_event_sync(c.h, _EV_UPLOADED + b))
+                        c.check(L.fml_event_sync(c.h, self._ev_uploaded + b))
                         self._stage(b, rows_of(s + 2), background=True)
-                c.check(L.fml_wait_event(c.h, -1, _EV_UPLOADED + b))
+                c.check(L.fml_wait_event(c.h, -1, self._ev_uploaded + b))
                 rows = hi - lo
                 yield tuple(dev if rows == B else dev.view(0, (rows,) + shp)
                             for dev, shp in zip(self.device[b], self.row_shapes))
                 # everything the consumer enqueued on the main stream for this batch precedes this record
-                c.check(L.fml_event_record_on(c.h, _EV_CONSUMED + b, -1))
+                c.check(L.fml_event_record_on(c.h, self._ev_consumed + b, -1))
                 self._used[b] = True
         finally:
             L.fml_stage_wait(c.h)      # also when the consumer stops early: no thread may outlive the arrays it reads

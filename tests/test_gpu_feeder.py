@@ -43,6 +43,13 @@ def test_feeder_delivers_every_row_in_order_including_a_short_last_batch():
         assert seen == n
     assert f.h2d_bytes == 2 * n * (7 + 1) * 4
     assert len(list(BatchFeeder(ctx, [X, y], B, drop_last=True).batches())) == 10
+    # two feeders walked in lock step on one context (training and validation): separate event slots
+    g = BatchFeeder(ctx, [X[::-1].copy(), y[::-1].copy()], B, event_slots=52)
+    for s, ((xa, ya), (xb, yb)) in enumerate(zip(f.batches(), g.batches())):
+        rows = min(B, n - s * B)
+        assert np.array_equal(xa.numpy(), X[s * B:s * B + rows].astype(np.float32))
+        assert np.array_equal(xb.numpy(), X[::-1][s * B:s * B + rows].astype(np.float32))
+        assert np.array_equal(yb.numpy(), y[::-1][s * B:s * B + rows].astype(np.int32))
     assert ctx.device_status() == 0
     ctx.close()
 
