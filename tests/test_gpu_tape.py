@@ -261,7 +261,9 @@ def test_tape_training_step_with_flat_parameter_arena(orc):
 
 def test_multi_tier_lstm_variant_as_a_tape(orc, fp32_ctx):
     """MultiTierLSTMLayer.forward (lib/layertypes/multilstm.dart:100-150): tier 0 sees [h_0, c_1, x_t] every
-    step, tier 1 sees [h_1, h_0] every second step.  The variant needs no kernel of its own: it is a list of the
+    step, tier 1 sees [h_1, h_0] every second step.  With two tiers this is also DualLSTMLayer.forward
+    (lib/layertypes/duallstm.dart:98-184: lower tier on [lh, hc, x_t], higher tier on [hh, lh] every
+    `lowerTierClockCycle` steps, output = final lh).  The variant needs no kernel of its own: it is a list of the
     same vector-form nodes, so it runs on the tape executor as it stands."""
     from flutter_ml_b200.tape import Tape
     I, H, Tn, cycle = 3, 10, 4, 2
@@ -288,6 +290,70 @@ def test_multi_tier_lstm_variant_as_a_tape(orc, fp32_ctx):
             if (g + 1) % cycle == 0:
                 h[1], c[1] = step(E.concatenate(h[1], h[0]), c[1], 1)
         return vec.mse(h[0], mk(target)), h[0], [w for tier in W for w in tier] + [v for tier in b for v in tier]
+
+    E = orc.Engine()
+
+    class OV:
+        add, sigmoid, tanh = staticmethod(E.addMatrix), staticmethod(E.sigmoidMatrix), staticmethod(E.tanhMatrix)
+        mse = staticmethod(E.mseMatrix)
+    oloss, oh, oparams = run(E, lambda a: orc.T(w64(a)), OV)
+    oloss.backward()
+    tp = Tape(fp32_ctx)
+
+    class TV:
+        add, sigmoid, tanh, mse = tp.addVector, tp.sigmoid, tp.vectorTanh, tp.mse
+    tloss, th, tparams = run(tp, tp.tensor, TV)
+    tp.forward()
+    tp.backward()
+    assert rel(th.numpy().ravel(), oh.value) <= 2e-6
+    assert abs(float(tloss.numpy()[0, 0]) - float(oloss.value)) <= 2e-6 * float(oloss.value)
+    for t, o in zip(tparams, oparams):
+        assert rel(t.grad_numpy().reshape(o.grad.shape), o.grad) <= 1e-5
+
+
+def test_chained_scale_lstm_variant_as_a_tape(orc, fp32_ctx):
+    """GeneralizedChainedScaleLayer.forward (lib/layertypes/trendmodelLayer.dart:134-204): each aggregation level
+    turns chunks of `grain` consecutive vectors into one summary tanh(W_agg . concat(chunk) + b_agg); then one LSTM
+    loop per tier, from the coarsest to the finest, each starting from the hidden state the coarser tier ended with
+    (cell state restarts at zero), the finest tier over the last `final_len` raw steps.  Again only vector-form
+    nodes: the executor runs it as it stands."""
+    from flutter_ml_b200.tape import Tape
+    I, H, steps, grains, final_len = 6, 6, 8, [2, 2], 3          # the context vector has the hidden size
+    tiers = len(grains) + 1
+    rng = np.random.default_rng(47)
+    f = lambda *s: (rng.standard_normal(s) * 0.4).astype(np.float32)
+    aggW, aggB = [f(I, g * I) for g in grains], [f(I) for _ in grains]
+    Ws = [[f(H, H + I) for _ in range(4)] for _ in range(tiers)]
+    bs = [[f(H) for _ in range(4)] for _ in range(tiers)]
+    xs, target = [f(I) for _ in range(steps)], f(H)
+
+    def run(E, mk, vec):
+        aW, aB = [mk(w) for w in aggW], [mk(v) for v in aggB]
+        W = [[mk(w) for w in tier] for tier in Ws]
+        b = [[mk(v) for v in tier] for tier in bs]
+        raw = [mk(x) for x in xs]
+        tier_inputs, level = [raw[len(raw) - final_len:]], raw
+        for i, g in enumerate(grains):
+            nxt = []
+            for j in range(0, len(level) - g + 1, g):
+                flat = level[j]
+                for v in level[j + 1:j + g]:
+                    flat = E.concatenate(flat, v)
+                nxt.append(vec.tanh(vec.add(E.matVecMul(aW[i], flat), aB[i])))
+            tier_inputs.append(nxt)
+            level = nxt
+        h = mk(np.zeros(H, np.float32))
+        for t in range(tiers - 1, -1, -1):
+            seq = tier_inputs[t][-(final_len if t == 0 else 10):]
+            c = mk(np.zeros(H, np.float32))
+            for x in seq:
+                z = E.concatenate(h, x)
+                gate = lambda k, fn: fn(vec.add(E.matVecMul(W[t][k], z), b[t][k]))
+                f_t, i_t, c_t = gate(0, vec.sigmoid), gate(1, vec.sigmoid), gate(2, vec.tanh)
+                c = vec.add(E.elementWiseMultiply(f_t, c), E.elementWiseMultiply(i_t, c_t))
+                h = E.elementWiseMultiply(gate(3, vec.sigmoid), vec.tanh(c))
+        params = aW + aB + [w for tier in W for w in tier] + [v for tier in b for v in tier]
+        return vec.mse(h, mk(target)), h, params
 
     E = orc.Engine()
 
