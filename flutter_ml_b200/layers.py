@@ -110,6 +110,72 @@ class Conv2DLayer(Layer):
         return T.conv2dBatch(x, self.kernels, self.biases, self.kernelSize, self.kernelSize, self.padding)
 
 
+class LSTMLayer(Layer):
+    """LSTMLayer (lib/layertypes/lstmLayer.dart:37-151): gates f, i, c~, o over the concatenated [h_{t-1}, x_t]
+    (:119), output = the last hidden state (:149).
+
+    Input: one sequence [T x I] (the reference's Tensor<Matrix>) or a time-major batch [T x B x I]; output
+    [B x H] (B = 1 for one sequence).  The four gate matrices [H x (H+I)] live in one [4H x (H+I)] buffer, the
+    four biases in one [4H] buffer, so that the whole recurrence runs in the library's fused LSTM kernels;
+    `parameters` hands out the eight tensors of the reference in its order (W_f, b_f, W_i, b_i, W_c, b_c, W_o,
+    b_o, :41) as views into those buffers.  Initial weights U(+-1/sqrt(H+I)) (:80) from the seeded generator
+    unless `weights` ([4H x (H+I)]) / `bias` ([4H]) are given."""
+    name = "lstm"
+
+    def __init__(self, hiddenSize: int, seed: int = 0, weights=None, bias=None):
+        super().__init__()
+        self.hiddenSize, self.seed, self._w0, self._b0 = hiddenSize, seed, weights, bias
+
+    @property
+    def parameters(self):
+        return self._params
+
+    def build(self, x: Tensor):
+        H, I = self.hiddenSize, x.shape[-1]
+        ctx = x.ctx
+        a = 1.0 / math.sqrt(H + I)
+        w = self._w0 if self._w0 is not None else synth.uniform(self.seed, 0, (4 * H, H + I), -a, a)
+        b = self._b0 if self._b0 is not None else np.zeros(4 * H, dtype=np.float32)
+        self.W, self.b = ctx.upload(np.asarray(w, np.float32)), ctx.upload(np.asarray(b, np.float32))
+        self.dW, self.db = ctx.zeros(4 * H, H + I), ctx.zeros(4 * H)
+        self._params = []
+        for g in range(4):
+            for buf, grad, off, shape in ((self.W, self.dW, g * H * (H + I), (H, H + I)), (self.b, self.db, g * H, (H,))):
+                t = Tensor(buf.view(off, shape), ctx)
+                t.grad = grad.view(off, shape)
+                self._params.append(t)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        import ctypes
+        from . import _lib
+        ctx, H = x.ctx, self.hiddenSize
+        Tn, B, I = (x.shape[0], 1, x.shape[1]) if len(x.shape) == 2 else x.shape
+        d = _lib.LstmDesc()
+        d.T, d.B, d.I, d.H = Tn, B, I, H
+        saved = dict(gates=ctx.empty(Tn, B, 4 * H), cells=ctx.empty(Tn + 1, B, H), hs=ctx.empty(Tn + 1, B, H),
+                     xproj=ctx.empty(Tn * B, 4 * H))
+        d.W, d.b, d.x = self.W.ptr, self.b.ptr, x.value.ptr
+        for k, v in saved.items():
+            setattr(d, k, v.ptr)
+        ctx.check(ctx.lib.fml_lstm_fwd(ctx.h, ctypes.byref(d)))
+        ctx.launches += 3
+        out = Tensor(saved["hs"].view(Tn * B * H, (B, H)), ctx)
+
+        def bw(_keep=saved):   # the descriptor points into the saved buffers: they live as long as this closure
+            scratch = ctx.empty(Tn * B * 4 * H + 2 * B * H)
+            dx = None
+            if x.creator is not None or x.grad is not None:    # someone upstream wants the input gradient
+                dx = ctx.empty(*x.shape)
+            ctx.check(ctx.lib.fml_lstm_bwd(ctx.h, ctypes.byref(d), out.grad.ptr, self.dW.ptr, self.db.ptr,
+                                           dx.ptr if dx is not None else None, scratch.ptr))
+            ctx.launches += 2 * Tn + 9
+            if dx is not None:
+                x._add_grad(dx, alias=True)
+        out.creator = T.Node([x] + self._params, bw, "lstm", cost=8 * Tn * B * H * (H + I))
+        return out
+
+
 class LayerNormalization(Layer):
     """lib/transformer/layerNormalization.dart:11-44: gamma = 1, beta = 0, epsilon = 1e-5."""
 

@@ -280,3 +280,62 @@ def test_conv2d_layer_batched(orc, padding):
     assert rel(layer.kernels.grad_numpy(), np.stack([t.grad.ravel() for t in ok])) <= 1e-5
     assert rel(layer.biases.grad_numpy(), np.array([float(t.grad) for t in ob])) <= 1e-5
     ctx.close()
+
+
+@pytest.mark.parametrize("B", [1, 6])
+def test_lstm_layer_mirror(orc, B):
+    """layers.LSTMLayer (lib/layertypes/lstmLayer.dart:37-151) on one sequence [T x I] and on a time-major batch:
+    last hidden state and the eight parameter gradients (handed out in the reference's order W_f, b_f, W_i, ...)
+    against the oracle's step-by-step recurrence and BPTT."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200 import tensor as T
+    from flutter_ml_b200.layers import LSTMLayer
+    from flutter_ml_b200.tensor import Tensor
+    ctx = _lib.Context(precision=_lib.PREC_3XTF32)
+    Tn, I, H = 9, 5, 16
+    rng = np.random.default_rng(23 + B)
+    a = 1 / np.sqrt(H + I)
+    W = rng.uniform(-a, a, (4, H, H + I)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (4, H)).astype(np.float32)
+    x = rng.standard_normal((B, Tn, I)).astype(np.float32)
+    target = rng.standard_normal((B, H)).astype(np.float32)
+    h_ref, loss_ref, dW_ref, db_ref = orc.Ops(omp=True).lstm_fwd_bwd(w64(W), w64(b), w64(x), w64(target))
+    layer = LSTMLayer(H, weights=W.reshape(4 * H, H + I), bias=b.reshape(4 * H))
+    xin = x[0] if B == 1 else np.ascontiguousarray(x.transpose(1, 0, 2))
+    out = layer(Tensor(xin, ctx))
+    assert out.shape == (B, H) and len(layer.parameters) == 8
+    loss = T.mseMatrix(out, Tensor(target, ctx))          # mean over B*H = (sum over sequences of mse) / B
+    loss.backward()
+    assert rel(out.numpy(), h_ref) <= 1e-5
+    assert abs(loss.numpy()[0] * B - loss_ref) <= 1e-5 * abs(loss_ref)
+    for g in range(4):
+        Wg, bg = layer.parameters[2 * g], layer.parameters[2 * g + 1]
+        assert np.array_equal(Wg.numpy(), W[g]) and np.array_equal(bg.numpy(), b[g])
+        assert rel(Wg.grad_numpy() * B, dW_ref[g]) <= 2e-5
+        assert rel(bg.grad_numpy() * B, db_ref[g]) <= 2e-5
+    assert ctx.device_status() == 0
+    ctx.close()
+
+
+def test_snetwork_with_lstm_layer_learns_a_sequence_task():
+    """SNetwork([LSTMLayer, DenseLayerMatrix]) trained per sample with fit(), the shape of the reference's
+    sequence demos (lib/layertypes/lstmLayer.dart:153-260): next value of a sine wave from the last 8."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200.layers import DenseLayerMatrix, LSTMLayer
+    from flutter_ml_b200.optimizers import Adam
+    from flutter_ml_b200.snet import SNetwork
+    from flutter_ml_b200.tensor import Tensor, set_default_context
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    set_default_context(ctx)
+    t = np.arange(0, 40) * 0.35
+    wave = np.sin(t).astype(np.float32)
+    xs = [Tensor(wave[i:i + 8].reshape(8, 1), ctx) for i in range(24)]
+    ys = [Tensor(wave[i + 8].reshape(1, 1), ctx) for i in range(24)]
+    net = SNetwork([LSTMLayer(12, seed=3), DenseLayerMatrix(1, None, seed=4)])
+    net.predict(xs[0])
+    assert len(net.parameters) == 10
+    net.compile(Adam(net.parameters, 0.02))
+    hist = net.fit(xs, ys, epochs=12)
+    assert hist[-1] < 0.25 * hist[0]
+    assert ctx.device_status() == 0
+    ctx.close()
