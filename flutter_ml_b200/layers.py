@@ -78,6 +78,34 @@ class DenseLayerMatrix(Layer):
         return T.denseMatrix(x, self.weights, self.biases, self.activation, self.precision)
 
 
+class DenseLayer(DenseLayerMatrix):
+    """The vector form act(W.x + b) with W stored [out x in] (lib/layertypes/denseLayer.dart:15-64: He-normal
+    weights :18-25, matVecMul + addVector :42).  The input vector is taken as a [1 x in] row (a flat [in] tensor is
+    reshaped), the product runs as x.W^T through the same fused dense node as the matrix form — the transpose is
+    a node of its own, so the gradient arrives in the [out x in] layout the reference's optimizer sees — and
+    the output is the [1 x out] row."""
+
+    name = "dense"
+
+    def build(self, x: Tensor):
+        fan_in = x.shape[-1]
+        w = self._w0 if self._w0 is not None else synth.normal(self.seed, 0, (self.outputSize, fan_in), math.sqrt(2.0 / fan_in))
+        b = self._b0 if self._b0 is not None else np.zeros(self.outputSize, dtype=np.float32)
+        self.weights, self.biases = Tensor(w, x.ctx), Tensor(b, x.ctx)
+        Layer.build(self, x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        if len(x.shape) == 1:
+            row = Tensor(x.value.reshape(1, x.shape[0]), x.ctx)
+            if x.creator is not None or x.grad is not None:
+                raise ValueError("DenseLayer: pass the input vector as a [1 x in] row when it needs a gradient")
+            x = row
+        wt = T.transpose(self.weights)
+        if self.activation in T.ACT2_BY_NAME:
+            return T.ACT2_BY_NAME[self.activation](T.denseMatrix(x, wt, self.biases, None, self.precision))
+        return T.denseMatrix(x, wt, self.biases, self.activation, self.precision)
+
+
 class Conv2DLayer(Layer):
     """lib/layertypes/conv2d.dart:11-75: `outChannels` square kernels over a single-channel input, one scalar bias
     each, padding 'valid' or 'same'.  The reference keeps a list of kernel matrices; here they are the rows of one

@@ -339,3 +339,37 @@ def test_snetwork_with_lstm_layer_learns_a_sequence_task():
     assert hist[-1] < 0.25 * hist[0]
     assert ctx.device_status() == 0
     ctx.close()
+
+
+@pytest.mark.parametrize("act", [None, "tanh", "relu"])
+def test_dense_layer_vector_form(orc, act):
+    """layers.DenseLayer (lib/layertypes/denseLayer.dart:15-64): act(W.x + b) with W [out x in], stacked twice so
+    the input gradient path through the first layer is exercised; against matVecMul + addVector on the oracle."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200 import tensor as T
+    from flutter_ml_b200.layers import DenseLayer
+    from flutter_ml_b200.tensor import Tensor
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    rng = np.random.default_rng(3)
+    n_in, n_mid, n_out = 12, 9, 4
+    W1, b1 = rng.standard_normal((n_mid, n_in)).astype(np.float32) * 0.4, rng.standard_normal(n_mid).astype(np.float32) * 0.1
+    W2, b2 = rng.standard_normal((n_out, n_mid)).astype(np.float32) * 0.4, rng.standard_normal(n_out).astype(np.float32) * 0.1
+    x, target = rng.standard_normal(n_in).astype(np.float32), rng.standard_normal(n_out).astype(np.float32)
+    l1, l2 = DenseLayer(n_mid, act, weights=W1, bias=b1), DenseLayer(n_out, None, weights=W2, bias=b2)
+    out = l2(l1(Tensor(x, ctx)))
+    assert out.shape == (1, n_out) and l1.weights.shape == (n_mid, n_in)
+    loss = T.mseMatrix(out, Tensor(target.reshape(1, -1), ctx))
+    loss.backward()
+    E = orc.Engine()
+    oW1, ob1, oW2, ob2 = (orc.T(w64(a)) for a in (W1, b1, W2, b2))
+    h = E.addMatrix(E.matVecMul(oW1, orc.T(w64(x))), ob1)
+    if act:
+        h = {"tanh": E.tanhMatrix, "relu": E.reluMatrix}[act](h)
+    o = E.addMatrix(E.matVecMul(oW2, h), ob2)
+    ol = E.mseMatrix(o, orc.T(w64(target)))
+    ol.backward()
+    assert rel(out.numpy().ravel(), o.value) <= 1e-5
+    for t, r in ((l1.weights, oW1), (l1.biases, ob1), (l2.weights, oW2), (l2.biases, ob2)):
+        assert rel(t.grad_numpy().reshape(r.grad.shape), r.grad) <= 1e-5
+    assert ctx.device_status() == 0
+    ctx.close()
