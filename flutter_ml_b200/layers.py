@@ -348,6 +348,41 @@ class TransformerEncoderBlock(Layer):
         return self.norm2(h, residual=f, alias_residual_grad=True)
 
 
+class PositionalEncoding(Layer):
+    """x + PE[0:S] (lib/transformer/positionalEncodingLayer.dart:15-66; the table keeps the reference's exponent
+    2i/dModel for every column i, :41).  No parameters.  Input [S x dModel] (one sequence, the reference's form) or
+    a batch flattened into rows [n_seq*S x dModel] with `seq_len=S`: the table rows repeat per sequence.  The
+    embedding layer can add the same table inside its gather (`EmbeddingLayer(positional_max_len=...)`); this class
+    is the stand-alone node."""
+
+    name = "positional_encoding"
+
+    def __init__(self, maxSequenceLength: int, dModel: int, seq_len: int = 0):
+        super().__init__()
+        self.maxSequenceLength, self.dModel, self.seq_len = maxSequenceLength, dModel, seq_len
+        self._tiled = {}
+
+    def build(self, x: Tensor):
+        self.pe = x.ctx.empty(self.maxSequenceLength, self.dModel)
+        x.ctx.call("fml_positional_table", self.pe, self.maxSequenceLength, self.dModel)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        rows, d = x.shape
+        S = self.seq_len or rows
+        if d != self.dModel or S > self.maxSequenceLength or rows % S:
+            raise ValueError("PositionalEncoding: input does not fit the table")
+        if rows not in self._tiled:      # the constant addend for this shape, built once on the device
+            if rows == S:
+                self._tiled[rows] = Tensor(self.pe.view(0, (S, d)), x.ctx)
+            else:
+                tiled = x.ctx.empty(rows, d)
+                for q in range(rows // S):
+                    x.ctx.copy(tiled.view(q * S * d, (S, d)), self.pe.view(0, (S, d)))
+                self._tiled[rows] = Tensor(tiled, x.ctx)
+        return T.addMatrix(x, self._tiled[rows])
+
+
 class EmbeddingLayer(Layer):
     """Row gather by token id (lib/transformer/embeddingLayer.dart:18-69), init uniform(+-0.01)
     (:38).  With `positional`, the reference's PositionalEncoding table

@@ -373,3 +373,29 @@ def test_dense_layer_vector_form(orc, act):
         assert rel(t.grad_numpy().reshape(r.grad.shape), r.grad) <= 1e-5
     assert ctx.device_status() == 0
     ctx.close()
+
+
+@pytest.mark.parametrize("n_seq", [1, 3])
+def test_positional_encoding_layer(orc, n_seq):
+    """layers.PositionalEncoding (lib/transformer/positionalEncodingLayer.dart:29-65): x + table rows, the gradient
+    passes through unchanged; table from the oracle's restatement (exponent 2i/dModel for every column)."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200 import tensor as T
+    from flutter_ml_b200.layers import PositionalEncoding
+    from flutter_ml_b200.tensor import Tensor
+    ctx = _lib.Context()
+    S, d, max_len = 7, 12, 16
+    rng = np.random.default_rng(n_seq)
+    x = rng.standard_normal((n_seq * S, d)).astype(np.float32)
+    target = rng.standard_normal((n_seq * S, d)).astype(np.float32)
+    layer = PositionalEncoding(max_len, d, seq_len=S if n_seq > 1 else 0)
+    xt = Tensor(x, ctx, requires_zero_grad=True)
+    out = layer(xt)
+    loss = T.mseMatrix(out, Tensor(target, ctx))
+    loss.backward()
+    pe = orc.Ops().positional_table(max_len, d)[:S]
+    want = w64(x) + np.tile(pe, (n_seq, 1))
+    assert layer.parameters == []
+    assert rel(out.numpy(), want) <= 1e-6
+    assert rel(xt.grad_numpy(), 2 * (want - w64(target)) / want.size) <= 1e-5
+    ctx.close()
