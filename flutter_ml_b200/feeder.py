@@ -21,8 +21,9 @@ import numpy as np
 
 from ._lib import Context, DeviceArray
 
-# event slots of the library's pool (0..63) owned by the feeder: +0 / +1 per buffer set
-_EV_UPLOADED, _EV_CONSUMED = 46, 48
+# first of the four event slots of the library's pool (0..63) a feeder owns by default: "uploaded" +0 / +1 per
+# buffer set, then "consumed" +2 / +3
+_EV_UPLOADED = 46
 _LANE = 0
 
 
