@@ -321,6 +321,7 @@ def main():
     ap.add_argument("--attention-only", action="store_true", help="run only the fused attention kernels (profiling)")
     ap.add_argument("--attention-seqs", type=int, default=32)
     ap.add_argument("--configs-only", action="store_true", help="run only configurations 1, 3, 4 (profiling)")
+    ap.add_argument("--config", type=int, default=0, choices=[0, 1, 3, 4], help="with --configs-only: just this one")
     ap.add_argument("--train-only", action="store_true", help="run only the data-parallel training step (profiling)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -365,7 +366,7 @@ def main():
         return
     if args.configs_only:
         from flutter_ml_b200 import config_bench
-        print(json.dumps({"configs": config_bench.run(ctx)}), flush=True)
+        print(json.dumps({"configs": config_bench.run(ctx, args.config)}), flush=True)
         ctx.close()
         return
     if args.attention_only:

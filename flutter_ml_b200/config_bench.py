@@ -172,5 +172,7 @@ def config4_lstm(ctx):
             "launches_per_step": launches}
 
 
-def run(ctx):
-    return [config1_mlp(ctx), config3_encoder_block(ctx), config4_lstm(ctx)]
+def run(ctx, only: int = 0):
+    """All three configurations, or just configuration `only` (1, 3 or 4; for profiling one of them)."""
+    fns = {1: config1_mlp, 3: config3_encoder_block, 4: config4_lstm}
+    return [fn(ctx) for k, fn in fns.items() if only in (0, k)]
