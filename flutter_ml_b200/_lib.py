@@ -102,6 +102,7 @@ PROTOTYPES = {
     "fml_timer_stop_ms": [fp, C.POINTER(f32)],
     "fml_gemm": [fp, C.POINTER(GemmDesc)],
     "fml_gemm_last_path": [fp, C.POINTER(i32)],
+    "fml_gemm_last_tile": [fp, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)],
     "multiplyMatrices": [fp, fp, fp, i32, i32, i32],
     "benchtest": [],
     "fml_act_fwd": [fp, i32, fp, fp, i64],
@@ -369,6 +370,12 @@ class Context:
         p = i32(0)
         self.check(self.lib.fml_gemm_last_path(self.h, C.byref(p)))
         return p.value
+
+    def gemm_last_tile(self):
+        """(CTAs per tile, tile columns, K splits, K chunks) of the last tensor-core product."""
+        v = [i32(0) for _ in range(4)]
+        self.check(self.lib.fml_gemm_last_tile(self.h, *[C.byref(x) for x in v]))
+        return tuple(x.value for x in v)
 
     def call(self, name, *args, launches=1):
         """Call any fml_* entry point that takes the context first; DeviceArrays become addresses."""

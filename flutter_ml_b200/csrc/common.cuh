@@ -31,6 +31,7 @@ struct fml_ctx {
   std::vector<cudaGraphExec_t> graphs;         // instantiated graphs, index = graph id
   bool capturing = false;
   int last_gemm_path = 0;
+  int last_gemm_tile[4] = {0, 0, 0, 0};  // of the last tensor-core launch: CTAs per tile (1 or 2), tile columns, K splits, K chunks
   // tensor-map cache: key -> encoded CUtensorMap
   std::map<std::tuple<const void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, int>, CUtensorMap> tmaps;
   // NCCL (loaded lazily with dlopen)

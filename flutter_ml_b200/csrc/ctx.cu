@@ -489,6 +489,15 @@ int32_t fml_gemm_last_path(fml_ctx* ctx, int32_t* path) {
   return FML_OK;
 }
 
+int32_t fml_gemm_last_tile(fml_ctx* ctx, int32_t* ctas_per_tile, int32_t* tile_cols, int32_t* k_splits, int32_t* k_chunks) {
+  FML_REQUIRE(ctx, ctx != nullptr, "fml_gemm_last_tile: ctx is NULL");
+  if (ctas_per_tile) *ctas_per_tile = ctx->last_gemm_tile[0];
+  if (tile_cols) *tile_cols = ctx->last_gemm_tile[1];
+  if (k_splits) *k_splits = ctx->last_gemm_tile[2];
+  if (k_chunks) *k_chunks = ctx->last_gemm_tile[3];
+  return FML_OK;
+}
+
 // ------------------------------------------------------------------- legacy symbols
 static fml_ctx* g_legacy = nullptr;
 static float *g_la = nullptr, *g_lb = nullptr, *g_lc = nullptr;

@@ -126,5 +126,6 @@ int32_t fml_gemm_simt(fml_ctx* ctx, const fml_gemm_desc* d) {
   gemm_simt_kernel<<<grid, 256, 0, ctx->stream>>>(p);
   FML_LAUNCH_CHECK(ctx, "gemm_simt_kernel");
   ctx->last_gemm_path = 2;
+  ctx->last_gemm_tile[0] = ctx->last_gemm_tile[1] = ctx->last_gemm_tile[2] = ctx->last_gemm_tile[3] = 0;
   return FML_OK;
 }

@@ -1038,5 +1038,9 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   }
   FML_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
   ctx->last_gemm_path = 1;
+  ctx->last_gemm_tile[0] = pair ? 2 : 1;
+  ctx->last_gemm_tile[1] = BN;
+  ctx->last_gemm_tile[2] = p.ksplit;
+  ctx->last_gemm_tile[3] = (p.kb_per_split + p.kchunk - 1) / p.kchunk;
   return FML_OK;
 }

@@ -30,6 +30,7 @@ _default_ctx: Optional[Context] = None
 FUSE_DACT_INTO_DX = False
 FUSE_SOFTMAX_BACKWARD = False
 FUSE_ATTENTION = True   # one kernel for softmax(scale Q.K^T).V (TF32 mode, d_head 64, seq_len % 128 == 0)
+fused_attention_calls = 0   # forward passes that took the fused kernels (lets a test prove which path it compared)
 
 
 def default_context() -> Context:
@@ -424,6 +425,8 @@ def _attentionFused(qkv: Tensor, q, k, v, Bn, S, H, dk, causal, scale):
     desc.scale, desc.causal = scale, int(bool(causal))
     ctx.check(ctx.lib.fml_attention_fwd(ctx.h, ctypes.byref(desc)))
     ctx.launches += 1
+    global fused_attention_calls
+    fused_attention_calls += 1
 
     def bw():
         g, acc = qkv._grad_target()

@@ -193,6 +193,11 @@ typedef struct {
 int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d);
 /* Which kernel the last fml_gemm used: 1 = tcgen05 tensor-core, 2 = CUDA-core. */
 int32_t fml_gemm_last_path(fml_ctx* ctx, int32_t* path);
+/* How the last tensor-core fml_gemm was tiled (all zero after a CUDA-core launch): ctas_per_tile = 1 (128-row tiles,
+ * one CTA each) or 2 (256 x 256 tiles over a pair of CTAs, cta_group::2), tile_cols = 64 / 128 / 256, k_splits =
+ * CTAs (or pairs) sharing one output tile along K, k_chunks = accumulation chunks per tile.  Any pointer may be
+ * NULL.  Lets a test prove which variant of the kernel produced the result it compares. */
+int32_t fml_gemm_last_tile(fml_ctx* ctx, int32_t* ctas_per_tile, int32_t* tile_cols, int32_t* k_splits, int32_t* k_chunks);
 
 /* ---- legacy symbols (cuda_lib/kernel.cu:6-11 and :57-58) --------------------
  * Host pointers, row-major, A m x k, B k x n, C m x n; same argument order as

@@ -229,6 +229,12 @@ class Engine:
 
     def __init__(self, omp: bool = False):
         self.ops = Ops(omp)
+        # Test aid, not reference behaviour: an iterator of boolean masks.  While it is set, every reluMatrix call
+        # takes its gate pattern from the next mask instead of from the sign of its own input.  ReLU's gate is
+        # discontinuous, so a device pre-activation that differs from the float64 one in the last TF32 bit can
+        # land on the other side of zero; handing the device's gate pattern to the checker separates that effect
+        # from the arithmetic of the kernels under test.
+        self.relu_gates = None
 
     # tensor.dart:867-947
     def matMul(self, a, b):
@@ -260,6 +266,13 @@ class Engine:
         return _node(out, [x], lambda: self.ops.unary_bwd(name, saved, out.grad, x.grad))
 
     def reluMatrix(self, x):      # tensor.dart:1013-1038
+        if self.relu_gates is not None:
+            gate = np.asarray(next(self.relu_gates), dtype=np.float64)
+            out = T(x.value * gate)
+
+            def bw():
+                x.grad += out.grad * gate
+            return _node(out, [x], bw)
         return self._unary("relu", x, False)
 
     def sigmoidMatrix(self, x):   # tensor.dart:1123-1151
@@ -471,11 +484,14 @@ def gemm_gelu_fwd_bwd(A, B, bias, dC, omp=False):
     return {"Z": z.value, "C": c.value, "dZ": z.grad, "dA": a.grad, "dB": b.grad, "dbias": bi.grad}
 
 
-def encoder_block_fwd_bwd(xs, params, targets, causal=True, omp=False):
+def encoder_block_fwd_bwd(xs, params, targets, causal=True, omp=False, relu_gates=None):
     """Config 3: one post-LN block over a batch of sequences.  Each sequence is one
     reference forward/backward (mseMatrix against its target); gradients accumulate
-    across sequences and the reported loss is the sum."""
+    across sequences and the reported loss is the sum.  `relu_gates` (one boolean mask
+    [seq x dff] per sequence) replaces the FFN's own gate pattern, see Engine.relu_gates."""
     E = Engine(omp)
+    if relu_gates is not None:
+        E.relu_gates = iter(relu_gates)
     pt = block_params_to_T(params)
     ys, loss, dxs = [], 0.0, []
     for x_np, t_np in zip(xs, targets):
