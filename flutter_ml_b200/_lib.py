@@ -71,7 +71,9 @@ PROTOTYPES = {
     "fml_sync": [fp],
     "fml_device_status": [fp, C.POINTER(i32)],
     "fml_selftest_wait_timeout": [fp, i32],
+    "fml_selftest_per_device_once": [i32, C.POINTER(i32)],
     "fml_alloc": [fp, i64, C.POINTER(fp)],
+    "fml_mem_info": [fp, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)],
     "fml_free": [fp, fp],
     "fml_zero": [fp, fp, i64],
     "fml_fill": [fp, fp, i64, f32],
@@ -121,11 +123,12 @@ PROTOTYPES = {
     "fml_softmax_xent_dbias": [fp, fp, fp, fp, fp, i64, i32, f32, fp],
     "fml_softmax_xent_static": [fp, fp, fp, fp, fp, i64, i32, f32],
     "fml_mse": [fp, fp, fp, fp, fp, i64, f32],
-    "fml_embedding_fwd": [fp, fp, fp, fp, fp, i64, i32, i32],
-    "fml_embedding_bwd": [fp, fp, fp, fp, i64, i32],
+    "fml_embedding_fwd": [fp, fp, fp, fp, fp, i64, i32, i32, i32],
+    "fml_embedding_bwd": [fp, fp, fp, fp, i64, i32, i32],
     "fml_positional_table": [fp, fp, i32, i32],
     "fml_sgd_step": [fp, fp, fp, i64, C.c_double, C.c_double],
     "fml_adam_step": [fp, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, i32, C.c_double],
+    "fml_adam_step_on": [fp, i32, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, i32, C.c_double, i32],
     "fml_optimizer_step": [fp, i32, fp, fp, fp, fp, fp, i64, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, i32],
     "fml_act2_fwd": [fp, i32, f32, fp, fp, i64],
     "fml_act2_bwd": [fp, i32, f32, fp, fp, fp, i64, i32],
@@ -141,6 +144,7 @@ PROTOTYPES = {
     "fml_lstm_bwd": [fp, C.POINTER(LstmDesc), fp, fp, fp, fp, fp],
     "fml_dp_unique_id": [C.c_char_p],
     "fml_dp_init": [fp, C.c_char_p, i32, i32],
+    "fml_dp_set_timeout": [fp, i32],
     "fml_dp_allreduce_sum": [fp, fp, i64],
     "fml_dp_allreduce_sum_on": [fp, i32, fp, i64],
     "fml_dp_shutdown": [fp],
@@ -241,6 +245,12 @@ class Context:
         p = fp()
         self.check(self.lib.fml_alloc(self.h, n, C.byref(p)))
         return DeviceArray(self, p.value, shape, dtype)
+
+    def mem_info(self):
+        """(free bytes on the device, total bytes, bytes of the context's scratch arena)."""
+        v = [i64(0) for _ in range(3)]
+        self.check(self.lib.fml_mem_info(self.h, *[C.byref(x) for x in v]))
+        return tuple(x.value for x in v)
 
     def zeros(self, *shape, dtype=np.float32):
         a = self.empty(*shape, dtype=dtype)

@@ -54,7 +54,11 @@ __device__ __forceinline__ float fa_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// round-to-nearest of a finite non-negative float to TF32 (10 mantissa bits) with two integer instructions
+// Round-to-nearest (ties away from zero) of a finite float to TF32 (10 mantissa bits) with two integer instructions;
+// the sign bit rides along.  The tensor core itself TRUNCATES fp32 operands to TF32 (measured: a product of operands
+// cut to 19 bits on the host reproduces the device result to 3e-7, and products of generic data come out 7.0e-4 low,
+// 3.5e-4 per operand).  Every operand this file builds on chip (P, dS and their transposes) is therefore rounded here
+// first, which removes that operand's share of the bias; Q, K, V, dO arrive by TMA and are used as they are.
 __device__ __forceinline__ float fa_round_tf32(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ uint32_t fa_idesc(int M, int N, int a_mn, int b_mn) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a_mn & 1) << 15) | ((uint32_t)(b_mn & 1) << 16) |
@@ -472,7 +476,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             for (int e = 0; e < 4; e++) {
               const int col = c * 32 + ch * 4 + e;
               const float pr = (col < lim) ? fa_exp2(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -L)) : 0.f;
-              de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dv) * p.scale;
+              de[e] = fa_round_tf32(pr * (__uint_as_float(dv[ch * 4 + e]) - Dv) * p.scale);
             }
             *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
           }
@@ -729,8 +733,8 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
               const bool vis = !p.causal || (q0 + col >= kj);
               const float Lc = Le[e], Dc = De[e];
               const float pr = vis ? fa_exp2(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -Lc)) : 0.f;
-              pe[e] = pr;
-              de[e] = pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale;
+              pe[e] = fa_round_tf32(pr);
+              de[e] = fa_round_tf32(pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale);
             }
             *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
             *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
@@ -799,6 +803,7 @@ __global__ void attention_rowdot_kernel(const float* __restrict__ dout, long lon
 extern "C" {
 
 int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, d && d->q && d->k && d->v && d->out, "fml_attention_fwd: NULL buffer");
   FML_REQUIRE(ctx, d->n_seq > 0 && d->heads > 0 && d->seq_len > 0, "fml_attention_fwd: bad sizes");
   FML_REQUIRE(ctx, d->d_head == DH, "fml_attention_fwd: d_head must be 64");
@@ -821,11 +826,7 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
   p.out = d->out; p.ld_out = d->ld_out;
   p.lse = d->lse;
   p.status = ctx->d_status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    FML_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
-    attr_set = true;
-  }
+  FML_ONCE_PER_DEVICE(ctx, { FML_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM)); });
   const long long items = (long long)Bn * H * p.n_qb;
   FML_REQUIRE(ctx, items <= 0x7fffffffLL, "fml_attention_fwd: too many work items");
   p.n_items = (int)items;
@@ -839,6 +840,7 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
 
 int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float* dout, int64_t ld_dout, float* dq, float* dk,
                           float* dv, int64_t ld_dqkv, int32_t accumulate, float* scratch) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, d && d->q && d->k && d->v && d->out && d->lse && dout && dq && dk && dv && scratch, "fml_attention_bwd: NULL buffer");
   FML_REQUIRE(ctx, d->n_seq > 0 && d->heads > 0 && d->seq_len > 0 && d->d_head == DH && d->seq_len % BQ == 0,
               "fml_attention_bwd: d_head must be 64 and seq_len a multiple of 128");
@@ -866,12 +868,10 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, BQ2, false, 0, &tmDO64))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmQmn))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, 32, true, 2, &tmDOmn))) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
+  FML_ONCE_PER_DEVICE(ctx, {
     FML_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
     FML_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA2_SMEM));
-    attr_set = true;
-  }
+  });
   const unsigned grid = (unsigned)((long long)Bn * H * (S / BQ));
   FaBwdParams p;
   p.S = S; p.H = H; p.n_qb = S / BQ; p.causal = d->causal ? 1 : 0;

@@ -71,6 +71,7 @@ extern "C" {
 
 int32_t fml_checkpoint_save(fml_ctx* ctx, const char* path, int64_t step, int32_t n, const char* const* names,
                             const float* const* bufs, const int64_t* sizes) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, path && n >= 0 && (n == 0 || (names && bufs && sizes)), "fml_checkpoint_save: bad arguments");
   for (int i = 0; i < n; i++)
     FML_REQUIRE(ctx, names[i] && bufs[i] && sizes[i] > 0 && std::strlen(names[i]) < 4096, "fml_checkpoint_save: bad entry");
@@ -130,6 +131,7 @@ int32_t fml_checkpoint_save(fml_ctx* ctx, const char* path, int64_t step, int32_
 
 int32_t fml_checkpoint_load(fml_ctx* ctx, const char* path, int64_t* step, int32_t n, const char* const* names,
                             float* const* bufs, const int64_t* sizes) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, path && n >= 0 && (n == 0 || (names && bufs && sizes)), "fml_checkpoint_load: bad arguments");
   crc_init();
   File in;

@@ -5,7 +5,9 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
 #include <map>
+#include <mutex>
 #include <string>
 #include <tuple>
 #include <unordered_set>
@@ -37,6 +39,7 @@ struct fml_ctx {
   // NCCL (loaded lazily with dlopen)
   void* nccl_comm = nullptr;
   int dp_rank = 0, dp_world = 1;
+  int dp_timeout_ms = 120000;  // host-side limit for communicator creation and for enqueueing a collective
 };
 
 void fml_set_global_error(const std::string& msg);
@@ -54,6 +57,32 @@ int32_t fml_ensure_workspace_keep(fml_ctx* ctx, size_t bytes);
       return fml_fail((ctx), FML_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__)); \
   } while (0)
 
+// One host thread may drive contexts on several GPUs (the reference's host is a single isolate), so every entry
+// point makes its context's device current before it touches the runtime.  cudaGetDevice is a thread-local read.
+#define FML_ENTER(ctx)                                                        \
+  do {                                                                        \
+    if (ctx) {                                                                \
+      int cur__ = -1;                                                         \
+      if (cudaGetDevice(&cur__) != cudaSuccess || cur__ != (ctx)->device)     \
+        FML_CUDA((ctx), cudaSetDevice((ctx)->device));                        \
+    }                                                                         \
+  } while (0)
+
+// Runs `...` once per (call site, device of ctx).  Function attributes such as the dynamic shared memory opt-in
+// belong to ONE device, so a process-wide flag would leave every later device without them.  Two threads may both
+// run the body the first time; the bodies used here are idempotent.
+#define FML_MAX_DEVICES 64
+#define FML_ONCE_PER_DEVICE(ctx, ...)                                                        \
+  do {                                                                                       \
+    static std::atomic<bool> done__[FML_MAX_DEVICES];                                        \
+    const int dev__ = (ctx)->device;                                                         \
+    const bool slot__ = dev__ >= 0 && dev__ < FML_MAX_DEVICES;                               \
+    if (!slot__ || !done__[dev__].load(std::memory_order_acquire)) {                         \
+      __VA_ARGS__;                                                                           \
+      if (slot__) done__[dev__].store(true, std::memory_order_release);                      \
+    }                                                                                        \
+  } while (0)
+
 #define FML_REQUIRE(ctx, cond, msg) \
   do {                              \
     if (!(cond)) return fml_fail((ctx), FML_ERR_INVALID, (msg)); \
@@ -65,6 +94,14 @@ int32_t fml_ensure_workspace_keep(fml_ctx* ctx, size_t bytes);
     if (e__ != cudaSuccess)                                                             \
       return fml_fail((ctx), FML_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e__)); \
   } while (0)
+
+// Second word of the context's status block: set (first writer wins) by a kernel that met a token id or a class label
+// outside its range.  The kernel skips the access, so a bad index is a reported error, never an illegal address.
+#define FML_STATUS_BAD_INDEX_WORD 1
+enum { FML_BAD_INDEX_EMBEDDING_FWD = 201, FML_BAD_INDEX_EMBEDDING_BWD = 202, FML_BAD_INDEX_LABEL = 203 };
+__device__ __forceinline__ void fml_flag_bad_index(int* status, int code) {
+  if (status) atomicCAS(status + FML_STATUS_BAD_INDEX_WORD, 0, code);
+}
 
 // LSTM gate epilogue of the tensor-core GEMM: the product's columns are gate-interleaved
 // (column 4*r + q = gate q of hidden unit r, q in f,i,c~,o); `addend` [M x N] is added to the product

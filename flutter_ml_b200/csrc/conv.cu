@@ -119,6 +119,7 @@ extern "C" {
 
 int32_t fml_conv2d_fwd(fml_ctx* ctx, const float* in, const float* w, const float* bias, float* out, int32_t n_img, int32_t H,
                        int32_t W, int32_t n_k, int32_t kh, int32_t kw, int32_t pad) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, in && w && out && n_img > 0 && H > 0 && W > 0 && n_k > 0 && kh > 0 && kw > 0 && pad >= 0, "fml_conv2d_fwd: bad arguments");
   const int OH = H + 2 * pad - kh + 1, OW = W + 2 * pad - kw + 1;
   FML_REQUIRE(ctx, OH > 0 && OW > 0, "fml_conv2d_fwd: kernel larger than the padded input");
@@ -130,6 +131,7 @@ int32_t fml_conv2d_fwd(fml_ctx* ctx, const float* in, const float* w, const floa
 
 int32_t fml_conv2d_bwd(fml_ctx* ctx, const float* in, const float* w, const float* dout, float* din, float* dw, float* dbias,
                        int32_t n_img, int32_t H, int32_t W, int32_t n_k, int32_t kh, int32_t kw, int32_t pad) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, in && w && dout && n_img > 0 && H > 0 && W > 0 && n_k > 0 && kh > 0 && kw > 0 && pad >= 0, "fml_conv2d_bwd: bad arguments");
   const int OH = H + 2 * pad - kh + 1, OW = W + 2 * pad - kw + 1;
   FML_REQUIRE(ctx, OH > 0 && OW > 0, "fml_conv2d_bwd: kernel larger than the padded input");

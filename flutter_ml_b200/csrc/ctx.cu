@@ -25,14 +25,15 @@ int32_t fml_ensure_workspace(fml_ctx* ctx, size_t bytes) {
   if (bytes <= ctx->ws_bytes) return FML_OK;
   if (ctx->capturing)
     return fml_fail(ctx, FML_ERR_INVALID, "the scratch arena would have to grow while a graph is being recorded; run the sequence once eagerly first");
+  // Stream-ordered: the old arena is released after everything already queued on the stream has used it, and the
+  // new one comes from the pool, so growing the arena in the middle of a step does not synchronise the device.
   if (ctx->ws) {
-    FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    cudaFree(ctx->ws);
+    FML_CUDA(ctx, cudaFreeAsync(ctx->ws, ctx->stream));
     ctx->ws = nullptr;
     ctx->ws_bytes = 0;
   }
   size_t want = std::max(bytes, (size_t)(64u << 20));
-  cudaError_t e = cudaMalloc(&ctx->ws, want);
+  cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&ctx->ws), want, ctx->stream);
   if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_OOM, std::string("workspace cudaMalloc: ") + cudaGetErrorString(e));
   ctx->ws_bytes = want;
   return FML_OK;
@@ -76,6 +77,36 @@ int32_t fml_device_name(int32_t device, char* buf, int32_t buf_len) {
   return FML_OK;
 }
 
+// Everything fml_init acquires after the context object exists; on any failure the caller releases what was
+// acquired so far and deletes the context (nothing is left behind by a failed fml_init).
+static int32_t init_resources(fml_ctx* ctx, const fml_config* cfg) {
+  FML_CUDA(ctx, cudaSetDevice(ctx->device));
+  FML_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+  {
+    cudaMemPool_t pool;
+    FML_CUDA(ctx, cudaDeviceGetDefaultMemPool(&pool, ctx->device));
+    uint64_t keep = UINT64_MAX;
+    FML_CUDA(ctx, cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+  }
+  FML_CUDA(ctx, cudaMalloc(&ctx->d_status, 256));
+  FML_CUDA(ctx, cudaMemset(ctx->d_status, 0, 256));
+  FML_CUDA(ctx, cudaEventCreate(&ctx->ev0));
+  FML_CUDA(ctx, cudaEventCreate(&ctx->ev1));
+  if (cfg && cfg->workspace_bytes > 0) {
+    int32_t rc = fml_ensure_workspace(ctx, (size_t)cfg->workspace_bytes);
+    if (rc) return rc;
+  }
+  return FML_OK;
+}
+static void release_resources(fml_ctx* ctx) {
+  if (ctx->ws) cudaFree(ctx->ws);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+  if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+  if (ctx->stream && ctx->own_stream) cudaStreamDestroy(ctx->stream);
+  ctx->ws = nullptr; ctx->d_status = nullptr; ctx->ev0 = ctx->ev1 = nullptr; ctx->stream = nullptr;
+}
+
 int32_t fml_init(const fml_config* cfg, fml_ctx** out) {
   if (!out) return fml_fail(nullptr, FML_ERR_INVALID, "fml_init: out is NULL");
   *out = nullptr;
@@ -92,21 +123,11 @@ int32_t fml_init(const fml_config* cfg, fml_ctx** out) {
   ctx->device = dev;
   ctx->sm_count = prop.multiProcessorCount;
   ctx->precision = cfg ? cfg->precision : FML_PREC_TF32;
-  FML_CUDA(ctx, cudaSetDevice(dev));
-  FML_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
-  {
-    cudaMemPool_t pool;
-    FML_CUDA(ctx, cudaDeviceGetDefaultMemPool(&pool, dev));
-    uint64_t keep = UINT64_MAX;
-    FML_CUDA(ctx, cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-  }
-  FML_CUDA(ctx, cudaMalloc(&ctx->d_status, 256));
-  FML_CUDA(ctx, cudaMemset(ctx->d_status, 0, 256));
-  FML_CUDA(ctx, cudaEventCreate(&ctx->ev0));
-  FML_CUDA(ctx, cudaEventCreate(&ctx->ev1));
-  if (cfg && cfg->workspace_bytes > 0) {
-    int32_t rc = fml_ensure_workspace(ctx, (size_t)cfg->workspace_bytes);
-    if (rc) return rc;
+  const int32_t rc = init_resources(ctx, cfg);
+  if (rc != FML_OK) {  // the message stays readable through fml_last_error(NULL)
+    release_resources(ctx);
+    delete ctx;
+    return rc;
   }
   *out = ctx;
   return FML_OK;
@@ -143,11 +164,13 @@ const char* fml_last_error(fml_ctx* ctx) {
 }
 
 int32_t fml_sm_count(fml_ctx* ctx, int32_t* count) {
+  FML_ENTER(ctx);
   *count = ctx->sm_count;
   return FML_OK;
 }
 
 int32_t fml_set_stream(fml_ctx* ctx, void* s) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   ctx->stream = reinterpret_cast<cudaStream_t>(s);
@@ -156,23 +179,42 @@ int32_t fml_set_stream(fml_ctx* ctx, void* s) {
 }
 
 int32_t fml_sync(fml_ctx* ctx) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return FML_OK;
 }
 
 int32_t fml_device_status(fml_ctx* ctx, int32_t* code) {
-  int v = 0;
-  FML_CUDA(ctx, cudaMemcpyAsync(&v, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  FML_ENTER(ctx);
+  int v[2] = {0, 0};  // word 0: expired waits; word 1: indices out of range
+  FML_CUDA(ctx, cudaMemcpyAsync(v, ctx->d_status, sizeof v, cudaMemcpyDeviceToHost, ctx->stream));
   FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  *code = v;
-  if (v != 0) {
+  *code = v[0] ? v[0] : v[1];
+  if (v[0] != 0) {
     cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
-    return fml_fail(ctx, FML_ERR_TIMEOUT, "a device-side bounded wait expired (role code " + std::to_string(v) + ")");
+    return fml_fail(ctx, FML_ERR_TIMEOUT, "a device-side bounded wait expired (role code " + std::to_string(v[0]) + ")");
+  }
+  if (v[1] != 0) {
+    cudaMemsetAsync(ctx->d_status + FML_STATUS_BAD_INDEX_WORD, 0, sizeof(int), ctx->stream);
+    return fml_fail(ctx, FML_ERR_INVALID,
+                    std::string(v[1] == FML_BAD_INDEX_LABEL ? "a class label was outside [0, cols)" : "a token id was outside [0, vocab)") +
+                        "; the access was skipped (code " + std::to_string(v[1]) + ")");
   }
   return FML_OK;
 }
 
+int32_t fml_mem_info(fml_ctx* ctx, int64_t* free_bytes, int64_t* total_bytes, int64_t* arena_bytes) {
+  FML_ENTER(ctx);
+  size_t f = 0, t = 0;
+  FML_CUDA(ctx, cudaMemGetInfo(&f, &t));
+  if (free_bytes) *free_bytes = (int64_t)f;
+  if (total_bytes) *total_bytes = (int64_t)t;
+  if (arena_bytes) *arena_bytes = (int64_t)ctx->ws_bytes;
+  return FML_OK;
+}
+
 int32_t fml_alloc(fml_ctx* ctx, int64_t n, float** out) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, n >= 0 && out, "fml_alloc: bad arguments");
   void* p = nullptr;
   // stream-ordered pool: a block freed on the context's stream is reused by later calls on the
@@ -185,6 +227,7 @@ int32_t fml_alloc(fml_ctx* ctx, int64_t n, float** out) {
 }
 
 int32_t fml_free(fml_ctx* ctx, float* p) {
+  FML_ENTER(ctx);
   if (!p) return FML_OK;
   auto it = ctx->allocs.find(p);
   FML_REQUIRE(ctx, it != ctx->allocs.end(), "fml_free: pointer was not allocated by this context");
@@ -196,19 +239,23 @@ int32_t fml_free(fml_ctx* ctx, float* p) {
 }
 
 int32_t fml_zero(fml_ctx* ctx, float* p, int64_t n) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaMemsetAsync(p, 0, (size_t)n * sizeof(float), ctx->stream));
   return FML_OK;
 }
 
 int32_t fml_upload_f32(fml_ctx* ctx, float* dst, const float* host, int64_t n) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
   return FML_OK;
 }
 int32_t fml_upload_i32(fml_ctx* ctx, int32_t* dst, const int32_t* host, int64_t n) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
   return FML_OK;
 }
 int32_t fml_upload_f64(fml_ctx* ctx, float* dst, const double* host, int64_t n) {
+  FML_ENTER(ctx);
   // stage the doubles in the scratch arena and narrow on the device
   int32_t rc = fml_ensure_workspace(ctx, (size_t)n * 8);
   if (rc) return rc;
@@ -220,11 +267,13 @@ int32_t fml_upload_f64(fml_ctx* ctx, float* dst, const double* host, int64_t n) 
   return FML_OK;
 }
 int32_t fml_download_f32(fml_ctx* ctx, float* host, const float* src, int64_t n) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaMemcpyAsync(host, src, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
   FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return FML_OK;
 }
 int32_t fml_download_f64(fml_ctx* ctx, double* host, const float* src, int64_t n) {
+  FML_ENTER(ctx);
   int32_t rc = fml_ensure_workspace(ctx, (size_t)n * 8);
   if (rc) return rc;
   f32_to_f64_kernel<<<(int)std::min<int64_t>((n + 255) / 256, 4096), 256, 0, ctx->stream>>>(
@@ -235,15 +284,18 @@ int32_t fml_download_f64(fml_ctx* ctx, double* host, const float* src, int64_t n
   return FML_OK;
 }
 int32_t fml_copy(fml_ctx* ctx, float* dst, const float* src, int64_t n) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaMemcpyAsync(dst, src, (size_t)n * 4, cudaMemcpyDeviceToDevice, ctx->stream));
   return FML_OK;
 }
 
 int32_t fml_timer_start(fml_ctx* ctx) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
   return FML_OK;
 }
 int32_t fml_timer_stop_ms(fml_ctx* ctx, float* ms) {
+  FML_ENTER(ctx);
   FML_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
   FML_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
   FML_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
@@ -251,12 +303,14 @@ int32_t fml_timer_stop_ms(fml_ctx* ctx, float* ms) {
 }
 
 int32_t fml_event_record(fml_ctx* ctx, int32_t slot) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, slot >= 0 && slot < 64, "fml_event_record: slot out of range");
   if (!ctx->ev_pool[slot]) FML_CUDA(ctx, cudaEventCreate(&ctx->ev_pool[slot]));
   FML_CUDA(ctx, cudaEventRecord(ctx->ev_pool[slot], ctx->stream));
   return FML_OK;
 }
 int32_t fml_event_elapsed_ms(fml_ctx* ctx, int32_t a, int32_t b, float* ms) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, a >= 0 && a < 64 && b >= 0 && b < 64 && ctx->ev_pool[a] && ctx->ev_pool[b],
               "fml_event_elapsed_ms: slot not recorded");
   FML_CUDA(ctx, cudaEventSynchronize(ctx->ev_pool[b]));
@@ -271,11 +325,13 @@ static int32_t lane_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
   return FML_OK;
 }
 int32_t fml_any_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
+  FML_ENTER(ctx);
   if (lane < 0) { *out = ctx->stream; return FML_OK; }
   return lane_stream(ctx, lane, out);
 }
 static int32_t any_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) { return fml_any_stream(ctx, lane, out); }
 int32_t fml_event_record_on(fml_ctx* ctx, int32_t slot, int32_t lane) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, slot >= 0 && slot < 64, "fml_event_record_on: slot out of range");
   cudaStream_t s;
   int32_t rc = any_stream(ctx, lane, &s);
@@ -285,6 +341,7 @@ int32_t fml_event_record_on(fml_ctx* ctx, int32_t slot, int32_t lane) {
   return FML_OK;
 }
 int32_t fml_wait_event(fml_ctx* ctx, int32_t lane, int32_t slot) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, slot >= 0 && slot < 64 && ctx->ev_pool[slot], "fml_wait_event: slot not recorded");
   cudaStream_t s;
   int32_t rc = any_stream(ctx, lane, &s);
@@ -293,11 +350,13 @@ int32_t fml_wait_event(fml_ctx* ctx, int32_t lane, int32_t slot) {
   return FML_OK;
 }
 int32_t fml_event_sync(fml_ctx* ctx, int32_t slot) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, slot >= 0 && slot < 64 && ctx->ev_pool[slot], "fml_event_sync: slot not recorded");
   FML_CUDA(ctx, cudaEventSynchronize(ctx->ev_pool[slot]));
   return FML_OK;
 }
 int32_t fml_lane_h2d(fml_ctx* ctx, int32_t lane, float* dst, const float* host, int64_t n) {
+  FML_ENTER(ctx);
   cudaStream_t s;
   int32_t rc = lane_stream(ctx, lane, &s);
   if (rc) return rc;
@@ -305,6 +364,7 @@ int32_t fml_lane_h2d(fml_ctx* ctx, int32_t lane, float* dst, const float* host, 
   return FML_OK;
 }
 int32_t fml_lane_d2h(fml_ctx* ctx, int32_t lane, float* host, const float* src, int64_t n) {
+  FML_ENTER(ctx);
   cudaStream_t s;
   int32_t rc = lane_stream(ctx, lane, &s);
   if (rc) return rc;
@@ -312,6 +372,7 @@ int32_t fml_lane_d2h(fml_ctx* ctx, int32_t lane, float* host, const float* src, 
   return FML_OK;
 }
 int32_t fml_lane_sync(fml_ctx* ctx, int32_t lane) {
+  FML_ENTER(ctx);
   cudaStream_t s;
   int32_t rc = lane_stream(ctx, lane, &s);
   if (rc) return rc;
@@ -320,12 +381,14 @@ int32_t fml_lane_sync(fml_ctx* ctx, int32_t lane) {
 }
 
 int32_t fml_graph_begin(fml_ctx* ctx) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, !ctx->capturing, "fml_graph_begin: a recording is already in progress");
   FML_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
   ctx->capturing = true;
   return FML_OK;
 }
 int32_t fml_graph_end(fml_ctx* ctx, int32_t* graph_id) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, ctx->capturing && graph_id, "fml_graph_end: no recording in progress");
   ctx->capturing = false;
   cudaGraph_t g = nullptr;
@@ -339,11 +402,13 @@ int32_t fml_graph_end(fml_ctx* ctx, int32_t* graph_id) {
   return FML_OK;
 }
 int32_t fml_graph_launch(fml_ctx* ctx, int32_t id) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, id >= 0 && id < (int32_t)ctx->graphs.size() && ctx->graphs[id], "fml_graph_launch: unknown graph");
   FML_CUDA(ctx, cudaGraphLaunch(ctx->graphs[id], ctx->stream));
   return FML_OK;
 }
 int32_t fml_graph_destroy(fml_ctx* ctx, int32_t id) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, id >= 0 && id < (int32_t)ctx->graphs.size() && ctx->graphs[id], "fml_graph_destroy: unknown graph");
   FML_CUDA(ctx, cudaGraphExecDestroy(ctx->graphs[id]));
   ctx->graphs[id] = nullptr;
@@ -351,12 +416,14 @@ int32_t fml_graph_destroy(fml_ctx* ctx, int32_t id) {
 }
 
 int32_t fml_host_alloc(fml_ctx* ctx, int64_t bytes, void** out) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, bytes > 0 && out, "fml_host_alloc: bad arguments");
   cudaError_t e = cudaHostAlloc(out, (size_t)bytes, cudaHostAllocDefault);
   if (e != cudaSuccess) return fml_fail(ctx, FML_ERR_OOM, std::string("fml_host_alloc: ") + cudaGetErrorString(e));
   return FML_OK;
 }
 int32_t fml_host_free(fml_ctx* ctx, void* p) {
+  FML_ENTER(ctx);
   if (p) FML_CUDA(ctx, cudaFreeHost(p));
   return FML_OK;
 }
@@ -458,6 +525,7 @@ int32_t fml_stage_wait(fml_ctx* ctx) {
 }
 
 int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, d && d->A && d->B && d->C, "fml_gemm: NULL operand");
   FML_REQUIRE(ctx, d->M > 0 && d->N > 0 && d->K > 0, "fml_gemm: M, N, K must be positive");
   FML_REQUIRE(ctx, d->beta == 0.f || d->beta == 1.f, "fml_gemm: beta must be 0 or 1");
@@ -486,6 +554,18 @@ int32_t fml_gemm(fml_ctx* ctx, const fml_gemm_desc* d) {
 
 int32_t fml_gemm_last_path(fml_ctx* ctx, int32_t* path) {
   *path = ctx->last_gemm_path;
+  return FML_OK;
+}
+
+int32_t fml_selftest_per_device_once(int32_t device, int32_t* runs) {
+  // host only: the same guard the kernels' one-time, per-device set-up uses, around a counter
+  static std::atomic<int> count[FML_MAX_DEVICES + 1];
+  if (!runs) return fml_fail(nullptr, FML_ERR_INVALID, "fml_selftest_per_device_once: runs is NULL");
+  fml_ctx probe;
+  probe.device = device;
+  const int slot = device >= 0 && device < FML_MAX_DEVICES ? device : FML_MAX_DEVICES;
+  FML_ONCE_PER_DEVICE(&probe, { count[slot]++; });
+  *runs = count[slot].load();
   return FML_OK;
 }
 

@@ -187,13 +187,16 @@ __device__ __forceinline__ void adam1(float& w, float g, float& m, float& v, con
   const float mh = m / c1, vh = v / c2;
   w -= lr * mh / (sqrtf(vh) + eps);
 }
-template <bool VEC>
-__global__ void adam_kernel(float* w, const float* __restrict__ g, float* m, float* v, long long n, const AdamK k) {
+// ZERO: the gradient is cleared as it is consumed (Optimizer.zeroGrad, optimizers.dart:62-66, folded into the
+// update: one pass over the gradient instead of a read here and a memset later).
+template <bool VEC, bool ZERO>
+__global__ void adam_kernel(float* w, float* g, float* m, float* v, long long n, const AdamK k) {
   const float gs = k.gs;
   if (VEC) {
     EW_LOOP(i, n >> 2) {
       float4 wv = reinterpret_cast<float4*>(w)[i];
       float4 gv = reinterpret_cast<const float4*>(g)[i];
+      if (ZERO) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       float4 mv = reinterpret_cast<float4*>(m)[i];
       float4 vv = reinterpret_cast<float4*>(v)[i];
       adam1(wv.x, gs * gv.x, mv.x, vv.x, k);
@@ -205,7 +208,10 @@ __global__ void adam_kernel(float* w, const float* __restrict__ g, float* m, flo
       reinterpret_cast<float4*>(v)[i] = vv;
     }
   } else {
-    EW_LOOP(i, n) adam1(w[i], gs * g[i], m[i], v[i], k);
+    EW_LOOP(i, n) {
+      adam1(w[i], gs * g[i], m[i], v[i], k);
+      if (ZERO) g[i] = 0.f;
+    }
   }
 }
 
@@ -279,14 +285,19 @@ __global__ void act2_bwd_kernel(int kind, float alpha, const float* __restrict__
 }
 
 // ------------------------------------------------------------------ embedding
+// A token id outside [0, vocab) reads nothing (its row comes out as the positional part only) and is reported
+// through the status block; the reference would throw a RangeError at embeddingLayer.dart:53.
 __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int* __restrict__ ids,
                                      const float* __restrict__ pe, float* __restrict__ out, long long n, int dim,
-                                     int period) {
+                                     int period, int vocab, int* status) {
   const int d4 = dim >> 2;
   EW_LOOP(i, n * d4) {
     const long long r = i / d4;
     const int c = (int)(i % d4);
-    float4 v = reinterpret_cast<const float4*>(table + (long long)ids[r] * dim)[c];
+    const int id = ids[r];
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((unsigned)id < (unsigned)vocab) v = reinterpret_cast<const float4*>(table + (long long)id * dim)[c];
+    else if (c == 0) fml_flag_bad_index(status, FML_BAD_INDEX_EMBEDDING_FWD);
     if (pe) {
       float4 q = reinterpret_cast<const float4*>(pe + (r % period) * dim)[c];
       v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
@@ -296,21 +307,26 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int*
 }
 __global__ void embedding_fwd_scalar_kernel(const float* __restrict__ table, const int* __restrict__ ids,
                                             const float* __restrict__ pe, float* __restrict__ out, long long n, int dim,
-                                            int period) {
+                                            int period, int vocab, int* status) {
   EW_LOOP(i, n * dim) {
     const long long r = i / dim;
     const int c = (int)(i % dim);
-    float v = table[(long long)ids[r] * dim + c];
+    const int id = ids[r];
+    float v = 0.f;
+    if ((unsigned)id < (unsigned)vocab) v = table[(long long)id * dim + c];
+    else if (c == 0) fml_flag_bad_index(status, FML_BAD_INDEX_EMBEDDING_FWD);
     if (pe) v += pe[(r % period) * dim + c];
     out[i] = v;
   }
 }
 __global__ void embedding_bwd_kernel(const float* __restrict__ dout, const int* __restrict__ ids, float* dtable,
-                                     long long n, int dim) {
+                                     long long n, int dim, int vocab, int* status) {
   EW_LOOP(i, n * dim) {
     const long long r = i / dim;
     const int c = (int)(i % dim);
-    atomicAdd(dtable + (long long)ids[r] * dim + c, dout[i]);
+    const int id = ids[r];
+    if ((unsigned)id < (unsigned)vocab) atomicAdd(dtable + (long long)id * dim + c, dout[i]);
+    else if (c == 0) fml_flag_bad_index(status, FML_BAD_INDEX_EMBEDDING_BWD);
   }
 }
 __global__ void positional_kernel(float* pe, int max_len, int d_model) {
@@ -336,6 +352,7 @@ int32_t launch_vec(fml_ctx* ctx, const char* name, bool vec, long long n, K kvec
 extern "C" {
 
 int32_t fml_fill(fml_ctx* ctx, float* p, int64_t n, float value) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, p && n >= 0, "fml_fill: bad arguments");
   if (n == 0) return FML_OK;
   fill_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(p, n, value);
@@ -344,12 +361,14 @@ int32_t fml_fill(fml_ctx* ctx, float* p, int64_t n, float value) {
 }
 
 int32_t fml_act_fwd(fml_ctx* ctx, int32_t act, const float* x, float* y, int64_t n) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, x && y && n >= 0, "fml_act_fwd: bad arguments");
   const bool vec = (n % 4 == 0) && al16(x) && al16(y);
   return launch_vec(ctx, "act_fwd_kernel", vec, n, act_fwd_kernel<true>, act_fwd_kernel<false>, act, x, y, (long long)n);
 }
 
 int32_t fml_col_sum(fml_ctx* ctx, const float* dy, float* db, int64_t rows, int64_t cols, int32_t accumulate) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, dy && db && rows > 0 && cols > 0, "fml_col_sum: bad arguments");
   if (!accumulate) FML_CUDA(ctx, cudaMemsetAsync(db, 0, (size_t)cols * 4, ctx->stream));
   const long long cb = (cols + 31) / 32;
@@ -363,6 +382,7 @@ int32_t fml_col_sum(fml_ctx* ctx, const float* dy, float* db, int64_t rows, int6
 
 int32_t fml_act_bwd(fml_ctx* ctx, int32_t act, const float* saved, const float* dy, float* dx, int64_t rows,
                     int64_t cols, int32_t accumulate, float* dbias) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, dy && dx && rows > 0 && cols > 0, "fml_act_bwd: bad arguments");
   FML_REQUIRE(ctx, act == FML_ACT_NONE || saved, "fml_act_bwd: saved tensor required");
   const long long n = rows * cols;
@@ -393,11 +413,15 @@ static int32_t binary(fml_ctx* ctx, int mode, float s, const float* a, const flo
   const bool vec = (n % 4 == 0) && al16(a) && al16(y) && (mode == 2 || al16(b));
   return launch_vec(ctx, "binary_kernel", vec, n, binary_kernel<true>, binary_kernel<false>, mode, s, a, b, y, (long long)n);
 }
-int32_t fml_add(fml_ctx* ctx, const float* a, const float* b, float* y, int64_t n) { return binary(ctx, 0, 0.f, a, b, y, n); }
-int32_t fml_mul(fml_ctx* ctx, const float* a, const float* b, float* y, int64_t n) { return binary(ctx, 1, 0.f, a, b, y, n); }
-int32_t fml_axpy(fml_ctx* ctx, float s, const float* x, float* y, int64_t n) { return binary(ctx, 2, s, x, nullptr, y, n); }
+int32_t fml_add(fml_ctx* ctx, const float* a, const float* b, float* y, int64_t n) {
+  FML_ENTER(ctx); return binary(ctx, 0, 0.f, a, b, y, n); }
+int32_t fml_mul(fml_ctx* ctx, const float* a, const float* b, float* y, int64_t n) {
+  FML_ENTER(ctx); return binary(ctx, 1, 0.f, a, b, y, n); }
+int32_t fml_axpy(fml_ctx* ctx, float s, const float* x, float* y, int64_t n) {
+  FML_ENTER(ctx); return binary(ctx, 2, s, x, nullptr, y, n); }
 
 int32_t fml_add_bias(fml_ctx* ctx, const float* x, const float* b, float* y, int64_t rows, int64_t cols) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, x && b && y && rows > 0 && cols > 0, "fml_add_bias: bad arguments");
   add_bias_kernel<<<ew_blocks(ctx, rows * cols), EW_THREADS, 0, ctx->stream>>>(x, b, y, rows, cols);
   FML_LAUNCH_CHECK(ctx, "add_bias_kernel");
@@ -405,6 +429,7 @@ int32_t fml_add_bias(fml_ctx* ctx, const float* x, const float* b, float* y, int
 }
 
 int32_t fml_transpose(fml_ctx* ctx, const float* in, float* out, int64_t rows, int64_t cols) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, in && out && rows > 0 && cols > 0, "fml_transpose: bad arguments");
   dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
   FML_REQUIRE(ctx, grid.y <= 65535, "fml_transpose: too many rows");
@@ -414,6 +439,7 @@ int32_t fml_transpose(fml_ctx* ctx, const float* in, float* out, int64_t rows, i
 }
 
 int32_t fml_sgd_step(fml_ctx* ctx, float* w, const float* g, int64_t n, double lr, double grad_scale) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, w && g && n >= 0, "fml_sgd_step: bad arguments");
   const bool vec = (n % 4 == 0) && al16(w) && al16(g);
   return launch_vec(ctx, "sgd_kernel", vec, n, sgd_kernel<true>, sgd_kernel<false>, w, g, (long long)n, (float)lr, (float)grad_scale);
@@ -421,17 +447,42 @@ int32_t fml_sgd_step(fml_ctx* ctx, float* w, const float* g, int64_t n, double l
 
 int32_t fml_adam_step(fml_ctx* ctx, float* w, const float* g, float* m, float* v, int64_t n, double lr, double beta1,
                       double beta2, double eps, int32_t t, double grad_scale) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, w && g && m && v && n >= 0 && t >= 1, "fml_adam_step: bad arguments");
   AdamK k;
   k.lr = (float)lr; k.b1 = (float)beta1; k.b2 = (float)beta2; k.eps = (float)eps; k.gs = (float)grad_scale;
   k.omb1 = (float)(1.0 - beta1); k.omb2 = (float)(1.0 - beta2);
   k.c1 = (float)(1.0 - pow(beta1, (double)t)); k.c2 = (float)(1.0 - pow(beta2, (double)t));
   const bool vec = (n % 4 == 0) && al16(w) && al16(g) && al16(m) && al16(v);
-  return launch_vec(ctx, "adam_kernel", vec, n, adam_kernel<true>, adam_kernel<false>, w, g, m, v, (long long)n, k);
+  return launch_vec(ctx, "adam_kernel", vec, n, adam_kernel<true, false>, adam_kernel<false, false>, w, const_cast<float*>(g), m, v,
+                    (long long)n, k);
+}
+
+int32_t fml_adam_step_on(fml_ctx* ctx, int32_t lane, float* w, float* g, float* m, float* v, int64_t n, double lr, double beta1,
+                         double beta2, double eps, int32_t t, double grad_scale, int32_t zero_grad) {
+  FML_ENTER(ctx);
+  FML_REQUIRE(ctx, w && g && m && v && n >= 0 && t >= 1, "fml_adam_step_on: bad arguments");
+  cudaStream_t s;
+  int32_t rc = fml_any_stream(ctx, lane, &s);
+  if (rc) return rc;
+  AdamK k;
+  k.lr = (float)lr; k.b1 = (float)beta1; k.b2 = (float)beta2; k.eps = (float)eps; k.gs = (float)grad_scale;
+  k.omb1 = (float)(1.0 - beta1); k.omb2 = (float)(1.0 - beta2);
+  k.c1 = (float)(1.0 - pow(beta1, (double)t)); k.c2 = (float)(1.0 - pow(beta2, (double)t));
+  if (n == 0) return FML_OK;
+  const bool vec = (n % 4 == 0) && al16(w) && al16(g) && al16(m) && al16(v);
+  const int blocks = ew_blocks(ctx, vec ? n >> 2 : n);
+  if (vec && zero_grad) adam_kernel<true, true><<<blocks, EW_THREADS, 0, s>>>(w, g, m, v, (long long)n, k);
+  else if (vec) adam_kernel<true, false><<<blocks, EW_THREADS, 0, s>>>(w, g, m, v, (long long)n, k);
+  else if (zero_grad) adam_kernel<false, true><<<blocks, EW_THREADS, 0, s>>>(w, g, m, v, (long long)n, k);
+  else adam_kernel<false, false><<<blocks, EW_THREADS, 0, s>>>(w, g, m, v, (long long)n, k);
+  FML_LAUNCH_CHECK(ctx, "adam_kernel");
+  return FML_OK;
 }
 
 int32_t fml_optimizer_step(fml_ctx* ctx, int32_t kind, float* w, const float* g, float* s1, float* s2, float* s3, int64_t n,
                            double lr, double h1, double h2, double h3, double h4, int32_t t) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, w && g && n >= 0, "fml_optimizer_step: bad arguments");
   const bool two = kind == FML_OPT_ADAMW || kind == FML_OPT_AMSGRAD;
   FML_REQUIRE(ctx, kind == FML_OPT_MOMENTUM || kind == FML_OPT_NAG || kind == FML_OPT_RMSPROP || kind == FML_OPT_ADAGRAD || two,
@@ -450,6 +501,7 @@ int32_t fml_optimizer_step(fml_ctx* ctx, int32_t kind, float* w, const float* g,
 }
 
 int32_t fml_act2_fwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, float* y, int64_t n) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, x && y && n >= 0 && kind >= FML_ACT2_LEAKY_RELU && kind <= FML_ACT2_MISH, "fml_act2_fwd: bad arguments");
   if (n == 0) return FML_OK;
   act2_fwd_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(kind, alpha, x, y, n);
@@ -458,6 +510,7 @@ int32_t fml_act2_fwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, fl
 }
 int32_t fml_act2_bwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, const float* dy, float* dx, int64_t n,
                      int32_t accumulate) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, x && dy && dx && n >= 0 && kind >= FML_ACT2_LEAKY_RELU && kind <= FML_ACT2_MISH, "fml_act2_bwd: bad arguments");
   if (n == 0) return FML_OK;
   act2_bwd_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(kind, alpha, x, dy, dx, n, accumulate);
@@ -466,25 +519,29 @@ int32_t fml_act2_bwd(fml_ctx* ctx, int32_t kind, float alpha, const float* x, co
 }
 
 int32_t fml_embedding_fwd(fml_ctx* ctx, const float* table, const int32_t* ids, const float* pe, float* out, int64_t n,
-                          int32_t dim, int32_t pe_period) {
-  FML_REQUIRE(ctx, table && ids && out && n > 0 && dim > 0, "fml_embedding_fwd: bad arguments");
+                          int32_t dim, int32_t pe_period, int32_t vocab) {
+  FML_ENTER(ctx);
+  FML_REQUIRE(ctx, table && ids && out && n > 0 && dim > 0 && vocab > 0, "fml_embedding_fwd: bad arguments");
   FML_REQUIRE(ctx, !pe || pe_period > 0, "fml_embedding_fwd: pe_period must be positive");
   if (dim % 4 == 0 && al16(table) && al16(out) && (!pe || al16(pe)))
-    embedding_fwd_kernel<<<ew_blocks(ctx, n * (dim / 4)), EW_THREADS, 0, ctx->stream>>>(table, ids, pe, out, n, dim, pe_period);
+    embedding_fwd_kernel<<<ew_blocks(ctx, n * (dim / 4)), EW_THREADS, 0, ctx->stream>>>(table, ids, pe, out, n, dim, pe_period, vocab, ctx->d_status);
   else
-    embedding_fwd_scalar_kernel<<<ew_blocks(ctx, n * dim), EW_THREADS, 0, ctx->stream>>>(table, ids, pe, out, n, dim, pe_period);
+    embedding_fwd_scalar_kernel<<<ew_blocks(ctx, n * dim), EW_THREADS, 0, ctx->stream>>>(table, ids, pe, out, n, dim, pe_period, vocab, ctx->d_status);
   FML_LAUNCH_CHECK(ctx, "embedding_fwd_kernel");
   return FML_OK;
 }
 
-int32_t fml_embedding_bwd(fml_ctx* ctx, const float* dout, const int32_t* ids, float* dtable, int64_t n, int32_t dim) {
-  FML_REQUIRE(ctx, dout && ids && dtable && n > 0 && dim > 0, "fml_embedding_bwd: bad arguments");
-  embedding_bwd_kernel<<<ew_blocks(ctx, n * dim), EW_THREADS, 0, ctx->stream>>>(dout, ids, dtable, n, dim);
+int32_t fml_embedding_bwd(fml_ctx* ctx, const float* dout, const int32_t* ids, float* dtable, int64_t n, int32_t dim,
+                          int32_t vocab) {
+  FML_ENTER(ctx);
+  FML_REQUIRE(ctx, dout && ids && dtable && n > 0 && dim > 0 && vocab > 0, "fml_embedding_bwd: bad arguments");
+  embedding_bwd_kernel<<<ew_blocks(ctx, n * dim), EW_THREADS, 0, ctx->stream>>>(dout, ids, dtable, n, dim, vocab, ctx->d_status);
   FML_LAUNCH_CHECK(ctx, "embedding_bwd_kernel");
   return FML_OK;
 }
 
 int32_t fml_positional_table(fml_ctx* ctx, float* pe, int32_t max_len, int32_t d_model) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, pe && max_len > 0 && d_model > 0, "fml_positional_table: bad arguments");
   positional_kernel<<<ew_blocks(ctx, (long long)max_len * d_model), EW_THREADS, 0, ctx->stream>>>(pe, max_len, d_model);
   FML_LAUNCH_CHECK(ctx, "positional_kernel");

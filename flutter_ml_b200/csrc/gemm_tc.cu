@@ -797,6 +797,7 @@ __global__ void wait_timeout_selftest_kernel(int* status, unsigned long long lim
 }  // namespace
 
 extern "C" int32_t fml_selftest_wait_timeout(fml_ctx* ctx, int32_t limit_us) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, ctx && limit_us > 0 && limit_us <= 1000000, "fml_selftest_wait_timeout: the limit must be 1 .. 1000000 us");
   wait_timeout_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, (unsigned long long)limit_us * 1000ull);
   FML_LAUNCH_CHECK(ctx, "wait_timeout_selftest_kernel");
@@ -818,12 +819,10 @@ bool fml_gemm_tc_eligible(const fml_gemm_desc* d) {
 }
 
 int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const fml_lstm_epilogue* lstm) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  FML_ONCE_PER_DEVICE(ctx, {
     FML_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES));
     FML_CUDA(ctx, cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
-    attr_set = true;
-  }
+  });
   const int nb1 = d->batch1 < 1 ? 1 : d->batch1, nb2 = d->batch2 < 1 ? 1 : d->batch2;
   // pair mode (256 x 256 tiles over two CTAs) when the problem has enough such tiles to occupy the
   // machine; FML_GEMM_PAIR=0/1 forces the choice (diagnostics)

@@ -106,6 +106,7 @@ int32_t temp_alloc(fml_ctx* ctx, size_t n_floats, float** out) {
 extern "C" {
 
 int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, d && d->W && d->b && d->x && d->gates && d->cells && d->hs && d->xproj, "fml_lstm_fwd: NULL buffer");
   FML_REQUIRE(ctx, d->T > 0 && d->B > 0 && d->I > 0 && d->H > 0, "fml_lstm_fwd: bad sizes");
   const int T = d->T, B = d->B, I = d->I, H = d->H, Z = H + I;
@@ -172,6 +173,7 @@ int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d) {
 
 int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last, float* dW, float* db, float* dx,
                      float* scratch) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, d && dh_last && dW && db && scratch, "fml_lstm_bwd: NULL buffer");
   const int T = d->T, B = d->B, I = d->I, H = d->H, Z = H + I;
   const long long bh = (long long)B * H, b4h = (long long)B * 4 * H;

@@ -214,6 +214,7 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmH, const __grid
 // Runs the recurrence of fml_lstm_fwd (after the input projection) in one kernel.  Returns 1 when the shape is not
 // eligible (the caller falls back to the per-step kernels), 0 on success, a negative status on failure.
 int32_t fml_lstm_fwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const float* Wi, int fast_math) {
+  FML_ENTER(ctx);
   const int T = d->T, B = d->B, H = d->H, I = d->I, Z = H + I;
   if (B > 128 || H % 32 != 0 || (4 * H) % NC != 0) return 1;
   const int n_cta = 4 * H / NC;
@@ -244,11 +245,7 @@ int32_t fml_lstm_fwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const floa
   p.T = T; p.B = B; p.H = H; p.kblocks = kblocks; p.ring = ring; p.w_bytes = w_bytes;
   p.xproj = d->xproj; p.gates = d->gates; p.cells = d->cells; p.hs = d->hs;
   p.gbar = gbar; p.fast_math = fast_math; p.status = ctx->d_status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    FML_CUDA(ctx, cudaFuncSetAttribute(lstm_fwd_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    attr_set = true;
-  }
+  FML_ONCE_PER_DEVICE(ctx, { FML_CUDA(ctx, cudaFuncSetAttribute(lstm_fwd_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); });
   void* args[] = {(void*)&tmH, (void*)&tmW, (void*)&p};
   cudaError_t e = cudaLaunchCooperativeKernel((void*)lstm_fwd_persistent_kernel, dim3(n_cta), dim3(LT_THREADS), args, smem, ctx->stream);
   cudaFreeAsync(gbar, ctx->stream);

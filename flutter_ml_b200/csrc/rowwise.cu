@@ -352,8 +352,11 @@ __global__ void __launch_bounds__(256) layernorm_bwd_block(const float* __restri
 // One block per row, online (max, sum) in a single read, then a second read (L2-resident for
 // rows of this size) that writes the gradient.  Per-row losses go to scratch and are summed in
 // double by a single block, so the result does not depend on the launch geometry.
+// A label outside [0, cols) is never used as an index: the row then contributes no loss and no one-hot term (its
+// gradient is the plain softmax) and the status block records FML_BAD_INDEX_LABEL.
 __global__ void __launch_bounds__(256) xent_kernel(const float* z, const int* __restrict__ labels, float* dz,
-                                                   float* __restrict__ row_loss, long long rows, int cols, float inv_count) {
+                                                   float* __restrict__ row_loss, long long rows, int cols, float inv_count,
+                                                   int* status) {
   __shared__ float red[8];
   __shared__ float zl_s;
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -368,10 +371,14 @@ __global__ void __launch_bounds__(256) xent_kernel(const float* z, const int* __
     s = (mx == NEG_INF) ? 0.f : s * expf(mx - bm);
     s = block_sum(s, red);
     const int lab = labels[r];
-    if (threadIdx.x == 0) zl_s = zr[lab];
+    const bool lab_ok = (unsigned)lab < (unsigned)cols;
+    if (threadIdx.x == 0) {
+      zl_s = lab_ok ? zr[lab] : 0.f;
+      if (!lab_ok) fml_flag_bad_index(status, FML_BAD_INDEX_LABEL);
+    }
     __syncthreads();
     const float zl = zl_s;
-    if (threadIdx.x == 0) row_loss[r] = -(zl - bm - logf(s)) * inv_count;
+    if (threadIdx.x == 0) row_loss[r] = lab_ok ? -(zl - bm - logf(s)) * inv_count : 0.f;
     if (dz) {
       float* dr = dz + r * cols;
       for (int c = threadIdx.x; c < cols; c += 256) dr[c] = (expf(zr[c] - bm) / s - (c == lab ? 1.f : 0.f)) * inv_count;
@@ -389,7 +396,8 @@ __global__ void __launch_bounds__(256) xent_kernel(const float* z, const int* __
 template <int NV, bool COLSUM>
 __global__ void __launch_bounds__(1024) xent_rowreg_kernel(const float* z, const int* __restrict__ labels,
                                                            float* dz /* may alias z */, float* __restrict__ row_loss,
-                                                           long long rows, int cols, float inv_count, float* __restrict__ colpart) {
+                                                           long long rows, int cols, float inv_count, float* __restrict__ colpart,
+                                                           int* status) {
   extern __shared__ float4 colacc[];   // [cols / 4], COLSUM only
   __shared__ float red[32];
   __shared__ float bcast[3];
@@ -412,6 +420,8 @@ __global__ void __launch_bounds__(1024) xent_rowreg_kernel(const float* z, const
       if (c4 * 4 < cols) v[i] = zr[c4];
     }
     const int lab = labels[r];
+    const bool lab_ok = (unsigned)lab < (unsigned)cols;   // otherwise no thread owns the label's column below
+    if (!lab_ok && threadIdx.x == 0) fml_flag_bad_index(status, FML_BAD_INDEX_LABEL);
     float mx = NEG_INF;
 #pragma unroll
     for (int i = 0; i < NV; i++) {
@@ -444,7 +454,7 @@ __global__ void __launch_bounds__(1024) xent_rowreg_kernel(const float* z, const
     }
     __syncthreads();
     const float tot = bcast[1];
-    if (threadIdx.x == 0) row_loss[r] = -(bcast[2] - bm - logf(tot)) * inv_count;
+    if (threadIdx.x == 0) row_loss[r] = lab_ok ? -(bcast[2] - bm - logf(tot)) * inv_count : 0.f;
     if (dz) {
       const float k = inv_count / tot;
       float4* dr = reinterpret_cast<float4*>(dz + r * cols);
@@ -534,6 +544,7 @@ extern "C" {
 
 int32_t fml_softmax_rows_fwd(fml_ctx* ctx, const float* x, float* y, int64_t rows, int32_t cols, float scale,
                              int32_t causal_period) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, x && y && rows > 0 && cols > 0, "fml_softmax_rows_fwd: bad arguments");
   if (cols % 4 == 0 && cols <= 2048 && al16(x) && al16(y)) {
 #define CALL(NV) softmax_fwd_warp<NV><<<warp_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(x, y, rows, cols, scale, causal_period)
@@ -548,6 +559,7 @@ int32_t fml_softmax_rows_fwd(fml_ctx* ctx, const float* x, float* y, int64_t row
 
 int32_t fml_softmax_rows_bwd(fml_ctx* ctx, const float* y, const float* dy, float* dx, int64_t rows, int32_t cols,
                              float scale, int32_t accumulate) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, y && dy && dx && rows > 0 && cols > 0, "fml_softmax_rows_bwd: bad arguments");
   if (cols % 4 == 0 && cols <= 2048 && al16(y) && al16(dy) && al16(dx)) {
 #define CALL(NV)                                                                                             \
@@ -568,6 +580,7 @@ int32_t fml_softmax_rows_bwd(fml_ctx* ctx, const float* y, const float* dy, floa
 
 int32_t fml_layernorm_fwd(fml_ctx* ctx, const float* x, const float* residual, const float* gamma, const float* beta,
                           float* y, float* xhat, float* rstd, int64_t rows, int32_t cols, float eps) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, x && gamma && beta && y && xhat && rstd && rows > 0 && cols > 0, "fml_layernorm_fwd: bad arguments");
   if (cols % 4 == 0 && cols <= 2048 && al16(x) && al16(y) && al16(xhat) && al16(gamma) && al16(beta) &&
       (!residual || al16(residual))) {
@@ -589,6 +602,7 @@ int32_t fml_layernorm_fwd(fml_ctx* ctx, const float* x, const float* residual, c
 
 int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, const float* xhat, const float* rstd,
                           float* dx, float* dgamma, float* dbeta, int64_t rows, int32_t cols, int32_t accumulate_dx) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, dy && gamma && xhat && rstd && rows > 0 && cols > 0, "fml_layernorm_bwd: bad arguments");
   if (cols % 4 == 0 && cols <= 1024 && al16(dy) && al16(xhat) && al16(gamma) && (!dx || al16(dx))) {
     // fewer, fatter blocks: every block ends with one atomic per column
@@ -596,12 +610,10 @@ int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, con
 #define CALL(NV)                                                                                                     \
   do {                                                                                                               \
     const size_t sm = (size_t)2 * 8 * NV * 128 * sizeof(float);                                                      \
-    static bool attr_set = false;                                                                                    \
-    if (!attr_set) {                                                                                                 \
+    FML_ONCE_PER_DEVICE(ctx, {                                                                                       \
       FML_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_warp<NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));  \
       FML_CUDA(ctx, cudaFuncSetAttribute(layernorm_bwd_warp<NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
-      attr_set = true;                                                                                               \
-    }                                                                                                                \
+    });                                                                                                              \
     if (accumulate_dx && dx)                                                                                         \
       layernorm_bwd_warp<NV, true><<<blocks, 256, sm, ctx->stream>>>(dy, gamma, xhat, rstd, dx, dgamma, dbeta, rows, cols);  \
     else                                                                                                             \
@@ -630,14 +642,12 @@ static int32_t softmax_xent_impl(fml_ctx* ctx, const float* z, const int32_t* la
 #define XENT(NV)                                                                                                              \
   do {                                                                                                                        \
     if (fuse) {                                                                                                               \
-      static bool attr_set = false;                                                                                           \
-      if (!attr_set) {                                                                                                        \
+      FML_ONCE_PER_DEVICE(ctx, {                                                                                              \
         FML_CUDA(ctx, cudaFuncSetAttribute(xent_rowreg_kernel<NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4)); \
-        attr_set = true;                                                                                                      \
-      }                                                                                                                       \
-      xent_rowreg_kernel<NV, true><<<blocks, 1024, (size_t)cols * 4, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, colpart); \
+      });                                                                                                                     \
+      xent_rowreg_kernel<NV, true><<<blocks, 1024, (size_t)cols * 4, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, colpart, ctx->d_status); \
     } else {                                                                                                                  \
-      xent_rowreg_kernel<NV, false><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, nullptr); \
+      xent_rowreg_kernel<NV, false><<<blocks, 1024, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, nullptr, ctx->d_status); \
     }                                                                                                                         \
   } while (0)
     if (cols <= 8192) XENT(2);
@@ -645,7 +655,7 @@ static int32_t softmax_xent_impl(fml_ctx* ctx, const float* z, const int32_t* la
     else XENT(8);
 #undef XENT
   } else {
-    xent_kernel<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+    xent_kernel<<<block_row_blocks(ctx, rows), 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, ctx->d_status);
   }
   final_sum_kernel<float><<<1, 256, 0, ctx->stream>>>(row_loss, rows, 1.0, loss_sum);
   FML_LAUNCH_CHECK(ctx, "xent_kernel");
@@ -659,12 +669,14 @@ static int32_t softmax_xent_impl(fml_ctx* ctx, const float* z, const int32_t* la
 
 int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum, int64_t rows,
                          int32_t cols, float inv_count) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, z && labels && loss_sum && rows > 0 && cols > 0, "fml_softmax_xent: bad arguments");
   return softmax_xent_impl(ctx, z, labels, dz, loss_sum, rows, cols, inv_count, nullptr);
 }
 
 int32_t fml_softmax_xent_dbias(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum, int64_t rows,
                                int32_t cols, float inv_count, float* dbias) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, z && labels && dz && loss_sum && dbias && rows > 0 && cols > 0, "fml_softmax_xent_dbias: bad arguments");
   return softmax_xent_impl(ctx, z, labels, dz, loss_sum, rows, cols, inv_count, dbias);
 }
@@ -693,6 +705,7 @@ int g_xent_static_sms[kMaxDevices] = {};
 
 int32_t fml_softmax_xent_static(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz, float* loss_sum,
                                 int64_t rows, int32_t cols, float inv_count) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, z && labels && loss_sum && rows > 0 && cols > 0, "fml_softmax_xent_static: bad arguments");
   if (rows > FML_XENT_STATIC_MAX_ROWS)
     return fml_fail(ctx, FML_ERR_OOM,
@@ -712,13 +725,14 @@ int32_t fml_softmax_xent_static(fml_ctx* ctx, const float* z, const int32_t* lab
   float* row_loss = g_xent_static_ptr[dev];
   // every row slot read by the final sum is written by this launch first, so nothing needs clearing
   const int blocks = (int)std::max<long long>(1, std::min<long long>(rows, (long long)g_xent_static_sms[dev] * 8));
-  xent_kernel<<<blocks, 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count);
+  xent_kernel<<<blocks, 256, 0, ctx->stream>>>(z, labels, dz, row_loss, rows, cols, inv_count, ctx->d_status);
   final_sum_kernel<float><<<1, 256, 0, ctx->stream>>>(row_loss, rows, 1.0, loss_sum);
   FML_LAUNCH_CHECK(ctx, "xent_kernel (static scratch)");
   return FML_OK;
 }
 
 int32_t fml_mse(fml_ctx* ctx, const float* p, const float* t, float* dp, float* loss_sum, int64_t n, float upstream) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, p && t && loss_sum && n > 0, "fml_mse: bad arguments");
   const int blocks = (int)std::max<long long>(1, std::min<long long>((n + 255) / 256, (long long)ctx->sm_count * 4));
   int32_t rc = fml_ensure_workspace(ctx, (size_t)blocks * sizeof(double));

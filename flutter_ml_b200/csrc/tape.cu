@@ -263,7 +263,7 @@ int32_t op_forward(fml_ctx* ctx, const fml_op& o, int idx) {
       return fml_layernorm_fwd(ctx, o.in[0], nullptr, o.in[1], o.in[2], o.out, o.aux[0], o.aux[1], o.rows, o.cols, o.s);
     case FML_OP_EMBEDDING_LOOKUP:
       FML_REQUIRE(ctx, o.in[0] && o.ids, where + " (embedding_lookup): missing table or ids");
-      return fml_embedding_fwd(ctx, o.in[0], o.ids, nullptr, o.out, o.rows, o.cols, 0);
+      return fml_embedding_fwd(ctx, o.in[0], o.ids, nullptr, o.out, o.rows, o.cols, 0, o.inner);
     case FML_OP_MSE: {
       FML_REQUIRE(ctx, o.in[0] && o.in[1] && o.inner > 0, where + " (mse): missing input (inner = element count)");
       TP_TRY(fml_zero(ctx, o.out, 1));
@@ -392,7 +392,7 @@ int32_t op_backward(fml_ctx* ctx, const fml_op& o, int idx) {
     case FML_OP_LAYER_NORM:
       return fml_layernorm_bwd(ctx, o.gout, o.in[1], o.aux[0], o.aux[1], o.gin[0], o.gin[1], o.gin[2], o.rows, o.cols, 1);
     case FML_OP_EMBEDDING_LOOKUP:
-      return o.gin[0] ? fml_embedding_bwd(ctx, o.gout, o.ids, o.gin[0], o.rows, o.cols) : FML_OK;
+      return o.gin[0] ? fml_embedding_bwd(ctx, o.gout, o.ids, o.gin[0], o.rows, o.cols, o.inner) : FML_OK;
     case FML_OP_MSE:
       if (o.gin[0]) {
         mse_bwd_kernel<<<tp_blocks(ctx, o.inner), TP_THREADS, 0, st>>>(o.in[0], o.in[1], o.gout, o.gin[0], 2.f / (float)o.inner, o.inner);
@@ -468,6 +468,7 @@ int32_t fml_tape_kind(const char* op_name) {
 }
 
 int32_t fml_tape_run(fml_ctx* ctx, const fml_op* ops, int32_t n_ops, int32_t direction) {
+  FML_ENTER(ctx);
   FML_REQUIRE(ctx, ctx && n_ops >= 0 && (ops || n_ops == 0), "fml_tape_run: bad arguments");
   FML_REQUIRE(ctx, direction >= FML_TAPE_FORWARD && direction <= FML_TAPE_BACKWARD_NOSEED, "fml_tape_run: unknown direction");
   if (n_ops == 0) return FML_OK;

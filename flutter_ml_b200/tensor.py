@@ -578,12 +578,12 @@ def embeddingLookup(table: Tensor, ids: DeviceArray, pe: Optional[DeviceArray] =
     ctx = table.ctx
     n, dim = ids.size, table.shape[1]
     out = Tensor(ctx.empty(n, dim), ctx)
-    ctx.call("fml_embedding_fwd", table.value, ids, pe, out.value, n, dim, int(period))
+    ctx.call("fml_embedding_fwd", table.value, ids, pe, out.value, n, dim, int(period), table.shape[0])
 
     def bw():
         if table.grad is None:
             table.zeroGrad()
-        ctx.call("fml_embedding_bwd", out.grad, ids, table.grad, n, dim)
+        ctx.call("fml_embedding_bwd", out.grad, ids, table.grad, n, dim, table.shape[0])
     out.creator = Node([table], bw, "embedding_lookup", 0)
     return out
 

@@ -15,7 +15,9 @@
  *   - Every function returns 0 on success or a negative fml_status;
  *     fml_last_error() gives the message.  Nothing throws, aborts or traps.
  *   - Calls are asynchronous on the context's stream; fml_download_* and
- *     fml_sync wait.  A context is driven by one host thread at a time.
+ *     fml_sync wait.  A context is driven by one host thread at a time; one thread may drive
+ *     several contexts, on the same or on different GPUs (every entry point makes its
+ *     context's device current first).
  *   - There is no CPU fallback: without a CUDA device fml_init fails.
  */
 #ifndef FML_H_
@@ -70,18 +72,31 @@ int32_t fml_sm_count(fml_ctx* ctx, int32_t* count);
 /* Use an existing cudaStream_t (as void*) instead of the context's own. */
 int32_t fml_set_stream(fml_ctx* ctx, void* cuda_stream);
 int32_t fml_sync(fml_ctx* ctx);
-/* Bounded device-side waits record a code here instead of hanging; reading it
- * synchronises.  0 means no kernel gave up. */
+/* What kernels could not do, read back once (reading synchronises, then clears):
+ *   - a bounded device-side wait that expired instead of hanging: returns FML_ERR_TIMEOUT, *code = the role that gave up;
+ *   - a token id or class label outside its range (201 embedding forward, 202 embedding backward, 203 cross-entropy
+ *     label): returns FML_ERR_INVALID, *code = which.  The kernel skipped the access, so memory is intact.
+ * 0 / FML_OK means neither happened. */
 int32_t fml_device_status(fml_ctx* ctx, int32_t* code);
 /* Failure-path self test: one CTA waits (with the bounded wait all pipeline roles use) on a barrier that nothing
  * signals; after limit_us microseconds it records code 99 and returns.  fml_device_status then reports
  * FML_ERR_TIMEOUT once and the context stays usable.  Nothing faults, traps or hangs. */
 int32_t fml_selftest_wait_timeout(fml_ctx* ctx, int32_t limit_us);
+/* Host-only self test (no device needed) of the bookkeeping behind one-time kernel set-up: function attributes such
+ * as the shared-memory opt-in belong to one device, so the library keeps one "done" flag per (call site, device).
+ * Each call passes through such a guard around a counter for `device` and returns the counter in *runs: it must read
+ * 1 however often the same ordinal is passed, and every new ordinal (0..63) must run the body once more.  Ordinals
+ * outside that range have no slot and run the body every time. */
+int32_t fml_selftest_per_device_once(int32_t device, int32_t* runs);
 
 /* ---- memory ---------------------------------------------------------------
  * Dart lists are float64 (lib/cuda/cudacaller.dart:38-43 narrows element by
  * element); the f64 variants convert once, in C. */
 int32_t fml_alloc(fml_ctx* ctx, int64_t n_floats, float** out);
+/* Free and total bytes of the context's device (cudaMemGetInfo) and the current size of the context's scratch
+ * arena; any pointer may be NULL.  A caller can hold the figures from before and after a call against each other
+ * to see whether the call took device memory. */
+int32_t fml_mem_info(fml_ctx* ctx, int64_t* free_bytes, int64_t* total_bytes, int64_t* arena_bytes);
 int32_t fml_free(fml_ctx* ctx, float* p);
 int32_t fml_zero(fml_ctx* ctx, float* p, int64_t n_floats);
 int32_t fml_fill(fml_ctx* ctx, float* p, int64_t n_floats, float value);
@@ -250,7 +265,8 @@ int32_t fml_layernorm_bwd(fml_ctx* ctx, const float* dy, const float* gamma, con
                           const float* rstd, float* dx, float* dgamma, float* dbeta, int64_t rows,
                           int32_t cols, int32_t accumulate_dx);
 /* Softmax cross-entropy (extension): loss_sum += sum_r -log softmax(z_r)[label_r] * inv_count,
- * dz = (softmax(z) - onehot) * inv_count written in place of z when dz == z. */
+ * dz = (softmax(z) - onehot) * inv_count written in place of z when dz == z.  A label outside
+ * [0, cols) contributes no loss and no one-hot term and is reported by fml_device_status. */
 int32_t fml_softmax_xent(fml_ctx* ctx, const float* z, const int32_t* labels, float* dz,
                          float* loss_sum, int64_t rows, int32_t cols, float inv_count);
 /* fml_softmax_xent that also ADDS the column sums of dz into dbias: the bias gradient of the layer that produced
@@ -279,11 +295,14 @@ int32_t fml_mse(fml_ctx* ctx, const float* p, const float* t, float* dp, float* 
 
 /* ---- embedding / positional --------------------------------------------------
  * out[i] = table[ids[i]] (+ pe[i mod period]) (embeddingLayer.dart:47-56,
- * positionalEncodingLayer.dart:55-65); backward scatter-adds (:58-65). */
+ * positionalEncodingLayer.dart:55-65); backward scatter-adds (:58-65).  table and dtable have
+ * `vocab` rows.  An id outside [0, vocab) (the reference would raise a RangeError at :53) is
+ * never used as an address: its row gets no table contribution, and fml_device_status reports
+ * FML_ERR_INVALID afterwards. */
 int32_t fml_embedding_fwd(fml_ctx* ctx, const float* table, const int32_t* ids, const float* pe,
-                          float* out, int64_t n, int32_t dim, int32_t pe_period);
+                          float* out, int64_t n, int32_t dim, int32_t pe_period, int32_t vocab);
 int32_t fml_embedding_bwd(fml_ctx* ctx, const float* dout, const int32_t* ids, float* dtable,
-                          int64_t n, int32_t dim);
+                          int64_t n, int32_t dim, int32_t vocab);
 /* The reference's table: angle = pos / 10000^(2i/dModel), sin for even i, cos for odd i
  * (positionalEncodingLayer.dart:39-48). */
 int32_t fml_positional_table(fml_ctx* ctx, float* pe, int32_t max_len, int32_t d_model);
@@ -296,6 +315,12 @@ int32_t fml_positional_table(fml_ctx* ctx, float* pe, int32_t max_len, int32_t d
 int32_t fml_sgd_step(fml_ctx* ctx, float* w, const float* g, int64_t n, double lr, double grad_scale);
 int32_t fml_adam_step(fml_ctx* ctx, float* w, const float* g, float* m, float* v, int64_t n,
                       double lr, double beta1, double beta2, double eps, int32_t t, double grad_scale);
+/* The same update enqueued on copy lane `lane` (-1: the main stream), for a slice of the parameters whose gradient
+ * exchange has just been enqueued on that lane: the update of finished layers then runs under the backward pass of
+ * the others.  zero_grad != 0 also clears g as it is read (Optimizer.zeroGrad, optimizers.dart:62-66, in the same
+ * pass).  Order it against the main stream with the event calls. */
+int32_t fml_adam_step_on(fml_ctx* ctx, int32_t lane, float* w, float* g, float* m, float* v, int64_t n,
+                         double lr, double beta1, double beta2, double eps, int32_t t, double grad_scale, int32_t zero_grad);
 
 /* The other optimizers of lib/optimizers, one kernel (state buffers start at zero; unused ones may be NULL):
  *   FML_OPT_MOMENTUM sgdmomentum.dart:56-57 (h1 = momentum; s1 = velocity)
@@ -469,7 +494,12 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
  * distributes the 128 bytes by any means, every rank joins, and gradients are
  * summed in place with NCCL over NVLink. */
 int32_t fml_dp_unique_id(uint8_t out[128]);
+/* Creates the communicator without blocking inside NCCL: the call polls its progress and, if the other ranks have
+ * not all joined within the limit (fml_dp_set_timeout, default 120 s), aborts it and returns FML_ERR_TIMEOUT; the
+ * context stays usable and fml_dp_init may be called again with a fresh id.  The same limit bounds the host side of
+ * every fml_dp_allreduce_sum* call (a rank that left between steps), which also reports NCCL's asynchronous errors. */
 int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id[128], int32_t rank, int32_t world);
+int32_t fml_dp_set_timeout(fml_ctx* ctx, int32_t timeout_ms);
 int32_t fml_dp_allreduce_sum(fml_ctx* ctx, float* buf, int64_t n);
 /* The same on copy lane `lane` (or -1: the main stream), to overlap the exchange of finished gradient
  * slices with the rest of the backward pass; order it against the main stream with the event calls. */

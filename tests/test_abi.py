@@ -103,3 +103,20 @@ def test_stage_rows_gathers_and_narrows_on_host_threads():
     assert L.fml_stage_wait(None) == 0                                         # nothing outstanding: returns at once
     assert L.fml_stage_rows(None, None, None, 0, 1, None, 0, 1, 0) != 0      # rejected, not a crash
     assert L.fml_stage_rows(None, dst.ctypes.data, src.ctypes.data, 9, row, None, 0, 1, 0) != 0
+
+
+def test_per_device_once_bookkeeping():
+    """One-time kernel set-up (the shared-memory opt-in of cudaFuncSetAttribute) is per DEVICE: the guard around it
+    must run its body once for every device ordinal, not once per process.  Host-only self test of that guard."""
+    import ctypes as C
+    from flutter_ml_b200 import _lib
+    L = _lib.load()
+    runs = C.c_int32(0)
+    for device in (0, 1, 5, 63):
+        for _ in range(3):
+            assert L.fml_selftest_per_device_once(device, C.byref(runs)) == 0
+            assert runs.value == 1, (device, runs.value)          # once per ordinal, however often it is asked
+    before = runs.value
+    assert L.fml_selftest_per_device_once(64, C.byref(runs)) == 0 and L.fml_selftest_per_device_once(64, C.byref(runs)) == 0
+    assert runs.value >= 2                                        # no slot for this ordinal: the body runs every time
+    assert L.fml_selftest_per_device_once(0, None) == -1

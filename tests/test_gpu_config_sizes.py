@@ -165,7 +165,7 @@ def test_config3_full_size_through_fused_attention(orc):
     assert own["dx"] <= 1e-2 and own["grad_max"] <= 5e-2                 # gate flips included
     assert aligned["dx"] <= 2e-3                                           # chains of up to eight TF32 products
     for n, e in aligned_g.items():
-        assert e <= 2e-3, (n, e)
+        assert e <= 5e-3, (n, e)
     c.close()
 
 

@@ -294,8 +294,8 @@ def test_embedding_and_positional(ctx, orc):
     dtab, dids, pe, out, ddout, dtable = (ctx.upload(table), ctx.upload(ids), ctx.empty(S, d), ctx.empty(Bn * S, d),
                                           ctx.upload(dout), ctx.zeros(V, d))
     ctx.call("fml_positional_table", pe, S, d)
-    ctx.call("fml_embedding_fwd", dtab, dids, pe, out, Bn * S, d, S)
-    ctx.call("fml_embedding_bwd", ddout, dids, dtable, Bn * S, d)
+    ctx.call("fml_embedding_fwd", dtab, dids, pe, out, Bn * S, d, S, V)
+    ctx.call("fml_embedding_bwd", ddout, dids, dtable, Bn * S, d, V)
     assert rel(pe.numpy(), pe_ref) <= 1e-7
     assert rel(out.numpy(), out_ref) <= 1e-7
     assert rel(dtable.numpy(), dt_ref) <= 1e-6
@@ -557,3 +557,144 @@ def test_gemm_full_size_sampled_entries_and_exact_properties(prec, tol):
     assert np.array_equal(D_.numpy()[ii, jj], 4.0 * C[ii, jj])
     assert c.device_status() == 0
     c.close()
+
+
+def test_out_of_range_ids_and_labels_are_reported_not_dereferenced(orc):
+    """A token id outside the table or a label outside the logits (the reference would raise a RangeError,
+    embeddingLayer.dart:53) is never used as an address: the kernels skip the access, fml_device_status returns
+    FML_ERR_INVALID once with the kernel's code, memory next to the table is untouched and the context stays usable."""
+    import ctypes
+    from flutter_ml_b200 import _lib
+    c = _lib.Context()
+    V, d, n = 50, 8, 6
+    rng = np.random.default_rng(3)
+    # table sits in the middle of a larger buffer so that a stray write would be visible on either side
+    guard = rng.standard_normal((3 * V, d)).astype(np.float32)
+    buf = c.upload(guard)
+    table = buf.view(V * d, (V, d))
+    ids = np.array([3, V, 7, -1, 49, 1 << 30], dtype=np.int32)
+    dids, out = c.upload(ids), c.empty(n, d)
+    c.call("fml_embedding_fwd", table, dids, None, out, n, d, 0, V)
+    code = ctypes.c_int32(0)
+    assert c.lib.fml_device_status(c.h, ctypes.byref(code)) == -1 and code.value == 201
+    assert b"token id" in c.lib.fml_last_error(c.h)
+    assert c.device_status() == 0                                   # reported once
+    got = out.numpy()
+    ok = (ids >= 0) & (ids < V)
+    assert np.array_equal(got[ok], guard[V:2 * V][ids[ok]]) and np.all(got[~ok] == 0)
+    dout = c.upload(np.ones((n, d), np.float32))
+    c.call("fml_embedding_bwd", dout, dids, table, n, d, V)         # adds into the table region only
+    assert c.lib.fml_device_status(c.h, ctypes.byref(code)) == -1 and code.value == 202
+    after = buf.numpy()
+    assert np.array_equal(after[:V], guard[:V]) and np.array_equal(after[2 * V:], guard[2 * V:])
+    expect = guard[V:2 * V].copy()
+    for i in ids[ok]:
+        expect[i] += 1
+    assert np.array_equal(after[V:2 * V], expect)
+    # labels: narrow rows (block-per-row kernel), wide rows (row-in-registers kernel), and the no-allocation entry point
+    for cols, fn in ((10, "fml_softmax_xent"), (4096, "fml_softmax_xent"), (10, "fml_softmax_xent_static")):
+        rows = 5
+        z = rng.standard_normal((rows, cols)).astype(np.float32)
+        labels = np.array([1, cols, 0, -3, cols - 1], dtype=np.int32)
+        dz, loss = c.empty(rows, cols), c.zeros(1)
+        c.call(fn, c.upload(z), c.upload(labels), dz, loss, rows, cols, 1.0 / rows, launches=2)
+        assert c.lib.fml_device_status(c.h, ctypes.byref(code)) == -1 and code.value == 203, (cols, fn)
+        good = (labels >= 0) & (labels < cols)
+        ref_good = np.zeros((int(good.sum()), cols))
+        ref_loss = orc.Ops().softmax_xent(w64(z[good]), np.ascontiguousarray(labels[good]), ref_good, 1.0 / rows)
+        assert abs(loss.numpy()[0] - ref_loss) <= 1e-5 * abs(ref_loss), (cols, fn)   # bad rows add no loss
+        assert rel(dz.numpy()[good], ref_good) <= 1e-5
+        p = np.exp(w64(z[~good]) - w64(z[~good]).max(1, keepdims=True))
+        assert rel(dz.numpy()[~good], p / p.sum(1, keepdims=True) / rows) <= 1e-5    # plain softmax, no one-hot term
+    # the context still computes
+    a = rng.standard_normal((64, 64)).astype(np.float32)
+    C_ = c.empty(64, 64)
+    c.gemm(c.upload(a), c.upload(a), C_, 64, 64, 64)
+    assert rel(C_.numpy(), w64(a) @ w64(a)) <= TOL_TF32 and c.device_status() == 0
+    c.close()
+
+
+def test_one_host_thread_drives_several_contexts():
+    """The reference's host is one isolate (lib/cuda/cudacaller.dart:25-60 runs on the caller's thread): one thread must be
+    able to interleave calls on several contexts.  Two contexts on the same device always; one context per device on
+    every visible GPU as well when there are several (each entry point makes its context's device current, and the
+    kernels' shared-memory opt-in is made once per device)."""
+    import ctypes
+    from flutter_ml_b200 import _lib
+    n_dev = ctypes.c_int32(0)
+    assert _lib.load().fml_device_count(ctypes.byref(n_dev)) == 0
+    devices = [0, 0] + list(range(1, min(n_dev.value, 4)))
+    ctxs = [_lib.Context(device=dv, precision=_lib.PREC_TF32) for dv in devices]
+    rng = np.random.default_rng(17)
+    M, N, K = 384, 320, 256                                         # tensor-core path: needs the shared-memory opt-in
+    jobs = []
+    for i, c in enumerate(ctxs):                                    # enqueue on every context before reading any result
+        a, b = rng.standard_normal((M, K)).astype(np.float32), rng.standard_normal((K, N)).astype(np.float32)
+        A, B, C_ = c.upload(a), c.upload(b), c.empty(M, N)
+        jobs.append((c, a, b, A, B, C_))
+    for c, a, b, A, B, C_ in jobs:
+        c.gemm(A, B, C_, M, N, K, act="gelu", bias=None)
+        assert c.gemm_last_path() == 1
+    for c, a, b, A, B, C_ in reversed(jobs):
+        z = w64(a) @ w64(b)
+        from math import sqrt
+        from scipy.special import erf
+        assert rel(C_.numpy(), 0.5 * z * (1 + erf(z / sqrt(2)))) <= TOL_TF32
+        assert c.device_status() == 0
+    for c in ctxs:
+        c.close()
+
+
+def test_communicator_creation_times_out_when_the_peer_never_joins():
+    """Failure made on the host, no kernel involved: rank 0 of a world of two whose peer never calls in.  The
+    non-blocking communicator creation is polled against the limit, aborted when it passes, and reported as
+    FML_ERR_TIMEOUT; the context then still computes and can join a new (single-rank) world."""
+    import ctypes
+    import os
+    import time
+    from flutter_ml_b200 import _lib
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    c = _lib.Context()
+    uid = ctypes.create_string_buffer(128)
+    assert c.lib.fml_dp_unique_id(uid) == 0
+    assert c.lib.fml_dp_set_timeout(c.h, 0) == -1
+    c.check(c.lib.fml_dp_set_timeout(c.h, 1500))
+    t0 = time.time()
+    rc = c.lib.fml_dp_init(c.h, uid.raw, 0, 2)
+    waited = time.time() - t0
+    assert rc == -4, (rc, c.lib.fml_last_error(c.h))
+    assert b"a peer did not arrive" in c.lib.fml_last_error(c.h)
+    assert 1.0 <= waited <= 20.0, waited
+    assert c.lib.fml_dp_allreduce_sum(c.h, None, 0) == 0             # back to a world of one: nothing to exchange
+    a = np.random.default_rng(1).standard_normal((128, 128)).astype(np.float32)
+    C_ = c.empty(128, 128)
+    c.gemm(c.upload(a), c.upload(a), C_, 128, 128, 128)
+    assert rel(C_.numpy(), w64(a) @ w64(a)) <= TOL_TF32 and c.device_status() == 0
+    c.check(c.lib.fml_dp_init(c.h, bytes(128), 0, 1))
+    c.close()
+
+
+@pytest.mark.parametrize("M,N,K,tA,tB", [(384, 320, 256, 0, 0), (2048, 2048, 512, 0, 0), (2048, 2048, 512, 0, 1), (2048, 2048, 512, 1, 0),
+                                         (300, 200, 100, 1, 1), (1024, 1024, 8192, 1, 0)])
+def test_tf32_product_is_the_exact_product_of_truncated_operands(ctx, M, N, K, tA, tB):
+    """Where the TF32 error comes from: the tensor core drops the low 13 mantissa bits of every fp32 operand and then
+    multiplies and accumulates (in fp32) without further loss.  A float64 product of operands cut to 19 bits on the
+    host must therefore reproduce the device result to fp32 accumulation accuracy, in every tile mode and operand
+    layout; the distance of both from the exact product is the operand truncation alone (about 7.7e-4 on generic
+    data, of which 7.0e-4 is a bias toward zero: 3.5e-4 per operand)."""
+    rng = np.random.default_rng(M + N + K + tA + 2 * tB)
+    A = rng.standard_normal((K, M) if tA else (M, K)).astype(np.float32)
+    B = rng.standard_normal((N, K) if tB else (K, N)).astype(np.float32)
+    dC = ctx.empty(M, N)
+    ctx.gemm(ctx.upload(A), ctx.upload(B), dC, M, N, K, transA=bool(tA), transB=bool(tB), precision=0)
+    assert ctx.gemm_last_path() == 1
+
+    def cut(x):
+        return (np.ascontiguousarray(x, np.float32).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32).astype(np.float64)
+    opA, opB = (A.T if tA else A), (B.T if tB else B)
+    got = dC.numpy()
+    assert rel(got, cut(opA) @ cut(opB)) <= 3e-6
+    exact = w64(opA) @ w64(opB)
+    assert 4e-4 <= rel(got, exact) <= TOL_TF32
+    shrink = float(np.sum(got * exact) / np.sum(exact * exact)) - 1.0          # least-squares scale of got against exact
+    assert -9e-4 <= shrink <= -5e-4, shrink

@@ -4,7 +4,9 @@ Hosts whose own allocator owns all device memory, or that cannot afford the devi
 synchronisation of cudaMalloc/cudaFree, call this variant; its per-row scratch is a fixed array
 inside the library instead of the context's growable arena.  The test calls it through the C ABI
 twice in a row (the array keeps the first call's contents) and compares loss and gradient with
-the regular entry point.  It lives in its own file, collected last, so that a run that stops at
+the regular entry point and with the float64 CPU checker, and it holds the device's free memory
+and the size of the context's arena from before the call against the figures after it: the one
+property the entry point exists for.  It lives in its own file, collected last, so that a run that stops at
 the first failure has already run everything else; it builds its own context and so passes both
 alone in a fresh process and after the other tests.
 """
@@ -14,7 +16,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def test_static_scratch_matches_regular_entry_point_twice():
+def test_static_scratch_matches_regular_entry_point_twice(orc):
     from flutter_ml_b200 import _lib
     ctx = _lib.Context()
     rng = np.random.default_rng(123)
@@ -23,10 +25,22 @@ def test_static_scratch_matches_regular_entry_point_twice():
         labels = rng.integers(0, cols, rows).astype(np.int32)
         inv = 1.0 / rows
         dl = ctx.upload(labels)
-        z_ref, dz_ref, loss_ref = ctx.upload(z), ctx.empty(rows, cols), ctx.zeros(1)
-        ctx.call("fml_softmax_xent", z_ref, dl, dz_ref, loss_ref, rows, cols, inv, launches=2)
         z_new, dz_new, loss_new = ctx.upload(z), ctx.empty(rows, cols), ctx.zeros(1)
+        z_ref, dz_ref, loss_ref = ctx.upload(z), ctx.empty(rows, cols), ctx.zeros(1)
+        # every buffer exists; from here to the second reading the only library call is the one under test
+        ctx.sync()
+        free0, _, arena0 = ctx.mem_info()
         ctx.call("fml_softmax_xent_static", z_new, dl, dz_new, loss_new, rows, cols, inv, launches=2)
+        ctx.sync()
+        free1, _, arena1 = ctx.mem_info()
+        assert arena1 == arena0, "the call grew the context's scratch arena"
+        assert free1 >= free0, f"the call took {free0 - free1} bytes of device memory"
+        ctx.call("fml_softmax_xent", z_ref, dl, dz_ref, loss_ref, rows, cols, inv, launches=2)
+        # against the float64 checker
+        dz64 = np.zeros((rows, cols))
+        loss64 = orc.Ops().softmax_xent(np.ascontiguousarray(z, dtype=np.float64), labels, dz64, inv)
+        assert abs(loss_new.numpy()[0] - loss64) <= 1e-5 * abs(loss64)
+        assert np.linalg.norm(dz_new.numpy() - dz64) <= 1e-5 * np.linalg.norm(dz64)
         # same kernels, same launch geometry: identical within the tolerance of the other xent tests
         a, b = loss_new.numpy()[0], loss_ref.numpy()[0]
         assert abs(a - b) <= 2e-6 * abs(b)
