@@ -7,9 +7,11 @@ bias+GELU epilogue (M=N=K=8192, fp32 storage, TF32 tensor-core products).
 Prints ONE JSON line.  `value` is whole-job TFLOP/s on algorithmic flops (6*M*N*K per step) with
 the operands resident in HBM; `e2e` is the same step driven from pinned host buffers (copies in
 the timed region); `roofline` is the tensor-core GEMM kernel against the measured tensor peak;
-`cpu_baseline` is the float64 CPU oracle on a bounded sample.  With N > 1 every rank runs the
-same step on its own GPU (no data-path collective; weak scaling) and the line also carries the
-data-parallel training step, which does all-reduce gradients over NCCL.
+`cpu_baseline` is the float64 CPU oracle on a bounded sample.  With N > 1 the step is the
+data-parallel form of the same layer: every rank holds the weights and its own 8192 rows of the batch
+(weak scaling), and the weight and bias gradients are summed over the ranks with one NCCL all-reduce
+per step, started right behind the dW product and overlapped with the dA product.  The line also
+carries the data-parallel transformer training step (configuration 5) as a sub-record.
 """
 from __future__ import annotations
 
@@ -26,9 +28,17 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch (mean of forward, dA, dW), from the ncu
-# captures summarised under profiles/ (keyed by M=N=K)
-NCU_DRAM_BYTES_PER_LAUNCH = {4096: 403_600_000, 8192: 3_051_000_000}
+
+
+def ncu_dram_bytes_per_launch(size):
+    """dram__bytes_read.sum + dram__bytes_write.sum per gemm_tc_kernel launch (mean of forward, dA, dW) at M=N=K=size,
+    from the file the ncu capture step writes next to its summaries; None when no capture covers this size."""
+    path = os.path.join(ROOT, "profiles", "gemm_tc_kernel_dram_bytes.json")
+    try:
+        with open(path) as f:
+            return json.load(f)["bytes_per_launch"].get(str(size))
+    except (OSError, KeyError, ValueError):
+        return None
 
 SWEEP = [(512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
          (16384, 4096, 1024)]
@@ -78,6 +88,7 @@ class ClockSampler:
         import datetime
         sm, pw, mx, reasons = [], [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        self.samples = []          # (timestamp, SM MHz) of every sample, for per-repeat medians
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             try:
@@ -86,6 +97,7 @@ class ClockSampler:
             except (ValueError, IndexError):
                 continue
             mx = mx_
+            self.samples.append((ts, clk))
             if self.t0 is not None and not (self.t0 <= ts <= self.t1 + 0.02):
                 continue  # outside the timed region
             sm.append(clk)
@@ -98,6 +110,11 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "samples": len(sm),
                 "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons)}
+
+    def window_mhz(self, t0, t1):
+        """Median SM clock of the samples taken between two host times (call after stop())."""
+        v = [c for ts, c in getattr(self, "samples", []) if t0 <= ts <= t1 + 0.02]
+        return statistics.median(v) if v else None
 
 
 def make_inputs(M, N, K, seed=1):
@@ -128,15 +145,17 @@ def run_reference(args, rank):
     # launchers such as torchrun export OMP_NUM_THREADS=1; this arm is meant to use every host thread
     oracle.Ops(True).set_threads(os.cpu_count() or 1)
     cores = oracle.Ops(True).threads()
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(args.warmup):
         cpu_step(S, S, S, True)
     times = [cpu_step(S, S, S, True) for _ in range(args.steps)]
     total = sum(times)
     tf = 6.0 * S ** 3 * args.steps / total / 1e12
     line = {"impl": "reference", "metric": "gemm_fwd_bwd_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * total / args.steps,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": {"workload": "dense fwd+bwd (bias+GELU), fp32 inputs, M=N=K=8192", "seed": 1},
+            "config": {"workload": f"dense fwd+bwd (bias+GELU epilogue, dZ+dbias, dA, dW), fp32, M=N=K={args.size}", "seed": 1,
+                       "timed_on": f"a bounded sample: M=N=K={S} per step (6*{S}^3 flop, float64 scalar loops); the RATE is "
+                                   f"compared, a full {args.size}^3 step would take about {total / args.steps * (args.size / S) ** 3:.0f} s"},
             "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                              "sample": f"M=N=K={S} fwd+bwd per step (6*{S}^3 flop), OpenMP over {cores} threads"},
             "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -303,14 +322,22 @@ def time_attention(ctx, n_seq=32, seq_len=512, heads=16, reps=10):
             "fwd_tflops_full_square": round(2 * unit / f_ms / 1e9, 1), "bwd_tflops_full_square": round(5 * unit / b_ms / 1e9, 1)}
 
 
+
+
+NOMINAL_TF32_TFLOPS = 1125.0   # dense TF32 per B200 (half the 2.25 PFLOP/s bf16 figure)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--size", type=int, default=8192, help="M=N=K of the timed step")
+    ap.add_argument("--size", type=int, default=8192, help="M=N=K of the timed step (rows per GPU when N > 1)")
     ap.add_argument("--ref-size", type=int, default=1024, help="M=N=K of one CPU sample step")
+    ap.add_argument("--repeats", type=int, default=0, help="timed regions of --steps steps each; 0 picks 10, fewer for long regions")
+    ap.add_argument("--reserve-sms", type=int, default=16, help="SMs the dA product leaves to the exchange that runs beside it (N > 1)")
+    ap.add_argument("--nccl-ctas", type=int, default=8, help="upper limit on the CTAs of the gradient exchange (N > 1)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-train", action="store_true")
@@ -323,6 +350,7 @@ def main():
     ap.add_argument("--configs-only", action="store_true", help="run only configurations 1, 3, 4 (profiling)")
     ap.add_argument("--config", type=int, default=0, choices=[0, 1, 3, 4], help="with --configs-only: just this one")
     ap.add_argument("--train-only", action="store_true", help="run only the data-parallel training step (profiling)")
+    ap.add_argument("--train-steps", type=int, default=20)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -334,7 +362,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from flutter_ml_b200 import _lib, ops
+    from flutter_ml_b200 import _lib, dp, ops
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
@@ -356,8 +384,8 @@ def main():
     peaks = measured_peaks()
     ctx = _lib.Context(device=local_rank, precision=_lib.PREC_TF32)
     if args.train_only:
-        from flutter_ml_b200 import train_bench
-        res = train_bench.run(ctx, rank, world, barrier, max_over_ranks, steps=max(1, min(args.steps, 3)), warmup=1)
+        import bench_train
+        res = bench_train.run(ctx, rank, world, barrier, max_over_ranks, steps=max(1, args.train_steps), warmup=3)
         if rank == 0:
             print(json.dumps({"train": res}), flush=True)
         ctx.close()
@@ -365,8 +393,8 @@ def main():
             dist.destroy_process_group()
         return
     if args.configs_only:
-        from flutter_ml_b200 import config_bench
-        print(json.dumps({"configs": config_bench.run(ctx, args.config)}), flush=True)
+        import bench_configs
+        print(json.dumps({"configs": bench_configs.run(ctx, args.config)}), flush=True)
         ctx.close()
         return
     if args.attention_only:
@@ -380,12 +408,25 @@ def main():
         return
     M = N = K = args.size
     flops_step = 6.0 * M * N * K
-    host = ops.DenseFwdBwdHost(ctx, M, N, K, act="gelu")
-    for name, arr in zip(("A", "B", "bias", "dC"), make_inputs(M, N, K)):
+    # N > 1: the exchange of the weight gradient gets its own communicator (a few CTAs) and the SMs the dA product leaves it
+    exchange = None
+    if world > 1:
+        dp.init_data_parallel(ctx, dist, rank, world, device="cuda", max_ctas=args.nccl_ctas)
+        exchange = ops.GradientExchange(ctx, world, lane=2, reserve_sms=args.reserve_sms)
+    host = ops.DenseFwdBwdHost(ctx, M, N, K, act="gelu", exchange=exchange)
+    seeds = make_inputs(M, N, K)
+    if world > 1:   # every rank has its own rows of the batch (A, dC); weights and bias are replicated
+        from flutter_ml_b200 import synth
+        sc = 1.0 / np.sqrt(K)
+        seeds = (synth.normal(1, 10 + rank, (M, K), sc), seeds[1], seeds[2], synth.normal(1, 30 + rank, (M, N), sc))
+    for name, arr in zip(("A", "B", "bias", "dC"), seeds):
         host.h_in[name][...] = arr
+    del seeds
     host()  # uploads the operands once; they stay resident for the device-timed loop
 
-    # ---- device-resident loop: per-launch events around the three GEMMs of the first steps
+    # ---- device-resident loop: R timed regions of K steps each (every region between a barrier and a synchronize on
+    # both sides); the headline is the MEDIAN region, and every region carries the SM clock sampled inside it
+    repeats = args.repeats or max(1, min(10, int(2000.0 / max(args.steps * 5.5, 1.0))))
     sampler = ClockSampler(local_rank)
     sampler.start()
     for _ in range(args.warmup):
@@ -393,50 +434,62 @@ def main():
     barrier()
     sampler.mark_begin()
     launches0 = ctx.launches
-    # per-launch events around the GEMMs of 10 steps spread evenly over the timed region (clocks settle
-    # during the first fraction of a second, so the first steps alone would flatter the kernel)
-    n_ev_steps = min(args.steps, 10)
-    ev_at = {int(i * args.steps / n_ev_steps): i for i in range(n_ev_steps)}
-    ctx.timer_start()
-    for step_i in range(args.steps):
-        if step_i in ev_at:
-            s = ev_at[step_i]
-            c = ctx
-            c.event_record(6 * s + 0)
-            ops.dense_forward(c, host.A, host.B, host.bias, "gelu", M, N, K, host.C, host.Z)
-            c.event_record(6 * s + 1)
-            c.zero(host.dbias)
-            c.call("fml_act_bwd", _lib.ACT_GELU, host.Z, host.dC, host.dZ, M, N, 0, host.dbias)
-            c.event_record(6 * s + 2)
-            c.gemm(host.dZ, host.B, host.dA, M, K, N, transB=True)
-            c.event_record(6 * s + 3)
-            c.gemm(host.A, host.dZ, host.dB, K, N, M, transA=True)
-            c.event_record(6 * s + 4)
-        else:
-            host.compute()
-    ms_total = ctx.timer_stop_ms()
-    barrier()
+    regions, n_ev_steps = [], min(args.steps, 10)
+    for rep in range(repeats):
+        barrier()
+        t_host0 = time.time()
+        ev_at = {int(i * args.steps / n_ev_steps): i for i in range(n_ev_steps)} if rep == 0 else {}
+        ctx.timer_start()
+        for step_i in range(args.steps):
+            if step_i in ev_at:
+                # per-launch events around the three products of 10 steps spread over the first region
+                sl, c = ev_at[step_i], ctx
+                c.event_record(6 * sl + 0)
+                ops.dense_forward(c, host.A, host.B, host.bias, "gelu", M, N, K, host.C, host.Z)
+                c.event_record(6 * sl + 1)
+                c.zero(host.dbias)
+                c.call("fml_act_bwd", _lib.ACT_GELU, host.Z, host.dC, host.dZ, M, N, 0, host.dbias)
+                c.event_record(6 * sl + 2)
+                c.gemm(host.A, host.dZ, host.dB, K, N, M, transA=True)
+                c.event_record(6 * sl + 3)
+                if exchange:
+                    exchange.start(host.grads, host.grads.size)
+                c.gemm(host.dZ, host.B, host.dA, M, K, N, transB=True)
+                c.event_record(6 * sl + 4)
+                if exchange:
+                    exchange.join()
+            else:
+                host.compute()
+        ms = ctx.timer_stop_ms()
+        barrier()
+        regions.append({"ms_per_step": max_over_ranks(ms) / args.steps, "t0": t_host0, "t1": time.time()})
     sampler.mark_end()
     clocks = sampler.stop()
-    launches = ctx.launches - launches0
-    ms_total = max_over_ranks(ms_total)
-    ms_step = ms_total / args.steps
+    launches = (ctx.launches - launches0) // repeats
+    for r in regions:
+        r["sm_mhz"] = sampler.window_mhz(r.pop("t0"), r.pop("t1"))
+        r["ms_per_step"] = round(r["ms_per_step"], 4)
+        r["ms_x_ghz"] = round(r["ms_per_step"] * r["sm_mhz"] / 1e3, 4) if r["sm_mhz"] else None
+    ms_step = statistics.median(r["ms_per_step"] for r in regions)
     value = world * flops_step / ms_step / 1e9
     gemm_ms = []
-    for s in range(n_ev_steps):
-        gemm_ms += [ctx.event_elapsed_ms(6 * s, 6 * s + 1), ctx.event_elapsed_ms(6 * s + 2, 6 * s + 3),
-                    ctx.event_elapsed_ms(6 * s + 3, 6 * s + 4)]
-    gemm_avg = sum(gemm_ms) / len(gemm_ms)
+    for sl in range(n_ev_steps):
+        gemm_ms += [ctx.event_elapsed_ms(6 * sl, 6 * sl + 1), ctx.event_elapsed_ms(6 * sl + 2, 6 * sl + 3),
+                    ctx.event_elapsed_ms(6 * sl + 3, 6 * sl + 4)]
+    # with an exchange running beside it the dA product is not a kernel-alone figure: the roofline uses fwd and dW then
+    alone = [m for i, m in enumerate(gemm_ms) if world == 1 or i % 3 != 2]
+    gemm_avg = sum(alone) / len(alone)
     achieved = 2.0 * M * N * K / gemm_avg / 1e9
-    long_run = ms_total > 1000.0
+    long_run = ms_step * args.steps > 1000.0
     tf32_peak = (peaks["bf16_sustained"] if long_run else peaks["bf16_burst"]) / 2.0
     roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel", "achieved": round(achieved, 1), "peak": round(tf32_peak, 1),
-                "unit": "TFLOP/s", "frac": round(achieved / tf32_peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(M),
+                "unit": "TFLOP/s", "frac": round(achieved / tf32_peak, 4), "traffic": ncu_dram_bytes_per_launch(M),
                 "algorithmic_bytes": 4 * (M * K + K * N + M * N),
                 "peak_source": f"{peaks['source']}: MEASURED_PEAKS bf16 {'sustained' if long_run else 'burst'} / 2 "
                                "(dense TF32 runs at half the bf16 rate; no TF32 figure is measured by the driver)",
-                "per_gemm_ms": {"fwd": round(statistics.mean(gemm_ms[0::3]), 4), "dA": round(statistics.mean(gemm_ms[1::3]), 4),
-                                "dW": round(statistics.mean(gemm_ms[2::3]), 4)}}
+                "frac_of_nominal_tf32": round(achieved / NOMINAL_TF32_TFLOPS, 4),
+                "per_gemm_ms": {"fwd": round(statistics.mean(gemm_ms[0::3]), 4), "dW": round(statistics.mean(gemm_ms[1::3]), 4),
+                                "dA" + (" (exchange beside it)" if world > 1 else ""): round(statistics.mean(gemm_ms[2::3]), 4)}}
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region.
     # Serial form (upload, kernels, download one after the other) and pipelined form (copies on two
@@ -452,33 +505,45 @@ def main():
     barrier()
     ctx.timer_start()
     host.pipelined(e2e_steps)
-    e2e_ms = ctx.timer_stop_ms()
+    e2e_ms_rank = ctx.timer_stop_ms() / e2e_steps
     barrier()
-    e2e_ms = max_over_ranks(e2e_ms) / e2e_steps
+    e2e_ms = max_over_ranks(e2e_ms_rank)
     e2e = {"value": round(world * flops_step / e2e_ms / 1e9, 2), "unit": "TFLOP/s", "ms_per_step": round(e2e_ms, 3),
            "h2d_bytes_per_step": host.h2d_bytes, "d2h_bytes_per_step": host.d2h_bytes, "steps": e2e_steps,
            "serial_ms_per_step": round(serial_ms, 3),
            "pcie_gbs_each_way": round(host.h2d_bytes / e2e_ms / 1e6, 1)}
+    if world > 1:   # every rank's own figure: the host side (one NUMA node, one memory system) is shared by all ranks
+        t = torch.zeros(world, dtype=torch.float64, device="cuda")
+        t[rank] = e2e_ms_rank
+        dist.all_reduce(t)
+        e2e["ms_per_step_by_rank"] = [round(float(x), 2) for x in t.tolist()]
+        e2e["note"] = ("all GPUs of the box hang off one NUMA node (nvidia-smi topo: CPU affinity 0-31, NUMA 0 for every GPU), so "
+                       "there is no closer memory to bind a rank's staging buffers to; the ranks share the host's copy bandwidth")
 
+    par = (f"data parallel x{world}: {M} rows per GPU, weights replicated, fp32 all-reduce of dW+dbias "
+           f"({host.grads.size * 4 // 2 ** 20} MiB) per step on a side stream beside the dA product") if world > 1 else "single GPU"
     line = {"metric": "gemm_fwd_bwd_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
             "config": {"workload": f"dense fwd+bwd (bias+GELU epilogue, dZ+dbias, dA, dW), fp32, M=N=K={M}", "seed": 1,
                        "l2": "operands (3 x %d MB) exceed the 126 MB L2; no flush needed" % (M * K * 4 // 2 ** 20),
-                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU"},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+                       "parallelism": par,
+                       "timed": f"median of {repeats} regions of {args.steps} steps, each between barrier+synchronize"},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "regions": regions,
             "frac_of_tf32_peak": round(value / world / tf32_peak, 4)}
+    if world > 1:
+        line["exchange"] = {"bytes_per_step": host.grads.size * 4, "nccl_max_ctas": args.nccl_ctas, "reserved_sms": args.reserve_sms}
 
     if rank == 0 and not args.no_sweep:
         line["sweep"] = time_sweep(ctx)
-    if rank == 0 and not args.no_sweep:
         try:
             line["calibration"] = cublas_tf32_yardstick()
+            line["roofline"]["frac_of_library_tf32_same_box"] = round(achieved / line["calibration"]["tflops"], 4)
         except Exception as exc:  # the yardstick must never break the benchmark
             line["calibration"] = {"error": str(exc)[:200]}
     if rank == 0 and not args.no_configs:
-        from flutter_ml_b200 import config_bench
-        line["configs"] = config_bench.run(ctx)
+        import bench_configs
+        line["configs"] = bench_configs.run(ctx)
         if local_rank == 0:  # the legacy symbol owns a context on device 0
             line["legacy_roundtrip"] = legacy_roundtrip()
     if rank == 0 and not args.no_membound:
@@ -491,12 +556,13 @@ def main():
         sec = cpu_step(S, S, S, False)
         line["cpu_baseline"] = {"value": 6.0 * S ** 3 / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
                                 "sample": f"M=N=K={S} fwd+bwd once ({sec:.1f} s), float64 scalar loops, 1 thread"}
+    del host
     if not args.no_train:
-        try:
-            from flutter_ml_b200 import train_bench
-            line["train"] = train_bench.run(ctx, rank, world, barrier, max_over_ranks)
-        except ImportError:
-            pass
+        if world > 1:
+            ctx.check(ctx.lib.fml_dp_shutdown(ctx.h))   # the training step makes its own communicator (NCCL's CTA choice)
+            ctx.check(ctx.lib.fml_dp_set_max_ctas(ctx.h, 0))
+        import bench_train
+        line["train"] = bench_train.run(ctx, rank, world, barrier, max_over_ranks, steps=max(1, args.train_steps))
     if rank == 0:
         print(json.dumps(line), flush=True)
     ctx.close()

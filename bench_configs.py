@@ -7,9 +7,9 @@ import ctypes
 
 import numpy as np
 
-from . import _lib, models, synth
-from . import tensor as T
-from .tensor import Tensor
+from flutter_ml_b200 import _lib, models, synth
+from flutter_ml_b200 import tensor as T
+from flutter_ml_b200.tensor import Tensor
 
 
 def _timed(ctx, fn, warm=2, reps=5):
@@ -43,7 +43,7 @@ def config1_mlp(ctx):
 
 def _feed_arms(ctx, mlp, X, y, B):
     """(prefetching feeder, blocking upload per step) in ms per step of batch B over the host arrays X, y."""
-    from .feeder import BatchFeeder
+    from flutter_ml_b200.feeder import BatchFeeder
     batches = X.shape[0] // B
     feeder = BatchFeeder(ctx, [X, y], B)
     for xb, yb in feeder.batches():      # warm-up epoch
@@ -75,7 +75,7 @@ def _config1_fed(ctx, mlp):
            "blocking_upload_us_per_step": round(blk_ms * 1e3, 1), "fed_h2d_bytes_per_step": 64 * 785 * 4}
     # fed + graph replay: one recorded step per device batch buffer of the feeder, replayed alternately, so a step
     # from host memory costs two library calls (events) and one graph launch
-    from .feeder import BatchFeeder
+    from flutter_ml_b200.feeder import BatchFeeder
     feeder = BatchFeeder(ctx, [X, y], 64)
     for b in range(2):                   # recording runs the step once eagerly: give it defined inputs
         ctx.zero(feeder.device[b][0])
@@ -101,8 +101,8 @@ def _config1_fed(ctx, mlp):
 def _config1_tape(ctx):
     """The same step as a node list for the tape executor: three `dense` nodes + softmax cross-entropy, one library
     call per sweep (forward, backward) and one for SGD over the six parameters' flat arena."""
-    from .optimizers import ParameterArena
-    from .tape import Tape
+    from flutter_ml_b200.optimizers import ParameterArena
+    from flutter_ml_b200.tape import Tape
     tp = Tape(ctx)
     P = [tp.tensor(p) for p in models.init_mlp(0)]
     h = tp.tensor(synth.uniform(0, 0, (64, 784)), requires_grad=False)
@@ -124,7 +124,7 @@ def _config1_tape(ctx):
 def config3_encoder_block(ctx):
     """Post-LN encoder block d512 h8 dff2048, seq 256, batch 32, causal, forward + backward."""
     d, heads, dff, S, B = 512, 8, 2048, 256, 32
-    from .layers import TransformerEncoderBlock
+    from flutter_ml_b200.layers import TransformerEncoderBlock
     block = TransformerEncoderBlock(d, heads, dff, seq_len=S, causal=True, params=models.init_block(2, d, heads, dff))
     x = ctx.upload(synth.normal(2, 500, (B * S, d)))
     tgt = Tensor(ctx.upload(synth.normal(2, 501, (B * S, d))), ctx)

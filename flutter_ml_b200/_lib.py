@@ -67,6 +67,7 @@ PROTOTYPES = {
     "fml_device_count": [C.POINTER(i32)],
     "fml_device_name": [i32, C.c_char_p, i32],
     "fml_sm_count": [fp, C.POINTER(i32)],
+    "fml_set_sm_reserve": [fp, i32],
     "fml_set_stream": [fp, fp],
     "fml_sync": [fp],
     "fml_device_status": [fp, C.POINTER(i32)],
@@ -145,6 +146,7 @@ PROTOTYPES = {
     "fml_dp_unique_id": [C.c_char_p],
     "fml_dp_init": [fp, C.c_char_p, i32, i32],
     "fml_dp_set_timeout": [fp, i32],
+    "fml_dp_set_max_ctas": [fp, i32],
     "fml_dp_allreduce_sum": [fp, fp, i64],
     "fml_dp_allreduce_sum_on": [fp, i32, fp, i64],
     "fml_dp_shutdown": [fp],

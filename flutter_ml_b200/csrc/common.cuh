@@ -29,9 +29,10 @@ struct fml_ctx {
   std::unordered_set<void*> allocs;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   cudaEvent_t ev_pool[64] = {};
-  cudaStream_t lanes[2] = {nullptr, nullptr};  // copy streams, created on first use
+  cudaStream_t lanes[4] = {nullptr, nullptr, nullptr, nullptr};  // side streams (copies, exchange), created on first use
   std::vector<cudaGraphExec_t> graphs;         // instantiated graphs, index = graph id
   bool capturing = false;
+  int sm_reserve = 0;  // SMs the persistent tensor-core kernels leave free (fml_set_sm_reserve)
   int last_gemm_path = 0;
   int last_gemm_tile[4] = {0, 0, 0, 0};  // of the last tensor-core launch: CTAs per tile (1 or 2), tile columns, K splits, K chunks
   // tensor-map cache: key -> encoded CUtensorMap
@@ -39,6 +40,7 @@ struct fml_ctx {
   // NCCL (loaded lazily with dlopen)
   void* nccl_comm = nullptr;
   int dp_rank = 0, dp_world = 1;
+  int dp_max_ctas = 0;         // upper limit on the CTAs of a collective (0: NCCL's choice)
   int dp_timeout_ms = 120000;  // host-side limit for communicator creation and for enqueueing a collective
 };
 

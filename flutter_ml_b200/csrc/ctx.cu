@@ -169,6 +169,12 @@ int32_t fml_sm_count(fml_ctx* ctx, int32_t* count) {
   return FML_OK;
 }
 
+int32_t fml_set_sm_reserve(fml_ctx* ctx, int32_t sms) {
+  FML_REQUIRE(ctx, ctx && sms >= 0 && sms < ctx->sm_count - 1, "fml_set_sm_reserve: must leave at least two SMs for the kernels");
+  ctx->sm_reserve = sms;
+  return FML_OK;
+}
+
 int32_t fml_set_stream(fml_ctx* ctx, void* s) {
   FML_ENTER(ctx);
   FML_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -319,7 +325,7 @@ int32_t fml_event_elapsed_ms(fml_ctx* ctx, int32_t a, int32_t b, float* ms) {
 }
 
 static int32_t lane_stream(fml_ctx* ctx, int32_t lane, cudaStream_t* out) {
-  FML_REQUIRE(ctx, lane >= 0 && lane < 2, "copy lane must be 0 or 1");
+  FML_REQUIRE(ctx, lane >= 0 && lane < 4, "copy lane must be 0 .. 3");
   if (!ctx->lanes[lane]) FML_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->lanes[lane], cudaStreamNonBlocking));
   *out = ctx->lanes[lane];
   return FML_OK;

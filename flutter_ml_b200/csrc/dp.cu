@@ -33,6 +33,7 @@ struct NcclApi {
   AllReduceFn all_reduce = nullptr;
   CommFn comm_destroy = nullptr;
   CommFn comm_abort = nullptr;
+  CommFn comm_finalize = nullptr;
   AsyncErrorFn async_error = nullptr;
   GetErrorStringFn error_string = nullptr;
 };
@@ -51,6 +52,7 @@ NcclApi* nccl() {
       api.all_reduce = (AllReduceFn)dlsym(api.handle, "ncclAllReduce");
       api.comm_destroy = (CommFn)dlsym(api.handle, "ncclCommDestroy");
       api.comm_abort = (CommFn)dlsym(api.handle, "ncclCommAbort");
+      api.comm_finalize = (CommFn)dlsym(api.handle, "ncclCommFinalize");
       api.async_error = (AsyncErrorFn)dlsym(api.handle, "ncclCommGetAsyncError");
       api.error_string = (GetErrorStringFn)dlsym(api.handle, "ncclGetErrorString");
     }
@@ -120,6 +122,13 @@ int32_t fml_dp_set_timeout(fml_ctx* ctx, int32_t timeout_ms) {
   return FML_OK;
 }
 
+int32_t fml_dp_set_max_ctas(fml_ctx* ctx, int32_t ctas) {
+  FML_REQUIRE(ctx, ctx && ctas >= 0 && ctas <= 64, "fml_dp_set_max_ctas: 0 (NCCL's choice) .. 64");
+  FML_REQUIRE(ctx, !ctx->nccl_comm, "fml_dp_set_max_ctas: call it before fml_dp_init");
+  ctx->dp_max_ctas = ctas;
+  return FML_OK;
+}
+
 int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id_bytes[128], int32_t rank, int32_t world) {
   FML_ENTER(ctx);
   FML_REQUIRE(ctx, world >= 1 && rank >= 0 && rank < world, "fml_dp_init: bad rank/world");
@@ -133,6 +142,7 @@ int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id_bytes[128], int32_t rank, int
   memcpy(id.internal, id_bytes, 128);
   ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
   cfg.blocking = 0;
+  if (ctx->dp_max_ctas > 0) cfg.maxCTAs = ctx->dp_max_ctas;  // keep the collective to the SMs set aside for it
   ncclComm_t comm = nullptr;
   ncclResult_t rc = a->comm_init_rank_config(&comm, world, id, rank, &cfg);
   ctx->nccl_comm = comm;
@@ -167,7 +177,16 @@ int32_t fml_dp_shutdown(fml_ctx* ctx) {
   FML_ENTER(ctx);
   if (ctx->nccl_comm) {
     NcclApi* a = nccl();
-    if (a) a->comm_destroy((ncclComm_t)ctx->nccl_comm);
+    if (a) {
+      // a non-blocking communicator is finalised first (flushes what was issued), polled until that has happened
+      // (settle aborts it instead when the limit passes), then destroyed
+      bool alive = true;
+      if (a->comm_finalize) {
+        ncclResult_t rc = a->comm_finalize((ncclComm_t)ctx->nccl_comm);
+        if (rc == ncclSuccess || rc == ncclInProgress) alive = settle(ctx, "fml_dp_shutdown (ncclCommFinalize)") == FML_OK;
+      }
+      if (alive && ctx->nccl_comm) a->comm_destroy((ncclComm_t)ctx->nccl_comm);
+    }
     ctx->nccl_comm = nullptr;
   }
   ctx->dp_world = 1;

@@ -103,7 +103,7 @@ struct TcParams {
   const float* rowop_aux;
   int lstm;     // 1: LSTM gate epilogue (see fml_lstm_epilogue); C is not written
   fml_lstm_epilogue le;
-  int debug;  // diagnostics only: 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
+  int debug;  // diagnostics builds only (-DFML_GEMM_DIAGNOSTICS): 1 = producer skips the TMA loads, 2 = issuer skips the MMAs
 };
 
 using namespace fml_tc;
@@ -246,11 +246,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const CUtensorMap* tb = (p.nseg == 3 && seg == 1) ? &tmBlo : &tmB;
           const uint32_t sa = smem_base + s * STAGE_BYTES;
           const uint32_t sb = sa + A_STAGE_BYTES;
+#ifdef FML_GEMM_DIAGNOSTICS
           if (p.debug & 1) {
             if (rank == 0) mbar_arrive(full_bar(s));
             if (++s == STAGES) { s = 0; ph ^= 1; }
             continue;
           }
+#endif
           if (rank == 0) mbar_expect_tx(full_bar(s), CTAS * (A_STAGE_BYTES + b_stage_bytes));
           auto load = [&](uint32_t dst, const CUtensorMap* tmap, int c0, int c1) {
             if (PAIR) tma_load_4d_pair(dst, tmap, full_bar(s), c0, c1, b1, b2);
@@ -310,12 +312,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sb = sa + A_STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(sa, a_lbo, p.a_mn ? 512u : 1024u, p.a_mn ? 1u : 2u);
           const uint64_t bdesc = make_smem_desc(sb, b_lbo, p.b_mn ? 512u : 1024u, p.b_mn ? 1u : 2u);
+#ifdef FML_GEMM_DIAGNOSTICS
           if (p.debug & 2) {
             if (PAIR) mbar_arrive_remote(empty_bar(s), 1);
             mbar_arrive(empty_bar(s));
             if (++s == STAGES) { s = 0; ph ^= 1; }
             continue;
           }
+#endif
 #pragma unroll
           for (int k = 0; k < BK / 8; k++) {
             const uint64_t ad = adesc + (uint64_t)(k * a_kstep), bd = bdesc + (uint64_t)(k * b_kstep);
@@ -982,6 +986,8 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   p.act = d->act; p.alpha = d->alpha; p.beta = d->beta;
   p.status = ctx->d_status;
   p.idesc = make_idesc(tile_m, BN, a_mn, b_mn);
+  p.debug = 0;
+#ifdef FML_GEMM_DIAGNOSTICS  // a build with -DFML_GEMM_DIAGNOSTICS can skip the loads or the MMAs (FML_GEMM_DEBUG=1|2) to time the other half
   {
     static int dbg = -1;
     if (dbg < 0) {
@@ -990,11 +996,14 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     }
     p.debug = dbg;
   }
+#endif
   const long long num_tiles = (long long)tiles_m * tiles_n * nb1 * nb2 * p.ksplit;  // work units
+  // SMs this persistent launch may occupy: all of them, less the ones set aside for a collective that runs beside it
+  const int grid_sms = std::max(2, ctx->sm_count - ctx->sm_reserve);
   if (p.kchunk < p.kb_per_split) {
     // slabs live behind whatever the 3xTF32 split already placed in the arena
-    const size_t grid_ctas = pair ? 2 * (size_t)std::min<long long>(num_tiles, ctx->sm_count / 2)
-                                  : (size_t)std::min<long long>(num_tiles, ctx->sm_count);
+    const size_t grid_ctas = pair ? 2 * (size_t)std::min<long long>(num_tiles, grid_sms / 2)
+                                  : (size_t)std::min<long long>(num_tiles, grid_sms);
     const size_t slab_bytes = grid_ctas * BM * 256 * sizeof(float);
     const size_t off = (split_bytes + 1023) & ~(size_t)1023;
     // with a split queued on the stream the arena must stay where it is (it was sized for the slabs above)
@@ -1018,7 +1027,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
   cfg.stream = ctx->stream;
   cfg.attrs = attr;
   if (pair) {
-    const int clusters = (int)std::min<long long>(num_tiles, ctx->sm_count / 2);
+    const int clusters = (int)std::min<long long>(num_tiles, grid_sms / 2);
     cfg.gridDim = dim3(2 * clusters);
     cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
     attr[na].id = cudaLaunchAttributeClusterDimension;
@@ -1029,7 +1038,7 @@ int32_t fml_gemm_tc(fml_ctx* ctx, const fml_gemm_desc* d, int precision, const f
     cfg.numAttrs = na;
     FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, tmA, tmB, tmAlo, tmBlo, p));
   } else {
-    const int grid = (int)std::min<long long>(d->rowop ? num_tiles / tiles_n : num_tiles, ctx->sm_count);
+    const int grid = (int)std::min<long long>(d->rowop ? num_tiles / tiles_n : num_tiles, grid_sms);
     cfg.gridDim = dim3(grid);
     cfg.dynamicSmemBytes = Cfg<false>::SMEM_BYTES;
     cfg.numAttrs = na;

@@ -30,9 +30,12 @@ def broadcast_unique_id(dist, make_id: Callable[[], bytes], device="cpu") -> byt
     return bytes(buf.cpu().tolist())
 
 
-def init_data_parallel(ctx, dist, rank: int, world: int, device="cpu"):
-    """Create the NCCL communicator of `ctx` (no-op for a single rank)."""
+def init_data_parallel(ctx, dist, rank: int, world: int, device="cpu", max_ctas: int = 0):
+    """Create the NCCL communicator of `ctx` (no-op for a single rank).  `max_ctas` > 0 limits the SMs a collective
+    occupies, for exchanges that run beside persistent kernels (see Context.set_sm_reserve)."""
     import ctypes
+    if max_ctas:
+        ctx.check(ctx.lib.fml_dp_set_max_ctas(ctx.h, int(max_ctas)))
     if world == 1:
         ctx.check(ctx.lib.fml_dp_init(ctx.h, bytes(128), 0, 1))
         return

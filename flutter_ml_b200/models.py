@@ -171,18 +171,25 @@ class TransformerLM:
         end = offs[first_param + n_params] if first_param + n_params < len(offs) else self.arena.size
         return offs[first_param], end - offs[first_param]
 
-    def _exchange(self, off: int, n: int):
+    def _exchange(self, off: int, n: int, update: bool = False):
         """Sum one finished slice of the gradient arena across ranks on the communication lane, after
-        everything queued so far on the main stream."""
+        everything queued so far on the main stream; with `update`, apply Adam to that slice (and clear its
+        gradient) on the same lane right behind the exchange."""
         c = self.ctx
         c.check(c.lib.fml_event_record_on(c.h, 50, -1))
         c.check(c.lib.fml_wait_event(c.h, 0, 50))
-        c.check(c.lib.fml_dp_allreduce_sum_on(c.h, 0, self.arena.grads.ptr + 4 * off, n))
+        if self.world > 1:
+            c.check(c.lib.fml_dp_allreduce_sum_on(c.h, 0, self.arena.grads.ptr + 4 * off, n))
+        if update:
+            self.optimizer.step_slice(off, n, lane=0, zero_grad=True)
 
-    def forward_backward(self, ids, labels, n_global_tokens: int, keep_logits: bool = False, overlap_exchange: bool = False):
+    def forward_backward(self, ids, labels, n_global_tokens: int, keep_logits: bool = False, overlap_exchange: bool = False,
+                         fused_update: bool = False):
         """ids, labels: int32 DeviceArrays [n_seq * seq_len] of this rank's shard.  With
         `overlap_exchange` the all-reduce of each finished slice of the gradient arena (head, then the
-        blocks from last to first, then the embedding) runs on a side stream under the rest of backward."""
+        blocks from last to first, then the embedding) runs on a side stream under the rest of backward;
+        with `fused_update` the Adam update of each slice follows its exchange on that stream, so that only the
+        embedding table's exchange and update remain after the last backward kernel."""
         ctx = self.ctx
         h = self.embedding(ids)
         inputs = []
@@ -192,12 +199,13 @@ class TransformerLM:
         inputs.append(h)
         logits = self.head(h)
         before = None
-        if overlap_exchange and self.world > 1:
+        if fused_update or (overlap_exchange and self.world > 1):
             per_block = len(self.blocks[0].parameters)
             L = len(self.blocks)
-            before = {id(inputs[L]): (lambda: self._exchange(*self._slice(1 + L * per_block, 2)))}
+            ex = lambda first, count: self._exchange(*self._slice(first, count), update=fused_update)  # noqa: E731
+            before = {id(inputs[L]): (lambda: ex(1 + L * per_block, 2))}
             for i in range(L - 1, -1, -1):
-                before[id(inputs[i])] = (lambda i=i: self._exchange(*self._slice(1 + i * per_block, per_block)))
+                before[id(inputs[i])] = (lambda i=i: ex(1 + i * per_block, per_block))
         kept = None
         if keep_logits:
             kept = ctx.empty(*logits.shape)
@@ -205,19 +213,31 @@ class TransformerLM:
         loss = T.softmaxCrossEntropy(logits, labels, 1.0 / n_global_tokens, bias_grad=True)
         loss.backward(before=before)
         if before:
-            self._exchange(*self._slice(0, 1))              # the embedding table's gradient, last
+            self._exchange(*self._slice(0, 1), update=fused_update)   # the embedding table's gradient, last
             c = self.ctx
             c.check(c.lib.fml_event_record_on(c.h, 51, 0))  # main stream continues once the lane is done
             c.check(c.lib.fml_wait_event(c.h, -1, 51))
         return loss, kept
 
     def train_step(self, ids, labels, n_global_tokens: int, overlap_exchange: bool = True):
-        loss, _ = self.forward_backward(ids, labels, n_global_tokens, overlap_exchange=overlap_exchange)
-        if self.world > 1 and not overlap_exchange:
+        """One step: forward, loss, backward, exchange, Adam, zeroGrad (lib/nets/snet.dart:74-85).  With
+        `overlap_exchange` (the default) the exchange and the update run slice by slice on the side stream."""
+        if overlap_exchange:
+            self.optimizer.begin_step()
+            loss, _ = self.forward_backward(ids, labels, n_global_tokens, overlap_exchange=True, fused_update=True)
+            return loss
+        loss, _ = self.forward_backward(ids, labels, n_global_tokens)
+        if self.world > 1:
             self.ctx.call("fml_dp_allreduce_sum", self.arena.grads, self.arena.size)
         self.optimizer.step()
         self.optimizer.zeroGrad()
         return loss
+
+    def check_values(self):
+        """(gradient-independent) figures that every rank count must reproduce after a step: the L2 norm and a
+        position-weighted checksum of the parameter arena, computed on the host in float64."""
+        w = self.arena.values.numpy().astype(np.float64)
+        return {"param_norm": float(np.sqrt(np.sum(w * w))), "param_checksum": float(np.sum(w * ((np.arange(w.size) % 251) + 1.0)))}
 
     def grads_in_reference_order(self):
         out = [self.embedding.embeddings.grad.numpy()]

@@ -19,22 +19,55 @@ def dense_forward(ctx, X, W, b, act, M, N, K, Y, Z=None, precision=-1):
 
 
 def dense_backward(ctx, X, W, saved, dY, act, M, N, K, dZ, dX=None, dW=None, db=None, accumulate=False,
-                   precision=-1):
+                   precision=-1, after_dW=None):
     """Gradients of dense_forward.  saved = Z for relu/gelu, Y for sigmoid/tanh.
     dZ = dY * act'(saved) and db = column sums (tensor.dart:1030, 698-704), then
     dX (+)= dZ.W^T (tensor.dart:918-924) and dW (+)= X^T.dZ (:935-941); the transposes are operand
-    layout flags, nothing is copied.  db must be zeroed by the caller unless it accumulates."""
+    layout flags, nothing is copied.  db must be zeroed by the caller unless it accumulates.  The weight gradient is
+    queued first; `after_dW()` (if given) runs on the host right behind it, which is where a data-parallel caller starts
+    the exchange of dW and db so that it overlaps the dX product."""
     code = ACT_BY_NAME[act]
     if code == _lib.ACT_NONE and db is None:
         dZ = dY
     else:
         ctx.call("fml_act_bwd", code, saved, dY, dZ, M, N, 0, db)
     beta = 1.0 if accumulate else 0.0
-    if dX is not None:
-        ctx.gemm(dZ, W, dX, M, K, N, transB=True, beta=beta, precision=precision)
     if dW is not None:
         ctx.gemm(X, dZ, dW, K, N, M, transA=True, beta=beta, precision=precision)
+    if after_dW is not None:
+        after_dW()
+    if dX is not None:
+        ctx.gemm(dZ, W, dX, M, K, N, transB=True, beta=beta, precision=precision)
     return dZ
+
+
+class GradientExchange:
+    """Data-parallel exchange of a layer's weight and bias gradient, overlapped with the product that follows: the
+    all-reduce (sum over ranks, NCCL) is enqueued on side stream `lane` behind everything queued so far, the persistent
+    products that run beside it leave `reserve_sms` SMs free for it, and `join` makes the main stream wait for it."""
+
+    def __init__(self, ctx, world: int, lane: int = 2, reserve_sms: int = 0, ev_start: int = 56, ev_done: int = 57):
+        self.ctx, self.world, self.lane, self.reserve = ctx, world, lane, reserve_sms
+        self.ev_start, self.ev_done = ev_start, ev_done
+
+    def start(self, buf, n):
+        if self.world == 1:
+            return
+        c, L = self.ctx, self.ctx.lib
+        c.check(L.fml_event_record_on(c.h, self.ev_start, -1))
+        c.check(L.fml_wait_event(c.h, self.lane, self.ev_start))
+        c.check(L.fml_dp_allreduce_sum_on(c.h, self.lane, buf.ptr, n))
+        c.check(L.fml_event_record_on(c.h, self.ev_done, self.lane))
+        if self.reserve:
+            c.check(L.fml_set_sm_reserve(c.h, self.reserve))
+
+    def join(self):
+        if self.world == 1:
+            return
+        c, L = self.ctx, self.ctx.lib
+        if self.reserve:
+            c.check(L.fml_set_sm_reserve(c.h, 0))
+        c.check(L.fml_wait_event(c.h, -1, self.ev_done))
 
 
 class DenseFwdBwdHost:
@@ -42,23 +75,33 @@ class DenseFwdBwdHost:
     binding is used (lib/cuda/cudacaller.dart:25-60: host lists in, host list out), but with
     device buffers and pinned staging kept between calls."""
 
-    def __init__(self, ctx, M, N, K, act="gelu", precision=-1):
+    def __init__(self, ctx, M, N, K, act="gelu", precision=-1, exchange=None):
         self.ctx, self.M, self.N, self.K, self.act, self.precision = ctx, M, N, K, act, precision
+        self.exchange = exchange     # GradientExchange or None: sums dB and dbias over the data-parallel ranks
         e = ctx.empty
         self.A, self.B, self.bias, self.dC = e(M, K), e(K, N), e(N), e(M, N)
-        self.C, self.Z, self.dZ, self.dA, self.dB, self.dbias = e(M, N), e(M, N), e(M, N), e(M, K), e(K, N), e(N)
+        self.C, self.Z, self.dZ, self.dA = e(M, N), e(M, N), e(M, N), e(M, K)
+        self._gb_off = (K * N + 3) & ~3          # bias gradient at a 16-byte aligned offset behind the weight gradient
+        self.grads = e(self._gb_off + N)         # side by side: one exchange
+        self.dB, self.dbias = self.grads.view(0, (K, N)), self.grads.view(self._gb_off, (N,))
         p = ctx.pinned
         self.h_in = {"A": p((M, K)), "B": p((K, N)), "bias": p((N,)), "dC": p((M, N))}
         self.h_out = {"C": p((M, N)), "dA": p((M, K)), "dB": p((K, N)), "dbias": p((N,))}
         self.h2d_bytes = sum(a.nbytes for a in self.h_in.values())
         self.d2h_bytes = sum(a.nbytes for a in self.h_out.values())
 
-    def compute(self):
+    def compute(self, d=None):
+        """Forward, dZ + dbias, dW, [exchange of dW and dbias started], dA, [exchange joined] on buffer set `d`."""
         c = self.ctx
-        dense_forward(c, self.A, self.B, self.bias, self.act, self.M, self.N, self.K, self.C, self.Z, self.precision)
-        c.zero(self.dbias)
-        dense_backward(c, self.A, self.B, self.Z, self.dC, self.act, self.M, self.N, self.K, self.dZ, self.dA, self.dB,
-                       self.dbias, precision=self.precision)
+        d = d or {k: getattr(self, k) for k in ("A", "B", "bias", "dC", "C", "Z", "dZ", "dA", "dB", "dbias", "grads")}
+        dense_forward(c, d["A"], d["B"], d["bias"], self.act, self.M, self.N, self.K, d["C"], d["Z"], self.precision)
+        c.zero(d["dbias"])
+        ex = self.exchange
+        dense_backward(c, d["A"], d["B"], d["Z"], d["dC"], self.act, self.M, self.N, self.K, d["dZ"], d["dA"], d["dB"],
+                       d["dbias"], precision=self.precision,
+                       after_dW=(lambda: ex.start(d["grads"], d["grads"].size)) if ex else None)
+        if ex:
+            ex.join()
 
     def pipelined(self, steps: int):
         """`steps` end-to-end steps with the copies on two side streams and two sets of device buffers,
@@ -68,7 +111,8 @@ class DenseFwdBwdHost:
         if not hasattr(self, "_sets"):
             e, (M, N, K) = c.empty, (self.M, self.N, self.K)
             second = dict(A=e(M, K), B=e(K, N), bias=e(N), dC=e(M, N), C=e(M, N), Z=e(M, N), dZ=e(M, N), dA=e(M, K),
-                          dB=e(K, N), dbias=e(N))
+                          grads=e(self._gb_off + N))
+            second["dB"], second["dbias"] = second["grads"].view(0, (K, N)), second["grads"].view(self._gb_off, (N,))
             first = {k: getattr(self, k) for k in second}
             self._sets = [first, second]
         EV_UP, EV_COMP, EV_DOWN = 40, 42, 44     # event slots, +0/+1 per buffer set
@@ -91,10 +135,7 @@ class DenseFwdBwdHost:
             chk(L.fml_wait_event(c.h, -1, EV_UP + b))
             if s >= 2:
                 chk(L.fml_wait_event(c.h, -1, EV_DOWN + b))  # the download of step s-2 has drained this set
-            dense_forward(c, d["A"], d["B"], d["bias"], self.act, self.M, self.N, self.K, d["C"], d["Z"], self.precision)
-            c.zero(d["dbias"])
-            dense_backward(c, d["A"], d["B"], d["Z"], d["dC"], self.act, self.M, self.N, self.K, d["dZ"], d["dA"], d["dB"],
-                           d["dbias"], precision=self.precision)
+            self.compute(d)
             chk(L.fml_event_record_on(c.h, EV_COMP + b, -1))
             chk(L.fml_wait_event(c.h, 1, EV_COMP + b))
             for k in ("C", "dA", "dB", "dbias"):

@@ -90,6 +90,21 @@ class Adam(Optimizer):
             if p.grad is not None:
                 p.ctx.call("fml_adam_step", p.value, p.grad, m, v, p.value.size, *hp)
 
+    def begin_step(self):
+        """Advance the step counter once (adam.dart:46) before the slices of one step are updated with `step_slice`."""
+        self._t += 1
+
+    def step_slice(self, offset: int, n: int, lane: int = 0, zero_grad: bool = True, grad_scale: float = 1.0):
+        """The update of arena elements [offset, offset + n) enqueued on copy lane `lane`, clearing that part of the
+        gradient in the same pass: lets the update of layers whose gradients are final (and exchanged) run under the
+        backward pass of the layers below them."""
+        a = self.arena
+        sl = lambda buf: buf.ptr + 4 * offset  # noqa: E731
+        a.ctx.check(a.ctx.lib.fml_adam_step_on(a.ctx.h, lane, sl(a.values), sl(a.grads), sl(self._m), sl(self._v), n,
+                                               float(self.learningRate), float(self.beta1), float(self.beta2), float(self.epsilon),
+                                               self._t, float(grad_scale), 1 if zero_grad else 0))
+        a.ctx.launches += 1
+
 
 class _StatefulOptimizer(Optimizer):
     """Shared host side of the optimizers that run through `fml_optimizer_step`: up to three

@@ -69,6 +69,11 @@ const char* fml_last_error(fml_ctx* ctx);
 int32_t fml_device_count(int32_t* count);
 int32_t fml_device_name(int32_t device, char* buf, int32_t buf_len);
 int32_t fml_sm_count(fml_ctx* ctx, int32_t* count);
+/* The persistent tensor-core products launched after this call occupy at most (SM count - sms) SMs.  A gradient
+ * exchange that runs on a side stream beside them needs SMs of its own: a persistent kernel that fills the machine
+ * (one CTA per SM, all of its shared memory) would otherwise hold the collective back until it retires, and nothing
+ * would overlap.  Set it before the products that run under an exchange and back to 0 afterwards. */
+int32_t fml_set_sm_reserve(fml_ctx* ctx, int32_t sms);
 /* Use an existing cudaStream_t (as void*) instead of the context's own. */
 int32_t fml_set_stream(fml_ctx* ctx, void* cuda_stream);
 int32_t fml_sync(fml_ctx* ctx);
@@ -125,7 +130,7 @@ int32_t fml_stage_rows_async(fml_ctx* ctx, void* dst, const void* src, int32_t s
                              const int64_t* index, int64_t first_row, int64_t rows, int32_t threads);
 int32_t fml_stage_wait(fml_ctx* ctx);
 
-/* Copy lanes: two extra streams (lane 0 and 1) for host<->device copies that overlap the kernels
+/* Copy lanes: four extra streams (lanes 0..3) for host<->device copies and gradient exchanges that overlap the kernels
  * on the context's stream (the reference copies synchronously before and after every product,
  * cuda_lib/kernel.cu:23-24,44).  Ordering between the main stream (lane -1) and the lanes is
  * expressed with the numbered events of the pool below: record on one, wait on another. */
@@ -500,6 +505,9 @@ int32_t fml_dp_unique_id(uint8_t out[128]);
  * every fml_dp_allreduce_sum* call (a rank that left between steps), which also reports NCCL's asynchronous errors. */
 int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id[128], int32_t rank, int32_t world);
 int32_t fml_dp_set_timeout(fml_ctx* ctx, int32_t timeout_ms);
+/* Upper limit on the CTAs (SMs) a collective of this context's communicator occupies; call before fml_dp_init.
+ * Together with fml_set_sm_reserve it partitions the SMs between an exchange and the products that run beside it. */
+int32_t fml_dp_set_max_ctas(fml_ctx* ctx, int32_t ctas);
 int32_t fml_dp_allreduce_sum(fml_ctx* ctx, float* buf, int64_t n);
 /* The same on copy lane `lane` (or -1: the main stream), to overlap the exchange of finished gradient
  * slices with the rest of the backward pass; order it against the main stream with the event calls. */

@@ -399,3 +399,30 @@ def test_positional_encoding_layer(orc, n_seq):
     assert rel(out.numpy(), want) <= 1e-6
     assert rel(xt.grad_numpy(), 2 * (want - w64(target)) / want.size) <= 1e-5
     ctx.close()
+
+
+def test_lm_step_with_update_on_the_side_stream_equals_the_plain_step():
+    """The training step that exchanges and updates slice by slice on the side stream (head, blocks last to first,
+    embedding; Adam and zeroGrad fused, under the rest of the backward pass) must leave exactly the parameters, the
+    optimizer state and the cleared gradients that forward, backward, one Adam launch and zeroGrad leave
+    (lib/nets/snet.dart:74-85), over several steps."""
+    from flutter_ml_b200 import _lib, models, synth
+    V, d, heads, dff, L, S, B = 600, 128, 2, 256, 2, 128, 2
+    params = models.init_lm(4, V, d, heads, dff, L, std=0.05)
+    ids, labels = synth.integers(4, 100, (B * S,), V), synth.integers(4, 101, (B * S,), V)
+    res = []
+    for overlap in (False, True):
+        ctx = _lib.Context(precision=_lib.PREC_TF32)
+        lm = models.TransformerLM(ctx, params, S, heads, lr=1e-3)
+        d_ids, d_lab = ctx.upload(ids), ctx.upload(labels)
+        losses = [float(lm.train_step(d_ids, d_lab, B * S, overlap_exchange=overlap).numpy()[0]) for _ in range(3)]
+        ctx.sync()
+        res.append((losses, lm.arena.values.numpy(), lm.optimizer._m.numpy(), lm.optimizer._v.numpy(), lm.arena.grads.numpy()))
+        assert ctx.device_status() == 0
+        ctx.close()
+    (l0, w0, m0, v0, g0), (l1, w1, m1, v1, g1) = res
+    assert l0[2] < l0[0]                                     # it trains
+    # split-K weight gradients add their partial sums with atomics in no fixed order: last-bit differences between runs
+    assert np.allclose(l0, l1, rtol=1e-5)
+    assert rel(w1, w0) <= 1e-4 and rel(m1, m0) <= 1e-4 and rel(v1, v0) <= 1e-4
+    assert not g0.any() and not g1.any()
