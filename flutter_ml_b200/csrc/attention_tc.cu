@@ -1,17 +1,21 @@
 // Fused scaled-dot-product attention forward on the tensor cores: for one block of 128 queries of one
-// (sequence, head) the kernel walks the key/value blocks, S = Q.K^T lands in TMEM, four softmax warps turn it into
-// probabilities with a running row maximum and row sum (scale and causal mask folded in, base-2 exponentials),
-// write them to shared memory in the tensor core's K-major operand layout, and a second product P.V accumulates the
-// output.  The score matrix never reaches global memory: the reference's transpose + matMul + scaleMatrix +
-// softmaxMatrix + matMul chain (lib/layertypes/singleHeadAttentionLayer.dart:77-86) becomes one pass over Q, K, V.
+// (sequence, head) the kernel walks the key/value blocks.  S = Q.K^T lands in tensor memory, four softmax warps turn
+// it into probabilities IN PLACE (tcgen05.ld -> registers -> tcgen05.st over the same columns; scale and causal mask
+// folded in, base-2 exponentials), and the second product P.V reads its A operand straight from tensor memory and
+// accumulates the output in tensor memory across all key blocks.  Neither the scores nor the probabilities touch
+// shared or global memory: the reference's transpose + matMul + scaleMatrix + softmaxMatrix + matMul chain
+// (lib/layertypes/singleHeadAttentionLayer.dart:77-86) becomes one pass over Q, K, V.
 //
-// One CTA = 192 threads:
-//   warp 0      TMA producer: Q once, then K_j / V_j through a two-stage ring
-//   warp 1      MMA issuer: S_j = Q.K_j^T (into one of two TMEM buffers, so S_{j+1} overlaps the softmax of S_j),
-//               then PV_j = P_j.V_j once the softmax warps have published P_j
-//   warps 2..5  softmax: thread = one query row (TMEM lane); keeps the running max m, the running sum l and the 64
-//               output values of its row in registers: O = O * 2^(m_old - m_new) + PV_j
-// Shared memory (224 KiB): Q 32 KiB, 2 x K 32 KiB, 2 x V 32 KiB, P 64 KiB.  TMEM: S0 [0,128), S1 [128,256), PV [256,320).
+// One CTA = 576 threads:
+//   warp 0      TMA producer: Q once per item, then K_j and V_j through two independent three-stage rings
+//   warp 1      MMA issuer: S_j = Q.K_j^T into one of two TMEM buffers (S_{j+1} is issued before P_j.V_j, so it runs
+//               under the softmax of block j), then O += P_j.V_j once the softmax warps have published P_j
+//   warps 2..17 softmax: thread = one query row (TMEM lane) and a quarter of the block's keys, 32 scores in registers
+//               (four warps per lane quarter, so that every scheduler has four warps to choose from).  The exponent
+//               reference m of a row is only moved when a block's maximum exceeds it by more than 2^8; until then the
+//               probabilities are formed against the old reference (they stay below 2^8, the row sum carries the same
+//               factor), so the accumulator in tensor memory needs no rescaling and the warps never wait for P.V.
+// Shared memory (224 KiB): Q 32 KiB, 3 x K 32 KiB, 3 x V 32 KiB.  TMEM: S/P buffers [0,128) and [128,256), O [256,320).
 // V is consumed as an MN-major B operand (32-byte-atom swizzle, the layout notes of gemm_tc.cu apply).
 // Requirements: d_head = 64, seq_len a multiple of 128, 16-byte aligned rows.  Every mbarrier wait is bounded.
 #include <cstdlib>
@@ -28,11 +32,14 @@ using namespace fml_tc;
 namespace {
 
 constexpr int BQ = 128, BKV = 128, DH = 64;
-constexpr int FA_THREADS = 192;      // forward: producer, issuer, 4 softmax warps
+constexpr int FA_THREADS = 576;      // forward: producer, issuer, 16 softmax warps (four per TMEM lane quarter, 32 keys each)
 constexpr int FA_BWD_THREADS = 320;  // backward: producer, issuer, 8 compute warps (two per TMEM lane quarter, alternate 32-column chunks)
-constexpr uint32_t OFF_Q = 0, OFF_K = 32768, OFF_V = 98304, OFF_P = 163840, OFF_BAR = 229376;
-constexpr int FA_SMEM = OFF_BAR + 256 + 1024;
-constexpr uint32_t TM_S = 0, TM_PV = 256;
+constexpr uint32_t OFF_Q = 0, OFF_K = 32768, OFF_V = 131072, OFF_BAR = 229376, OFF_XCH = OFF_BAR + 256;
+constexpr int FA_SMEM = OFF_BAR + 256 + 2048 + 512;   // barriers, the row exchange (forward), alignment slack
+constexpr int KV_STAGES = 3;
+constexpr uint32_t TM_S = 0, TM_O = 256;
+constexpr int FA_MAX_SEQ_TMEM_P = 512;    // longest sequence the tensor-memory forward kernel is used for (four key blocks per item)
+constexpr float FA_RESCALE_LOG2 = 8.f;   // a row's exponent reference moves only when a block maximum exceeds it by 2^8
 
 struct FaParams {
   int S, H, n_qb;        // sequence length, heads, query blocks per sequence
@@ -45,7 +52,10 @@ struct FaParams {
   int* status;
 };
 
-enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KVEMPTY = 5, B_SFULL = 7, B_SEMPTY = 9, B_PFULL = 11, B_PVFULL = 12, B_QEMPTY = 13, B_COUNT = 14 };
+// barriers: Q full/empty, K ring full/empty, V ring full/empty, S full (per buffer), P full (per buffer), P.V done (per
+// buffer), O read by the softmax warps
+enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 5, B_VFULL = 8, B_VEMPTY = 11, B_SFULL = 14, B_PFULL = 16, B_PVDONE = 18,
+       B_OEMPTY = 20, B_ROW = 21 /* one per lane quarter: the four threads of a row meet here */, B_COUNT = 25 };
 
 // 2^x on the special-function unit with flush-to-zero: the library exp2f adds a rescaling sequence for results below
 // 2^-126, which are zero for every purpose here
@@ -75,6 +85,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The layout leaves 512 bytes of slack for rounding the dynamic shared memory base up to 1 KiB.  Should a driver ever
+  // hand out a base that needs more, every thread leaves here (same condition for all) and the host reads code 7.
+  if ((smem_base - smem_u32(smem_raw)) + OFF_XCH + 2048u > (uint32_t)FA_SMEM) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, 7);
+    return;
+  }
 
   // Persistent loop: this CTA takes work items blockIdx.x, blockIdx.x + gridDim.x, ...  Items are ordered heaviest
   // first (all last query blocks, then the ones before, ...), so the causal triangle spreads evenly over the CTAs.
@@ -91,8 +107,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < B_COUNT; i++) {
-      const bool from_softmax = (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL);
-      mbar_init(bar(i), from_softmax ? 128u : 1u);
+      const bool from_softmax = (i == B_PFULL || i == B_PFULL + 1 || i == B_OEMPTY);
+      mbar_init(bar(i), from_softmax ? 512u : (i >= B_ROW ? 128u : 1u));
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -122,16 +138,285 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mbar_expect_tx(bar(B_QFULL), BQ * DH * 4);
         for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + kb * 16384, &tmQ, bar(B_QFULL), kb * 32, qb * BQ, h, b);
         for (int j = 0; j < n_kv && ok; j++, g++) {
-          const int s = g & 1;
-          const uint32_t ph = (g >> 1) & 1u;
-          ok = mbar_wait(bar(B_KVEMPTY + s), ph ^ 1u, abort_flag, p.status, 11);
+          const int s = g % KV_STAGES;
+          const uint32_t ph = (g / KV_STAGES) & 1u;
+          ok = mbar_wait(bar(B_KEMPTY + s), ph ^ 1u, abort_flag, p.status, 11);
           if (!ok) break;
           mbar_expect_tx(bar(B_KFULL + s), BKV * DH * 4);
           for (int kb = 0; kb < 2; kb++)
             tma_load_4d(smem_base + OFF_K + s * 32768 + kb * 16384, &tmK, bar(B_KFULL + s), kb * 32, j * BKV, h, b);
+          ok = mbar_wait(bar(B_VEMPTY + s), ph ^ 1u, abort_flag, p.status, 9);
+          if (!ok) break;
           mbar_expect_tx(bar(B_VFULL + s), BKV * DH * 4);
           for (int c = 0; c < 4; c++)
             tma_load_5d(smem_base + OFF_V + s * 32768 + c * 8192, &tmV, bar(B_VFULL + s), 0, j * BKV + 32 * c, 0, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = fa_idesc(BQ, BKV, 0, 0), idesc_pv = fa_idesc(BQ, DH, 0, 1);
+      bool ok = true;
+      // Cursor of the next S product: it runs one key block ahead of the P.V products, across item boundaries.  S_{g+1}
+      // overwrites the TMEM buffer P_{g-1} lived in; P_{g-1}.V_{g-1} was issued earlier by this thread and tensor-core
+      // operations execute in issue order, so no barrier is needed for that hand-over.
+      int s_item = blockIdx.x, s_j = 0, s_nkv = 0;
+      uint32_t s_g = 0, s_it = 0;
+      if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
+      auto issue_next_s = [&]() {
+        if (s_item >= p.n_items) return true;
+        const int ks = s_g % KV_STAGES;
+        const uint32_t kph = (s_g / KV_STAGES) & 1u;
+        const int buf = s_g & 1;
+        if (s_j == 0 && !mbar_wait(bar(B_QFULL), s_it & 1u, abort_flag, p.status, 12)) return false;
+        if (!mbar_wait(bar(B_KFULL + ks), kph, abort_flag, p.status, 13)) return false;
+        tc_fence_after();
+        for (int kb = 0; kb < 2; kb++) {
+          const uint64_t ad = make_smem_desc(smem_base + OFF_Q + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bd = make_smem_desc(smem_base + OFF_K + ks * 32768 + kb * 16384, 16u, 1024u, 2u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + buf * 128, ad + 2u * k, bd + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+        }
+        umma_commit(bar(B_SFULL + buf));
+        umma_commit(bar(B_KEMPTY + ks));   // K_j is read by nothing else
+        s_g++;
+        if (++s_j == s_nkv) {   // last S of its item: Q may be replaced
+          umma_commit(bar(B_QEMPTY));
+          s_item += gridDim.x;
+          s_it++;
+          s_j = 0;
+          if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
+        }
+        return true;
+      };
+      uint32_t g = 0, it = 0;
+      ok = issue_next_s();
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        for (int j = 0; j < n_kv && ok; j++, g++) {
+          const int vs = g % KV_STAGES;
+          const uint32_t vph = (g / KV_STAGES) & 1u;
+          const int buf = g & 1;
+          if (s_g == g + 1) ok = issue_next_s();   // keep one S product ahead
+          if (!ok) break;
+          // the first P.V of an item overwrites O: the softmax warps must have read the previous item's output
+          if (j == 0 && it > 0) ok = mbar_wait(bar(B_OEMPTY), (it - 1) & 1u, abort_flag, p.status, 8);
+          ok = ok && mbar_wait(bar(B_PFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 15) &&
+               mbar_wait(bar(B_VFULL + vs), vph, abort_flag, p.status, 16);
+          if (!ok) break;
+          tc_fence_after();
+          for (int c = 0; c < 4; c++) {  // 32 keys per chunk of V, 8 keys per instruction
+            const uint64_t bd = make_smem_desc(smem_base + OFF_V + vs * 32768 + c * 8192, 4096u, 512u, 1u);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+              umma_tf32_ts(tmem_base + TM_O, tmem_base + TM_S + buf * 128 + c * 32 + k * 8, bd + 64u * k, idesc_pv, (j | c | k) ? 1u : 0u);
+          }
+          umma_commit(bar(B_PVDONE + buf));
+          umma_commit(bar(B_VEMPTY + vs));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / output
+    // Four warps per TMEM lane quarter: thread = one query row and one QUARTER of the block's 128 keys (32 scores in
+    // registers).  The four threads of a row agree on the block maximum through shared memory (two 128-thread named
+    // barriers per block); everything else (probabilities, partial row sum, the thread's 16 output columns) needs no
+    // exchange.  Sixteen softmax warps give every scheduler four warps to choose from: with one or two, the issue slots
+    // stayed three quarters empty (tensor-memory loads, the exponential's latency and the barriers all stall a warp).
+    const int q4 = warp & 3;                        // TMEM lane quarter of this warp
+    const int part = (warp - 2) >> 2;               // which 32 keys of every block, and which 16 output columns
+    const int row = q4 * 32 + lane;                 // row inside the query block
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+    float* xch = reinterpret_cast<float*>(smem_gen + OFF_XCH);   // [4 parts][128 rows]
+    // The meeting point of a row's four threads is an mbarrier, not a named hardware barrier: its wait is bounded like
+    // every other wait of this kernel, so a CTA that gives up somewhere cannot leave partner warps parked forever.
+    uint32_t n_sync = 0;
+    auto row_sync = [&]() {
+      mbar_arrive(bar(B_ROW + q4));
+      return mbar_wait(bar(B_ROW + q4), (n_sync++) & 1u, abort_flag, p.status, 5);
+    };
+    bool ok = true;
+    uint32_t v0[32];
+    uint32_t o16[16];
+    uint32_t g = 0;
+    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      int qb, h, b, n_kv;
+      item_coords(item, qb, h, b, n_kv);
+      const int qi = qb * BQ + row;                 // position in the sequence
+      float m = -INFINITY, l = 0.f;                 // l: this thread's share of the row sum
+      for (int j = 0; j < n_kv && ok; j++, g++) {
+        const int buf = g & 1;
+        const uint32_t sp = lane_addr + TM_S + buf * 128 + part * 32;
+        ok = mbar_wait(bar(B_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 17);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(sp, v0);
+        tmem_ld_wait();
+        const bool diag = p.causal && j == qb;
+        const int lim = (diag ? row + 1 : BKV) - part * 32;   // valid keys of this row inside this thread's part
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (diag) {
+#pragma unroll
+          for (int e = 0; e < 32; e++) mx4[e & 3] = fmaxf(mx4[e & 3], (e < lim) ? __uint_as_float(v0[e]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e++) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v0[e]));
+        }
+        xch[part * 128 + row] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        ok = row_sync();
+        if (!ok) break;
+        const float bm = fmaxf(fmaxf(xch[row], xch[128 + row]), fmaxf(xch[256 + row], xch[384 + row])) * p.k2;   // k2 > 0
+        ok = row_sync();                             // all reads done before the next block's writes
+        if (!ok) break;
+        if (bm > m + FA_RESCALE_LOG2) {
+          // Move the reference (the four threads of the row take the same decision from the same numbers).  Block 0 of an
+          // item always lands here (m = -inf) with nothing to rescale; later blocks rescale the accumulator in tensor
+          // memory, which the previous P.V must have finished writing.
+          if (j > 0) {
+            ok = mbar_wait(bar(B_PVDONE + (buf ^ 1)), ((g - 1) >> 1) & 1u, abort_flag, p.status, 18);
+            if (!ok) break;
+            tc_fence_after();
+            const float alpha = fa_exp2(m - bm);
+            tmem_ld16(lane_addr + TM_O + part * 16, o16);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; e++) o16[e] = __float_as_uint(__uint_as_float(o16[e]) * alpha);
+            tmem_st16(lane_addr + TM_O + part * 16, o16);
+            l *= alpha;
+          }
+          m = bm;
+        }
+        // probabilities (unnormalised, below 2^8) over the scores, rounded to TF32; the ROUNDED value enters the row sum:
+        // the tensor core would otherwise cut the low mantissa bits of P on its own and bias every output low
+        float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float k2 = p.k2, nm = -m;
+        const bool rnd = p.round_p != 0;
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          float p0 = fa_exp2(fmaf(__uint_as_float(v0[e]), k2, nm));
+          if (rnd) p0 = fa_round_tf32(p0);
+          if (diag) p0 = (e < lim) ? p0 : 0.f;
+          ls4[e & 3] += p0;
+          v0[e] = __float_as_uint(p0);
+        }
+        l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        tmem_st32(sp, v0);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar(B_PFULL + buf));
+      }
+      if (ok) ok = mbar_wait(bar(B_PVDONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1u, abort_flag, p.status, 19);
+      if (ok) {
+        tc_fence_after();
+        tmem_ld16(lane_addr + TM_O + part * 16, o16);
+        tmem_ld_wait();
+        // the accumulator has been read: the next item's first P.V product may overwrite it
+        tc_fence_before();
+        mbar_arrive(bar(B_OEMPTY));
+        xch[part * 128 + row] = l;
+        ok = row_sync();
+        const float lt = (xch[row] + xch[128 + row]) + (xch[256 + row] + xch[384 + row]);
+        ok = ok && row_sync();
+        if (!ok) break;
+        const float inv = 1.f / lt;
+        float* orow = p.out + ((long long)b * p.S + qi) * p.ld_out + h * DH + part * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4)
+          *reinterpret_cast<float4*>(orow + i) = make_float4(__uint_as_float(o16[i]) * inv, __uint_as_float(o16[i + 1]) * inv,
+                                                             __uint_as_float(o16[i + 2]) * inv, __uint_as_float(o16[i + 3]) * inv);
+        if (p.lse && part == 0) p.lse[((long long)b * p.H + h) * p.S + qi] = m + log2f(lt);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Forward for sequences longer than 512: the same products with the probabilities staged through shared memory (a
+// K-major A operand with a hand-written 128-byte swizzle) and the output accumulated in registers, one softmax warp per
+// lane quarter.  It is the slower of the two forward kernels per key block, and the one whose long-sequence behaviour
+// has been verified (up to 8 x 16 x 2048, many work items per CTA); the kernel above is used where IT has been
+// verified, i.e. for up to four key blocks per work item.
+// Shared memory (224 KiB): Q 32 KiB, 2 x K 32 KiB, 2 x V 32 KiB, P 64 KiB.  TMEM: S0 [0,128), S1 [128,256), PV [256,320).
+constexpr int FA_LONG_THREADS = 192;   // producer, issuer, 4 softmax warps
+constexpr uint32_t LO_Q = 0, LO_K = 32768, LO_V = 98304, LO_P = 163840;
+constexpr uint32_t LT_S = 0, LT_PV = 256;
+enum { L_QFULL = 0, L_KFULL = 1, L_VFULL = 3, L_KVEMPTY = 5, L_SFULL = 7, L_SEMPTY = 9, L_PFULL = 11, L_PVFULL = 12, L_QEMPTY = 13, L_COUNT = 14 };
+
+__global__ void __launch_bounds__(FA_LONG_THREADS, 1)
+attention_fwd_long_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  auto bar = [&](int i) { return smem_base + OFF_BAR + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + 8 * L_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // Persistent loop: this CTA takes work items blockIdx.x, blockIdx.x + gridDim.x, ...  Items are ordered heaviest
+  // first (all last query blocks, then the ones before, ...), so the causal triangle spreads evenly over the CTAs.
+  // Barrier phases are driven by running counters (g = key blocks processed so far, it = items), which lets the
+  // producer and the MMA issuer run ahead into the next item while the softmax warps finish the current one.
+  const int n_bh = p.n_items / p.n_qb;
+  auto item_coords = [&](int item, int& qb, int& h, int& b, int& n_kv) {
+    qb = p.n_qb - 1 - item / n_bh;
+    const int bh = item - (item / n_bh) * n_bh;
+    h = bh % p.H;
+    b = bh / p.H;
+    n_kv = p.causal ? qb + 1 : p.S / BKV;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < L_COUNT; i++) {
+      const bool from_softmax = (i == L_SEMPTY || i == L_SEMPTY + 1 || i == L_PFULL);
+      mbar_init(bar(i), from_softmax ? 128u : 1u);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t g = 0, it = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        // Q is single-buffered: the previous item's last S product must have read it
+        ok = mbar_wait(bar(L_QEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 10);
+        if (!ok) break;
+        mbar_expect_tx(bar(L_QFULL), BQ * DH * 4);
+        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + LO_Q + kb * 16384, &tmQ, bar(L_QFULL), kb * 32, qb * BQ, h, b);
+        for (int j = 0; j < n_kv && ok; j++, g++) {
+          const int s = g & 1;
+          const uint32_t ph = (g >> 1) & 1u;
+          ok = mbar_wait(bar(L_KVEMPTY + s), ph ^ 1u, abort_flag, p.status, 11);
+          if (!ok) break;
+          mbar_expect_tx(bar(L_KFULL + s), BKV * DH * 4);
+          for (int kb = 0; kb < 2; kb++)
+            tma_load_4d(smem_base + LO_K + s * 32768 + kb * 16384, &tmK, bar(L_KFULL + s), kb * 32, j * BKV, h, b);
+          mbar_expect_tx(bar(L_VFULL + s), BKV * DH * 4);
+          for (int c = 0; c < 4; c++)
+            tma_load_5d(smem_base + LO_V + s * 32768 + c * 8192, &tmV, bar(L_VFULL + s), 0, j * BKV + 32 * c, 0, h, b);
         }
       }
     }
@@ -148,20 +433,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (s_item >= p.n_items) return true;
         const int s = s_g & 1;
         const uint32_t ph = (s_g >> 1) & 1u;
-        if (s_j == 0 && !mbar_wait(bar(B_QFULL), s_it & 1u, abort_flag, p.status, 12)) return false;
-        if (!mbar_wait(bar(B_KFULL + s), ph, abort_flag, p.status, 13)) return false;
-        if (!mbar_wait(bar(B_SEMPTY + s), ph ^ 1u, abort_flag, p.status, 14)) return false;
+        if (s_j == 0 && !mbar_wait(bar(L_QFULL), s_it & 1u, abort_flag, p.status, 12)) return false;
+        if (!mbar_wait(bar(L_KFULL + s), ph, abort_flag, p.status, 13)) return false;
+        if (!mbar_wait(bar(L_SEMPTY + s), ph ^ 1u, abort_flag, p.status, 14)) return false;
         tc_fence_after();
         for (int kb = 0; kb < 2; kb++) {
-          const uint64_t ad = make_smem_desc(smem_base + OFF_Q + kb * 16384, 16u, 1024u, 2u);
-          const uint64_t bd = make_smem_desc(smem_base + OFF_K + s * 32768 + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t ad = make_smem_desc(smem_base + LO_Q + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bd = make_smem_desc(smem_base + LO_K + s * 32768 + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
-          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + s * 128, ad + 2u * k, bd + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + LT_S + s * 128, ad + 2u * k, bd + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
         }
-        umma_commit(bar(B_SFULL + s));
+        umma_commit(bar(L_SFULL + s));
         s_g++;
         if (++s_j == s_nkv) {   // last S of its item: Q may be replaced
-          umma_commit(bar(B_QEMPTY));
+          umma_commit(bar(L_QEMPTY));
           s_item += gridDim.x;
           s_it++;
           s_j = 0;
@@ -179,17 +464,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const uint32_t ph = (g >> 1) & 1u;
           if (s_g == g + 1) ok = issue_next_s();   // keep one S product ahead
           if (!ok) break;
-          ok = mbar_wait(bar(B_PFULL), g & 1u, abort_flag, p.status, 15) && mbar_wait(bar(B_VFULL + s), ph, abort_flag, p.status, 16);
+          ok = mbar_wait(bar(L_PFULL), g & 1u, abort_flag, p.status, 15) && mbar_wait(bar(L_VFULL + s), ph, abort_flag, p.status, 16);
           if (!ok) break;
           tc_fence_after();
           for (int c = 0; c < 4; c++) {  // 32 keys per chunk
-            const uint64_t ad = make_smem_desc(smem_base + OFF_P + c * 16384, 16u, 1024u, 2u);
-            const uint64_t bd = make_smem_desc(smem_base + OFF_V + s * 32768 + c * 8192, 4096u, 512u, 1u);
+            const uint64_t ad = make_smem_desc(smem_base + LO_P + c * 16384, 16u, 1024u, 2u);
+            const uint64_t bd = make_smem_desc(smem_base + LO_V + s * 32768 + c * 8192, 4096u, 512u, 1u);
 #pragma unroll
-            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_PV, ad + 2u * k, bd + 64u * k, idesc_pv, (c | k) ? 1u : 0u);
+            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + LT_PV, ad + 2u * k, bd + 64u * k, idesc_pv, (c | k) ? 1u : 0u);
           }
-          umma_commit(bar(B_PVFULL));       // PV readable, P free again
-          umma_commit(bar(B_KVEMPTY + s));  // K and V of this block consumed
+          umma_commit(bar(L_PVFULL));       // PV readable, P free again
+          umma_commit(bar(L_KVEMPTY + s));  // K and V of this block consumed
         }
       }
     }
@@ -211,7 +496,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int i = 0; i < DH; i++) o[i] = 0.f;
       for (int j = 0; j < n_kv && ok; j++, g++) {
         const int s = g & 1;
-        ok = mbar_wait(bar(B_SFULL + s), (g >> 1) & 1u, abort_flag, p.status, 17);
+        ok = mbar_wait(bar(L_SFULL + s), (g >> 1) & 1u, abort_flag, p.status, 17);
         if (!ok) break;
         tc_fence_after();
         const bool diag = p.causal && j == qb;
@@ -219,7 +504,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         // pass 1: row maximum of the scores (four chains instead of one of 128 dependent maxima)
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         for (int c = 0; c < 4; c++) {
-          tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
+          tmem_ld32(lane_addr + LT_S + s * 128 + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; e++) {
@@ -232,11 +517,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const float alpha = fa_exp2(m - m_new);        // 0 for the first block (m = -inf)
         // the previous block's P.V must be folded in (and P be free) before P is overwritten
         if (j > 0) {
-          ok = mbar_wait(bar(B_PVFULL), (g - 1) & 1u, abort_flag, p.status, 18);
+          ok = mbar_wait(bar(L_PVFULL), (g - 1) & 1u, abort_flag, p.status, 18);
           if (!ok) break;
           tc_fence_after();
           for (int c = 0; c < 2; c++) {
-            tmem_ld32(lane_addr + TM_PV + c * 32, v);
+            tmem_ld32(lane_addr + LT_PV + c * 32, v);
             tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 32; e++) o[c * 32 + e] += __uint_as_float(v[e]);
@@ -249,9 +534,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         // per query, 16-byte chunks XOR-swizzled with the row index
         float ls4[4] = {0.f, 0.f, 0.f, 0.f};
         for (int c = 0; c < 4; c++) {
-          tmem_ld32(lane_addr + TM_S + s * 128 + c * 32, v);
+          tmem_ld32(lane_addr + LT_S + s * 128 + c * 32, v);
           tmem_ld_wait();
-          uint8_t* prow = smem_gen + OFF_P + c * 16384 + row * 128;
+          uint8_t* prow = smem_gen + LO_P + c * 16384 + row * 128;
 #pragma unroll
           for (int ch = 0; ch < 8; ch++) {
             float4 pv;
@@ -273,14 +558,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         m = m_new;
         tc_fence_before();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(bar(B_PFULL));
-        mbar_arrive(bar(B_SEMPTY + s));
+        mbar_arrive(bar(L_PFULL));
+        mbar_arrive(bar(L_SEMPTY + s));
       }
-      if (ok) ok = mbar_wait(bar(B_PVFULL), (g - 1) & 1u, abort_flag, p.status, 19);
+      if (ok) ok = mbar_wait(bar(L_PVFULL), (g - 1) & 1u, abort_flag, p.status, 19);
       if (ok) {
         tc_fence_after();
         for (int c = 0; c < 2; c++) {
-          tmem_ld32(lane_addr + TM_PV + c * 32, v);
+          tmem_ld32(lane_addr + LT_PV + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; e++) o[c * 32 + e] += __uint_as_float(v[e]);
@@ -826,13 +1111,17 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
   p.out = d->out; p.ld_out = d->ld_out;
   p.lse = d->lse;
   p.status = ctx->d_status;
-  FML_ONCE_PER_DEVICE(ctx, { FML_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM)); });
+  FML_ONCE_PER_DEVICE(ctx, {
+    FML_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
+    FML_CUDA(ctx, cudaFuncSetAttribute(attention_fwd_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
+  });
   const long long items = (long long)Bn * H * p.n_qb;
   FML_REQUIRE(ctx, items <= 0x7fffffffLL, "fml_attention_fwd: too many work items");
   p.n_items = (int)items;
   p.round_p = getenv("FML_FA_NOROUND") ? 0 : 1;
   const unsigned grid = (unsigned)std::min<long long>(items, ctx->sm_count);
-  attention_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
+  if (S <= FA_MAX_SEQ_TMEM_P) attention_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
+  else attention_fwd_long_kernel<<<grid, FA_LONG_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
   FML_LAUNCH_CHECK(ctx, "attention_fwd_kernel");
   return FML_OK;
 }

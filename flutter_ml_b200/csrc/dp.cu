@@ -142,7 +142,12 @@ int32_t fml_dp_init(fml_ctx* ctx, const uint8_t id_bytes[128], int32_t rank, int
   memcpy(id.internal, id_bytes, 128);
   ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
   cfg.blocking = 0;
-  if (ctx->dp_max_ctas > 0) cfg.maxCTAs = ctx->dp_max_ctas;  // keep the collective to the SMs set aside for it
+  if (ctx->dp_max_ctas > 0) {
+    // Keep the collective to the SMs set aside for it, and do not group its CTAs into clusters: a cluster needs all of
+    // its SMs free inside ONE GPC at the same moment, which a persistent product spread over the machine never leaves.
+    cfg.maxCTAs = ctx->dp_max_ctas;
+    cfg.cgaClusterSize = 0;
+  }
   ncclComm_t comm = nullptr;
   ncclResult_t rc = a->comm_init_rank_config(&comm, world, id, rank, &cfg);
   ctx->nccl_comm = comm;

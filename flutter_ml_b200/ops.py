@@ -46,7 +46,7 @@ class GradientExchange:
     all-reduce (sum over ranks, NCCL) is enqueued on side stream `lane` behind everything queued so far, the persistent
     products that run beside it leave `reserve_sms` SMs free for it, and `join` makes the main stream wait for it."""
 
-    def __init__(self, ctx, world: int, lane: int = 2, reserve_sms: int = 0, ev_start: int = 56, ev_done: int = 57):
+    def __init__(self, ctx, world: int, lane: int = 2, reserve_sms: int = 0, ev_start: int = 60, ev_done: int = 61):
         self.ctx, self.world, self.lane, self.reserve = ctx, world, lane, reserve_sms
         self.ev_start, self.ev_done = ev_start, ev_done
 

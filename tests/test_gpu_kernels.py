@@ -693,7 +693,8 @@ def test_tf32_product_is_the_exact_product_of_truncated_operands(ctx, M, N, K, t
         return (np.ascontiguousarray(x, np.float32).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32).astype(np.float64)
     opA, opB = (A.T if tA else A), (B.T if tB else B)
     got = dC.numpy()
-    assert rel(got, cut(opA) @ cut(opB)) <= 3e-6
+    # fp32 accumulation inside the tensor core: its error grows with the length of the chain (about 1.5e-9 per term)
+    assert rel(got, cut(opA) @ cut(opB)) <= max(3e-6, 3e-9 * K), rel(got, cut(opA) @ cut(opB))
     exact = w64(opA) @ w64(opB)
     assert 4e-4 <= rel(got, exact) <= TOL_TF32
     shrink = float(np.sum(got * exact) / np.sum(exact * exact)) - 1.0          # least-squares scale of got against exact

@@ -85,8 +85,19 @@ def test_transformer_lm_step_config5_scaled(orc, prec):
     t_out, t_grad = TOLS[prec]
     lg = logits.numpy().reshape(B, S, V)
     assert rel(lg, ref["logits"]) <= t_out
-    agree = (lg.argmax(-1) == ref["logits"].argmax(-1)).mean()
-    assert agree == 1.0 if prec == 1 else agree >= 0.99   # near-ties among 1000 random logits can flip under TF32
+    # Argmax: identical on every row whose float64 top-2 margin exceeds twice the largest logit error measured here (such a
+    # row cannot flip); the rows below that margin are near-ties among 1000 random logits and are counted, not asserted.
+    r64 = ref["logits"].reshape(-1, V)
+    top2 = np.sort(r64, axis=1)[:, -2:]
+    margin = top2[:, 1] - top2[:, 0]
+    max_err = float(np.max(np.abs(lg.reshape(-1, V) - r64)))
+    same = lg.reshape(-1, V).argmax(1) == r64.argmax(1)
+    safe = margin > 2 * max_err
+    print(f"PARITY lm-head argmax prec{prec}: rows {same.size}, max |logit error| {max_err:.2e}, top-2 margin min {margin.min():.2e} "
+          f"median {np.median(margin):.2e}, rows with margin <= 2 max error: {int((~safe).sum())}, of which flipped: {int((~same & ~safe).sum())}")
+    assert same[safe].all()
+    if prec == 1:
+        assert same.all()
     assert abs(loss.numpy()[0] - ref["loss"]) <= t_out * abs(ref["loss"])
     for g, r in zip(lm.grads_in_reference_order(), ref["grads"]):
         assert rel(g, r) <= t_grad
