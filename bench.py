@@ -337,7 +337,8 @@ def main():
     ap.add_argument("--ref-size", type=int, default=1024, help="M=N=K of one CPU sample step")
     ap.add_argument("--repeats", type=int, default=0, help="timed regions of --steps steps each; 0 picks 10, fewer for long regions")
     ap.add_argument("--reserve-sms", type=int, default=16, help="SMs the dA product leaves to the exchange that runs beside it (N > 1)")
-    ap.add_argument("--nccl-ctas", type=int, default=8, help="upper limit on the CTAs of the gradient exchange (N > 1)")
+    ap.add_argument("--nccl-ctas", type=int, default=8, help="upper limit on the CTAs of the gradient exchange (N > 1; 0: NCCL's choice)")
+    ap.add_argument("--overlap-rows", type=int, default=0, help="rows of the dA product computed beside the exchange on the reduced SM set (0: all)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-train", action="store_true")
@@ -412,7 +413,7 @@ def main():
     exchange = None
     if world > 1:
         dp.init_data_parallel(ctx, dist, rank, world, device="cuda", max_ctas=args.nccl_ctas)
-        exchange = ops.GradientExchange(ctx, world, lane=2, reserve_sms=args.reserve_sms)
+        exchange = ops.GradientExchange(ctx, world, lane=2, reserve_sms=args.reserve_sms, overlap_rows=args.overlap_rows)
     host = ops.DenseFwdBwdHost(ctx, M, N, K, act="gelu", exchange=exchange)
     seeds = make_inputs(M, N, K)
     if world > 1:   # every rank has its own rows of the batch (A, dC); weights and bias are replicated
@@ -454,7 +455,11 @@ def main():
                 c.event_record(6 * sl + 3)
                 if exchange:
                     exchange.start(host.grads, host.grads.size)
-                c.gemm(host.dZ, host.B, host.dA, M, K, N, transB=True)
+                r1 = exchange.overlap_rows if (exchange and 0 < exchange.overlap_rows < M) else M
+                c.gemm(host.dZ, host.B, host.dA, r1, K, N, transB=True)
+                if r1 < M:
+                    exchange.release_sms()
+                    c.gemm(host.dZ.view(r1 * N, (M - r1, N)), host.B, host.dA.view(r1 * K, (M - r1, K)), M - r1, K, N, transB=True)
                 c.event_record(6 * sl + 4)
                 if exchange:
                     exchange.join()
@@ -532,7 +537,8 @@ def main():
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "regions": regions,
             "frac_of_tf32_peak": round(value / world / tf32_peak, 4)}
     if world > 1:
-        line["exchange"] = {"bytes_per_step": host.grads.size * 4, "nccl_max_ctas": args.nccl_ctas, "reserved_sms": args.reserve_sms}
+        line["exchange"] = {"bytes_per_step": host.grads.size * 4, "nccl_max_ctas": args.nccl_ctas, "reserved_sms": args.reserve_sms,
+                            "rows_of_dA_beside_it": args.overlap_rows or M}
 
     if rank == 0 and not args.no_sweep:
         line["sweep"] = time_sweep(ctx)

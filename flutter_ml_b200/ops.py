@@ -46,9 +46,13 @@ class GradientExchange:
     all-reduce (sum over ranks, NCCL) is enqueued on side stream `lane` behind everything queued so far, the persistent
     products that run beside it leave `reserve_sms` SMs free for it, and `join` makes the main stream wait for it."""
 
-    def __init__(self, ctx, world: int, lane: int = 2, reserve_sms: int = 0, ev_start: int = 60, ev_done: int = 61):
+    def __init__(self, ctx, world: int, lane: int = 2, reserve_sms: int = 0, ev_start: int = 60, ev_done: int = 61,
+                 overlap_rows: int = 0):
         self.ctx, self.world, self.lane, self.reserve = ctx, world, lane, reserve_sms
         self.ev_start, self.ev_done = ev_start, ev_done
+        # rows of the product that follows which are computed on the reduced SM set while the exchange runs; the rest of
+        # it is launched with all SMs again (0: the whole product runs on the reduced set)
+        self.overlap_rows = overlap_rows
 
     def start(self, buf, n):
         if self.world == 1:
@@ -61,12 +65,16 @@ class GradientExchange:
         if self.reserve:
             c.check(L.fml_set_sm_reserve(c.h, self.reserve))
 
+    def release_sms(self):
+        """Later launches may use every SM again (the exchange is expected to be over by the time they start)."""
+        if self.world > 1 and self.reserve:
+            self.ctx.check(self.ctx.lib.fml_set_sm_reserve(self.ctx.h, 0))
+
     def join(self):
         if self.world == 1:
             return
         c, L = self.ctx, self.ctx.lib
-        if self.reserve:
-            c.check(L.fml_set_sm_reserve(c.h, 0))
+        self.release_sms()
         c.check(L.fml_wait_event(c.h, -1, self.ev_done))
 
 
@@ -97,9 +105,17 @@ class DenseFwdBwdHost:
         dense_forward(c, d["A"], d["B"], d["bias"], self.act, self.M, self.N, self.K, d["C"], d["Z"], self.precision)
         c.zero(d["dbias"])
         ex = self.exchange
-        dense_backward(c, d["A"], d["B"], d["Z"], d["dC"], self.act, self.M, self.N, self.K, d["dZ"], d["dA"], d["dB"],
+        M, N, K = self.M, self.N, self.K
+        split = ex.overlap_rows if (ex and ex.world > 1 and 0 < ex.overlap_rows < M) else 0
+        dense_backward(c, d["A"], d["B"], d["Z"], d["dC"], self.act, M, N, K, d["dZ"], None if split else d["dA"], d["dB"],
                        d["dbias"], precision=self.precision,
                        after_dW=(lambda: ex.start(d["grads"], d["grads"].size)) if ex else None)
+        if split:
+            # dA in two row blocks: the first beside the exchange on the reduced SM set, the second on all SMs
+            c.gemm(d["dZ"], d["B"], d["dA"], split, K, N, transB=True, precision=self.precision)
+            ex.release_sms()
+            c.gemm(d["dZ"].view(split * N, (M - split, N)), d["B"], d["dA"].view(split * K, (M - split, K)), M - split, K, N,
+                   transB=True, precision=self.precision)
         if ex:
             ex.join()
 
