@@ -16,6 +16,9 @@
 #include <string>
 #include <vector>
 
+#include <fcntl.h>
+#include <unistd.h>
+
 #include "common.cuh"
 
 namespace {
@@ -60,8 +63,23 @@ struct Staging {
 
 struct File {
   FILE* f = nullptr;
-  ~File() { if (f) std::fclose(f); }
+  std::string unlink_on_failure;   // a partly written temporary is removed unless the save completed
+  ~File() {
+    if (f) std::fclose(f);
+    if (!unlink_on_failure.empty()) std::remove(unlink_on_failure.c_str());
+  }
 };
+
+// flush a directory entry (the rename) to stable storage
+void sync_parent_dir(const std::string& path) {
+  const size_t slash = path.find_last_of('/');
+  const std::string dir = slash == std::string::npos ? "." : (slash == 0 ? "/" : path.substr(0, slash));
+  const int fd = ::open(dir.c_str(), O_RDONLY | O_DIRECTORY);
+  if (fd >= 0) {
+    ::fsync(fd);
+    ::close(fd);
+  }
+}
 
 struct Entry { std::string name; uint64_t n; uint32_t crc; };
 
@@ -89,6 +107,7 @@ int32_t fml_checkpoint_save(fml_ctx* ctx, const char* path, int64_t step, int32_
   File out;
   out.f = std::fopen(tmp.c_str(), "wb");
   if (!out.f) return fml_fail(ctx, FML_ERR_INVALID, "fml_checkpoint_save: cannot open " + tmp);
+  out.unlink_on_failure = tmp;
   // header with zero CRCs first; rewritten once the payload has passed through the host
   std::vector<uint32_t> crcs(n, 0);
   auto write_header = [&]() -> bool {
@@ -121,11 +140,15 @@ int32_t fml_checkpoint_save(fml_ctx* ctx, const char* path, int64_t step, int32_
       if (std::fwrite(st.buf[k & 1], 4, cnt, out.f) != cnt) return fml_fail(ctx, FML_ERR_INVALID, "fml_checkpoint_save: write failed");
     }
   }
-  if (std::fseek(out.f, 0, SEEK_SET) != 0 || !write_header() || std::fflush(out.f) != 0)
+  // the bytes reach stable storage before the file takes its final name, and the rename itself is made durable:
+  // after a crash the name holds either the old complete file or the new complete file
+  if (std::fseek(out.f, 0, SEEK_SET) != 0 || !write_header() || std::fflush(out.f) != 0 || ::fsync(::fileno(out.f)) != 0)
     return fml_fail(ctx, FML_ERR_INVALID, "fml_checkpoint_save: write failed");
   std::fclose(out.f);
   out.f = nullptr;
   if (std::rename(tmp.c_str(), path) != 0) return fml_fail(ctx, FML_ERR_INVALID, std::string("fml_checkpoint_save: cannot rename to ") + path);
+  out.unlink_on_failure.clear();
+  sync_parent_dir(path);
   return FML_OK;
 }
 

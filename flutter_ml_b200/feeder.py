@@ -135,3 +135,8 @@ class BatchFeeder:
                 self._used[b] = True
         finally:
             L.fml_stage_wait(c.h)      # also when the consumer stops early: no thread may outlive the arrays it reads
+            # A consumer that leaves early (break, exception) never reaches the record behind its last yield: record both
+            # device sets as consumed after everything now queued on the main stream, so that the next epoch's uploads
+            # wait for the abandoned step's kernels instead of the stale event of an older step.
+            for b in range(2):
+                L.fml_event_record_on(c.h, self._ev_consumed + b, -1)

@@ -245,10 +245,12 @@ class MultiHeadAttention(Layer):
 
     name = "multi_head_attention"
 
-    def __init__(self, numHeads: int, dModel: int, seq_len: Optional[int] = None, causal: bool = False, seed: int = 0,
+    def __init__(self, dModel: int, numHeads: int, seq_len: Optional[int] = None, causal: bool = False, seed: int = 0,
                  head_weights=None, Wo=None, precision: int = -1):
+        """Argument order of the reference: MultiHeadAttention(dModel, numHeads) (multiHeadAttentionLayer.dart:33)."""
         super().__init__()
-        assert dModel % numHeads == 0
+        if numHeads <= 0 or dModel % numHeads != 0:
+            raise ValueError(f"MultiHeadAttention(dModel={dModel}, numHeads={numHeads}): dModel must be a multiple of numHeads")
         self.numHeads, self.dModel, self.dK = numHeads, dModel, dModel // numHeads
         self.seq_len, self.causal, self.seed, self.precision = seq_len, causal, seed, precision
         self._heads0, self._wo0 = head_weights, Wo
@@ -297,7 +299,7 @@ class SingleHeadAttention(MultiHeadAttention):
 
     def __init__(self, dModel: int, dK: int, dV: int, seq_len=None, causal=False, seed: int = 0, weights=None, precision=-1):
         assert dK == dV == dModel, "the fused kernel path covers dK = dV = dModel for a single head"
-        super().__init__(1, dModel, seq_len, causal, seed, [weights] if weights is not None else None, None, precision)
+        super().__init__(dModel, 1, seq_len, causal, seed, [weights] if weights is not None else None, None, precision)
 
     @property
     def parameters(self):
@@ -321,7 +323,7 @@ class TransformerEncoderBlock(Layer):
                  precision: int = -1):
         super().__init__()
         p = params or {}
-        self.attention = MultiHeadAttention(numHeads, dModel, seq_len, causal, seed, p.get("heads"), p.get("Wo"), precision)
+        self.attention = MultiHeadAttention(dModel, numHeads, seq_len, causal, seed, p.get("heads"), p.get("Wo"), precision)
         self.norm1, self.norm2 = LayerNormalization(), LayerNormalization()
         self.ffn1 = DenseLayerMatrix(dff, "relu", seed + 1, p.get("W1"), p.get("b1"), precision)
         self.ffn2 = DenseLayerMatrix(dModel, None, seed + 2, p.get("W2"), p.get("b2"), precision)

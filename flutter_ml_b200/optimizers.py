@@ -167,7 +167,7 @@ class RMSprop(_StatefulOptimizer):
     """s = beta*s + (1-beta)*g^2; w -= lr*g/(sqrt(s)+eps) (lib/optimizers/rmsprop.dart:57-58)."""
     KIND, N_STATE = 3, 1
 
-    def __init__(self, parameters, learningRate, beta=0.9, epsilon=1e-8, arena=None):
+    def __init__(self, parameters, learningRate, beta=0.99, epsilon=1e-8, arena=None):   # defaults of rmsprop.dart
         super().__init__(parameters, learningRate, arena)
         self.beta, self.epsilon = beta, epsilon
 

@@ -468,7 +468,11 @@ int32_t fml_conv2d_bwd(fml_ctx* ctx, const float* in, const float* w, const floa
  * (No counterpart in the reference, which has no serialisation.)  One file holds named fp32 device buffers -
  * parameter arena, optimizer state - plus a caller-defined step counter; every entry carries a CRC-32.  Load
  * looks entries up by name, checks sizes and checksums BEFORE it overwrites anything, and may restore a subset.
- * Both calls stage through pinned memory on a copy lane and return when the file / the buffers are complete. */
+ * Both calls stage through pinned memory on a copy lane and return when the file / the buffers are complete.
+ * Save orders itself behind everything queued on the context's MAIN stream; work still running on the copy lanes
+ * (an overlapped gradient exchange, an upload) must be joined by the caller first (fml_lane_sync or an event).  The
+ * file is written under <path>.tmp, flushed to stable storage, renamed, and the directory entry flushed: after a
+ * crash the name holds the old complete file or the new complete file; a failed save removes its temporary. */
 int32_t fml_checkpoint_save(fml_ctx* ctx, const char* path, int64_t step, int32_t n, const char* const* names,
                             const float* const* bufs, const int64_t* sizes);
 int32_t fml_checkpoint_load(fml_ctx* ctx, const char* path, int64_t* step, int32_t n, const char* const* names,

@@ -120,3 +120,25 @@ def test_per_device_once_bookkeeping():
     assert L.fml_selftest_per_device_once(64, C.byref(runs)) == 0 and L.fml_selftest_per_device_once(64, C.byref(runs)) == 0
     assert runs.value >= 2                                        # no slot for this ordinal: the body runs every time
     assert L.fml_selftest_per_device_once(0, None) == -1
+
+
+def test_host_mirror_defaults_match_the_reference_constructors():
+    """Default hyper-parameters and argument order of the host mirror against the reference's constructors (values read
+    from lib/optimizers/{adam.dart:17-19, adamw.dart:41-44, amsgrad.dart:32-34, rmsprop.dart:28-29, adagrad.dart:26,
+    nag.dart:30, sgdmomentum.dart:28} and lib/transformer/multiHeadAttentionLayer.dart:33): a ported call with default
+    arguments must mean the same thing."""
+    import inspect
+    from flutter_ml_b200 import layers, optimizers as O
+    d = lambda cls: {k: v.default for k, v in inspect.signature(cls.__init__).parameters.items() if v.default is not inspect.Parameter.empty}  # noqa: E731
+    assert (d(O.Adam)["beta1"], d(O.Adam)["beta2"], d(O.Adam)["epsilon"]) == (0.9, 0.999, 1e-8)
+    aw = d(O.AdamW)
+    assert (aw["beta1"], aw["beta2"], aw["epsilon"], aw["weightDecay"]) == (0.9, 0.999, 1e-8, 0.01)
+    am = d(O.AMSGrad)
+    assert (am["beta1"], am["beta2"], am["epsilon"]) == (0.9, 0.999, 1e-8)
+    assert (d(O.RMSprop)["beta"], d(O.RMSprop)["epsilon"]) == (0.99, 1e-8)
+    assert d(O.Adagrad)["epsilon"] == 1e-8
+    assert d(O.NAG)["momentum"] == 0.9 and d(O.SGDMomentum)["momentum"] == 0.9
+    assert list(inspect.signature(layers.MultiHeadAttention.__init__).parameters)[1:3] == ["dModel", "numHeads"]
+    import pytest as _pytest
+    with _pytest.raises(ValueError):
+        layers.MultiHeadAttention(8, 64)          # (numHeads, dModel) order of a mis-ported call: 8 is not a multiple of 64

@@ -220,7 +220,8 @@ def test_dense_net_with_other_activations_and_optimizers(orc, act, opt_name):
     params = l1.parameters + l2.parameters
     ref = [p.numpy(np.float64).copy() for p in params]
     arena = optimizers.ParameterArena(ctx, params)
-    kind, h, nstate = {"SGDMomentum": (1, (0.9,), 1), "NAG": (2, (0.9,), 1), "RMSprop": (3, (0.9, 1e-8), 1),
+    kind, h, nstate = {"SGDMomentum": (1, (0.9,), 1), "NAG": (2, (0.9,), 1), "RMSprop": (3, (0.99, 1e-8), 1),   # the reference's default beta (rmsprop.dart:28)
+                      
                        "Adagrad": (4, (0.0, 1e-8), 1), "AdamW": (6, (0.9, 0.999, 1e-8, 0.01), 2),
                        "AMSGrad": (7, (0.9, 0.999, 1e-8), 3)}[opt_name]
     opt = getattr(optimizers, opt_name)(params, 0.01, arena=arena)
