@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libflutter_ml_b200.so")
-SOURCES = ["ctx.cu", "gemm_tc.cu", "gemm_simt.cu", "elementwise.cu", "rowwise.cu", "lstm.cu", "dp.cu", "tape.cu", "checkpoint.cu", "conv.cu", "attention_tc.cu", "lstm_tc.cu"]
+SOURCES = ["ctx.cu", "gemm_tc.cu", "gemm_simt.cu", "elementwise.cu", "rowwise.cu", "lstm.cu", "dp.cu", "tape.cu", "checkpoint.cu", "conv.cu", "attention_tc.cu", "lstm_tc.cu", "lstm_bwd_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE]
 
@@ -32,7 +32,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(HERE, "build", src.replace(".cu", ".o"))
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        # FML_NVCC_DEFINES="-DFML_GEMM_DIAGNOSTICS -DFML_LSTM_PROFILE" builds the optional diagnostics in
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("FML_NVCC_DEFINES", "").split(), "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

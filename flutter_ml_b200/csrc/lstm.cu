@@ -18,6 +18,9 @@
 
 // the recurrence of all time steps in one cooperative kernel (lstm_tc.cu); 1 = shape not eligible
 int32_t fml_lstm_fwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const float* Wi, int fast_math);
+// the backward recurrence of all time steps in one cooperative kernel (lstm_bwd_tc.cu); 1 = not eligible / launch refused
+int32_t fml_lstm_bwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const float* Wi, const float* dh_last, float* dpre,
+                                float* dh_a, float* dh_b);
 
 namespace {
 
@@ -188,9 +191,27 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
   float* dbi = dWi + (size_t)4 * H * Z;
   lstm_interleave_rows_kernel<<<blocks_for(ctx, 4ll * H * Z), 256, 0, ctx->stream>>>(d->W, Wi, H, Z);
   cudaMemsetAsync(dWi, 0, ((size_t)4 * H * Z + 4 * H) * sizeof(float), ctx->stream);
-  cudaMemcpyAsync(dh, dh_last, bh * 4, cudaMemcpyDeviceToDevice, ctx->stream);
-  cudaMemsetAsync(dc, 0, bh * 4, ctx->stream);
-  for (int t = T - 1; t >= 0 && rc == FML_OK; t--) {
+  bool recurrence_done = false;
+  {
+    // Opt-in (FML_LSTM_BWD_SINGLE_KERNEL=1, read at every call): the whole recurrence as one cooperative kernel that sums
+    // the split contraction in a fixed order, so dpre, dW, db come out bit for bit the same on every run.  It is NOT the
+    // default because it is slower than the two launches per step below (24 us against 12 us per step at H 512, B 128:
+    // measured phase by phase, see lstm_bwd_tc.cu), whose K split adds its partial sums with atomics in no fixed order.
+    const char* e = getenv("FML_LSTM_BWD_SINGLE_KERNEL");
+    if (e && atoi(e) != 0 && ctx->precision == FML_PREC_TF32) {
+      const int32_t pr = fml_lstm_bwd_persistent(ctx, d, Wi, dh_last, dpre, dh, dc);   // dh, dc: its two dh buffers
+      if (pr < 0) {
+        cudaFreeAsync(Wi, ctx->stream);
+        return pr;
+      }
+      recurrence_done = pr == 0;
+    }
+  }
+  if (!recurrence_done) {
+    cudaMemcpyAsync(dh, dh_last, bh * 4, cudaMemcpyDeviceToDevice, ctx->stream);
+    cudaMemsetAsync(dc, 0, bh * 4, ctx->stream);
+  }
+  for (int t = T - 1; t >= 0 && rc == FML_OK && !recurrence_done; t--) {
     {
       cudaLaunchConfig_t cfg = {};
       cudaLaunchAttribute attr[1];

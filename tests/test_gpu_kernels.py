@@ -699,3 +699,45 @@ def test_tf32_product_is_the_exact_product_of_truncated_operands(ctx, M, N, K, t
     assert 4e-4 <= rel(got, exact) <= TOL_TF32
     shrink = float(np.sum(got * exact) / np.sum(exact * exact)) - 1.0          # least-squares scale of got against exact
     assert -9e-4 <= shrink <= -5e-4, shrink
+
+
+@pytest.mark.parametrize("T,B,I,H", [(6, 128, 16, 256), (5, 70, 8, 512), (3, 3, 4, 128), (1, 9, 4, 128), (9, 33, 12, 384)])
+def test_lstm_single_kernel_backward_recurrence(orc, T, B, I, H):
+    """The opt-in cooperative backward kernel (TF32 mode, batch <= 128, H a multiple of 128 up to 512: the contraction split
+    over a cluster of sixteen CTAs and summed in a fixed order through distributed shared memory) against the oracle's BPTT (lstmLayer.dart:112-150 walked backwards): dW and db; and run twice to show
+    that the recurrence is bit-for-bit reproducible, which the K split with atomics it replaces was not."""
+    import ctypes
+    import os
+    from flutter_ml_b200 import _lib
+    os.environ["FML_LSTM_BWD_SINGLE_KERNEL"] = "1"      # opt-in: the default is two launches per step (faster, not reproducible)
+    c = _lib.Context(precision=_lib.PREC_TF32)
+    rng = np.random.default_rng(100 * T + H + B)
+    a = 1 / np.sqrt(H)
+    W = rng.uniform(-a, a, (4, H, H + I)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (4, H)).astype(np.float32)
+    x = rng.standard_normal((B, T, I)).astype(np.float32)
+    target = rng.standard_normal((B, H)).astype(np.float32)
+    h_ref, loss_ref, dW_ref, db_ref = orc.Ops(omp=True).lstm_fwd_bwd(w64(W), w64(b), w64(x), w64(target))
+    d = _lib.LstmDesc()
+    d.T, d.B, d.I, d.H = T, B, I, H
+    bufs = dict(W=c.upload(W), b=c.upload(b), x=c.upload(np.ascontiguousarray(x.transpose(1, 0, 2))),
+                gates=c.empty(T, B, 4 * H), cells=c.empty(T + 1, B, H), hs=c.empty(T + 1, B, H), xproj=c.empty(T * B, 4 * H))
+    for k, v in bufs.items():
+        setattr(d, k, v.ptr)
+    c.check(c.lib.fml_lstm_fwd(c.h, ctypes.byref(d)))
+    h_last = bufs["hs"].view(T * B * H, (B, H))
+    dh, loss = c.empty(B, H), c.zeros(1)
+    c.call("fml_mse", h_last, c.upload(target), dh, loss, B * H, float(B))
+    scratch = c.empty(T * B * 4 * H + 2 * B * H)
+    runs = []
+    for _ in range(2):
+        dW_, db_, dx_ = c.zeros(4 * H, H + I), c.zeros(4 * H), c.empty(T * B, I)
+        c.check(c.lib.fml_lstm_bwd(c.h, ctypes.byref(d), dh.ptr, dW_.ptr, db_.ptr, dx_.ptr, scratch.ptr))
+        assert c.device_status() == 0
+        runs.append((scratch.numpy()[:T * B * 4 * H].copy(), dx_.numpy()))
+    assert rel(h_last.numpy(), h_ref) <= TOL_TF32
+    assert rel(dW_.numpy().reshape(4, H, H + I), dW_ref) <= 2 * TOL_TF32
+    assert rel(db_.numpy().reshape(4, H), db_ref) <= 2 * TOL_TF32
+    assert np.array_equal(runs[0][0], runs[1][0])      # dpre of every step, i.e. the whole dh chain, bit for bit
+    os.environ.pop("FML_LSTM_BWD_SINGLE_KERNEL")
+    c.close()
