@@ -596,15 +596,24 @@ namespace {
 // ------------------------------------------------------------------------------------------------------------
 // Backward, first kernel: for one block of 128 queries it rebuilds the probabilities of every key block from the
 // saved row statistics, forms dS = scale * P * (dP - D) with dP = dO.V^T and D = rowsum(dO * O), and accumulates
-// dQ = dS.K over the key blocks in TMEM.
-//   warp 0      TMA: Q, dO once; per key block K_j, V_j (K-major) and K_j again as an MN-major B operand
-//   warp 1      MMA: S = Q.K_j^T and dP = dO.V_j^T into TMEM, then dQ += dS.K_j once dS is published
-//   warps 2..9  thread = query row and half of the columns: P, dS from TMEM, dS into the K-major operand layout
-// Shared memory (224 KiB): Q, dO, K, V, K(MN) 32 KiB each, dS 64 KiB.  TMEM: S [0,128), dP [128,256), dQ [256,320).
-constexpr uint32_t BO_Q = 0, BO_DO = 32768, BO_K = 65536, BO_V = 98304, BO_KMN = 131072, BO_DS = 163840;
-constexpr uint32_t TM_DP = 128, TM_DQ = 256;
-enum { C_QFULL = 0, C_KVFULL = 1, C_KVEMPTY = 2, C_KMNFULL = 3, C_KMNEMPTY = 4, C_SDPFULL = 5, C_SDPEMPTY = 6, C_DSFULL = 7,
-       C_DQDONE = 8, C_QEMPTY = 9, C_COUNT = 10 };
+// dQ = dS.K over the key blocks in TMEM.  dS never leaves tensor memory: the compute warps write it over dP
+// (tcgen05.st) and the third product reads its A operand from there.
+//   warp 0      TMA: Q (two buffers, one item ahead), dO; per key block K_j, V_j (K-major) and K_j again as an MN-major
+//               B operand (two buffers)
+//   warp 1      MMA, in this order on the tensor pipe: ... dP_j, S_{j+1}, dQ_j, dP_{j+1}, S_{j+2}, dQ_{j+1} ...
+//               S_{j+1} = Q.K_{j+1}^T is issued BEFORE the issuer waits for dS_j, so the exponentials of block j+1 run
+//               under dQ_j += dS_j.K_j; dP_{j+1} = dO.V_{j+1}^T follows dQ_j because it overwrites dS_j (the pipe
+//               executes in issue order, no barrier needed for that hand-over)
+//   warps 2..9  thread = query row and two of the four 32-column chunks.  Phase A (needs S only): P = 2^(S k2 - L) into
+//               registers.  Phase B (needs dP): dS = round_tf32(scale P (dP - D)) over dP in tensor memory.
+// The running counters g (key blocks) and it (items) drive every barrier phase, so all three roles run on across item
+// boundaries; the dQ tile of a finished item is read between phase A and phase B of the next item's first block.
+// Shared memory (224 KiB): Q 2 x 32 KiB, dO, K, V 32 KiB each, K(MN) 2 x 32 KiB.
+// TMEM: S [0,128) and [128,256), dP/dS [256,384), dQ [384,448).
+constexpr uint32_t BO_Q = 0, BO_DO = 65536, BO_K = 98304, BO_V = 131072, BO_KMN = 163840;
+constexpr uint32_t TM_DP = 256, TM_DQ = 384;
+enum { C_QFULL = 0, C_QEMPTY = 2, C_DOFULL = 4, C_DOEMPTY = 5, C_KFULL = 6, C_KEMPTY = 7, C_VFULL = 8, C_VEMPTY = 9, C_KMNFULL = 10,
+       C_KMNEMPTY = 12, C_SFULL = 14, C_SEMPTY = 16, C_DPFULL = 18, C_DSFULL = 19, C_DQDONE = 20, C_COUNT = 21 };
 
 struct FaBwdParams {
   int S, H, n_qb, causal;
@@ -628,7 +637,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + OFF_BAR + 8 * C_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // persistent loop over work items (heaviest first), barrier phases from running counters: g = key blocks, it = items
+  // persistent loop over work items (heaviest first)
   const int n_bh = p.n_items / p.n_qb;
   auto item_coords = [&](int item, int& qb, int& h, int& b, int& n_kv) {
     qb = p.n_qb - 1 - item / n_bh;
@@ -639,7 +648,10 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C_COUNT; i++) mbar_init(bar(i), (i == C_SDPEMPTY || i == C_DSFULL) ? 256u : 1u);
+    for (int i = 0; i < C_COUNT; i++) {
+      const bool from_compute = (i == C_SEMPTY || i == C_SEMPTY + 1 || i == C_DSFULL);
+      mbar_init(bar(i), from_compute ? 256u : 1u);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -661,26 +673,34 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
         int qb, h, b, n_kv;
         item_coords(item, qb, h, b, n_kv);
-        ok = mbar_wait(bar(C_QEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 20);   // previous item's score products done
+        const uint32_t qs = it & 1u;
+        ok = mbar_wait(bar(C_QEMPTY + qs), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 20);   // last S of item it-2 has read it
         if (!ok) break;
-        mbar_expect_tx(bar(C_QFULL), 2 * BQ * DH * 4);
-        for (int kb = 0; kb < 2; kb++) {
-          tma_load_4d(smem_base + BO_Q + kb * 16384, &tmQ, bar(C_QFULL), kb * 32, qb * BQ, h, b);
-          tma_load_4d(smem_base + BO_DO + kb * 16384, &tmDO, bar(C_QFULL), kb * 32, qb * BQ, h, b);
-        }
+        mbar_expect_tx(bar(C_QFULL + qs), BQ * DH * 4);
+        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + BO_Q + qs * 32768 + kb * 16384, &tmQ, bar(C_QFULL + qs), kb * 32, qb * BQ, h, b);
         for (int j = 0; j < n_kv && ok; j++, g++) {
-          const uint32_t ph = g & 1u;
-          ok = mbar_wait(bar(C_KVEMPTY), ph ^ 1u, abort_flag, p.status, 21);
+          const uint32_t ph = g & 1u, ms = g & 1u;
+          ok = mbar_wait(bar(C_KEMPTY), ph ^ 1u, abort_flag, p.status, 22);
           if (!ok) break;
-          mbar_expect_tx(bar(C_KVFULL), 2 * BKV * DH * 4);
-          for (int kb = 0; kb < 2; kb++) {
-            tma_load_4d(smem_base + BO_K + kb * 16384, &tmK, bar(C_KVFULL), kb * 32, j * BKV, h, b);
-            tma_load_4d(smem_base + BO_V + kb * 16384, &tmV, bar(C_KVFULL), kb * 32, j * BKV, h, b);
+          mbar_expect_tx(bar(C_KFULL), BKV * DH * 4);
+          for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + BO_K + kb * 16384, &tmK, bar(C_KFULL), kb * 32, j * BKV, h, b);
+          ok = mbar_wait(bar(C_KMNEMPTY + ms), ((g >> 1) & 1u) ^ 1u, abort_flag, p.status, 31);
+          if (!ok) break;
+          mbar_expect_tx(bar(C_KMNFULL + ms), BKV * DH * 4);
+          for (int c = 0; c < 4; c++)
+            tma_load_5d(smem_base + BO_KMN + ms * 32768 + c * 8192, &tmKmn, bar(C_KMNFULL + ms), 0, j * BKV + 32 * c, 0, h, b);
+          if (j == 0) {
+            // dO after the first K of the item: the wait below ends only when the previous item's last dP has run, and the
+            // next S product (which needs K, not dO) must not queue behind it
+            ok = mbar_wait(bar(C_DOEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 21);
+            if (!ok) break;
+            mbar_expect_tx(bar(C_DOFULL), BQ * DH * 4);
+            for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + BO_DO + kb * 16384, &tmDO, bar(C_DOFULL), kb * 32, qb * BQ, h, b);
           }
-          ok = mbar_wait(bar(C_KMNEMPTY), ph ^ 1u, abort_flag, p.status, 22);
+          ok = mbar_wait(bar(C_VEMPTY), ph ^ 1u, abort_flag, p.status, 32);
           if (!ok) break;
-          mbar_expect_tx(bar(C_KMNFULL), BKV * DH * 4);
-          for (int c = 0; c < 4; c++) tma_load_5d(smem_base + BO_KMN + c * 8192, &tmKmn, bar(C_KMNFULL), 0, j * BKV + 32 * c, 0, h, b);
+          mbar_expect_tx(bar(C_VFULL), BKV * DH * 4);
+          for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + BO_V + kb * 16384, &tmV, bar(C_VFULL), kb * 32, j * BKV, h, b);
         }
       }
     }
@@ -688,42 +708,69 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     if (lane == 0) {
       const uint32_t idesc_s = fa_idesc(BQ, BKV, 0, 0), idesc_dq = fa_idesc(BQ, DH, 0, 1);
       bool ok = true;
+      // cursor of the next S product: one key block ahead of the dP / dQ products, across item boundaries
+      int s_item = blockIdx.x, s_j = 0, s_nkv = 0;
+      uint32_t s_g = 0, s_it = 0;
+      if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
+      auto issue_next_s = [&]() {
+        if (s_item >= p.n_items) return true;
+        const uint32_t buf = s_g & 1u, qs = s_it & 1u;
+        if (s_j == 0 && !mbar_wait(bar(C_QFULL + qs), (s_it >> 1) & 1u, abort_flag, p.status, 23)) return false;
+        if (!mbar_wait(bar(C_KFULL), s_g & 1u, abort_flag, p.status, 24)) return false;
+        if (!mbar_wait(bar(C_SEMPTY + buf), ((s_g >> 1) & 1u) ^ 1u, abort_flag, p.status, 25)) return false;   // phase A of block s_g-2 done
+        tc_fence_after();
+        for (int kb = 0; kb < 2; kb++) {
+          const uint64_t aq = make_smem_desc(smem_base + BO_Q + qs * 32768 + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t bk = make_smem_desc(smem_base + BO_K + kb * 16384, 16u, 1024u, 2u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + buf * 128, aq + 2u * k, bk + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
+        }
+        umma_commit(bar(C_SFULL + buf));
+        umma_commit(bar(C_KEMPTY));
+        s_g++;
+        if (++s_j == s_nkv) {   // last S of its item: this Q buffer may be replaced
+          umma_commit(bar(C_QEMPTY + qs));
+          s_item += gridDim.x;
+          s_it++;
+          s_j = 0;
+          if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
+        }
+        return true;
+      };
       uint32_t g = 0, it = 0;
+      ok = issue_next_s();
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
         int qb, h, b, n_kv;
         item_coords(item, qb, h, b, n_kv);
-        ok = mbar_wait(bar(C_QFULL), it & 1u, abort_flag, p.status, 23);
         for (int j = 0; j < n_kv && ok; j++, g++) {
-          const uint32_t ph = g & 1u;
-          ok = mbar_wait(bar(C_KVFULL), ph, abort_flag, p.status, 24) && mbar_wait(bar(C_SDPEMPTY), ph ^ 1u, abort_flag, p.status, 25);
+          const uint32_t ph = g & 1u, ms = g & 1u;
+          // dP_g: overwrites dS_{g-1}, which dQ_{g-1} (issued earlier by this thread) has read by then
+          if (j == 0) ok = mbar_wait(bar(C_DOFULL), it & 1u, abort_flag, p.status, 26);
+          ok = ok && mbar_wait(bar(C_VFULL), ph, abort_flag, p.status, 27);
           if (!ok) break;
           tc_fence_after();
-          for (int kb = 0; kb < 2; kb++) {
-            const uint64_t aq = make_smem_desc(smem_base + BO_Q + kb * 16384, 16u, 1024u, 2u);
-            const uint64_t bk = make_smem_desc(smem_base + BO_K + kb * 16384, 16u, 1024u, 2u);
-#pragma unroll
-            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S, aq + 2u * k, bk + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
-          }
           for (int kb = 0; kb < 2; kb++) {
             const uint64_t ad = make_smem_desc(smem_base + BO_DO + kb * 16384, 16u, 1024u, 2u);
             const uint64_t bv = make_smem_desc(smem_base + BO_V + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
             for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DP, ad + 2u * k, bv + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
           }
-          umma_commit(bar(C_SDPFULL));
-          umma_commit(bar(C_KVEMPTY));
-          if (j == n_kv - 1) umma_commit(bar(C_QEMPTY));   // Q and dO of this item are no longer read
-          ok = mbar_wait(bar(C_DSFULL), ph, abort_flag, p.status, 26) && mbar_wait(bar(C_KMNFULL), ph, abort_flag, p.status, 27);
+          umma_commit(bar(C_DPFULL));
+          umma_commit(bar(C_VEMPTY));
+          if (j == n_kv - 1) umma_commit(bar(C_DOEMPTY));
+          if (s_g == g + 1) ok = issue_next_s();   // S_{g+1} runs under the compute phase of block g
+          if (!ok) break;
+          ok = mbar_wait(bar(C_DSFULL), ph, abort_flag, p.status, 28) && mbar_wait(bar(C_KMNFULL + ms), (g >> 1) & 1u, abort_flag, p.status, 29);
           if (!ok) break;
           tc_fence_after();
-          for (int c = 0; c < 4; c++) {
-            const uint64_t ad = make_smem_desc(smem_base + BO_DS + c * 16384, 16u, 1024u, 2u);
-            const uint64_t bd = make_smem_desc(smem_base + BO_KMN + c * 8192, 4096u, 512u, 1u);
+          for (int c = 0; c < 4; c++) {   // 32 keys per chunk of K, 8 keys per instruction, A operand = dS in tensor memory
+            const uint64_t bd = make_smem_desc(smem_base + BO_KMN + ms * 32768 + c * 8192, 4096u, 512u, 1u);
 #pragma unroll
-            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_DQ, ad + 2u * k, bd + 64u * k, idesc_dq, (j | c | k) ? 1u : 0u);
+            for (int k = 0; k < 4; k++)
+              umma_tf32_ts(tmem_base + TM_DQ, tmem_base + TM_DP + c * 32 + k * 8, bd + 64u * k, idesc_dq, (j | c | k) ? 1u : 0u);
           }
           umma_commit(bar(C_DQDONE));
-          umma_commit(bar(C_KMNEMPTY));
+          umma_commit(bar(C_KMNEMPTY + ms));
         }
       }
     }
@@ -733,8 +780,31 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const int row = q4 * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
     bool ok = true;
-    uint32_t sv[32], dv[32];
+    uint32_t tv[32];
+    float pr[64];
     uint32_t g = 0;
+    bool pending = false;        // a finished item whose dQ tile is still to be read
+    long long pend_off = 0;
+    auto flush_dq = [&]() {      // after dQ of block g-1 (the pending item's last) has been accumulated
+      if (!mbar_wait(bar(C_DQDONE), (g - 1) & 1u, abort_flag, p.status, 30)) return false;
+      tc_fence_after();
+      tmem_ld32(lane_addr + TM_DQ + half * 32, tv);
+      tmem_ld_wait();
+      tc_fence_before();   // the accumulator has been read before this thread publishes the next item's first dS
+      float* qrow = p.dq + pend_off + half * 32;
+#pragma unroll
+      for (int e = 0; e < 32; e += 4) {
+        float4 o = make_float4(__uint_as_float(tv[e]), __uint_as_float(tv[e + 1]), __uint_as_float(tv[e + 2]), __uint_as_float(tv[e + 3]));
+        float4* dst = reinterpret_cast<float4*>(qrow + e);
+        if (p.accumulate) {
+          const float4 old = *dst;
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        *dst = o;
+      }
+      pending = false;
+      return true;
+    };
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
       int qb, h, b, n_kv;
       item_coords(item, qb, h, b, n_kv);
@@ -742,55 +812,50 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       const long long stat = ((long long)b * p.H + h) * p.S + qi;
       const float L = p.lse[stat], Dv = p.dsum[stat];
       for (int j = 0; j < n_kv && ok; j++, g++) {
-        const uint32_t ph = g & 1u;
-        ok = mbar_wait(bar(C_SDPFULL), ph, abort_flag, p.status, 28);
-        if (ok && j > 0) ok = mbar_wait(bar(C_DQDONE), ph ^ 1u, abort_flag, p.status, 29);  // dS tile free again
+        const uint32_t buf = g & 1u;
+        // phase A: probabilities of this thread's 64 columns from S alone
+        ok = mbar_wait(bar(C_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 33);
         if (!ok) break;
         tc_fence_after();
         const int lim = (p.causal && j == qb) ? row + 1 : BKV;
-        for (int c = half; c < 4; c += 2) {
-          tmem_ld32(lane_addr + TM_S + c * 32, sv);
-          tmem_ld32(lane_addr + TM_DP + c * 32, dv);
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+          const int c = half + 2 * ci;
+          tmem_ld32(lane_addr + TM_S + buf * 128 + c * 32, tv);
           tmem_ld_wait();
-          uint8_t* srow = smem_gen + BO_DS + c * 16384 + row * 128;
 #pragma unroll
-          for (int ch = 0; ch < 8; ch++) {
-            float4 dsv;
-            float* de = reinterpret_cast<float*>(&dsv);
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-              const int col = c * 32 + ch * 4 + e;
-              const float pr = (col < lim) ? fa_exp2(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -L)) : 0.f;
-              de[e] = fa_round_tf32(pr * (__uint_as_float(dv[ch * 4 + e]) - Dv) * p.scale);
-            }
-            *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
-          }
+          for (int e = 0; e < 32; e++)
+            pr[ci * 32 + e] = (c * 32 + e < lim) ? fa_exp2(fmaf(__uint_as_float(tv[e]), p.k2, -L)) * p.scale : 0.f;
         }
         tc_fence_before();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(bar(C_DSFULL));
-        mbar_arrive(bar(C_SDPEMPTY));
-      }
-      if (ok) ok = mbar_wait(bar(C_DQDONE), (g - 1) & 1u, abort_flag, p.status, 30);
-      if (ok) {
-        tc_fence_after();
-        float* qrow = p.dq + ((long long)b * p.S + qi) * p.ld_dq + h * DH;
-        const int c = half;
-        tmem_ld32(lane_addr + TM_DQ + c * 32, sv);
-        tmem_ld_wait();
-        tc_fence_before();   // the accumulator has been read before this thread publishes the next item's first dS
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          float4 o = make_float4(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1]), __uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3]));
-          float4* dst = reinterpret_cast<float4*>(qrow + c * 32 + e);
-          if (p.accumulate) {
-            const float4 old = *dst;
-            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-          }
-          *dst = o;
+        mbar_arrive(bar(C_SEMPTY + buf));
+        if (pending) {
+          ok = flush_dq();
+          if (!ok) break;
         }
+        // phase B: dS over dP
+        ok = mbar_wait(bar(C_DPFULL), g & 1u, abort_flag, p.status, 34);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+          const int c = half + 2 * ci;
+          tmem_ld32(lane_addr + TM_DP + c * 32, tv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e++) tv[e] = __float_as_uint(fa_round_tf32(pr[ci * 32 + e] * (__uint_as_float(tv[e]) - Dv)));
+          tmem_st32(lane_addr + TM_DP + c * 32, tv);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar(C_DSFULL));
+      }
+      if (ok) {
+        pending = true;
+        pend_off = ((long long)b * p.S + qi) * p.ld_dq + h * DH;
       }
     }
+    if (ok && pending) ok = flush_dq();
   }
   tc_fence_before();
   __syncthreads();
@@ -801,24 +866,24 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Backward, second kernel: dK and dV of one block of 128 keys, accumulated over the query blocks that see it.
+// Backward, second kernel: dK and dV of one block of 128 keys, accumulated over the 128-query blocks that see it.
 // The contraction of both products runs over the queries, so the tensor core needs P^T and dS^T with the KEY
 // index on the TMEM lanes.  The kernel therefore rebuilds the scores transposed, S^T = K_j.Q_i^T and
-// dP^T = V_j.dO_i^T (both operands K-major), lets each thread (= one key) form its row of P^T and dS^T from the
-// saved row statistics of the queries, and writes them to shared memory as K-major A operands of
+// dP^T = V_j.dO_i^T (both operands K-major); each thread (= one key) turns its row of S^T into P^T and its row of
+// dP^T into dS^T IN PLACE in tensor memory, from the saved row statistics of the queries, and the accumulating products
 //   dV_j += P^T . dO_i      dK_j += dS^T . Q_i        (dO_i and Q_i as MN-major B operands)
-// Nothing score-sized is written to global memory.  Query blocks are 64 rows here (shared memory budget):
-//   K_j, V_j 32 KiB each (resident), Q_i, dO_i as K-major and as MN-major tiles 16 KiB each, P^T, dS^T 32 KiB each.
-// TMEM: two buffers of S^T / dP^T ([0,128) and [128,256)), dV [256,320), dK [320,384): the score products of the next
-// query block run while the compute warps work on the current one.  The K-major copies of Q_i / dO_i are released as
-// soon as the score products have read them, the MN-major copies after the accumulating products.
-constexpr int BQ2 = 64;
-constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 81920, CO_QMN = 98304, CO_DOMN = 114688, CO_PT = 131072,
-                   CO_DST = 163840, CO_STAT = 196608, CO_BAR = 197632;
+// read their A operand from there.  Nothing score-sized touches shared or global memory.
+// Order on the tensor pipe: ... dP^T_i, S^T_{i+1}, dV_i, dK_i, dP^T_{i+1} ...: the next block's scores are issued before
+// the issuer waits for this block's P^T, so its exponentials run under dV_i and dK_i; dP^T_{i+1} overwrites dS^T_i after
+// dK_i has read it, and S^T_{i+2} overwrites P^T_i after dV_i (issue order, no barrier).
+// Shared memory (192 KiB): K_j, V_j (resident), Q_i, dO_i as K-major and as MN-major tiles, 32 KiB each; the producer
+// refills each of the four per-block tiles in the order in which the pipe releases them (Q_i runs one block ahead).
+// TMEM: S^T/P^T [0,128) and [128,256), dP^T/dS^T [256,384), dV [384,448), dK [448,512).
+constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 98304, CO_QMN = 131072, CO_DOMN = 163840, CO_BAR = 196608;
 constexpr int FA2_SMEM = CO_BAR + 256 + 1024;
-constexpr uint32_t T2_ST = 0, T2_DPT = 64, T2_BUF = 128, T2_DV = 256, T2_DK = 320;   // S^T / dP^T double-buffered (+T2_BUF)
-enum { D_KVFULL = 0, D_QKFULL = 1, D_QKEMPTY = 2, D_QMNFULL = 3, D_QMNEMPTY = 4, D_STFULL = 5, D_STEMPTY = 7, D_PTFULL = 9,
-       D_ACCDONE = 10, D_KVEMPTY = 11, D_COUNT = 12 };
+constexpr uint32_t T2_ST = 0, T2_DPT = 256, T2_DV = 384, T2_DK = 448;
+enum { D_KFULL = 0, D_KEMPTY, D_VFULL, D_VEMPTY, D_QKFULL, D_QKEMPTY, D_DOKFULL, D_DOKEMPTY, D_QMNFULL, D_QMNEMPTY, D_DOMNFULL,
+       D_DOMNEMPTY, D_STFULL /* two */, D_STFULL1, D_DPTFULL, D_PTFULL, D_DSTFULL, D_ACCDONE, D_COUNT };
 
 struct FaBwd2Params {
   int S, H, n_kb, causal;
@@ -844,20 +909,20 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Persistent loop over (sequence, head, key block) items, heaviest first (key block 0 is seen by every query block).
-  // u counts 64-query iterations over all items of this CTA, it counts items; every barrier phase derives from them.
+  // u counts query blocks over all items of this CTA, it counts items; every barrier phase derives from them.
   const int n_bh = p.n_items / p.n_kb;
-  const int n_q = p.S / BQ2;
+  const int n_q = p.S / BQ;
   auto item_coords = [&](int item, int& kbk, int& h, int& b, int& i0, int& n_it) {
     kbk = item / n_bh;
     const int bh = item - kbk * n_bh;
     h = bh % p.H;
     b = bh / p.H;
-    i0 = p.causal ? kbk * (BKV / BQ2) : 0;   // first 64-row query block that sees this key block
+    i0 = p.causal ? kbk : 0;   // first query block that sees this key block
     n_it = n_q - i0;
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_STEMPTY || i == D_STEMPTY + 1 || i == D_PTFULL) ? 256u : 1u);
+    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_PTFULL || i == D_DSTFULL) ? 256u : 1u);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -875,68 +940,85 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
+      // cursor of the K-major Q tile (and, at the first block of an item, of K_j): one block ahead of the other loads
+      int q_item = blockIdx.x, q_i = 0, q_nit = 0, q_kbk = 0, q_h = 0, q_b = 0, q_i0 = 0;
+      uint32_t q_u = 0, q_it = 0;
+      if (q_item < p.n_items) item_coords(q_item, q_kbk, q_h, q_b, q_i0, q_nit);
+      auto load_qk = [&]() {
+        if (q_item >= p.n_items) return true;
+        if (q_i == 0) {
+          if (!mbar_wait(bar(D_KEMPTY), (q_it & 1u) ^ 1u, abort_flag, p.status, 41)) return false;   // previous item's last S^T
+          mbar_expect_tx(bar(D_KFULL), BKV * DH * 4);
+          for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + CO_K + kb * 16384, &tmK, bar(D_KFULL), kb * 32, q_kbk * BKV, q_h, q_b);
+        }
+        if (!mbar_wait(bar(D_QKEMPTY), (q_u & 1u) ^ 1u, abort_flag, p.status, 31)) return false;
+        mbar_expect_tx(bar(D_QKFULL), BQ * DH * 4);
+        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + CO_Q + kb * 16384, &tmQ, bar(D_QKFULL), kb * 32, (q_i0 + q_i) * BQ, q_h, q_b);
+        q_u++;
+        if (++q_i == q_nit) {
+          q_item += gridDim.x;
+          q_it++;
+          q_i = 0;
+          if (q_item < p.n_items) item_coords(q_item, q_kbk, q_h, q_b, q_i0, q_nit);
+        }
+        return true;
+      };
+      ok = load_qk();
       uint32_t u = 0, it = 0;
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
         int kbk, h, b, i0, n_it;
         item_coords(item, kbk, h, b, i0, n_it);
-        ok = mbar_wait(bar(D_KVEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 41);   // previous item's score products done
-        if (!ok) break;
-        mbar_expect_tx(bar(D_KVFULL), 2 * BKV * DH * 4);
-        for (int kb = 0; kb < 2; kb++) {
-          tma_load_4d(smem_base + CO_K + kb * 16384, &tmK, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
-          tma_load_4d(smem_base + CO_V + kb * 16384, &tmV, bar(D_KVFULL), kb * 32, kbk * BKV, h, b);
-        }
         for (int i = 0; i < n_it && ok; i++, u++) {
           const uint32_t ph = u & 1u;
-          const int q0 = (i0 + i) * BQ2;
-          ok = mbar_wait(bar(D_QKEMPTY), ph ^ 1u, abort_flag, p.status, 31);
-          if (!ok) break;
-          mbar_expect_tx(bar(D_QKFULL), 2 * BQ2 * DH * 4);
-          for (int kb = 0; kb < 2; kb++) {
-            tma_load_4d(smem_base + CO_Q + kb * 8192, &tmQ, bar(D_QKFULL), kb * 32, q0, h, b);
-            tma_load_4d(smem_base + CO_DO + kb * 8192, &tmDO, bar(D_QKFULL), kb * 32, q0, h, b);
+          const int q0 = (i0 + i) * BQ;
+          if (i == 0) {
+            ok = mbar_wait(bar(D_VEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 42);   // previous item's last dP^T
+            if (!ok) break;
+            mbar_expect_tx(bar(D_VFULL), BKV * DH * 4);
+            for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + CO_V + kb * 16384, &tmV, bar(D_VFULL), kb * 32, kbk * BKV, h, b);
           }
+          ok = mbar_wait(bar(D_DOKEMPTY), ph ^ 1u, abort_flag, p.status, 43);
+          if (!ok) break;
+          mbar_expect_tx(bar(D_DOKFULL), BQ * DH * 4);
+          for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + CO_DO + kb * 16384, &tmDO, bar(D_DOKFULL), kb * 32, q0, h, b);
+          ok = load_qk();   // Q of the NEXT block: its tile is released by S^T of this block, before dV / dK of the previous one
+          if (!ok) break;
+          ok = mbar_wait(bar(D_DOMNEMPTY), ph ^ 1u, abort_flag, p.status, 44);
+          if (!ok) break;
+          mbar_expect_tx(bar(D_DOMNFULL), BQ * DH * 4);
+          for (int c = 0; c < 4; c++) tma_load_5d(smem_base + CO_DOMN + c * 8192, &tmDOmn, bar(D_DOMNFULL), 0, q0 + 32 * c, 0, h, b);
           ok = mbar_wait(bar(D_QMNEMPTY), ph ^ 1u, abort_flag, p.status, 39);
           if (!ok) break;
-          mbar_expect_tx(bar(D_QMNFULL), 2 * BQ2 * DH * 4);
-          for (int c = 0; c < 2; c++) {
-            tma_load_5d(smem_base + CO_QMN + c * 8192, &tmQmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
-            tma_load_5d(smem_base + CO_DOMN + c * 8192, &tmDOmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
-          }
+          mbar_expect_tx(bar(D_QMNFULL), BQ * DH * 4);
+          for (int c = 0; c < 4; c++) tma_load_5d(smem_base + CO_QMN + c * 8192, &tmQmn, bar(D_QMNFULL), 0, q0 + 32 * c, 0, h, b);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_st = fa_idesc(BKV, BQ2, 0, 0), idesc_acc = fa_idesc(BKV, DH, 0, 1);
+      const uint32_t idesc_st = fa_idesc(BKV, BQ, 0, 0), idesc_acc = fa_idesc(BKV, DH, 0, 1);
       bool ok = true;
-      // cursor of the next pair of score products: one iteration ahead of the accumulating products, across items
+      // cursor of the next S^T product: one block ahead of the other three products, across items
       int s_item = blockIdx.x, s_i = 0, s_nit = 0;
       uint32_t s_u = 0, s_it = 0;
       if (s_item < p.n_items) { int a, b2, c, d2; item_coords(s_item, a, b2, c, d2, s_nit); }
-      auto issue_scores = [&]() {   // S^T and dP^T of the next query block into TMEM buffer s_u & 1
+      auto issue_st = [&]() {
         if (s_item >= p.n_items) return true;
-        const int bf = s_u & 1;
-        if (s_i == 0 && !mbar_wait(bar(D_KVFULL), s_it & 1u, abort_flag, p.status, 32)) return false;
+        const uint32_t bf = s_u & 1u;
+        if (s_i == 0 && !mbar_wait(bar(D_KFULL), s_it & 1u, abort_flag, p.status, 32)) return false;
         if (!mbar_wait(bar(D_QKFULL), s_u & 1u, abort_flag, p.status, 33)) return false;
-        if (!mbar_wait(bar(D_STEMPTY + bf), ((s_u >> 1) & 1u) ^ 1u, abort_flag, p.status, 34)) return false;
         tc_fence_after();
         for (int kb = 0; kb < 2; kb++) {
           const uint64_t ak = make_smem_desc(smem_base + CO_K + kb * 16384, 16u, 1024u, 2u);
-          const uint64_t bq = make_smem_desc(smem_base + CO_Q + kb * 8192, 16u, 1024u, 2u);
-          const uint64_t av = make_smem_desc(smem_base + CO_V + kb * 16384, 16u, 1024u, 2u);
-          const uint64_t bd = make_smem_desc(smem_base + CO_DO + kb * 8192, 16u, 1024u, 2u);
+          const uint64_t bq = make_smem_desc(smem_base + CO_Q + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
-          for (int k = 0; k < 4; k++) {
-            umma_tf32(tmem_base + bf * T2_BUF + T2_ST, ak + 2u * k, bq + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
-            umma_tf32(tmem_base + bf * T2_BUF + T2_DPT, av + 2u * k, bd + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
-          }
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base + T2_ST + bf * 128, ak + 2u * k, bq + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
         }
         umma_commit(bar(D_STFULL + bf));
-        umma_commit(bar(D_QKEMPTY));   // the K-major copies of Q_i, dO_i may be replaced
+        umma_commit(bar(D_QKEMPTY));
         s_u++;
-        if (++s_i == s_nit) {          // last score products of the item: K_j, V_j may be replaced
-          umma_commit(bar(D_KVEMPTY));
+        if (++s_i == s_nit) {          // last S^T of the item: K_j may be replaced
+          umma_commit(bar(D_KEMPTY));
           s_item += gridDim.x;
           s_it++;
           s_i = 0;
@@ -944,28 +1026,46 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
         return true;
       };
-      uint32_t u = 0;
-      ok = issue_scores();
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      uint32_t u = 0, it = 0;
+      ok = issue_st();
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
         int kbk, h, b, i0, n_it;
         item_coords(item, kbk, h, b, i0, n_it);
         for (int i = 0; i < n_it && ok; i++, u++) {
-          const uint32_t ph = u & 1u;
-          if (s_u == u + 1) ok = issue_scores();   // overlaps the compute warps' work on this block
-          if (!ok) break;
-          ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35) && mbar_wait(bar(D_QMNFULL), ph, abort_flag, p.status, 40);
+          const uint32_t ph = u & 1u, bf = u & 1u;
+          if (i == 0) ok = mbar_wait(bar(D_VFULL), it & 1u, abort_flag, p.status, 34);
+          ok = ok && mbar_wait(bar(D_DOKFULL), ph, abort_flag, p.status, 45);
           if (!ok) break;
           tc_fence_after();
-          for (int c = 0; c < 2; c++) {   // 32 queries per chunk
-            const uint64_t ap = make_smem_desc(smem_base + CO_PT + c * 16384, 16u, 1024u, 2u);
-            const uint64_t as = make_smem_desc(smem_base + CO_DST + c * 16384, 16u, 1024u, 2u);
+          for (int kb = 0; kb < 2; kb++) {
+            const uint64_t av = make_smem_desc(smem_base + CO_V + kb * 16384, 16u, 1024u, 2u);
+            const uint64_t bd = make_smem_desc(smem_base + CO_DO + kb * 16384, 16u, 1024u, 2u);
+#pragma unroll
+            for (int k = 0; k < 4; k++) umma_tf32(tmem_base + T2_DPT, av + 2u * k, bd + 2u * k, idesc_st, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(bar(D_DPTFULL));
+          umma_commit(bar(D_DOKEMPTY));
+          if (i == n_it - 1) umma_commit(bar(D_VEMPTY));
+          if (s_u == u + 1) ok = issue_st();   // S^T of the next block: its exponentials overlap dV and dK of this one
+          if (!ok) break;
+          ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35) && mbar_wait(bar(D_DOMNFULL), ph, abort_flag, p.status, 40);
+          if (!ok) break;
+          tc_fence_after();
+          for (int c = 0; c < 4; c++) {   // 32 queries per chunk, 8 per instruction; A operand = P^T in tensor memory
             const uint64_t bdo = make_smem_desc(smem_base + CO_DOMN + c * 8192, 4096u, 512u, 1u);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+              umma_tf32_ts(tmem_base + T2_DV, tmem_base + T2_ST + bf * 128 + c * 32 + k * 8, bdo + 64u * k, idesc_acc, (i | c | k) ? 1u : 0u);
+          }
+          umma_commit(bar(D_DOMNEMPTY));
+          ok = mbar_wait(bar(D_DSTFULL), ph, abort_flag, p.status, 46) && mbar_wait(bar(D_QMNFULL), ph, abort_flag, p.status, 47);
+          if (!ok) break;
+          tc_fence_after();
+          for (int c = 0; c < 4; c++) {
             const uint64_t bq = make_smem_desc(smem_base + CO_QMN + c * 8192, 4096u, 512u, 1u);
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-              umma_tf32(tmem_base + T2_DV, ap + 2u * k, bdo + 64u * k, idesc_acc, (i | c | k) ? 1u : 0u);
-              umma_tf32(tmem_base + T2_DK, as + 2u * k, bq + 64u * k, idesc_acc, (i | c | k) ? 1u : 0u);
-            }
+            for (int k = 0; k < 4; k++)
+              umma_tf32_ts(tmem_base + T2_DK, tmem_base + T2_DPT + c * 32 + k * 8, bq + 64u * k, idesc_acc, (i | c | k) ? 1u : 0u);
           }
           umma_commit(bar(D_ACCDONE));
           umma_commit(bar(D_QMNEMPTY));
@@ -974,87 +1074,110 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
   } else {
     const int q4 = warp & 3;
-    const int half = (warp - 2) >> 2;          // which 32-query chunk of every block this warp handles
+    const int half = (warp - 2) >> 2;          // the two warps of a lane quarter take alternate 32-query chunks
     const int row = q4 * 32 + lane;            // key inside the block
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
     bool ok = true;
-    uint32_t sv[32], dv[32];
+    uint32_t tv[32];
+    float prs[64];
     uint32_t u = 0;
+    bool pending = false;        // a finished item whose dV / dK tiles are still to be read
+    long long pend_off = 0;
+    auto flush_acc = [&]() {     // after dK of block u-1 (the pending item's last) has been accumulated
+      if (!mbar_wait(bar(D_ACCDONE), (u - 1) & 1u, abort_flag, p.status, 38)) return false;
+      tc_fence_after();
+      for (int which = 0; which < 2; which++) {   // one tile after the other: 32 live registers instead of 64
+        tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + half * 32, tv);
+        tmem_ld_wait();
+        float* grow = (which ? p.dk : p.dv) + pend_off + half * 32;
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 o = make_float4(__uint_as_float(tv[e]), __uint_as_float(tv[e + 1]), __uint_as_float(tv[e + 2]), __uint_as_float(tv[e + 3]));
+          float4* dst = reinterpret_cast<float4*>(grow + e);
+          if (p.accumulate) {
+            const float4 old = *dst;
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          *dst = o;
+        }
+      }
+      tc_fence_before();   // both accumulators read before this thread publishes the next item's first P^T
+      pending = false;
+      return true;
+    };
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
       int kbk, h, b, i0, n_it;
       item_coords(item, kbk, h, b, i0, n_it);
       const int kj = kbk * BKV + row;            // key position in the sequence
       const long long stat_base = ((long long)b * p.H + h) * p.S;
       for (int i = 0; i < n_it && ok; i++, u++) {
-        const uint32_t ph = u & 1u;
-        const int q0 = (i0 + i) * BQ2;
-        // row statistics of the 32 queries this warp handles: every lane reads the same addresses (one transaction per
-        // warp, L1 hits); shuffles cost a warp-wide issue slot each and were a seventh of this loop
-        const float4* Lp = reinterpret_cast<const float4*>(p.lse + stat_base + q0 + half * 32);
-        const float4* Dp = reinterpret_cast<const float4*>(p.dsum + stat_base + q0 + half * 32);
-        const int bf = u & 1;
+        const uint32_t bf = u & 1u;
+        const int q0 = (i0 + i) * BQ;
+        // phase A: P^T over S^T.  The row statistics of the queries are the same addresses for every lane (one
+        // transaction per warp, L1 hits).
         ok = mbar_wait(bar(D_STFULL + bf), (u >> 1) & 1u, abort_flag, p.status, 36);
-        if (ok && i > 0) ok = mbar_wait(bar(D_ACCDONE), ph ^ 1u, abort_flag, p.status, 37);   // P^T / dS^T tiles free again
         if (!ok) break;
         tc_fence_after();
-        {
-          const int c = half;
-          tmem_ld32(lane_addr + bf * T2_BUF + T2_ST + c * 32, sv);
-          tmem_ld32(lane_addr + bf * T2_BUF + T2_DPT + c * 32, dv);
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+          const int c = half + 2 * ci;
+          const uint32_t ta = lane_addr + T2_ST + bf * 128 + c * 32;
+          tmem_ld32(ta, tv);
           tmem_ld_wait();
-          uint8_t* prow = smem_gen + CO_PT + c * 16384 + row * 128;
-          uint8_t* srow = smem_gen + CO_DST + c * 16384 + row * 128;
+          const float4* Lp = reinterpret_cast<const float4*>(p.lse + stat_base + q0 + c * 32);
 #pragma unroll
           for (int ch = 0; ch < 8; ch++) {
-            float4 pv, dsv;
-            float* pe = reinterpret_cast<float*>(&pv);
-            float* de = reinterpret_cast<float*>(&dsv);
-            const float4 L4 = __ldg(Lp + ch), D4 = __ldg(Dp + ch);
+            const float4 L4 = __ldg(Lp + ch);
             const float* Le = reinterpret_cast<const float*>(&L4);
-            const float* De = reinterpret_cast<const float*>(&D4);
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const int col = c * 32 + ch * 4 + e;            // query inside the block
               const bool vis = !p.causal || (q0 + col >= kj);
-              const float Lc = Le[e], Dc = De[e];
-              const float pr = vis ? fa_exp2(fmaf(__uint_as_float(sv[ch * 4 + e]), p.k2, -Lc)) : 0.f;
-              pe[e] = fa_round_tf32(pr);
-              de[e] = fa_round_tf32(pr * (__uint_as_float(dv[ch * 4 + e]) - Dc) * p.scale);
+              const float pr = vis ? fa_exp2(fmaf(__uint_as_float(tv[ch * 4 + e]), p.k2, -Le[e])) : 0.f;
+              prs[ci * 32 + ch * 4 + e] = pr * p.scale;
+              tv[ch * 4 + e] = __float_as_uint(fa_round_tf32(pr));
             }
-            *reinterpret_cast<float4*>(prow + ((ch ^ (row & 7)) << 4)) = pv;
-            *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) = dsv;
           }
+          tmem_st32(ta, tv);
         }
+        tmem_st_wait();
         tc_fence_before();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(bar(D_PTFULL));
-        mbar_arrive(bar(D_STEMPTY + bf));
-      }
-      if (ok && n_it > 0) ok = mbar_wait(bar(D_ACCDONE), (u - 1) & 1u, abort_flag, p.status, 38);
-      if (ok) {
-        tc_fence_after();
-        uint32_t kv[32];
-        const int c = half;
-        tmem_ld32(lane_addr + T2_DV + c * 32, sv);
-        tmem_ld32(lane_addr + T2_DK + c * 32, kv);
-        tmem_ld_wait();
-        tc_fence_before();   // both accumulators read before this thread publishes the next item's first P^T
-        for (int which = 0; which < 2; which++) {
-          float* grow = (which ? p.dk : p.dv) + ((long long)b * p.S + kj) * p.ld + h * DH;
-          const uint32_t* src = which ? kv : sv;
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            float4 o = make_float4(__uint_as_float(src[e]), __uint_as_float(src[e + 1]), __uint_as_float(src[e + 2]), __uint_as_float(src[e + 3]));
-            float4* dst = reinterpret_cast<float4*>(grow + c * 32 + e);
-            if (p.accumulate) {
-              const float4 old = *dst;
-              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-            }
-            *dst = o;
-          }
+        if (pending) {
+          ok = flush_acc();
+          if (!ok) break;
         }
+        mbar_arrive(bar(D_PTFULL));
+        // phase B: dS^T over dP^T
+        ok = mbar_wait(bar(D_DPTFULL), u & 1u, abort_flag, p.status, 37);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+          const int c = half + 2 * ci;
+          const uint32_t ta = lane_addr + T2_DPT + c * 32;
+          tmem_ld32(ta, tv);
+          tmem_ld_wait();
+          const float4* Dp = reinterpret_cast<const float4*>(p.dsum + stat_base + q0 + c * 32);
+#pragma unroll
+          for (int ch = 0; ch < 8; ch++) {
+            const float4 D4 = __ldg(Dp + ch);
+            const float* De = reinterpret_cast<const float*>(&D4);
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+              tv[ch * 4 + e] = __float_as_uint(fa_round_tf32(prs[ci * 32 + ch * 4 + e] * (__uint_as_float(tv[ch * 4 + e]) - De[e])));
+          }
+          tmem_st32(ta, tv);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar(D_DSTFULL));
+      }
+      if (ok && n_it > 0) {
+        pending = true;
+        pend_off = ((long long)b * p.S + kj) * p.ld + h * DH;
       }
     }
+    if (ok && pending) ok = flush_acc();
   }
   tc_fence_before();
   __syncthreads();
@@ -1145,7 +1268,7 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
     attention_rowdot_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(dout, ld_dout, d->out, d->ld_out, dsum, rows, S, H);
     FML_LAUNCH_CHECK(ctx, "attention_rowdot_kernel");
   }
-  CUtensorMap tmQ, tmDO, tmK, tmV, tmKmn, tmQ64, tmDO64, tmQmn, tmDOmn;
+  CUtensorMap tmQ, tmDO, tmK, tmV, tmKmn, tmQmn, tmDOmn;
   int32_t rc;
   const int64_t s2 = (int64_t)S * d->ld_qkv, s2o = (int64_t)S * ld_dout;
   if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BQ, false, 0, &tmQ))) return rc;
@@ -1153,8 +1276,6 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   if ((rc = fml_tc_make_tmap(ctx, d->k, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BKV, false, 0, &tmK))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->v, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BKV, false, 0, &tmV))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->k, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmKmn))) return rc;
-  if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BQ2, false, 0, &tmQ64))) return rc;
-  if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, BQ2, false, 0, &tmDO64))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmQmn))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, 32, true, 2, &tmDOmn))) return rc;
   FML_ONCE_PER_DEVICE(ctx, {
@@ -1177,7 +1298,7 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   p2.dk = dk; p2.dv = dv; p2.ld = ld_dqkv; p2.accumulate = p.accumulate;
   p2.status = ctx->d_status;
   p2.n_items = (int)grid;
-  attention_bwd_dkv_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ64, tmDO64, tmQmn,
+  attention_bwd_dkv_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ, tmDO, tmQmn,
                                                                                                                     tmDOmn, p2);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dkv_kernel");
   return FML_OK;
