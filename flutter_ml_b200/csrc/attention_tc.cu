@@ -6,8 +6,9 @@
 // shared or global memory: the reference's transpose + matMul + scaleMatrix + softmaxMatrix + matMul chain
 // (lib/layertypes/singleHeadAttentionLayer.dart:77-86) becomes one pass over Q, K, V.
 //
-// One CTA = 576 threads:
-//   warp 0      TMA producer: Q once per item, then K_j and V_j through two independent three-stage rings
+// One CTA = 608 threads:
+//   warp 0      TMA producer: Q (two buffers, one item ahead) and K_j (two-stage ring); when all loads of an item are
+//               issued it prefetches the next item's first tiles into L2
 //   warp 1      MMA issuer: S_j = Q.K_j^T into one of two TMEM buffers (S_{j+1} is issued before P_j.V_j, so it runs
 //               under the softmax of block j), then O += P_j.V_j once the softmax warps have published P_j
 //   warps 2..17 softmax: thread = one query row (TMEM lane) and a quarter of the block's keys, 32 scores in registers
@@ -15,7 +16,10 @@
 //               reference m of a row is only moved when a block's maximum exceeds it by more than 2^8; until then the
 //               probabilities are formed against the old reference (they stay below 2^8, the row sum carries the same
 //               factor), so the accumulator in tensor memory needs no rescaling and the warps never wait for P.V.
-// Shared memory (224 KiB): Q 32 KiB, 3 x K 32 KiB, 3 x V 32 KiB.  TMEM: S/P buffers [0,128) and [128,256), O [256,320).
+//               The output pass of an item is deferred behind the first softmax of the next item.
+//   warp 18     TMA producer of V_j (two-stage ring)
+// Shared memory: 2 x Q, 2 x K, 2 x V of 32 KiB, 8 KiB row exchange.  TMEM: S/P buffers [0,128) and [128,256), two O
+// accumulators [256,320) and [320,384) that alternate from item to item.
 // V is consumed as an MN-major B operand (32-byte-atom swizzle, the layout notes of gemm_tc.cu apply).
 // Requirements: d_head = 64, seq_len a multiple of 128, 16-byte aligned rows.  Every mbarrier wait is bounded.
 #include <cstdlib>
@@ -32,13 +36,14 @@ using namespace fml_tc;
 namespace {
 
 constexpr int BQ = 128, BKV = 128, DH = 64;
-constexpr int FA_THREADS = 576;      // forward: producer, issuer, 16 softmax warps (four per TMEM lane quarter, 32 keys each)
-constexpr int FA_BWD_THREADS = 320;  // backward: producer, issuer, 8 compute warps (two per TMEM lane quarter, alternate 32-column chunks)
-constexpr uint32_t OFF_Q = 0, OFF_K = 32768, OFF_V = 131072, OFF_BAR = 229376, OFF_XCH = OFF_BAR + 256;
+constexpr int FA_THREADS = 608;      // forward: Q/K producer, issuer, 16 softmax warps (four per TMEM lane quarter, 32 keys each), V producer
+constexpr int FA_BWD_THREADS = 352;  // backward: producer, issuer, 8 compute warps (two per TMEM lane quarter, alternate 32-column chunks), store warp
+constexpr uint32_t OFF_Q = 0, OFF_K = 65536, OFF_V = 131072, OFF_XCH = 196608, OFF_BAR = 229376;   // forward: 2 x Q, 2 x K, 2 x V, row exchange
 constexpr int FA_SMEM = OFF_BAR + 256 + 2048 + 512;   // barriers, the row exchange (forward), alignment slack
-constexpr int KV_STAGES = 3;
-constexpr uint32_t TM_S = 0, TM_O = 256;
+constexpr int KV_STAGES = 2;
+constexpr uint32_t TM_S = 0, TM_O = 256;   // two S/P buffers of 128 columns, two O accumulators of 64 columns (alternate items)
 constexpr int FA_MAX_SEQ_TMEM_P = 512;    // longest sequence the tensor-memory forward kernel is used for (four key blocks per item)
+constexpr int FA_PREFETCH_BLOCKS = 4;       // key blocks of the NEXT work item a producer prefetches into L2
 constexpr float FA_RESCALE_LOG2 = 8.f;   // a row's exponent reference moves only when a block maximum exceeds it by 2^8
 
 struct FaParams {
@@ -50,12 +55,24 @@ struct FaParams {
   float* out; long long ld_out;
   float* lse;            // [n_seq][H][S]: m + log2(l) of every row in the scaled base-2 domain, or NULL
   int* status;
+  long long* prof;       // -DFML_FA_PROFILE builds: clock64 stamps of key blocks 8..15 of CTA 0, else NULL
 };
+
+// Phase stamps for the diagnostics build (-DFML_FA_PROFILE): slot k of key block g, blocks 8..15 of CTA 0 only.
+#ifdef FML_FA_PROFILE
+#define FA_STAMP(prof, g, k) do { if ((prof) && blockIdx.x == 0 && (g) >= 8u && (g) < 16u) (prof)[((g) - 8u) * 16u + (k)] = clock64(); } while (0)
+#define FA_TOTAL_BEGIN() const long long fa_c0 = clock64(); const unsigned long long fa_n0 = globaltimer_ns()
+#define FA_TOTAL_END(prof) do { if ((prof) && threadIdx.x == 0) { (prof)[128 + 2 * blockIdx.x] = clock64() - fa_c0; (prof)[129 + 2 * blockIdx.x] = (long long)(globaltimer_ns() - fa_n0); } } while (0)
+#else
+#define FA_STAMP(prof, g, k) do { } while (0)
+#define FA_TOTAL_BEGIN() do { } while (0)
+#define FA_TOTAL_END(prof) do { } while (0)
+#endif
 
 // barriers: Q full/empty, K ring full/empty, V ring full/empty, S full (per buffer), P full (per buffer), P.V done (per
 // buffer), O read by the softmax warps
-enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 5, B_VFULL = 8, B_VEMPTY = 11, B_SFULL = 14, B_PFULL = 16, B_PVDONE = 18,
-       B_OEMPTY = 20, B_ROW = 21 /* one per lane quarter: the four threads of a row meet here */, B_COUNT = 25 };
+enum { B_QFULL = 0, B_QEMPTY = 2, B_KFULL = 4, B_KEMPTY = 6, B_VFULL = 8, B_VEMPTY = 10, B_SFULL = 12, B_PFULL = 14, B_PVDONE = 16,
+       B_OEMPTY = 18 /* one per O accumulator */, B_ROW = 20 /* one per lane quarter: the four threads of a row meet here */, B_COUNT = 24 };
 
 // 2^x on the special-function unit with flush-to-zero: the library exp2f adds a rescaling sequence for results below
 // 2^-126, which are zero for every purpose here
@@ -87,7 +104,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The layout leaves 512 bytes of slack for rounding the dynamic shared memory base up to 1 KiB.  Should a driver ever
   // hand out a base that needs more, every thread leaves here (same condition for all) and the host reads code 7.
-  if ((smem_base - smem_u32(smem_raw)) + OFF_XCH + 2048u > (uint32_t)FA_SMEM) {
+  if ((smem_base - smem_u32(smem_raw)) + OFF_BAR + 256u > (uint32_t)FA_SMEM) {
     if (threadIdx.x == 0) atomicCAS(p.status, 0, 7);
     return;
   }
@@ -98,6 +115,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   // producer and the MMA issuer run ahead into the next item while the softmax warps finish the current one.
   const int n_bh = p.n_items / p.n_qb;
   auto item_coords = [&](int item, int& qb, int& h, int& b, int& n_kv) {
+    // CTAs walk the item list in alternating directions from round to round (full rounds only), which evens out the block
+    // counts: with plain striding CTA c gets the same rank in every round and the heaviest CTAs end 4 % above the mean.
+    {
+      const int G = gridDim.x, k = item / G;
+      if ((k & 1) && k < p.n_items / G) item = k * G + (G - 1 - (item - k * G));
+    }
     qb = p.n_qb - 1 - item / n_bh;
     const int bh = item - (item / n_bh) * n_bh;
     h = bh % p.H;
@@ -107,7 +130,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < B_COUNT; i++) {
-      const bool from_softmax = (i == B_PFULL || i == B_PFULL + 1 || i == B_OEMPTY);
+      const bool from_softmax = (i == B_PFULL || i == B_PFULL + 1 || i == B_OEMPTY || i == B_OEMPTY + 1);
       mbar_init(bar(i), from_softmax ? 512u : (i >= B_ROW ? 128u : 1u));
     }
     *abort_flag = 0;
@@ -123,6 +146,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  FA_TOTAL_BEGIN();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -132,11 +156,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
         int qb, h, b, n_kv;
         item_coords(item, qb, h, b, n_kv);
-        // Q is single-buffered: the previous item's last S product must have read it
-        ok = mbar_wait(bar(B_QEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 10);
+        // Q has two buffers: this load is issued while the previous item is still being worked on
+        const uint32_t qs = it & 1u;
+        ok = mbar_wait(bar(B_QEMPTY + qs), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 10);
         if (!ok) break;
-        mbar_expect_tx(bar(B_QFULL), BQ * DH * 4);
-        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + kb * 16384, &tmQ, bar(B_QFULL), kb * 32, qb * BQ, h, b);
+        mbar_expect_tx(bar(B_QFULL + qs), BQ * DH * 4);
+        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + qs * 32768 + kb * 16384, &tmQ, bar(B_QFULL + qs), kb * 32, qb * BQ, h, b);
         for (int j = 0; j < n_kv && ok; j++, g++) {
           const int s = g % KV_STAGES;
           const uint32_t ph = (g / KV_STAGES) & 1u;
@@ -145,6 +170,33 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           mbar_expect_tx(bar(B_KFULL + s), BKV * DH * 4);
           for (int kb = 0; kb < 2; kb++)
             tma_load_4d(smem_base + OFF_K + s * 32768 + kb * 16384, &tmK, bar(B_KFULL + s), kb * 32, j * BKV, h, b);
+        }
+        if (ok && item + (int)gridDim.x < p.n_items) {
+          // This thread would now only wait for a K buffer: it brings the next item's Q and first key/value blocks into L2
+          // meanwhile, so that their loads, which are issued only when the buffers come free, do not pay the DRAM latency
+          // (about 4000 cycles under load, measured) on top.
+          int qb2, h2, b2, n2;
+          item_coords(item + gridDim.x, qb2, h2, b2, n2);
+          for (int kb = 0; kb < 2; kb++) tma_prefetch_4d(&tmQ, kb * 32, qb2 * BQ, h2, b2);
+          for (int j = 0; j < min(n2, FA_PREFETCH_BLOCKS); j++) {
+            for (int kb = 0; kb < 2; kb++) tma_prefetch_4d(&tmK, kb * 32, j * BKV, h2, b2);
+            for (int c = 0; c < 4; c++) tma_prefetch_5d(&tmV, 0, j * BKV + 32 * c, 0, h2, b2);
+          }
+        }
+      }
+    }
+  } else if (warp == FA_THREADS / 32 - 1) {
+    // ------------------------------------------------------------------ V producer (its own thread: a V buffer comes free
+    // one P.V product later than the K buffer of the same block, and one thread loading both held the K loads back)
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t g = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        for (int j = 0; j < n_kv && ok; j++, g++) {
+          const int s = g % KV_STAGES;
+          const uint32_t ph = (g / KV_STAGES) & 1u;
           ok = mbar_wait(bar(B_VEMPTY + s), ph ^ 1u, abort_flag, p.status, 9);
           if (!ok) break;
           mbar_expect_tx(bar(B_VFULL + s), BKV * DH * 4);
@@ -169,11 +221,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int ks = s_g % KV_STAGES;
         const uint32_t kph = (s_g / KV_STAGES) & 1u;
         const int buf = s_g & 1;
-        if (s_j == 0 && !mbar_wait(bar(B_QFULL), s_it & 1u, abort_flag, p.status, 12)) return false;
+        const uint32_t qs = s_it & 1u;
+        if (s_j == 0 && !mbar_wait(bar(B_QFULL + qs), (s_it >> 1) & 1u, abort_flag, p.status, 12)) return false;
         if (!mbar_wait(bar(B_KFULL + ks), kph, abort_flag, p.status, 13)) return false;
+        FA_STAMP(p.prof, s_g - 1u, 14);   // operands of the next S product ready
         tc_fence_after();
         for (int kb = 0; kb < 2; kb++) {
-          const uint64_t ad = make_smem_desc(smem_base + OFF_Q + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t ad = make_smem_desc(smem_base + OFF_Q + qs * 32768 + kb * 16384, 16u, 1024u, 2u);
           const uint64_t bd = make_smem_desc(smem_base + OFF_K + ks * 32768 + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
           for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + buf * 128, ad + 2u * k, bd + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
@@ -181,8 +235,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         umma_commit(bar(B_SFULL + buf));
         umma_commit(bar(B_KEMPTY + ks));   // K_j is read by nothing else
         s_g++;
-        if (++s_j == s_nkv) {   // last S of its item: Q may be replaced
-          umma_commit(bar(B_QEMPTY));
+        if (++s_j == s_nkv) {   // last S of its item: this Q buffer may be replaced
+          umma_commit(bar(B_QEMPTY + qs));
           s_item += gridDim.x;
           s_it++;
           s_j = 0;
@@ -199,22 +253,28 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const int vs = g % KV_STAGES;
           const uint32_t vph = (g / KV_STAGES) & 1u;
           const int buf = g & 1;
+          FA_STAMP(p.prof, g, 8);
           if (s_g == g + 1) ok = issue_next_s();   // keep one S product ahead
           if (!ok) break;
-          // the first P.V of an item overwrites O: the softmax warps must have read the previous item's output
-          if (j == 0 && it > 0) ok = mbar_wait(bar(B_OEMPTY), (it - 1) & 1u, abort_flag, p.status, 8);
+          FA_STAMP(p.prof, g, 9);
+          // the first P.V of an item overwrites its O accumulator (items alternate between two): the softmax warps must
+          // have read the output of the item before the previous one
+          if (j == 0) ok = mbar_wait(bar(B_OEMPTY + (it & 1u)), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 8);
           ok = ok && mbar_wait(bar(B_PFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 15) &&
                mbar_wait(bar(B_VFULL + vs), vph, abort_flag, p.status, 16);
           if (!ok) break;
+          FA_STAMP(p.prof, g, 10);
           tc_fence_after();
           for (int c = 0; c < 4; c++) {  // 32 keys per chunk of V, 8 keys per instruction
             const uint64_t bd = make_smem_desc(smem_base + OFF_V + vs * 32768 + c * 8192, 4096u, 512u, 1u);
 #pragma unroll
             for (int k = 0; k < 4; k++)
-              umma_tf32_ts(tmem_base + TM_O, tmem_base + TM_S + buf * 128 + c * 32 + k * 8, bd + 64u * k, idesc_pv, (j | c | k) ? 1u : 0u);
+              umma_tf32_ts(tmem_base + TM_O + (it & 1u) * 64, tmem_base + TM_S + buf * 128 + c * 32 + k * 8, bd + 64u * k, idesc_pv, (j | c | k) ? 1u : 0u);
           }
           umma_commit(bar(B_PVDONE + buf));
           umma_commit(bar(B_VEMPTY + vs));
+          FA_STAMP(p.prof, g, 11);
+          FA_STAMP(p.prof, g, 12 + (j == n_kv - 1));   // slot 13 is written on the last block of an item only
         }
       }
     }
@@ -229,7 +289,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int part = (warp - 2) >> 2;               // which 32 keys of every block, and which 16 output columns
     const int row = q4 * 32 + lane;                 // row inside the query block
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
-    float* xch = reinterpret_cast<float*>(smem_gen + OFF_XCH);   // [4 parts][128 rows]
+    // Row exchange, [2][4 parts][128 rows] of {block maximum, share of the finished item's row sum}: the buffers alternate
+    // from block to block, so one meeting per block is enough (a thread can be at most one meeting ahead of its
+    // partners, and then writes the other buffer), and the row sum of a finished item rides along with the first
+    // maximum of the next one instead of costing two more meetings.
+    float2* xch = reinterpret_cast<float2*>(smem_gen + OFF_XCH);
     // The meeting point of a row's four threads is an mbarrier, not a named hardware barrier: its wait is bounded like
     // every other wait of this kernel, so a CTA that gives up somewhere cannot leave partner warps parked forever.
     uint32_t n_sync = 0;
@@ -241,6 +305,33 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     uint32_t v0[32];
     uint32_t o16[16];
     uint32_t g = 0;
+    // The output pass of a finished item (wait for its last P.V, normalise, store) is deferred until the first block of the
+    // NEXT item has been turned into probabilities: done right away it kept the tensor pipe idle for the whole pass plus
+    // that block's softmax (measured: 6000 cycles per item against 2400 per key block).
+    bool pending = false;
+    float pend_m = 0.f, pend_l = 0.f, pend_lt = 0.f;   // exponent reference, this thread's share of the row sum, the row sum
+    long long pend_out = 0, pend_stat = 0;
+    uint32_t pend_g = 0, pend_o = 0, it = 0;
+    auto finish_item = [&]() {   // pend_lt is known by now
+      if (!mbar_wait(bar(B_PVDONE + (pend_g & 1)), (pend_g >> 1) & 1u, abort_flag, p.status, 19)) return false;
+      tc_fence_after();
+      tmem_ld16(lane_addr + TM_O + pend_o * 64 + part * 16, o16);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(bar(B_OEMPTY + pend_o));   // this accumulator may be overwritten by the item after the next
+      const float inv = 1.f / pend_lt;
+      float* orow = p.out + pend_out;
+#pragma unroll
+      for (int i = 0; i < 16; i += 4)
+        *reinterpret_cast<float4*>(orow + i) = make_float4(__uint_as_float(o16[i]) * inv, __uint_as_float(o16[i + 1]) * inv,
+                                                           __uint_as_float(o16[i + 2]) * inv, __uint_as_float(o16[i + 3]) * inv);
+      if (p.lse && part == 0) p.lse[pend_stat] = pend_m + log2f(pend_lt);
+#ifdef FML_FA_PROFILE
+      if (threadIdx.x == 64) FA_STAMP(p.prof, pend_g, 7);   // end of the item's output pass
+#endif
+      pending = false;
+      return true;
+    };
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
       int qb, h, b, n_kv;
       item_coords(item, qb, h, b, n_kv);
@@ -249,11 +340,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int j = 0; j < n_kv && ok; j++, g++) {
         const int buf = g & 1;
         const uint32_t sp = lane_addr + TM_S + buf * 128 + part * 32;
+#ifdef FML_FA_PROFILE
+        long long* const sprof = threadIdx.x == 64 ? p.prof : nullptr;
+#else
+        long long* const sprof = nullptr;
+        (void)sprof;
+#endif
+        FA_STAMP(sprof, g, 0);
         ok = mbar_wait(bar(B_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 17);
         if (!ok) break;
+        FA_STAMP(sprof, g, 1);
         tc_fence_after();
         tmem_ld32(sp, v0);
         tmem_ld_wait();
+        FA_STAMP(sprof, g, 2);
         const bool diag = p.causal && j == qb;
         const int lim = (diag ? row + 1 : BKV) - part * 32;   // valid keys of this row inside this thread's part
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -264,12 +364,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int e = 0; e < 32; e++) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(v0[e]));
         }
-        xch[part * 128 + row] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        float2* xb = xch + (g & 1u) * 512;
+        xb[part * 128 + row] = make_float2(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), pend_l);
         ok = row_sync();
         if (!ok) break;
-        const float bm = fmaxf(fmaxf(xch[row], xch[128 + row]), fmaxf(xch[256 + row], xch[384 + row])) * p.k2;   // k2 > 0
-        ok = row_sync();                             // all reads done before the next block's writes
-        if (!ok) break;
+        FA_STAMP(sprof, g, 3);
+        const float2 e0 = xb[row], e1 = xb[128 + row], e2 = xb[256 + row], e3 = xb[384 + row];
+        const float bm = fmaxf(fmaxf(e0.x, e1.x), fmaxf(e2.x, e3.x)) * p.k2;   // k2 > 0
+        if (pending) pend_lt = (e0.y + e1.y) + (e2.y + e3.y);
+        FA_STAMP(sprof, g, 4);
         if (bm > m + FA_RESCALE_LOG2) {
           // Move the reference (the four threads of the row take the same decision from the same numbers).  Block 0 of an
           // item always lands here (m = -inf) with nothing to rescale; later blocks rescale the accumulator in tensor
@@ -279,11 +382,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (!ok) break;
             tc_fence_after();
             const float alpha = fa_exp2(m - bm);
-            tmem_ld16(lane_addr + TM_O + part * 16, o16);
+            tmem_ld16(lane_addr + TM_O + (it & 1u) * 64 + part * 16, o16);
             tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 16; e++) o16[e] = __float_as_uint(__uint_as_float(o16[e]) * alpha);
-            tmem_st16(lane_addr + TM_O + part * 16, o16);
+            tmem_st16(lane_addr + TM_O + (it & 1u) * 64 + part * 16, o16);
             l *= alpha;
           }
           m = bm;
@@ -302,34 +405,39 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           v0[e] = __float_as_uint(p0);
         }
         l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        FA_STAMP(sprof, g, 5);
         tmem_st32(sp, v0);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(bar(B_PFULL + buf));
+        FA_STAMP(sprof, g, 6);
+        if (pending) {   // the previous item's output, now that this item's first P.V has its operand
+          ok = finish_item();
+          if (!ok) break;
+        }
       }
-      if (ok) ok = mbar_wait(bar(B_PVDONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1u, abort_flag, p.status, 19);
       if (ok) {
-        tc_fence_after();
-        tmem_ld16(lane_addr + TM_O + part * 16, o16);
-        tmem_ld_wait();
-        // the accumulator has been read: the next item's first P.V product may overwrite it
-        tc_fence_before();
-        mbar_arrive(bar(B_OEMPTY));
-        xch[part * 128 + row] = l;
-        ok = row_sync();
-        const float lt = (xch[row] + xch[128 + row]) + (xch[256 + row] + xch[384 + row]);
-        ok = ok && row_sync();
-        if (!ok) break;
-        const float inv = 1.f / lt;
-        float* orow = p.out + ((long long)b * p.S + qi) * p.ld_out + h * DH + part * 16;
-#pragma unroll
-        for (int i = 0; i < 16; i += 4)
-          *reinterpret_cast<float4*>(orow + i) = make_float4(__uint_as_float(o16[i]) * inv, __uint_as_float(o16[i + 1]) * inv,
-                                                             __uint_as_float(o16[i + 2]) * inv, __uint_as_float(o16[i + 3]) * inv);
-        if (p.lse && part == 0) p.lse[((long long)b * p.H + h) * p.S + qi] = m + log2f(lt);
+        pending = true;
+        pend_m = m;
+        pend_l = l;
+        pend_out = ((long long)b * p.S + qi) * p.ld_out + h * DH + part * 16;
+        pend_stat = ((long long)b * p.H + h) * p.S + qi;
+        pend_g = g - 1;
+        pend_o = it & 1u;
+      }
+      it++;
+    }
+    if (ok && pending) {   // the CTA's last item: no next block to ride along with
+      float2* xb = xch + (g & 1u) * 512;
+      xb[part * 128 + row] = make_float2(0.f, pend_l);
+      ok = row_sync();
+      if (ok) {
+        pend_lt = (xb[row].y + xb[128 + row].y) + (xb[256 + row].y + xb[384 + row].y);
+        ok = finish_item();
       }
     }
   }
+  FA_TOTAL_END(p.prof);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -608,12 +716,17 @@ namespace {
 //               registers.  Phase B (needs dP): dS = round_tf32(scale P (dP - D)) over dP in tensor memory.
 // The running counters g (key blocks) and it (items) drive every barrier phase, so all three roles run on across item
 // boundaries; the dQ tile of a finished item is read between phase A and phase B of the next item's first block.
-// Shared memory (224 KiB): Q 2 x 32 KiB, dO, K, V 32 KiB each, K(MN) 2 x 32 KiB.
+//   warp 10     stores: the dQ tile of a finished item goes from tensor memory through a swizzled shared-memory tile
+//               to global memory with one tile store (accumulate form: a tile reduction).  Written row by row from the
+//               registers (thread = row) the tile cost every warp 8 instructions x 32 separate lines, about 3000 cycles
+//               of load/store-unit time per item on the critical path (measured).
+// Shared memory (224 KiB): Q, dO, K, V 32 KiB each, K(MN) 2 x 32 KiB, dQ staging 32 KiB.  Q of the next item is
+// prefetched into L2 (two instructions), so its load after the item's last S product is short.
 // TMEM: S [0,128) and [128,256), dP/dS [256,384), dQ [384,448).
-constexpr uint32_t BO_Q = 0, BO_DO = 65536, BO_K = 98304, BO_V = 131072, BO_KMN = 163840;
+constexpr uint32_t BO_Q = 0, BO_DO = 32768, BO_K = 65536, BO_V = 98304, BO_KMN = 131072, BO_ST = 196608;
 constexpr uint32_t TM_DP = 256, TM_DQ = 384;
 enum { C_QFULL = 0, C_QEMPTY = 2, C_DOFULL = 4, C_DOEMPTY = 5, C_KFULL = 6, C_KEMPTY = 7, C_VFULL = 8, C_VEMPTY = 9, C_KMNFULL = 10,
-       C_KMNEMPTY = 12, C_SFULL = 14, C_SEMPTY = 16, C_DPFULL = 18, C_DSFULL = 19, C_DQDONE = 20, C_COUNT = 21 };
+       C_KMNEMPTY = 12, C_SFULL = 14, C_SEMPTY = 16, C_DPFULL = 18, C_DSFULL = 19, C_DQDONE = 20, C_STAGED = 21, C_STFREE = 22, C_COUNT = 23 };
 
 struct FaBwdParams {
   int S, H, n_qb, causal;
@@ -624,12 +737,13 @@ struct FaBwdParams {
   float* dq; long long ld_dq;
   int accumulate;
   int* status;
+  long long* prof;    // -DFML_FA_PROFILE builds, else NULL
 };
 
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                        const __grid_constant__ CUtensorMap tmKmn, const FaBwdParams p) {
+                        const __grid_constant__ CUtensorMap tmKmn, const __grid_constant__ CUtensorMap tmDQ, const FaBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -640,6 +754,12 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   // persistent loop over work items (heaviest first)
   const int n_bh = p.n_items / p.n_qb;
   auto item_coords = [&](int item, int& qb, int& h, int& b, int& n_kv) {
+    // CTAs walk the item list in alternating directions from round to round (full rounds only), which evens out the block
+    // counts: with plain striding CTA c gets the same rank in every round and the heaviest CTAs end 4 % above the mean.
+    {
+      const int G = gridDim.x, k = item / G;
+      if ((k & 1) && k < p.n_items / G) item = k * G + (G - 1 - (item - k * G));
+    }
     qb = p.n_qb - 1 - item / n_bh;
     const int bh = item - (item / n_bh) * n_bh;
     h = bh % p.H;
@@ -649,7 +769,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C_COUNT; i++) {
-      const bool from_compute = (i == C_SEMPTY || i == C_SEMPTY + 1 || i == C_DSFULL);
+      const bool from_compute = (i == C_SEMPTY || i == C_SEMPTY + 1 || i == C_DSFULL || i == C_STAGED);
       mbar_init(bar(i), from_compute ? 256u : 1u);
     }
     *abort_flag = 0;
@@ -665,6 +785,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  FA_TOTAL_BEGIN();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -673,11 +794,10 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
         int qb, h, b, n_kv;
         item_coords(item, qb, h, b, n_kv);
-        const uint32_t qs = it & 1u;
-        ok = mbar_wait(bar(C_QEMPTY + qs), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 20);   // last S of item it-2 has read it
+        ok = mbar_wait(bar(C_QEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 20);   // the previous item's last S has read it
         if (!ok) break;
-        mbar_expect_tx(bar(C_QFULL + qs), BQ * DH * 4);
-        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + BO_Q + qs * 32768 + kb * 16384, &tmQ, bar(C_QFULL + qs), kb * 32, qb * BQ, h, b);
+        mbar_expect_tx(bar(C_QFULL), BQ * DH * 4);
+        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + BO_Q + kb * 16384, &tmQ, bar(C_QFULL), kb * 32, qb * BQ, h, b);
         for (int j = 0; j < n_kv && ok; j++, g++) {
           const uint32_t ph = g & 1u, ms = g & 1u;
           ok = mbar_wait(bar(C_KEMPTY), ph ^ 1u, abort_flag, p.status, 22);
@@ -701,6 +821,13 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           if (!ok) break;
           mbar_expect_tx(bar(C_VFULL), BKV * DH * 4);
           for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + BO_V + kb * 16384, &tmV, bar(C_VFULL), kb * 32, j * BKV, h, b);
+          if (j == 0 && item + (int)gridDim.x < p.n_items) {
+            // Q of the next item into L2 (more prefetching was measured to cost more than it saves: a prefetch occupies
+            // this SM's copy engine like a load, and the loads of the running item queue behind it)
+            int qb2, h2, b2, n2;
+            item_coords(item + gridDim.x, qb2, h2, b2, n2);
+            for (int kb = 0; kb < 2; kb++) tma_prefetch_4d(&tmQ, kb * 32, qb2 * BQ, h2, b2);
+          }
         }
       }
     }
@@ -714,13 +841,14 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
       auto issue_next_s = [&]() {
         if (s_item >= p.n_items) return true;
-        const uint32_t buf = s_g & 1u, qs = s_it & 1u;
-        if (s_j == 0 && !mbar_wait(bar(C_QFULL + qs), (s_it >> 1) & 1u, abort_flag, p.status, 23)) return false;
+        const uint32_t buf = s_g & 1u;
+        if (s_j == 0 && !mbar_wait(bar(C_QFULL), s_it & 1u, abort_flag, p.status, 23)) return false;
         if (!mbar_wait(bar(C_KFULL), s_g & 1u, abort_flag, p.status, 24)) return false;
         if (!mbar_wait(bar(C_SEMPTY + buf), ((s_g >> 1) & 1u) ^ 1u, abort_flag, p.status, 25)) return false;   // phase A of block s_g-2 done
+        FA_STAMP(p.prof, s_g - 1u, 11);   // operands of the next S product ready
         tc_fence_after();
         for (int kb = 0; kb < 2; kb++) {
-          const uint64_t aq = make_smem_desc(smem_base + BO_Q + qs * 32768 + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t aq = make_smem_desc(smem_base + BO_Q + kb * 16384, 16u, 1024u, 2u);
           const uint64_t bk = make_smem_desc(smem_base + BO_K + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
           for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + buf * 128, aq + 2u * k, bk + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
@@ -728,8 +856,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         umma_commit(bar(C_SFULL + buf));
         umma_commit(bar(C_KEMPTY));
         s_g++;
-        if (++s_j == s_nkv) {   // last S of its item: this Q buffer may be replaced
-          umma_commit(bar(C_QEMPTY + qs));
+        if (++s_j == s_nkv) {   // last S of its item: Q may be replaced
+          umma_commit(bar(C_QEMPTY));
           s_item += gridDim.x;
           s_it++;
           s_j = 0;
@@ -745,9 +873,11 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         for (int j = 0; j < n_kv && ok; j++, g++) {
           const uint32_t ph = g & 1u, ms = g & 1u;
           // dP_g: overwrites dS_{g-1}, which dQ_{g-1} (issued earlier by this thread) has read by then
+          FA_STAMP(p.prof, g, 8);
           if (j == 0) ok = mbar_wait(bar(C_DOFULL), it & 1u, abort_flag, p.status, 26);
           ok = ok && mbar_wait(bar(C_VFULL), ph, abort_flag, p.status, 27);
           if (!ok) break;
+          FA_STAMP(p.prof, g, 9);
           tc_fence_after();
           for (int kb = 0; kb < 2; kb++) {
             const uint64_t ad = make_smem_desc(smem_base + BO_DO + kb * 16384, 16u, 1024u, 2u);
@@ -758,10 +888,13 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           umma_commit(bar(C_DPFULL));
           umma_commit(bar(C_VEMPTY));
           if (j == n_kv - 1) umma_commit(bar(C_DOEMPTY));
+          FA_STAMP(p.prof, g, 10);
           if (s_g == g + 1) ok = issue_next_s();   // S_{g+1} runs under the compute phase of block g
           if (!ok) break;
+          FA_STAMP(p.prof, g, 12);
           ok = mbar_wait(bar(C_DSFULL), ph, abort_flag, p.status, 28) && mbar_wait(bar(C_KMNFULL + ms), (g >> 1) & 1u, abort_flag, p.status, 29);
           if (!ok) break;
+          FA_STAMP(p.prof, g, 13);
           tc_fence_after();
           for (int c = 0; c < 4; c++) {   // 32 keys per chunk of K, 8 keys per instruction, A operand = dS in tensor memory
             const uint64_t bd = make_smem_desc(smem_base + BO_KMN + ms * 32768 + c * 8192, 4096u, 512u, 1u);
@@ -771,7 +904,29 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           }
           umma_commit(bar(C_DQDONE));
           umma_commit(bar(C_KMNEMPTY + ms));
+          FA_STAMP(p.prof, g, 14);
+          if (j == n_kv - 1) FA_STAMP(p.prof, g, 15);   // slot 15 on the last block of an item only
         }
+      }
+    }
+  } else if (warp == FA_BWD_THREADS / 32 - 1) {
+    // ------------------------------------------------------------------ store warp
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t it = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        ok = mbar_wait(bar(C_STAGED), it & 1u, abort_flag, p.status, 48);   // all 256 rows of the tile are in shared memory
+        if (!ok) break;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int kb = 0; kb < 2; kb++) {
+          if (p.accumulate) tma_reduce_add_4d(&tmDQ, smem_base + BO_ST + kb * 16384, kb * 32, qb * BQ, h, b);
+          else tma_store_4d(&tmDQ, smem_base + BO_ST + kb * 16384, kb * 32, qb * BQ, h, b);
+        }
+        tma_store_commit();
+        tma_store_wait_read();            // the staging tile has been read: the next item may overwrite it
+        mbar_arrive(bar(C_STFREE));
       }
     }
   } else {
@@ -782,40 +937,56 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     bool ok = true;
     uint32_t tv[32];
     float pr[64];
-    uint32_t g = 0;
+    uint32_t g = 0, n_flush = 0;
     bool pending = false;        // a finished item whose dQ tile is still to be read
-    long long pend_off = 0;
     auto flush_dq = [&]() {      // after dQ of block g-1 (the pending item's last) has been accumulated
       if (!mbar_wait(bar(C_DQDONE), (g - 1) & 1u, abort_flag, p.status, 30)) return false;
       tc_fence_after();
       tmem_ld32(lane_addr + TM_DQ + half * 32, tv);
       tmem_ld_wait();
       tc_fence_before();   // the accumulator has been read before this thread publishes the next item's first dS
-      float* qrow = p.dq + pend_off + half * 32;
+      if (!mbar_wait(bar(C_STFREE), (n_flush & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
+      uint8_t* srow = smem_gen + BO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, 16-byte chunks swizzled
 #pragma unroll
-      for (int e = 0; e < 32; e += 4) {
-        float4 o = make_float4(__uint_as_float(tv[e]), __uint_as_float(tv[e + 1]), __uint_as_float(tv[e + 2]), __uint_as_float(tv[e + 3]));
-        float4* dst = reinterpret_cast<float4*>(qrow + e);
-        if (p.accumulate) {
-          const float4 old = *dst;
-          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-        }
-        *dst = o;
-      }
+      for (int ch = 0; ch < 8; ch++)
+        *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) =
+            make_float4(__uint_as_float(tv[4 * ch]), __uint_as_float(tv[4 * ch + 1]), __uint_as_float(tv[4 * ch + 2]), __uint_as_float(tv[4 * ch + 3]));
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(bar(C_STAGED));
+      n_flush++;
       pending = false;
       return true;
     };
+    // The row statistics of an item are loaded one item ahead: read at the item's start they cost a DRAM round trip
+    // (2000 cycles, measured) in front of its first exponentials.
+    float L_next = 0.f, D_next = 0.f;
+    auto load_stats = [&](int item) {
+      if (item >= p.n_items) return;
+      int qb, h, b, n_kv;
+      item_coords(item, qb, h, b, n_kv);
+      const long long stat = ((long long)b * p.H + h) * p.S + qb * BQ + row;
+      L_next = __ldg(p.lse + stat);
+      D_next = __ldg(p.dsum + stat);
+    };
+    load_stats(blockIdx.x);
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
       int qb, h, b, n_kv;
       item_coords(item, qb, h, b, n_kv);
-      const int qi = qb * BQ + row;
-      const long long stat = ((long long)b * p.H + h) * p.S + qi;
-      const float L = p.lse[stat], Dv = p.dsum[stat];
+      const float L = L_next, Dv = D_next;
+      load_stats(item + gridDim.x);
       for (int j = 0; j < n_kv && ok; j++, g++) {
         const uint32_t buf = g & 1u;
         // phase A: probabilities of this thread's 64 columns from S alone
+#ifdef FML_FA_PROFILE
+        long long* const sprof = threadIdx.x == 64 ? p.prof : nullptr;
+#else
+        long long* const sprof = nullptr;
+        (void)sprof;
+#endif
+        FA_STAMP(sprof, g, 0);
         ok = mbar_wait(bar(C_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 33);
         if (!ok) break;
+        FA_STAMP(sprof, g, 1);
         tc_fence_after();
         const int lim = (p.causal && j == qb) ? row + 1 : BKV;
 #pragma unroll
@@ -829,13 +1000,16 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         tc_fence_before();
         mbar_arrive(bar(C_SEMPTY + buf));
+        FA_STAMP(sprof, g, 2);
         if (pending) {
           ok = flush_dq();
           if (!ok) break;
         }
+        FA_STAMP(sprof, g, 3);
         // phase B: dS over dP
         ok = mbar_wait(bar(C_DPFULL), g & 1u, abort_flag, p.status, 34);
         if (!ok) break;
+        FA_STAMP(sprof, g, 4);
         tc_fence_after();
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
@@ -849,14 +1023,13 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(bar(C_DSFULL));
+        FA_STAMP(sprof, g, 5);
       }
-      if (ok) {
-        pending = true;
-        pend_off = ((long long)b * p.S + qi) * p.ld_dq + h * DH;
-      }
+      if (ok) pending = true;
     }
     if (ok && pending) ok = flush_dq();
   }
+  FA_TOTAL_END(p.prof);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -876,14 +1049,15 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 // Order on the tensor pipe: ... dP^T_i, S^T_{i+1}, dV_i, dK_i, dP^T_{i+1} ...: the next block's scores are issued before
 // the issuer waits for this block's P^T, so its exponentials run under dV_i and dK_i; dP^T_{i+1} overwrites dS^T_i after
 // dK_i has read it, and S^T_{i+2} overwrites P^T_i after dV_i (issue order, no barrier).
-// Shared memory (192 KiB): K_j, V_j (resident), Q_i, dO_i as K-major and as MN-major tiles, 32 KiB each; the producer
-// refills each of the four per-block tiles in the order in which the pipe releases them (Q_i runs one block ahead).
+// Shared memory (224 KiB): K_j, V_j (resident), Q_i, dO_i as K-major and as MN-major tiles, 32 KiB each; the producer
+// refills each of the four per-block tiles in the order in which the pipe releases them (Q_i runs one block ahead);
+// 32 KiB staging tile through which the store warp writes dV, then dK, of a finished item with tile stores.
 // TMEM: S^T/P^T [0,128) and [128,256), dP^T/dS^T [256,384), dV [384,448), dK [448,512).
-constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 98304, CO_QMN = 131072, CO_DOMN = 163840, CO_BAR = 196608;
+constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 98304, CO_QMN = 131072, CO_DOMN = 163840, CO_ST = 196608, CO_BAR = 229376;
 constexpr int FA2_SMEM = CO_BAR + 256 + 1024;
 constexpr uint32_t T2_ST = 0, T2_DPT = 256, T2_DV = 384, T2_DK = 448;
 enum { D_KFULL = 0, D_KEMPTY, D_VFULL, D_VEMPTY, D_QKFULL, D_QKEMPTY, D_DOKFULL, D_DOKEMPTY, D_QMNFULL, D_QMNEMPTY, D_DOMNFULL,
-       D_DOMNEMPTY, D_STFULL /* two */, D_STFULL1, D_DPTFULL, D_PTFULL, D_DSTFULL, D_ACCDONE, D_COUNT };
+       D_DOMNEMPTY, D_STFULL /* two */, D_STFULL1, D_DPTFULL, D_PTFULL, D_DSTFULL, D_ACCDONE, D_STAGED, D_STFREE, D_COUNT };
 
 struct FaBwd2Params {
   int S, H, n_kb, causal;
@@ -900,7 +1074,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                          const __grid_constant__ CUtensorMap tmQmn, const __grid_constant__ CUtensorMap tmDOmn,
-                         const FaBwd2Params p) {
+                         const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV, const FaBwd2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -913,6 +1087,12 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   const int n_bh = p.n_items / p.n_kb;
   const int n_q = p.S / BQ;
   auto item_coords = [&](int item, int& kbk, int& h, int& b, int& i0, int& n_it) {
+    // CTAs walk the item list in alternating directions from round to round (full rounds only), which evens out the block
+    // counts: with plain striding CTA c gets the same rank in every round and the heaviest CTAs end 4 % above the mean.
+    {
+      const int G = gridDim.x, k = item / G;
+      if ((k & 1) && k < p.n_items / G) item = k * G + (G - 1 - (item - k * G));
+    }
     kbk = item / n_bh;
     const int bh = item - kbk * n_bh;
     h = bh % p.H;
@@ -922,7 +1102,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_PTFULL || i == D_DSTFULL) ? 256u : 1u);
+    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_PTFULL || i == D_DSTFULL || i == D_STAGED) ? 256u : 1u);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1072,6 +1252,29 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
       }
     }
+  } else if (warp == FA_BWD_THREADS / 32 - 1) {
+    // ------------------------------------------------------------------ store warp: dV, then dK, of every finished item
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t n = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        int kbk, h, b, i0, n_it;
+        item_coords(item, kbk, h, b, i0, n_it);
+        for (int which = 0; which < 2 && ok; which++, n++) {
+          ok = mbar_wait(bar(D_STAGED), n & 1u, abort_flag, p.status, 48);   // all 256 rows of the tile are in shared memory
+          if (!ok) break;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          const CUtensorMap* tm = which ? &tmDK : &tmDV;
+          for (int kb = 0; kb < 2; kb++) {
+            if (p.accumulate) tma_reduce_add_4d(tm, smem_base + CO_ST + kb * 16384, kb * 32, kbk * BKV, h, b);
+            else tma_store_4d(tm, smem_base + CO_ST + kb * 16384, kb * 32, kbk * BKV, h, b);
+          }
+          tma_store_commit();
+          tma_store_wait_read();          // the staging tile has been read and may be overwritten
+          mbar_arrive(bar(D_STFREE));
+        }
+      }
+    }
   } else {
     const int q4 = warp & 3;
     const int half = (warp - 2) >> 2;          // the two warps of a lane quarter take alternate 32-query chunks
@@ -1080,26 +1283,22 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     bool ok = true;
     uint32_t tv[32];
     float prs[64];
-    uint32_t u = 0;
+    uint32_t u = 0, n_st = 0;
     bool pending = false;        // a finished item whose dV / dK tiles are still to be read
-    long long pend_off = 0;
     auto flush_acc = [&]() {     // after dK of block u-1 (the pending item's last) has been accumulated
       if (!mbar_wait(bar(D_ACCDONE), (u - 1) & 1u, abort_flag, p.status, 38)) return false;
       tc_fence_after();
-      for (int which = 0; which < 2; which++) {   // one tile after the other: 32 live registers instead of 64
+      for (int which = 0; which < 2; which++, n_st++) {   // one tile after the other through the one staging tile
         tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + half * 32, tv);
         tmem_ld_wait();
-        float* grow = (which ? p.dk : p.dv) + pend_off + half * 32;
+        if (!mbar_wait(bar(D_STFREE), (n_st & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
+        uint8_t* srow = smem_gen + CO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, chunks swizzled
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          float4 o = make_float4(__uint_as_float(tv[e]), __uint_as_float(tv[e + 1]), __uint_as_float(tv[e + 2]), __uint_as_float(tv[e + 3]));
-          float4* dst = reinterpret_cast<float4*>(grow + e);
-          if (p.accumulate) {
-            const float4 old = *dst;
-            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-          }
-          *dst = o;
-        }
+        for (int ch = 0; ch < 8; ch++)
+          *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) =
+              make_float4(__uint_as_float(tv[4 * ch]), __uint_as_float(tv[4 * ch + 1]), __uint_as_float(tv[4 * ch + 2]), __uint_as_float(tv[4 * ch + 3]));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(bar(D_STAGED));
       }
       tc_fence_before();   // both accumulators read before this thread publishes the next item's first P^T
       pending = false;
@@ -1113,6 +1312,10 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       for (int i = 0; i < n_it && ok; i++, u++) {
         const uint32_t bf = u & 1u;
         const int q0 = (i0 + i) * BQ;
+        if (lane < 8 && i + 1 < n_it) {   // statistics of the next query block (2 x 512 bytes): the loads below then hit the cache
+          const float* nx = (lane < 4 ? p.lse : p.dsum) + stat_base + q0 + BQ + (lane & 3) * 32;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
+        }
         // phase A: P^T over S^T.  The row statistics of the queries are the same addresses for every lane (one
         // transaction per warp, L1 hits).
         ok = mbar_wait(bar(D_STFULL + bf), (u >> 1) & 1u, abort_flag, p.status, 36);
@@ -1172,10 +1375,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tc_fence_before();
         mbar_arrive(bar(D_DSTFULL));
       }
-      if (ok && n_it > 0) {
-        pending = true;
-        pend_off = ((long long)b * p.S + kj) * p.ld + h * DH;
-      }
+      if (ok && n_it > 0) pending = true;
     }
     if (ok && pending) ok = flush_acc();
   }
@@ -1243,9 +1443,45 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
   p.n_items = (int)items;
   p.round_p = getenv("FML_FA_NOROUND") ? 0 : 1;
   const unsigned grid = (unsigned)std::min<long long>(items, ctx->sm_count);
+  p.prof = nullptr;
+#ifdef FML_FA_PROFILE
+  static long long* prof_buf = nullptr;
+  static int prof_calls = 0;
+  if (!prof_buf) { cudaMalloc(&prof_buf, 512 * sizeof(long long)); }
+  cudaMemsetAsync(prof_buf, 0, 512 * sizeof(long long), ctx->stream);
+  p.prof = prof_buf;
+#endif
   if (S <= FA_MAX_SEQ_TMEM_P) attention_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
   else attention_fwd_long_kernel<<<grid, FA_LONG_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
   FML_LAUNCH_CHECK(ctx, "attention_fwd_kernel");
+#ifdef FML_FA_PROFILE
+  if (++prof_calls == 4) {
+    long long h[512];
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost);
+    fprintf(stderr, "attention fwd, CTA 0, key blocks 8..15, cycles relative to block 8's first stamp\n"
+                    "softmax: top | S full | S loaded | max exchanged | max read | P formed | P published | item end;  issuer: top | next S issued | P,V ready | PV issued | last-of-item\n");
+    const long long t0 = h[0];
+    for (int g = 0; g < 8; g++) {
+      fprintf(stderr, "g=%d sm:", g + 8);
+      for (int k = 0; k < 8; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
+      fprintf(stderr, "  is:");
+      for (int k = 8; k < 12; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
+      fprintf(stderr, " (next S operands ready %lld) %s\n", h[g * 16 + 14] ? h[g * 16 + 14] - t0 : -1, h[g * 16 + 13] ? "last" : "");
+    }
+    {
+      long long cmin = 1LL << 62, cmax = 0, csum = 0, nmax = 0;
+      int n = 0;
+      for (int c = 0; c < 148; c++) {
+        const long long cy = h[128 + 2 * c], ns = h[129 + 2 * c];
+        if (!cy) continue;
+        n++; csum += cy; cmin = cy < cmin ? cy : cmin; cmax = cy > cmax ? cy : cmax; nmax = ns > nmax ? ns : nmax;
+      }
+      if (n) fprintf(stderr, "per-CTA cycles over %d CTAs: min %lld avg %lld max %lld; longest CTA %lld ns; CTA 0: %lld cycles in %lld ns = %.3f GHz\n",
+                     n, cmin, csum / n, cmax, nmax, h[128], h[129], (double)h[128] / (double)h[129]);
+    }
+  }
+#endif
   return FML_OK;
 }
 
@@ -1268,7 +1504,7 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
     attention_rowdot_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(dout, ld_dout, d->out, d->ld_out, dsum, rows, S, H);
     FML_LAUNCH_CHECK(ctx, "attention_rowdot_kernel");
   }
-  CUtensorMap tmQ, tmDO, tmK, tmV, tmKmn, tmQmn, tmDOmn;
+  CUtensorMap tmQ, tmDO, tmK, tmV, tmKmn, tmQmn, tmDOmn, tmDQ, tmDK, tmDV;
   int32_t rc;
   const int64_t s2 = (int64_t)S * d->ld_qkv, s2o = (int64_t)S * ld_dout;
   if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BQ, false, 0, &tmQ))) return rc;
@@ -1277,6 +1513,9 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   if ((rc = fml_tc_make_tmap(ctx, d->v, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BKV, false, 0, &tmV))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->k, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmKmn))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmQmn))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, dq, DH, S, ld_dqkv, H, Bn, DH, (int64_t)S * ld_dqkv, 32, BQ, false, 0, &tmDQ))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, dk, DH, S, ld_dqkv, H, Bn, DH, (int64_t)S * ld_dqkv, 32, BKV, false, 0, &tmDK))) return rc;
+  if ((rc = fml_tc_make_tmap(ctx, dv, DH, S, ld_dqkv, H, Bn, DH, (int64_t)S * ld_dqkv, 32, BKV, false, 0, &tmDV))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, dout, DH, S, ld_dout, H, Bn, DH, s2o, 32, 32, true, 2, &tmDOmn))) return rc;
   FML_ONCE_PER_DEVICE(ctx, {
     FML_CUDA(ctx, cudaFuncSetAttribute(attention_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM));
@@ -1290,8 +1529,44 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   p.dq = dq; p.ld_dq = ld_dqkv; p.accumulate = accumulate ? 1 : 0;
   p.status = ctx->d_status;
   p.n_items = (int)grid;
-  attention_bwd_dq_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, p);
+  p.prof = nullptr;
+#ifdef FML_FA_PROFILE
+  static long long* prof_buf = nullptr;
+  static int prof_calls = 0;
+  if (!prof_buf) { cudaMalloc(&prof_buf, 512 * sizeof(long long)); }
+  cudaMemsetAsync(prof_buf, 0, 512 * sizeof(long long), ctx->stream);
+  p.prof = prof_buf;
+#endif
+  attention_bwd_dq_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, tmDQ, p);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dq_kernel");
+#ifdef FML_FA_PROFILE
+  if (++prof_calls == 4) {
+    long long h[512];
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost);
+    fprintf(stderr, "attention bwd dQ, CTA 0, key blocks 8..15, cycles relative to block 8's first stamp\n"
+                    "compute: top | S full | P formed | dQ flushed | dP full | dS published;  issuer: top | V,dO ready | dP issued | next K ready | next S issued | dS,K ready | dQ issued | last-of-item\n");
+    const long long t0 = h[0];
+    for (int g = 0; g < 8; g++) {
+      fprintf(stderr, "g=%d cp:", g + 8);
+      for (int k = 0; k < 6; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
+      fprintf(stderr, "  is:");
+      for (int k = 8; k < 15; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
+      fprintf(stderr, " %s\n", h[g * 16 + 15] ? "last" : "");
+    }
+    {
+      long long cmin = 1LL << 62, cmax = 0, csum = 0, nmax = 0;
+      int n = 0;
+      for (int c = 0; c < 148; c++) {
+        const long long cy = h[128 + 2 * c], ns = h[129 + 2 * c];
+        if (!cy) continue;
+        n++; csum += cy; cmin = cy < cmin ? cy : cmin; cmax = cy > cmax ? cy : cmax; nmax = ns > nmax ? ns : nmax;
+      }
+      if (n) fprintf(stderr, "per-CTA cycles over %d CTAs: min %lld avg %lld max %lld; longest CTA %lld ns; CTA 0: %lld cycles in %lld ns = %.3f GHz\n",
+                     n, cmin, csum / n, cmax, nmax, h[128], h[129], (double)h[128] / (double)h[129]);
+    }
+  }
+#endif
   FaBwd2Params p2;
   p2.S = S; p2.H = H; p2.n_kb = S / BKV; p2.causal = p.causal;
   p2.k2 = p.k2; p2.scale = p.scale; p2.lse = d->lse; p2.dsum = dsum;
@@ -1299,7 +1574,7 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   p2.status = ctx->d_status;
   p2.n_items = (int)grid;
   attention_bwd_dkv_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ, tmDO, tmQmn,
-                                                                                                                    tmDOmn, p2);
+                                                                                                                    tmDOmn, tmDK, tmDV, p2);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dkv_kernel");
   return FML_OK;
 }
