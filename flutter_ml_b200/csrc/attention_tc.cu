@@ -6,9 +6,9 @@
 // shared or global memory: the reference's transpose + matMul + scaleMatrix + softmaxMatrix + matMul chain
 // (lib/layertypes/singleHeadAttentionLayer.dart:77-86) becomes one pass over Q, K, V.
 //
-// One CTA = 608 threads:
-//   warp 0      TMA producer: Q (two buffers, one item ahead) and K_j (two-stage ring); when all loads of an item are
-//               issued it prefetches the next item's first tiles into L2
+// One CTA = 640 threads:
+//   warp 0      TMA producer: Q and K_j (two-stage ring); when all loads of an item are issued it prefetches the next
+//               item's first tiles into L2
 //   warp 1      MMA issuer: S_j = Q.K_j^T into one of two TMEM buffers (S_{j+1} is issued before P_j.V_j, so it runs
 //               under the softmax of block j), then O += P_j.V_j once the softmax warps have published P_j
 //   warps 2..17 softmax: thread = one query row (TMEM lane) and a quarter of the block's keys, 32 scores in registers
@@ -17,8 +17,9 @@
 //               probabilities are formed against the old reference (they stay below 2^8, the row sum carries the same
 //               factor), so the accumulator in tensor memory needs no rescaling and the warps never wait for P.V.
 //               The output pass of an item is deferred behind the first softmax of the next item.
-//   warp 18     TMA producer of V_j (two-stage ring)
-// Shared memory: 2 x Q, 2 x K, 2 x V of 32 KiB, 8 KiB row exchange.  TMEM: S/P buffers [0,128) and [128,256), two O
+//   warp 18     TMA producer of V_j (three-stage ring)
+//   warp 19     stores: the normalised output tile goes through a 16 KiB staging tile, half by half, with tile stores
+// Shared memory: Q, 2 x K, 3 x V of 32 KiB, 8 KiB row exchange, 16 KiB output staging.  TMEM: S/P buffers [0,128) and [128,256), two O
 // accumulators [256,320) and [320,384) that alternate from item to item.
 // V is consumed as an MN-major B operand (32-byte-atom swizzle, the layout notes of gemm_tc.cu apply).
 // Requirements: d_head = 64, seq_len a multiple of 128, 16-byte aligned rows.  Every mbarrier wait is bounded.
@@ -36,14 +37,13 @@ using namespace fml_tc;
 namespace {
 
 constexpr int BQ = 128, BKV = 128, DH = 64;
-constexpr int FA_THREADS = 608;      // forward: Q/K producer, issuer, 16 softmax warps (four per TMEM lane quarter, 32 keys each), V producer
+constexpr int FA_THREADS = 640;      // forward: Q/K producer, issuer, 16 softmax warps (four per TMEM lane quarter, 32 keys each), V producer, store warp
 constexpr int FA_BWD_THREADS = 352;  // backward: producer, issuer, 8 compute warps (two per TMEM lane quarter, alternate 32-column chunks), store warp
-constexpr uint32_t OFF_Q = 0, OFF_K = 65536, OFF_V = 131072, OFF_XCH = 196608, OFF_BAR = 229376;   // forward: 2 x Q, 2 x K, 2 x V, row exchange
+constexpr uint32_t OFF_Q = 0, OFF_K = 32768, OFF_V = 98304, OFF_XCH = 196608, OFF_ST = 204800, OFF_BAR = 229376;   // forward: Q, 2 x K, 3 x V, row exchange, output staging (16 KiB)
 constexpr int FA_SMEM = OFF_BAR + 256 + 2048 + 512;   // barriers, the row exchange (forward), alignment slack
-constexpr int KV_STAGES = 2;
+constexpr int K_STAGES = 2, V_STAGES = 3;   // a V tile arrived about 5000 cycles after its buffer came free (measured): two stages stalled every item's first P.V
 constexpr uint32_t TM_S = 0, TM_O = 256;   // two S/P buffers of 128 columns, two O accumulators of 64 columns (alternate items)
 constexpr int FA_MAX_SEQ_TMEM_P = 512;    // longest sequence the tensor-memory forward kernel is used for (four key blocks per item)
-constexpr int FA_PREFETCH_BLOCKS = 4;       // key blocks of the NEXT work item a producer prefetches into L2
 constexpr float FA_RESCALE_LOG2 = 8.f;   // a row's exponent reference moves only when a block maximum exceeds it by 2^8
 
 struct FaParams {
@@ -71,8 +71,8 @@ struct FaParams {
 
 // barriers: Q full/empty, K ring full/empty, V ring full/empty, S full (per buffer), P full (per buffer), P.V done (per
 // buffer), O read by the softmax warps
-enum { B_QFULL = 0, B_QEMPTY = 2, B_KFULL = 4, B_KEMPTY = 6, B_VFULL = 8, B_VEMPTY = 10, B_SFULL = 12, B_PFULL = 14, B_PVDONE = 16,
-       B_OEMPTY = 18 /* one per O accumulator */, B_ROW = 20 /* one per lane quarter: the four threads of a row meet here */, B_COUNT = 24 };
+enum { B_QFULL = 0, B_QEMPTY = 1, B_KFULL = 2, B_KEMPTY = 4, B_VFULL = 6, B_VEMPTY = 9, B_SFULL = 12, B_PFULL = 14, B_PVDONE = 16,
+       B_OEMPTY = 18 /* one per O accumulator */, B_ROW = 20 /* one per lane quarter: the four threads of a row meet here */, B_STAGED = 24, B_STFREE = 25 /* one per half of the output tile */, B_COUNT = 27 };
 
 // 2^x on the special-function unit with flush-to-zero: the library exp2f adds a rescaling sequence for results below
 // 2^-126, which are zero for every purpose here
@@ -94,7 +94,7 @@ __device__ __forceinline__ uint32_t fa_idesc(int M, int N, int a_mn, int b_mn) {
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FaParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -131,7 +131,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     for (int i = 0; i < B_COUNT; i++) {
       const bool from_softmax = (i == B_PFULL || i == B_PFULL + 1 || i == B_OEMPTY || i == B_OEMPTY + 1);
-      mbar_init(bar(i), from_softmax ? 512u : (i >= B_ROW ? 128u : 1u));
+      mbar_init(bar(i), from_softmax ? 16u : (i == B_STAGED ? 8u : (i >= B_STFREE ? 1u : (i >= B_ROW ? 4u : 1u))));   // warps, not threads (mbar_arrive_warp)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -156,15 +156,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, it++) {
         int qb, h, b, n_kv;
         item_coords(item, qb, h, b, n_kv);
-        // Q has two buffers: this load is issued while the previous item is still being worked on
-        const uint32_t qs = it & 1u;
-        ok = mbar_wait(bar(B_QEMPTY + qs), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 10);
+        // Q is single-buffered (the previous item's last S product must have read it); it was prefetched into L2
+        ok = mbar_wait(bar(B_QEMPTY), (it & 1u) ^ 1u, abort_flag, p.status, 10);
         if (!ok) break;
-        mbar_expect_tx(bar(B_QFULL + qs), BQ * DH * 4);
-        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + qs * 32768 + kb * 16384, &tmQ, bar(B_QFULL + qs), kb * 32, qb * BQ, h, b);
+        mbar_expect_tx(bar(B_QFULL), BQ * DH * 4);
+        for (int kb = 0; kb < 2; kb++) tma_load_4d(smem_base + OFF_Q + kb * 16384, &tmQ, bar(B_QFULL), kb * 32, qb * BQ, h, b);
         for (int j = 0; j < n_kv && ok; j++, g++) {
-          const int s = g % KV_STAGES;
-          const uint32_t ph = (g / KV_STAGES) & 1u;
+          const int s = g % K_STAGES;
+          const uint32_t ph = (g / K_STAGES) & 1u;
           ok = mbar_wait(bar(B_KEMPTY + s), ph ^ 1u, abort_flag, p.status, 11);
           if (!ok) break;
           mbar_expect_tx(bar(B_KFULL + s), BKV * DH * 4);
@@ -172,20 +171,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             tma_load_4d(smem_base + OFF_K + s * 32768 + kb * 16384, &tmK, bar(B_KFULL + s), kb * 32, j * BKV, h, b);
         }
         if (ok && item + (int)gridDim.x < p.n_items) {
-          // This thread would now only wait for a K buffer: it brings the next item's Q and first key/value blocks into L2
-          // meanwhile, so that their loads, which are issued only when the buffers come free, do not pay the DRAM latency
-          // (about 4000 cycles under load, measured) on top.
+          // Q of the next item into L2: its load is issued only when this item's last S product has read the buffer, one
+          // block before it is needed, and from DRAM it took about 4000 cycles under load (measured)
           int qb2, h2, b2, n2;
           item_coords(item + gridDim.x, qb2, h2, b2, n2);
           for (int kb = 0; kb < 2; kb++) tma_prefetch_4d(&tmQ, kb * 32, qb2 * BQ, h2, b2);
-          for (int j = 0; j < min(n2, FA_PREFETCH_BLOCKS); j++) {
-            for (int kb = 0; kb < 2; kb++) tma_prefetch_4d(&tmK, kb * 32, j * BKV, h2, b2);
-            for (int c = 0; c < 4; c++) tma_prefetch_5d(&tmV, 0, j * BKV + 32 * c, 0, h2, b2);
-          }
         }
       }
     }
-  } else if (warp == FA_THREADS / 32 - 1) {
+  } else if (warp == 18) {
     // ------------------------------------------------------------------ V producer (its own thread: a V buffer comes free
     // one P.V product later than the K buffer of the same block, and one thread loading both held the K loads back)
     if (lane == 0) {
@@ -195,8 +189,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         int qb, h, b, n_kv;
         item_coords(item, qb, h, b, n_kv);
         for (int j = 0; j < n_kv && ok; j++, g++) {
-          const int s = g % KV_STAGES;
-          const uint32_t ph = (g / KV_STAGES) & 1u;
+          const int s = g % V_STAGES;
+          const uint32_t ph = (g / V_STAGES) & 1u;
           ok = mbar_wait(bar(B_VEMPTY + s), ph ^ 1u, abort_flag, p.status, 9);
           if (!ok) break;
           mbar_expect_tx(bar(B_VFULL + s), BKV * DH * 4);
@@ -218,16 +212,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (s_item < p.n_items) { int a, b2, c; item_coords(s_item, a, b2, c, s_nkv); }
       auto issue_next_s = [&]() {
         if (s_item >= p.n_items) return true;
-        const int ks = s_g % KV_STAGES;
-        const uint32_t kph = (s_g / KV_STAGES) & 1u;
+        const int ks = s_g % K_STAGES;
+        const uint32_t kph = (s_g / K_STAGES) & 1u;
         const int buf = s_g & 1;
-        const uint32_t qs = s_it & 1u;
-        if (s_j == 0 && !mbar_wait(bar(B_QFULL + qs), (s_it >> 1) & 1u, abort_flag, p.status, 12)) return false;
+        if (s_j == 0 && !mbar_wait(bar(B_QFULL), s_it & 1u, abort_flag, p.status, 12)) return false;
         if (!mbar_wait(bar(B_KFULL + ks), kph, abort_flag, p.status, 13)) return false;
         FA_STAMP(p.prof, s_g - 1u, 14);   // operands of the next S product ready
         tc_fence_after();
         for (int kb = 0; kb < 2; kb++) {
-          const uint64_t ad = make_smem_desc(smem_base + OFF_Q + qs * 32768 + kb * 16384, 16u, 1024u, 2u);
+          const uint64_t ad = make_smem_desc(smem_base + OFF_Q + kb * 16384, 16u, 1024u, 2u);
           const uint64_t bd = make_smem_desc(smem_base + OFF_K + ks * 32768 + kb * 16384, 16u, 1024u, 2u);
 #pragma unroll
           for (int k = 0; k < 4; k++) umma_tf32(tmem_base + TM_S + buf * 128, ad + 2u * k, bd + 2u * k, idesc_s, (kb | k) ? 1u : 0u);
@@ -235,8 +228,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         umma_commit(bar(B_SFULL + buf));
         umma_commit(bar(B_KEMPTY + ks));   // K_j is read by nothing else
         s_g++;
-        if (++s_j == s_nkv) {   // last S of its item: this Q buffer may be replaced
-          umma_commit(bar(B_QEMPTY + qs));
+        if (++s_j == s_nkv) {   // last S of its item: Q may be replaced
+          umma_commit(bar(B_QEMPTY));
           s_item += gridDim.x;
           s_it++;
           s_j = 0;
@@ -250,8 +243,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         int qb, h, b, n_kv;
         item_coords(item, qb, h, b, n_kv);
         for (int j = 0; j < n_kv && ok; j++, g++) {
-          const int vs = g % KV_STAGES;
-          const uint32_t vph = (g / KV_STAGES) & 1u;
+          const int vs = g % V_STAGES;
+          const uint32_t vph = (g / V_STAGES) & 1u;
           const int buf = g & 1;
           FA_STAMP(p.prof, g, 8);
           if (s_g == g + 1) ok = issue_next_s();   // keep one S product ahead
@@ -260,8 +253,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           // the first P.V of an item overwrites its O accumulator (items alternate between two): the softmax warps must
           // have read the output of the item before the previous one
           if (j == 0) ok = mbar_wait(bar(B_OEMPTY + (it & 1u)), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 8);
-          ok = ok && mbar_wait(bar(B_PFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 15) &&
-               mbar_wait(bar(B_VFULL + vs), vph, abort_flag, p.status, 16);
+          FA_STAMP(p.prof, g, 12);
+          ok = ok && mbar_wait(bar(B_PFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 15);
+          FA_STAMP(p.prof, g, 15);
+          ok = ok && mbar_wait(bar(B_VFULL + vs), vph, abort_flag, p.status, 16);
           if (!ok) break;
           FA_STAMP(p.prof, g, 10);
           tc_fence_after();
@@ -274,7 +269,29 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           umma_commit(bar(B_PVDONE + buf));
           umma_commit(bar(B_VEMPTY + vs));
           FA_STAMP(p.prof, g, 11);
-          FA_STAMP(p.prof, g, 12 + (j == n_kv - 1));   // slot 13 is written on the last block of an item only
+          if (j == n_kv - 1) FA_STAMP(p.prof, g, 13);   // slot 13 is written on the last block of an item only
+        }
+      }
+    }
+  } else if (warp == 19) {
+    // ------------------------------------------------------------------ store warp: the output tile of every finished item
+    // leaves in two halves of 32 columns through one 16 KiB staging tile.  Stored row by row from the registers it cost
+    // 16 warps x 4 instructions x 32 separate lines, and while the load/store unit worked through them the issuer's
+    // barrier polls queued behind (measured: 1700 cycles between an operand being ready and the issuer noticing).
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t n = 0;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        int qb, h, b, n_kv;
+        item_coords(item, qb, h, b, n_kv);
+        for (int r = 0; r < 2 && ok; r++, n++) {
+          ok = mbar_wait(bar(B_STAGED), n & 1u, abort_flag, p.status, 48);
+          if (!ok) break;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          tma_store_4d(&tmO, smem_base + OFF_ST, r * 32, qb * BQ, h, b);
+          tma_store_commit();
+          tma_store_wait_read();
+          mbar_arrive(bar(B_STFREE + r));
         }
       }
     }
@@ -298,8 +315,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // every other wait of this kernel, so a CTA that gives up somewhere cannot leave partner warps parked forever.
     uint32_t n_sync = 0;
     auto row_sync = [&]() {
-      mbar_arrive(bar(B_ROW + q4));
-      return mbar_wait(bar(B_ROW + q4), (n_sync++) & 1u, abort_flag, p.status, 5);
+      mbar_arrive_warp(bar(B_ROW + q4));
+      return mbar_wait_warp(bar(B_ROW + q4), (n_sync++) & 1u, abort_flag, p.status, 5);
     };
     bool ok = true;
     uint32_t v0[32];
@@ -310,21 +327,35 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // that block's softmax (measured: 6000 cycles per item against 2400 per key block).
     bool pending = false;
     float pend_m = 0.f, pend_l = 0.f, pend_lt = 0.f;   // exponent reference, this thread's share of the row sum, the row sum
-    long long pend_out = 0, pend_stat = 0;
-    uint32_t pend_g = 0, pend_o = 0, it = 0;
+    long long pend_stat = 0;
+    uint32_t pend_g = 0, pend_o = 0, it = 0, n_out = 0;
     auto finish_item = [&]() {   // pend_lt is known by now
-      if (!mbar_wait(bar(B_PVDONE + (pend_g & 1)), (pend_g >> 1) & 1u, abort_flag, p.status, 19)) return false;
+      if (!mbar_wait_warp(bar(B_PVDONE + (pend_g & 1)), (pend_g >> 1) & 1u, abort_flag, p.status, 19)) return false;
       tc_fence_after();
       tmem_ld16(lane_addr + TM_O + pend_o * 64 + part * 16, o16);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(bar(B_OEMPTY + pend_o));   // this accumulator may be overwritten by the item after the next
+      mbar_arrive_warp(bar(B_OEMPTY + pend_o));   // this accumulator may be overwritten by the item after the next
       const float inv = 1.f / pend_lt;
-      float* orow = p.out + pend_out;
+      // parts 0, 1 fill the staging tile with columns [0,32), parts 2, 3 with [32,64) once the first half has been read
+      // Two barriers, one per half: a parity wait can only tell the current phase from the previous one, so every waiter
+      // must see every phase of its barrier, in order.  Parts 0, 1 wait for the previous item's second half to have been
+      // read, parts 2, 3 for this item's first half.  (With one barrier for both, a thread that looked at every other
+      // phase overwrote a half that had not been read yet whenever a tile store took longer than a key block.)
+      if (part < 2) {
+        if (!mbar_wait_warp(bar(B_STFREE + 1), (n_out & 1u) ^ 1u, abort_flag, p.status, 49)) return false;
+      } else {
+        if (!mbar_wait_warp(bar(B_STFREE), n_out & 1u, abort_flag, p.status, 50)) return false;
+      }
+      uint8_t* srow = smem_gen + OFF_ST + row * 128;   // 128-byte rows, 16-byte chunks swizzled (the tile store's layout)
 #pragma unroll
-      for (int i = 0; i < 16; i += 4)
-        *reinterpret_cast<float4*>(orow + i) = make_float4(__uint_as_float(o16[i]) * inv, __uint_as_float(o16[i + 1]) * inv,
-                                                           __uint_as_float(o16[i + 2]) * inv, __uint_as_float(o16[i + 3]) * inv);
+      for (int i = 0; i < 4; i++)
+        *reinterpret_cast<float4*>(srow + ((((part & 1) * 4 + i) ^ (row & 7)) << 4)) =
+            make_float4(__uint_as_float(o16[4 * i]) * inv, __uint_as_float(o16[4 * i + 1]) * inv, __uint_as_float(o16[4 * i + 2]) * inv,
+                        __uint_as_float(o16[4 * i + 3]) * inv);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive_warp(bar(B_STAGED));
+      n_out++;
       if (p.lse && part == 0) p.lse[pend_stat] = pend_m + log2f(pend_lt);
 #ifdef FML_FA_PROFILE
       if (threadIdx.x == 64) FA_STAMP(p.prof, pend_g, 7);   // end of the item's output pass
@@ -347,7 +378,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         (void)sprof;
 #endif
         FA_STAMP(sprof, g, 0);
-        ok = mbar_wait(bar(B_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 17);
+#ifdef FML_FA_PROFILE
+        if (p.prof && blockIdx.x == 0 && lane == 0 && g == 12u) p.prof[464 + warp] = clock64();   // every warp's arrival at the item's first block
+#endif
+        ok = mbar_wait_warp(bar(B_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 17);
         if (!ok) break;
         FA_STAMP(sprof, g, 1);
         tc_fence_after();
@@ -373,24 +407,25 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const float bm = fmaxf(fmaxf(e0.x, e1.x), fmaxf(e2.x, e3.x)) * p.k2;   // k2 > 0
         if (pending) pend_lt = (e0.y + e1.y) + (e2.y + e3.y);
         FA_STAMP(sprof, g, 4);
-        if (bm > m + FA_RESCALE_LOG2) {
-          // Move the reference (the four threads of the row take the same decision from the same numbers).  Block 0 of an
-          // item always lands here (m = -inf) with nothing to rescale; later blocks rescale the accumulator in tensor
-          // memory, which the previous P.V must have finished writing.
-          if (j > 0) {
-            ok = mbar_wait(bar(B_PVDONE + (buf ^ 1)), ((g - 1) >> 1) & 1u, abort_flag, p.status, 18);
-            if (!ok) break;
-            tc_fence_after();
-            const float alpha = fa_exp2(m - bm);
-            tmem_ld16(lane_addr + TM_O + (it & 1u) * 64 + part * 16, o16);
-            tmem_ld_wait();
+        // Move the reference where a block maximum exceeds it by 2^8 (the four threads of a row take the same decision from
+        // the same numbers).  Block 0 of an item always moves it (m = -inf) with nothing to rescale; in later blocks the
+        // accumulator in tensor memory is rescaled, which the previous P.V must have finished writing.  The tensor-memory
+        // accesses are warp-wide instructions, so the whole warp goes through them as soon as one of its rows moves; rows that
+        // keep their reference scale by one.
+        const bool move = bm > m + FA_RESCALE_LOG2;
+        if (j > 0 && __any_sync(0xffffffffu, move)) {
+          ok = mbar_wait_warp(bar(B_PVDONE + (buf ^ 1)), ((g - 1) >> 1) & 1u, abort_flag, p.status, 18);
+          if (!ok) break;
+          tc_fence_after();
+          const float alpha = move ? fa_exp2(m - bm) : 1.f;
+          tmem_ld16(lane_addr + TM_O + (it & 1u) * 64 + part * 16, o16);
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 16; e++) o16[e] = __float_as_uint(__uint_as_float(o16[e]) * alpha);
-            tmem_st16(lane_addr + TM_O + (it & 1u) * 64 + part * 16, o16);
-            l *= alpha;
-          }
-          m = bm;
+          for (int e = 0; e < 16; e++) o16[e] = __float_as_uint(__uint_as_float(o16[e]) * alpha);
+          tmem_st16(lane_addr + TM_O + (it & 1u) * 64 + part * 16, o16);
+          l *= alpha;
         }
+        if (move) m = bm;
         // probabilities (unnormalised, below 2^8) over the scores, rounded to TF32; the ROUNDED value enters the row sum:
         // the tensor core would otherwise cut the low mantissa bits of P on its own and bias every output low
         float ls4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -409,8 +444,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_st32(sp, v0);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(bar(B_PFULL + buf));
+        mbar_arrive_warp(bar(B_PFULL + buf));
         FA_STAMP(sprof, g, 6);
+#ifdef FML_FA_PROFILE
+        if (p.prof && blockIdx.x == 0 && lane == 0 && (g == 12u || g == 13u)) p.prof[424 + (g - 12u) * 20 + warp] = clock64();   // every warp's publish time
+#endif
         if (pending) {   // the previous item's output, now that this item's first P.V has its operand
           ok = finish_item();
           if (!ok) break;
@@ -420,7 +458,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         pending = true;
         pend_m = m;
         pend_l = l;
-        pend_out = ((long long)b * p.S + qi) * p.ld_out + h * DH + part * 16;
         pend_stat = ((long long)b * p.H + h) * p.S + qi;
         pend_g = g - 1;
         pend_o = it & 1u;
@@ -770,7 +807,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   if (threadIdx.x == 0) {
     for (int i = 0; i < C_COUNT; i++) {
       const bool from_compute = (i == C_SEMPTY || i == C_SEMPTY + 1 || i == C_DSFULL || i == C_STAGED);
-      mbar_init(bar(i), from_compute ? 256u : 1u);
+      mbar_init(bar(i), from_compute ? 8u : 1u);   // warps, not threads (mbar_arrive_warp)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -940,19 +977,19 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     uint32_t g = 0, n_flush = 0;
     bool pending = false;        // a finished item whose dQ tile is still to be read
     auto flush_dq = [&]() {      // after dQ of block g-1 (the pending item's last) has been accumulated
-      if (!mbar_wait(bar(C_DQDONE), (g - 1) & 1u, abort_flag, p.status, 30)) return false;
+      if (!mbar_wait_warp(bar(C_DQDONE), (g - 1) & 1u, abort_flag, p.status, 30)) return false;
       tc_fence_after();
       tmem_ld32(lane_addr + TM_DQ + half * 32, tv);
       tmem_ld_wait();
       tc_fence_before();   // the accumulator has been read before this thread publishes the next item's first dS
-      if (!mbar_wait(bar(C_STFREE), (n_flush & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
+      if (!mbar_wait_warp(bar(C_STFREE), (n_flush & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
       uint8_t* srow = smem_gen + BO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, 16-byte chunks swizzled
 #pragma unroll
       for (int ch = 0; ch < 8; ch++)
         *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) =
             make_float4(__uint_as_float(tv[4 * ch]), __uint_as_float(tv[4 * ch + 1]), __uint_as_float(tv[4 * ch + 2]), __uint_as_float(tv[4 * ch + 3]));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(bar(C_STAGED));
+      mbar_arrive_warp(bar(C_STAGED));
       n_flush++;
       pending = false;
       return true;
@@ -984,7 +1021,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         (void)sprof;
 #endif
         FA_STAMP(sprof, g, 0);
-        ok = mbar_wait(bar(C_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 33);
+        ok = mbar_wait_warp(bar(C_SFULL + buf), (g >> 1) & 1u, abort_flag, p.status, 33);
         if (!ok) break;
         FA_STAMP(sprof, g, 1);
         tc_fence_after();
@@ -999,7 +1036,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             pr[ci * 32 + e] = (c * 32 + e < lim) ? fa_exp2(fmaf(__uint_as_float(tv[e]), p.k2, -L)) * p.scale : 0.f;
         }
         tc_fence_before();
-        mbar_arrive(bar(C_SEMPTY + buf));
+        mbar_arrive_warp(bar(C_SEMPTY + buf));
         FA_STAMP(sprof, g, 2);
         if (pending) {
           ok = flush_dq();
@@ -1007,7 +1044,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         FA_STAMP(sprof, g, 3);
         // phase B: dS over dP
-        ok = mbar_wait(bar(C_DPFULL), g & 1u, abort_flag, p.status, 34);
+        ok = mbar_wait_warp(bar(C_DPFULL), g & 1u, abort_flag, p.status, 34);
         if (!ok) break;
         FA_STAMP(sprof, g, 4);
         tc_fence_after();
@@ -1022,7 +1059,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(bar(C_DSFULL));
+        mbar_arrive_warp(bar(C_DSFULL));
         FA_STAMP(sprof, g, 5);
       }
       if (ok) pending = true;
@@ -1102,7 +1139,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_PTFULL || i == D_DSTFULL || i == D_STAGED) ? 256u : 1u);
+    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_PTFULL || i == D_DSTFULL || i == D_STAGED) ? 8u : 1u);   // warps (mbar_arrive_warp)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1286,19 +1323,19 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     uint32_t u = 0, n_st = 0;
     bool pending = false;        // a finished item whose dV / dK tiles are still to be read
     auto flush_acc = [&]() {     // after dK of block u-1 (the pending item's last) has been accumulated
-      if (!mbar_wait(bar(D_ACCDONE), (u - 1) & 1u, abort_flag, p.status, 38)) return false;
+      if (!mbar_wait_warp(bar(D_ACCDONE), (u - 1) & 1u, abort_flag, p.status, 38)) return false;
       tc_fence_after();
       for (int which = 0; which < 2; which++, n_st++) {   // one tile after the other through the one staging tile
         tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + half * 32, tv);
         tmem_ld_wait();
-        if (!mbar_wait(bar(D_STFREE), (n_st & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
+        if (!mbar_wait_warp(bar(D_STFREE), (n_st & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
         uint8_t* srow = smem_gen + CO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, chunks swizzled
 #pragma unroll
         for (int ch = 0; ch < 8; ch++)
           *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) =
               make_float4(__uint_as_float(tv[4 * ch]), __uint_as_float(tv[4 * ch + 1]), __uint_as_float(tv[4 * ch + 2]), __uint_as_float(tv[4 * ch + 3]));
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(bar(D_STAGED));
+        mbar_arrive_warp(bar(D_STAGED));
       }
       tc_fence_before();   // both accumulators read before this thread publishes the next item's first P^T
       pending = false;
@@ -1318,7 +1355,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
         // phase A: P^T over S^T.  The row statistics of the queries are the same addresses for every lane (one
         // transaction per warp, L1 hits).
-        ok = mbar_wait(bar(D_STFULL + bf), (u >> 1) & 1u, abort_flag, p.status, 36);
+        ok = mbar_wait_warp(bar(D_STFULL + bf), (u >> 1) & 1u, abort_flag, p.status, 36);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -1349,9 +1386,9 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           ok = flush_acc();
           if (!ok) break;
         }
-        mbar_arrive(bar(D_PTFULL));
+        mbar_arrive_warp(bar(D_PTFULL));
         // phase B: dS^T over dP^T
-        ok = mbar_wait(bar(D_DPTFULL), u & 1u, abort_flag, p.status, 37);
+        ok = mbar_wait_warp(bar(D_DPTFULL), u & 1u, abort_flag, p.status, 37);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -1373,7 +1410,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(bar(D_DSTFULL));
+        mbar_arrive_warp(bar(D_DSTFULL));
       }
       if (ok && n_it > 0) pending = true;
     }
@@ -1421,9 +1458,10 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
               "fml_attention_fwd: operands must be 16-byte aligned with row strides that are multiples of 4 floats");
   FML_REQUIRE(ctx, d->ld_qkv >= (int64_t)d->heads * DH && d->ld_out >= (int64_t)d->heads * DH, "fml_attention_fwd: row stride smaller than heads * 64");
   const int S = d->seq_len, H = d->heads, Bn = d->n_seq;
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;
   int32_t rc;
   const int64_t s2 = (int64_t)S * d->ld_qkv;
+  if ((rc = fml_tc_make_tmap(ctx, d->out, DH, S, d->ld_out, H, Bn, DH, (int64_t)S * d->ld_out, 32, BQ, false, 0, &tmO))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->q, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BQ, false, 0, &tmQ))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->k, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, BKV, false, 0, &tmK))) return rc;
   if ((rc = fml_tc_make_tmap(ctx, d->v, DH, S, d->ld_qkv, H, Bn, DH, s2, 32, 32, true, 2, &tmV))) return rc;
@@ -1451,7 +1489,7 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
   cudaMemsetAsync(prof_buf, 0, 512 * sizeof(long long), ctx->stream);
   p.prof = prof_buf;
 #endif
-  if (S <= FA_MAX_SEQ_TMEM_P) attention_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
+  if (S <= FA_MAX_SEQ_TMEM_P) attention_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, tmO, p);
   else attention_fwd_long_kernel<<<grid, FA_LONG_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmK, tmV, p);
   FML_LAUNCH_CHECK(ctx, "attention_fwd_kernel");
 #ifdef FML_FA_PROFILE
@@ -1467,8 +1505,11 @@ int32_t fml_attention_fwd(fml_ctx* ctx, const fml_attention_desc* d) {
       for (int k = 0; k < 8; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
       fprintf(stderr, "  is:");
       for (int k = 8; k < 12; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
-      fprintf(stderr, " (next S operands ready %lld) %s\n", h[g * 16 + 14] ? h[g * 16 + 14] - t0 : -1, h[g * 16 + 13] ? "last" : "");
+      fprintf(stderr, " (next S operands ready %lld, O free %lld, P ready %lld) %s\n", h[g * 16 + 14] ? h[g * 16 + 14] - t0 : -1,
+              h[g * 16 + 12] ? h[g * 16 + 12] - t0 : -1, h[g * 16 + 15] ? h[g * 16 + 15] - t0 : -1, h[g * 16 + 13] ? "last" : "");
     }
+    fprintf(stderr, "per softmax warp (2..17): arrival at block 12 | P_12 published | P_13 published\n");
+    for (int w = 2; w < 18; w++) fprintf(stderr, "  w%d: %lld %lld %lld\n", w, h[464 + w] - t0, h[424 + w] - t0, h[444 + w] - t0);
     {
       long long cmin = 1LL << 62, cmax = 0, csum = 0, nmax = 0;
       int n = 0;

@@ -22,6 +22,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One arrival for a whole warp: the lanes meet (which also orders their earlier writes before lane 0's arrival), lane 0
+// arrives.  Thirty-two separate arrivals on one barrier word are processed one after the other; with sixteen warps
+// publishing at once the last arrival landed more than 1000 cycles after the first (measured), on the critical path
+// of the product that waits for it.  Barriers used this way are initialised with the number of WARPS.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -59,6 +67,11 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   return mbar_wait_limit(bar, parity, abort_flag, status, code, WAIT_LIMIT_NS);
+}
+// The same wait executed by all 32 lanes of a warp, with one verdict for the warp: if the wait gave up for any lane, every
+// lane gets false, so that the warp leaves its loop together and no lane is left behind in a later __syncwarp.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code)) != 0;
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
                                             int c1, int c2, int c3) {

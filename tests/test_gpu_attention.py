@@ -125,6 +125,60 @@ def test_fused_attention_forward(orc, S, causal):
     ctx.close()
 
 
+@pytest.mark.parametrize("S,causal", [(256, False), (512, True), (512, False)])
+def test_fused_attention_forward_moves_the_exponent_reference(S, causal):
+    """Keys whose magnitude changes from block to block (x1, x3.2, x1/3, x4.5): in many rows, but not in all rows of a warp, a
+    later block's maximum exceeds the exponent reference by more than 2^8, so the accumulator in tensor memory is rescaled in
+    the middle of an item (random data of one magnitude never gets there).  Output and row statistics against the float64
+    emulation of the kernel's rule, and against exact softmax attention; the moved rows are counted."""
+    from flutter_ml_b200 import _lib
+    ctx = _lib.Context(precision=_lib.PREC_TF32)
+    Bn, H, dk = 1, 2, 64
+    dm = H * dk
+    rng = np.random.default_rng(7 * S + causal)
+    qkv = rng.standard_normal((Bn * S, 3 * dm)).astype(np.float32)
+    gain = np.array([1.0, 3.2, 1.0 / 3.0, 4.5], np.float32)
+    for j in range(S // 128):
+        qkv[j * 128:(j + 1) * 128, dm:2 * dm] *= gain[j]
+    scale = 1 / math.sqrt(dk)
+    dq, out, lse = ctx.upload(qkv), ctx.empty(Bn * S, dm), ctx.empty(Bn * H * S)
+    d = attention_desc(ctx, dq, out, lse, Bn, S, H, causal, scale)
+    ctx.check(ctx.lib.fml_attention_fwd(ctx.h, C.byref(d)))
+    assert ctx.device_status() == 0
+    got, got_lse = out.numpy(), lse.numpy().reshape(Bn, H, S)
+    k2 = scale * 1.4426950408889634
+    for h in range(H):
+        Q32, K32, V32 = (qkv[:, i * dm + h * dk:i * dm + (h + 1) * dk] for i in range(3))
+        # how many rows move their reference after the first block, and how many keep it although a neighbour moves
+        s = trunc_tf32(Q32) @ trunc_tf32(K32).T * k2
+        moved = np.zeros(S, bool)
+        for q0 in range(0, S, 128):
+            m = np.full(128, -np.inf)
+            for j in range(q0 // 128 + 1 if causal else S // 128):
+                blk = s[q0:q0 + 128, j * 128:(j + 1) * 128]
+                if causal and j == q0 // 128:
+                    blk = np.where(np.tril(np.ones((128, 128), bool)), blk, -np.inf)
+                mv = blk.max(1) > m + 8.0
+                if j > 0:
+                    moved[q0:q0 + 128] |= mv
+                m = np.where(mv, blk.max(1), m)
+        per_warp = moved.reshape(-1, 32)
+        mixed = int(((per_warp.sum(1) > 0) & (per_warp.sum(1) < 32)).sum())
+        print(f"S {S} causal {causal} head {h}: rows that move the reference after block 0: {int(moved.sum())} of {S}, "
+              f"warps with both kinds of rows: {mixed}")
+        assert moved.sum() > S // 8 and mixed > 0
+        o_emu, lse_emu = emulate_forward(Q32, K32, V32, scale, causal, lazy=True)
+        assert rel(got[:, h * dk:(h + 1) * dk], o_emu) <= 2e-4, rel(got[:, h * dk:(h + 1) * dk], o_emu)
+        assert np.max(np.abs(got_lse[0, h] - lse_emu)) <= 2e-4
+        sc = w64(Q32) @ w64(K32).T * scale
+        if causal:
+            sc = np.where(np.tril(np.ones((S, S), bool)), sc, -np.inf)
+        pr = np.exp(sc - sc.max(1, keepdims=True))
+        o_ref = (pr / pr.sum(1, keepdims=True)) @ w64(V32)
+        assert rel(got[:, h * dk:(h + 1) * dk], o_ref) <= 5e-3    # sharply peaked rows: the truncation of one dominant score
+    ctx.close()
+
+
 def test_fused_attention_rejects_unsupported_shapes():
     from flutter_ml_b200 import _lib
     ctx = _lib.Context()
@@ -218,5 +272,25 @@ def test_fused_attention_full_size_properties():
     o = out.numpy().reshape(Bn, S, dm)
     v = qkv[:, 2 * dm:].reshape(Bn, S, dm)
     assert rel(o[:, 0, :], v[:, 0, :]) <= 1e-3        # one TF32 rounding of V
+    # Every CTA works through about fourteen tiles here (one each in the small cases above), so where a tile lands is part of
+    # what is tested: whole heads, spread over the batch, against exact float64 attention, forward and backward.
+    ctx.check(ctx.lib.fml_attention_bwd(ctx.h, C.byref(d2), dG.ptr, dm, dqkv.ptr, dqkv.ptr + 4 * dm, dqkv.ptr + 8 * dm, 3 * dm, 0,
+                                        scratch.ptr))
+    g = dqkv.numpy()
+    tril = np.tril(np.ones((S, S), bool))
+    picks = [(0, 0), (Bn - 1, H - 1)] + [(int(rng.integers(Bn)), int(rng.integers(H))) for _ in range(8)]
+    for b, h in picks:
+        rows, cols = slice(b * S, (b + 1) * S), slice(h * dk, (h + 1) * dk)
+        Q, K, V = (w64(qkv[rows, i * dm + h * dk:i * dm + (h + 1) * dk]) for i in range(3))
+        sc = np.where(tril, Q @ K.T * 0.125, -np.inf)
+        P = np.exp(sc - sc.max(1, keepdims=True))
+        P /= P.sum(1, keepdims=True)
+        dO = w64(G[rows, cols])
+        dP = dO @ V.T
+        dS = P * (dP - (dP * P).sum(1, keepdims=True)) * 0.125
+        assert rel(o[b][:, cols], P @ V) <= 2e-3, (b, h)
+        assert rel(g[rows, h * dk:(h + 1) * dk], dS @ K) <= 5e-3, (b, h)
+        assert rel(g[rows, dm + h * dk:dm + (h + 1) * dk], dS.T @ Q) <= 5e-3, (b, h)
+        assert rel(g[rows, 2 * dm + h * dk:2 * dm + (h + 1) * dk], P.T @ dO) <= 5e-3, (b, h)
     assert ctx.device_status() == 0
     ctx.close()

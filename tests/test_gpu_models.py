@@ -423,7 +423,7 @@ def test_lm_step_with_update_on_the_side_stream_equals_the_plain_step():
     params = models.init_lm(4, V, d, heads, dff, L, std=0.05)
     ids, labels = synth.integers(4, 100, (B * S,), V), synth.integers(4, 101, (B * S,), V)
     res = []
-    for overlap in (False, True):
+    for overlap in (False, False, True):
         ctx = _lib.Context(precision=_lib.PREC_TF32)
         lm = models.TransformerLM(ctx, params, S, heads, lr=1e-3)
         d_ids, d_lab = ctx.upload(ids), ctx.upload(labels)
@@ -432,9 +432,15 @@ def test_lm_step_with_update_on_the_side_stream_equals_the_plain_step():
         res.append((losses, lm.arena.values.numpy(), lm.optimizer._m.numpy(), lm.optimizer._v.numpy(), lm.arena.grads.numpy()))
         assert ctx.device_status() == 0
         ctx.close()
-    (l0, w0, m0, v0, g0), (l1, w1, m1, v1, g1) = res
+    (l0, w0, m0, v0, g0), (lr_, wr, mr, vr, gr), (l1, w1, m1, v1, g1) = res
     assert l0[2] < l0[0]                                     # it trains
-    # split-K weight gradients add their partial sums with atomics in no fixed order: last-bit differences between runs
-    assert np.allclose(l0, l1, rtol=1e-5)
-    assert rel(w1, w0) <= 1e-4 and rel(m1, m0) <= 1e-4 and rel(v1, v0) <= 1e-4
-    assert not g0.any() and not g1.any()
+    # Split-K weight gradients add their partial sums with atomics in no fixed order, so two runs of the SAME step differ in
+    # the last bits of the gradients, and Adam turns that into full-size steps of either sign wherever a gradient is
+    # mathematically zero (the key bias: softmax is invariant to a shift of the scores).  The yardstick is therefore the
+    # difference between two plain runs: the overlapped step may differ from a plain run by no more than three times that.
+    noise_w, noise_m, noise_v = rel(wr, w0), rel(mr, m0), rel(vr, v0)
+    print(f"plain vs plain: w {noise_w:.2e} m {noise_m:.2e} v {noise_v:.2e}; overlapped vs plain: w {rel(w1, w0):.2e} "
+          f"m {rel(m1, m0):.2e} v {rel(v1, v0):.2e}")
+    assert np.allclose(l0, l1, rtol=1e-5) and np.allclose(l0, lr_, rtol=1e-5)
+    assert rel(w1, w0) <= max(1e-4, 3 * noise_w) and rel(m1, m0) <= max(1e-4, 3 * noise_m) and rel(v1, v0) <= max(1e-4, 3 * noise_v)
+    assert not g0.any() and not g1.any() and not gr.any()
