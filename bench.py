@@ -284,6 +284,11 @@ def time_membound(ctx, hbm_gbs, reps=5, rows=262144, params=1 << 28):
         t[0] += 1
         ctx.call("fml_adam_step", w, gr, m, v, P, 1e-3, 0.9, 0.999, 1e-8, t[0], 1.0)
     record("adam_step", timed(adam), 28 * P, [P])
+
+    def adam_zero():   # the training step's form: per-slice update with the gradient cleared in the same pass
+        t[0] += 1
+        ctx.call("fml_adam_step_on", -1, w, gr, m, v, P, 1e-3, 0.9, 0.999, 1e-8, t[0], 1.0, 1)   # lane -1: the timed stream
+    record("adam_step+zero_grad", timed(adam_zero), 32 * P, [P])
     return out
 
 

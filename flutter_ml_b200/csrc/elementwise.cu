@@ -190,15 +190,18 @@ __device__ __forceinline__ void adam1(float& w, float g, float& m, float& v, con
 // ZERO: the gradient is cleared as it is consumed (Optimizer.zeroGrad, optimizers.dart:62-66, folded into the
 // update: one pass over the gradient instead of a read here and a memset later).
 template <bool VEC, bool ZERO>
-__global__ void adam_kernel(float* w, float* g, float* m, float* v, long long n, const AdamK k) {
+__global__ void adam_kernel(float* __restrict__ w, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, long long n,
+                            const AdamK k) {
   const float gs = k.gs;
   if (VEC) {
+    // All four loads first, the stores (the cleared gradient among them) last: with the gradient cleared between the
+    // loads, and pointers that may alias, the compiler kept the loads of m and v behind that store and the kernel ran at
+    // 1.6 TB/s instead of 6.2 (measured on the 33 M-parameter slice of the language-model step).
     EW_LOOP(i, n >> 2) {
-      float4 wv = reinterpret_cast<float4*>(w)[i];
-      float4 gv = reinterpret_cast<const float4*>(g)[i];
-      if (ZERO) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      float4 mv = reinterpret_cast<float4*>(m)[i];
-      float4 vv = reinterpret_cast<float4*>(v)[i];
+      float4 wv = reinterpret_cast<const float4*>(w)[i];
+      const float4 gv = reinterpret_cast<const float4*>(g)[i];
+      float4 mv = reinterpret_cast<const float4*>(m)[i];
+      float4 vv = reinterpret_cast<const float4*>(v)[i];
       adam1(wv.x, gs * gv.x, mv.x, vv.x, k);
       adam1(wv.y, gs * gv.y, mv.y, vv.y, k);
       adam1(wv.z, gs * gv.z, mv.z, vv.z, k);
@@ -206,10 +209,12 @@ __global__ void adam_kernel(float* w, float* g, float* m, float* v, long long n,
       reinterpret_cast<float4*>(w)[i] = wv;
       reinterpret_cast<float4*>(m)[i] = mv;
       reinterpret_cast<float4*>(v)[i] = vv;
+      if (ZERO) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   } else {
     EW_LOOP(i, n) {
-      adam1(w[i], gs * g[i], m[i], v[i], k);
+      const float gi = g[i];
+      adam1(w[i], gs * gi, m[i], v[i], k);
       if (ZERO) g[i] = 0.f;
     }
   }
