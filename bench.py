@@ -341,8 +341,8 @@ def main():
     ap.add_argument("--size", type=int, default=8192, help="M=N=K of the timed step (rows per GPU when N > 1)")
     ap.add_argument("--ref-size", type=int, default=1024, help="M=N=K of one CPU sample step")
     ap.add_argument("--repeats", type=int, default=0, help="timed regions of --steps steps each; 0 picks 10, fewer for long regions")
-    ap.add_argument("--reserve-sms", type=int, default=32, help="SMs the dA product leaves to the exchange that runs beside it (N > 1)")
-    ap.add_argument("--nccl-ctas", type=int, default=32, help="upper limit on the CTAs of the gradient exchange (N > 1; 0: NCCL's choice)")
+    ap.add_argument("--reserve-sms", type=int, default=20, help="SMs the dA product leaves to the exchange that runs beside it (N > 1)")
+    ap.add_argument("--nccl-ctas", type=int, default=16, help="upper limit on the CTAs of the gradient exchange (N > 1; 0: NCCL's choice)")
     ap.add_argument("--overlap-rows", type=int, default=0, help="rows of the dA product computed beside the exchange on the reduced SM set (0: all)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
