@@ -172,7 +172,26 @@ def config4_lstm(ctx):
             "launches_per_step": launches}
 
 
+def tiered_lstm(ctx):
+    """The two-tier layer (lib/layertypes/duallstm.dart) at configuration 4's sizes: I 256, H 512, T 128, batch 128, clock
+    cycle 7; forward + backward through layers.DualLSTMLayer (three products and one cell kernel per update)."""
+    from flutter_ml_b200.layers import DualLSTMLayer
+    I, H, Tn, B, cyc = 256, 512, 128, 128, 7
+    x = Tensor(synth.normal(3, 40, (Tn, B, I)), ctx)
+    target = Tensor(synth.normal(3, 41, (B, H)), ctx)
+    layer = DualLSTMLayer(H, cyc, seed=3)
+
+    def step():
+        loss = T.mseMatrix(layer(x), target)
+        loss.backward()
+    ms, launches = _timed(ctx, step, warm=2, reps=3)
+    updates = Tn + sum(1 for t in range(Tn) if t > 0 and (t + 1) % cyc == 0)
+    flops = 3.0 * 2 * B * 4 * H * (Tn * (2 * H + I) + (updates - Tn) * 2 * H)
+    return {"config": f"DualLSTM I{I} H{H} T{Tn} B{B} cycle {cyc} fwd+bwd (next-row layer, not a BASELINE config)", "ms_per_step": round(ms, 3),
+            "tflops": round(flops / ms / 1e9, 1), "us_per_update_and_direction": round(ms * 1e3 / (2 * updates), 1), "launches_per_step": launches}
+
+
 def run(ctx, only: int = 0):
-    """All three configurations, or just configuration `only` (1, 3 or 4; for profiling one of them)."""
-    fns = {1: config1_mlp, 3: config3_encoder_block, 4: config4_lstm}
+    """All three configurations plus the tiered layer, or just configuration `only` (1, 3 or 4; for profiling one of them)."""
+    fns = {1: config1_mlp, 3: config3_encoder_block, 4: config4_lstm, 6: tiered_lstm}
     return [fn(ctx) for k, fn in fns.items() if only in (0, k)]

@@ -143,6 +143,8 @@ PROTOTYPES = {
     "fml_tape_kind": [C.c_char_p],
     "fml_lstm_fwd": [fp, C.POINTER(LstmDesc)],
     "fml_lstm_bwd": [fp, C.POINTER(LstmDesc), fp, fp, fp, fp, fp],
+    "fml_lstm_cell_fwd": [fp, fp, fp, fp, fp, fp, i64, i64],
+    "fml_lstm_cell_bwd": [fp, fp, fp, fp, fp, fp, fp, fp, i32, i64, i64],
     "fml_dp_unique_id": [C.c_char_p],
     "fml_dp_init": [fp, C.c_char_p, i32, i32],
     "fml_dp_set_timeout": [fp, i32],

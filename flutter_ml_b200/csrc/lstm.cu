@@ -85,6 +85,46 @@ __global__ void lstm_gates_bwd_kernel(float* __restrict__ dh, float* dc, const f
   }
 }
 
+// One cell update on pre-activations the CALLER formed (the tiered layers, lib/layertypes/multilstm.dart:160-178): gate
+// blocks f | i | c~ | o, column g*H + u of a [B][4H] row, the order of the reference's four weight matrices stacked.
+__global__ void lstm_cell_fwd_kernel(const float* __restrict__ pre, const float* __restrict__ c_prev, float* __restrict__ gates,
+                                     float* __restrict__ c_out, float* __restrict__ h_out, int B, int H) {
+  const int n = B * H;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+    const int b = idx / H, u = idx - b * H;
+    const float* pr = pre + (long long)b * 4 * H + u;
+    float* gr = gates + (long long)b * 4 * H + u;
+    const float f = fml_sigmoid(pr[0]), i = fml_sigmoid(pr[H]), g = fml_tanh_ref(pr[2 * H]), o = fml_sigmoid(pr[3 * H]);
+    const float c = f * c_prev[idx] + i * g;
+    gr[0] = f; gr[H] = i; gr[2 * H] = g; gr[3 * H] = o;
+    c_out[idx] = c;
+    h_out[idx] = o * fml_tanh_ref(c);
+  }
+}
+
+// dh and (optionally) dc flowing into the cell from later steps -> gradient of the pre-activations and of c_prev; the
+// derivatives are formed from the saved outputs as in the reference (sigmoid y(1-y) tensor.dart:552, tanh 1-y^2 :598)
+__global__ void lstm_cell_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ c_prev, const float* __restrict__ c_cur,
+                                     const float* __restrict__ dh, const float* __restrict__ dc_in, float* __restrict__ dpre,
+                                     float* __restrict__ dc_prev, int accumulate_dc_prev, int B, int H) {
+  const int n = B * H;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
+    const int b = idx / H, u = idx - b * H;
+    const float* gr = gates + (long long)b * 4 * H + u;
+    float* dp = dpre + (long long)b * 4 * H + u;
+    const float f = gr[0], i = gr[H], g = gr[2 * H], o = gr[3 * H];
+    const float tc = fml_tanh_ref(c_cur[idx]);
+    const float dhv = dh ? dh[idx] : 0.f;
+    const float dct = (dc_in ? dc_in[idx] : 0.f) + dhv * o * (1.f - tc * tc);
+    dp[0] = dct * c_prev[idx] * (f * (1.f - f));
+    dp[H] = dct * g * (i * (1.f - i));
+    dp[2 * H] = dct * i * (1.f - g * g);
+    dp[3 * H] = dhv * tc * (o * (1.f - o));
+    const float v = dct * f;
+    dc_prev[idx] = accumulate_dc_prev ? dc_prev[idx] + v : v;
+  }
+}
+
 inline int blocks_for(fml_ctx* ctx, long long n) {
   return (int)std::max<long long>(1, std::min<long long>((n + 255) / 256, (long long)ctx->sm_count * 4));
 }
@@ -270,6 +310,26 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
   cudaFreeAsync(Wi, ctx->stream);
   if (rc) return rc;
   FML_LAUNCH_CHECK(ctx, "lstm backward");
+  return FML_OK;
+}
+
+int32_t fml_lstm_cell_fwd(fml_ctx* ctx, const float* pre, const float* c_prev, float* gates, float* c, float* h, int64_t B, int64_t H) {
+  FML_ENTER(ctx);
+  FML_REQUIRE(ctx, pre && c_prev && gates && c && h, "fml_lstm_cell_fwd: NULL buffer");
+  FML_REQUIRE(ctx, B > 0 && H > 0 && B * H <= 0x7fffffffLL / 4, "fml_lstm_cell_fwd: bad sizes");
+  lstm_cell_fwd_kernel<<<blocks_for(ctx, B * H), 256, 0, ctx->stream>>>(pre, c_prev, gates, c, h, (int)B, (int)H);
+  FML_LAUNCH_CHECK(ctx, "lstm_cell_fwd_kernel");
+  return FML_OK;
+}
+
+int32_t fml_lstm_cell_bwd(fml_ctx* ctx, const float* gates, const float* c_prev, const float* c, const float* dh, const float* dc,
+                          float* dpre, float* dc_prev, int32_t accumulate_dc_prev, int64_t B, int64_t H) {
+  FML_ENTER(ctx);
+  FML_REQUIRE(ctx, gates && c_prev && c && dpre && dc_prev, "fml_lstm_cell_bwd: NULL buffer");
+  FML_REQUIRE(ctx, B > 0 && H > 0 && B * H <= 0x7fffffffLL / 4, "fml_lstm_cell_bwd: bad sizes");
+  lstm_cell_bwd_kernel<<<blocks_for(ctx, B * H), 256, 0, ctx->stream>>>(gates, c_prev, c, dh, dc, dpre, dc_prev, accumulate_dc_prev ? 1 : 0,
+                                                                        (int)B, (int)H);
+  FML_LAUNCH_CHECK(ctx, "lstm_cell_bwd_kernel");
   return FML_OK;
 }
 

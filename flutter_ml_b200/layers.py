@@ -204,6 +204,146 @@ class LSTMLayer(Layer):
         return out
 
 
+class MultiTierLSTMLayer(Layer):
+    """MultiTierLSTMLayer (lib/layertypes/multilstm.dart:14-208): a stack of LSTM tiers on different clocks.
+
+    Tier 0 runs at every step on [h_0, c_1, ..., c_{n-1}, x_t] (its own hidden state, the CELL states of all higher tiers
+    as context, the input: :137-150); tier i >= 1 runs when (step + 1) is a multiple of the product of the first i clock
+    cycles (:155), on [h_i, h_{i-1}] with h_{i-1} as just updated in the same step (:157).  Output: the last hidden state
+    of tier 0 (:166).  All states start at zero (:117-121).
+
+    Input: one sequence [T x I] or a time-major batch [T x B x I]; output [B x H].  Per tier the four gate matrices
+    [H x combined] of the reference live in one [4H x combined] buffer (gate blocks f, i, c~, o), the biases in one [4H]
+    buffer; `parameters` hands out the reference's tensors in its order, tier by tier (W_f, b_f, W_i, b_i, W_c, b_c, W_o,
+    b_o, :44-52), as views.  A cell update is: one product per input block into the [B x 4H] pre-activations (the first
+    with the bias in its epilogue, the others accumulating; the concatenated input of the reference never exists), then
+    fml_lstm_cell_fwd.  Backward runs the recorded updates in reverse with fml_lstm_cell_bwd and the transposed
+    products; gradients of states that feed several later updates accumulate in place.  Initial weights
+    U(+-sqrt(1/fanIn)) (:66-77) from the seeded generator unless `weights` / `biases` (one array per tier) are given."""
+    name = "multitier_lstm"
+
+    def __init__(self, hiddenSize: int, tierClockCycles, seed: int = 0, weights=None, biases=None):
+        super().__init__()
+        self.hiddenSize, self.tierClockCycles = hiddenSize, list(tierClockCycles)
+        self.numTiers = len(self.tierClockCycles) + 1
+        self.cumulativeClockCycles, prod = [], 1
+        for c in self.tierClockCycles:
+            if c < 1:
+                raise ValueError("clock cycles must be positive")
+            prod *= c
+            self.cumulativeClockCycles.append(prod)
+        self.seed, self._w0, self._b0 = seed, weights, biases
+
+    def _fires(self, tier: int, step: int) -> bool:
+        return (step + 1) % self.cumulativeClockCycles[tier - 1] == 0      # multilstm.dart:155
+
+    def _combined(self, tier: int, I: int) -> int:
+        H = self.hiddenSize
+        return H + (self.numTiers - 1) * H + I if tier == 0 else 2 * H     # multilstm.dart:82-88
+
+    @property
+    def parameters(self):
+        return self._params
+
+    def build(self, x: Tensor):
+        H, I, ctx = self.hiddenSize, x.shape[-1], x.ctx
+        self.W, self.b, self.dW, self.db, self._params = [], [], [], [], []
+        for i in range(self.numTiers):
+            comb = self._combined(i, I)
+            a = math.sqrt(1.0 / comb)
+            w = self._w0[i] if self._w0 is not None else synth.uniform(self.seed, 10 + i, (4 * H, comb), -a, a)
+            b = self._b0[i] if self._b0 is not None else np.zeros(4 * H, dtype=np.float32)
+            w = np.ascontiguousarray(w, np.float32)
+            if w.shape != (4 * H, comb):
+                raise ValueError(f"tier {i}: weights must be [4H x {comb}]")
+            self.W.append(ctx.upload(w))
+            self.b.append(ctx.upload(np.asarray(b, np.float32)))
+            self.dW.append(ctx.zeros(4 * H, comb))
+            self.db.append(ctx.zeros(4 * H))
+            for g in range(4):
+                for buf, grad, off, shape in ((self.W[i], self.dW[i], g * H * comb, (H, comb)), (self.b[i], self.db[i], g * H, (H,))):
+                    t = Tensor(buf.view(off, shape), ctx)
+                    t.grad = grad.view(off, shape)
+                    self._params.append(t)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        ctx, H, n = x.ctx, self.hiddenSize, self.numTiers
+        Tn, B, I = (x.shape[0], 1, x.shape[1]) if len(x.shape) == 2 else x.shape
+        zero = ctx.zeros(B, H)                       # every initial state (read only)
+        h, c = [zero] * n, [zero] * n
+        records = []                                 # (tier, [(input block, width, first column, step or -1)], c_prev, gates, c_new, h_new)
+
+        def update(tier, blocks):
+            comb = self._combined(tier, I)
+            pre = ctx.empty(B, 4 * H)
+            for k, (arr, w, col, _) in enumerate(blocks):
+                ctx.gemm(arr, self.W[tier].view(col, (4 * H, w)), pre, B, 4 * H, w, transB=True, ldb=comb,
+                         bias=self.b[tier] if k == 0 else None, beta=0.0 if k == 0 else 1.0)
+            gates, c_new, h_new = ctx.empty(B, 4 * H), ctx.empty(B, H), ctx.empty(B, H)
+            ctx.call("fml_lstm_cell_fwd", pre, c[tier], gates, c_new, h_new, B, H)
+            records.append((tier, blocks, c[tier], gates, c_new, h_new))
+            h[tier], c[tier] = h_new, c_new
+
+        for t in range(Tn):
+            x_t = x.value.view(t * B * I, (B, I))
+            blocks = [(h[0], H, 0, -1)] + [(c[j], H, j * H, -1) for j in range(1, n)] + [(x_t, I, n * H, t)]
+            update(0, blocks)
+            for i in range(1, n):
+                if self._fires(i, t):
+                    update(i, [(h[i], H, 0, -1), (h[i - 1], H, H, -1)])
+        out = Tensor(h[0], ctx)
+        want_dx = x.creator is not None or x.grad is not None
+
+        def bw():
+            grads = {id(out.value): out.grad}
+
+            def grad_of(arr):
+                g = grads.get(id(arr))
+                if g is None:
+                    g = grads[id(arr)] = ctx.zeros(B, H)
+                return g
+            dx = ctx.zeros(*x.shape) if want_dx else None
+            for tier, blocks, c_prev, gates, c_new, h_new in reversed(records):
+                dh, dc = grads.get(id(h_new)), grads.get(id(c_new))
+                if dh is None and dc is None:
+                    continue                          # nothing downstream read this update
+                comb = self._combined(tier, I)
+                dpre = ctx.empty(B, 4 * H)
+                if c_prev is zero:
+                    dcp, acc = ctx.empty(B, H), 0     # gradient of the initial state: formed, not used
+                else:
+                    acc = 1 if id(c_prev) in grads else 0
+                    dcp = grads.setdefault(id(c_prev), ctx.empty(B, H)) if not acc else grads[id(c_prev)]
+                ctx.call("fml_lstm_cell_bwd", gates, c_prev, c_new, dh, dc, dpre, dcp, acc, B, H)
+                ctx.call("fml_col_sum", dpre, self.db[tier], B, 4 * H, 1)
+                for arr, w, col, step in blocks:
+                    ctx.gemm(dpre, arr, self.dW[tier].view(col, (4 * H, w)), 4 * H, w, B, transA=True, ldc=comb, beta=1.0)
+                    if arr is zero or (step >= 0 and dx is None):
+                        continue
+                    target = dx.view(step * B * I, (B, I)) if step >= 0 else grad_of(arr)
+                    ctx.gemm(dpre, self.W[tier].view(col, (4 * H, w)), target, B, w, 4 * H, ldb=comb, beta=1.0)
+            if dx is not None:
+                x._add_grad(dx, alias=True)
+        out.creator = T.Node([x] + self._params, bw, self.name, cost=8 * len(records) * B * H * 2 * H)
+        return out
+
+
+class DualLSTMLayer(MultiTierLSTMLayer):
+    """DualLSTMLayer (lib/layertypes/duallstm.dart:26-175): two tiers; the higher one runs when step > 0 and (step + 1) is
+    a multiple of `lowerTierClockCycle` (:145), on [h_higher, h_lower] (:149); the lower one at every step on
+    [h_lower, c_higher, x_t] (:116-117).  Parameters in the reference's order: the lower tier's eight, then the higher
+    tier's (:43-46)."""
+    name = "duallstm"
+
+    def __init__(self, hiddenSize: int, lowerTierClockCycle: int = 7, seed: int = 0, weights=None, biases=None):
+        super().__init__(hiddenSize, [lowerTierClockCycle], seed=seed, weights=weights, biases=biases)
+        self.lowerTierClockCycle = lowerTierClockCycle
+
+    def _fires(self, tier: int, step: int) -> bool:
+        return step > 0 and (step + 1) % self.lowerTierClockCycle == 0
+
+
 class LayerNormalization(Layer):
     """lib/transformer/layerNormalization.dart:11-44: gamma = 1, beta = 0, epsilon = 1e-5."""
 

@@ -498,6 +498,16 @@ int32_t fml_lstm_fwd(fml_ctx* ctx, const fml_lstm_desc* d);
 int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last, float* dW, float* db,
                      float* dx, float* scratch /* [T*B][4H] + 2*[B][H] floats */);
 
+/* One LSTM cell update on pre-activations the caller has formed: the pointwise part of the reference's tiered recurrent
+ * layers (MultiTierLSTMLayer._lstmStep lib/layertypes/multilstm.dart:160-178, DualLSTMLayer lib/layertypes/duallstm.dart),
+ * whose tiers combine different inputs at different clocks.  pre and gates are [B][4H] in gate blocks f | i | c~ | o
+ * (column g*H + u: the reference's four weight matrices stacked), c_prev, c, h are [B][H].
+ * Backward: dh and dc are the gradients arriving at h and c from later steps (either may be NULL = zero); writes the
+ * gradient of the pre-activations and writes, or adds to (accumulate_dc_prev != 0), the gradient of c_prev. */
+int32_t fml_lstm_cell_fwd(fml_ctx* ctx, const float* pre, const float* c_prev, float* gates, float* c, float* h, int64_t B, int64_t H);
+int32_t fml_lstm_cell_bwd(fml_ctx* ctx, const float* gates, const float* c_prev, const float* c, const float* dh, const float* dc,
+                          float* dpre, float* dc_prev, int32_t accumulate_dc_prev, int64_t B, int64_t H);
+
 /* ---- data parallel (one process per GPU) -------------------------------------
  * The reference has no multi-device code.  Rank 0 creates an id, the host
  * distributes the 128 bytes by any means, every rank joins, and gradients are

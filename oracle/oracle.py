@@ -534,3 +534,50 @@ def lm_forward_backward(ids, labels, params, n_global_tokens, causal=True, omp=F
     plist += [Wh, bh]
     return {"loss": loss, "logits": np.stack(logits_all), "grads": [p.grad for p in plist],
             "params": [p.value for p in plist]}
+
+
+def tiered_lstm_fwd_bwd(x, Ws, bs, cycles, target, dual=False, omp=False):
+    """MultiTierLSTMLayer.forward (lib/layertypes/multilstm.dart:111-167) or, with `dual`, DualLSTMLayer.forward
+    (lib/layertypes/duallstm.dart:98-175) for ONE sequence x [T x I], composed from the tape's vector operations the way
+    the reference composes them (concatenate :437-455, matVecMul :949-980, addVector :395-414, sigmoid :541-559,
+    vectorTanh :581-605, elementWiseMultiply :478-497 of lib/autogradEngine/tensor.dart), then mse against `target`
+    (tensor.dart:499-519) and the tape's backward sweep.  Ws[i] is [4H x combined_i], the four gate matrices of tier i
+    stacked f, i, c~, o; bs[i] is [4H].  Returns the last hidden state of tier 0, the loss, dWs, dbs and dx."""
+    e = Engine(omp)
+    n = len(cycles) + 1
+    H = Ws[0].shape[0] // 4
+    cum, prod = [], 1
+    for c in cycles:
+        prod *= c
+        cum.append(prod)
+    Wt = [[T(W[g * H:(g + 1) * H]) for g in range(4)] for W in Ws]
+    bt = [[T(b[g * H:(g + 1) * H]) for g in range(4)] for b in bs]
+    xs = [T(row) for row in np.asarray(x, dtype=np.float64)]
+    h = [T(np.zeros(H)) for _ in range(n)]
+    c_ = [T(np.zeros(H)) for _ in range(n)]
+
+    def step(combined, c_prev, tier):     # multilstm.dart:160-178
+        W, b = Wt[tier], bt[tier]
+        f = e._unary("sigmoid", e.addMatrix(e.matVecMul(W[0], combined), b[0]), True)
+        i = e._unary("sigmoid", e.addMatrix(e.matVecMul(W[1], combined), b[1]), True)
+        g = e._unary("tanh", e.addMatrix(e.matVecMul(W[2], combined), b[2]), True)
+        c_next = e.addMatrix(e.elementWiseMultiply(f, c_prev), e.elementWiseMultiply(i, g))
+        o = e._unary("sigmoid", e.addMatrix(e.matVecMul(W[3], combined), b[3]), True)
+        return e.elementWiseMultiply(o, e._unary("tanh", c_next, True)), c_next
+
+    for t, x_t in enumerate(xs):
+        combined = h[0]
+        for j in range(1, n):             # [h_0, c_1, ..., c_{n-1}, x_t]  (multilstm.dart:137-150, duallstm.dart:116-117)
+            combined = e.concatenate(combined, c_[j])
+        combined = e.concatenate(combined, x_t)
+        h[0], c_[0] = step(combined, c_[0], 0)
+        for i in range(1, n):
+            fires = (t + 1) % cum[i - 1] == 0 and (t > 0 or not dual)     # multilstm.dart:155, duallstm.dart:145
+            if fires:
+                h[i], c_[i] = step(e.concatenate(h[i], h[i - 1]), c_[i], i)
+    out = h[0]
+    loss = e.mseMatrix(out, T(target))
+    loss.backward()
+    dWs = [np.concatenate([w.grad for w in W], axis=0) for W in Wt]
+    dbs = [np.concatenate([v.grad for v in b]) for b in bt]
+    return out.value.copy(), float(loss.value), dWs, dbs, np.stack([v.grad for v in xs])

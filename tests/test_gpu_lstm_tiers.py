@@ -1,0 +1,120 @@
+"""The tiered recurrent layers on the GPU (layers.MultiTierLSTMLayer, layers.DualLSTMLayer over fml_lstm_cell_fwd/bwd and
+the library's products) against the oracle's composition of the reference's vector operations
+(lib/layertypes/multilstm.dart:111-178, lib/layertypes/duallstm.dart:98-175)."""
+import numpy as np
+import pytest
+
+from tests.gpu_util import rel
+
+pytestmark = pytest.mark.gpu
+w64 = lambda x: np.ascontiguousarray(x, dtype=np.float64)  # noqa: E731
+
+
+def test_lstm_cell_kernels(orc):
+    """fml_lstm_cell_fwd / _bwd alone: gate blocks f | i | c~ | o, the reference's activation rules (sigmoid, tanh with its
+    overflow rule, derivatives from the outputs), with and without incoming dc, writing and accumulating dc_prev."""
+    from flutter_ml_b200 import _lib
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    rng = np.random.default_rng(3)
+    B, H = 7, 20
+    pre, cp = rng.standard_normal((B, 4 * H)).astype(np.float32) * 2, rng.standard_normal((B, H)).astype(np.float32)
+    dh, dc = rng.standard_normal((B, H)).astype(np.float32), rng.standard_normal((B, H)).astype(np.float32)
+    d_pre, d_cp = ctx.upload(pre), ctx.upload(cp)
+    gates, c, h = ctx.empty(B, 4 * H), ctx.empty(B, H), ctx.empty(B, H)
+    ctx.call("fml_lstm_cell_fwd", d_pre, d_cp, gates, c, h, B, H)
+    sg = lambda z: 1 / (1 + np.exp(-z))  # noqa: E731
+    p = w64(pre)
+    f, i, g, o = sg(p[:, :H]), sg(p[:, H:2 * H]), np.tanh(p[:, 2 * H:3 * H]), sg(p[:, 3 * H:])
+    c_ref = f * w64(cp) + i * g
+    h_ref = o * np.tanh(c_ref)
+    assert rel(gates.numpy(), np.concatenate([f, i, g, o], 1)) <= 1e-6
+    assert rel(c.numpy(), c_ref) <= 1e-6 and rel(h.numpy(), h_ref) <= 1e-6
+    for use_dc in (True, False):
+        for acc in (0, 1):
+            dpre, dcp0 = ctx.empty(B, 4 * H), rng.standard_normal((B, H)).astype(np.float32)
+            dcp = ctx.upload(dcp0)
+            ctx.call("fml_lstm_cell_bwd", gates, d_cp, c, ctx.upload(dh), ctx.upload(dc) if use_dc else None, dpre, dcp, acc, B, H)
+            tc = np.tanh(c_ref)
+            dct = (w64(dc) if use_dc else 0.0) + w64(dh) * o * (1 - tc * tc)
+            ref = np.concatenate([dct * w64(cp) * f * (1 - f), dct * g * i * (1 - i), dct * i * (1 - g * g), w64(dh) * tc * o * (1 - o)], 1)
+            assert rel(dpre.numpy(), ref) <= 2e-6
+            assert rel(dcp.numpy(), dct * f + (w64(dcp0) if acc else 0.0)) <= 2e-6
+    assert ctx.device_status() == 0
+    ctx.close()
+
+
+@pytest.mark.parametrize("kind,cycles,B,Tn,H,I,prec", [
+    ("multi", [3, 2], 4, 14, 32, 12, 1), ("multi", [2], 1, 9, 16, 5, 1), ("multi", [2, 2, 2], 3, 17, 8, 4, 2),
+    ("dual", [4], 3, 13, 64, 8, 1), ("dual", [1], 2, 6, 16, 4, 2), ("multi", [3, 2], 5, 14, 32, 12, 0)])
+def test_tiered_lstm_layers(orc, kind, cycles, B, Tn, H, I, prec):
+    """Last hidden state of tier 0, loss, every parameter gradient (in the reference's order, tier by tier) and the input
+    gradient against the oracle, sequence by sequence; 3xTF32 and FP32 at 1e-5 / 2e-5, TF32 at the bounds of a chain of
+    truncating products."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200 import tensor as T
+    from flutter_ml_b200.layers import DualLSTMLayer, MultiTierLSTMLayer
+    from flutter_ml_b200.tensor import Tensor
+    ctx = _lib.Context(precision=prec)
+    rng = np.random.default_rng(100 * B + Tn + H)
+    n = len(cycles) + 1
+    combs = [H + (n - 1) * H + I] + [2 * H] * (n - 1)
+    Ws = [rng.uniform(-1, 1, (4 * H, cb)).astype(np.float32) * np.float32(np.sqrt(1.0 / cb)) for cb in combs]
+    bs = [rng.uniform(-0.1, 0.1, 4 * H).astype(np.float32) for _ in range(n)]
+    x = rng.standard_normal((Tn, B, I)).astype(np.float32)
+    target = rng.standard_normal((B, H)).astype(np.float32)
+    layer = (DualLSTMLayer(H, cycles[0], weights=Ws, biases=bs) if kind == "dual" else MultiTierLSTMLayer(H, cycles, weights=Ws, biases=bs))
+    xin = Tensor(x[:, 0, :] if B == 1 else x, ctx)
+    xin.zeroGrad()                                   # ask for the input gradient
+    out = layer(xin)
+    assert out.shape == (B, H) and len(layer.parameters) == 8 * n
+    loss = T.mseMatrix(out, Tensor(target, ctx), weight=float(B))       # = sum over sequences of mse(h_b, target_b)
+    loss.backward()
+    h_ref, loss_ref = np.zeros((B, H)), 0.0
+    dW_ref, db_ref, dx_ref = [np.zeros_like(w64(w)) for w in Ws], [np.zeros(4 * H) for _ in range(n)], np.zeros((Tn, B, I))
+    for b in range(B):
+        h_b, l_b, dWs, dbs, dx_b = orc.tiered_lstm_fwd_bwd(w64(x[:, b, :]), [w64(w) for w in Ws], [w64(v) for v in bs], cycles, w64(target[b]),
+                                                            dual=(kind == "dual"))
+        h_ref[b], loss_ref = h_b, loss_ref + l_b
+        for i in range(n):
+            dW_ref[i] += dWs[i]
+            db_ref[i] += dbs[i]
+        dx_ref[:, b, :] = dx_b
+    t_out, t_grad = {0: (2e-3, 5e-3), 1: (1e-5, 2e-5), 2: (1e-5, 2e-5)}[prec]
+    errs = {"h": rel(out.numpy(), h_ref), "dx": rel(xin.grad_numpy().reshape(Tn, B, I), dx_ref)}
+    for i in range(n):
+        for g in range(4):
+            Wg, bg = layer.parameters[8 * i + 2 * g], layer.parameters[8 * i + 2 * g + 1]
+            assert np.array_equal(Wg.numpy(), Ws[i][g * H:(g + 1) * H]) and np.array_equal(bg.numpy(), bs[i][g * H:(g + 1) * H])
+        errs[f"dW{i}"] = rel(np.concatenate([layer.parameters[8 * i + 2 * g].grad_numpy() for g in range(4)]), dW_ref[i])
+        errs[f"db{i}"] = rel(np.concatenate([layer.parameters[8 * i + 2 * g + 1].grad_numpy() for g in range(4)]), db_ref[i])
+    print(f"PARITY tiered-lstm {kind} {cycles} B{B} T{Tn} H{H} prec{prec}: " + " ".join(f"{k} {v:.1e}" for k, v in errs.items()))
+    assert errs["h"] <= t_out and abs(loss.numpy()[0] - loss_ref) <= 2 * t_out * abs(loss_ref)
+    for k, v in errs.items():
+        if k != "h":
+            assert v <= t_grad, (k, v)
+    assert ctx.device_status() == 0
+    ctx.close()
+
+
+def test_snetwork_with_a_dual_lstm_layer_trains():
+    """SNetwork([DualLSTMLayer, DenseLayerMatrix]) with fit(), the shape of the reference's demo
+    (lib/layertypes/duallstm.dart:180-300): the loss goes down."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200.layers import DenseLayerMatrix, DualLSTMLayer
+    from flutter_ml_b200.optimizers import Adam
+    from flutter_ml_b200.snet import SNetwork
+    from flutter_ml_b200.tensor import Tensor, set_default_context
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    set_default_context(ctx)
+    rng = np.random.default_rng(1)
+    t = np.arange(400) * 0.3
+    wave = np.sin(t) + 0.5 * np.sin(t / 7.0)
+    xs = [Tensor(wave[i:i + 14].reshape(14, 1).astype(np.float32), ctx) for i in range(0, 60, 3)]
+    ys = [Tensor(np.array([[wave[i + 14]]], dtype=np.float32), ctx) for i in range(0, 60, 3)]
+    net = SNetwork([DualLSTMLayer(12, 7, seed=2), DenseLayerMatrix(1, None, seed=3)])
+    net.predict(xs[0])
+    net.compile(Adam(net.parameters, 0.02))
+    hist = net.fit(xs, ys, epochs=12)
+    assert hist[-1] < 0.5 * hist[0]
+    assert ctx.device_status() == 0
+    ctx.close()
