@@ -216,8 +216,8 @@ class MultiTierLSTMLayer(Layer):
     [H x combined] of the reference live in one [4H x combined] buffer (gate blocks f, i, c~, o), the biases in one [4H]
     buffer; `parameters` hands out the reference's tensors in its order, tier by tier (W_f, b_f, W_i, b_i, W_c, b_c, W_o,
     b_o, :44-52), as views.  A cell update is: one product per input block into the [B x 4H] pre-activations (the first
-    with the bias in its epilogue, the others accumulating; the concatenated input of the reference never exists), then
-    fml_lstm_cell_fwd.  Backward runs the recorded updates in reverse with fml_lstm_cell_bwd and the transposed
+    with the bias in its epilogue, the others accumulating; the concatenated input of the reference never exists; the
+    input's block of tier 0 is one product over all time steps), then fml_lstm_cell_fwd.  Backward runs the recorded updates in reverse with fml_lstm_cell_bwd and the transposed
     products; gradients of states that feed several later updates accumulate in place.  Initial weights
     U(+-sqrt(1/fanIn)) (:66-77) from the seeded generator unless `weights` / `biases` (one array per tier) are given."""
     name = "multitier_lstm"
@@ -272,26 +272,34 @@ class MultiTierLSTMLayer(Layer):
         Tn, B, I = (x.shape[0], 1, x.shape[1]) if len(x.shape) == 2 else x.shape
         zero = ctx.zeros(B, H)                       # every initial state (read only)
         h, c = [zero] * n, [zero] * n
-        records = []                                 # (tier, [(input block, width, first column, step or -1)], c_prev, gates, c_new, h_new)
+        records = []                                 # (tier, step, [(input block, width, first column)], c_prev, gates, c_new, h_new)
+        comb0 = self._combined(0, I)
+        # The input's share of tier 0's pre-activations does not depend on the recurrence: one product for all steps
+        # (bias in its epilogue); the recurrent blocks are added step by step.
+        pre_all = ctx.empty(Tn * B, 4 * H)
+        ctx.gemm(x.value, self.W[0].view(n * H, (4 * H, I)), pre_all, Tn * B, 4 * H, I, transB=True, ldb=comb0, bias=self.b[0])
 
-        def update(tier, blocks):
+        def update(tier, step, blocks, pre=None):
             comb = self._combined(tier, I)
-            pre = ctx.empty(B, 4 * H)
-            for k, (arr, w, col, _) in enumerate(blocks):
+            first = pre is None
+            if first:
+                pre = ctx.empty(B, 4 * H)
+            for k, (arr, w, col) in enumerate(blocks):
+                if arr is zero and not (first and k == 0):
+                    continue                          # an initial state adds nothing
                 ctx.gemm(arr, self.W[tier].view(col, (4 * H, w)), pre, B, 4 * H, w, transB=True, ldb=comb,
-                         bias=self.b[tier] if k == 0 else None, beta=0.0 if k == 0 else 1.0)
+                         bias=self.b[tier] if (first and k == 0) else None, beta=0.0 if (first and k == 0) else 1.0)
             gates, c_new, h_new = ctx.empty(B, 4 * H), ctx.empty(B, H), ctx.empty(B, H)
             ctx.call("fml_lstm_cell_fwd", pre, c[tier], gates, c_new, h_new, B, H)
-            records.append((tier, blocks, c[tier], gates, c_new, h_new))
+            records.append((tier, step, blocks, c[tier], gates, c_new, h_new))
             h[tier], c[tier] = h_new, c_new
 
         for t in range(Tn):
-            x_t = x.value.view(t * B * I, (B, I))
-            blocks = [(h[0], H, 0, -1)] + [(c[j], H, j * H, -1) for j in range(1, n)] + [(x_t, I, n * H, t)]
-            update(0, blocks)
+            blocks = [(h[0], H, 0)] + [(c[j], H, j * H) for j in range(1, n)]
+            update(0, t, blocks, pre_all.view(t * B * 4 * H, (B, 4 * H)))
             for i in range(1, n):
                 if self._fires(i, t):
-                    update(i, [(h[i], H, 0, -1), (h[i - 1], H, H, -1)])
+                    update(i, t, [(h[i], H, 0), (h[i - 1], H, H)])
         out = Tensor(h[0], ctx)
         want_dx = x.creator is not None or x.grad is not None
 
@@ -303,27 +311,32 @@ class MultiTierLSTMLayer(Layer):
                 if g is None:
                     g = grads[id(arr)] = ctx.zeros(B, H)
                 return g
-            dx = ctx.zeros(*x.shape) if want_dx else None
-            for tier, blocks, c_prev, gates, c_new, h_new in reversed(records):
+            dpre_all = ctx.zeros(Tn * B, 4 * H)       # tier 0's pre-activation gradients of all steps (zero where none flows)
+            for tier, step, blocks, c_prev, gates, c_new, h_new in reversed(records):
                 dh, dc = grads.get(id(h_new)), grads.get(id(c_new))
                 if dh is None and dc is None:
                     continue                          # nothing downstream read this update
                 comb = self._combined(tier, I)
-                dpre = ctx.empty(B, 4 * H)
+                dpre = dpre_all.view(step * B * 4 * H, (B, 4 * H)) if tier == 0 else ctx.empty(B, 4 * H)
                 if c_prev is zero:
                     dcp, acc = ctx.empty(B, H), 0     # gradient of the initial state: formed, not used
                 else:
                     acc = 1 if id(c_prev) in grads else 0
-                    dcp = grads.setdefault(id(c_prev), ctx.empty(B, H)) if not acc else grads[id(c_prev)]
+                    dcp = grads[id(c_prev)] if acc else grads.setdefault(id(c_prev), ctx.empty(B, H))
                 ctx.call("fml_lstm_cell_bwd", gates, c_prev, c_new, dh, dc, dpre, dcp, acc, B, H)
-                ctx.call("fml_col_sum", dpre, self.db[tier], B, 4 * H, 1)
-                for arr, w, col, step in blocks:
+                if tier > 0:
+                    ctx.call("fml_col_sum", dpre, self.db[tier], B, 4 * H, 1)
+                for arr, w, col in blocks:
+                    if arr is zero:
+                        continue                      # no weight gradient from a zero input, no gradient into it
                     ctx.gemm(dpre, arr, self.dW[tier].view(col, (4 * H, w)), 4 * H, w, B, transA=True, ldc=comb, beta=1.0)
-                    if arr is zero or (step >= 0 and dx is None):
-                        continue
-                    target = dx.view(step * B * I, (B, I)) if step >= 0 else grad_of(arr)
-                    ctx.gemm(dpre, self.W[tier].view(col, (4 * H, w)), target, B, w, 4 * H, ldb=comb, beta=1.0)
-            if dx is not None:
+                    ctx.gemm(dpre, self.W[tier].view(col, (4 * H, w)), grad_of(arr), B, w, 4 * H, ldb=comb, beta=1.0)
+            # the input's share, all steps at once
+            ctx.call("fml_col_sum", dpre_all, self.db[0], Tn * B, 4 * H, 1)
+            ctx.gemm(dpre_all, x.value, self.dW[0].view(n * H, (4 * H, I)), 4 * H, I, Tn * B, transA=True, ldc=comb0, beta=1.0)
+            if want_dx:
+                dx = ctx.empty(*x.shape)
+                ctx.gemm(dpre_all, self.W[0].view(n * H, (4 * H, I)), dx, Tn * B, I, 4 * H, ldb=comb0)
                 x._add_grad(dx, alias=True)
         out.creator = T.Node([x] + self._params, bw, self.name, cost=8 * len(records) * B * H * 2 * H)
         return out

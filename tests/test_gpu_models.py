@@ -8,7 +8,9 @@ pytestmark = pytest.mark.gpu
 w64 = lambda x: np.ascontiguousarray(x, dtype=np.float64)  # noqa: E731
 
 # Whole-model tolerances (relative Frobenius error vs the float64 oracle): (outputs, gradients).
-#  - 3xTF32: 2e-5 / 5e-5.  This mode pins the LOGIC of every layer and of the tape.
+#  - 3xTF32: 1e-5 for both, the tolerance stated for one product.  Measured on these three models: logits / outputs
+#    5e-7 .. 2.3e-6, gradients 7e-7 .. 6.8e-6 (the deepest chain, the language model's embedding gradient); every test
+#    prints its figures.  This mode pins the LOGIC of every layer and of the tape.
 #  - TF32: a single product is within 1e-3 (5.5e-4 measured, test_gpu_kernels.py); outputs of a chain of
 #    products are held to 2e-3.  Gradients of these three models pass through ReLU gates
 #    (tensor.dart:1030), which are discontinuous: a pre-activation within ~5e-4 of zero can land on the
@@ -16,7 +18,7 @@ w64 = lambda x: np.ascontiguousarray(x, dtype=np.float64)  # noqa: E731
 #    error of about sqrt(f) (f ~ 5e-4 -> ~2e-2) for ANY TF32 product, however exact the kernel is.  The
 #    gradient bound in TF32 mode is therefore 5e-2; per-kernel gradient parity at 1e-3 is asserted in
 #    test_gpu_kernels.py on identical gate inputs.
-TOLS = {0: (2e-3, 5e-2), 1: (2e-5, 5e-5)}
+TOLS = {0: (2e-3, 5e-2), 1: (1e-5, 1e-5)}
 
 
 @pytest.mark.parametrize("prec", [0, 1])
