@@ -185,10 +185,23 @@ def tiered_lstm(ctx):
         loss = T.mseMatrix(layer(x), target)
         loss.backward()
     ms, launches = _timed(ctx, step, warm=2, reps=3)
+    # the same step recorded once as a CUDA graph and replayed: what is left when the host's launch calls are out of the way
+    import gc
+    gc.collect()
+    graph_ms = None
+    ctx.graph_begin()
+    try:
+        step()
+        gc.collect()                    # every buffer allocated while recording is freed while recording
+    finally:
+        gid = ctx.graph_end()
+    if gid >= 0:
+        graph_ms, _ = _timed(ctx, lambda: ctx.graph_launch(gid), warm=2, reps=5)
     updates = Tn + sum(1 for t in range(Tn) if t > 0 and (t + 1) % cyc == 0)
     flops = 3.0 * 2 * B * 4 * H * (Tn * (2 * H + I) + (updates - Tn) * 2 * H)
     return {"config": f"DualLSTM I{I} H{H} T{Tn} B{B} cycle {cyc} fwd+bwd (next-row layer, not a BASELINE config)", "ms_per_step": round(ms, 3),
-            "tflops": round(flops / ms / 1e9, 1), "us_per_update_and_direction": round(ms * 1e3 / (2 * updates), 1), "launches_per_step": launches}
+            "tflops": round(flops / ms / 1e9, 1), "us_per_update_and_direction": round(ms * 1e3 / (2 * updates), 1), "launches_per_step": launches,
+            "graph_ms_per_step": round(graph_ms, 3) if graph_ms else None}
 
 
 def run(ctx, only: int = 0):
