@@ -1094,7 +1094,7 @@ constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 98304, CO_QMN =
 constexpr int FA2_SMEM = CO_BAR + 256 + 1024;
 constexpr uint32_t T2_ST = 0, T2_DPT = 256, T2_DV = 384, T2_DK = 448;
 enum { D_KFULL = 0, D_KEMPTY, D_VFULL, D_VEMPTY, D_QKFULL, D_QKEMPTY, D_DOKFULL, D_DOKEMPTY, D_QMNFULL, D_QMNEMPTY, D_DOMNFULL,
-       D_DOMNEMPTY, D_STFULL /* two */, D_STFULL1, D_DPTFULL, D_PTFULL, D_DSTFULL, D_ACCDONE, D_STAGED, D_STFREE, D_COUNT };
+       D_DOMNEMPTY, D_STFULL /* two */, D_STFULL1, D_DPTFULL, D_PTFULL, D_DSTFULL, D_DVDONE, D_ACCDONE, D_STAGED, D_STFREE, D_COUNT };
 
 struct FaBwd2Params {
   int S, H, n_kb, causal;
@@ -1275,6 +1275,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
               umma_tf32_ts(tmem_base + T2_DV, tmem_base + T2_ST + bf * 128 + c * 32 + k * 8, bdo + 64u * k, idesc_acc, (i | c | k) ? 1u : 0u);
           }
           umma_commit(bar(D_DOMNEMPTY));
+          umma_commit(bar(D_DVDONE));
           ok = mbar_wait(bar(D_DSTFULL), ph, abort_flag, p.status, 46) && mbar_wait(bar(D_QMNFULL), ph, abort_flag, p.status, 47);
           if (!ok) break;
           tc_fence_after();
@@ -1322,23 +1323,25 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     float prs[64];
     uint32_t u = 0, n_st = 0;
     bool pending = false;        // a finished item whose dV / dK tiles are still to be read
-    auto flush_acc = [&]() {     // after dK of block u-1 (the pending item's last) has been accumulated
-      if (!mbar_wait_warp(bar(D_ACCDONE), (u - 1) & 1u, abort_flag, p.status, 38)) return false;
+    // The two tiles of a finished item leave one after the other through the one staging tile: dV as soon as its last
+    // product has run (dK's last product is still running then), before this thread publishes the next item's first P^T
+    // (whose product overwrites the dV accumulator); dK before it publishes the next item's first dS^T.  In between the
+    // thread waits for dP^T of the new block anyway, which is when the store warp reads the staging tile.
+    auto flush_tile = [&](int which) {
+      if (!mbar_wait_warp(bar(which ? D_ACCDONE : D_DVDONE), (u - 1) & 1u, abort_flag, p.status, which ? 38 : 51)) return false;
       tc_fence_after();
-      for (int which = 0; which < 2; which++, n_st++) {   // one tile after the other through the one staging tile
-        tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + half * 32, tv);
-        tmem_ld_wait();
-        if (!mbar_wait_warp(bar(D_STFREE), (n_st & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
-        uint8_t* srow = smem_gen + CO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, chunks swizzled
+      tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + half * 32, tv);
+      tmem_ld_wait();
+      tc_fence_before();   // the accumulator has been read before this thread's next arrival lets a product overwrite it
+      if (!mbar_wait_warp(bar(D_STFREE), (n_st & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
+      uint8_t* srow = smem_gen + CO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, chunks swizzled
 #pragma unroll
-        for (int ch = 0; ch < 8; ch++)
-          *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) =
-              make_float4(__uint_as_float(tv[4 * ch]), __uint_as_float(tv[4 * ch + 1]), __uint_as_float(tv[4 * ch + 2]), __uint_as_float(tv[4 * ch + 3]));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive_warp(bar(D_STAGED));
-      }
-      tc_fence_before();   // both accumulators read before this thread publishes the next item's first P^T
-      pending = false;
+      for (int ch = 0; ch < 8; ch++)
+        *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) =
+            make_float4(__uint_as_float(tv[4 * ch]), __uint_as_float(tv[4 * ch + 1]), __uint_as_float(tv[4 * ch + 2]), __uint_as_float(tv[4 * ch + 3]));
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive_warp(bar(D_STAGED));
+      n_st++;
       return true;
     };
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
@@ -1383,7 +1386,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         tmem_st_wait();
         tc_fence_before();
         if (pending) {
-          ok = flush_acc();
+          ok = flush_tile(0);
           if (!ok) break;
         }
         mbar_arrive_warp(bar(D_PTFULL));
@@ -1410,11 +1413,16 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
         tmem_st_wait();
         tc_fence_before();
+        if (pending) {
+          ok = flush_tile(1);
+          if (!ok) break;
+          pending = false;
+        }
         mbar_arrive_warp(bar(D_DSTFULL));
       }
       if (ok && n_it > 0) pending = true;
     }
-    if (ok && pending) ok = flush_acc();
+    if (ok && pending) ok = flush_tile(0) && flush_tile(1);
   }
   tc_fence_before();
   __syncthreads();
