@@ -137,8 +137,21 @@ def config3_encoder_block(ctx):
             p.grad = None
     ms, launches = _timed(ctx, step)
     flops = 1.675e11
-    return {"config": "C3 encoder block d512 h8 dff2048 S256 B32 causal fwd+bwd", "ms_per_step": round(ms, 3),
-            "tflops": round(flops / ms / 1e9, 1), "sequences_per_s": round(B / ms * 1e3, 1), "launches_per_step": launches}
+    out = {"config": "C3 encoder block d512 h8 dff2048 S256 B32 causal fwd+bwd", "ms_per_step": round(ms, 3),
+           "tflops": round(flops / ms / 1e9, 1), "sequences_per_s": round(B / ms * 1e3, 1), "launches_per_step": launches}
+    # the same step recorded once as a CUDA graph and replayed (29 launches issued with one call)
+    import gc
+    gc.collect()
+    ctx.graph_begin()
+    try:
+        step()
+        gc.collect()                    # every buffer allocated while recording is freed while recording
+    finally:
+        gid = ctx.graph_end()
+    if gid >= 0:
+        gms, _ = _timed(ctx, lambda: ctx.graph_launch(gid), warm=3, reps=20)
+        out.update({"graph_ms_per_step": round(gms, 3), "graph_tflops": round(flops / gms / 1e9, 1)})
+    return out
 
 
 def config4_lstm(ctx):

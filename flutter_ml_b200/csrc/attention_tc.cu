@@ -38,7 +38,8 @@ namespace {
 
 constexpr int BQ = 128, BKV = 128, DH = 64;
 constexpr int FA_THREADS = 640;      // forward: Q/K producer, issuer, 16 softmax warps (four per TMEM lane quarter, 32 keys each), V producer, store warp
-constexpr int FA_BWD_THREADS = 352;  // backward: producer, issuer, 8 compute warps (two per TMEM lane quarter, alternate 32-column chunks), store warp
+constexpr int FA_BWD_THREADS = 352;  // dQ kernel: producer, issuer, 8 compute warps (two per TMEM lane quarter, alternate 32-column chunks), store warp
+constexpr int FA_DKV_THREADS = 608;  // dK/dV kernel: producer, issuer, 16 compute warps (four per TMEM lane quarter, one 32-query chunk each), store warp
 constexpr uint32_t OFF_Q = 0, OFF_K = 32768, OFF_V = 98304, OFF_XCH = 196608, OFF_ST = 204800, OFF_BAR = 229376;   // forward: Q, 2 x K, 3 x V, row exchange, output staging (16 KiB)
 constexpr int FA_SMEM = OFF_BAR + 256 + 2048 + 512;   // barriers, the row exchange (forward), alignment slack
 constexpr int K_STAGES = 2, V_STAGES = 3;   // a V tile arrived about 5000 cycles after its buffer came free (measured): two stages stalled every item's first P.V
@@ -1094,7 +1095,7 @@ constexpr uint32_t CO_K = 0, CO_V = 32768, CO_Q = 65536, CO_DO = 98304, CO_QMN =
 constexpr int FA2_SMEM = CO_BAR + 256 + 1024;
 constexpr uint32_t T2_ST = 0, T2_DPT = 256, T2_DV = 384, T2_DK = 448;
 enum { D_KFULL = 0, D_KEMPTY, D_VFULL, D_VEMPTY, D_QKFULL, D_QKEMPTY, D_DOKFULL, D_DOKEMPTY, D_QMNFULL, D_QMNEMPTY, D_DOMNFULL,
-       D_DOMNEMPTY, D_STFULL /* two */, D_STFULL1, D_DPTFULL, D_PTFULL, D_DSTFULL, D_DVDONE, D_ACCDONE, D_STAGED, D_STFREE, D_COUNT };
+       D_DOMNEMPTY, D_STFULL /* two */, D_STFULL1, D_DPTFULL, D_PTFULL, D_DSTFULL, D_DVDONE, D_ACCDONE, D_STAGED, D_STFREE, D_DVREAD, D_DKREAD, D_COUNT };
 
 struct FaBwd2Params {
   int S, H, n_kb, causal;
@@ -1105,9 +1106,10 @@ struct FaBwd2Params {
   float* dk; float* dv; long long ld;
   int accumulate;
   int* status;
+  long long* prof;    // -DFML_FA_PROFILE builds, else NULL
 };
 
-__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
+__global__ void __launch_bounds__(FA_DKV_THREADS, 1)
 attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                          const __grid_constant__ CUtensorMap tmQmn, const __grid_constant__ CUtensorMap tmDOmn,
@@ -1139,7 +1141,8 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < D_COUNT; i++) mbar_init(bar(i), (i == D_PTFULL || i == D_DSTFULL || i == D_STAGED) ? 8u : 1u);   // warps (mbar_arrive_warp)
+    for (int i = 0; i < D_COUNT; i++)
+      mbar_init(bar(i), (i == D_PTFULL || i == D_DSTFULL || i == D_STAGED || i == D_DVREAD || i == D_DKREAD) ? 16u : 1u);   // warps (mbar_arrive_warp)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1153,6 +1156,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  FA_TOTAL_BEGIN();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1250,9 +1254,11 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         item_coords(item, kbk, h, b, i0, n_it);
         for (int i = 0; i < n_it && ok; i++, u++) {
           const uint32_t ph = u & 1u, bf = u & 1u;
+          FA_STAMP(p.prof, u, 8);
           if (i == 0) ok = mbar_wait(bar(D_VFULL), it & 1u, abort_flag, p.status, 34);
           ok = ok && mbar_wait(bar(D_DOKFULL), ph, abort_flag, p.status, 45);
           if (!ok) break;
+          FA_STAMP(p.prof, u, 9);
           tc_fence_after();
           for (int kb = 0; kb < 2; kb++) {
             const uint64_t av = make_smem_desc(smem_base + CO_V + kb * 16384, 16u, 1024u, 2u);
@@ -1263,10 +1269,15 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           umma_commit(bar(D_DPTFULL));
           umma_commit(bar(D_DOKEMPTY));
           if (i == n_it - 1) umma_commit(bar(D_VEMPTY));
+          FA_STAMP(p.prof, u, 10);
           if (s_u == u + 1) ok = issue_st();   // S^T of the next block: its exponentials overlap dV and dK of this one
           if (!ok) break;
+          FA_STAMP(p.prof, u, 11);
           ok = mbar_wait(bar(D_PTFULL), ph, abort_flag, p.status, 35) && mbar_wait(bar(D_DOMNFULL), ph, abort_flag, p.status, 40);
+          // the first dV product of an item overwrites the accumulator: the compute warps must have read the previous item's
+          if (ok && i == 0 && it > 0) ok = mbar_wait(bar(D_DVREAD), (it - 1) & 1u, abort_flag, p.status, 52);
           if (!ok) break;
+          FA_STAMP(p.prof, u, 12);
           tc_fence_after();
           for (int c = 0; c < 4; c++) {   // 32 queries per chunk, 8 per instruction; A operand = P^T in tensor memory
             const uint64_t bdo = make_smem_desc(smem_base + CO_DOMN + c * 8192, 4096u, 512u, 1u);
@@ -1276,8 +1287,11 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           }
           umma_commit(bar(D_DOMNEMPTY));
           umma_commit(bar(D_DVDONE));
+          FA_STAMP(p.prof, u, 13);
           ok = mbar_wait(bar(D_DSTFULL), ph, abort_flag, p.status, 46) && mbar_wait(bar(D_QMNFULL), ph, abort_flag, p.status, 47);
+          if (ok && i == 0 && it > 0) ok = mbar_wait(bar(D_DKREAD), (it - 1) & 1u, abort_flag, p.status, 53);   // likewise for dK
           if (!ok) break;
+          FA_STAMP(p.prof, u, 14);
           tc_fence_after();
           for (int c = 0; c < 4; c++) {
             const uint64_t bq = make_smem_desc(smem_base + CO_QMN + c * 8192, 4096u, 512u, 1u);
@@ -1287,10 +1301,11 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           }
           umma_commit(bar(D_ACCDONE));
           umma_commit(bar(D_QMNEMPTY));
+          FA_STAMP(p.prof, u, 15);
         }
       }
     }
-  } else if (warp == FA_BWD_THREADS / 32 - 1) {
+  } else if (warp == FA_DKV_THREADS / 32 - 1) {
     // ------------------------------------------------------------------ store warp: dV, then dK, of every finished item
     if (lane == 0) {
       bool ok = true;
@@ -1299,7 +1314,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         int kbk, h, b, i0, n_it;
         item_coords(item, kbk, h, b, i0, n_it);
         for (int which = 0; which < 2 && ok; which++, n++) {
-          ok = mbar_wait(bar(D_STAGED), n & 1u, abort_flag, p.status, 48);   // all 256 rows of the tile are in shared memory
+          ok = mbar_wait(bar(D_STAGED), n & 1u, abort_flag, p.status, 48);   // the whole tile is in shared memory
           if (!ok) break;
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           const CUtensorMap* tm = which ? &tmDK : &tmDV;
@@ -1315,30 +1330,34 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
   } else {
     const int q4 = warp & 3;
-    const int half = (warp - 2) >> 2;          // the two warps of a lane quarter take alternate 32-query chunks
+    const int part = (warp - 2) >> 2;          // which 32-query chunk of every block, and which 16 columns of dV / dK
     const int row = q4 * 32 + lane;            // key inside the block
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
     bool ok = true;
     uint32_t tv[32];
-    float prs[64];
+    float prs[32];
     uint32_t u = 0, n_st = 0;
     bool pending = false;        // a finished item whose dV / dK tiles are still to be read
-    // The two tiles of a finished item leave one after the other through the one staging tile: dV as soon as its last
-    // product has run (dK's last product is still running then), before this thread publishes the next item's first P^T
-    // (whose product overwrites the dV accumulator); dK before it publishes the next item's first dS^T.  In between the
-    // thread waits for dP^T of the new block anyway, which is when the store warp reads the staging tile.
+    // The tiles of a finished item are read AFTER this thread has published the next item's first P^T / dS^T (the issuer
+    // holds the first overwriting product back until all warps have read: D_DVREAD, D_DKREAD), so that reading, staging
+    // and storing them is off the path from an operand to its product; measured with the reads in front of the
+    // publication, an item boundary cost 5000 cycles, as much as a whole block.  Sixteen compute warps: with eight, the
+    // same ordering gained nothing (293 us for the backward pass); with sixteen the boundary shrinks to about 1400 cycles
+    // although the products of the steady state get slower (126 against 104 cycles per instruction), 278 us in all.
     auto flush_tile = [&](int which) {
       if (!mbar_wait_warp(bar(which ? D_ACCDONE : D_DVDONE), (u - 1) & 1u, abort_flag, p.status, which ? 38 : 51)) return false;
       tc_fence_after();
-      tmem_ld32(lane_addr + (which ? T2_DK : T2_DV) + half * 32, tv);
+      uint32_t t16[16];
+      tmem_ld16(lane_addr + (which ? T2_DK : T2_DV) + part * 16, t16);
       tmem_ld_wait();
-      tc_fence_before();   // the accumulator has been read before this thread's next arrival lets a product overwrite it
+      tc_fence_before();
+      mbar_arrive_warp(bar(which ? D_DKREAD : D_DVREAD));
       if (!mbar_wait_warp(bar(D_STFREE), (n_st & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
-      uint8_t* srow = smem_gen + CO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, chunks swizzled
+      uint8_t* srow = smem_gen + CO_ST + (part >> 1) * 16384 + row * 128;   // K-major tile layout: 128-byte rows, chunks swizzled
 #pragma unroll
-      for (int ch = 0; ch < 8; ch++)
-        *reinterpret_cast<float4*>(srow + ((ch ^ (row & 7)) << 4)) =
-            make_float4(__uint_as_float(tv[4 * ch]), __uint_as_float(tv[4 * ch + 1]), __uint_as_float(tv[4 * ch + 2]), __uint_as_float(tv[4 * ch + 3]));
+      for (int i = 0; i < 4; i++)
+        *reinterpret_cast<float4*>(srow + ((((part & 1) * 4 + i) ^ (row & 7)) << 4)) =
+            make_float4(__uint_as_float(t16[4 * i]), __uint_as_float(t16[4 * i + 1]), __uint_as_float(t16[4 * i + 2]), __uint_as_float(t16[4 * i + 3]));
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive_warp(bar(D_STAGED));
       n_st++;
@@ -1352,32 +1371,38 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       for (int i = 0; i < n_it && ok; i++, u++) {
         const uint32_t bf = u & 1u;
         const int q0 = (i0 + i) * BQ;
-        if (lane < 8 && i + 1 < n_it) {   // statistics of the next query block (2 x 512 bytes): the loads below then hit the cache
+        if (lane < 8 && part == 0 && i + 1 < n_it) {   // statistics of the next query block (2 x 512 bytes): the loads below then hit the cache
           const float* nx = (lane < 4 ? p.lse : p.dsum) + stat_base + q0 + BQ + (lane & 3) * 32;
           asm volatile("prefetch.global.L2 [%0];" ::"l"(nx));
         }
         // phase A: P^T over S^T.  The row statistics of the queries are the same addresses for every lane (one
         // transaction per warp, L1 hits).
+#ifdef FML_FA_PROFILE
+        long long* const sprof = threadIdx.x == 64 ? p.prof : nullptr;
+#else
+        long long* const sprof = nullptr;
+        (void)sprof;
+#endif
+        FA_STAMP(sprof, u, 0);
         ok = mbar_wait_warp(bar(D_STFULL + bf), (u >> 1) & 1u, abort_flag, p.status, 36);
         if (!ok) break;
+        FA_STAMP(sprof, u, 1);
         tc_fence_after();
-#pragma unroll
-        for (int ci = 0; ci < 2; ci++) {
-          const int c = half + 2 * ci;
-          const uint32_t ta = lane_addr + T2_ST + bf * 128 + c * 32;
+        {
+          const uint32_t ta = lane_addr + T2_ST + bf * 128 + part * 32;
           tmem_ld32(ta, tv);
           tmem_ld_wait();
-          const float4* Lp = reinterpret_cast<const float4*>(p.lse + stat_base + q0 + c * 32);
+          const float4* Lp = reinterpret_cast<const float4*>(p.lse + stat_base + q0 + part * 32);
 #pragma unroll
           for (int ch = 0; ch < 8; ch++) {
             const float4 L4 = __ldg(Lp + ch);
             const float* Le = reinterpret_cast<const float*>(&L4);
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-              const int col = c * 32 + ch * 4 + e;            // query inside the block
+              const int col = part * 32 + ch * 4 + e;            // query inside the block
               const bool vis = !p.causal || (q0 + col >= kj);
               const float pr = vis ? fa_exp2(fmaf(__uint_as_float(tv[ch * 4 + e]), p.k2, -Le[e])) : 0.f;
-              prs[ci * 32 + ch * 4 + e] = pr * p.scale;
+              prs[ch * 4 + e] = pr * p.scale;
               tv[ch * 4 + e] = __float_as_uint(fa_round_tf32(pr));
             }
           }
@@ -1385,45 +1410,49 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
         tmem_st_wait();
         tc_fence_before();
+        FA_STAMP(sprof, u, 2);
+        mbar_arrive_warp(bar(D_PTFULL));
+        FA_STAMP(sprof, u, 3);
         if (pending) {
           ok = flush_tile(0);
           if (!ok) break;
         }
-        mbar_arrive_warp(bar(D_PTFULL));
         // phase B: dS^T over dP^T
         ok = mbar_wait_warp(bar(D_DPTFULL), u & 1u, abort_flag, p.status, 37);
         if (!ok) break;
+        FA_STAMP(sprof, u, 4);
         tc_fence_after();
-#pragma unroll
-        for (int ci = 0; ci < 2; ci++) {
-          const int c = half + 2 * ci;
-          const uint32_t ta = lane_addr + T2_DPT + c * 32;
+        {
+          const uint32_t ta = lane_addr + T2_DPT + part * 32;
           tmem_ld32(ta, tv);
           tmem_ld_wait();
-          const float4* Dp = reinterpret_cast<const float4*>(p.dsum + stat_base + q0 + c * 32);
+          const float4* Dp = reinterpret_cast<const float4*>(p.dsum + stat_base + q0 + part * 32);
 #pragma unroll
           for (int ch = 0; ch < 8; ch++) {
             const float4 D4 = __ldg(Dp + ch);
             const float* De = reinterpret_cast<const float*>(&D4);
 #pragma unroll
             for (int e = 0; e < 4; e++)
-              tv[ch * 4 + e] = __float_as_uint(fa_round_tf32(prs[ci * 32 + ch * 4 + e] * (__uint_as_float(tv[ch * 4 + e]) - De[e])));
+              tv[ch * 4 + e] = __float_as_uint(fa_round_tf32(prs[ch * 4 + e] * (__uint_as_float(tv[ch * 4 + e]) - De[e])));
           }
           tmem_st32(ta, tv);
         }
         tmem_st_wait();
         tc_fence_before();
+        FA_STAMP(sprof, u, 5);
+        mbar_arrive_warp(bar(D_DSTFULL));
+        FA_STAMP(sprof, u, 6);
         if (pending) {
           ok = flush_tile(1);
           if (!ok) break;
           pending = false;
         }
-        mbar_arrive_warp(bar(D_DSTFULL));
       }
       if (ok && n_it > 0) pending = true;
     }
     if (ok && pending) ok = flush_tile(0) && flush_tile(1);
   }
+  FA_TOTAL_END(p.prof);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -1589,7 +1618,8 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   attention_bwd_dq_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA_SMEM, ctx->stream>>>(tmQ, tmDO, tmK, tmV, tmKmn, tmDQ, p);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dq_kernel");
 #ifdef FML_FA_PROFILE
-  if (++prof_calls == 4) {
+  ++prof_calls;
+  if (prof_calls == 4) {
     long long h[512];
     cudaStreamSynchronize(ctx->stream);
     cudaMemcpy(h, prof_buf, sizeof h, cudaMemcpyDeviceToHost);
@@ -1622,9 +1652,41 @@ int32_t fml_attention_bwd(fml_ctx* ctx, const fml_attention_desc* d, const float
   p2.dk = dk; p2.dv = dv; p2.ld = ld_dqkv; p2.accumulate = p.accumulate;
   p2.status = ctx->d_status;
   p2.n_items = (int)grid;
-  attention_bwd_dkv_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_BWD_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ, tmDO, tmQmn,
+  p2.prof = nullptr;
+#ifdef FML_FA_PROFILE
+  static long long* prof_buf2 = nullptr;
+  if (!prof_buf2) { cudaMalloc(&prof_buf2, 512 * sizeof(long long)); }
+  cudaMemsetAsync(prof_buf2, 0, 512 * sizeof(long long), ctx->stream);
+  p2.prof = prof_buf2;
+#endif
+  attention_bwd_dkv_kernel<<<std::min<unsigned>(grid, (unsigned)ctx->sm_count), FA_DKV_THREADS, FA2_SMEM, ctx->stream>>>(tmK, tmV, tmQ, tmDO, tmQmn,
                                                                                                                     tmDOmn, tmDK, tmDV, p2);
   FML_LAUNCH_CHECK(ctx, "attention_bwd_dkv_kernel");
+#ifdef FML_FA_PROFILE
+  if (prof_calls == 4) {
+    long long h[512];
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(h, prof_buf2, sizeof h, cudaMemcpyDeviceToHost);
+    fprintf(stderr, "attention bwd dK/dV, CTA 0, query blocks 8..15, cycles relative to block 8's first stamp\n"
+                    "compute: top | S^T full | P^T stored | P^T published | dP^T full | dS^T stored | dS^T published;  issuer: top | V,dO ready | dP^T issued | next S^T issued | P^T,dO ready | dV issued | dS^T,Q ready | dK issued\n");
+    const long long t0 = h[0];
+    for (int g = 0; g < 8; g++) {
+      fprintf(stderr, "u=%d cp:", g + 8);
+      for (int k = 0; k < 7; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
+      fprintf(stderr, "  is:");
+      for (int k = 8; k < 16; k++) fprintf(stderr, " %lld", h[g * 16 + k] ? h[g * 16 + k] - t0 : -1);
+      fprintf(stderr, "\n");
+    }
+    long long cmin = 1LL << 62, cmax = 0, csum = 0;
+    int n = 0;
+    for (int c = 0; c < 148; c++) {
+      const long long cy = h[128 + 2 * c];
+      if (!cy) continue;
+      n++; csum += cy; cmin = cy < cmin ? cy : cmin; cmax = cy > cmax ? cy : cmax;
+    }
+    if (n) fprintf(stderr, "per-CTA cycles over %d CTAs: min %lld avg %lld max %lld; CTA 0: %lld cycles in %lld ns\n", n, cmin, csum / n, cmax, h[128], h[129]);
+  }
+#endif
   return FML_OK;
 }
 
