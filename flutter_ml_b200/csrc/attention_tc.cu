@@ -764,7 +764,7 @@ namespace {
 constexpr uint32_t BO_Q = 0, BO_DO = 32768, BO_K = 65536, BO_V = 98304, BO_KMN = 131072, BO_ST = 196608;
 constexpr uint32_t TM_DP = 256, TM_DQ = 384;
 enum { C_QFULL = 0, C_QEMPTY = 2, C_DOFULL = 4, C_DOEMPTY = 5, C_KFULL = 6, C_KEMPTY = 7, C_VFULL = 8, C_VEMPTY = 9, C_KMNFULL = 10,
-       C_KMNEMPTY = 12, C_SFULL = 14, C_SEMPTY = 16, C_DPFULL = 18, C_DSFULL = 19, C_DQDONE = 20, C_STAGED = 21, C_STFREE = 22, C_COUNT = 23 };
+       C_KMNEMPTY = 12, C_SFULL = 14, C_SEMPTY = 16, C_DPFULL = 18, C_DSFULL = 19, C_DQDONE = 20, C_STAGED = 21, C_STFREE = 22, C_DQREAD = 23, C_COUNT = 24 };
 
 struct FaBwdParams {
   int S, H, n_qb, causal;
@@ -807,7 +807,7 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C_COUNT; i++) {
-      const bool from_compute = (i == C_SEMPTY || i == C_SEMPTY + 1 || i == C_DSFULL || i == C_STAGED);
+      const bool from_compute = (i == C_SEMPTY || i == C_SEMPTY + 1 || i == C_DSFULL || i == C_STAGED || i == C_DQREAD);
       mbar_init(bar(i), from_compute ? 8u : 1u);   // warps, not threads (mbar_arrive_warp)
     }
     *abort_flag = 0;
@@ -931,6 +931,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           if (!ok) break;
           FA_STAMP(p.prof, g, 12);
           ok = mbar_wait(bar(C_DSFULL), ph, abort_flag, p.status, 28) && mbar_wait(bar(C_KMNFULL + ms), (g >> 1) & 1u, abort_flag, p.status, 29);
+          // the first dQ product of an item overwrites the accumulator: the compute warps must have read the previous item's
+          if (ok && j == 0 && it > 0) ok = mbar_wait(bar(C_DQREAD), (it - 1) & 1u, abort_flag, p.status, 54);
           if (!ok) break;
           FA_STAMP(p.prof, g, 13);
           tc_fence_after();
@@ -982,7 +984,8 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       tc_fence_after();
       tmem_ld32(lane_addr + TM_DQ + half * 32, tv);
       tmem_ld_wait();
-      tc_fence_before();   // the accumulator has been read before this thread publishes the next item's first dS
+      tc_fence_before();
+      mbar_arrive_warp(bar(C_DQREAD));   // the issuer holds the next item's first dQ product back until all warps are here
       if (!mbar_wait_warp(bar(C_STFREE), (n_flush & 1u) ^ 1u, abort_flag, p.status, 49)) return false;   // previous tile stored
       uint8_t* srow = smem_gen + BO_ST + half * 16384 + row * 128;   // K-major tile layout: 128-byte rows, 16-byte chunks swizzled
 #pragma unroll
@@ -1039,10 +1042,6 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tc_fence_before();
         mbar_arrive_warp(bar(C_SEMPTY + buf));
         FA_STAMP(sprof, g, 2);
-        if (pending) {
-          ok = flush_dq();
-          if (!ok) break;
-        }
         FA_STAMP(sprof, g, 3);
         // phase B: dS over dP
         ok = mbar_wait_warp(bar(C_DPFULL), g & 1u, abort_flag, p.status, 34);
@@ -1062,6 +1061,10 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tc_fence_before();
         mbar_arrive_warp(bar(C_DSFULL));
         FA_STAMP(sprof, g, 5);
+        if (pending) {   // the finished item's tile, now that this item's first dS is published (off the operand's path)
+          ok = flush_dq();
+          if (!ok) break;
+        }
       }
       if (ok) pending = true;
     }
