@@ -1,5 +1,5 @@
 // Fused scaled-dot-product attention forward on the tensor cores: for one block of 128 queries of one
-// (sequence, head) the kernel walks the key/value blocks.  S = Q.K^T lands in tensor memory, four softmax warps turn
+// (sequence, head) the kernel walks the key/value blocks.  S = Q.K^T lands in tensor memory, sixteen softmax warps turn
 // it into probabilities IN PLACE (tcgen05.ld -> registers -> tcgen05.st over the same columns; scale and causal mask
 // folded in, base-2 exponentials), and the second product P.V reads its A operand straight from tensor memory and
 // accumulates the output in tensor memory across all key blocks.  Neither the scores nor the probabilities touch
@@ -8,7 +8,7 @@
 //
 // One CTA = 640 threads:
 //   warp 0      TMA producer: Q and K_j (two-stage ring); when all loads of an item are issued it prefetches the next
-//               item's first tiles into L2
+//               item's Q into L2
 //   warp 1      MMA issuer: S_j = Q.K_j^T into one of two TMEM buffers (S_{j+1} is issued before P_j.V_j, so it runs
 //               under the softmax of block j), then O += P_j.V_j once the softmax warps have published P_j
 //   warps 2..17 softmax: thread = one query row (TMEM lane) and a quarter of the block's keys, 32 scores in registers
@@ -744,8 +744,7 @@ namespace {
 // saved row statistics, forms dS = scale * P * (dP - D) with dP = dO.V^T and D = rowsum(dO * O), and accumulates
 // dQ = dS.K over the key blocks in TMEM.  dS never leaves tensor memory: the compute warps write it over dP
 // (tcgen05.st) and the third product reads its A operand from there.
-//   warp 0      TMA: Q (two buffers, one item ahead), dO; per key block K_j, V_j (K-major) and K_j again as an MN-major
-//               B operand (two buffers)
+//   warp 0      TMA: Q, dO; per key block K_j, V_j (K-major) and K_j again as an MN-major B operand (two buffers)
 //   warp 1      MMA, in this order on the tensor pipe: ... dP_j, S_{j+1}, dQ_j, dP_{j+1}, S_{j+2}, dQ_{j+1} ...
 //               S_{j+1} = Q.K_{j+1}^T is issued BEFORE the issuer waits for dS_j, so the exponentials of block j+1 run
 //               under dQ_j += dS_j.K_j; dP_{j+1} = dO.V_{j+1}^T follows dQ_j because it overwrites dS_j (the pipe
@@ -753,7 +752,8 @@ namespace {
 //   warps 2..9  thread = query row and two of the four 32-column chunks.  Phase A (needs S only): P = 2^(S k2 - L) into
 //               registers.  Phase B (needs dP): dS = round_tf32(scale P (dP - D)) over dP in tensor memory.
 // The running counters g (key blocks) and it (items) drive every barrier phase, so all three roles run on across item
-// boundaries; the dQ tile of a finished item is read between phase A and phase B of the next item's first block.
+// boundaries; the dQ tile of a finished item is read after the next item's first dS has been published, and the issuer
+// holds that item's first dQ product back until every warp has read (C_DQREAD).
 //   warp 10     stores: the dQ tile of a finished item goes from tensor memory through a swizzled shared-memory tile
 //               to global memory with one tile store (accumulate form: a tile reduction).  Written row by row from the
 //               registers (thread = row) the tile cost every warp 8 instructions x 32 separate lines, about 3000 cycles
