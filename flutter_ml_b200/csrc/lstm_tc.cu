@@ -241,6 +241,7 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmH, const __grid
 // for the partner, and adds the partner's 16 through distributed shared memory.  Twice the CTAs (8H / 32, 128 of 148 SMs
 // at H = 512), half the bytes, instructions and gate arithmetic per CTA.
 constexpr int PART_LD = 20;   // floats per row of the parked half (16 + padding: rows 80 bytes apart spread over the banks)
+constexpr int LP_THREADS = 320;   // paired kernel: producer warp, issuer warp, 8 gate warps
 enum { P_WFULL = 0, P_ACCFULL = 1, P_ACCEMPTY = 2, P_STEPDONE = 3, P_PARTREADY = 4, P_FULL = 5, P_EMPTY = 5 + MAX_RING, P_COUNT = 5 + 2 * MAX_RING };
 
 __device__ __forceinline__ bool mbar_wait_cluster_acq(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
@@ -272,7 +273,7 @@ __device__ __forceinline__ float4 ld_peer_f4(uint32_t local_addr, uint32_t cta) 
   return v;
 }
 
-__global__ void __launch_bounds__(LT_THREADS, 1)
+__global__ void __launch_bounds__(LP_THREADS, 1)
 lstm_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant__ CUtensorMap tmW, const LstmPParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -291,7 +292,7 @@ lstm_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
   const int kb0 = (int)rank * kb_half;          // first k-block of this CTA's half
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < P_COUNT; i++) mbar_init(bar(i), (i == P_ACCEMPTY || i == P_STEPDONE || i == P_PARTREADY) ? 4u : 1u);   // warps
+    for (int i = 0; i < P_COUNT; i++) mbar_init(bar(i), (i == P_ACCEMPTY || i == P_STEPDONE || i == P_PARTREADY) ? 8u : 1u);   // gate warps
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -373,24 +374,27 @@ lstm_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
       }
     }
   } else {
-    // ------------------------------------------------------------------ gate warps: thread = batch row, 4 hidden units
+    // ------------------------------------------------------------------ gate warps: thread = batch row and 2 of the CTA's 4
+    // hidden units (two warps per TMEM lane quarter: the gate functions are chains of dependent special-function
+    // instructions, bound by latency, so more warps shorten the phase where fewer units per thread alone did not)
     const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;         // which two of the four units, and which 8 of the 16 parked columns
     const int row = q4 * 32 + lane;
     const bool active = row < p.B;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
     const int N = 4 * p.H;
-    const int c0 = (int)rank * 16;            // the 16 gate columns (of the pair's 32) this CTA finalises
-    const int u0 = (n0 + c0) >> 2;            // their first hidden unit
+    const int c0 = (int)rank * 16 + half * 8;  // the 8 gate columns (of the pair's 32) this thread finalises
+    const int u0 = (n0 + c0) >> 2;             // their first hidden unit
     float* part = reinterpret_cast<float*>(smem_gen + off_part);
-    const uint32_t part_addr = smem_base + off_part + (uint32_t)row * PART_LD * 4u;
-    float c[4] = {0.f, 0.f, 0.f, 0.f};        // c_0 = 0 (lstmLayer.dart:115)
+    const uint32_t part_addr = smem_base + off_part + ((uint32_t)row * PART_LD + (uint32_t)half * 8u) * 4u;
+    float c[2] = {0.f, 0.f};                   // c_0 = 0 (lstmLayer.dart:115)
     bool ok = true;
     uint32_t v[32];
     for (int t = 0; t < p.T && ok; t++) {
-      float4 xa[4];
+      float4 xa[2];
       const long long po = ((long long)t * p.B + row) * N + n0 + c0;
 #pragma unroll
-      for (int i = 0; i < 4; i++) xa[i] = active ? __ldg(reinterpret_cast<const float4*>(p.xproj + po) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int i = 0; i < 2; i++) xa[i] = active ? __ldg(reinterpret_cast<const float4*>(p.xproj + po) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
       ok = mbar_wait_warp(bar(P_ACCFULL), (uint32_t)t & 1u, abort_flag, p.status, 57);
       if (!ok) break;
       if (threadIdx.x == 64) LT_STAMP(5);
@@ -399,41 +403,41 @@ lstm_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive_warp(bar(P_ACCEMPTY));
-      // park the partner's 16 columns of this CTA's partial sums, tell the partner, wait for the partner's half
-      // (static register indices with selects: an index that depends on the rank would put the array in local memory)
-      float own[16];
+      // park 8 of the partner's 16 columns of this CTA's partial sums, tell the partner, wait for the partner's half
+      // (static register indices with selects: an index that depends on rank or warp would put the array in local memory)
+      float own[8];
       {
-        float* dst = part + row * PART_LD;
+        float* dst = part + row * PART_LD + half * 8;
 #pragma unroll
-        for (int i = 0; i < 16; i += 4) {
+        for (int i = 0; i < 8; i += 4) {
           float4 o;
-          o.x = __uint_as_float(rank ? v[i] : v[16 + i]);
-          o.y = __uint_as_float(rank ? v[i + 1] : v[16 + i + 1]);
-          o.z = __uint_as_float(rank ? v[i + 2] : v[16 + i + 2]);
-          o.w = __uint_as_float(rank ? v[i + 3] : v[16 + i + 3]);
+          o.x = __uint_as_float(rank ? (half ? v[8 + i] : v[i]) : (half ? v[24 + i] : v[16 + i]));
+          o.y = __uint_as_float(rank ? (half ? v[8 + i + 1] : v[i + 1]) : (half ? v[24 + i + 1] : v[16 + i + 1]));
+          o.z = __uint_as_float(rank ? (half ? v[8 + i + 2] : v[i + 2]) : (half ? v[24 + i + 2] : v[16 + i + 2]));
+          o.w = __uint_as_float(rank ? (half ? v[8 + i + 3] : v[i + 3]) : (half ? v[24 + i + 3] : v[16 + i + 3]));
           *reinterpret_cast<float4*>(dst + i) = o;
         }
 #pragma unroll
-        for (int i = 0; i < 16; i++) own[i] = __uint_as_float(rank ? v[16 + i] : v[i]);
+        for (int i = 0; i < 8; i++) own[i] = __uint_as_float(rank ? (half ? v[24 + i] : v[16 + i]) : (half ? v[8 + i] : v[i]));
       }
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(bar(P_PARTREADY), peer);
       ok = __all_sync(0xffffffffu, mbar_wait_cluster_acq(bar(P_PARTREADY), (uint32_t)t & 1u, abort_flag, p.status, 58)) != 0;
       if (!ok) break;
       if (threadIdx.x == 64) LT_STAMP(6);
-      float z[16];
+      float z[8];
 #pragma unroll
-      for (int i = 0; i < 16; i += 4) {
+      for (int i = 0; i < 8; i += 4) {
         const float4 o = ld_peer_f4(part_addr + i * 4, peer);
         z[i] = own[i] + o.x;
         z[i + 1] = own[i + 1] + o.y;
         z[i + 2] = own[i + 2] + o.z;
         z[i + 3] = own[i + 3] + o.w;
       }
-      float hn[4];
-      float4 gt[4];
+      float hn[2];
+      float4 gt[2];
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
+      for (int i = 0; i < 2; i++) {
         const float zf = z[4 * i] + xa[i].x, zi = z[4 * i + 1] + xa[i].y, zg = z[4 * i + 2] + xa[i].z, zo = z[4 * i + 3] + xa[i].w;
         float f, ig, g, o;
         if (p.fast_math) {
@@ -447,15 +451,15 @@ lstm_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
       }
       if (threadIdx.x == 64) LT_STAMP(7);
       const long long ho = ((long long)(t + 1) * p.B + row) * p.H + u0;
-      if (active) *reinterpret_cast<float4*>(p.hs + ho) = make_float4(hn[0], hn[1], hn[2], hn[3]);
+      if (active) *reinterpret_cast<float2*>(p.hs + ho) = make_float2(hn[0], hn[1]);
       __threadfence();
       asm volatile("fence.proxy.async.global;" ::: "memory");
       mbar_arrive_warp(bar(P_STEPDONE));
       if (threadIdx.x == 64) LT_STAMP(8);
       if (active) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) reinterpret_cast<float4*>(p.gates + po)[i] = gt[i];
-        *reinterpret_cast<float4*>(p.cells + ho) = make_float4(c[0], c[1], c[2], c[3]);
+        for (int i = 0; i < 2; i++) reinterpret_cast<float4*>(p.gates + po)[i] = gt[i];
+        *reinterpret_cast<float2*>(p.cells + ho) = make_float2(c[0], c[1]);
       }
     }
   }
@@ -531,7 +535,7 @@ int32_t fml_lstm_fwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const floa
       attr[1].id = cudaLaunchAttributeCooperative;
       attr[1].val.cooperative = 1;
       cfg.gridDim = dim3(2 * n_cta);
-      cfg.blockDim = dim3(LT_THREADS);
+      cfg.blockDim = dim3(LP_THREADS);
       cfg.dynamicSmemBytes = smem2;
       cfg.stream = ctx->stream;
       cfg.attrs = attr;
