@@ -102,8 +102,9 @@ lstm_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tmH, const __grid
           ok = mbar_wait(bar(L_STEPDONE), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 51);
           if (!ok) break;
           LT_STAMP(0);
-          __threadfence();
-          atomicAdd(p.gbar, 1u);
+          // one release-add without a return value: the gate warps' stores of h_t (each behind its own fence, observed by this
+          // thread through the mbarrier) are ordered before it, and nothing waits for the counter's old value
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.gbar) : "memory");
           const unsigned int target = (unsigned int)t * gridDim.x;
           const unsigned long long t0 = globaltimer_ns();
           while (ld_acquire_gpu(p.gbar) < target) {
@@ -319,8 +320,9 @@ lstm_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
           ok = mbar_wait(bar(P_STEPDONE), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 51);
           if (!ok) break;
           LT_STAMP(0);
-          __threadfence();
-          atomicAdd(p.gbar, 1u);
+          // one release-add without a return value: the gate warps' stores of h_t (each behind its own fence, observed by this
+          // thread through the mbarrier) are ordered before it, and nothing waits for the counter's old value
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.gbar) : "memory");
           const unsigned int target = (unsigned int)t * gridDim.x;
           const unsigned long long t0 = globaltimer_ns();
           while (ld_acquire_gpu(p.gbar) < target) {
