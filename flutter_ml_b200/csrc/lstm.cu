@@ -66,22 +66,37 @@ __global__ void lstm_gates_fwd_kernel(const float* __restrict__ pre, const float
 __global__ void lstm_gates_bwd_kernel(float* __restrict__ dh, float* dc, const float* __restrict__ gates,
                                       const float* __restrict__ c_prev, const float* __restrict__ c_cur,
                                       float* __restrict__ dpre, int B, int H) {
-  // the recurrent product queued behind this kernel may set up (barriers, TMEM) while this one runs, and this
-  // kernel itself is launched while the previous product drains: it waits here for that product's dh
+  // The recurrent product queued behind this kernel may set up (barriers, TMEM) while this one runs, and this kernel
+  // itself is launched while the previous product drains.  What does not depend on that product (the saved gates and
+  // cells of this step, a DRAM round trip) is loaded BEFORE the wait for it; only dh and dc are read after.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int n = B * H;
-  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += gridDim.x * blockDim.x) {
-    const float4 gt = reinterpret_cast<const float4*>(gates)[idx];
+  const int stride = gridDim.x * blockDim.x;
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  float4 gt = make_float4(0.f, 0.f, 0.f, 0.f);
+  float cc = 0.f, cp = 0.f;
+  if (idx < n) {
+    gt = __ldg(reinterpret_cast<const float4*>(gates) + idx);
+    cc = __ldg(c_cur + idx);
+    cp = __ldg(c_prev + idx);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (; idx < n; idx += stride) {
     const float f = gt.x, i = gt.y, g = gt.z, o = gt.w;
-    const float tc = fml_tanh_ref(c_cur[idx]);
+    const float tc = fml_tanh_ref(cc);
     const float dhv = dh[idx];
     dh[idx] = 0.f;  // the product that follows ADDS dpre_t . Wh into dh (its K-split partial sums need a zeroed target)
     const float d_o = dhv * tc;
     const float dct = dc[idx] + dhv * o * (1.f - tc * tc);
-    reinterpret_cast<float4*>(dpre)[idx] = make_float4(dct * c_prev[idx] * (f * (1.f - f)), dct * g * (i * (1.f - i)),
-                                                       dct * i * (1.f - g * g), d_o * (o * (1.f - o)));
+    reinterpret_cast<float4*>(dpre)[idx] = make_float4(dct * cp * (f * (1.f - f)), dct * g * (i * (1.f - i)), dct * i * (1.f - g * g),
+                                                       d_o * (o * (1.f - o)));
     dc[idx] = dct * f;
+    const int nx = idx + stride;   // grids smaller than B*H (very large batches): the next element's inputs
+    if (nx < n) {
+      gt = __ldg(reinterpret_cast<const float4*>(gates) + nx);
+      cc = __ldg(c_cur + nx);
+      cp = __ldg(c_prev + nx);
+    }
   }
 }
 
