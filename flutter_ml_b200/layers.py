@@ -357,6 +357,97 @@ class DualLSTMLayer(MultiTierLSTMLayer):
         return step > 0 and (step + 1) % self.lowerTierClockCycle == 0
 
 
+class ConvLSTMLayer(Layer):
+    """ConvLSTMLayer (lib/layertypes/convlstmLayer.dart:37-159): an LSTM whose gates are single-channel convolutions with
+    'same' padding over the frame and over the hidden map, one bias MATRIX per gate (:83-96); hidden and cell states are
+    [H x W] maps, the output is the last hidden map (:157).  `hiddenFilters` is accepted and, as in the reference, unused.
+
+    Input: one sequence of frames [T x H x W] or a time-major batch [T x B x H x W]; output [H x W] or [B x H x W].  The four
+    input kernels are the rows of one [4 x k^2] tensor, likewise the four hidden kernels, the four bias matrices one
+    [4 x H*W] buffer; `parameters` hands out the reference's twelve tensors in its order (K_xf, K_hf, b_f, K_xi, ... :51-56)
+    as views.  A step is two launches of the batched convolution (all four gates of a frame at once: their output
+    [B x 4 x H*W] IS the gate-blocked pre-activation layout), the bias, and fml_lstm_cell_fwd with one "hidden unit" per
+    pixel; backward fml_lstm_cell_bwd and the convolution's backward, which adds into the kernel gradients.  Initial kernels
+    U(+-sqrt(1/k^2)) (:66-76) from the seeded generator unless given."""
+    name = "conv_lstm"
+
+    def __init__(self, hiddenFilters: int, kernelSize: int, seed: int = 0, kernels_x=None, kernels_h=None, biases=None):
+        super().__init__()
+        if kernelSize % 2 == 0:
+            raise ValueError("'same' padding needs an odd kernel size")
+        self.hiddenFilters, self.kernelSize, self.seed = hiddenFilters, kernelSize, seed
+        self._kx0, self._kh0, self._b0 = kernels_x, kernels_h, biases
+
+    @property
+    def parameters(self):
+        return self._params
+
+    def build(self, x: Tensor):
+        k2, ctx = self.kernelSize ** 2, x.ctx
+        Hh, Ww = x.shape[-2], x.shape[-1]
+        a = math.sqrt(1.0 / k2)
+        kx = self._kx0 if self._kx0 is not None else synth.uniform(self.seed, 20, (4, k2), -a, a)
+        kh = self._kh0 if self._kh0 is not None else synth.uniform(self.seed, 21, (4, k2), -a, a)
+        b = self._b0 if self._b0 is not None else np.zeros((4, Hh * Ww), dtype=np.float32)
+        self.Kx = ctx.upload(np.asarray(kx, np.float32).reshape(4, k2))
+        self.Kh = ctx.upload(np.asarray(kh, np.float32).reshape(4, k2))
+        self.b = ctx.upload(np.asarray(b, np.float32).reshape(4 * Hh * Ww))
+        self.dKx, self.dKh, self.db = ctx.zeros(4, k2), ctx.zeros(4, k2), ctx.zeros(4 * Hh * Ww)
+        self._params = []
+        k = self.kernelSize
+        for g in range(4):
+            for buf, grad, off, shape in ((self.Kx, self.dKx, g * k2, (k, k)), (self.Kh, self.dKh, g * k2, (k, k)),
+                                          (self.b, self.db, g * Hh * Ww, (Hh, Ww))):
+                t = Tensor(buf.view(off, shape), ctx)
+                t.grad = grad.view(off, shape)
+                self._params.append(t)
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        ctx, k = x.ctx, self.kernelSize
+        single = len(x.shape) == 3
+        Tn, B, Hh, Ww = (x.shape[0], 1, x.shape[1], x.shape[2]) if single else x.shape
+        P, pad = Hh * Ww, (k - 1) // 2
+        cargs = (B, Hh, Ww, 4, k, k, pad)
+        zero = ctx.zeros(B, P)
+        h, c = zero, zero
+        records = []
+        for t in range(Tn):
+            x_t = x.value.view(t * B * P, (B, P))
+            pre, hc = ctx.empty(B, 4 * P), ctx.empty(B, 4 * P)
+            ctx.call("fml_conv2d_fwd", x_t, self.Kx, None, pre, *cargs)
+            if h is not zero:
+                ctx.call("fml_conv2d_fwd", h, self.Kh, None, hc, *cargs)
+                ctx.call("fml_axpy", 1.0, hc, pre, B * 4 * P)
+            ctx.call("fml_add_bias", pre, self.b, pre, B, 4 * P)
+            gates, c_new, h_new = ctx.empty(B, 4 * P), ctx.empty(B, P), ctx.empty(B, P)
+            ctx.call("fml_lstm_cell_fwd", pre, c, gates, c_new, h_new, B, P)
+            records.append((t, h, c, gates, c_new, h_new))
+            h, c = h_new, c_new
+        out = Tensor(h.view(0, (Hh, Ww) if single else (B, Hh, Ww)), ctx)
+        want_dx = x.creator is not None or x.grad is not None
+
+        def bw():
+            dh, dc = out.grad, None                   # gradients arriving at the states of the step being undone
+            dx = ctx.zeros(*x.shape) if want_dx else None
+            for t, h_prev, c_prev, gates, c_new, h_new in reversed(records):
+                dpre, dc_prev = ctx.empty(B, 4 * P), ctx.empty(B, P)
+                ctx.call("fml_lstm_cell_bwd", gates, c_prev, c_new, dh, dc, dpre, dc_prev, 0, B, P)
+                ctx.call("fml_col_sum", dpre, self.db, B, 4 * P, 1)
+                x_t = x.value.view(t * B * P, (B, P))
+                ctx.call("fml_conv2d_bwd", x_t, self.Kx, dpre, dx.view(t * B * P, (B, P)) if dx is not None else None, self.dKx, None,
+                         *cargs, launches=2)
+                if h_prev is zero:
+                    break                             # the first step: no hidden map before it
+                dh_prev = ctx.zeros(B, P)
+                ctx.call("fml_conv2d_bwd", h_prev, self.Kh, dpre, dh_prev, self.dKh, None, *cargs, launches=2)
+                dh, dc = dh_prev, dc_prev
+            if dx is not None:
+                x._add_grad(dx, alias=True)
+        out.creator = T.Node([x] + self._params, bw, self.name, cost=2 * Tn * B * 8 * P * k * k)
+        return out
+
+
 class LayerNormalization(Layer):
     """lib/transformer/layerNormalization.dart:11-44: gamma = 1, beta = 0, epsilon = 1e-5."""
 

@@ -581,3 +581,35 @@ def tiered_lstm_fwd_bwd(x, Ws, bs, cycles, target, dual=False, omp=False):
     dWs = [np.concatenate([w.grad for w in W], axis=0) for W in Wt]
     dbs = [np.concatenate([v.grad for v in b]) for b in bt]
     return out.value.copy(), float(loss.value), dWs, dbs, np.stack([v.grad for v in xs])
+
+
+def conv_lstm_fwd_bwd(x, Kx, Kh, bias, target, omp=False):
+    """ConvLSTMLayer.forward (lib/layertypes/convlstmLayer.dart:107-159) for ONE sequence of frames x [T x H x W], composed
+    from the tape's operations the way the reference composes them (conv2d with 'same' padding tensor.dart:765-833,
+    addMatrix :651-677, sigmoidMatrix :1123-1151, tanhMatrix :1178-1209, elementWiseMultiplyMatrix :835-865), then
+    mseMatrix against `target` [H x W] (:982-1011) and the tape's backward sweep.  Kx, Kh are [4 x k x k] (the input and
+    hidden kernels of the gates f, i, c~, o), bias is [4 x H x W] (one bias MATRIX per gate, :83-96).  Returns the last
+    hidden map, the loss, dKx, dKh, dbias and dx."""
+    e = Engine(omp)
+    kx = [T(k) for k in np.asarray(Kx, dtype=np.float64)]
+    kh = [T(k) for k in np.asarray(Kh, dtype=np.float64)]
+    bs = [T(b) for b in np.asarray(bias, dtype=np.float64)]
+    xs = [T(f) for f in np.asarray(x, dtype=np.float64)]
+    H, W = xs[0].value.shape
+    h, c = T(np.zeros((H, W))), T(np.zeros((H, W)))
+
+    def gate(g, x_t, act):
+        z = e.addMatrix(e.addMatrix(e.conv2d(x_t, kx[g], "same"), e.conv2d(h, kh[g], "same")), bs[g])
+        return e._unary(act, z, True)
+
+    for x_t in xs:
+        f = gate(0, x_t, "sigmoid")
+        i = gate(1, x_t, "sigmoid")
+        g = gate(2, x_t, "tanh")
+        c = e.addMatrix(e.elementWiseMultiply(f, c), e.elementWiseMultiply(i, g))
+        o = gate(3, x_t, "sigmoid")
+        h = e.elementWiseMultiply(o, e._unary("tanh", c, True))
+    loss = e.mseMatrix(h, T(target))
+    loss.backward()
+    return (h.value.copy(), float(loss.value), np.stack([k.grad for k in kx]), np.stack([k.grad for k in kh]),
+            np.stack([b.grad for b in bs]), np.stack([v.grad for v in xs]))

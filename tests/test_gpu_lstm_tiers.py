@@ -118,3 +118,49 @@ def test_snetwork_with_a_dual_lstm_layer_trains():
     assert hist[-1] < 0.5 * hist[0]
     assert ctx.device_status() == 0
     ctx.close()
+
+
+@pytest.mark.parametrize("B,Tn,H,W,k", [(1, 4, 7, 7, 3), (3, 5, 9, 6, 3), (2, 3, 8, 8, 5)])
+def test_conv_lstm_layer(orc, B, Tn, H, W, k):
+    """layers.ConvLSTMLayer (lib/layertypes/convlstmLayer.dart:37-159): last hidden map, loss, the twelve parameter
+    gradients in the reference's order and the input gradient against the oracle, sequence by sequence."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200 import tensor as T
+    from flutter_ml_b200.layers import ConvLSTMLayer
+    from flutter_ml_b200.tensor import Tensor
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    rng = np.random.default_rng(10 * B + Tn + k)
+    Kx = (rng.uniform(-1, 1, (4, k, k)) / k).astype(np.float32)
+    Kh = (rng.uniform(-1, 1, (4, k, k)) / k).astype(np.float32)
+    bias = rng.uniform(-0.1, 0.1, (4, H, W)).astype(np.float32)
+    x = rng.standard_normal((Tn, B, H, W)).astype(np.float32)
+    target = rng.standard_normal((B, H, W)).astype(np.float32)
+    layer = ConvLSTMLayer(8, k, kernels_x=Kx, kernels_h=Kh, biases=bias)
+    xin = Tensor(x[:, 0] if B == 1 else x, ctx)
+    xin.zeroGrad()
+    out = layer(xin)
+    assert out.shape == ((H, W) if B == 1 else (B, H, W)) and len(layer.parameters) == 12
+    loss = T.mseMatrix(out, Tensor(target[0] if B == 1 else target, ctx), weight=float(B))   # = sum over sequences of mseMatrix
+    loss.backward()
+    h_ref, loss_ref = np.zeros((B, H, W)), 0.0
+    dKx_ref, dKh_ref, db_ref, dx_ref = np.zeros((4, k, k)), np.zeros((4, k, k)), np.zeros((4, H, W)), np.zeros((Tn, B, H, W))
+    for b in range(B):
+        h_b, l_b, a, c_, d_, e_ = orc.conv_lstm_fwd_bwd(w64(x[:, b]), w64(Kx), w64(Kh), w64(bias), w64(target[b]))
+        h_ref[b], loss_ref = h_b, loss_ref + l_b
+        dKx_ref += a
+        dKh_ref += c_
+        db_ref += d_
+        dx_ref[:, b] = e_
+    P = layer.parameters
+    for g in range(4):
+        assert np.array_equal(P[3 * g].numpy(), Kx[g]) and np.array_equal(P[3 * g + 1].numpy(), Kh[g]) and np.array_equal(P[3 * g + 2].numpy(), bias[g])
+    errs = {"h": rel(out.numpy().reshape(B, H, W), h_ref), "dx": rel(xin.grad_numpy().reshape(Tn, B, H, W), dx_ref),
+            "dKx": rel(np.stack([P[3 * g].grad_numpy() for g in range(4)]), dKx_ref),
+            "dKh": rel(np.stack([P[3 * g + 1].grad_numpy() for g in range(4)]), dKh_ref),
+            "db": rel(np.stack([P[3 * g + 2].grad_numpy() for g in range(4)]), db_ref)}
+    print(f"PARITY conv-lstm B{B} T{Tn} {H}x{W} k{k}: " + " ".join(f"{n} {v:.1e}" for n, v in errs.items()))
+    assert abs(loss.numpy()[0] - loss_ref) <= 1e-5 * abs(loss_ref)
+    for n, v in errs.items():
+        assert v <= 1e-5, (n, v)
+    assert ctx.device_status() == 0
+    ctx.close()

@@ -77,3 +77,26 @@ def test_a_single_tier_is_the_plain_lstm(orc):
     assert np.allclose(h, h_ref[0], rtol=1e-12, atol=1e-14) and abs(loss - loss_ref) <= 1e-12 * abs(loss_ref)
     assert np.allclose(dWs[0].reshape(4, H, H + I), dW_ref, rtol=1e-10, atol=1e-14)
     assert np.allclose(dbs[0].reshape(4, H), db_ref, rtol=1e-10, atol=1e-14)
+
+
+def test_conv_lstm_gradients_match_central_differences(orc):
+    """The oracle's ConvLSTM (lib/layertypes/convlstmLayer.dart:107-159, composed from its conv2d / addMatrix / sigmoidMatrix /
+    tanhMatrix / elementWiseMultiplyMatrix): analytic gradients against central differences of its own loss."""
+    rng = np.random.default_rng(1)
+    Tn, H, W, k = 4, 5, 6, 3
+    Kx, Kh = rng.standard_normal((4, k, k)) * 0.4, rng.standard_normal((4, k, k)) * 0.4
+    b, x, tgt = rng.standard_normal((4, H, W)) * 0.1, rng.standard_normal((Tn, H, W)), rng.standard_normal((H, W))
+    h, loss, dKx, dKh, db, dx = orc.conv_lstm_fwd_bwd(x, Kx, Kh, b, tgt)
+    assert h.shape == (H, W) and np.isfinite(loss)
+    arrs, grads = {"Kx": Kx, "Kh": Kh, "b": b, "x": x}, {"Kx": dKx, "Kh": dKh, "b": db, "x": dx}
+    eps = 1e-6
+    for name, arr in arrs.items():
+        for _ in range(5):
+            pos = tuple(int(rng.integers(n)) for n in arr.shape)
+            vals = []
+            for sgn in (+1, -1):
+                a2 = {k_: v.copy() for k_, v in arrs.items()}
+                a2[name][pos] += sgn * eps
+                vals.append(orc.conv_lstm_fwd_bwd(a2["x"], a2["Kx"], a2["Kh"], a2["b"], tgt)[1])
+            num = (vals[0] - vals[1]) / (2 * eps)
+            assert abs(grads[name][pos] - num) <= 1e-7 + 1e-5 * abs(num), (name, pos)
