@@ -448,6 +448,171 @@ class ConvLSTMLayer(Layer):
         return out
 
 
+class GeneralizedChainedScaleLayer(Layer):
+    """GeneralizedChainedScaleLayer (lib/layertypes/trendmodelLayer.dart:42-218): a chain of LSTMs over coarser and coarser
+    summaries of the past.  Level i + 1 of the data is tanh(aggW_i . [grain_i consecutive rows of level i, flattened] +
+    aggB_i) for every complete chunk (:146-158); the LSTM of the highest level runs first over (at most) its last 10
+    summaries, its final hidden state initialises the hidden state of the LSTM one level down (cell state zero again),
+    and so on down to level 0, which reads the last `finalSequenceLength` raw rows (:163-178).  Output: the last hidden
+    state of level 0.
+
+    Input: one sequence [T x I] or a batch-major batch [B x T x I] (consecutive rows of a sequence are contiguous, so a
+    chunk is one row of a [chunks x grain*I] view and every aggregation level is one product with the tanh in its
+    epilogue per sequence); output [H] / [B x H].  Every LSTM step is the input's share (one product per tier and sequence
+    for all its steps, bias in the epilogue) plus h . Wh^T accumulated into it, then fml_lstm_cell_fwd on the whole batch.
+    `parameters` in the reference's order (:70-84): per tier W_f, b_f, W_i, b_i, W_c, b_c, W_o, b_o (views of one
+    [4H x (H+I)] / [4H] buffer, columns [h | x] as in `concatenate(h, x_t)` :193), then aggW_i, aggB_i per level."""
+    name = "generalized_chained_scale"
+    HIGHER_TIER_LOOKBACK = 10      # trendmodelLayer.dart:168
+
+    def __init__(self, hiddenSize: int, grainingSizes, finalSequenceLength: int = 7, seed: int = 0, lstm_weights=None, lstm_biases=None,
+                 agg_weights=None, agg_biases=None):
+        super().__init__()
+        self.hiddenSize, self.grainingSizes, self.finalSequenceLength = hiddenSize, list(grainingSizes), finalSequenceLength
+        self.numTiers = len(self.grainingSizes) + 1
+        self.seed, self._w0, self._b0, self._aw0, self._ab0 = seed, lstm_weights, lstm_biases, agg_weights, agg_biases
+
+    @property
+    def parameters(self):
+        return self._params
+
+    def build(self, x: Tensor):
+        H, I, ctx = self.hiddenSize, x.shape[-1], x.ctx
+        Z = H + I
+        self.W, self.b, self.dW, self.db, self.aW, self.ab, self.daW, self.dab = [], [], [], [], [], [], [], []
+        self._params = []
+        a = math.sqrt(1.0 / Z)
+        for i in range(self.numTiers):
+            w = self._w0[i] if self._w0 is not None else synth.uniform(self.seed, 30 + i, (4 * H, Z), -a, a)
+            b = self._b0[i] if self._b0 is not None else np.zeros(4 * H, dtype=np.float32)
+            self.W.append(ctx.upload(np.ascontiguousarray(w, np.float32).reshape(4 * H, Z)))
+            self.b.append(ctx.upload(np.asarray(b, np.float32)))
+            self.dW.append(ctx.zeros(4 * H, Z))
+            self.db.append(ctx.zeros(4 * H))
+            for g in range(4):
+                for buf, grad, off, shape in ((self.W[i], self.dW[i], g * H * Z, (H, Z)), (self.b[i], self.db[i], g * H, (H,))):
+                    t = Tensor(buf.view(off, shape), ctx)
+                    t.grad = grad.view(off, shape)
+                    self._params.append(t)
+        for i, grain in enumerate(self.grainingSizes):
+            fan = grain * I
+            aa = math.sqrt(1.0 / fan)
+            w = self._aw0[i] if self._aw0 is not None else synth.uniform(self.seed, 40 + i, (I, fan), -aa, aa)
+            b = self._ab0[i] if self._ab0 is not None else np.zeros(I, dtype=np.float32)
+            wt, bt = Tensor(np.ascontiguousarray(w, np.float32).reshape(I, fan), ctx), Tensor(np.asarray(b, np.float32), ctx)
+            wt.zeroGrad()
+            bt.zeroGrad()
+            self.aW.append(wt)
+            self.ab.append(bt)
+            self._params += [wt, bt]
+        super().build(x)
+
+    def forward(self, x: Tensor) -> Tensor:
+        ctx, H, n = x.ctx, self.hiddenSize, self.numTiers
+        single = len(x.shape) == 2
+        B, T0, I = (1,) + tuple(x.shape) if single else x.shape
+        Z = H + I
+        if T0 < self.finalSequenceLength:
+            raise ValueError("the sequence is shorter than finalSequenceLength")
+        # ---- aggregation: level i + 1 from level i, every sequence one product with the tanh in its epilogue
+        data, lens = [x.value], [T0]
+        for i, grain in enumerate(self.grainingSizes):
+            cnt = lens[i] // grain                    # complete chunks only (trendmodelLayer.dart:150)
+            S = ctx.empty(B, max(cnt, 1), I)
+            for bq in range(B if cnt else 0):
+                ctx.gemm(data[i].view(bq * lens[i] * I, (cnt, grain * I)), self.aW[i].value, S.view(bq * cnt * I, (cnt, I)), cnt, I, grain * I,
+                         transB=True, bias=self.ab[i].value, act="tanh")
+            data.append(S)
+            lens.append(cnt)
+        # ---- the chain of LSTMs, highest level first
+        zero = ctx.zeros(B, H)
+        context = zero
+        tiers = []                                    # per tier, in the order run: (i, L, first row, xproj, [(h_prev, c_prev, gates, c_new, h_new)])
+        for i in range(n - 1, -1, -1):
+            look = self.finalSequenceLength if i == 0 else self.HIGHER_TIER_LOOKBACK
+            L = min(lens[i], look)
+            first = lens[i] - L
+            if L == 0:
+                tiers.append((i, 0, 0, None, []))
+                continue
+            xproj = ctx.empty(L, B, 4 * H)            # the input's share of every step's pre-activations, bias included
+            for bq in range(B):
+                ctx.gemm(data[i].view((bq * lens[i] + first) * I, (L, I)), self.W[i].view(H, (4 * H, I)), xproj.view(bq * 4 * H, (L, 4 * H)),
+                         L, 4 * H, I, transB=True, ldb=Z, ldc=B * 4 * H, bias=self.b[i])
+            h, c, steps = context, zero, []
+            for l in range(L):
+                pre = xproj.view(l * B * 4 * H, (B, 4 * H))
+                if h is not zero:
+                    ctx.gemm(h, self.W[i].view(0, (4 * H, H)), pre, B, 4 * H, H, transB=True, ldb=Z, beta=1.0)
+                gates, c_new, h_new = ctx.empty(B, 4 * H), ctx.empty(B, H), ctx.empty(B, H)
+                ctx.call("fml_lstm_cell_fwd", pre, c, gates, c_new, h_new, B, H)
+                steps.append((h, c, gates, c_new, h_new))
+                h, c = h_new, c_new
+            tiers.append((i, L, first, xproj, steps))
+            context = h
+        out = Tensor(context.view(0, (H,)) if single else context, ctx)
+        want_dx = x.creator is not None or x.grad is not None
+
+        def bw():
+            ddata = [None] * n                        # gradient of every level of the data, allocated when first needed
+
+            def grad_level(i):
+                if ddata[i] is None:
+                    ddata[i] = ctx.zeros(B, max(lens[i], 1), I)
+                return ddata[i]
+            dctx = out.grad                           # gradient of the context handed down the chain
+            for i, L, first, xproj, steps in reversed(tiers):      # level 0 ran last
+                if L == 0 or dctx is None:
+                    continue
+                dpre_all = ctx.empty(L, B, 4 * H)
+                dh, dc = dctx, None
+                for l in range(L - 1, -1, -1):
+                    h_prev, c_prev, gates, c_new, h_new = steps[l]
+                    dpre, dc_prev = dpre_all.view(l * B * 4 * H, (B, 4 * H)), ctx.empty(B, H)
+                    ctx.call("fml_lstm_cell_bwd", gates, c_prev, c_new, dh, dc, dpre, dc_prev, 0, B, H)
+                    if h_prev is zero:
+                        dh = None                     # the chain started from the zero context: nothing above to receive it
+                    else:
+                        ctx.gemm(dpre, h_prev, self.dW[i].view(0, (4 * H, H)), 4 * H, H, B, transA=True, ldc=Z, beta=1.0)
+                        dh_prev = ctx.empty(B, H)
+                        ctx.gemm(dpre, self.W[i].view(0, (4 * H, H)), dh_prev, B, H, 4 * H, ldb=Z)
+                        dh = dh_prev
+                    dc = dc_prev if l > 0 else None
+                dctx = dh                             # gradient of this tier's initial hidden state = the tier above's output
+                ctx.call("fml_col_sum", dpre_all, self.db[i], L * B, 4 * H, 1)
+                need_rows = i > 0 or want_dx
+                for bq in range(B):
+                    rows = data[i].view((bq * lens[i] + first) * I, (L, I))
+                    ctx.gemm(dpre_all.view(bq * 4 * H, (L, 4 * H)), rows, self.dW[i].view(H, (4 * H, I)), 4 * H, I, L, transA=True,
+                             lda=B * 4 * H, ldc=Z, beta=1.0)
+                    if need_rows:
+                        ctx.gemm(dpre_all.view(bq * 4 * H, (L, 4 * H)), self.W[i].view(H, (4 * H, I)),
+                                 grad_level(i).view((bq * lens[i] + first) * I, (L, I)), L, I, 4 * H, lda=B * 4 * H, ldb=Z, beta=1.0)
+            # ---- aggregation levels, highest first: dS -> dZ = dS (1 - S^2), then into the weights and the level below
+            for i in range(len(self.grainingSizes) - 1, -1, -1):
+                cnt, grain = lens[i + 1], self.grainingSizes[i]
+                if cnt == 0 or ddata[i + 1] is None:
+                    continue
+                dZ = ctx.empty(B, cnt, I)
+                ctx.call("fml_act_bwd", _lib_act("tanh"), data[i + 1], ddata[i + 1], dZ, B * cnt, I, 0, self.ab[i].grad, launches=2)
+                need_rows = i > 0 or want_dx
+                for bq in range(B):
+                    chunks = data[i].view(bq * lens[i] * I, (cnt, grain * I))
+                    ctx.gemm(dZ.view(bq * cnt * I, (cnt, I)), chunks, self.aW[i].grad, I, grain * I, cnt, transA=True, beta=1.0)
+                    if need_rows:
+                        ctx.gemm(dZ.view(bq * cnt * I, (cnt, I)), self.aW[i].value, grad_level(i).view(bq * lens[i] * I, (cnt, grain * I)),
+                                 cnt, grain * I, I, beta=1.0)
+            if want_dx:
+                x._add_grad(grad_level(0).view(0, x.shape), alias=False)
+        out.creator = T.Node([x] + self._params, bw, self.name, cost=8 * sum(t[1] for t in tiers) * B * H * Z)
+        return out
+
+
+def _lib_act(name: str) -> int:
+    from . import _lib
+    return _lib.ACT_BY_NAME[name]
+
+
 class LayerNormalization(Layer):
     """lib/transformer/layerNormalization.dart:11-44: gamma = 1, beta = 0, epsilon = 1e-5."""
 

@@ -613,3 +613,52 @@ def conv_lstm_fwd_bwd(x, Kx, Kh, bias, target, omp=False):
     loss.backward()
     return (h.value.copy(), float(loss.value), np.stack([k.grad for k in kx]), np.stack([k.grad for k in kh]),
             np.stack([b.grad for b in bs]), np.stack([v.grad for v in xs]))
+
+
+def chained_scale_fwd_bwd(x, Ws, bs, aWs, abs_, grains, final_len, target, lookback=10, omp=False):
+    """GeneralizedChainedScaleLayer.forward (lib/layertypes/trendmodelLayer.dart:134-204) for ONE sequence x [T x I], composed
+    from the tape's vector operations as the reference composes them: every complete chunk of grain_i consecutive
+    vectors of level i is flattened (concatenate, tensor.dart:437-455) and summarised by vectorTanh(aggW_i . chunk +
+    aggB_i) (:146-158); then one LSTM loop per level from the highest down (:163-178, :181-204), each over at most
+    `lookback` (level 0: `final_len`) of its most recent inputs, its hidden state initialised with the level above's
+    result, its cell state with zeros; mse against `target`; the tape's backward sweep.  Ws[i] = [4H x (H + I)] (gates f, i,
+    c~, o stacked, columns [h | x]), bs[i] = [4H], aWs[i] = [I x grain_i * I], abs_[i] = [I].
+    Returns h, loss, dWs, dbs, daWs, dabs, dx."""
+    e = Engine(omp)
+    n = len(grains) + 1
+    H = Ws[0].shape[0] // 4
+    Wt = [[T(W[g * H:(g + 1) * H]) for g in range(4)] for W in Ws]
+    bt = [[T(b[g * H:(g + 1) * H]) for g in range(4)] for b in bs]
+    aWt, abt = [T(w) for w in aWs], [T(b) for b in abs_]
+    xs = [T(row) for row in np.asarray(x, dtype=np.float64)]
+    tier_inputs = [xs[len(xs) - final_len:]] + [[] for _ in range(n - 1)]
+    current = xs
+    for i, grain in enumerate(grains):
+        nxt = []
+        for j in range(0, len(current) - grain + 1, grain):
+            flat = current[j]
+            for v in current[j + 1:j + grain]:
+                flat = e.concatenate(flat, v)
+            nxt.append(e._unary("tanh", e.addMatrix(e.matVecMul(aWt[i], flat), abt[i]), True))
+        tier_inputs[i + 1] = nxt
+        current = nxt
+    context = T(np.zeros(H))
+    for i in range(n - 1, -1, -1):
+        seq = tier_inputs[i]
+        look = final_len if i == 0 else lookback
+        seq = seq[max(0, len(seq) - look):]
+        h, c = context, T(np.zeros(H))
+        W, b = Wt[i], bt[i]
+        for x_t in seq:
+            comb = e.concatenate(h, x_t)
+            f = e._unary("sigmoid", e.addMatrix(e.matVecMul(W[0], comb), b[0]), True)
+            ig = e._unary("sigmoid", e.addMatrix(e.matVecMul(W[1], comb), b[1]), True)
+            g = e._unary("tanh", e.addMatrix(e.matVecMul(W[2], comb), b[2]), True)
+            c = e.addMatrix(e.elementWiseMultiply(f, c), e.elementWiseMultiply(ig, g))
+            o = e._unary("sigmoid", e.addMatrix(e.matVecMul(W[3], comb), b[3]), True)
+            h = e.elementWiseMultiply(o, e._unary("tanh", c, True))
+        context = h
+    loss = e.mseMatrix(context, T(target))
+    loss.backward()
+    return (context.value.copy(), float(loss.value), [np.concatenate([w.grad for w in W], axis=0) for W in Wt],
+            [np.concatenate([v.grad for v in b]) for b in bt], [w.grad for w in aWt], [b.grad for b in abt], np.stack([v.grad for v in xs]))

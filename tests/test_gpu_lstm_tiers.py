@@ -164,3 +164,64 @@ def test_conv_lstm_layer(orc, B, Tn, H, W, k):
         assert v <= 1e-5, (n, v)
     assert ctx.device_status() == 0
     ctx.close()
+
+
+@pytest.mark.parametrize("grains,B,Tn,H,I,final_len,prec", [([7, 4], 1, 60, 16, 4, 7, 1), ([3, 2], 3, 31, 32, 8, 4, 1), ([4], 2, 9, 8, 4, 5, 2),
+                                                            ([2, 2, 2], 2, 40, 16, 4, 3, 2), ([3, 2], 4, 50, 32, 8, 6, 0)])
+def test_chained_scale_layer(orc, grains, B, Tn, H, I, final_len, prec):
+    """layers.GeneralizedChainedScaleLayer (lib/layertypes/trendmodelLayer.dart:42-218): last hidden state of level 0, loss,
+    every LSTM and aggregation parameter gradient (in the reference's order) and the input gradient against the oracle,
+    sequence by sequence."""
+    from flutter_ml_b200 import _lib
+    from flutter_ml_b200 import tensor as T
+    from flutter_ml_b200.layers import GeneralizedChainedScaleLayer
+    from flutter_ml_b200.tensor import Tensor
+    ctx = _lib.Context(precision=prec)
+    rng = np.random.default_rng(7 * B + Tn + H)
+    n = len(grains) + 1
+    Z = H + I
+    Ws = [(rng.uniform(-1, 1, (4 * H, Z)) * np.sqrt(1.0 / Z)).astype(np.float32) for _ in range(n)]
+    bs = [rng.uniform(-0.1, 0.1, 4 * H).astype(np.float32) for _ in range(n)]
+    aWs = [(rng.uniform(-1, 1, (I, g * I)) * np.sqrt(1.0 / (g * I))).astype(np.float32) for g in grains]
+    abs_ = [rng.uniform(-0.1, 0.1, I).astype(np.float32) for _ in grains]
+    x = rng.standard_normal((B, Tn, I)).astype(np.float32)
+    target = rng.standard_normal((B, H)).astype(np.float32)
+    layer = GeneralizedChainedScaleLayer(H, grains, final_len, lstm_weights=Ws, lstm_biases=bs, agg_weights=aWs, agg_biases=abs_)
+    xin = Tensor(x[0] if B == 1 else x, ctx)
+    xin.zeroGrad()
+    out = layer(xin)
+    assert out.shape == ((H,) if B == 1 else (B, H)) and len(layer.parameters) == 8 * n + 2 * len(grains)
+    loss = T.mseMatrix(out, Tensor(target[0] if B == 1 else target, ctx), weight=float(B))
+    loss.backward()
+    h_ref, loss_ref = np.zeros((B, H)), 0.0
+    dW_ref, db_ref = [np.zeros((4 * H, Z)) for _ in range(n)], [np.zeros(4 * H) for _ in range(n)]
+    daW_ref, dab_ref, dx_ref = [np.zeros_like(w64(w)) for w in aWs], [np.zeros(I) for _ in grains], np.zeros((B, Tn, I))
+    for b in range(B):
+        h_b, l_b, dWs, dbs, daWs, dabs, dx_b = orc.chained_scale_fwd_bwd(w64(x[b]), [w64(w) for w in Ws], [w64(v) for v in bs], [w64(w) for w in aWs],
+                                                                         [w64(v) for v in abs_], grains, final_len, w64(target[b]))
+        h_ref[b], loss_ref, dx_ref[b] = h_b, loss_ref + l_b, dx_b
+        for i in range(n):
+            dW_ref[i] += dWs[i]
+            db_ref[i] += dbs[i]
+        for i in range(len(grains)):
+            daW_ref[i] += daWs[i]
+            dab_ref[i] += dabs[i]
+    P = layer.parameters
+    errs = {"h": rel(out.numpy().reshape(B, H), h_ref), "dx": rel(xin.grad_numpy().reshape(B, Tn, I), dx_ref)}
+    for i in range(n):
+        errs[f"dW{i}"] = rel(np.concatenate([P[8 * i + 2 * g].grad_numpy() for g in range(4)]), dW_ref[i])
+        errs[f"db{i}"] = rel(np.concatenate([P[8 * i + 2 * g + 1].grad_numpy() for g in range(4)]), db_ref[i])
+    for i in range(len(grains)):
+        errs[f"daW{i}"] = rel(P[8 * n + 2 * i].grad_numpy(), daW_ref[i])
+        errs[f"dab{i}"] = rel(P[8 * n + 2 * i + 1].grad_numpy(), dab_ref[i])
+    print(f"PARITY chained-scale {grains} B{B} T{Tn} H{H} prec{prec}: " + " ".join(f"{k} {v:.1e}" for k, v in errs.items()))
+    # TF32: the gradient of the highest aggregation level has passed through three LSTM loops (up to 26 steps, two
+    # truncating products each) and two aggregation products; the operand truncation biases every product by the same
+    # sign, so the error grows with the depth of the chain (measured 5.6e-3 at the top, 9e-4 at the bottom).
+    t_out, t_grad = {0: (2e-3, 1e-2), 1: (1e-5, 2e-5), 2: (1e-5, 2e-5)}[prec]
+    assert errs["h"] <= t_out and abs(loss.numpy()[0] - loss_ref) <= 2 * t_out * abs(loss_ref)
+    for k, v in errs.items():
+        if k != "h":
+            assert v <= t_grad, (k, v)
+    assert ctx.device_status() == 0
+    ctx.close()

@@ -100,3 +100,48 @@ def test_conv_lstm_gradients_match_central_differences(orc):
                 vals.append(orc.conv_lstm_fwd_bwd(a2["x"], a2["Kx"], a2["Kh"], a2["b"], tgt)[1])
             num = (vals[0] - vals[1]) / (2 * eps)
             assert abs(grads[name][pos] - num) <= 1e-7 + 1e-5 * abs(num), (name, pos)
+
+
+@pytest.mark.parametrize("grains,Tn,final_len", [([3, 2], 31, 4), ([4], 9, 5), ([2, 2, 2], 40, 3)])
+def test_chained_scale_gradients_match_central_differences(orc, grains, Tn, final_len):
+    """The oracle's GeneralizedChainedScaleLayer (lib/layertypes/trendmodelLayer.dart:134-204): analytic gradients against
+    central differences of its own loss, for the LSTM weights of every tier, the aggregation weights of every level and
+    the input (old rows reach the loss only through the summaries)."""
+    rng = np.random.default_rng(len(grains) + Tn)
+    H, I = 3, 2
+    n = len(grains) + 1
+    Ws = [rng.standard_normal((4 * H, H + I)) * 0.5 for _ in range(n)]
+    bs = [rng.standard_normal(4 * H) * 0.1 for _ in range(n)]
+    aWs = [rng.standard_normal((I, g * I)) * 0.5 for g in grains]
+    abs_ = [rng.standard_normal(I) * 0.1 for _ in grains]
+    x, tgt = rng.standard_normal((Tn, I)), rng.standard_normal(H)
+    h, loss, dWs, dbs, daWs, dabs, dx = orc.chained_scale_fwd_bwd(x, Ws, bs, aWs, abs_, grains, final_len, tgt)
+    assert h.shape == (H,) and np.isfinite(loss)
+
+    def L(**kw):
+        a = dict(Ws=Ws, bs=bs, aWs=aWs, abs_=abs_, x=x)
+        a.update(kw)
+        return orc.chained_scale_fwd_bwd(a["x"], a["Ws"], a["bs"], a["aWs"], a["abs_"], grains, final_len, tgt)[1]
+    eps = 1e-6
+
+    def check(name, arrs, grads, i, pos):
+        p_, m_ = [a.copy() for a in arrs], [a.copy() for a in arrs]
+        p_[i][pos] += eps
+        m_[i][pos] -= eps
+        num = (L(**{name: p_}) - L(**{name: m_})) / (2 * eps)
+        assert abs(grads[i][pos] - num) <= 2e-9 + 1e-4 * abs(num), (name, i, pos, grads[i][pos], num)
+    for i in range(n):
+        for _ in range(3):
+            check("Ws", Ws, dWs, i, (int(rng.integers(4 * H)), int(rng.integers(H + I))))
+        check("bs", bs, dbs, i, (int(rng.integers(4 * H)),))
+    for i in range(len(grains)):
+        for _ in range(3):
+            check("aWs", aWs, daWs, i, (int(rng.integers(I)), int(rng.integers(grains[i] * I))))
+        check("abs_", abs_, dabs, i, (int(rng.integers(I)),))
+    for _ in range(5):
+        pos = (int(rng.integers(Tn)), int(rng.integers(I)))
+        xp, xm = x.copy(), x.copy()
+        xp[pos] += eps
+        xm[pos] -= eps
+        num = (L(x=xp) - L(x=xm)) / (2 * eps)
+        assert abs(dx[pos] - num) <= 2e-9 + 1e-4 * abs(num), (pos, dx[pos], num)
