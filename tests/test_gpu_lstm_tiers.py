@@ -43,6 +43,25 @@ def test_lstm_cell_kernels(orc):
     ctx.close()
 
 
+def test_lstm_cell_kernels_reject_bad_arguments():
+    """NULL buffers and non-positive or oversize extents come back as an error status with a message; the context stays
+    usable (the reference's FFI surface returns nothing at all, lib/cuda/cudacaller.dart:25-60)."""
+    from flutter_ml_b200 import _lib
+    ctx = _lib.Context(precision=_lib.PREC_FP32)
+    B, H = 4, 8
+    pre, cp = ctx.zeros(B, 4 * H), ctx.zeros(B, H)
+    gates, c, h = ctx.empty(B, 4 * H), ctx.empty(B, H), ctx.empty(B, H)
+    for bad in ((None, cp, gates, c, h, B, H), (pre, cp, gates, c, None, B, H), (pre, cp, gates, c, h, 0, H), (pre, cp, gates, c, h, B, -1),
+                (pre, cp, gates, c, h, 1 << 20, 1 << 20)):
+        with pytest.raises(RuntimeError):
+            ctx.call("fml_lstm_cell_fwd", *bad)
+    with pytest.raises(RuntimeError):
+        ctx.call("fml_lstm_cell_bwd", gates, cp, c, None, None, None, cp, 0, B, H)      # no dpre
+    ctx.call("fml_lstm_cell_fwd", pre, cp, gates, c, h, B, H)                            # still works
+    assert np.allclose(h.numpy(), 0.0) and ctx.device_status() == 0
+    ctx.close()
+
+
 @pytest.mark.parametrize("kind,cycles,B,Tn,H,I,prec", [
     ("multi", [3, 2], 4, 14, 32, 12, 1), ("multi", [2], 1, 9, 16, 5, 1), ("multi", [2, 2, 2], 3, 17, 8, 4, 2),
     ("dual", [4], 3, 13, 64, 8, 1), ("dual", [1], 2, 6, 16, 4, 2), ("multi", [3, 2], 5, 14, 32, 12, 0)])
