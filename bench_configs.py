@@ -175,7 +175,7 @@ def config4_lstm(ctx):
         ctx.check(ctx.lib.fml_lstm_fwd(ctx.h, ctypes.byref(d)))
         ctx.call("fml_mse", h_last, target, dh, loss, B * H, float(B), launches=2)
         ctx.check(ctx.lib.fml_lstm_bwd(ctx.h, ctypes.byref(d), dh.ptr, dW.ptr, db.ptr, None, scratch.ptr))
-        ctx.launches += 2 * Tn + 12   # forward: regrouping, input projection, ONE recurrence kernel; backward: 2 per step + the weight-gradient products
+        ctx.launches += Tn + 11   # forward: regrouping, input projection, ONE recurrence kernel; backward: ONE fused launch per step + the weight-gradient products
     ms, launches = _timed(ctx, step)
     fwd_ms, _ = _timed(ctx, lambda: ctx.check(ctx.lib.fml_lstm_fwd(ctx.h, ctypes.byref(d))))
     bwd_ms, _ = _timed(ctx, lambda: ctx.check(ctx.lib.fml_lstm_bwd(ctx.h, ctypes.byref(d), dh.ptr, dW.ptr, db.ptr, None, scratch.ptr)))

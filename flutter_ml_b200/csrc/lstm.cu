@@ -4,8 +4,9 @@
 //   - each timestep is ONE tensor-core GEMM h_{t-1}.Wh^T whose epilogue adds the input projection,
 //     applies the four gate nonlinearities and the cell update, and writes gates, c_t and h_t
 //     (a thread owns one batch row and 32 consecutive columns = 8 hidden units x 4 gates);
-//   - BPTT is one gate-gradient kernel and one small (split-K) GEMM per step, then the weight
-//     gradients of all timesteps as two large GEMMs, regrouped back to the reference's row order.
+//   - BPTT is ONE fused launch per step in TF32 mode (gate derivatives + product + sum over the K split,
+//     lstm_bwd_tc.cu; other modes and shapes: one gate-gradient kernel and one small split-K GEMM per step), then the
+//     weight gradients of all timesteps as two large GEMMs, regrouped back to the reference's row order.
 // Saved gates are [T][B][H][4] (f, i, c~, o per hidden unit).
 //
 // Reference: LSTMLayer.forward lib/layertypes/lstmLayer.dart:112-150.  Gate order f,i,c~,o
@@ -21,6 +22,9 @@ int32_t fml_lstm_fwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const floa
 // the backward recurrence of all time steps in one cooperative kernel (lstm_bwd_tc.cu); 1 = not eligible / launch refused
 int32_t fml_lstm_bwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const float* Wi, const float* dh_last, float* dpre,
                                 float* dh_a, float* dh_b);
+// steps T-1 .. 1 of the backward recurrence as one fused launch per step (lstm_bwd_tc.cu); 1 = shape not eligible
+int32_t fml_lstm_bwd_steps(fml_ctx* ctx, const fml_lstm_desc* d, const float* Wi, const float* dh_last, float* dpre, float* work,
+                           float** dh_final, float** dc_final);
 
 namespace {
 
@@ -250,8 +254,8 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
   {
     // Opt-in (FML_LSTM_BWD_SINGLE_KERNEL=1, read at every call): the whole recurrence as one cooperative kernel that sums
     // the split contraction in a fixed order, so dpre, dW, db come out bit for bit the same on every run.  It is NOT the
-    // default because it is slower than the two launches per step below (24 us against 12 us per step at H 512, B 128:
-    // measured phase by phase, see lstm_bwd_tc.cu), whose K split adds its partial sums with atomics in no fixed order.
+    // default because it is slower than the launch per step below (24 us against 8 us per step at H 512, B 128:
+    // measured phase by phase, see lstm_bwd_tc.cu), which sums the K split's partial tiles in no fixed order.
     const char* e = getenv("FML_LSTM_BWD_SINGLE_KERNEL");
     if (e && atoi(e) != 0 && ctx->precision == FML_PREC_TF32) {
       const int32_t pr = fml_lstm_bwd_persistent(ctx, d, Wi, dh_last, dpre, dh, dc);   // dh, dc: its two dh buffers
@@ -262,11 +266,38 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
       recurrence_done = pr == 0;
     }
   }
-  if (!recurrence_done) {
+  // Default for TF32 at batch <= 128 and H in {128, 256, 384, 512}: one fused launch per step (gate derivatives, product
+  // and the sum over the K split in one kernel, consecutive steps chained by programmatic dependent launch);
+  // FML_LSTM_BWD_FUSED=0 keeps the gate kernel + K-split product per step below (diagnostics, read at every call).
+  int t_first = T - 1;
+  float* work = nullptr;
+  if (!recurrence_done && ctx->precision == FML_PREC_TF32) {
+    const char* e = getenv("FML_LSTM_BWD_FUSED");
+    if (!(e && atoi(e) == 0)) {
+      rc = temp_alloc(ctx, (size_t)5 * bh, &work);
+      if (rc) {
+        cudaFreeAsync(Wi, ctx->stream);
+        return rc;
+      }
+      float *dh_f = nullptr, *dc_f = nullptr;
+      const int32_t pr = fml_lstm_bwd_steps(ctx, d, Wi, dh_last, dpre, work, &dh_f, &dc_f);
+      if (pr < 0) {
+        cudaFreeAsync(work, ctx->stream);
+        cudaFreeAsync(Wi, ctx->stream);
+        return pr;
+      }
+      if (pr == 0) {   // only dpre_0 is left: the gate kernel on the buffers the chain ended in
+        dh = dh_f;
+        dc = dc_f;
+        t_first = 0;
+      }
+    }
+  }
+  if (!recurrence_done && t_first == T - 1) {
     cudaMemcpyAsync(dh, dh_last, bh * 4, cudaMemcpyDeviceToDevice, ctx->stream);
     cudaMemsetAsync(dc, 0, bh * 4, ctx->stream);
   }
-  for (int t = T - 1; t >= 0 && rc == FML_OK && !recurrence_done; t--) {
+  for (int t = t_first; t >= 0 && rc == FML_OK && !recurrence_done; t--) {
     {
       cudaLaunchConfig_t cfg = {};
       cudaLaunchAttribute attr[1];
@@ -322,6 +353,7 @@ int32_t fml_lstm_bwd(fml_ctx* ctx, const fml_lstm_desc* d, const float* dh_last,
     gx.C = dx; gx.ldc = I;
     rc = fml_gemm(ctx, &gx);
   }
+  if (work) cudaFreeAsync(work, ctx->stream);
   cudaFreeAsync(Wi, ctx->stream);
   if (rc) return rc;
   FML_LAUNCH_CHECK(ctx, "lstm backward");

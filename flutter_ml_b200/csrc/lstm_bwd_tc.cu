@@ -1,4 +1,4 @@
-// LSTM backward recurrence (BPTT) as ONE cooperative kernel for all time steps.
+// LSTM backward recurrence (BPTT): ONE cooperative kernel for all time steps (opt-in), and one fused launch per step (default).
 //
 // Per step the recurrence needs dh_{t-1} = dpre_t . Wh with dpre_t [B x 4H] built from dh_t, the carried dc and the
 // saved gates and cells (the chain matVecMul / sigmoid / tanh / multiply backward of lib/layertypes/lstmLayer.dart:119-146
@@ -24,7 +24,8 @@
 // 0.8 us: 24 us per step, against 12 us for the two dependent launches per step it was meant to replace.  Even with the
 // gate and cell loads moved in front of the grid barrier the sum over the cluster and the two barriers leave about 11 us.
 // The kernel is therefore OPT-IN (FML_LSTM_BWD_SINGLE_KERNEL=1): what it offers is not speed but a recurrence whose
-// result is bit for bit reproducible.
+// result is bit for bit reproducible.  The DEFAULT is lstm_bwd_step_kernel further down: the same tiling as one launch
+// per step, 8.2 us per step (1.05 ms for the 127 products of H 512, B 128, T 128).
 // Every wait is bounded (mbarriers, also across the cluster: arrivals on peers' barriers instead of barrier.cluster
 // inside the loop); the two cluster-wide hardware barriers, after set-up and before exit, are reached by every thread on
 // every path.  Requirements: TF32 mode, batch <= 128, H a multiple of 128 and at most 512, a device that can place
@@ -306,6 +307,189 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const LstmBP
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// One time step of the backward recurrence as ONE launch: dpre_t from dh_t, dc and the saved gates and cells, and
+// dh_{t-1} = dpre_t . Wh, with the launches of consecutive steps chained by programmatic dependent launch.
+//   - grid = (H / 128) column blocks x 16 slices of the contraction, as above; every CTA forms the dpre tile of ITS slice
+//     itself (lane = hidden unit, warp = 16 batch rows), so no launch separates the gate derivatives from the product;
+//   - everything that does not depend on the previous step is done BEFORE griddepcontrol.wait, while the previous step
+//     still runs on other SMs: barriers, tensor memory, the Wh slice (a bulk tensor copy) and the saved gates and cells
+//     of all sixteen rows of a thread (registers);
+//   - after the wait: dh_t and dc (L2), the dpre tile into shared memory in the tensor core's operand layout, sixteen
+//     MMAs, the partial [128 x 128] copied from tensor memory into a swizzled staging tile, and four bulk tensor
+//     REDUCE-ADD copies into dh_{t-1}: the memory system sums the sixteen slices, whole 128-byte lines at a time;
+//   - dh rotates through THREE buffers: step t reads buffer t % 3, adds into (t - 1) % 3 and zeroes (t + 1) % 3 (the
+//     target of step t - 1, last read by step t + 1, which has completed when this step's wait returns).
+// The sums of the slices arrive in no fixed order (as with the K-split product this replaces).
+constexpr int LS_THREADS = 320;
+
+struct LstmStepParams {
+  int B, H, kc;
+  const float* gates;     // [B][H][4] of this step
+  const float* c_prev;    // [B][H] cells before this step
+  const float* c_cur;     // [B][H] cells after this step
+  const float* dh_in;     // [B][H]
+  const float* dc_in;     // [B][H]
+  float* dc_out;          // [B][H], written by column block 0
+  float* dh_zero;         // [B][H] the buffer the NEXT launch accumulates into
+  float* dpre;            // [B][4H] of this step, written by column block 0
+  int* status;
+};
+
+enum { S_WFULL = 0, S_AFULL = 1, S_ACCFULL = 2, S_COUNT = 3 };
+
+__global__ void __launch_bounds__(LS_THREADS, 1)
+lstm_bwd_step_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmDH, const LstmStepParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t w_bytes = (uint32_t)p.kc * NT * 4;     // Wh slice: kc/32 chunks of 32 rows x 128 columns
+  const uint32_t off_a = w_bytes;                       // A tile (kc/32 k-blocks of 16 KB), then reused as the staging tile (64 KB)
+  const uint32_t off_bar = off_a + 65536u;
+  auto bar = [&](int i) { return smem_base + off_bar + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + off_bar + 8 * S_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x % KS;                   // which sixteenth of the contraction
+  const int n = blockIdx.x / KS;                   // which 128 columns of dh
+  const int G = 4 * p.H;
+  const int k0 = r * p.kc;                         // first gate column of this CTA
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(S_WFULL), 1);
+    mbar_init(bar(S_AFULL), 8);
+    mbar_init(bar(S_ACCFULL), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // the next step's launch may begin its own set-up on the idle SMs from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the weights do not depend on the previous step
+      mbar_expect_tx(bar(S_WFULL), w_bytes);
+      for (int c = 0; c < p.kc / 32; c++) tma_load_5d(smem_base + c * (32 * NT * 4), &tmW, bar(S_WFULL), 0, k0 + 32 * c, n * (NT / 32), 0, 0);
+    }
+    // this warp zeroes the CTA's share of the buffer the next launch adds into (a buffer the previous launch read)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int n4 = (p.B * p.H) >> 2;
+    float4* z = reinterpret_cast<float4*>(p.dh_zero);
+    for (int i = blockIdx.x * 32 + lane; i < n4; i += gridDim.x * 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      bool ok = mbar_wait(bar(S_WFULL), 0, abort_flag, p.status, 71);
+      ok = ok && mbar_wait(bar(S_AFULL), 0, abort_flag, p.status, 72);
+      if (ok) {
+        tc_fence_after();
+        for (int c = 0; c < p.kc / 32; c++) {
+          const uint64_t ad = make_smem_desc(smem_base + off_a + c * 16384, 16u, 1024u, 2u);
+          const uint64_t bd = make_smem_desc(smem_base + c * (32 * NT * 4), 4096u, 512u, 1u);
+#pragma unroll
+          for (int k = 0; k < 4; k++) umma_tf32(tmem_base, ad + 2u * k, bd + 64u * k, idesc, (c | k) ? 1u : 0u);
+        }
+        umma_commit(bar(S_ACCFULL));
+      }
+    }
+  } else {
+    const int cw = warp - 2;                        // 0..7
+    const int nuc = p.kc >> 2;                      // hidden units of this CTA (32 at H = 512)
+    const bool unit_ok = lane < nuc;
+    const int u = (k0 >> 2) + lane;                 // this lane's hidden unit
+    uint8_t* a_tile = smem_gen + off_a + (lane >> 3) * 16384;   // k-block of this lane's unit (8 units = 32 columns each)
+    const int chunk = lane & 7;                                  // 16-byte chunk of the unit inside its k-block row
+    // saved state of this thread's sixteen (row, unit) elements: independent of the previous step
+    float4 gt[ROWS_PER_WARP];
+    float cpv[ROWS_PER_WARP], ccv[ROWS_PER_WARP];
+#pragma unroll
+    for (int j = 0; j < ROWS_PER_WARP; j++) {
+      const int rw = cw * ROWS_PER_WARP + j;
+      const bool live = unit_ok && rw < p.B;
+      const long long o = (long long)rw * p.H + u;
+      gt[j] = live ? __ldg(reinterpret_cast<const float4*>(p.gates) + o) : make_float4(0.f, 0.f, 0.f, 0.f);
+      cpv[j] = live ? __ldg(p.c_prev + o) : 0.f;
+      ccv[j] = live ? __ldg(p.c_cur + o) : 0.f;
+    }
+    // tanh of the cell does not depend on the previous step either
+#pragma unroll
+    for (int j = 0; j < ROWS_PER_WARP; j++) ccv[j] = fml_tanh_ref(ccv[j]);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float dhv[ROWS_PER_WARP], dcv[ROWS_PER_WARP];
+#pragma unroll
+    for (int j = 0; j < ROWS_PER_WARP; j++) {
+      const int rw = cw * ROWS_PER_WARP + j;
+      const bool live = unit_ok && rw < p.B;
+      const long long o = (long long)rw * p.H + u;
+      dhv[j] = live ? __ldcg(p.dh_in + o) : 0.f;   // summed by the previous launch in L2
+      dcv[j] = live ? __ldcg(p.dc_in + o) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < ROWS_PER_WARP; j++) {
+      const int rw = cw * ROWS_PER_WARP + j;
+      const float f = gt[j].x, ig = gt[j].y, g = gt[j].z, o = gt[j].w;
+      const float tc = ccv[j];
+      const float d_o = dhv[j] * tc;
+      const float dct = dcv[j] + dhv[j] * o * (1.f - tc * tc);
+      const float4 dp = make_float4(dct * cpv[j] * (f * (1.f - f)), dct * g * (ig * (1.f - ig)), dct * ig * (1.f - g * g),
+                                    d_o * (o * (1.f - o)));
+      if (unit_ok) {
+        *reinterpret_cast<float4*>(a_tile + rw * 128 + ((chunk ^ (rw & 7)) << 4)) = dp;   // rows >= B: zeros
+        if (n == 0 && rw < p.B) {
+          *reinterpret_cast<float4*>(p.dpre + (long long)rw * G + k0 + lane * 4) = dp;
+          p.dc_out[(long long)rw * p.H + u] = dct * f;
+        }
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores of the A tile -> tensor core reads
+    mbar_arrive_warp(bar(S_AFULL));
+    // the partial product [128 x 128] -> staging tile (four boxes of 32 columns, 128-byte swizzle) -> reduce-add into dh
+    const int q4 = warp & 3, half = cw >> 2;
+    const int row = q4 * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
+    const bool ok = mbar_wait_warp(bar(S_ACCFULL), 0, abort_flag, p.status, 73);
+    if (ok) {
+      tc_fence_after();
+      uint32_t v[32];
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        tmem_ld32(lane_addr + half * 64 + c * 32, v);
+        tmem_ld_wait();
+        uint8_t* dst = smem_gen + off_a + (half * 2 + c) * 16384 + row * 128;
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          *reinterpret_cast<float4*>(dst + ((i ^ (row & 7)) << 4)) =
+              make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight compute warps; reached on every path
+    if (ok && threadIdx.x == 64) {
+#pragma unroll
+      for (int b = 0; b < 4; b++) tma_reduce_add_4d(&tmDH, smem_base + off_a + b * 16384, n * NT + b * 32, 0, 0, 0);
+      tma_store_commit();
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // performed, not only read: the next launch reads the sums
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+  }
+}
+
 }  // namespace
 
 // Runs the recurrence of fml_lstm_bwd (dpre of every step and the dh chain) in one kernel.  dh_a and dh_b are two
@@ -387,5 +571,61 @@ int32_t fml_lstm_bwd_persistent(fml_ctx* ctx, const fml_lstm_desc* d, const floa
     cudaGetLastError();
     return 1;
   }
+  return FML_OK;
+}
+
+// The recurrence of fml_lstm_bwd as one launch per time step (lstm_bwd_step_kernel), steps T-1 .. 1; the caller forms
+// dpre_0 from the returned buffers.  work holds five [B x H] buffers (three for dh, two for dc).  On success *dh_final
+// and *dc_final are the buffers holding dh_0 and the dc flowing into step 0.  Returns 1 when the shape is not eligible.
+int32_t fml_lstm_bwd_steps(fml_ctx* ctx, const fml_lstm_desc* d, const float* Wi, const float* dh_last, float* dpre, float* work,
+                           float** dh_final, float** dc_final) {
+  FML_ENTER(ctx);
+  const int T = d->T, B = d->B, H = d->H, I = d->I, Z = H + I;
+  if (B > 128 || H % NT != 0 || H > 512 || T < 1) return 1;
+  const int kc = 4 * H / KS;
+  if (kc % 32 != 0 || kc > 128) return 1;
+  const int n_cta = (H / NT) * KS;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al16(Wi) || !al16(d->gates) || !al16(d->cells) || !al16(dpre) || !al16(work) || Z % 4 != 0) return 1;
+  const size_t smem = (size_t)kc * NT * 4 + 65536 + 8 * S_COUNT + 64 + 1024;
+  const long long bh = (long long)B * H, b4h = 4 * bh;
+  float* dh[3] = {work, work + bh, work + 2 * bh};
+  float* dc[2] = {work + 3 * bh, work + 4 * bh};
+  CUtensorMap tmW, tmDH[3];
+  int32_t rc;
+  if ((rc = fml_tc_make_tmap(ctx, Wi, H, 4 * H, Z, 1, 1, 0, 0, 32, 32, true, NT / 32, &tmW))) return rc;
+  for (int i = 0; i < 3; i++)
+    if ((rc = fml_tc_make_tmap(ctx, dh[i], H, B, H, 1, 1, 0, 0, 32, 128, false, 0, &tmDH[i]))) return rc;
+  FML_ONCE_PER_DEVICE(ctx, {
+    FML_CUDA(ctx, cudaFuncSetAttribute(lstm_bwd_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+  });
+  FML_CUDA(ctx, cudaMemsetAsync(work, 0, (size_t)5 * bh * 4, ctx->stream));
+  FML_CUDA(ctx, cudaMemcpyAsync(dh[(T - 1) % 3], dh_last, (size_t)bh * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  for (int t = T - 1; t >= 1; t--) {
+    LstmStepParams p;
+    p.B = B; p.H = H; p.kc = kc;
+    p.gates = d->gates + t * b4h;
+    p.c_prev = d->cells + t * bh;
+    p.c_cur = d->cells + (t + 1) * bh;
+    p.dh_in = dh[t % 3];
+    p.dh_zero = dh[(t + 1) % 3];
+    p.dc_in = dc[t & 1];
+    p.dc_out = dc[(t - 1) & 1];
+    p.dpre = dpre + t * b4h;
+    p.status = ctx->d_status;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(n_cta);
+    cfg.blockDim = dim3(LS_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FML_CUDA(ctx, cudaLaunchKernelEx(&cfg, lstm_bwd_step_kernel, tmW, tmDH[(t - 1) % 3], p));
+  }
+  *dh_final = dh[0];
+  *dc_final = dc[0];
   return FML_OK;
 }

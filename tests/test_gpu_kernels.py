@@ -701,6 +701,59 @@ def test_tf32_product_is_the_exact_product_of_truncated_operands(ctx, M, N, K, t
     assert -9e-4 <= shrink <= -5e-4, shrink
 
 
+@pytest.mark.parametrize("T,B,I,H", [(6, 128, 16, 256), (5, 70, 8, 512), (3, 3, 4, 128), (1, 9, 4, 128), (9, 33, 12, 384), (40, 128, 8, 512)])
+def test_lstm_fused_step_backward_recurrence(orc, T, B, I, H):
+    """The default backward recurrence in TF32 mode at batch <= 128 and H a multiple of 128 up to 512: one launch per step
+    that forms the gate derivatives, multiplies by Wh and sums the sixteen slices of the contraction with bulk reduce-add
+    copies, the steps chained by programmatic dependent launch.  Against the oracle's BPTT (lstmLayer.dart:112-150 walked
+    backwards) for dW and db, and against the gate kernel + K-split product per step (FML_LSTM_BWD_FUSED=0) for the dpre of
+    every step: the same TF32 products of the same operands, summed in another order."""
+    import ctypes
+    import os
+    from flutter_ml_b200 import _lib
+    c = _lib.Context(precision=_lib.PREC_TF32)
+    rng = np.random.default_rng(100 * T + H + B + 1)
+    a = 1 / np.sqrt(H)
+    W = rng.uniform(-a, a, (4, H, H + I)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (4, H)).astype(np.float32)
+    x = rng.standard_normal((B, T, I)).astype(np.float32)
+    target = rng.standard_normal((B, H)).astype(np.float32)
+    h_ref, loss_ref, dW_ref, db_ref = orc.Ops(omp=True).lstm_fwd_bwd(w64(W), w64(b), w64(x), w64(target))
+    d = _lib.LstmDesc()
+    d.T, d.B, d.I, d.H = T, B, I, H
+    bufs = dict(W=c.upload(W), b=c.upload(b), x=c.upload(np.ascontiguousarray(x.transpose(1, 0, 2))),
+                gates=c.empty(T, B, 4 * H), cells=c.empty(T + 1, B, H), hs=c.empty(T + 1, B, H), xproj=c.empty(T * B, 4 * H))
+    for k, v in bufs.items():
+        setattr(d, k, v.ptr)
+    c.check(c.lib.fml_lstm_fwd(c.h, ctypes.byref(d)))
+    h_last = bufs["hs"].view(T * B * H, (B, H))
+    dh, loss = c.empty(B, H), c.zeros(1)
+    c.call("fml_mse", h_last, c.upload(target), dh, loss, B * H, float(B))
+    scratch = c.empty(T * B * 4 * H + 2 * B * H)
+    runs = {}
+    try:
+        for fused in ("1", "0"):
+            os.environ["FML_LSTM_BWD_FUSED"] = fused
+            dW_, db_, dx_ = c.zeros(4 * H, H + I), c.zeros(4 * H), c.empty(T * B, I)
+            c.check(c.lib.fml_lstm_bwd(c.h, ctypes.byref(d), dh.ptr, dW_.ptr, db_.ptr, dx_.ptr, scratch.ptr))
+            assert c.device_status() == 0
+            runs[fused] = (scratch.numpy()[:T * B * 4 * H].copy(), dW_.numpy().copy(), db_.numpy().copy(), dx_.numpy().copy())
+    finally:
+        os.environ.pop("FML_LSTM_BWD_FUSED", None)
+    dpre, dW_g, db_g, dx_g = runs["1"]
+    assert rel(dW_g.reshape(4, H, H + I), dW_ref) <= 2 * TOL_TF32
+    assert rel(db_g.reshape(4, H), db_ref) <= 2 * TOL_TF32
+    # step by step against the two-launch path (the last step first: it involves no product at all)
+    per = B * 4 * H
+    for t in range(T - 1, -1, -1):
+        r_t = rel(dpre[t * per:(t + 1) * per], runs["0"][0][t * per:(t + 1) * per])
+        # equal up to the order of the fp32 sums at the last step; each further step rounds the slightly different dpre
+        # to TF32 again, so the two chains drift apart by a few 1e-6 per step (measured 2.1e-5 after eight)
+        assert r_t <= 1e-5 * (T - t), (t, r_t)
+    assert rel(dx_g, runs["0"][3]) <= 1e-5 * T
+    c.close()
+
+
 @pytest.mark.parametrize("T,B,I,H", [(6, 128, 16, 256), (5, 70, 8, 512), (3, 3, 4, 128), (1, 9, 4, 128), (9, 33, 12, 384)])
 def test_lstm_single_kernel_backward_recurrence(orc, T, B, I, H):
     """The opt-in cooperative backward kernel (TF32 mode, batch <= 128, H a multiple of 128 up to 512: the contraction split
