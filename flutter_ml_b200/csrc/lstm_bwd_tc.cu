@@ -331,7 +331,9 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const LstmBP
 // the gate kernel and the K-split product as two launches.  Storing dpre and dc AFTER the hand-over to the product, and
 // sharing those stores among the column blocks, did not shorten the step (7.4 us): the hand-over waits for the slowest
 // warp's loads either way.
-constexpr int LS_THREADS = 320;
+constexpr int LS_WARPS = 16;                       // compute warps: 8 batch rows each in the dpre phase, one 32-column box each in the epilogue
+constexpr int LS_ROWS = 128 / LS_WARPS;
+constexpr int LS_THREADS = 32 * (2 + LS_WARPS);    // + weight copy / zeroing warp, issuer warp
 
 struct LstmStepParams {
   int B, H, kc;
@@ -367,7 +369,7 @@ lstm_bwd_step_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(bar(S_WFULL), 1);
-    mbar_init(bar(S_AFULL), 8);
+    mbar_init(bar(S_AFULL), LS_WARPS);
     mbar_init(bar(S_ACCFULL), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -412,18 +414,18 @@ lstm_bwd_step_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
       }
     }
   } else {
-    const int cw = warp - 2;                        // 0..7
+    const int cw = warp - 2;                        // 0..15
     const int nuc = p.kc >> 2;                      // hidden units of this CTA (32 at H = 512)
     const bool unit_ok = lane < nuc;
     const int u = (k0 >> 2) + lane;                 // this lane's hidden unit
     uint8_t* a_tile = smem_gen + off_a + (lane >> 3) * 16384;   // k-block of this lane's unit (8 units = 32 columns each)
     const int chunk = lane & 7;                                  // 16-byte chunk of the unit inside its k-block row
-    // saved state of this thread's sixteen (row, unit) elements: independent of the previous step
-    float4 gt[ROWS_PER_WARP];
-    float cpv[ROWS_PER_WARP], ccv[ROWS_PER_WARP];
+    // saved state of this thread's eight (row, unit) elements: independent of the previous step
+    float4 gt[LS_ROWS];
+    float cpv[LS_ROWS], ccv[LS_ROWS];
 #pragma unroll
-    for (int j = 0; j < ROWS_PER_WARP; j++) {
-      const int rw = cw * ROWS_PER_WARP + j;
+    for (int j = 0; j < LS_ROWS; j++) {
+      const int rw = cw * LS_ROWS + j;
       const bool live = unit_ok && rw < p.B;
       const long long o = (long long)rw * p.H + u;
       gt[j] = live ? __ldg(reinterpret_cast<const float4*>(p.gates) + o) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -432,20 +434,20 @@ lstm_bwd_step_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
     }
     // tanh of the cell does not depend on the previous step either
 #pragma unroll
-    for (int j = 0; j < ROWS_PER_WARP; j++) ccv[j] = fml_tanh_ref(ccv[j]);
+    for (int j = 0; j < LS_ROWS; j++) ccv[j] = fml_tanh_ref(ccv[j]);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    float dhv[ROWS_PER_WARP], dcv[ROWS_PER_WARP];
+    float dhv[LS_ROWS], dcv[LS_ROWS];
 #pragma unroll
-    for (int j = 0; j < ROWS_PER_WARP; j++) {
-      const int rw = cw * ROWS_PER_WARP + j;
+    for (int j = 0; j < LS_ROWS; j++) {
+      const int rw = cw * LS_ROWS + j;
       const bool live = unit_ok && rw < p.B;
       const long long o = (long long)rw * p.H + u;
       dhv[j] = live ? __ldcg(p.dh_in + o) : 0.f;   // summed by the previous launch in L2
       dcv[j] = live ? __ldcg(p.dc_in + o) : 0.f;
     }
 #pragma unroll
-    for (int j = 0; j < ROWS_PER_WARP; j++) {
-      const int rw = cw * ROWS_PER_WARP + j;
+    for (int j = 0; j < LS_ROWS; j++) {
+      const int rw = cw * LS_ROWS + j;
       const float f = gt[j].x, ig = gt[j].y, g = gt[j].z, o = gt[j].w;
       const float tc = ccv[j];
       const float d_o = dhv[j] * tc;
@@ -463,27 +465,24 @@ lstm_bwd_step_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores of the A tile -> tensor core reads
     mbar_arrive_warp(bar(S_AFULL));
     // the partial product [128 x 128] -> staging tile (four boxes of 32 columns, 128-byte swizzle) -> reduce-add into dh
-    const int q4 = warp & 3, half = cw >> 2;
+    const int q4 = warp & 3, box = cw >> 2;          // tcgen05.ld hands lanes 32 q4 .. 32 q4 + 31 to warp % 4 == q4
     const int row = q4 * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
     const bool ok = mbar_wait_warp(bar(S_ACCFULL), 0, abort_flag, p.status, 73);
     if (ok) {
       tc_fence_after();
       uint32_t v[32];
+      tmem_ld32(lane_addr + box * 32, v);
+      tmem_ld_wait();
+      uint8_t* dst = smem_gen + off_a + box * 16384 + row * 128;
 #pragma unroll
-      for (int c = 0; c < 2; c++) {
-        tmem_ld32(lane_addr + half * 64 + c * 32, v);
-        tmem_ld_wait();
-        uint8_t* dst = smem_gen + off_a + (half * 2 + c) * 16384 + row * 128;
-#pragma unroll
-        for (int i = 0; i < 8; i++)
-          *reinterpret_cast<float4*>(dst + ((i ^ (row & 7)) << 4)) =
-              make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-      }
+      for (int i = 0; i < 8; i++)
+        *reinterpret_cast<float4*>(dst + ((i ^ (row & 7)) << 4)) =
+            make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight compute warps; reached on every path
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * LS_WARPS) : "memory");   // the compute warps; reached on every path
     if (ok && threadIdx.x == 64) {
 #pragma unroll
       for (int b = 0; b < 4; b++) tma_reduce_add_4d(&tmDH, smem_base + off_a + b * 16384, n * NT + b * 32, 0, 0, 0);
