@@ -330,7 +330,9 @@ lstm_bwd_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const LstmBP
 // step to step (8.2 us per step for the whole backward pass, which also forms the weight gradients), against 12.2 us for
 // the gate kernel and the K-split product as two launches.  Storing dpre and dc AFTER the hand-over to the product, and
 // sharing those stores among the column blocks, did not shorten the step (7.4 us): the hand-over waits for the slowest
-// warp's loads either way.
+// warp's loads either way.  Sixteen compute warps instead of eight (eight rows per thread instead of sixteen) did: 7.0
+// -> 6.4 us from step to step.  Threads that own a row x FOUR units (16-byte loads of dh, dc and the cells, four times fewer
+// requests after the wait) were slower, 8.0 us: lane = hidden unit with 4-byte loads stays.
 constexpr int LS_WARPS = 16;                       // compute warps: 8 batch rows each in the dpre phase, one 32-column box each in the epilogue
 constexpr int LS_ROWS = 128 / LS_WARPS;
 constexpr int LS_THREADS = 32 * (2 + LS_WARPS);    // + weight copy / zeroing warp, issuer warp
